@@ -1,0 +1,39 @@
+"""The ``"native"`` target: this framework's own runtime.
+
+``build(sch, target="native", config=..., mesh=..., loss_fn=...)`` returns
+``(TrainEngine, engine)`` - the engine plays both the model and the optimizer
+role (``engine.train_batch``); with pipeline cuts it returns a
+``PipelineEngine`` running the 1F1B schedule over NCCL p2p.
+"""
+from __future__ import annotations
+
+from .registry import register_framework_dialect
+
+
+@register_framework_dialect("native", "runtime_engine")
+def init_native_engine(sch, model, config=None, mesh=None, loss_fn=None, dp_group=None,
+                       **kwargs):
+    from ..runtime.engine import TrainEngine
+    from ..runtime.pipeline_engine import PipelineEngine, PipelineModel
+
+    if isinstance(model, PipelineModel):
+        engine = PipelineEngine(model, config=config, mesh=mesh, loss_fn=loss_fn,
+                                tp_group=sch.group, **kwargs)
+        return engine, engine
+    engine = TrainEngine(model, config=config, mesh=mesh, tp_group=sch.group,
+                         dp_group=dp_group, loss_fn=loss_fn)
+    return engine, engine
+
+
+@register_framework_dialect("native", "pipeline_stage")
+def native_pipeline_stage(*args, **kwargs):
+    from ..runtime.pipeline_engine import PipelineStage
+
+    return PipelineStage(*args, **kwargs)
+
+
+@register_framework_dialect("native", "pipeline_engine")
+def native_pipeline_engine(*args, **kwargs):
+    from ..runtime.pipeline_engine import PipelineModel
+
+    return PipelineModel(*args, **kwargs)

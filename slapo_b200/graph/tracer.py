@@ -1,0 +1,234 @@
+"""Hierarchy-preserving graph capture.
+
+``trace(model, ...)`` turns an ``nn.Module`` tree into a tree of
+``torch.fx.GraphModule`` objects that has the *same* shape as the module tree:
+each level is traced with its direct children (and every element of a child
+``ModuleList``) kept as opaque ``call_module`` nodes, and each child is then
+traced on its own and re-attached under the same name.  A level that cannot
+be traced (data-dependent control flow, ...) is left as the original module
+and a warning is logged, so scheduling of the rest of the model goes on.
+
+``flatten=True`` produces a single graph with dotted targets instead.
+
+Three capture engines are selectable by name:
+
+* ``"pytorch"`` - ``torch.fx`` symbolic tracing (default);
+* ``"huggingface"`` - accepted for source compatibility and served by the same
+  engine (``transformers.utils.fx`` no longer exists); ``concrete_args`` are
+  the forward arguments to freeze, lower levels freeze every optional
+  argument their call site leaves out;
+* ``"dynamo"`` - ``torch.export`` capture (always flat).
+
+Parity: slapo/tracer.py:150-272 (hierarchical tracing), :24-25,:511-520
+(leaf rule), :275-667 (entry point) of the reference.
+"""
+from __future__ import annotations
+
+import inspect
+import traceback
+
+import torch
+from torch import fx, nn
+
+from ..logger import get_logger
+
+logger = get_logger("tracer")
+
+
+def is_fx_tracing() -> bool:
+    """True while an fx symbolic trace is running (works on every torch 2.x)."""
+    try:
+        from torch.fx._symbolic_trace import is_fx_tracing as _f
+
+        return bool(_f())
+    except Exception:  # pragma: no cover
+        return False
+
+
+class HierTracer(fx.Tracer):
+    """fx tracer with name/class based leaf rules.
+
+    A module is a leaf when ``module.traceable is False``, when its qualified
+    name is listed in ``leaf_modules``, when an entry of ``leaf_modules`` is a
+    substring of its class name, or by the stock fx rule (``torch.nn`` layers).
+    """
+
+    name = "pytorch"
+
+    def __init__(self, leaf_modules=None, forced_leaf_names=None):
+        super().__init__(param_shapes_constant=True)
+        self.leaf_modules = list(leaf_modules or [])
+        self.forced_leaf_names = set(forced_leaf_names or [])
+
+    def user_leaf(self, m: nn.Module, qualname: str) -> bool:
+        if getattr(m, "traceable", True) is False:
+            return True
+        cls = type(m).__name__
+        for pat in self.leaf_modules:
+            if isinstance(pat, type):
+                if isinstance(m, pat):
+                    return True
+            elif pat == qualname or (pat and pat in cls):
+                return True
+        return False
+
+    def is_leaf_module(self, m: nn.Module, module_qualified_name: str) -> bool:
+        if module_qualified_name in self.forced_leaf_names:
+            return True
+        if self.user_leaf(m, module_qualified_name):
+            return True
+        if isinstance(m, fx.GraphModule):
+            return False
+        return super().is_leaf_module(m, module_qualified_name)
+
+
+def _direct_child_names(root: nn.Module):
+    names = []
+    for key, child in root.named_children():
+        if isinstance(child, nn.ModuleList):
+            names += [f"{key}.{sub}" for sub, _ in child.named_children()]
+        else:
+            names.append(key)
+    return names
+
+
+def _fill_concrete_args(root, concrete_args, call_node):
+    """Values to specialise the trace of ``root`` on.
+
+    Top level: the user's ``concrete_args``.  Lower levels: every forward
+    parameter that the parent's call site does not bind and that has a
+    default is frozen at that default, so an optional input that is never
+    passed does not turn into a required placeholder."""
+    if call_node is None:
+        return dict(concrete_args or {})
+    sig = inspect.signature(root.forward)
+    params = [p for p in sig.parameters.values()
+              if p.kind not in (p.VAR_POSITIONAL, p.VAR_KEYWORD)]
+    bound = dict(zip((p.name for p in params), call_node.args))
+    bound.update(call_node.kwargs)
+    frozen = {}
+    for p in params:
+        if p.name in bound:
+            val = bound[p.name]
+            if val is None or isinstance(val, bool):
+                frozen[p.name] = val  # the call site passes a literal
+        elif p.default is not inspect.Parameter.empty:
+            frozen[p.name] = p.default
+    return frozen
+
+
+def _strip_specialisation_guards(graph: fx.Graph, frozen: dict):
+    """fx keeps a placeholder ``<name>_1`` plus an assert for every frozen
+    argument.  Give the placeholder its original name back (so keyword calls
+    keep working) and drop the guards, which would otherwise run on every
+    forward."""
+    if not frozen:
+        return
+    for node in list(graph.nodes):
+        if node.op != "placeholder":
+            continue
+        base = node.target[:-2] if node.target.endswith("_1") else None
+        if base not in frozen:
+            continue
+        node.target = base
+        work = list(node.users)
+        while work:
+            user = work.pop()
+            if user.op == "call_function" and (
+                    user.target is torch._assert
+                    or getattr(user.target, "__name__", "") == "_assert_is_none"):
+                graph.erase_node(user)
+            elif user.op == "call_function" and all(
+                    u.op == "call_function" and (u.target is torch._assert) for u in user.users):
+                for u in list(user.users):
+                    graph.erase_node(u)
+                graph.erase_node(user)
+
+
+def _get_submodule_or_none(root, target):
+    cur = root
+    for tok in target.split("."):
+        if not hasattr(cur, tok):
+            return None
+        cur = getattr(cur, tok)
+    return cur
+
+
+def _trace_level(root: nn.Module, *, leaf_modules, flatten, recursive, concrete_args,
+                 call_node=None):
+    if isinstance(root, fx.GraphModule):
+        return root
+    judge = HierTracer(leaf_modules)
+    forced = [] if flatten else _direct_child_names(root)
+    tracer = HierTracer(leaf_modules, forced)
+    try:
+        cargs = _fill_concrete_args(root, concrete_args, call_node)
+        graph = tracer.trace(root, concrete_args=cargs or None)
+    except Exception as err:  # untraceable level: keep the eager module
+        logger.debug(traceback.format_exc())
+        logger.warning("cannot trace %s (%s); left as an eager module",
+                       type(root).__name__, err)
+        return root
+
+    _strip_specialisation_guards(graph, cargs)
+    if flatten:
+        gm = fx.GraphModule(root, graph, class_name=type(root).__name__)
+    else:
+        pieces = {}
+        for node in graph.nodes:
+            if node.op == "call_module":
+                child = _get_submodule_or_none(root, node.target)
+                qual = node.target
+                if (recursive and child is not None and not judge.user_leaf(child, qual)
+                        and not fx.Tracer.is_leaf_module(judge, child, qual)):
+                    child = _trace_level(
+                        child, leaf_modules=leaf_modules, flatten=False, recursive=True,
+                        concrete_args=concrete_args, call_node=node)
+                pieces[node.target] = child
+            elif node.op == "get_attr":
+                pieces[node.target] = _get_submodule_or_none(root, node.target)
+        gm = fx.GraphModule(pieces, graph, class_name=type(root).__name__)
+    gm.graph.eliminate_dead_code()
+    gm.delete_all_unused_submodules()
+    gm.graph.lint()
+    gm.recompile()
+    # keep plain-data attributes (configs, flags) that schedules may read later
+    for key, val in vars(root).items():
+        if key.startswith("_") or key in ("training",) or hasattr(gm, key):
+            continue
+        if isinstance(val, (int, float, str, bool, tuple)) or val is None:
+            try:
+                setattr(gm, key, val)
+            except Exception:  # pragma: no cover
+                pass
+    gm.train(root.training)
+    return gm
+
+
+def _trace_dynamo(root, concrete_args):
+    example = (concrete_args or {}).get("example_inputs")
+    if example is None:
+        raise ValueError('the "dynamo" tracer needs concrete_args={"example_inputs": (...)}')
+    exported = torch.export.export(root, tuple(example), strict=False)
+    return exported.module()
+
+
+def trace(model: nn.Module, tracer: str = "pytorch", recursive: bool = True,
+          flatten: bool = False, leaf_modules=None, concrete_args=None, config=None,
+          **_unused):
+    """Capture ``model`` as a (tree of) GraphModule(s); see the module docstring.
+
+    Returns the original module unchanged when the top level cannot be traced.
+    """
+    if not isinstance(tracer, str):
+        raise NotImplementedError("custom tracer classes are not supported; pass a name")
+    if tracer == "dynamo":
+        return _trace_dynamo(model, concrete_args)
+    if tracer not in ("pytorch", "huggingface"):
+        raise ValueError(f"unknown tracer {tracer}")
+    return _trace_level(
+        model, leaf_modules=list(leaf_modules or []), flatten=flatten, recursive=recursive,
+        concrete_args=concrete_args)
+
+
+trace_module = trace

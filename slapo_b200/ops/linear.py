@@ -1,0 +1,142 @@
+"""Linear-layer variants that schedules swap in.
+
+* ``LinearWithSeparateBias`` - matmul then an explicit ``+ bias`` (what
+  ``decompose`` produces).
+* ``LinearWithSyncFunc`` - matmul -> collective -> ``+ bias`` for
+  row-parallel layers whose output is a partial sum.
+* ``LinearWithAct`` - matmul -> collective -> fused bias + activation.
+* ``LinearWithDropout`` - matmul -> collective -> fused bias + dropout.
+* ``FusedQKV`` - one projection producing q, k, v for the local heads.
+
+On CUDA the bias/activation/dropout tails run as single sm_100a kernels (see
+:mod:`slapo_b200.ops.functional`); on CPU they are plain PyTorch.
+
+Parity: slapo/op/linear.py:20-264 of the reference.
+"""
+from __future__ import annotations
+
+import torch
+import torch.nn.functional as F
+from torch import nn
+
+from . import functional as NF
+
+
+class LinearWithSeparateBias(nn.Linear):
+    def forward(self, x):
+        out = F.linear(x, self.weight, None)
+        return out + self.bias if self.bias is not None else out
+
+
+class LinearWithSyncFunc(nn.Linear):
+    """``F.linear(x, W) -> sync_fn -> + bias``."""
+
+    traceable = False
+
+    def __init__(self, in_features, out_features, bias=True, device=None, dtype=None,
+                 sync_fn=None):
+        super().__init__(in_features, out_features, bias, device, dtype)
+        self.sync_fn = sync_fn
+
+    def forward(self, x, skip_bias: bool = False):
+        """``skip_bias=True`` leaves the bias to the caller, which fuses it
+        into the kernel that follows (dropout / residual / LayerNorm)."""
+        out = F.linear(x, self.weight, None)
+        if self.sync_fn is not None:
+            out = self.sync_fn(out)
+        if self.bias is not None and not skip_bias:
+            out = out + self.bias
+        return out
+
+    @classmethod
+    def from_linear(cls, linear: nn.Linear, **kwargs):
+        """Same parameters (shared objects), new forward."""
+        new = cls(linear.in_features, linear.out_features, bias=linear.bias is not None,
+                  device="meta", **kwargs)
+        new.weight = linear.weight
+        if linear.bias is not None:
+            new.bias = linear.bias
+        return new
+
+    def _sync_repr(self):
+        fn = self.sync_fn
+        if fn is None:
+            return "None"
+        op = getattr(fn, "sync_op", None)
+        if op is not None:
+            kw = ", ".join(f"{k}={v}" for k, v in getattr(fn, "sync_kwargs", {}).items())
+            return f"{op}({kw})"
+        inner = getattr(fn, "func", fn)
+        text = getattr(inner, "__name__", repr(inner))
+        kws = getattr(fn, "keywords", None)
+        if kws:
+            text += "(" + ", ".join(f"{k}={v}" for k, v in kws.items() if k != "group") + ")"
+        return text
+
+    def extra_repr(self):
+        return f"{super().extra_repr()}, sync_fn={self._sync_repr()}"
+
+
+_ACTS = ("gelu", "gelu_new", "gelu_tanh", "gelu_pytorch_tanh", "relu")
+
+
+class LinearWithAct(LinearWithSyncFunc):
+    """Linear whose bias add and activation run as one kernel."""
+
+    def __init__(self, in_features, out_features, bias=True, act_fn="gelu", device=None,
+                 dtype=None, sync_fn=None):
+        super().__init__(in_features, out_features, bias, device, dtype, sync_fn)
+        if act_fn not in _ACTS:
+            raise NotImplementedError(f"unsupported activation {act_fn}")
+        self.act_fn = act_fn
+
+    def forward(self, x):
+        out = F.linear(x, self.weight, None)
+        if self.sync_fn is not None:
+            out = self.sync_fn(out)
+        return NF.bias_act(out, self.bias, self.act_fn)
+
+    def extra_repr(self):
+        return f"{super().extra_repr()}, act_fn={self.act_fn}"
+
+
+class LinearWithDropout(LinearWithSyncFunc):
+    """Linear whose bias add and dropout run as one kernel."""
+
+    def __init__(self, in_features, out_features, bias=True, p=0.5, inplace=False,
+                 device=None, dtype=None, sync_fn=None):
+        super().__init__(in_features, out_features, bias, device, dtype, sync_fn)
+        self.p = p
+
+    def forward(self, x):
+        out = F.linear(x, self.weight, None)
+        if self.sync_fn is not None:
+            out = self.sync_fn(out)
+        return NF.bias_dropout(out, self.bias, self.p, self.training)
+
+    def extra_repr(self):
+        return f"{super().extra_repr()}, p={self.p}"
+
+
+class FusedQKV(nn.Module):
+    """Fused q/k/v projection for ``num_heads // world_size`` local heads.
+
+    The weight rows are ordered ``[head][q|k|v][head_dim]``, so slicing axis 0
+    by the tensor-parallel size hands each rank whole heads."""
+
+    def __init__(self, hidden_size, num_heads, world_size=1, bias=True, device=None, dtype=None):
+        super().__init__()
+        if hidden_size % num_heads != 0 or num_heads % world_size != 0:
+            raise ValueError("hidden_size % num_heads and num_heads % world_size must be 0")
+        self.hidden_size = hidden_size
+        self.num_heads = num_heads
+        self.head_size = hidden_size // num_heads
+        self.world_size = world_size
+        self.fused_linear = nn.Linear(hidden_size, 3 * num_heads // world_size * self.head_size,
+                                      bias=bias, device=device, dtype=dtype)
+
+    def forward(self, hidden_states):
+        qkv = self.fused_linear(hidden_states)
+        new_shape = qkv.shape[:-1] + (self.num_heads // self.world_size, 3, self.head_size)
+        qkv = qkv.view(new_shape)
+        return qkv[..., 0, :], qkv[..., 1, :], qkv[..., 2, :]

@@ -1,0 +1,77 @@
+"""``checkpoint``: activation checkpointing of a module or a matched sub-graph.
+
+Parity: slapo/primitives/checkpoint.py:12-58 of the reference.
+"""
+from __future__ import annotations
+
+import inspect
+
+from torch import nn
+
+from ..checkpoint import checkpoint as checkpoint_fn
+from .base import Primitive, register_primitive
+
+
+class CheckPointWrapper(nn.Module):
+    """Runs the wrapped module under activation checkpointing.
+
+    Keyword arguments are bound to the wrapped forward's signature and passed
+    positionally (checkpointing with RNG replay is positional); a custom
+    ``order_args_fn(*args, **kwargs) -> list`` overrides the binding."""
+
+    traceable = False
+
+    def __init__(self, mod: nn.Module, order_args_fn=None):
+        super().__init__()
+        self.mod = mod
+        self.order_args_fn = order_args_fn
+        try:
+            self._sig = inspect.signature(mod.forward)
+        except (TypeError, ValueError):
+            self._sig = None
+
+    def _ordered(self, args, kwargs):
+        if self.order_args_fn is not None:
+            return list(self.order_args_fn(*args, **kwargs))
+        if not kwargs:
+            return list(args)
+        if self._sig is None:
+            raise ValueError("cannot order keyword arguments; pass order_args_fn")
+        bound = self._sig.bind(*args, **kwargs)
+        bound.apply_defaults()
+        ordered = []
+        for name, par in self._sig.parameters.items():
+            if par.kind is par.VAR_POSITIONAL:
+                ordered += list(bound.arguments.get(name, ()))
+            elif par.kind is par.VAR_KEYWORD:
+                if bound.arguments.get(name):
+                    raise ValueError("**kwargs cannot be checkpointed positionally")
+            else:
+                ordered.append(bound.arguments[name])
+        return ordered
+
+    def forward(self, *args, **kwargs):
+        return checkpoint_fn(self.mod, *self._ordered(args, kwargs))
+
+
+@register_primitive()
+class CheckpointPrimitive(Primitive):
+    """``sch.checkpoint()`` wraps this module; ``sch.checkpoint(subgraph)``
+    extracts the matched chain into its own module first and wraps that."""
+
+    @staticmethod
+    def name():
+        return "checkpoint"
+
+    @staticmethod
+    def apply(sch, subgraph=None, order_args_fn=None):
+        if subgraph is None:
+            if isinstance(sch.mod, CheckPointWrapper):
+                return
+            sch.replace(CheckPointWrapper(sch.mod, order_args_fn))
+            return
+        if len(subgraph) != 1:
+            raise ValueError("checkpoint takes exactly one matched sub-graph")
+        chain = subgraph[0] if isinstance(subgraph[0], list) else subgraph
+        gm = sch._construct_fx_graph(chain)
+        sch.replace(CheckPointWrapper(gm, order_args_fn), [chain], name="CheckPointWrapper")

@@ -1,0 +1,452 @@
+"""The native training engine: what ``build(sch, target="native")`` returns.
+
+It owns everything the reference leaves to DeepSpeed / Megatron:
+
+* **flat storage** - all parameters live in one contiguous buffer per dtype
+  (``p.data`` are views), gradients in a second one (``p.grad`` are views), so
+  the optimizer, the gradient-norm and every data-parallel collective are a
+  handful of launches over large 180-GB-class HBM buffers, never a Python
+  loop over tensors;
+* **mixed precision** - bf16 (or fp16/fp32) model parameters, fp32 master
+  weights and Adam moments;
+* **data parallelism, ZeRO-1 style** - the flat gradient buffer is cut into
+  buckets in *reverse* registration order (the order backward produces
+  them); as soon as a bucket's last gradient has been accumulated the bucket
+  is reduce-scattered on a side stream, overlapping the rest of backward.
+  Each data-parallel rank keeps master weights and moments only for its
+  1/dp slice of every bucket, updates that slice with the fused AdamW kernel
+  and all-gathers the updated parameters in place;
+* **tensor / sequence parallel awareness** - gradients of parameters that
+  are replicated over the TP group but computed from sequence-sharded
+  activations (tagged ``replicated_param`` by the schedules) are all-reduced
+  over the TP group; the global gradient norm counts TP-sharded parameters on
+  every rank and replicated ones once;
+* **device timing** - ``StepTimer`` brackets steps with CUDA events.
+
+It runs on CPU ranks (gloo) too, with PyTorch ops instead of the kernels,
+which is how the multi-rank logic is tested without GPUs.
+"""
+from __future__ import annotations
+
+import math
+from dataclasses import dataclass, field
+
+import torch
+import torch.distributed as dist
+from torch import nn
+
+from ..logger import get_logger
+from ..ops import native
+
+logger = get_logger("engine")
+
+
+@dataclass
+class EngineConfig:
+    lr: float = 1e-4
+    betas: tuple = (0.9, 0.999)
+    eps: float = 1e-8
+    weight_decay: float = 0.01
+    clip_grad: float = 1.0
+    bucket_mb: float = 64.0        # DP reduce-scatter bucket (launch-latency sized, not link sized)
+    zero: bool = True              # shard optimizer state over the DP group
+    overlap_comm: bool = True
+    grad_accum_steps: int = 1
+    lr_schedule: object = None     # callable(step) -> lr multiplier
+    profile: bool = False
+    extra: dict = field(default_factory=dict)
+
+    @classmethod
+    def from_dict(cls, cfg):
+        if cfg is None:
+            return cls()
+        if isinstance(cfg, cls):
+            return cfg
+        known = {f for f in cls.__dataclass_fields__}
+        cfg = dict(cfg)
+        # accept the DeepSpeed-style layout used by the reference examples
+        opt = cfg.pop("optimizer", None)
+        if isinstance(opt, dict):
+            params = opt.get("params", {})
+            for k in ("lr", "betas", "eps", "weight_decay"):
+                if k in params:
+                    cfg[k] = tuple(params[k]) if k == "betas" else params[k]
+        if "gradient_clipping" in cfg:
+            cfg["clip_grad"] = cfg.pop("gradient_clipping")
+        if "gradient_accumulation_steps" in cfg:
+            cfg["grad_accum_steps"] = cfg.pop("gradient_accumulation_steps")
+        kwargs = {k: v for k, v in cfg.items() if k in known}
+        extra = {k: v for k, v in cfg.items() if k not in known}
+        return cls(**kwargs, extra=extra)
+
+
+def _is_tp_sharded(p) -> bool:
+    return hasattr(p, "orig_shape") and tuple(p.orig_shape) != tuple(p.shape)
+
+
+class _Bucket:
+    __slots__ = ("start", "end", "pending", "n_params", "event", "handle")
+
+    def __init__(self, start):
+        self.start, self.end = start, start
+        self.pending = 0
+        self.n_params = 0
+        self.event = None
+        self.handle = None
+
+
+class TrainEngine:
+    """See the module docstring.  ``engine(*inputs)`` runs the forward,
+    ``engine.backward(loss)`` the backward, ``engine.step()`` the optimizer;
+    ``engine.train_batch(*inputs, **kw)`` does all three and returns the loss."""
+
+    def __init__(self, model: nn.Module, config=None, mesh=None, tp_group=None, dp_group=None,
+                 loss_fn=None):
+        self.model = model
+        self.cfg = EngineConfig.from_dict(config)
+        self.mesh = mesh
+        self.tp_group = tp_group if tp_group is not None else (mesh.tp_group if mesh else None)
+        self.dp_group = dp_group if dp_group is not None else (mesh.dp_group if mesh else None)
+        self.tp_size = mesh.tp_size if mesh else (dist.get_world_size(tp_group) if tp_group is not None else 1)
+        if mesh is not None:
+            self.dp_size, self.dp_rank = mesh.dp_size, mesh.dp_rank
+        elif dp_group is not None:
+            self.dp_size, self.dp_rank = dist.get_world_size(dp_group), dist.get_rank(dp_group)
+        else:
+            self.dp_size, self.dp_rank = 1, 0
+        self.loss_fn = loss_fn
+        self.step_count = 0
+        self.micro_step = 0
+        self.last_grad_norm = None
+        self._build_flat_storage()
+        self._build_optimizer_state()
+        self._install_grad_hooks()
+
+    # ------------------------------------------------------------------ #
+    def _build_flat_storage(self):
+        params, seen = [], set()
+        for p in self.model.parameters():
+            if p.requires_grad and id(p) not in seen:
+                seen.add(id(p))
+                params.append(p)
+        if not params:
+            raise ValueError("the model has no trainable parameter")
+        if any(p.is_meta for p in params):
+            raise RuntimeError("parameters are still on the meta device; build with init_weights")
+        self.device = params[0].device
+        self.param_dtype = params[0].dtype
+        if any(p.dtype != self.param_dtype for p in params):
+            raise ValueError("all trainable parameters must share one dtype")
+        # reverse registration order ~ the order in which backward finishes them
+        self.params = list(reversed(params))
+        align = 128 * max(self.dp_size, 1)  # elements; keeps every shard 256-byte aligned
+        bucket_elems = max(int(self.cfg.bucket_mb * 2**20 / params[0].element_size()), align)
+        self.buckets: list[_Bucket] = []
+        self.param_slices = []
+        offset = 0
+        bucket = _Bucket(0)
+        for p in self.params:
+            n = p.numel()
+            padded = (n + 7) // 8 * 8
+            if bucket.end - bucket.start > 0 and (bucket.end - bucket.start) + padded > bucket_elems:
+                offset = (offset + align - 1) // align * align
+                bucket.end = offset
+                self.buckets.append(bucket)
+                bucket = _Bucket(offset)
+            self.param_slices.append((offset, n, len(self.buckets)))
+            offset += padded
+            bucket.end = offset
+            bucket.n_params += 1
+        offset = (offset + align - 1) // align * align
+        bucket.end = offset
+        self.buckets.append(bucket)
+        self.total = offset
+        self.flat_param = torch.zeros(self.total, dtype=self.param_dtype, device=self.device)
+        self.flat_grad = torch.zeros(self.total, dtype=self.param_dtype, device=self.device)
+        self.sp_sync_params = []
+        for p, (off, n, _) in zip(self.params, self.param_slices):
+            view = self.flat_param[off:off + n].view(p.shape)
+            view.copy_(p.data)
+            p.data = view
+            p.grad = self.flat_grad[off:off + n].view(p.shape)
+            if getattr(p, "replicated_param", False) and self.tp_size > 1:
+                self.sp_sync_params.append(p)
+        self.n_params_local = sum(n for _, n, _ in self.param_slices)
+
+    def _shard_range(self, bucket):
+        if not (self.cfg.zero and self.dp_size > 1):
+            return bucket.start, bucket.end
+        per = (bucket.end - bucket.start) // self.dp_size
+        lo = bucket.start + self.dp_rank * per
+        return lo, lo + per
+
+    def _build_optimizer_state(self):
+        # this rank's slice of every bucket, packed back to back
+        self.shard_ranges = [self._shard_range(b) for b in self.buckets]
+        n_own = sum(hi - lo for lo, hi in self.shard_ranges)
+        self.master = torch.empty(n_own, dtype=torch.float32, device=self.device)
+        self.exp_avg = torch.zeros(n_own, dtype=torch.float32, device=self.device)
+        self.exp_avg_sq = torch.zeros(n_own, dtype=torch.float32, device=self.device)
+        self.grad_shard = None
+        if self.cfg.zero and self.dp_size > 1:
+            self.grad_shard = torch.zeros(n_own, dtype=self.param_dtype, device=self.device)
+        self.shard_offsets = []
+        pos = 0
+        for lo, hi in self.shard_ranges:
+            self.master[pos:pos + hi - lo].copy_(self.flat_param[lo:hi])
+            self.shard_offsets.append(pos)
+            pos += hi - lo
+        # weight-decay mask: no decay for 1-D tensors (biases, norm weights)
+        self.decay_mask = None
+        wd_flat = torch.zeros(self.total, dtype=torch.bool, device=self.device)
+        for p, (off, n, _) in zip(self.params, self.param_slices):
+            if p.dim() > 1 and not getattr(p, "no_weight_decay", False):
+                wd_flat[off:off + n] = True
+        self.decay_mask = torch.cat([wd_flat[lo:hi] for lo, hi in self.shard_ranges]).to(torch.uint8)
+        # norm bookkeeping: replicated-over-TP parameters are counted once
+        self.tp_dup_mask = None
+        if self.tp_size > 1:
+            dup = torch.zeros(self.total, dtype=torch.bool, device=self.device)
+            for p, (off, n, _) in zip(self.params, self.param_slices):
+                if not _is_tp_sharded(p):
+                    dup[off:off + n] = True
+            self.tp_dup_mask = torch.cat([dup[lo:hi] for lo, hi in self.shard_ranges])
+        self.comm_stream = torch.cuda.Stream() if self.device.type == "cuda" else None
+
+    def _install_grad_hooks(self):
+        self._overlap = (self.cfg.overlap_comm and self.dp_size > 1 and self.device.type == "cuda")
+        if not self._overlap:
+            return
+        for p, (_, _, b_idx) in zip(self.params, self.param_slices):
+            p.register_post_accumulate_grad_hook(self._make_hook(b_idx))
+
+    def _make_hook(self, b_idx):
+        def hook(_param):
+            if (self.micro_step + 1) % self.cfg.grad_accum_steps != 0:
+                return
+            bucket = self.buckets[b_idx]
+            bucket.pending += 1
+            if bucket.pending == bucket.n_params:
+                self._launch_bucket_reduce(b_idx)
+
+        return hook
+
+    # ------------------------------------------------------------------ #
+    def _launch_bucket_reduce(self, b_idx):
+        bucket = self.buckets[b_idx]
+        grad = self.flat_grad[bucket.start:bucket.end]
+        if self.comm_stream is not None:
+            self.comm_stream.wait_stream(torch.cuda.current_stream())
+            ctx = torch.cuda.stream(self.comm_stream)
+        else:
+            import contextlib
+
+            ctx = contextlib.nullcontext()
+        with ctx:
+            if self.cfg.zero:
+                pos = self.shard_offsets[b_idx]
+                lo, hi = self.shard_ranges[b_idx]
+                out = self.grad_shard[pos:pos + hi - lo]
+                dist.reduce_scatter_tensor(out, grad, op=dist.ReduceOp.AVG
+                                           if self.device.type == "cuda" else dist.ReduceOp.SUM,
+                                           group=self.dp_group)
+                if self.device.type != "cuda":
+                    out.div_(self.dp_size)
+            else:
+                dist.all_reduce(grad, group=self.dp_group)
+                grad.div_(self.dp_size)
+        bucket.pending = 0
+        bucket.handle = True
+
+    def _reduce_all_buckets(self):
+        for i, bucket in enumerate(self.buckets):
+            if bucket.handle is None:
+                self._launch_bucket_reduce(i)
+        if self.comm_stream is not None:
+            torch.cuda.current_stream().wait_stream(self.comm_stream)
+        for bucket in self.buckets:
+            bucket.handle = None
+            bucket.pending = 0
+
+    # ------------------------------------------------------------------ #
+    def __call__(self, *args, **kwargs):
+        return self.model(*args, **kwargs)
+
+    def backward(self, loss):
+        if self.cfg.grad_accum_steps > 1:
+            loss = loss / self.cfg.grad_accum_steps
+        loss.backward()
+        self.micro_step += 1
+
+    def _own_grad(self):
+        """This rank's reduced gradient slice as one flat view list."""
+        if self.grad_shard is not None:
+            return self.grad_shard
+        if len(self.shard_ranges) == 1 or not (self.cfg.zero and self.dp_size > 1):
+            return self.flat_grad  # ranges cover the whole buffer back to back
+        return torch.cat([self.flat_grad[lo:hi] for lo, hi in self.shard_ranges])
+
+    def _grad_norm(self, grad):
+        g = grad.float()
+        if self.tp_dup_mask is not None:
+            dup = self.tp_dup_mask
+            sq_shard = (g * (~dup)).pow(2).sum()
+            sq_dup = (g * dup).pow(2).sum()
+            parts = torch.stack([sq_shard, sq_dup])
+        else:
+            parts = torch.stack([g.pow(2).sum(), torch.zeros((), device=g.device)])
+        if self.cfg.zero and self.dp_size > 1:
+            dist.all_reduce(parts, group=self.dp_group)
+        if self.tp_size > 1:
+            shard_part = parts[0:1].clone()
+            dist.all_reduce(shard_part, group=self.tp_group)
+            total = shard_part[0] + parts[1]
+        else:
+            total = parts[0] + parts[1]
+        return total.sqrt()
+
+    def step(self):
+        """Synchronise gradients, clip, AdamW-update, re-gather parameters."""
+        if self.micro_step % self.cfg.grad_accum_steps != 0:
+            return False
+        # sequence-parallel: replicated parameters got partial gradients
+        if self.sp_sync_params:
+            flat = torch.cat([p.grad.reshape(-1) for p in self.sp_sync_params])
+            dist.all_reduce(flat, group=self.tp_group)
+            pos = 0
+            for p in self.sp_sync_params:
+                p.grad.copy_(flat[pos:pos + p.numel()].view_as(p.grad))
+                pos += p.numel()
+        if self.dp_size > 1:
+            self._reduce_all_buckets()
+        grad = self._own_grad()
+        self.step_count += 1
+        lr = self.cfg.lr
+        if self.cfg.lr_schedule is not None:
+            lr = lr * self.cfg.lr_schedule(self.step_count)
+        clip_coef = None
+        if self.cfg.clip_grad and self.cfg.clip_grad > 0:
+            norm = self._grad_norm(grad)
+            self.last_grad_norm = norm
+            clip_coef = torch.clamp(self.cfg.clip_grad / (norm + 1e-6), max=1.0)
+        self._adamw(grad, lr, clip_coef)
+        self._gather_params()
+        self.flat_grad.zero_()
+        return True
+
+    def _adamw(self, grad, lr, clip_coef):
+        b1, b2 = self.cfg.betas
+        t = self.step_count
+        bc1, bc2 = 1 - b1**t, 1 - b2**t
+        contiguous_owner = not (self.cfg.zero and self.dp_size > 1)
+        if self.device.type == "cuda" and native.available() and hasattr(
+                torch.ops.slapo_b200, "fused_adamw"):
+            coef = clip_coef if clip_coef is not None else torch.ones((), device=self.device)
+            if contiguous_owner:
+                native.ops().fused_adamw(self.flat_param, grad, self.master, self.exp_avg,
+                                         self.exp_avg_sq, self.decay_mask, coef.float().reshape(1),
+                                         lr, b1, b2, self.cfg.eps, self.cfg.weight_decay, bc1, bc2)
+            else:
+                for (lo, hi), pos in zip(self.shard_ranges, self.shard_offsets):
+                    n = hi - lo
+                    native.ops().fused_adamw(
+                        self.flat_param[lo:hi], grad[pos:pos + n], self.master[pos:pos + n],
+                        self.exp_avg[pos:pos + n], self.exp_avg_sq[pos:pos + n],
+                        self.decay_mask[pos:pos + n], coef.float().reshape(1), lr, b1, b2,
+                        self.cfg.eps, self.cfg.weight_decay, bc1, bc2)
+            return
+        g = grad.float()
+        if clip_coef is not None:
+            g = g * clip_coef
+        self.exp_avg.mul_(b1).add_(g, alpha=1 - b1)
+        self.exp_avg_sq.mul_(b2).addcmul_(g, g, value=1 - b2)
+        denom = (self.exp_avg_sq / bc2).sqrt_().add_(self.cfg.eps)
+        update = (self.exp_avg / bc1) / denom
+        update.add_(self.master * self.decay_mask, alpha=self.cfg.weight_decay)
+        self.master.add_(update, alpha=-lr)
+        for (lo, hi), pos in zip(self.shard_ranges, self.shard_offsets):
+            self.flat_param[lo:hi].copy_(self.master[pos:pos + hi - lo])
+
+    def _gather_params(self):
+        if not (self.cfg.zero and self.dp_size > 1):
+            return
+        for bucket, (lo, hi) in zip(self.buckets, self.shard_ranges):
+            full = self.flat_param[bucket.start:bucket.end]
+            if self.device.type == "cuda":
+                dist.all_gather_into_tensor(full, self.flat_param[lo:hi], group=self.dp_group)
+            else:
+                dist.all_gather_into_tensor(full, self.flat_param[lo:hi].clone(), group=self.dp_group)
+
+    # ------------------------------------------------------------------ #
+    def train_batch(self, *args, labels=None, **kwargs):
+        out = self.model(*args, **kwargs)
+        if self.loss_fn is not None:
+            loss = self.loss_fn(out, labels)
+        elif torch.is_tensor(out):
+            loss = out
+        elif isinstance(out, dict):
+            loss = out["loss"]
+        else:
+            loss = out[0]
+        if loss.dim() > 0:
+            loss = loss.float().mean()
+        self.backward(loss)
+        self.step()
+        return loss.detach()
+
+    # ---- checkpoint support ------------------------------------------ #
+    def optimizer_state(self):
+        return {"step": self.step_count, "master": self.master, "exp_avg": self.exp_avg,
+                "exp_avg_sq": self.exp_avg_sq, "shard_ranges": list(self.shard_ranges),
+                "dp_size": self.dp_size, "dp_rank": self.dp_rank, "zero": self.cfg.zero}
+
+    def load_optimizer_state(self, state):
+        self.step_count = int(state["step"])
+        for key in ("master", "exp_avg", "exp_avg_sq"):
+            getattr(self, key).copy_(state[key])
+        for (lo, hi), pos in zip(self.shard_ranges, self.shard_offsets):
+            self.flat_param[lo:hi].copy_(self.master[pos:pos + hi - lo])
+        self._gather_params()
+
+    def refresh_master_from_params(self):
+        """After loading model weights into ``p.data``: re-seed the fp32 master."""
+        for (lo, hi), pos in zip(self.shard_ranges, self.shard_offsets):
+            self.master[pos:pos + hi - lo].copy_(self.flat_param[lo:hi])
+
+
+class StepTimer:
+    """Device-side step timing: CUDA events on the current stream (wall
+    clock on CPU); ``max_over_ranks`` reduces with MAX over a group."""
+
+    def __init__(self, device):
+        self.cuda = torch.device(device).type == "cuda"
+        self.t0 = self.t1 = None
+
+    def start(self):
+        if self.cuda:
+            torch.cuda.synchronize()
+            self.t0 = torch.cuda.Event(enable_timing=True)
+            self.t1 = torch.cuda.Event(enable_timing=True)
+            self.t0.record()
+        else:
+            import time
+
+            self.t0 = time.perf_counter()
+
+    def stop(self) -> float:
+        """Elapsed milliseconds."""
+        if self.cuda:
+            self.t1.record()
+            torch.cuda.synchronize()
+            return self.t0.elapsed_time(self.t1)
+        import time
+
+        return (time.perf_counter() - self.t0) * 1e3
+
+    @staticmethod
+    def max_over_ranks(ms: float, device, group=None) -> float:
+        if not (dist.is_available() and dist.is_initialized()):
+            return ms
+        t = torch.tensor([ms], dtype=torch.float64, device=device)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX, group=group)
+        return float(t.item())
