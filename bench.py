@@ -1,0 +1,306 @@
+"""Headline benchmark: BERT-large masked-LM training throughput (samples/s).
+
+    python bench.py --gpus 1 --steps 10 --warmup 3
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node 8 --master-addr 127.0.0.1 \
+        --master-port 29500 bench.py --gpus 8 --steps 10 --warmup 3
+
+Config (the reference's BERT-large benchmark shape): 24 layers, hidden 1024,
+16 heads, FFN 4096 GeLU, vocab 30522 (padded to a multiple of the TP size),
+sequence 512, bf16, synthetic uniform token ids with 15 % masked labels,
+random-init weights, 32 samples per GPU (global batch 256 on 8 GPUs),
+activation checkpointing on every other layer, AdamW.  With N > 1 GPUs the
+model is tensor-parallel over all N (TP = N, with sequence parallelism for
+the native arm), i.e. weak scaling of the global batch.
+
+Two arms:
+
+* default: this framework (``apply_schedule`` -> ``build(target="native")``
+  -> ``engine.train_batch``);
+* ``--impl reference``: the unmodified reference package from
+  ``baseline/_ref`` through its public API (``create_schedule`` / ``shard`` /
+  ``sync`` / ``checkpoint`` / ``build``) on a Hugging Face ``BertForMaskedLM``
+  with a plain PyTorch AdamW loop, which is what the reference's
+  ``examples/utils.py`` does when no DeepSpeed / Megatron runtime exists.
+
+Rank 0 prints ONE JSON line.  ``value`` is device-timed (CUDA events, max
+over ranks) over exactly K steps with inputs resident on the device; ``e2e``
+repeats the measurement through the public API including, every step, the
+pinned-host -> device copy of the batch and a device -> host read of the loss.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+MODEL = dict(layers=24, hidden=1024, heads=16, ffn=4096, vocab=30522, seq=512)
+
+
+def parse_args():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=8)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="native", choices=["native", "reference"])
+    ap.add_argument("--batch-per-gpu", type=int, default=32)
+    ap.add_argument("--seq", type=int, default=MODEL["seq"])
+    ap.add_argument("--layers", type=int, default=MODEL["layers"])
+    ap.add_argument("--ckpt-ratio", type=float, default=0.5)
+    ap.add_argument("--parallelism", default="tp", choices=["tp", "dp"])
+    ap.add_argument("--no-sequence-parallel", action="store_true")
+    ap.add_argument("--no-e2e", action="store_true")
+    return ap.parse_args()
+
+
+# --------------------------------------------------------------------------- #
+class ClockSampler(threading.Thread):
+    """Samples SM clock and throttle reasons of one GPU through NVML (read only)."""
+
+    def __init__(self, index, period=0.2):
+        super().__init__(daemon=True)
+        self.index, self.period = index, period
+        self.samples, self.reasons = [], set()
+        self.max_mhz = None
+        self._stop = threading.Event()
+        self.ok = False
+        try:
+            import pynvml
+
+            pynvml.nvmlInit()
+            self.nv = pynvml
+            self.handle = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(self.handle, pynvml.NVML_CLOCK_SM)
+            self.ok = True
+        except Exception:
+            self.nv = None
+
+    def run(self):
+        if not self.ok:
+            return
+        nv = self.nv
+        names = {
+            getattr(nv, "nvmlClocksEventReasonHwSlowdown", 0x8): "hw_slowdown",
+            getattr(nv, "nvmlClocksEventReasonHwThermalSlowdown", 0x40): "hw_thermal_slowdown",
+            getattr(nv, "nvmlClocksEventReasonSwThermalSlowdown", 0x20): "sw_thermal_slowdown",
+            getattr(nv, "nvmlClocksEventReasonSwPowerCap", 0x4): "sw_power_cap",
+        }
+        while not self._stop.is_set():
+            try:
+                self.samples.append(nv.nvmlDeviceGetClockInfo(self.handle, nv.NVML_CLOCK_SM))
+                try:
+                    mask = nv.nvmlDeviceGetCurrentClocksEventReasons(self.handle)
+                except Exception:
+                    mask = nv.nvmlDeviceGetCurrentClocksThrottleReasons(self.handle)
+                for bit, name in names.items():
+                    if mask & bit:
+                        self.reasons.add(name)
+            except Exception:
+                pass
+            self._stop.wait(self.period)
+
+    def finish(self):
+        self._stop.set()
+        if self.is_alive():
+            self.join(timeout=2)
+        med = sorted(self.samples)[len(self.samples) // 2] if self.samples else None
+        return {"sm_mhz": med, "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons),
+                "samples": len(self.samples)}
+
+
+def make_batch(vocab, batch, seq, seed, device="cpu", pin=False):
+    import torch
+
+    g = torch.Generator().manual_seed(seed)
+    ids = torch.randint(0, vocab, (batch, seq), generator=g)
+    labels = torch.full_like(ids, -100)
+    pick = torch.rand(batch, seq, generator=g) < 0.15
+    labels[pick] = ids[pick]
+    if pin:
+        ids, labels = ids.pin_memory(), labels.pin_memory()
+    return ids.to(device), labels.to(device)
+
+
+def dist_setup(args):
+    import torch
+    import torch.distributed as dist
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    return world, rank, local
+
+
+def timed_loop(step_fn, steps, device, world):
+    """Time exactly ``steps`` calls of ``step_fn`` on the device; max over ranks."""
+    import torch
+    import torch.distributed as dist
+
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+    t0 = torch.cuda.Event(enable_timing=True)
+    t1 = torch.cuda.Event(enable_timing=True)
+    t0.record()
+    for i in range(steps):
+        step_fn(i)
+    t1.record()
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    ms = t0.elapsed_time(t1)
+    if world > 1:
+        t = torch.tensor([ms], dtype=torch.float64, device=device)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+    return ms
+
+
+# --------------------------------------------------------------------------- #
+def build_native(args, world, rank):
+    import torch
+
+    import slapo_b200 as slapo
+    from slapo_b200.models import BertConfig, BertForMaskedLM, mlm_loss
+    from slapo_b200.models.schedules.common import pad_vocab
+    from slapo_b200.parallel.mesh import DeviceMesh
+
+    tp = world if args.parallelism == "tp" else 1
+    dp = world // tp
+    mesh = DeviceMesh(pp=1, dp=dp, tp=tp) if world > 1 else None
+    vocab = pad_vocab(MODEL["vocab"], 8 * tp if tp > 1 else 8)
+    cfg = BertConfig(vocab_size=vocab, hidden_size=MODEL["hidden"],
+                     num_hidden_layers=args.layers, num_attention_heads=MODEL["heads"],
+                     intermediate_size=MODEL["ffn"], max_position_embeddings=max(512, args.seq))
+    sp = tp > 1 and not args.no_sequence_parallel
+    slapo.set_random_seed(2013, dp_rank=mesh.dp_rank if mesh else 0,
+                          tp_rank=mesh.tp_rank if mesh else 0, always_enable_tp_seed=sp)
+    with slapo.init_empty_weights():
+        model = BertForMaskedLM(cfg)
+    sch = slapo.model_schedule.apply_schedule(
+        model, "bert", model_config=cfg, bf16=True, group=mesh.tp_group if mesh else None,
+        ckpt_ratio=args.ckpt_ratio, sequence_parallel=sp)
+    vocab_parallel = tp > 1
+    tp_group = mesh.tp_group if mesh else None
+
+    def loss_fn(out, labels):
+        return mlm_loss(out["logits"], labels, tp_group, vocab_parallel)
+
+    engine, _ = slapo.build(sch, target="native", mesh=mesh, loss_fn=loss_fn,
+                            config={"lr": 1e-4, "weight_decay": 0.01, "clip_grad": 1.0})
+    parallelism = f"tp{tp}" + ("+sp" if sp else "") if tp > 1 else (f"dp{dp}" if dp > 1 else "single")
+    return engine, vocab, parallelism, dp
+
+
+def run_native(args):
+    import torch
+
+    from slapo_b200.ops import native
+
+    world, rank, local = dist_setup(args)
+    device = torch.device("cuda", local)
+    engine, vocab, parallelism, dp = build_native(args, world, rank)
+    tp = world // dp
+    # TP ranks consume the same batch; DP replicas different ones
+    local_batch = args.batch_per_gpu * tp
+    dp_rank = rank // tp
+    ids, labels = make_batch(vocab, local_batch, args.seq, 1234 + dp_rank, device)
+    global_batch = local_batch * dp
+
+    def step(_i):
+        engine.train_batch(ids, labels=labels)
+
+    for i in range(args.warmup):
+        step(i)
+    sampler = ClockSampler(local)
+    sampler.start()
+    launches0 = native.launch_count()
+    ms = timed_loop(step, args.steps, device, world)
+    launches = native.launch_count() - launches0
+    clocks = sampler.finish()
+    value = global_batch * args.steps / (ms / 1e3)
+
+    e2e = None
+    if not args.no_e2e:
+        host = [make_batch(vocab, local_batch, args.seq, 77 + dp_rank * 100 + i, "cpu", pin=True)
+                for i in range(2)]
+        h2d = sum(t.numel() * t.element_size() for t in host[0])
+
+        def e2e_step(i):
+            hi, hl = host[i % 2]
+            di = hi.to(device, non_blocking=True)
+            dl = hl.to(device, non_blocking=True)
+            loss = engine.train_batch(di, labels=dl)
+            return float(loss.item())  # device -> host read of the result
+
+        e2e_step(0)
+        ms_e = timed_loop(e2e_step, args.steps, device, world)
+        e2e = {"value": global_batch * args.steps / (ms_e / 1e3), "unit": "samples/s",
+               "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": 4,
+               "ms_per_step": ms_e / args.steps}
+    if rank == 0:
+        print(json.dumps({
+            "metric": "train samples/sec, BERT-large MLM", "value": value, "unit": "samples/s",
+            "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "impl": "native",
+            "config": {"model": "bert-large", "layers": args.layers, "global_batch": global_batch,
+                       "seq_len": args.seq, "parallelism": parallelism,
+                       "ckpt_ratio": args.ckpt_ratio, "optimizer": "AdamW",
+                       "l2_policy": "per-step working set (weights+activations, >10 GB) "
+                                    "exceeds the 126 MB L2, nothing survives between steps"},
+            "clocks": clocks, "e2e": e2e, "gpu_launches": int(launches),
+            "max_mem_mb": torch.cuda.max_memory_allocated() / 2**20,
+        }), flush=True)
+    if world > 1:
+        import torch.distributed as dist
+
+        dist.destroy_process_group()
+
+
+# --------------------------------------------------------------------------- #
+def run_reference(args):
+    ref_root = os.path.join(ROOT, "baseline", "_ref")
+    if not os.path.isdir(os.path.join(ref_root, "slapo")):
+        print(json.dumps({"impl": "reference",
+                          "unavailable": "baseline/_ref is missing (offline pip install not done)"}))
+        return
+    try:
+        from baseline.reference_arm import run
+    except Exception as err:  # pragma: no cover
+        print(json.dumps({"impl": "reference", "unavailable": f"harness import failed: {err}"}))
+        return
+    run(args, ref_root, MODEL, dist_setup, make_batch, timed_loop, ClockSampler)
+
+
+def maybe_self_launch(args):
+    """``python bench.py --gpus N`` without torchrun: start the ranks ourselves."""
+    if args.gpus > 1 and "RANK" not in os.environ:
+        port = 29500 + (os.getpid() % 2000)
+        cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1",
+               f"--nproc-per-node={args.gpus}", "--master-addr", "127.0.0.1",
+               "--master-port", str(port), os.path.abspath(__file__)] + sys.argv[1:]
+        sys.exit(subprocess.call(cmd))
+
+
+def main():
+    args = parse_args()
+    maybe_self_launch(args)
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_native(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,35 @@
+// Launchers that take a PhiloxArgs by value need its full definition; it is
+// kept free of device-only constructs so that host compilers can include it.
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#ifndef __CUDACC__
+namespace slapo {
+struct PhiloxArgs {
+  uint64_t seed;
+  uint64_t offset;
+  const int64_t* seed_ptr;
+  const int64_t* offset_ptr;
+  uint32_t offset_intragraph;
+  int captured;
+};
+}  // namespace slapo
+#endif
+
+namespace slapo {
+void launch_bias_dropout_add_fwd(const void* x, const void* bias, const void* residual, void* y,
+                                 int64_t rows, int cols, float p, PhiloxArgs rng, int dtype,
+                                 cudaStream_t stream);
+void launch_bias_dropout_add_bwd(const void* dy, void* dx, void* dbias, float* partial, int rows,
+                                 int cols, float p, PhiloxArgs rng, int dtype,
+                                 cudaStream_t stream);
+void launch_ln_fwd(const void* x, const void* bias, const void* residual, const void* gamma,
+                   const void* beta, void* y, void* z, float* mean, float* rstd, int rows,
+                   int cols, float eps, float p, PhiloxArgs rng, int rms, int dtype,
+                   cudaStream_t stream);
+void launch_ln_bwd(const void* gy, const void* gz, const void* zin, const void* gamma,
+                   const float* mean, const float* rstd, void* dx, void* dres, void* dgamma,
+                   void* dbeta, void* dbias, float* partial, int rows, int cols, float p,
+                   PhiloxArgs rng, int rms, int dtype, cudaStream_t stream);
+}  // namespace slapo

@@ -1,0 +1,33 @@
+// Host-side launchers of the sm_100a kernels.  Plain CUDA types only: the
+// torch bindings (bindings.cpp) and stand-alone C callers share this header.
+// dtype codes: 0 = bf16, 1 = fp16, 2 = fp32.
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace slapo {
+
+struct PhiloxArgs;
+
+// number of kernels launched by this library since load (host-side counter)
+void count_launch(int n = 1);
+int64_t launch_count();
+
+int colsum_chunks(int rows, int cols);
+int ln_bwd_grid(int rows, int cols);
+
+void launch_bias_act_fwd(const void* x, const void* bias, void* y, int64_t rows, int cols,
+                         int act, int dtype, cudaStream_t stream);
+void launch_bias_act_bwd(const void* dy, const void* x, const void* bias, void* dx, void* dbias,
+                         float* partial, int rows, int cols, int act, int dtype,
+                         cudaStream_t stream);
+void launch_colsum_finalize(const float* partial, void* out, int chunks, int cols, int dtype,
+                            cudaStream_t stream);
+void launch_fused_adamw(void* param, const void* grad, float* master, float* exp_avg,
+                        float* exp_avg_sq, const uint8_t* decay_mask, const float* grad_scale,
+                        int64_t n, float lr, float beta1, float beta2, float eps,
+                        float weight_decay, float bc1, float bc2, int dtype, cudaStream_t stream);
+
+}  // namespace slapo
+
+#include "common_host.h"

@@ -21,23 +21,23 @@ def native_supported(q, k, v) -> bool:
 class _FlashAttnFn(torch.autograd.Function):
     @staticmethod
     def forward(ctx, q, k, v, key_bias, causal, scale, p, rel_table, rel_bidir, rel_maxd):
-        from .functional import _philox_args
+        from .functional import _philox_reserve
 
         b, sq, h, d = q.shape
-        seed, offset = _philox_args(b * h * sq * k.shape[1]) if p > 0 else (0, 0)
+        rng = _philox_reserve(b * h * sq * k.shape[1]) if p > 0 else None
         out, lse = native.ops().flash_attn_fwd(
-            q, k, v, key_bias, rel_table, causal, scale, p, seed, offset, rel_bidir, rel_maxd)
+            q, k, v, key_bias, rel_table, causal, scale, p, rng, rel_bidir, rel_maxd)
         ctx.save_for_backward(q, k, v, out, lse, key_bias, rel_table)
-        ctx.cfg = (causal, scale, p, seed, offset, rel_bidir, rel_maxd)
+        ctx.cfg = (causal, scale, p, rng, rel_bidir, rel_maxd)
         return out
 
     @staticmethod
     def backward(ctx, dout):
         q, k, v, out, lse, key_bias, rel_table = ctx.saved_tensors
-        causal, scale, p, seed, offset, rel_bidir, rel_maxd = ctx.cfg
+        causal, scale, p, rng, rel_bidir, rel_maxd = ctx.cfg
         dq, dk, dv, dtable = native.ops().flash_attn_bwd(
-            dout.contiguous(), q, k, v, out, lse, key_bias, rel_table, causal, scale, p, seed,
-            offset, rel_bidir, rel_maxd)
+            dout.contiguous(), q, k, v, out, lse, key_bias, rel_table, causal, scale, p, rng,
+            rel_bidir, rel_maxd)
         return dq, dk, dv, None, None, None, None, (dtable if rel_table is not None else None), None, None
 
 

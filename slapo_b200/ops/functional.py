@@ -86,35 +86,27 @@ def bias_gelu(x, bias, approximate: str = "none"):
 
 # ---------------------------------------------------------------------- #
 # dropout family
-def _philox_args(numel):
-    """Reserve a Philox (seed, offset) range on the current CUDA generator,
-    so that the masks follow torch's RNG state (fork_rng, checkpoint replay)."""
-    gen = torch.cuda.default_generators[torch.cuda.current_device()]
-    seed = gen.initial_seed()
-    # each thread consumes 4 x 32 bits per 4 elements; reserve generously and
-    # keep the offset a multiple of 4 as the generator requires
-    inc = ((numel + 3) // 4) * 4
-    offset = gen.get_offset()
-    gen.set_offset(offset + inc)
-    return seed, offset
+def _philox_reserve(numel):
+    """Reserve Philox offsets on the current CUDA generator (so masks follow
+    torch's RNG state: manual_seed, fork_rng, checkpoint replay).  Returns the
+    opaque CPU int64[4] state the kernels take; valid under graph capture."""
+    return native.ops().philox_reserve(int(numel))
 
 
 class _BiasDropoutAddFn(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x, bias, residual, p):
-        seed, offset = _philox_args(x.numel())
-        ctx.p, ctx.seed, ctx.offset = p, seed, offset
+        rng = _philox_reserve(x.numel())
+        ctx.p, ctx.rng = p, rng
         ctx.has_bias, ctx.has_res = bias is not None, residual is not None
-        ctx.cols = x.shape[-1]
         return native.ops().bias_dropout_add_fwd(
             x.contiguous(), bias, residual.contiguous() if residual is not None else None,
-            p, seed, offset)
+            p, rng)
 
     @staticmethod
     def backward(ctx, grad):
         grad = grad.contiguous()
-        dx, dbias = native.ops().bias_dropout_add_bwd(grad, ctx.p, ctx.seed, ctx.offset,
-                                                      ctx.has_bias)
+        dx, dbias = native.ops().bias_dropout_add_bwd(grad, ctx.p, ctx.rng, ctx.has_bias)
         return dx, (dbias if ctx.has_bias else None), (grad if ctx.has_res else None), None
 
 
@@ -173,13 +165,12 @@ class _DropoutAddLayerNormFn(torch.autograd.Function):
         x2 = x.contiguous().view(-1, cols)
         r2 = residual.contiguous().view(-1, cols)
         p_eff = p if training else 0.0
-        seed, offset = _philox_args(x.numel()) if p_eff > 0 else (0, 0)
+        rng = _philox_reserve(x.numel()) if p_eff > 0 else None
         y, z, mean, rstd = native.ops().dropout_add_ln_fwd(
-            x2, bias, r2, weight, ln_bias, p_eff, eps, seed, offset)
+            x2, bias, r2, weight, ln_bias, p_eff, eps, rng)
         ctx.save_for_backward(z, weight, mean, rstd)
-        ctx.p, ctx.seed, ctx.offset = p_eff, seed, offset
+        ctx.p, ctx.rng = p_eff, rng
         ctx.has_bias, ctx.shape = bias is not None, shape
-        ctx.mark_non_differentiable()
         return y.view(shape), z.view(shape)
 
     @staticmethod
@@ -189,7 +180,7 @@ class _DropoutAddLayerNormFn(torch.autograd.Function):
         gy2 = gy.contiguous().view(-1, cols)
         gz2 = gz.contiguous().view(-1, cols) if gz is not None else None
         dx, dres, dw, db, dbias = native.ops().dropout_add_ln_bwd(
-            gy2, gz2, z, weight, mean, rstd, ctx.p, ctx.seed, ctx.offset, ctx.has_bias)
+            gy2, gz2, z, weight, mean, rstd, ctx.p, ctx.rng, ctx.has_bias)
         return (dx.view(ctx.shape), (dbias if ctx.has_bias else None), dres.view(ctx.shape),
                 dw, db, None, None, None)
 

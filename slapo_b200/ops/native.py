@@ -45,3 +45,9 @@ def ops():
 def reset():
     """Forget a failed load (used after building in the same process)."""
     _STATE.update(tried=False, ok=False, error=None)
+
+
+def launch_count() -> int:
+    """Kernels launched by the extension since it was loaded (host counter;
+    a CUDA-graph replay re-runs captured launches without counting them)."""
+    return int(ops().launch_count()) if available() else 0
