@@ -150,6 +150,11 @@ def consolidate_model(sch, target=None, init_weights=True, device=None, **kwargs
             for src_param, cur in list(tie.items()):
                 if cur is old:
                     tie[src_param] = new_param
+    # tensors that were never on meta (e.g. index buffers) follow to the device
+    for mod in top_mod.modules():
+        for n, b in list(mod._buffers.items()):
+            if b is not None and not b.is_meta and b.device != device:
+                mod._buffers[n] = b.to(device)
     if torch.cuda.is_available() and device.type == "cuda":
         torch.cuda.empty_cache()
     return sch

@@ -28,6 +28,12 @@ void launch_fused_adamw(void* param, const void* grad, float* master, float* exp
                         int64_t n, float lr, float beta1, float beta2, float eps,
                         float weight_decay, float bc1, float bc2, int dtype, cudaStream_t stream);
 
+// C[M,N] = act(A B^T + bias); a_mn / b_mn select M/N-major operands (see gemm.cu).
+// Returns 0 on success, >0 when the launch was refused on the host.
+int launch_gemm(const void* A, const void* B, void* C, const void* bias, int M, int N, int K,
+                int lda, int ldb, int ldc, bool a_mn, bool b_mn, bool bf16, int act, int* status,
+                cudaStream_t stream);
+
 }  // namespace slapo
 
 #include "common_host.h"

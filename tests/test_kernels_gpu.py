@@ -14,7 +14,7 @@ DTYPES = [torch.bfloat16, torch.float16, torch.float32]
 
 def _tol(dtype):
     return {torch.bfloat16: (2e-2, 2e-2), torch.float16: (4e-3, 4e-3),
-            torch.float32: (2e-5, 2e-5)}[dtype]
+            torch.float32: (2e-4, 2e-4)}[dtype]  # kernels use fast-math intrinsics
 
 
 @pytest.fixture(autouse=True)
