@@ -33,3 +33,21 @@ void launch_ln_bwd(const void* gy, const void* gz, const void* zin, const void* 
                    void* dbeta, void* dbias, float* partial, int rows, int cols, float p,
                    PhiloxArgs rng, int rms, int dtype, cudaStream_t stream);
 }  // namespace slapo
+
+namespace slapo {
+// Flash attention on [B, S, H, D] tensors (D contiguous, D in {64, 128});
+// *_strides = element strides of (B, S, H).  Return 0 on success.
+int launch_flash_fwd(const void* q, const void* k, const void* v, void* o, float* lse,
+                     const float* kbias, const float* rel, int B, int H, int Sq, int Sk, int D,
+                     const int64_t* q_strides, const int64_t* k_strides, const int64_t* v_strides,
+                     float scale, int causal, float p_drop, PhiloxArgs rng, bool bf16, int* status,
+                     cudaStream_t stream);
+int launch_flash_bwd(const void* q, const void* k, const void* v, const void* o, const void* dout,
+                     const float* lse, float* delta, float* dq_accum, void* dk, void* dv,
+                     const float* kbias, const float* rel, float* drel, int B, int H, int Sq, int Sk,
+                     int D, const int64_t* q_strides, const int64_t* k_strides,
+                     const int64_t* v_strides, float scale, int causal, float p_drop,
+                     PhiloxArgs rng, bool bf16, int* status, cudaStream_t stream);
+void launch_flash_dropout_mask(uint8_t* mask, int B, int H, int Sq, int Sk, float p_drop,
+                               PhiloxArgs rng, cudaStream_t stream);
+}  // namespace slapo

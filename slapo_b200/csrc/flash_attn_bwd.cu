@@ -1,0 +1,465 @@
+// Flash attention backward on tcgen05 / TMEM (sm_100a).
+//
+// One CTA owns 128 keys of one (batch, head) and walks over the query tiles
+// (128 rows) that can see them.  Per query tile:
+//   tensor core   S  = Q K^T            dP = dO V^T                (fp32 in TMEM)
+//   128 threads   p  = exp2(s - lse),   ds = p * (dp - delta)      (one query row each,
+//                 Philox dropout replayed), P and scale*dS written as 16-bit
+//                 tiles into swizzled shared memory
+//   tensor core   dV += P^T dO          dK += dS^T Q               (TMEM accumulators
+//                 dQ_tile = dS K                                    over all query tiles)
+//   128 threads   dQ_tile -> fp32 global accumulator (vector red.add)
+// The same shared-memory bytes serve as K-major and M/N-major operands: only
+// the descriptors differ, nothing is transposed.  delta = rowsum(dO * O) comes
+// from a small pre-pass; the fp32 dQ accumulator is converted by the caller.
+#include "common.cuh"
+#include "kernels.h"
+#include "tc05.cuh"
+
+namespace slapo {
+
+constexpr float kLog2eB = 1.4426950408889634f;
+
+struct FlashBwdParams {
+  int B, H, Sq, Sk;
+  const float* lse;     // [B, H, Sq]
+  const float* delta;   // [B, H, Sq]
+  float* dq_accum;      // [B, Sq, H, D] fp32, zero-initialised
+  void* dK;             // [B, Sk, H, D]
+  void* dV;             // [B, Sk, H, D]
+  const float* kbias;   // [B, Sk] or nullptr
+  const float* rel;     // [H, Sq + Sk - 1] or nullptr
+  float* drel;          // same shape fp32 accumulator or nullptr
+  float scale, scale_log2;
+  int causal;
+  float p_drop;
+  PhiloxArgs rng;
+  int bf16;
+  uint32_t idesc_s, idesc_dvk, idesc_dq;
+  int* status;
+};
+
+__device__ __forceinline__ uint32_t pack_pair_b(float a, float b, int bf16) {
+  if (bf16) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(a, b);
+    return *reinterpret_cast<uint32_t*>(&v);
+  }
+  __half2 v = __floats2half2_rn(a, b);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+
+__device__ __forceinline__ void red_add_v4(float* addr, float a, float b, float c, float d) {
+  asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(addr), "f"(a), "f"(b), "f"(c),
+               "f"(d)
+               : "memory");
+}
+
+// delta[b, h, i] = sum_d dO[b, i, h, d] * O[b, i, h, d]   (both contiguous [B, Sq, H, D])
+template <typename T>
+__global__ void flash_bwd_delta_kernel(const T* __restrict__ dout, const T* __restrict__ out,
+                                       float* __restrict__ delta, int B, int H, int Sq, int D) {
+  const int warps_per_block = blockDim.x >> 5;
+  const int64_t row = static_cast<int64_t>(blockIdx.x) * warps_per_block + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  const int64_t rows = static_cast<int64_t>(B) * Sq * H;
+  if (row >= rows) return;
+  float s = 0.f;
+  for (int d = lane * 8; d < D; d += 256) {
+    float a[8], b[8];
+    Vec8<T>::load(dout + row * D + d, a);
+    Vec8<T>::load(out + row * D + d, b);
+#pragma unroll
+    for (int k = 0; k < 8; ++k) s += a[k] * b[k];
+  }
+  s = warp_sum(s);
+  if (lane == 0) {
+    const int h = static_cast<int>(row % H);
+    const int64_t bi = row / H;
+    const int i = static_cast<int>(bi % Sq);
+    const int b = static_cast<int>(bi / Sq);
+    delta[(static_cast<int64_t>(b) * H + h) * Sq + i] = s;
+  }
+}
+
+template <int D>
+__global__ void __launch_bounds__(192, 1)
+flash_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
+                 const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_do,
+                 const FlashBwdParams p) {
+  constexpr int kTileBytes = 128 * D * 2;
+  constexpr int kBlkBytes = 128 * 128;
+  constexpr int kDBlocks = D / 64;
+  constexpr int kStages = D == 64 ? 2 : 1;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>(
+      (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
+  uint8_t* s_k = smem;
+  uint8_t* s_v = s_k + kTileBytes;
+  uint8_t* s_q = s_v + kTileBytes;                  // kStages
+  uint8_t* s_do = s_q + kStages * kTileBytes;       // kStages
+  uint8_t* s_p = s_do + kStages * kTileBytes;       // 2 blocks
+  uint8_t* s_ds = s_p + 2 * kBlkBytes;              // 2 blocks
+  uint64_t* bars = reinterpret_cast<uint64_t*>(s_ds + 2 * kBlkBytes);
+  uint64_t* kv_full = bars;            // 1
+  uint64_t* qdo_full = bars + 1;       // kStages (<= 2)
+  uint64_t* qdo_empty = bars + 3;      // kStages
+  uint64_t* sdp_full = bars + 5;
+  uint64_t* pds_full = bars + 6;       // 4 arrivals
+  uint64_t* dq_full = bars + 7;
+  uint64_t* dq_empty = bars + 8;       // 4 arrivals
+  uint64_t* acc_full = bars + 9;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 10);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  float* kb_tile = reinterpret_cast<float*>(bars + 12);  // 128 floats
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int n0 = blockIdx.x * 128;
+  const int head = blockIdx.y, batch = blockIdx.z;
+  const int diag = p.Sk - p.Sq;
+  const int q_tiles = (p.Sq + 127) / 128;
+  int i_begin = 0;
+  if (p.causal) i_begin = max(0, (n0 - diag) / 128);
+  i_begin = min(i_begin, q_tiles);
+  const int n_iter = q_tiles - i_begin;
+
+  constexpr uint32_t kTmemCols = 512;
+  constexpr uint32_t kColS = 0, kColDP = 128, kColDV = 256, kColDK = 256 + D;
+  constexpr uint32_t kColDQ = D == 64 ? 384 : 0;  // D = 128: dQ reuses the S columns
+
+  if (threadIdx.x == 0) {
+    tc::mbar_init(kv_full, 1);
+    for (int s = 0; s < 2; ++s) {
+      tc::mbar_init(&qdo_full[s], 1);
+      tc::mbar_init(&qdo_empty[s], 1);
+    }
+    tc::mbar_init(sdp_full, 1);
+    tc::mbar_init(pds_full, 4);
+    tc::mbar_init(dq_full, 1);
+    tc::mbar_init(dq_empty, 4);
+    tc::mbar_init(acc_full, 1);
+    *abort_flag = 0;
+    tc::fence_barrier_init();
+  }
+  if (warp == 1) {
+    tc::tmem_alloc(tmem_slot, kTmemCols);
+    tc::tmem_relinquish();
+  }
+  if (warp >= 2) {
+    const int t = (warp - 2) * 32 + lane;
+    const int key = n0 + t;
+    kb_tile[t] = (p.kbias != nullptr && key < p.Sk)
+                     ? p.kbias[static_cast<int64_t>(batch) * p.Sk + key] * kLog2eB : 0.f;
+  }
+  tc::fence_before_sync();
+  __syncthreads();
+  tc::fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      tc::tma_prefetch_desc(&tm_q);
+      tc::tma_prefetch_desc(&tm_do);
+      tc::mbar_arrive_expect_tx(kv_full, 2 * kTileBytes);
+#pragma unroll
+      for (int d = 0; d < kDBlocks; ++d) {
+        tc::tma_load_4d(s_k + d * kBlkBytes, &tm_k, kv_full, d * 64, head, n0, batch);
+        tc::tma_load_4d(s_v + d * kBlkBytes, &tm_v, kv_full, d * 64, head, n0, batch);
+      }
+      bool ok = true;
+      for (int it = 0; it < n_iter && ok; ++it) {
+        const int st = it % kStages;
+        const uint32_t ph = (it / kStages) & 1;
+        if (!tc::mbar_wait(&qdo_empty[st], ph ^ 1, abort_flag)) { ok = false; break; }
+        tc::mbar_arrive_expect_tx(&qdo_full[st], 2 * kTileBytes);
+        const int m0 = (i_begin + it) * 128;
+#pragma unroll
+        for (int d = 0; d < kDBlocks; ++d) {
+          tc::tma_load_4d(s_q + st * kTileBytes + d * kBlkBytes, &tm_q, &qdo_full[st], d * 64, head,
+                          m0, batch);
+          tc::tma_load_4d(s_do + st * kTileBytes + d * kBlkBytes, &tm_do, &qdo_full[st], d * 64,
+                          head, m0, batch);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      bool ok = tc::mbar_wait(kv_full, 0, abort_flag);
+      const uint32_t k_addr = tc::smem_u32(s_k), v_addr = tc::smem_u32(s_v);
+      const uint32_t p_addr = tc::smem_u32(s_p), ds_addr = tc::smem_u32(s_ds);
+      auto issue_s_dp = [&](int it) -> bool {
+        const int st = it % kStages;
+        if (!tc::mbar_wait(&qdo_full[st], (it / kStages) & 1, abort_flag)) return false;
+        if (D == 128 && it > 0 && !tc::mbar_wait(dq_empty, (it - 1) & 1, abort_flag)) return false;
+        tc::fence_after_sync();
+        const uint32_t q_addr = tc::smem_u32(s_q + st * kTileBytes);
+        const uint32_t do_addr = tc::smem_u32(s_do + st * kTileBytes);
+#pragma unroll
+        for (int kk = 0; kk < D / 16; ++kk) {
+          const uint32_t off = (kk >> 2) * kBlkBytes + (kk & 3) * 32;
+          tc::umma_f16(tmem_base + kColS, tc::smem_desc(q_addr + off, 16, 1024),
+                       tc::smem_desc(k_addr + off, 16, 1024), p.idesc_s, kk != 0 ? 1u : 0u);
+        }
+#pragma unroll
+        for (int kk = 0; kk < D / 16; ++kk) {
+          const uint32_t off = (kk >> 2) * kBlkBytes + (kk & 3) * 32;
+          tc::umma_f16(tmem_base + kColDP, tc::smem_desc(do_addr + off, 16, 1024),
+                       tc::smem_desc(v_addr + off, 16, 1024), p.idesc_s, kk != 0 ? 1u : 0u);
+        }
+        tc::umma_commit(sdp_full);
+        return true;
+      };
+      if (ok && n_iter > 0) ok = issue_s_dp(0);
+      for (int it = 0; it < n_iter && ok; ++it) {
+        const int st = it % kStages;
+        if (!tc::mbar_wait(pds_full, it & 1, abort_flag)) { ok = false; break; }
+        if (D == 64 && it > 0 && !tc::mbar_wait(dq_empty, (it - 1) & 1, abort_flag)) { ok = false; break; }
+        tc::fence_after_sync();
+        const uint32_t q_addr = tc::smem_u32(s_q + st * kTileBytes);
+        const uint32_t do_addr = tc::smem_u32(s_do + st * kTileBytes);
+        // dV += P^T dO ; dK += dS^T Q : A = [q rows x keys] read M-major (M = keys, K = q rows),
+        // B = [q rows x D] read N-major.  16 query rows per instruction.
+#pragma unroll
+        for (int kk = 0; kk < 128 / 16; ++kk) {
+          const uint64_t b_do = tc::smem_desc(do_addr + kk * 2048, kBlkBytes, 1024);
+          const uint64_t b_q = tc::smem_desc(q_addr + kk * 2048, kBlkBytes, 1024);
+          const uint64_t a_p = tc::smem_desc(p_addr + kk * 2048, kBlkBytes, 1024);
+          const uint64_t a_ds = tc::smem_desc(ds_addr + kk * 2048, kBlkBytes, 1024);
+          const uint32_t accum = (it | kk) != 0 ? 1u : 0u;
+          tc::umma_f16(tmem_base + kColDV, a_p, b_do, p.idesc_dvk, accum);
+          tc::umma_f16(tmem_base + kColDK, a_ds, b_q, p.idesc_dvk, accum);
+        }
+        // dQ_tile = dS K : A = dS K-major (M = q rows, K = keys), B = K read N-major
+#pragma unroll
+        for (int kk = 0; kk < 128 / 16; ++kk) {
+          const uint64_t a_ds =
+              tc::smem_desc(ds_addr + (kk >> 2) * kBlkBytes + (kk & 3) * 32, 16, 1024);
+          const uint64_t b_k = tc::smem_desc(k_addr + kk * 2048, kBlkBytes, 1024);
+          tc::umma_f16(tmem_base + kColDQ, a_ds, b_k, p.idesc_dq, kk != 0 ? 1u : 0u);
+        }
+        tc::umma_commit(dq_full);
+        tc::umma_commit(&qdo_empty[st]);
+        if (it + 1 < n_iter && !issue_s_dp(it + 1)) { ok = false; break; }
+      }
+      if (ok) tc::umma_commit(acc_full);
+    }
+  } else {
+    const int quarter = warp & 3;
+    const int r_in = quarter * 32 + lane;
+    const uint32_t lane_sel = static_cast<uint32_t>(quarter * 32) << 16;
+    uint64_t seed = 0, offset = 0;
+    if (p.p_drop > 0.f) philox_unpack(p.rng, seed, offset);
+    const uint32_t thr16 = static_cast<uint32_t>(p.p_drop * 65536.f);
+    const float inv_keep = 1.f / (1.f - p.p_drop);
+    const int sk8 = (p.Sk + 7) >> 3;
+    bool ok = true;
+    for (int it = 0; it < n_iter && ok; ++it) {
+      const int row = (i_begin + it) * 128 + r_in;
+      const bool row_ok = row < p.Sq;
+      const int64_t stat_idx = (static_cast<int64_t>(batch) * p.H + head) * p.Sq + min(row, p.Sq - 1);
+      const float lse2 = row_ok ? p.lse[stat_idx] * kLog2eB : -INFINITY;
+      const float delta = row_ok ? p.delta[stat_idx] : 0.f;
+      const uint64_t drop_row_base = static_cast<uint64_t>(stat_idx) * sk8;
+      const float* rel_row = nullptr;
+      float* drel_row = nullptr;
+      if (p.rel != nullptr) {
+        const int64_t base = static_cast<int64_t>(head) * (p.Sq + p.Sk - 1) + (p.Sq - 1) - min(row, p.Sq - 1);
+        rel_row = p.rel + base;
+        if (p.drel != nullptr) drel_row = p.drel + base;
+      }
+      int key_limit = p.Sk;
+      if (p.causal) key_limit = min(key_limit, row + diag + 1);
+      if (!row_ok || lse2 == -INFINITY) key_limit = 0;
+      if (!tc::mbar_wait(sdp_full, it & 1, abort_flag)) { ok = false; break; }
+      tc::fence_after_sync();
+      uint8_t* p_row = s_p + r_in * 128;
+      uint8_t* ds_row = s_ds + r_in * 128;
+#pragma unroll 1
+      for (int c = 0; c < 4; ++c) {
+        uint32_t s_raw[32], dp_raw[32];
+        tc::tmem_ld_x32(tmem_base + kColS + c * 32 + lane_sel, s_raw);
+        tc::tmem_ld_x32(tmem_base + kColDP + c * 32 + lane_sel, dp_raw);
+        tc::tmem_ld_wait();
+        float pv[32], dsv[32];
+#pragma unroll
+        for (int t = 0; t < 32; ++t) {
+          const int key = n0 + c * 32 + t;
+          float s2 = __uint_as_float(s_raw[t]) * p.scale_log2 + kb_tile[c * 32 + t];
+          if (rel_row != nullptr) s2 += rel_row[key] * kLog2eB;
+          const float pr = key < key_limit ? exp2f(s2 - lse2) : 0.f;
+          pv[t] = pr;
+          dsv[t] = __uint_as_float(dp_raw[t]);
+        }
+        if (p.p_drop > 0.f) {
+#pragma unroll
+          for (int g = 0; g < 4; ++g) {
+            const uint32_t bits = philox_keep8_u16(
+                seed, offset, drop_row_base + ((n0 + c * 32 + g * 8) >> 3), thr16);
+#pragma unroll
+            for (int t = 0; t < 8; ++t) {
+              const bool keep = (bits >> t) & 1u;
+              const float pr = pv[g * 8 + t];
+              // grad wrt the un-dropped probability, then softmax backward
+              dsv[g * 8 + t] = pr * ((keep ? dsv[g * 8 + t] * inv_keep : 0.f) - delta);
+              pv[g * 8 + t] = keep ? pr * inv_keep : 0.f;
+            }
+          }
+        } else {
+#pragma unroll
+          for (int t = 0; t < 32; ++t) dsv[t] = pv[t] * (dsv[t] - delta);
+        }
+        if (drel_row != nullptr) {
+#pragma unroll
+          for (int t = 0; t < 32; ++t) {
+            const int key = n0 + c * 32 + t;
+            if (key < key_limit && dsv[t] != 0.f) atomicAdd(drel_row + key, dsv[t]);
+          }
+        }
+#pragma unroll
+        for (int g = 0; g < 4; ++g) {
+          const int chunk = (c & 1) * 4 + g;
+          const int off = (c >> 1) * kBlkBytes + ((chunk ^ (r_in & 7)) << 4);
+          uint4 pk = make_uint4(pack_pair_b(pv[g * 8 + 0], pv[g * 8 + 1], p.bf16),
+                                pack_pair_b(pv[g * 8 + 2], pv[g * 8 + 3], p.bf16),
+                                pack_pair_b(pv[g * 8 + 4], pv[g * 8 + 5], p.bf16),
+                                pack_pair_b(pv[g * 8 + 6], pv[g * 8 + 7], p.bf16));
+          *reinterpret_cast<uint4*>(p_row + off) = pk;
+          uint4 dk = make_uint4(
+              pack_pair_b(dsv[g * 8 + 0] * p.scale, dsv[g * 8 + 1] * p.scale, p.bf16),
+              pack_pair_b(dsv[g * 8 + 2] * p.scale, dsv[g * 8 + 3] * p.scale, p.bf16),
+              pack_pair_b(dsv[g * 8 + 4] * p.scale, dsv[g * 8 + 5] * p.scale, p.bf16),
+              pack_pair_b(dsv[g * 8 + 6] * p.scale, dsv[g * 8 + 7] * p.scale, p.bf16));
+          *reinterpret_cast<uint4*>(ds_row + off) = dk;
+        }
+      }
+      tc::fence_before_sync();
+      tc::fence_proxy_async();
+      __syncwarp();
+      if (lane == 0) tc::mbar_arrive(pds_full);
+      // dQ tile of this query block
+      if (!tc::mbar_wait(dq_full, it & 1, abort_flag)) { ok = false; break; }
+      tc::fence_after_sync();
+      float* dq_dst = p.dq_accum +
+                      ((static_cast<int64_t>(batch) * p.Sq + min(row, p.Sq - 1)) * p.H + head) * D;
+#pragma unroll
+      for (int c = 0; c < D / 32; ++c) {
+        uint32_t r[32];
+        tc::tmem_ld_x32(tmem_base + kColDQ + c * 32 + lane_sel, r);
+        tc::tmem_ld_wait();
+        if (row_ok) {
+#pragma unroll
+          for (int g = 0; g < 8; ++g)
+            red_add_v4(dq_dst + c * 32 + g * 4, __uint_as_float(r[g * 4]), __uint_as_float(r[g * 4 + 1]),
+                       __uint_as_float(r[g * 4 + 2]), __uint_as_float(r[g * 4 + 3]));
+        }
+      }
+      tc::fence_before_sync();
+      __syncwarp();
+      if (lane == 0) tc::mbar_arrive(dq_empty);
+    }
+    // dK / dV of this key tile: thread = key row
+    if (ok && n_iter > 0) ok = tc::mbar_wait(acc_full, 0, abort_flag);
+    tc::fence_after_sync();
+    const int key = n0 + r_in;
+    if (ok && key < p.Sk) {
+      uint8_t* dk_dst = static_cast<uint8_t*>(p.dK) +
+                        ((static_cast<int64_t>(batch) * p.Sk + key) * p.H + head) * D * 2;
+      uint8_t* dv_dst = static_cast<uint8_t*>(p.dV) +
+                        ((static_cast<int64_t>(batch) * p.Sk + key) * p.H + head) * D * 2;
+#pragma unroll
+      for (int which = 0; which < 2; ++which) {
+        uint8_t* dst = which == 0 ? dv_dst : dk_dst;
+        const uint32_t col = which == 0 ? kColDV : kColDK;
+#pragma unroll
+        for (int c = 0; c < D / 32; ++c) {
+          uint32_t r[32];
+          if (n_iter > 0) {
+            tc::tmem_ld_x32(tmem_base + col + c * 32 + lane_sel, r);
+            tc::tmem_ld_wait();
+          } else {
+#pragma unroll
+            for (int t = 0; t < 32; ++t) r[t] = 0u;
+          }
+#pragma unroll
+          for (int g = 0; g < 4; ++g) {
+            uint4 pk = make_uint4(
+                pack_pair_b(__uint_as_float(r[g * 8 + 0]), __uint_as_float(r[g * 8 + 1]), p.bf16),
+                pack_pair_b(__uint_as_float(r[g * 8 + 2]), __uint_as_float(r[g * 8 + 3]), p.bf16),
+                pack_pair_b(__uint_as_float(r[g * 8 + 4]), __uint_as_float(r[g * 8 + 5]), p.bf16),
+                pack_pair_b(__uint_as_float(r[g * 8 + 6]), __uint_as_float(r[g * 8 + 7]), p.bf16));
+            *reinterpret_cast<uint4*>(dst + (c * 32 + g * 8) * 2) = pk;
+          }
+        }
+      }
+    }
+  }
+
+  tc::fence_before_sync();
+  __syncthreads();
+  if (threadIdx.x == 0 && *abort_flag != 0 && p.status != nullptr) atomicExch(p.status, 3);
+  if (warp == 1) {
+    tc::fence_after_sync();
+    tc::tmem_dealloc(tmem_base, kTmemCols);
+  }
+}
+
+template <int D>
+static int launch_bwd_d(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv,
+                        const CUtensorMap& tdo, const FlashBwdParams& p, cudaStream_t stream) {
+  constexpr int kStages = D == 64 ? 2 : 1;
+  constexpr int kSmem = (2 + 2 * kStages) * 128 * D * 2 + 4 * 128 * 128 + 12 * 8 + 128 * 4 + 1024;
+  auto kernel = flash_bwd_kernel<D>;
+  static bool configured = false;
+  if (!configured) {
+    if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem) !=
+        cudaSuccess)
+      return 3;
+    configured = true;
+  }
+  dim3 grid((p.Sk + 127) / 128, p.H, p.B);
+  count_launch();
+  kernel<<<grid, 192, kSmem, stream>>>(tq, tk, tv, tdo, p);
+  return cudaGetLastError() == cudaSuccess ? 0 : 4;
+}
+
+int launch_flash_bwd(const void* q, const void* k, const void* v, const void* o, const void* dout,
+                     const float* lse, float* delta, float* dq_accum, void* dk, void* dv,
+                     const float* kbias, const float* rel, float* drel, int B, int H, int Sq, int Sk,
+                     int D, const int64_t* q_strides, const int64_t* k_strides,
+                     const int64_t* v_strides, float scale, int causal, float p_drop,
+                     PhiloxArgs rng, bool bf16, int* status, cudaStream_t stream) {
+  if (D != 64 && D != 128) return 1;
+  // pre-pass: delta (o and dout are contiguous [B, Sq, H, D])
+  {
+    const int64_t rows = static_cast<int64_t>(B) * Sq * H;
+    const int wpb = 8;
+    const unsigned blocks = static_cast<unsigned>((rows + wpb - 1) / wpb);
+    count_launch();
+    if (bf16)
+      flash_bwd_delta_kernel<__nv_bfloat16><<<blocks, wpb * 32, 0, stream>>>(
+          static_cast<const __nv_bfloat16*>(dout), static_cast<const __nv_bfloat16*>(o), delta, B, H,
+          Sq, D);
+    else
+      flash_bwd_delta_kernel<__half><<<blocks, wpb * 32, 0, stream>>>(
+          static_cast<const __half*>(dout), static_cast<const __half*>(o), delta, B, H, Sq, D);
+  }
+  CUtensorMap tq, tk, tv, tdo;
+  const int64_t do_strides[3] = {static_cast<int64_t>(Sq) * H * D, static_cast<int64_t>(H) * D, D};
+  if (!make_tmap_bshd(&tq, q, B, Sq, H, D, q_strides[0], q_strides[1], q_strides[2], 128, bf16) ||
+      !make_tmap_bshd(&tk, k, B, Sk, H, D, k_strides[0], k_strides[1], k_strides[2], 128, bf16) ||
+      !make_tmap_bshd(&tv, v, B, Sk, H, D, v_strides[0], v_strides[1], v_strides[2], 128, bf16) ||
+      !make_tmap_bshd(&tdo, dout, B, Sq, H, D, do_strides[0], do_strides[1], do_strides[2], 128, bf16))
+    return 2;
+  FlashBwdParams p;
+  p.B = B; p.H = H; p.Sq = Sq; p.Sk = Sk; p.lse = lse; p.delta = delta; p.dq_accum = dq_accum;
+  p.dK = dk; p.dV = dv; p.kbias = kbias; p.rel = rel; p.drel = drel; p.scale = scale;
+  p.scale_log2 = scale * kLog2eB; p.causal = causal; p.p_drop = p_drop; p.rng = rng;
+  p.bf16 = bf16 ? 1 : 0; p.status = status;
+  const int f = bf16 ? 1 : 0;
+  p.idesc_s = tc::instr_desc_f16(128, 128, f, false, false);   // S, dP
+  p.idesc_dvk = tc::instr_desc_f16(128, D, f, true, true);     // dV, dK
+  p.idesc_dq = tc::instr_desc_f16(128, D, f, false, true);     // dQ
+  return D == 64 ? launch_bwd_d<64>(tq, tk, tv, tdo, p, stream)
+                 : launch_bwd_d<128>(tq, tk, tv, tdo, p, stream);
+}
+
+}  // namespace slapo

@@ -77,6 +77,14 @@ __device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* t
       ::"r"(smem_u32(smem_dst)), "l"(tmap), "r"(smem_u32(bar)), "r"(c0), "r"(c1)
       : "memory");
 }
+__device__ __forceinline__ void tma_load_4d(void* smem_dst, const CUtensorMap* tmap,
+                                            uint64_t* bar, int c0, int c1, int c2, int c3) {
+  asm volatile(
+      "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes"
+      " [%0], [%1, {%3, %4, %5, %6}], [%2];"
+      ::"r"(smem_u32(smem_dst)), "l"(tmap), "r"(smem_u32(bar)), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
+      : "memory");
+}
 __device__ __forceinline__ void tma_prefetch_desc(const CUtensorMap* tmap) {
   asm volatile("prefetch.tensormap [%0];" ::"l"(tmap) : "memory");
 }
@@ -216,5 +224,12 @@ __host__ __device__ inline uint32_t instr_desc_f16(int m, int n, int ab_format, 
 bool make_tmap_2d(CUtensorMap* out, const void* base, uint64_t inner, uint64_t outer,
                   uint64_t row_stride_elems, uint32_t box_inner, uint32_t box_outer,
                   int elem_bytes, bool is_bf16);
+
+// 4-D view [B, S, H, D] of 16-bit elements with arbitrary (16-byte multiple)
+// strides for B, S, H and contiguous D; box = [1, box_s rows, 1, 64 elements],
+// 128-B swizzle.  Coordinates of a load are (d, h, s, b).
+bool make_tmap_bshd(CUtensorMap* out, const void* base, uint64_t B, uint64_t S, uint64_t H,
+                    uint64_t D, uint64_t stride_b, uint64_t stride_s, uint64_t stride_h,
+                    uint32_t box_s, bool is_bf16);
 
 }  // namespace slapo

@@ -1,4 +1,12 @@
-"""Python binding of the tcgen05 flash-attention kernels."""
+"""Python binding of the tcgen05 flash-attention kernels.
+
+``flash_attention_native`` is differentiable in q, k, v and in the T5
+relative-position table.  The table ``[num_buckets, H]`` is expanded with
+plain (differentiable) torch indexing into a per-distance bias ``[H, Sq + Sk -
+1]`` - entry ``(key - query) + Sq - 1`` - which the kernels add in-line, so the
+``[H, Sq, Sk]`` bias matrix is never materialised and the table gradient flows
+back through that small gather.
+"""
 from __future__ import annotations
 
 import math
@@ -13,38 +21,59 @@ _HEAD_DIMS = (64, 128)
 def native_supported(q, k, v) -> bool:
     if not (q.is_cuda and q.dtype in (torch.bfloat16, torch.float16)):
         return False
-    if q.shape[-1] not in _HEAD_DIMS or q.stride(-1) != 1 or k.stride(-1) != 1 or v.stride(-1) != 1:
+    if q.dim() != 4 or q.shape[-1] not in _HEAD_DIMS:
         return False
-    return native.available() and hasattr(torch.ops.slapo_b200, "flash_attn_fwd")
+    for t in (q, k, v):
+        if t.stride(-1) != 1 or any(s % 8 for s in t.stride()[:3]) or t.data_ptr() % 16:
+            return False
+    return native.available()
 
 
 class _FlashAttnFn(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, q, k, v, key_bias, causal, scale, p, rel_table, rel_bidir, rel_maxd):
-        from .functional import _philox_reserve
-
-        b, sq, h, d = q.shape
-        rng = _philox_reserve(b * h * sq * k.shape[1]) if p > 0 else None
-        out, lse = native.ops().flash_attn_fwd(
-            q, k, v, key_bias, rel_table, causal, scale, p, rng, rel_bidir, rel_maxd)
-        ctx.save_for_backward(q, k, v, out, lse, key_bias, rel_table)
-        ctx.cfg = (causal, scale, p, rng, rel_bidir, rel_maxd)
+    def forward(ctx, q, k, v, key_bias, rel, causal, scale, p):
+        rng = native.ops().philox_reserve(q.shape[0] * q.shape[2] * q.shape[1] * k.shape[1]) \
+            if p > 0 else None
+        out, lse = native.ops().flash_attn_fwd(q, k, v, key_bias, rel, causal, scale, p, rng)
+        ctx.save_for_backward(q, k, v, out, lse, key_bias, rel)
+        ctx.cfg = (causal, scale, p, rng)
         return out
 
     @staticmethod
     def backward(ctx, dout):
-        q, k, v, out, lse, key_bias, rel_table = ctx.saved_tensors
-        causal, scale, p, rng, rel_bidir, rel_maxd = ctx.cfg
-        dq, dk, dv, dtable = native.ops().flash_attn_bwd(
-            dout.contiguous(), q, k, v, out, lse, key_bias, rel_table, causal, scale, p, rng,
-            rel_bidir, rel_maxd)
-        return dq, dk, dv, None, None, None, None, (dtable if rel_table is not None else None), None, None
+        q, k, v, out, lse, key_bias, rel = ctx.saved_tensors
+        causal, scale, p, rng = ctx.cfg
+        dq, dk, dv, drel = native.ops().flash_attn_bwd(
+            dout.contiguous(), q, k, v, out, lse, key_bias, rel, causal, scale, p, rng)
+        return dq, dk, dv, None, (drel if rel is not None else None), None, None, None
+
+
+def relative_bias_by_distance(table, sq, sk, bidirectional, max_distance):
+    """``[num_buckets, H]`` table -> ``[H, sq + sk - 1]`` bias per (key - query)."""
+    from .functional import t5_relative_position_bucket
+
+    # query i sits at absolute position i + (sk - sq); distance = key - that
+    dist = torch.arange(-(sq - 1), sk, device=table.device) - (sk - sq)
+    buckets = t5_relative_position_bucket(dist, bidirectional, table.shape[0], max_distance)
+    return table.float()[buckets].t().contiguous()
 
 
 def flash_attention_native(q, k, v, key_bias, causal, scale, p, rel_table, rel_bidir, rel_maxd):
     scale = 1.0 / math.sqrt(q.shape[-1]) if scale is None else scale
     if key_bias is not None:
         key_bias = key_bias.float().contiguous()
+    rel = None
     if rel_table is not None:
-        rel_table = rel_table.float()
-    return _FlashAttnFn.apply(q, k, v, key_bias, causal, scale, p, rel_table, rel_bidir, rel_maxd)
+        rel = relative_bias_by_distance(rel_table, q.shape[1], k.shape[1], rel_bidir, rel_maxd)
+    return _FlashAttnFn.apply(q, k, v, key_bias, rel, bool(causal), float(scale), float(p))
+
+
+def dropout_keep_mask(b, h, sq, sk, p):
+    """The keep mask the next flash-attention call with dropout ``p`` would
+    draw, WITHOUT advancing the generator (testing aid)."""
+    gen = torch.cuda.default_generators[torch.cuda.current_device()]
+    state = gen.get_state()
+    rng = native.ops().philox_reserve(b * h * sq * sk)
+    mask = native.ops().flash_attn_dropout_mask(b, h, sq, sk, p, rng)
+    gen.set_state(state)
+    return mask.bool()
