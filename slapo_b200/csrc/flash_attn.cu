@@ -256,7 +256,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
 
     auto fold = [&](int jt) -> bool {
       const int ob = jt & 1;
-      if (!tc::mbar_wait(&o_full[ob], (jt >> 1) & 1, abort_flag)) return false;
+      if (!tc::mbar_wait_warp(&o_full[ob], (jt >> 1) & 1, abort_flag)) return false;
       tc::fence_after_sync();
 #pragma unroll
       for (int c = 0; c < D / 32; ++c) {
@@ -281,7 +281,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
         kb_tile[sm_tid] = key < p.Sk ? p.kbias[static_cast<int64_t>(batch) * p.Sk + key] * kLog2e : 0.f;
         softmax_bar_sync();
       }
-      if (!tc::mbar_wait(s_full, j & 1, abort_flag)) { ok = false; break; }
+      if (!tc::mbar_wait_warp(s_full, j & 1, abort_flag)) { ok = false; break; }
       tc::fence_after_sync();
       int key_limit = p.Sk;
       if (p.causal) key_limit = min(key_limit, row + diag + 1);
@@ -303,7 +303,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
       const float alpha = m_run == -INFINITY ? 0.f : exp2f(m_run - m_use);
       // the P buffer is single: the previous P V product must have retired
       // before it is overwritten (the fold below consumes the same phase)
-      if (j > 0 && !tc::mbar_wait(&o_full[(j - 1) & 1], ((j - 1) >> 1) & 1, abort_flag)) {
+      if (j > 0 && !tc::mbar_wait_warp(&o_full[(j - 1) & 1], ((j - 1) >> 1) & 1, abort_flag)) {
         ok = false;
         break;
       }

@@ -269,7 +269,7 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
       int key_limit = p.Sk;
       if (p.causal) key_limit = min(key_limit, row + diag + 1);
       if (!row_ok || lse2 == -INFINITY) key_limit = 0;
-      if (!tc::mbar_wait(sdp_full, it & 1, abort_flag)) { ok = false; break; }
+      if (!tc::mbar_wait_warp(sdp_full, it & 1, abort_flag)) { ok = false; break; }
       tc::fence_after_sync();
       uint8_t* p_row = s_p + r_in * 128;
       uint8_t* ds_row = s_ds + r_in * 128;
@@ -336,7 +336,7 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
       __syncwarp();
       if (lane == 0) tc::mbar_arrive(pds_full);
       // dQ tile of this query block
-      if (!tc::mbar_wait(dq_full, it & 1, abort_flag)) { ok = false; break; }
+      if (!tc::mbar_wait_warp(dq_full, it & 1, abort_flag)) { ok = false; break; }
       tc::fence_after_sync();
       float* dq_dst = p.dq_accum +
                       ((static_cast<int64_t>(batch) * p.Sq + min(row, p.Sq - 1)) * p.H + head) * D;
@@ -357,14 +357,17 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
       if (lane == 0) tc::mbar_arrive(dq_empty);
     }
     // dK / dV of this key tile: thread = key row
-    if (ok && n_iter > 0) ok = tc::mbar_wait(acc_full, 0, abort_flag);
+    if (ok && n_iter > 0) ok = tc::mbar_wait_warp(acc_full, 0, abort_flag);
     tc::fence_after_sync();
     const int key = n0 + r_in;
-    if (ok && key < p.Sk) {
+    // tcgen05.ld is warp-collective: every lane takes part, only the stores
+    // are predicated on the key being in range
+    if (ok) {
+      const int key_c = min(key, p.Sk - 1);
       uint8_t* dk_dst = static_cast<uint8_t*>(p.dK) +
-                        ((static_cast<int64_t>(batch) * p.Sk + key) * p.H + head) * D * 2;
+                        ((static_cast<int64_t>(batch) * p.Sk + key_c) * p.H + head) * D * 2;
       uint8_t* dv_dst = static_cast<uint8_t*>(p.dV) +
-                        ((static_cast<int64_t>(batch) * p.Sk + key) * p.H + head) * D * 2;
+                        ((static_cast<int64_t>(batch) * p.Sk + key_c) * p.H + head) * D * 2;
 #pragma unroll
       for (int which = 0; which < 2; ++which) {
         uint8_t* dst = which == 0 ? dv_dst : dk_dst;
@@ -379,14 +382,16 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
 #pragma unroll
             for (int t = 0; t < 32; ++t) r[t] = 0u;
           }
+          if (key < p.Sk) {
 #pragma unroll
-          for (int g = 0; g < 4; ++g) {
-            uint4 pk = make_uint4(
-                pack_pair_b(__uint_as_float(r[g * 8 + 0]), __uint_as_float(r[g * 8 + 1]), p.bf16),
-                pack_pair_b(__uint_as_float(r[g * 8 + 2]), __uint_as_float(r[g * 8 + 3]), p.bf16),
-                pack_pair_b(__uint_as_float(r[g * 8 + 4]), __uint_as_float(r[g * 8 + 5]), p.bf16),
-                pack_pair_b(__uint_as_float(r[g * 8 + 6]), __uint_as_float(r[g * 8 + 7]), p.bf16));
-            *reinterpret_cast<uint4*>(dst + (c * 32 + g * 8) * 2) = pk;
+            for (int g = 0; g < 4; ++g) {
+              uint4 pk = make_uint4(
+                  pack_pair_b(__uint_as_float(r[g * 8 + 0]), __uint_as_float(r[g * 8 + 1]), p.bf16),
+                  pack_pair_b(__uint_as_float(r[g * 8 + 2]), __uint_as_float(r[g * 8 + 3]), p.bf16),
+                  pack_pair_b(__uint_as_float(r[g * 8 + 4]), __uint_as_float(r[g * 8 + 5]), p.bf16),
+                  pack_pair_b(__uint_as_float(r[g * 8 + 6]), __uint_as_float(r[g * 8 + 7]), p.bf16));
+              *reinterpret_cast<uint4*>(dst + (c * 32 + g * 8) * 2) = pk;
+            }
           }
         }
       }

@@ -222,7 +222,7 @@ gemm_tc05_kernel(const __grid_constant__ CUtensorMap tmap_a,
       const int n0 = (tile % tiles_n) * BN;
       const int acc = iter & 1;
       const uint32_t acc_phase = (iter >> 1) & 1;
-      if (!tc::mbar_wait(&tmem_full[acc], acc_phase, abort_flag)) { ok = false; break; }
+      if (!tc::mbar_wait_warp(&tmem_full[acc], acc_phase, abort_flag)) { ok = false; break; }
       tc::fence_after_sync();
       const int row = m0 + quarter * 32 + lane;
       const uint32_t t_row = tmem_base + acc * BN + (static_cast<uint32_t>(quarter * 32) << 16);

@@ -12,7 +12,7 @@
 namespace slapo {
 namespace tc {
 
-constexpr long long kWaitCycles = 4000000000LL;  // ~2 s at 2 GHz
+constexpr long long kWaitCycles = 400000000LL;  // ~0.2 s at 2 GHz
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
   return static_cast<uint32_t>(__cvta_generic_to_shared(p));
@@ -66,6 +66,14 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity,
     }
   }
   return true;
+}
+
+// Same, called by all 32 lanes of a warp: the result is made warp-uniform so
+// that warp-collective instructions after it never run under divergence.
+__device__ __forceinline__ bool mbar_wait_warp(uint64_t* bar, uint32_t parity,
+                                               volatile int* abort_flag) {
+  const bool ok = mbar_wait(bar, parity, abort_flag);
+  return __all_sync(0xffffffffu, ok);
 }
 
 // ---- TMA (tile mode, this CTA's shared memory only) -------------------------
