@@ -76,14 +76,27 @@ std::tuple<Tensor, Tensor> flash_attn_fwd(const Tensor& q, const Tensor& k, cons
 std::tuple<Tensor, Tensor, Tensor, Tensor> flash_attn_bwd(
     const Tensor& dout, const Tensor& q, const Tensor& k, const Tensor& v, const Tensor& o,
     const Tensor& lse, const optional<Tensor>& kbias, const optional<Tensor>& rel, bool causal,
-    double scale, double p_drop, const optional<Tensor>& rng) {
+    double scale, double p_drop, const optional<Tensor>& rng, bool packed_qkv) {
   check_bshd(q, "q"); check_bshd(k, "k"); check_bshd(v, "v");
   TORCH_CHECK(dout.is_contiguous() && o.is_contiguous(), "dout and out must be contiguous");
   c10::cuda::CUDAGuard guard(q.device());
   const int B = q.size(0), Sq = q.size(1), H = q.size(2), D = q.size(3), Sk = k.size(1);
   Tensor dq_accum = at::zeros({B, Sq, H, D}, q.options().dtype(at::kFloat));
-  Tensor dk = at::empty({B, Sk, H, D}, q.options());
-  Tensor dv = at::empty({B, Sk, H, D}, q.options());
+  // packed_qkv: q, k, v are the slices [..., 0/1/2, :] of one [B, S, H, 3, D]
+  // projection output; the gradients are written into one tensor of that
+  // layout so that autograd needs no concatenation
+  Tensor dk, dv, dqkv;
+  int64_t dkv_stride = D;
+  if (packed_qkv) {
+    TORCH_CHECK(Sq == Sk, "packed QKV needs equal query and key lengths");
+    dqkv = at::empty({B, Sq, H, 3, D}, q.options());
+    dk = dqkv.select(3, 1);
+    dv = dqkv.select(3, 2);
+    dkv_stride = 3 * D;
+  } else {
+    dk = at::empty({B, Sk, H, D}, q.options());
+    dv = at::empty({B, Sk, H, D}, q.options());
+  }
   Tensor delta = at::empty({B, H, Sq}, q.options().dtype(at::kFloat));
   Tensor drel;
   const bool has_rel = rel.has_value() && rel->defined();
@@ -95,12 +108,16 @@ std::tuple<Tensor, Tensor, Tensor, Tensor> flash_attn_bwd(
   int rc = slapo::launch_flash_bwd(
       q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), dout.data_ptr(),
       lse.data_ptr<float>(), delta.data_ptr<float>(), dq_accum.data_ptr<float>(), dk.data_ptr(),
-      dv.data_ptr(), opt_f32(kbias, "key bias"), opt_f32(rel, "relative bias"),
+      dv.data_ptr(), dkv_stride, opt_f32(kbias, "key bias"), opt_f32(rel, "relative bias"),
       has_rel ? drel.data_ptr<float>() : nullptr, B, H, Sq, Sk, D, qs, ks, vs,
       static_cast<float>(scale), causal ? 1 : 0, static_cast<float>(p_drop), unpack_rng(rng),
       q.scalar_type() == at::kBFloat16, slapo_status_ptr(q.get_device()),
       at::cuda::getCurrentCUDAStream().stream());
   TORCH_CHECK(rc == 0, "flash_attn_bwd: launch refused (code ", rc, ")");
+  if (packed_qkv) {
+    dqkv.select(3, 0).copy_(dq_accum);
+    return {dqkv, dk, dv, drel};
+  }
   return {dq_accum.to(q.scalar_type()), dk, dv, drel};
 }
 
@@ -118,7 +135,7 @@ Tensor flash_attn_dropout_mask(int64_t B, int64_t H, int64_t Sq, int64_t Sk, dou
 void register_attn_ops(torch::Library& m) {
   m.def("flash_attn_fwd(Tensor q, Tensor k, Tensor v, Tensor? kbias, Tensor? rel, bool causal, float scale, float p_drop, Tensor? rng) -> (Tensor, Tensor)",
         &flash_attn_fwd);
-  m.def("flash_attn_bwd(Tensor dout, Tensor q, Tensor k, Tensor v, Tensor o, Tensor lse, Tensor? kbias, Tensor? rel, bool causal, float scale, float p_drop, Tensor? rng) -> (Tensor, Tensor, Tensor, Tensor)",
+  m.def("flash_attn_bwd(Tensor dout, Tensor q, Tensor k, Tensor v, Tensor o, Tensor lse, Tensor? kbias, Tensor? rel, bool causal, float scale, float p_drop, Tensor? rng, bool packed_qkv) -> (Tensor, Tensor, Tensor, Tensor)",
         &flash_attn_bwd);
   m.def("flash_attn_dropout_mask(int B, int H, int Sq, int Sk, float p_drop, Tensor rng) -> Tensor",
         &flash_attn_dropout_mask);

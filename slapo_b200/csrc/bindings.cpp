@@ -259,6 +259,7 @@ void fused_adamw(Tensor param, const Tensor& grad, Tensor master, Tensor exp_avg
 void register_gemm_ops(torch::Library& m);
 void register_attn_ops(torch::Library& m);
 void register_comm_ops(torch::Library& m);
+void register_loss_ops(torch::Library& m);
 
 TORCH_LIBRARY(slapo_b200, m) {
   m.def("philox_reserve(int increment) -> Tensor", &philox_reserve);
@@ -283,4 +284,5 @@ TORCH_LIBRARY(slapo_b200, m) {
   register_gemm_ops(m);
   register_attn_ops(m);
   register_comm_ops(m);
+  register_loss_ops(m);
 }

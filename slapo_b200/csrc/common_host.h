@@ -44,8 +44,8 @@ int launch_flash_fwd(const void* q, const void* k, const void* v, void* o, float
                      cudaStream_t stream);
 int launch_flash_bwd(const void* q, const void* k, const void* v, const void* o, const void* dout,
                      const float* lse, float* delta, float* dq_accum, void* dk, void* dv,
-                     const float* kbias, const float* rel, float* drel, int B, int H, int Sq, int Sk,
-                     int D, const int64_t* q_strides, const int64_t* k_strides,
+                     int64_t dkv_row_stride, const float* kbias, const float* rel, float* drel,
+                     int B, int H, int Sq, int Sk, int D, const int64_t* q_strides, const int64_t* k_strides,
                      const int64_t* v_strides, float scale, int causal, float p_drop,
                      PhiloxArgs rng, bool bf16, int* status, cudaStream_t stream);
 void launch_flash_dropout_mask(uint8_t* mask, int B, int H, int Sq, int Sk, float p_drop,

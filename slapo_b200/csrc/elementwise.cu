@@ -206,13 +206,13 @@ __global__ void __launch_bounds__(256) fused_adamw_kernel(
 // ------------------------------------------------------------------------ //
 static inline int flat_grid(int64_t n_vec) {
   int64_t blocks = (n_vec + 255) / 256;
-  int64_t cap = static_cast<int64_t>(sm_count()) * 8;
+  int64_t cap = static_cast<int64_t>(sm_count()) * 16;
   return static_cast<int>(blocks < cap ? (blocks > 0 ? blocks : 1) : cap);
 }
 
 int colsum_chunks(int rows, int cols) {
   const int slabs = (cols + 255) / 256;
-  int chunks = (sm_count() * 4 + slabs - 1) / slabs;
+  int chunks = (sm_count() * 8 + slabs - 1) / slabs;
   const int max_chunks = (rows + 7) / 8;
   if (chunks > max_chunks) chunks = max_chunks;
   if (chunks < 1) chunks = 1;

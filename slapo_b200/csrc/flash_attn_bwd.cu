@@ -25,8 +25,9 @@ struct FlashBwdParams {
   const float* lse;     // [B, H, Sq]
   const float* delta;   // [B, H, Sq]
   float* dq_accum;      // [B, Sq, H, D] fp32, zero-initialised
-  void* dK;             // [B, Sk, H, D]
-  void* dV;             // [B, Sk, H, D]
+  void* dK;             // rows (b, key, head) spaced dkv_row_stride elements apart
+  void* dV;
+  int64_t dkv_row_stride;  // D for contiguous [B, Sk, H, D]; 3 D inside a packed QKV gradient
   const float* kbias;   // [B, Sk] or nullptr
   const float* rel;     // [H, Sq + Sk - 1] or nullptr
   float* drel;          // same shape fp32 accumulator or nullptr
@@ -365,9 +366,9 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
     if (ok) {
       const int key_c = min(key, p.Sk - 1);
       uint8_t* dk_dst = static_cast<uint8_t*>(p.dK) +
-                        ((static_cast<int64_t>(batch) * p.Sk + key_c) * p.H + head) * D * 2;
+                        ((static_cast<int64_t>(batch) * p.Sk + key_c) * p.H + head) * p.dkv_row_stride * 2;
       uint8_t* dv_dst = static_cast<uint8_t*>(p.dV) +
-                        ((static_cast<int64_t>(batch) * p.Sk + key_c) * p.H + head) * D * 2;
+                        ((static_cast<int64_t>(batch) * p.Sk + key_c) * p.H + head) * p.dkv_row_stride * 2;
 #pragma unroll
       for (int which = 0; which < 2; ++which) {
         uint8_t* dst = which == 0 ? dv_dst : dk_dst;
@@ -428,8 +429,8 @@ static int launch_bwd_d(const CUtensorMap& tq, const CUtensorMap& tk, const CUte
 
 int launch_flash_bwd(const void* q, const void* k, const void* v, const void* o, const void* dout,
                      const float* lse, float* delta, float* dq_accum, void* dk, void* dv,
-                     const float* kbias, const float* rel, float* drel, int B, int H, int Sq, int Sk,
-                     int D, const int64_t* q_strides, const int64_t* k_strides,
+                     int64_t dkv_row_stride, const float* kbias, const float* rel, float* drel,
+                     int B, int H, int Sq, int Sk, int D, const int64_t* q_strides, const int64_t* k_strides,
                      const int64_t* v_strides, float scale, int causal, float p_drop,
                      PhiloxArgs rng, bool bf16, int* status, cudaStream_t stream) {
   if (D != 64 && D != 128) return 1;
@@ -456,7 +457,7 @@ int launch_flash_bwd(const void* q, const void* k, const void* v, const void* o,
     return 2;
   FlashBwdParams p;
   p.B = B; p.H = H; p.Sq = Sq; p.Sk = Sk; p.lse = lse; p.delta = delta; p.dq_accum = dq_accum;
-  p.dK = dk; p.dV = dv; p.kbias = kbias; p.rel = rel; p.drel = drel; p.scale = scale;
+  p.dK = dk; p.dV = dv; p.dkv_row_stride = dkv_row_stride; p.kbias = kbias; p.rel = rel; p.drel = drel; p.scale = scale;
   p.scale_log2 = scale * kLog2eB; p.causal = causal; p.p_drop = p_drop; p.rng = rng;
   p.bf16 = bf16 ? 1 : 0; p.status = status;
   const int f = bf16 ? 1 : 0;

@@ -34,6 +34,17 @@ int launch_gemm(const void* A, const void* B, void* C, const void* bias, int M, 
                 int lda, int ldb, int ldc, bool a_mn, bool b_mn, bool bf16, int act, int* status,
                 cudaStream_t stream);
 
+// Cross entropy in two steps (per-row statistics, then gradient); see loss.cu.
+void launch_ce_stats(const void* logits, const int64_t* labels, float* stats, int rows, int cols,
+                     int64_t row_stride, int vocab_start, int64_t ignore_index, int dtype,
+                     cudaStream_t stream);
+void launch_ce_grad(const void* logits, const int64_t* labels, const float* lse,
+                    const float* coef, void* grad, int rows, int cols, int64_t row_stride,
+                    int vocab_start, int64_t ignore_index, int dtype, cudaStream_t stream);
+// out2[0] += sum x^2 where mask == 0 (or no mask), out2[1] += sum x^2 where mask != 0
+void launch_sq_norm(const void* x, const uint8_t* mask, float* out2, int64_t n, int dtype,
+                    cudaStream_t stream);
+
 }  // namespace slapo
 
 #include "common_host.h"

@@ -274,12 +274,13 @@ __global__ void ln_bwd_finalize_kernel(const float* __restrict__ partial, T* __r
 struct LnShape { int vpl; int wpr; };
 
 static LnShape pick_shape(int cols) {
+  // few values per thread keeps the register footprint small, so many warps
+  // are resident and enough loads are in flight to saturate HBM
   const int vecs = cols / 8;
   if (vecs <= 32) return {1, 1};
-  if (vecs <= 64) return {2, 1};
-  if (vecs <= 128) return {4, 1};
+  if (vecs <= 128) return {1, 4};
   if (vecs <= 256) return {2, 4};
-  if (vecs <= 512) return {4, 4};
+  if (vecs <= 512) return {1, 16};
   if (vecs <= 1024) return {2, 16};
   return {4, 16};
 }
@@ -288,23 +289,23 @@ int ln_bwd_grid(int rows, int cols) {
   const LnShape s = pick_shape(cols);
   const int rows_per_cta = s.wpr == 1 ? 4 : 1;
   const int want = (rows + rows_per_cta - 1) / rows_per_cta;
-  const int cap = sm_count() * (s.wpr == 16 ? 1 : 2);
+  const int cap = sm_count() * (s.wpr == 16 ? 2 : 4);
   return want < cap ? (want > 0 ? want : 1) : cap;
 }
 
 #define LN_SHAPE_SWITCH(s, ...)                                                     \
   if (s.wpr == 1) {                                                                 \
     constexpr int WPR = 1;                                                          \
-    if (s.vpl == 1) { constexpr int VPL = 1; __VA_ARGS__; }                         \
-    else if (s.vpl == 2) { constexpr int VPL = 2; __VA_ARGS__; }                    \
-    else { constexpr int VPL = 4; __VA_ARGS__; }                                    \
+    constexpr int VPL = 1;                                                          \
+    __VA_ARGS__;                                                                    \
   } else if (s.wpr == 4) {                                                          \
     constexpr int WPR = 4;                                                          \
-    if (s.vpl == 2) { constexpr int VPL = 2; __VA_ARGS__; }                         \
-    else { constexpr int VPL = 4; __VA_ARGS__; }                                    \
+    if (s.vpl == 1) { constexpr int VPL = 1; __VA_ARGS__; }                         \
+    else { constexpr int VPL = 2; __VA_ARGS__; }                                    \
   } else {                                                                          \
     constexpr int WPR = 16;                                                         \
-    if (s.vpl == 2) { constexpr int VPL = 2; __VA_ARGS__; }                         \
+    if (s.vpl == 1) { constexpr int VPL = 1; __VA_ARGS__; }                         \
+    else if (s.vpl == 2) { constexpr int VPL = 2; __VA_ARGS__; }                    \
     else { constexpr int VPL = 4; __VA_ARGS__; }                                    \
   }
 
@@ -323,7 +324,7 @@ void launch_ln_fwd(const void* x, const void* bias, const void* residual, const 
   const LnShape s = pick_shape(cols);
   const int rows_per_cta = s.wpr == 1 ? 4 : 1;
   const int want = (rows + rows_per_cta - 1) / rows_per_cta;
-  const int cap = sm_count() * (s.wpr == 16 ? 2 : 8);
+  const int cap = sm_count() * (s.wpr == 16 ? 4 : 16);
   const int grid = want < cap ? want : cap;
   count_launch();
   DISPATCH_DTYPE(dtype, LN_SHAPE_SWITCH(s, (ln_fwd_kernel<T, VPL, WPR>

@@ -243,11 +243,13 @@ class BertLMPredictionHead(nn.Module):
     def __init__(self, config):
         super().__init__()
         self.transform = BertPredictionHeadTransform(config)
-        self.decoder = nn.Linear(config.hidden_size, config.vocab_size, bias=False)
+        self.decoder = nn.Linear(config.hidden_size, config.vocab_size, bias=True)
         self.bias = nn.Parameter(torch.zeros(config.vocab_size))
+        # one bias under two names, like Hugging Face: the GEMM adds it
+        self.decoder.bias = self.bias
 
     def forward(self, hidden_states):
-        return self.decoder(self.transform(hidden_states)) + self.bias
+        return self.decoder(self.transform(hidden_states))
 
 
 class BertOnlyMLMHead(nn.Module):
@@ -286,15 +288,14 @@ class BertForMaskedLM(BertPreTrainedModel):
 
 
 def mlm_loss(logits, labels, tp_group=None, vocab_parallel=False):
-    """Mean cross entropy over the positions with ``labels != -100``."""
-    if vocab_parallel:
-        from ..ops.cross_entropy import vocab_parallel_cross_entropy
+    """Mean cross entropy over the positions with ``labels != -100``.
 
-        valid = labels != -100
-        per_tok = vocab_parallel_cross_entropy(logits, labels.clamp(min=0), tp_group)
-        return (per_tok * valid).sum() / valid.sum().clamp(min=1)
-    return F.cross_entropy(logits.view(-1, logits.size(-1)).float(), labels.view(-1),
-                           ignore_index=-100)
+    ``vocab_parallel``: ``logits`` hold this rank's vocabulary slice."""
+    from ..ops.cross_entropy import LOCAL, vocab_parallel_cross_entropy
+
+    per_tok = vocab_parallel_cross_entropy(logits, labels, tp_group if vocab_parallel else LOCAL)
+    n_valid = (labels != -100).sum().clamp(min=1)
+    return per_tok.float().sum() / n_valid
 
 
 RobertaConfig = BertConfig

@@ -140,8 +140,9 @@ def shard_lm_head(sch, config, prefix):
     if "cls.predictions" in sch:
         head = sch["cls.predictions"]
         head["decoder"].shard("weight", axis=0)  # tied: same shard as the embedding
+        head["decoder"].shard("bias", axis=0)
+        head.shard("bias", axis=0)               # the same Parameter under its second name
         head["decoder"].sync("bwd_post", "all_reduce")
-        head.shard("bias", axis=0)
 
 
 def pipeline_cut(sch, prefix, cuts):

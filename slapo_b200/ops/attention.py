@@ -58,6 +58,29 @@ class FlashAttentionOp(nn.Module):
             return NF.attention_reference(*args)
         return NF.flash_attention(*args)
 
+    def _key_bias(self, attention_mask, b, sk):
+        if attention_mask is None:
+            return None
+        if attention_mask.dim() == 4:
+            if attention_mask.shape[1] != 1 or attention_mask.shape[2] != 1:
+                raise NotImplementedError(
+                    "only key-padding masks [B,1,1,Sk] are supported; use causal=True "
+                    "for the triangular part")
+            return attention_mask.reshape(attention_mask.shape[0], sk).expand(b, sk)
+        return attention_mask.reshape(-1, sk).expand(b, sk)
+
+    def forward_packed(self, qkv, attention_mask=None, p=0.0):
+        """Attention on a packed ``[B, S, H, 3, D]`` tensor, or None when the
+        packed kernel path does not apply (the caller then slices q/k/v)."""
+        from .flash_attn import flash_attention_qkvpacked, packed_supported
+
+        if self.attn_op_name in _REFERENCE_NAMES or not packed_supported(qkv):
+            return None
+        key_bias = self._key_bias(attention_mask, qkv.shape[0], qkv.shape[1])
+        return flash_attention_qkvpacked(
+            qkv, key_bias, self.apply_causal_mask, self.scale, p if self.training else 0.0,
+            self.rel_bias_table, self.rel_bidirectional, self.rel_max_distance)
+
     def extra_repr(self):
         return f"op={self.attn_op_name}, causal={self.apply_causal_mask}, scale={self.scale}"
 
@@ -113,15 +136,23 @@ class FlashAttention(nn.Module):
             raise NotImplementedError("cross attention is not supported by FlashAttention")
         if head_mask is not None or output_attentions:
             raise NotImplementedError("head_mask / output_attentions are not supported")
+        past = layer_past if layer_past is not None else past_key_value
         if self.fused_qkv:
             qkv = self.qkv(hidden_states)
             qkv = qkv.view(qkv.shape[:-1] + (-1, 3, self.head_size))
+            if past is None and not use_cache:
+                packed = self.attn_op.forward_packed(
+                    qkv, attention_mask, self.attn_pdrop if self.training else 0.0)
+                if packed is not None:
+                    ctx = packed.reshape(packed.shape[:-2] + (-1,))
+                    if self.output_proj:
+                        ctx = self.resid_dropout(self.out_proj(ctx))
+                    return ctx, None
             q, k, v = qkv[..., 0, :], qkv[..., 1, :], qkv[..., 2, :]
         else:
             q = self.reshape_for_scores(self.query(hidden_states))
             k = self.reshape_for_scores(self.key(hidden_states))
             v = self.reshape_for_scores(self.value(hidden_states))
-        past = layer_past if layer_past is not None else past_key_value
         if past is not None:
             k = torch.cat((past[0], k), dim=1)
             v = torch.cat((past[1], v), dim=1)

@@ -44,8 +44,34 @@ class _FlashAttnFn(torch.autograd.Function):
         q, k, v, out, lse, key_bias, rel = ctx.saved_tensors
         causal, scale, p, rng = ctx.cfg
         dq, dk, dv, drel = native.ops().flash_attn_bwd(
-            dout.contiguous(), q, k, v, out, lse, key_bias, rel, causal, scale, p, rng)
+            dout.contiguous(), q, k, v, out, lse, key_bias, rel, causal, scale, p, rng, False)
         return dq, dk, dv, None, (drel if rel is not None else None), None, None, None
+
+
+class _FlashAttnPackedFn(torch.autograd.Function):
+    """Same kernels on a packed projection output ``[B, S, H, 3, D]``: q, k, v
+    are read in place through strided views and the three gradients are
+    written into one tensor of the packed layout (no slicing copies, no
+    concatenation in autograd)."""
+
+    @staticmethod
+    def forward(ctx, qkv, key_bias, rel, causal, scale, p):
+        q, k, v = qkv[..., 0, :], qkv[..., 1, :], qkv[..., 2, :]
+        rng = native.ops().philox_reserve(q.shape[0] * q.shape[2] * q.shape[1] * k.shape[1]) \
+            if p > 0 else None
+        out, lse = native.ops().flash_attn_fwd(q, k, v, key_bias, rel, causal, scale, p, rng)
+        ctx.save_for_backward(qkv, out, lse, key_bias, rel)
+        ctx.cfg = (causal, scale, p, rng)
+        return out
+
+    @staticmethod
+    def backward(ctx, dout):
+        qkv, out, lse, key_bias, rel = ctx.saved_tensors
+        causal, scale, p, rng = ctx.cfg
+        q, k, v = qkv[..., 0, :], qkv[..., 1, :], qkv[..., 2, :]
+        dqkv, _, _, drel = native.ops().flash_attn_bwd(
+            dout.contiguous(), q, k, v, out, lse, key_bias, rel, causal, scale, p, rng, True)
+        return dqkv, None, (drel if rel is not None else None), None, None, None
 
 
 def relative_bias_by_distance(table, sq, sk, bidirectional, max_distance):
@@ -66,6 +92,24 @@ def flash_attention_native(q, k, v, key_bias, causal, scale, p, rel_table, rel_b
     if rel_table is not None:
         rel = relative_bias_by_distance(rel_table, q.shape[1], k.shape[1], rel_bidir, rel_maxd)
     return _FlashAttnFn.apply(q, k, v, key_bias, rel, bool(causal), float(scale), float(p))
+
+
+def flash_attention_qkvpacked(qkv, key_bias=None, causal=False, scale=None, p=0.0,
+                              rel_table=None, rel_bidir=True, rel_maxd=128):
+    """Attention on a packed ``[B, S, H, 3, D]`` projection output."""
+    scale = 1.0 / math.sqrt(qkv.shape[-1]) if scale is None else scale
+    if key_bias is not None:
+        key_bias = key_bias.float().contiguous()
+    rel = None
+    if rel_table is not None:
+        rel = relative_bias_by_distance(rel_table, qkv.shape[1], qkv.shape[1], rel_bidir, rel_maxd)
+    return _FlashAttnPackedFn.apply(qkv, key_bias, rel, bool(causal), float(scale), float(p))
+
+
+def packed_supported(qkv) -> bool:
+    return (torch.is_tensor(qkv) and qkv.is_cuda and qkv.dim() == 5 and qkv.shape[3] == 3
+            and qkv.is_contiguous() and qkv.dtype in (torch.bfloat16, torch.float16)
+            and qkv.shape[-1] in _HEAD_DIMS and native.available())
 
 
 def dropout_keep_mask(b, h, sq, sk, p):

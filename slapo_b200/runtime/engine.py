@@ -211,6 +211,7 @@ class TrainEngine:
                 if not _is_tp_sharded(p):
                     dup[off:off + n] = True
             self.tp_dup_mask = torch.cat([dup[lo:hi] for lo, hi in self.shard_ranges])
+            self.tp_dup_mask_u8 = self.tp_dup_mask.to(torch.uint8)
         self.comm_stream = torch.cuda.Stream() if self.device.type == "cuda" else None
 
     def _install_grad_hooks(self):
@@ -287,6 +288,12 @@ class TrainEngine:
         return torch.cat([self.flat_grad[lo:hi] for lo, hi in self.shard_ranges])
 
     def _grad_norm(self, grad):
+        if (self.device.type == "cuda" and native.available() and grad.numel() % 8 == 0
+                and hasattr(torch.ops.slapo_b200, "sq_norm")):
+            # one streaming pass; [0] = TP-sharded part, [1] = replicated part
+            mask = self.tp_dup_mask_u8 if self.tp_dup_mask is not None else None
+            parts = native.ops().sq_norm(grad, mask)
+            return self._finish_norm(parts)
         g = grad.float()
         if self.tp_dup_mask is not None:
             dup = self.tp_dup_mask
@@ -295,6 +302,9 @@ class TrainEngine:
             parts = torch.stack([sq_shard, sq_dup])
         else:
             parts = torch.stack([g.pow(2).sum(), torch.zeros((), device=g.device)])
+        return self._finish_norm(parts)
+
+    def _finish_norm(self, parts):
         if self.cfg.zero and self.dp_size > 1:
             dist.all_reduce(parts, group=self.dp_group)
         if self.tp_size > 1:
