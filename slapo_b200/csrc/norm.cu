@@ -12,44 +12,50 @@
 
 namespace slapo {
 
+// Threads of a CTA are organised as RG row groups of WPR warps; each group
+// normalises one row per iteration (VPL vectors of 8 values per thread).
+// Several rows in flight per CTA keep enough loads outstanding to cover the
+// HBM latency; group-local reductions use named barriers.
 template <int WPR>
-__device__ __forceinline__ float row_sum(float v, float* smem) {
+__device__ __forceinline__ void group_sync(int group) {
+  asm volatile("bar.sync %0, %1;" ::"r"(group + 1), "r"(32 * WPR) : "memory");
+}
+
+template <int WPR>
+__device__ __forceinline__ float row_sum(float v, float* red, int group, int wir) {
   v = warp_sum(v);
   if constexpr (WPR == 1) {
     return v;
   } else {
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    if (lane == 0) smem[warp] = v;
-    __syncthreads();
+    const int lane = threadIdx.x & 31;
+    if (lane == 0) red[group * WPR + wir] = v;
+    group_sync<WPR>(group);
     float t = 0.f;
 #pragma unroll
-    for (int w = 0; w < WPR; ++w) t += smem[w];
-    __syncthreads();
+    for (int w = 0; w < WPR; ++w) t += red[group * WPR + w];
+    group_sync<WPR>(group);
     return t;
   }
 }
 
-template <typename T, int VPL, int WPR>
-__global__ void __launch_bounds__(WPR == 1 ? 128 : 32 * WPR) ln_fwd_kernel(
+template <typename T, int VPL, int WPR, int RG>
+__global__ void __launch_bounds__(32 * WPR * RG) ln_fwd_kernel(
     const T* __restrict__ x, const T* __restrict__ bias, const T* __restrict__ residual,
     const T* __restrict__ gamma, const T* __restrict__ beta, T* __restrict__ y,
     T* __restrict__ z, float* __restrict__ mean_out, float* __restrict__ rstd_out, int rows,
     int cols, float eps, float p, PhiloxArgs rng, int rms) {
-  __shared__ float red[WPR == 1 ? 1 : WPR];
-  constexpr int ROWS_PER_CTA = WPR == 1 ? 4 : 1;
+  __shared__ float red[WPR * RG];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int warp_in_row = WPR == 1 ? 0 : warp;
-  const int row_in_cta = WPR == 1 ? warp : 0;
+  const int group = warp / WPR, wir = warp % WPR;
   uint64_t seed = 0, offset = 0;
   if (p > 0.f) philox_unpack(rng, seed, offset);
   const float scale = 1.f / (1.f - p);
   const float inv_cols = 1.f / static_cast<float>(cols);
 
-  // gamma / beta are row-invariant: keep them in registers
   float gw[VPL][8], gb[VPL][8];
 #pragma unroll
   for (int i = 0; i < VPL; ++i) {
-    const int col = (i * 32 * WPR + warp_in_row * 32 + lane) * 8;
+    const int col = (i * 32 * WPR + wir * 32 + lane) * 8;
     if (col < cols) {
       Vec8<T>::load(gamma + col, gw[i]);
       if (beta != nullptr) Vec8<T>::load(beta + col, gb[i]);
@@ -60,14 +66,14 @@ __global__ void __launch_bounds__(WPR == 1 ? 128 : 32 * WPR) ln_fwd_kernel(
     }
   }
 
-  for (int row0 = blockIdx.x * ROWS_PER_CTA; row0 < rows; row0 += gridDim.x * ROWS_PER_CTA) {
-    const int row = row0 + row_in_cta;
+  for (int row0 = blockIdx.x * RG; row0 < rows; row0 += gridDim.x * RG) {
+    const int row = row0 + group;
     const bool row_ok = row < rows;
     float v[VPL][8];
     float s = 0.f;
 #pragma unroll
     for (int i = 0; i < VPL; ++i) {
-      const int col = (i * 32 * WPR + warp_in_row * 32 + lane) * 8;
+      const int col = (i * 32 * WPR + wir * 32 + lane) * 8;
       if (row_ok && col < cols) {
         const int64_t e = static_cast<int64_t>(row) * cols + col;
         Vec8<T>::load(x + e, v[i]);
@@ -102,21 +108,21 @@ __global__ void __launch_bounds__(WPR == 1 ? 128 : 32 * WPR) ln_fwd_kernel(
       }
     }
     float mean = 0.f;
-    if (!rms) mean = row_sum<WPR>(s, red) * inv_cols;
+    if (!rms) mean = row_sum<WPR>(s, red, group, wir) * inv_cols;
     float sq = 0.f;
 #pragma unroll
     for (int i = 0; i < VPL; ++i) {
-      const int col = (i * 32 * WPR + warp_in_row * 32 + lane) * 8;
+      const int col = (i * 32 * WPR + wir * 32 + lane) * 8;
       if (col < cols) {
 #pragma unroll
         for (int k = 0; k < 8; ++k) { const float d = v[i][k] - mean; sq += d * d; }
       }
     }
-    const float rstd = rsqrtf(row_sum<WPR>(sq, red) * inv_cols + eps);
+    const float rstd = rsqrtf(row_sum<WPR>(sq, red, group, wir) * inv_cols + eps);
     if (row_ok) {
 #pragma unroll
       for (int i = 0; i < VPL; ++i) {
-        const int col = (i * 32 * WPR + warp_in_row * 32 + lane) * 8;
+        const int col = (i * 32 * WPR + wir * 32 + lane) * 8;
         if (col < cols) {
           float o[8];
 #pragma unroll
@@ -124,7 +130,7 @@ __global__ void __launch_bounds__(WPR == 1 ? 128 : 32 * WPR) ln_fwd_kernel(
           Vec8<T>::store(y + static_cast<int64_t>(row) * cols + col, o);
         }
       }
-      if (lane == 0 && warp_in_row == 0) {
+      if (lane == 0 && wir == 0) {
         mean_out[row] = mean;
         rstd_out[row] = rstd;
       }
@@ -132,18 +138,16 @@ __global__ void __launch_bounds__(WPR == 1 ? 128 : 32 * WPR) ln_fwd_kernel(
   }
 }
 
-template <typename T, int VPL, int WPR>
-__global__ void __launch_bounds__(WPR == 1 ? 128 : 32 * WPR) ln_bwd_kernel(
+template <typename T, int VPL, int WPR, int RG>
+__global__ void __launch_bounds__(32 * WPR * RG) ln_bwd_kernel(
     const T* __restrict__ gy, const T* __restrict__ gz, const T* __restrict__ zin,
     const T* __restrict__ gamma, const float* __restrict__ mean_in,
     const float* __restrict__ rstd_in, T* __restrict__ dx, T* __restrict__ dres,
     float* __restrict__ partial, int rows, int cols, float p, PhiloxArgs rng, int rms,
     int want_dbias) {
-  __shared__ float red[WPR == 1 ? 1 : WPR];
-  constexpr int ROWS_PER_CTA = WPR == 1 ? 4 : 1;
+  __shared__ float red[WPR * RG];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int warp_in_row = WPR == 1 ? 0 : warp;
-  const int row_in_cta = WPR == 1 ? warp : 0;
+  const int group = warp / WPR, wir = warp % WPR;
   uint64_t seed = 0, offset = 0;
   if (p > 0.f) philox_unpack(rng, seed, offset);
   const float scale = 1.f / (1.f - p);
@@ -152,14 +156,14 @@ __global__ void __launch_bounds__(WPR == 1 ? 128 : 32 * WPR) ln_bwd_kernel(
   float gw[VPL][8], dgam[VPL][8], dbet[VPL][8], dbia[VPL][8];
 #pragma unroll
   for (int i = 0; i < VPL; ++i) {
-    const int col = (i * 32 * WPR + warp_in_row * 32 + lane) * 8;
+    const int col = (i * 32 * WPR + wir * 32 + lane) * 8;
     if (col < cols) Vec8<T>::load(gamma + col, gw[i]);
 #pragma unroll
     for (int k = 0; k < 8; ++k) { dgam[i][k] = 0.f; dbet[i][k] = 0.f; dbia[i][k] = 0.f; }
   }
 
-  for (int row0 = blockIdx.x * ROWS_PER_CTA; row0 < rows; row0 += gridDim.x * ROWS_PER_CTA) {
-    const int row = row0 + row_in_cta;
+  for (int row0 = blockIdx.x * RG; row0 < rows; row0 += gridDim.x * RG) {
+    const int row = row0 + group;
     const bool row_ok = row < rows;
     const float mean = row_ok ? mean_in[row] : 0.f;
     const float rstd = row_ok ? rstd_in[row] : 0.f;
@@ -167,7 +171,7 @@ __global__ void __launch_bounds__(WPR == 1 ? 128 : 32 * WPR) ln_bwd_kernel(
     float s1 = 0.f, s2 = 0.f;
 #pragma unroll
     for (int i = 0; i < VPL; ++i) {
-      const int col = (i * 32 * WPR + warp_in_row * 32 + lane) * 8;
+      const int col = (i * 32 * WPR + wir * 32 + lane) * 8;
       if (row_ok && col < cols) {
         const int64_t e = static_cast<int64_t>(row) * cols + col;
         Vec8<T>::load(gy + e, g[i]);
@@ -187,12 +191,12 @@ __global__ void __launch_bounds__(WPR == 1 ? 128 : 32 * WPR) ln_bwd_kernel(
       }
     }
     float m1 = 0.f;
-    if (!rms) m1 = row_sum<WPR>(s1, red) * inv_cols;
-    const float m2 = row_sum<WPR>(s2, red) * inv_cols;
+    if (!rms) m1 = row_sum<WPR>(s1, red, group, wir) * inv_cols;
+    const float m2 = row_sum<WPR>(s2, red, group, wir) * inv_cols;
     if (row_ok) {
 #pragma unroll
       for (int i = 0; i < VPL; ++i) {
-        const int col = (i * 32 * WPR + warp_in_row * 32 + lane) * 8;
+        const int col = (i * 32 * WPR + wir * 32 + lane) * 8;
         if (col < cols) {
           const int64_t e = static_cast<int64_t>(row) * cols + col;
           float d[8];
@@ -221,17 +225,19 @@ __global__ void __launch_bounds__(WPR == 1 ? 128 : 32 * WPR) ln_bwd_kernel(
     }
   }
 
-  // one partial row per CTA: [grid][3][cols]
+  // one partial row per CTA: [grid][3][cols]; row groups are combined in
+  // shared memory first
   float* out = partial + static_cast<int64_t>(blockIdx.x) * 3 * cols;
-  if constexpr (WPR == 1) {
-    __shared__ float acc[3][VPL * 256];
-    for (int i = threadIdx.x; i < 3 * VPL * 256; i += blockDim.x) (&acc[0][0])[i] = 0.f;
+  if constexpr (RG > 1) {
+    constexpr int kCap = 32 * WPR * VPL * 8;
+    __shared__ float acc[3][kCap];
+    for (int i = threadIdx.x; i < 3 * kCap; i += blockDim.x) (&acc[0][0])[i] = 0.f;
     __syncthreads();
 #pragma unroll
     for (int i = 0; i < VPL; ++i) {
 #pragma unroll
       for (int k = 0; k < 8; ++k) {
-        const int c = (i * 32 + lane) * 8 + k;
+        const int c = (i * 32 * WPR + wir * 32 + lane) * 8 + k;
         atomicAdd(&acc[0][c], dgam[i][k]);
         atomicAdd(&acc[1][c], dbet[i][k]);
         atomicAdd(&acc[2][c], dbia[i][k]);
@@ -246,7 +252,7 @@ __global__ void __launch_bounds__(WPR == 1 ? 128 : 32 * WPR) ln_bwd_kernel(
   } else {
 #pragma unroll
     for (int i = 0; i < VPL; ++i) {
-      const int col = (i * 32 * WPR + warp_in_row * 32 + lane) * 8;
+      const int col = (i * 32 * WPR + wir * 32 + lane) * 8;
       if (col < cols) {
         Vec8<float>::store(out + col, dgam[i]);
         Vec8<float>::store(out + cols + col, dbet[i]);
@@ -271,39 +277,40 @@ __global__ void ln_bwd_finalize_kernel(const float* __restrict__ partial, T* __r
 }
 
 // ------------------------------------------------------------------------ //
-struct LnShape { int vpl; int wpr; };
+struct LnShape { int vpl; int wpr; int rg; };
 
 static LnShape pick_shape(int cols) {
-  // few values per thread keeps the register footprint small, so many warps
-  // are resident and enough loads are in flight to saturate HBM
   const int vecs = cols / 8;
-  if (vecs <= 32) return {1, 1};
-  if (vecs <= 128) return {1, 4};
-  if (vecs <= 256) return {2, 4};
-  if (vecs <= 512) return {1, 16};
-  if (vecs <= 1024) return {2, 16};
-  return {4, 16};
+  if (vecs <= 32) return {1, 1, 4};
+  if (vecs <= 128) return {1, 4, 4};
+  if (vecs <= 256) return {2, 4, 4};
+  if (vecs <= 512) return {1, 16, 1};
+  if (vecs <= 1024) return {2, 16, 1};
+  return {4, 16, 1};
+}
+
+static int ln_grid(int rows, int cols, int ctas_per_sm) {
+  const LnShape s = pick_shape(cols);
+  const int want = (rows + s.rg - 1) / s.rg;
+  const int cap = sm_count() * ctas_per_sm;
+  return want < cap ? (want > 0 ? want : 1) : cap;
 }
 
 int ln_bwd_grid(int rows, int cols) {
   const LnShape s = pick_shape(cols);
-  const int rows_per_cta = s.wpr == 1 ? 4 : 1;
-  const int want = (rows + rows_per_cta - 1) / rows_per_cta;
-  const int cap = sm_count() * (s.wpr == 16 ? 2 : 4);
-  return want < cap ? (want > 0 ? want : 1) : cap;
+  return ln_grid(rows, cols, s.wpr * s.rg >= 16 ? 2 : 8);
 }
 
 #define LN_SHAPE_SWITCH(s, ...)                                                     \
   if (s.wpr == 1) {                                                                 \
-    constexpr int WPR = 1;                                                          \
-    constexpr int VPL = 1;                                                          \
+    constexpr int WPR = 1, RG = 4, VPL = 1;                                         \
     __VA_ARGS__;                                                                    \
   } else if (s.wpr == 4) {                                                          \
-    constexpr int WPR = 4;                                                          \
+    constexpr int WPR = 4, RG = 4;                                                  \
     if (s.vpl == 1) { constexpr int VPL = 1; __VA_ARGS__; }                         \
     else { constexpr int VPL = 2; __VA_ARGS__; }                                    \
   } else {                                                                          \
-    constexpr int WPR = 16;                                                         \
+    constexpr int WPR = 16, RG = 1;                                                 \
     if (s.vpl == 1) { constexpr int VPL = 1; __VA_ARGS__; }                         \
     else if (s.vpl == 2) { constexpr int VPL = 2; __VA_ARGS__; }                    \
     else { constexpr int VPL = 4; __VA_ARGS__; }                                    \
@@ -322,13 +329,10 @@ void launch_ln_fwd(const void* x, const void* bias, const void* residual, const 
                    cudaStream_t stream) {
   if (rows == 0) return;
   const LnShape s = pick_shape(cols);
-  const int rows_per_cta = s.wpr == 1 ? 4 : 1;
-  const int want = (rows + rows_per_cta - 1) / rows_per_cta;
-  const int cap = sm_count() * (s.wpr == 16 ? 4 : 16);
-  const int grid = want < cap ? want : cap;
+  const int grid = ln_grid(rows, cols, s.wpr * s.rg >= 16 ? 2 : 16);
   count_launch();
-  DISPATCH_DTYPE(dtype, LN_SHAPE_SWITCH(s, (ln_fwd_kernel<T, VPL, WPR>
-      <<<grid, WPR == 1 ? 128 : 32 * WPR, 0, stream>>>(
+  DISPATCH_DTYPE(dtype, LN_SHAPE_SWITCH(s, (ln_fwd_kernel<T, VPL, WPR, RG>
+      <<<grid, 32 * WPR * RG, 0, stream>>>(
           static_cast<const T*>(x), static_cast<const T*>(bias), static_cast<const T*>(residual),
           static_cast<const T*>(gamma), static_cast<const T*>(beta), static_cast<T*>(y),
           static_cast<T*>(z), mean, rstd, rows, cols, eps, p, rng, rms))));
@@ -343,8 +347,8 @@ void launch_ln_bwd(const void* gy, const void* gz, const void* zin, const void* 
   const int grid = ln_bwd_grid(rows, cols);
   const int want_dbias = dbias != nullptr;
   count_launch(2);
-  DISPATCH_DTYPE(dtype, LN_SHAPE_SWITCH(s, (ln_bwd_kernel<T, VPL, WPR>
-      <<<grid, WPR == 1 ? 128 : 32 * WPR, 0, stream>>>(
+  DISPATCH_DTYPE(dtype, LN_SHAPE_SWITCH(s, (ln_bwd_kernel<T, VPL, WPR, RG>
+      <<<grid, 32 * WPR * RG, 0, stream>>>(
           static_cast<const T*>(gy), static_cast<const T*>(gz), static_cast<const T*>(zin),
           static_cast<const T*>(gamma), mean, rstd, static_cast<T*>(dx), static_cast<T*>(dres),
           partial, rows, cols, p, rng, rms, want_dbias))));
