@@ -39,7 +39,7 @@ __device__ __forceinline__ float row_sum(float v, float* red, int group, int wir
 }
 
 template <typename T, int VPL, int WPR, int RG>
-__global__ void __launch_bounds__(32 * WPR * RG) ln_fwd_kernel(
+__global__ void __launch_bounds__(32 * WPR * RG, (VPL == 1 && WPR * RG == 16) ? 2 : 1) ln_fwd_kernel(
     const T* __restrict__ x, const T* __restrict__ bias, const T* __restrict__ residual,
     const T* __restrict__ gamma, const T* __restrict__ beta, T* __restrict__ y,
     T* __restrict__ z, float* __restrict__ mean_out, float* __restrict__ rstd_out, int rows,
@@ -139,7 +139,7 @@ __global__ void __launch_bounds__(32 * WPR * RG) ln_fwd_kernel(
 }
 
 template <typename T, int VPL, int WPR, int RG>
-__global__ void __launch_bounds__(32 * WPR * RG) ln_bwd_kernel(
+__global__ void __launch_bounds__(32 * WPR * RG, (VPL == 1 && WPR * RG == 16) ? 2 : 1) ln_bwd_kernel(
     const T* __restrict__ gy, const T* __restrict__ gz, const T* __restrict__ zin,
     const T* __restrict__ gamma, const float* __restrict__ mean_in,
     const float* __restrict__ rstd_in, T* __restrict__ dx, T* __restrict__ dres,
