@@ -1,0 +1,546 @@
+// Fused GEMM + collective kernels over NVLink peer memory (sm_100a).
+//
+// One persistent tcgen05 kernel (same pipeline as gemm.cu: TMA producer warp,
+// MMA warp, four epilogue warps, TMEM double buffering) extended so that the
+// collective which precedes or follows a tensor-parallel GEMM happens inside
+// the kernel, tile by tile, while the tensor core keeps working:
+//
+//   all-gather -> GEMM   an operand is "segmented": segment r lives in rank
+//                        r's symmetric buffer and is read in place with TMA
+//                        tile loads through a per-peer tensor map (plain tile
+//                        loads, this CTA's shared memory only).  Either the
+//                        rows of A (forward of a column-parallel layer under
+//                        sequence parallelism, dgrad of a row-parallel one) or
+//                        the contraction dimension of A or B (weight
+//                        gradients, where the gathered tensor is contracted).
+//   GEMM -> reduce-scatter   the epilogue pushes each 16-bit partial tile with
+//                        peer stores into the slot [owner][source] of the
+//                        owner rank's receive buffer; when a source has
+//                        finished a row block it releases a flag on the owner;
+//                        after its own tiles every CTA joins the reduction of
+//                        this rank's rows (fp32 sum over the p slots, optional
+//                        bias) - still the same launch.
+//   GEMM -> all-reduce   reduce-scatter as above, then the reduced rows are
+//                        pushed to every peer's output buffer and a second
+//                        flag round closes the operation.
+//
+// Flow control is an int32 flag pad in symmetric memory and one job-wide
+// monotone epoch number per fused operation (identical on all ranks):
+//   ready[src] >= epoch   rank src has entered this operation, i.e. everything
+//                         it launched before (producers of its buffers,
+//                         consumers of what we are about to overwrite) is done
+//   done[src]  >= epoch   rank src has delivered its contribution to my rows
+//   done2[src] >= epoch   rank src has delivered its reduced rows (all-reduce)
+// Every wait is bounded; on time-out the kernel records an error code in the
+// device status word, stops issuing work and leaves (TMEM freed).
+#include "common.cuh"
+#include "kernels.h"
+#include "tc05.cuh"
+
+namespace slapo {
+
+constexpr int kMaxRanks = 8;
+constexpr int CBM = 128;
+constexpr int CBK = 64;
+
+struct SegMaps {
+  CUtensorMap map[kMaxRanks];
+};
+
+enum CommMode { kModeLocal = 0, kModeReduceScatter = 1, kModeAllReduce = 2 };
+
+struct CommGemmParams {
+  int M, N, K;
+  int world, rank;
+  // operand gathering: 0 none, 1 rows of A (M), 2 contraction dim of A, 3 contraction dim of B
+  int gather;
+  int seg_len;          // extent of one rank's segment along the gathered dimension
+  int mode;
+  int epoch;
+  // local output (kModeLocal) or reduced output [M / world, N] (reduce-scatter) or [M, N] (all-reduce)
+  void* out;
+  int ldo;
+  const void* bias;     // added after the reduction (or in the plain epilogue)
+  int act;
+  int bf16;
+  uint32_t idesc;
+  // symmetric state
+  int* flags;                    // local pad: ready[8] | done[8] | done2[8] | counters[8]
+  int* peer_flags[kMaxRanks];    // the same pad on every rank
+  void* peer_recv[kMaxRanks];    // receive buffers [world][M / world, N] 16-bit
+  void* peer_out[kMaxRanks];     // all-reduce output buffers [M, N]
+  int* status;
+  long long wait_cycles;         // budget of a cross-GPU wait
+};
+
+__device__ __forceinline__ void st_release_sys(int* addr, int v) {
+  asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(addr), "r"(v) : "memory");
+}
+__device__ __forceinline__ int ld_acquire_sys(const int* addr) {
+  int v;
+  asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(addr) : "memory");
+  return v;
+}
+
+// bounded spin on a flag written by another GPU
+__device__ __forceinline__ bool wait_flag(const int* addr, int epoch, long long budget,
+                                          volatile int* abort_flag) {
+  if (ld_acquire_sys(addr) >= epoch) return true;
+  const long long start = clock64();
+  int spins = 0;
+  while (ld_acquire_sys(addr) < epoch) {
+    if ((++spins & 0x3f) == 0) {
+      if (*abort_flag != 0) return false;
+      if (clock64() - start > budget) {
+        *abort_flag = 1;
+        return false;
+      }
+    }
+    __nanosleep(64);
+  }
+  return true;
+}
+
+template <int BN, int STAGES>
+struct CommSmem {
+  static constexpr int kABytes = CBM * CBK * 2;
+  static constexpr int kBBytes = BN * CBK * 2;
+  static constexpr int kBarOffset = STAGES * (kABytes + kBBytes);
+  static constexpr int kTotal = kBarOffset + 256 + 1024;
+};
+
+__device__ __forceinline__ uint32_t cpack2(float a, float b, int bf16) {
+  if (bf16) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(a, b);
+    return *reinterpret_cast<uint32_t*>(&v);
+  }
+  __half2 v = __floats2half2_rn(a, b);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+__device__ __forceinline__ float cload(const void* p, int64_t i, int bf16) {
+  if (bf16) return __bfloat162float(static_cast<const __nv_bfloat16*>(p)[i]);
+  return __half2float(static_cast<const __half*>(p)[i]);
+}
+
+// Tile order: row blocks are visited owner by owner starting with the rank
+// after this one (its data has the longest way to go) and ending with the
+// local block; inside an owner, row blocks then column tiles.
+__device__ __forceinline__ void tile_coords(int t, int tiles_n, int blocks_per_owner, int world,
+                                            int rank, bool rotate, int& m_blk, int& n_blk) {
+  n_blk = t % tiles_n;
+  int mb = t / tiles_n;
+  if (rotate) {
+    const int o_idx = mb / blocks_per_owner;
+    const int owner = (rank + 1 + o_idx) % world;
+    mb = owner * blocks_per_owner + mb % blocks_per_owner;
+  }
+  m_blk = mb;
+}
+
+template <int BN, int STAGES, bool A_MN, bool B_MN>
+__global__ void __launch_bounds__(192, 1)
+comm_gemm_kernel(const __grid_constant__ SegMaps maps_a, const __grid_constant__ SegMaps maps_b,
+                 const CommGemmParams p) {
+  using S = CommSmem<BN, STAGES>;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>(
+      (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
+  uint8_t* smem_a = smem;
+  uint8_t* smem_b = smem + STAGES * S::kABytes;
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + S::kBarOffset);
+  uint64_t* empty_bar = full_bar + STAGES;
+  uint64_t* tmem_full = empty_bar + STAGES;
+  uint64_t* tmem_empty = tmem_full + 2;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tmem_empty + 2);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int tiles_m = (p.M + CBM - 1) / CBM;
+  const int tiles_n = (p.N + BN - 1) / BN;
+  const int num_tiles = tiles_m * tiles_n;
+  const int num_kb = (p.K + CBK - 1) / CBK;
+  const bool scatter = p.mode != kModeLocal;
+  const int rows_per_rank = p.M / p.world;               // used when rows are owned (gather 1 / scatter)
+  const bool rotate = p.world > 1 && (scatter || p.gather == 1) && rows_per_rank % CBM == 0;
+  const int blocks_per_owner = rotate ? rows_per_rank / CBM : tiles_m;
+  constexpr uint32_t kTmemCols = 2 * BN <= 128 ? 128 : (2 * BN <= 256 ? 256 : 512);
+
+  int* ready = p.flags;
+  int* done = p.flags + 8;
+  int* done2 = p.flags + 16;
+  int* counters = p.flags + 24;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      tc::mbar_init(&full_bar[s], 1);
+      tc::mbar_init(&empty_bar[s], 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      tc::mbar_init(&tmem_full[a], 1);
+      tc::mbar_init(&tmem_empty[a], 4);
+    }
+    *abort_flag = 0;
+    tc::fence_barrier_init();
+    // announce: this rank has entered operation `epoch`
+    if (blockIdx.x == 0 && p.world > 1) {
+      for (int r = 0; r < p.world; ++r) st_release_sys(p.peer_flags[r] + p.rank, p.epoch);
+    }
+  }
+  if (warp == 1) {
+    tc::tmem_alloc(tmem_slot, kTmemCols);
+    tc::tmem_relinquish();
+  }
+  tc::fence_before_sync();
+  __syncthreads();
+  tc::fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ------------------------------ TMA producer ------------------------------
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      uint32_t seen_ready = 1u << p.rank;  // peers whose ready flag has been observed
+      auto need_ready = [&](int r) -> bool {
+        if (seen_ready & (1u << r)) return true;
+        if (!wait_flag(ready + r, p.epoch, p.wait_cycles, abort_flag)) return false;
+        // order the flag observation before the TMA engine's reads of that peer
+        asm volatile("fence.proxy.async;" ::: "memory");
+        seen_ready |= 1u << r;
+        return true;
+      };
+      for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+        int m_blk, n_blk;
+        tile_coords(t, tiles_n, blocks_per_owner, p.world, p.rank, rotate, m_blk, n_blk);
+        const int m0 = m_blk * CBM, n0 = n_blk * BN;
+        int a_seg = 0, a_row = m0;
+        if (p.gather == 1) {
+          a_seg = m0 / p.seg_len;
+          a_row = m0 - a_seg * p.seg_len;
+          if (!need_ready(a_seg)) { ok = false; break; }
+        }
+        for (int kb = 0; kb < num_kb; ++kb) {
+          int k_a = kb * CBK, k_b = kb * CBK, seg_a = a_seg, seg_b = 0;
+          if (p.gather == 2) {
+            seg_a = k_a / p.seg_len;
+            k_a -= seg_a * p.seg_len;
+            if (!need_ready(seg_a)) { ok = false; break; }
+          } else if (p.gather == 3) {
+            seg_b = k_b / p.seg_len;
+            k_b -= seg_b * p.seg_len;
+            if (!need_ready(seg_b)) { ok = false; break; }
+          }
+          if (!tc::mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag)) { ok = false; break; }
+          tc::mbar_arrive_expect_tx(&full_bar[stage], S::kABytes + S::kBBytes);
+          uint8_t* sa = smem_a + stage * S::kABytes;
+          uint8_t* sb = smem_b + stage * S::kBBytes;
+          const CUtensorMap* ta = &maps_a.map[seg_a];
+          const CUtensorMap* tb = &maps_b.map[seg_b];
+          if constexpr (!A_MN) {
+            tc::tma_load_2d(sa, ta, &full_bar[stage], k_a, a_row);
+          } else {
+#pragma unroll
+            for (int j = 0; j < CBM / 64; ++j)
+              tc::tma_load_2d(sa + j * (CBK * 128), ta, &full_bar[stage], a_row + j * 64, k_a);
+          }
+          if constexpr (!B_MN) {
+            tc::tma_load_2d(sb, tb, &full_bar[stage], k_b, n0);
+          } else {
+#pragma unroll
+            for (int j = 0; j < BN / 64; ++j)
+              tc::tma_load_2d(sb + j * (CBK * 128), tb, &full_bar[stage], n0 + j * 64, k_b);
+          }
+          if (++stage == STAGES) { stage = 0; phase ^= 1; }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------ MMA issuer --------------------------------
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      int iter = 0;
+      bool ok = true;
+      for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, ++iter) {
+        const int acc = iter & 1;
+        const uint32_t acc_phase = (iter >> 1) & 1;
+        if (!tc::mbar_wait(&tmem_empty[acc], acc_phase ^ 1, abort_flag)) { ok = false; break; }
+        tc::fence_after_sync();
+        const uint32_t d_tmem = tmem_base + acc * BN;
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!tc::mbar_wait(&full_bar[stage], phase, abort_flag)) { ok = false; break; }
+          tc::fence_after_sync();
+          const uint32_t a_addr = tc::smem_u32(smem_a + stage * S::kABytes);
+          const uint32_t b_addr = tc::smem_u32(smem_b + stage * S::kBBytes);
+#pragma unroll
+          for (int k = 0; k < CBK / 16; ++k) {
+            const uint64_t a_desc = A_MN ? tc::smem_desc(a_addr + k * 2048, CBK * 128, 1024)
+                                         : tc::smem_desc(a_addr + k * 32, 16, 1024);
+            const uint64_t b_desc = B_MN ? tc::smem_desc(b_addr + k * 2048, CBK * 128, 1024)
+                                         : tc::smem_desc(b_addr + k * 32, 16, 1024);
+            tc::umma_f16(d_tmem, a_desc, b_desc, p.idesc, (kb | k) != 0 ? 1u : 0u);
+          }
+          tc::umma_commit(&empty_bar[stage]);
+          if (++stage == STAGES) { stage = 0; phase ^= 1; }
+        }
+        if (ok) tc::umma_commit(&tmem_full[acc]);
+      }
+    }
+  } else {
+    // ------------------------------ epilogue ----------------------------------
+    const int quarter = warp & 3;
+    int iter = 0;
+    bool ok = true;
+    uint32_t seen_ready = 1u << p.rank;
+    const int tiles_per_owner = blocks_per_owner * tiles_n;
+    for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, ++iter) {
+      int m_blk, n_blk;
+      tile_coords(t, tiles_n, blocks_per_owner, p.world, p.rank, rotate, m_blk, n_blk);
+      const int m0 = m_blk * CBM, n0 = n_blk * BN;
+      const int acc = iter & 1;
+      const uint32_t acc_phase = (iter >> 1) & 1;
+      int owner = p.rank;
+      uint8_t* dst_base;
+      int64_t dst_ld;
+      int row_off = 0;
+      if (scatter) {
+        owner = m0 / rows_per_rank;
+        // slot [owner][source = this rank] of the owner's receive buffer
+        dst_base = static_cast<uint8_t*>(p.peer_recv[owner]) +
+                   static_cast<int64_t>(p.rank) * rows_per_rank * p.N * 2;
+        dst_ld = p.N;
+        row_off = owner * rows_per_rank;
+        if (!(seen_ready & (1u << owner))) {
+          // the owner must have left its previous consumers of the buffer
+          bool w = true;
+          if (lane == 0) w = wait_flag(ready + owner, p.epoch, p.wait_cycles, abort_flag);
+          w = __shfl_sync(0xffffffffu, w ? 1 : 0, 0) != 0;
+          if (!w) { ok = false; break; }
+          seen_ready |= 1u << owner;
+        }
+      } else {
+        dst_base = static_cast<uint8_t*>(p.out);
+        dst_ld = p.ldo;
+      }
+      if (!tc::mbar_wait_warp(&tmem_full[acc], acc_phase, abort_flag)) { ok = false; break; }
+      tc::fence_after_sync();
+      const int row = m0 + quarter * 32 + lane;
+      const uint32_t t_row = tmem_base + acc * BN + (static_cast<uint32_t>(quarter * 32) << 16);
+#pragma unroll 1
+      for (int c = 0; c < BN / 32; ++c) {
+        uint32_t r[32];
+        tc::tmem_ld_x32(t_row + c * 32, r);
+        tc::tmem_ld_wait();
+        const int col0 = n0 + c * 32;
+        if (row < p.M && col0 < p.N) {
+          uint32_t packed[16];
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            float v0 = __uint_as_float(r[2 * j]);
+            float v1 = __uint_as_float(r[2 * j + 1]);
+            if (!scatter) {
+              if (p.bias != nullptr) {
+                const int cc = min(col0 + 2 * j, p.N - 2);
+                v0 += cload(p.bias, cc, p.bf16);
+                v1 += cload(p.bias, cc + 1, p.bf16);
+              }
+              if (p.act >= 0) {
+                v0 = act_fwd(v0, p.act);
+                v1 = act_fwd(v1, p.act);
+              }
+            }
+            packed[j] = cpack2(v0, v1, p.bf16);
+          }
+          uint8_t* dst = dst_base + (static_cast<int64_t>(row - row_off) * dst_ld + col0) * 2;
+#pragma unroll
+          for (int v = 0; v < 4; ++v) {
+            if (col0 + v * 8 < p.N)
+              *reinterpret_cast<uint4*>(dst + v * 16) =
+                  make_uint4(packed[4 * v], packed[4 * v + 1], packed[4 * v + 2], packed[4 * v + 3]);
+          }
+        }
+      }
+      tc::fence_before_sync();
+      __syncwarp();
+      if (lane == 0) tc::mbar_arrive(&tmem_empty[acc]);
+      if (scatter) {
+        // publish: make this warp's peer stores visible, count it; the warp
+        // that completes the owner's row block releases the owner's flag
+        __threadfence_system();
+        __syncwarp();
+        if (lane == 0) {
+          const int prev = atomicAdd(counters + owner, 1);
+          if (prev + 1 == tiles_per_owner * 4) {
+            atomicExch(counters + owner, 0);
+            __threadfence_system();
+            st_release_sys(p.peer_flags[owner] + 8 + p.rank, p.epoch);
+          }
+        }
+      }
+    }
+  }
+
+  // ------------------------------ reduction phase --------------------------------
+  tc::fence_before_sync();
+  __syncthreads();
+  if (scatter && *abort_flag == 0) {
+    __shared__ int s_ok;
+    if (threadIdx.x == 0) {
+      int okk = 1;
+      for (int r = 0; r < p.world && okk; ++r)
+        if (!wait_flag(done + r, p.epoch, p.wait_cycles, abort_flag)) okk = 0;
+      s_ok = okk;
+    }
+    __syncthreads();
+    if (s_ok) {
+      const int64_t vec_per_row = p.N / 8;
+      const int64_t n_vec = static_cast<int64_t>(rows_per_rank) * vec_per_row;
+      const int64_t slot = static_cast<int64_t>(rows_per_rank) * p.N;  // elements per source slot
+      const uint8_t* recv = static_cast<const uint8_t*>(p.peer_recv[p.rank]);
+      for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < n_vec;
+           i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+        const int64_t e = i * 8;
+        float acc8[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+        for (int r = 0; r < p.world; ++r) {
+          float v[8];
+          if (p.bf16) Vec8<__nv_bfloat16>::load(reinterpret_cast<const __nv_bfloat16*>(recv) + r * slot + e, v);
+          else Vec8<__half>::load(reinterpret_cast<const __half*>(recv) + r * slot + e, v);
+#pragma unroll
+          for (int k = 0; k < 8; ++k) acc8[k] += v[k];
+        }
+        const int col = static_cast<int>(e % p.N);
+        if (p.bias != nullptr) {
+#pragma unroll
+          for (int k = 0; k < 8; ++k) acc8[k] += cload(p.bias, col + k, p.bf16);
+        }
+        if (p.act >= 0) {
+#pragma unroll
+          for (int k = 0; k < 8; ++k) acc8[k] = act_fwd(acc8[k], p.act);
+        }
+        const int64_t lrow = e / p.N;
+        if (p.mode == kModeReduceScatter) {
+          void* o = static_cast<uint8_t*>(p.out) + (lrow * p.ldo + col) * 2;
+          if (p.bf16) Vec8<__nv_bfloat16>::store(static_cast<__nv_bfloat16*>(o), acc8);
+          else Vec8<__half>::store(static_cast<__half*>(o), acc8);
+        } else {
+          // all-reduce: the reduced rows go to every rank's output buffer
+          const int64_t grow = static_cast<int64_t>(p.rank) * rows_per_rank + lrow;
+          for (int r = 0; r < p.world; ++r) {
+            const int peer = (p.rank + r) % p.world;
+            void* o = static_cast<uint8_t*>(p.peer_out[peer]) + (grow * p.ldo + col) * 2;
+            if (p.bf16) Vec8<__nv_bfloat16>::store(static_cast<__nv_bfloat16*>(o), acc8);
+            else Vec8<__half>::store(static_cast<__half*>(o), acc8);
+          }
+        }
+      }
+      if (p.mode == kModeAllReduce) {
+        // close the all-gather half: count CTAs, the last one releases done2
+        __threadfence_system();
+        __syncthreads();
+        if (threadIdx.x == 0) {
+          const int prev = atomicAdd(counters + 8, 1);
+          if (prev + 1 == static_cast<int>(gridDim.x)) {
+            atomicExch(counters + 8, 0);
+            __threadfence_system();
+            for (int r = 0; r < p.world; ++r) st_release_sys(p.peer_flags[r] + 16 + p.rank, p.epoch);
+          }
+          int okk = 1;
+          for (int r = 0; r < p.world && okk; ++r)
+            if (!wait_flag(done2 + r, p.epoch, p.wait_cycles, abort_flag)) okk = 0;
+        }
+        __syncthreads();
+      }
+    }
+  }
+
+  // ------------------------------ teardown ------------------------------------
+  __syncthreads();
+  if (threadIdx.x == 0 && *abort_flag != 0 && p.status != nullptr) atomicExch(p.status, 4);
+  if (warp == 1) {
+    tc::fence_after_sync();
+    tc::tmem_dealloc(tmem_base, kTmemCols);
+  }
+}
+
+// ------------------------------------------------------------------------ //
+template <int BN, int STAGES, bool A_MN, bool B_MN>
+static int launch_comm_variant(const SegMaps& ma, const SegMaps& mb, const CommGemmParams& p,
+                               cudaStream_t stream) {
+  using S = CommSmem<BN, STAGES>;
+  auto kernel = comm_gemm_kernel<BN, STAGES, A_MN, B_MN>;
+  static bool configured = false;
+  if (!configured) {
+    if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, S::kTotal) !=
+        cudaSuccess)
+      return 3;
+    configured = true;
+  }
+  const int tiles = ((p.M + CBM - 1) / CBM) * ((p.N + BN - 1) / BN);
+  int grid = tiles < sm_count() ? tiles : sm_count();
+  if (p.mode != kModeLocal) grid = sm_count();  // all CTAs take part in the reduction
+  count_launch();
+  kernel<<<grid, 192, S::kTotal, stream>>>(ma, mb, p);
+  return cudaGetLastError() == cudaSuccess ? 0 : 4;
+}
+
+// a_ptrs / b_ptrs: one base pointer per segment (rank) when the operand is
+// gathered, else only entry 0 is used.  Shapes follow gemm.cu (a_mn / b_mn).
+int launch_comm_gemm(void* const* a_ptrs, void* const* b_ptrs, int M, int N, int K, int lda,
+                     int ldb, bool a_mn, bool b_mn, bool bf16, int gather, int seg_len, int mode,
+                     int world, int rank, int epoch, void* out, int ldo, const void* bias, int act,
+                     int* flags, int* const* peer_flags, void* const* peer_recv,
+                     void* const* peer_out, int* status, double wait_seconds,
+                     cudaStream_t stream) {
+  if (M <= 0 || N <= 0 || K <= 0) return 0;
+  if (N % 8 || K % 8 || lda % 8 || ldb % 8 || ldo % 8) return 1;
+  if (world < 1 || world > kMaxRanks) return 1;
+  if (a_mn && M % 8) return 1;
+  if (mode != kModeLocal && (M % world != 0 || (M / world) % CBM != 0)) return 1;
+  if (gather == 1 && (seg_len % CBM != 0 || seg_len * world != M)) return 1;
+  if ((gather == 2 || gather == 3) && (seg_len % CBK != 0 || seg_len * world != K)) return 1;
+  const int BN = N > 128 ? 256 : (N > 64 ? 128 : 64);
+  SegMaps ma, mb;
+  const int a_segs = (gather == 1 || gather == 2) ? world : 1;
+  const int b_segs = gather == 3 ? world : 1;
+  for (int s = 0; s < a_segs; ++s) {
+    // extents of one segment
+    const uint64_t rows = gather == 1 ? seg_len : M;
+    const uint64_t kk = gather == 2 ? seg_len : K;
+    const bool ok = a_mn ? make_tmap_2d(&ma.map[s], a_ptrs[s], rows, kk, lda, 64, CBK, 2, bf16)
+                         : make_tmap_2d(&ma.map[s], a_ptrs[s], kk, rows, lda, 64, CBM, 2, bf16);
+    if (!ok) return 2;
+  }
+  for (int s = 0; s < b_segs; ++s) {
+    const uint64_t kk = gather == 3 ? seg_len : K;
+    const bool ok = b_mn ? make_tmap_2d(&mb.map[s], b_ptrs[s], N, kk, ldb, 64, CBK, 2, bf16)
+                         : make_tmap_2d(&mb.map[s], b_ptrs[s], kk, N, ldb, 64, BN, 2, bf16);
+    if (!ok) return 2;
+  }
+  CommGemmParams p{};
+  p.M = M; p.N = N; p.K = K; p.world = world; p.rank = rank; p.gather = gather;
+  p.seg_len = seg_len > 0 ? seg_len : 1; p.mode = mode; p.epoch = epoch; p.out = out; p.ldo = ldo;
+  p.bias = bias; p.act = act; p.bf16 = bf16 ? 1 : 0; p.flags = flags; p.status = status;
+  p.idesc = tc::instr_desc_f16(CBM, BN, bf16 ? 1 : 0, a_mn, b_mn);
+  p.wait_cycles = static_cast<long long>(wait_seconds * 1.9e9);
+  for (int r = 0; r < world; ++r) {
+    p.peer_flags[r] = peer_flags != nullptr ? peer_flags[r] : flags;
+    p.peer_recv[r] = peer_recv != nullptr ? peer_recv[r] : nullptr;
+    p.peer_out[r] = peer_out != nullptr ? peer_out[r] : nullptr;
+  }
+
+#define COMM_CASE(BN_, ST_)                                                                   \
+  if (BN == BN_) {                                                                            \
+    if (!a_mn && !b_mn) return launch_comm_variant<BN_, ST_, false, false>(ma, mb, p, stream); \
+    if (!a_mn && b_mn) return launch_comm_variant<BN_, ST_, false, true>(ma, mb, p, stream);   \
+    if (a_mn && !b_mn) return launch_comm_variant<BN_, ST_, true, false>(ma, mb, p, stream);   \
+    return launch_comm_variant<BN_, ST_, true, true>(ma, mb, p, stream);                       \
+  }
+  COMM_CASE(256, 4)
+  COMM_CASE(128, 6)
+  COMM_CASE(64, 8)
+#undef COMM_CASE
+  return 1;
+}
+
+}  // namespace slapo

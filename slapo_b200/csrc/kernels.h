@@ -45,6 +45,16 @@ void launch_ce_grad(const void* logits, const int64_t* labels, const float* lse,
 void launch_sq_norm(const void* x, const uint8_t* mask, float* out2, int64_t n, int dtype,
                     cudaStream_t stream);
 
+// Fused GEMM + collective over peer memory (comm_gemm.cu).
+//   gather: 0 none, 1 rows of A, 2 contraction dim of A, 3 contraction dim of B
+//   mode:   0 local output, 1 reduce-scatter, 2 all-reduce
+int launch_comm_gemm(void* const* a_ptrs, void* const* b_ptrs, int M, int N, int K, int lda,
+                     int ldb, bool a_mn, bool b_mn, bool bf16, int gather, int seg_len, int mode,
+                     int world, int rank, int epoch, void* out, int ldo, const void* bias, int act,
+                     int* flags, int* const* peer_flags, void* const* peer_recv,
+                     void* const* peer_out, int* status, double wait_seconds,
+                     cudaStream_t stream);
+
 }  // namespace slapo
 
 #include "common_host.h"

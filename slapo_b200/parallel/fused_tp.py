@@ -1,0 +1,212 @@
+"""Tensor-parallel linear layers on the fused GEMM+collective kernels.
+
+Three differentiable ops replace "collective, then GEMM" / "GEMM, then
+collective" pairs that ``shard`` + ``sync`` describe:
+
+=================  ==========================  =====================================
+op                 forward                     backward
+=================  ==========================  =====================================
+``ag_linear``      Y = all_gather(Xs) W^T      dXs = reduce_scatter(dY W)   (fused)
+                   (gather inside the GEMM)    dW  = dY^T all_gather(Xs)    (fused)
+``rs_linear``      Ys = reduce_scatter(X W^T)  dX  = all_gather(dYs) W      (fused)
+                   (+ bias after reduction)    dW  = all_gather(dYs)^T X    (fused)
+``ar_linear``      Y = all_reduce(X W^T)       dX  = dY W,  dW = dY^T X     (local)
+=================  ==========================  =====================================
+
+Activations are 2-D ``[tokens, features]``; the sharded ("sequence-parallel")
+dimension is the token dimension, i.e. rank r holds rows ``[r*T/p, (r+1)*T/p)``.
+``ctx`` is a :class:`~slapo_b200.parallel.symm.SymmContext` (or the local
+stand-in used by the single-GPU tests).  Every op takes the next epoch of the
+context, so all ranks must issue the same ops in the same order - which the
+SPMD schedules do.
+
+Reference behaviour being replaced: slapo/sharding/sync_ops.py:13-87 (blocking
+NCCL collectives around cuBLAS GEMMs) and slapo/op/linear.py:105-111
+(matmul -> sync -> bias).
+"""
+from __future__ import annotations
+
+import torch
+
+from ..ops import native
+
+GATHER_NONE, GATHER_A_ROWS, GATHER_A_K, GATHER_B_K = 0, 1, 2, 3
+MODE_LOCAL, MODE_RS, MODE_AR = 0, 1, 2
+
+
+def supported(x: torch.Tensor) -> bool:
+    return (torch.is_tensor(x) and x.is_cuda and x.dtype in (torch.bfloat16, torch.float16)
+            and native.available() and hasattr(torch.ops.slapo_b200, "comm_gemm"))
+
+
+def _check_status():
+    code = int(native.ops().device_status())
+    if code:
+        raise RuntimeError(f"fused kernel reported error code {code}: a bounded wait on a peer "
+                           "ran out (a rank is missing or stuck)")
+
+
+def comm_gemm(ctx, *, a_ptrs, b_ptrs, M, N, K, lda, ldb, a_mn, b_mn, dtype, gather=GATHER_NONE,
+              seg_len=0, mode=MODE_LOCAL, out_ptr=0, ldo=0, bias=None, act=-1, recv=None,
+              ar_out=None):
+    """Thin wrapper of ``torch.ops.slapo_b200.comm_gemm``; takes the next epoch."""
+    epoch = ctx.next_epoch()
+    native.ops().comm_gemm(
+        [int(p) for p in a_ptrs], [int(p) for p in b_ptrs], M, N, K, lda, ldb, a_mn, b_mn,
+        dtype == torch.bfloat16, gather, seg_len, mode, ctx.world, ctx.rank, epoch, int(out_ptr),
+        ldo, bias.data_ptr() if bias is not None else 0, act, ctx.flags_ptr,
+        list(ctx.peer_flag_ptrs), list(recv.ptrs()) if recv is not None else [],
+        list(ar_out.ptrs()) if ar_out is not None else [], float(ctx.wait_seconds))
+    return epoch
+
+
+def _stage(ctx, name, t: torch.Tensor):
+    """Copy a local tensor into the symmetric buffer ``name`` (peers read it)."""
+    buf = ctx.buffer(name, t.numel() * t.element_size())
+    buf.view(t.dtype, tuple(t.shape)).copy_(t)
+    return buf
+
+
+# ---------------------------------------------------------------------- #
+def ag_gemm(ctx, x_shard, w, bias=None, act=-1, name="ag_in", staged=None):
+    """``all_gather(x_shard) @ w.T`` with the gather inside the GEMM."""
+    ts, k = x_shard.shape
+    n = w.shape[0]
+    t = ts * ctx.world
+    buf = staged if staged is not None else _stage(ctx, name, x_shard)
+    y = torch.empty(t, n, dtype=x_shard.dtype, device=x_shard.device)
+    comm_gemm(ctx, a_ptrs=buf.ptrs(), b_ptrs=[w.data_ptr()], M=t, N=n, K=k, lda=k,
+              ldb=w.stride(0), a_mn=False, b_mn=False, dtype=x_shard.dtype,
+              gather=GATHER_A_ROWS, seg_len=ts, out_ptr=y.data_ptr(), ldo=n, bias=bias, act=act)
+    return y
+
+
+def gemm_rs(ctx, x, w, bias=None, b_mn=False, name="rs_recv"):
+    """``reduce_scatter(x @ w.T)`` (rows) with the scatter in the epilogue;
+    ``bias`` is added once, after the reduction.  ``b_mn``: ``w`` is ``[K, N]``."""
+    t, k = x.shape
+    n = w.shape[1] if b_mn else w.shape[0]
+    recv = ctx.buffer(name, t * n * x.element_size())
+    y = torch.empty(t // ctx.world, n, dtype=x.dtype, device=x.device)
+    comm_gemm(ctx, a_ptrs=[x.data_ptr()], b_ptrs=[w.data_ptr()], M=t, N=n, K=k, lda=x.stride(0),
+              ldb=w.stride(0), a_mn=False, b_mn=b_mn, dtype=x.dtype, mode=MODE_RS,
+              out_ptr=y.data_ptr(), ldo=n, bias=bias, recv=recv)
+    return y
+
+
+def gemm_ar(ctx, x, w, bias=None, b_mn=False, name="ar"):
+    """``all_reduce(x @ w.T)``: reduce-scatter + all-gather halves in one kernel."""
+    t, k = x.shape
+    n = w.shape[1] if b_mn else w.shape[0]
+    recv = ctx.buffer(name + "_recv", t * n * x.element_size())
+    out = ctx.buffer(name + "_out", t * n * x.element_size())
+    comm_gemm(ctx, a_ptrs=[x.data_ptr()], b_ptrs=[w.data_ptr()], M=t, N=n, K=k, lda=x.stride(0),
+              ldb=w.stride(0), a_mn=False, b_mn=b_mn, dtype=x.dtype, mode=MODE_AR,
+              out_ptr=0, ldo=n, bias=bias, recv=recv, ar_out=out)
+    # the symmetric output is reused by the next all-reduce: hand out a copy
+    return out.view(x.dtype, (t, n)).clone()
+
+
+# ---------------------------------------------------------------------- #
+class _AGLinear(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x_shard, w, bias, sctx):
+        ctx.sctx = sctx
+        ctx.save_for_backward(x_shard, w)
+        ctx.has_bias = bias is not None
+        return ag_gemm(sctx, x_shard.contiguous(), w, bias)
+
+    @staticmethod
+    def backward(ctx, dy):
+        x_shard, w = ctx.saved_tensors
+        sctx = ctx.sctx
+        dy = dy.contiguous()
+        # dXs = reduce_scatter(dY @ W):  B = W read N-major ([N_local, K] = [contraction, out])
+        dx = gemm_rs(sctx, dy, w, None, b_mn=True, name="rs_recv_bwd")
+        # dW = dY^T @ all_gather(Xs): A = dY M-major, B = X gathered along the contraction
+        ts, k = x_shard.shape
+        n = w.shape[0]
+        staged = _stage(sctx, "ag_in_bwd", x_shard.contiguous())
+        dw = torch.empty_like(w)
+        comm_gemm(sctx, a_ptrs=[dy.data_ptr()], b_ptrs=staged.ptrs(), M=n, N=k, K=ts * sctx.world,
+                  lda=dy.stride(0), ldb=k, a_mn=True, b_mn=True, dtype=dy.dtype,
+                  gather=GATHER_B_K, seg_len=ts, out_ptr=dw.data_ptr(), ldo=k)
+        db = dy.float().sum(0).to(dy.dtype) if ctx.has_bias else None
+        return dx, dw, db, None
+
+
+class _RSLinear(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, w, bias, sctx):
+        ctx.sctx = sctx
+        ctx.save_for_backward(x, w)
+        ctx.has_bias = bias is not None
+        return gemm_rs(sctx, x.contiguous(), w, bias)
+
+    @staticmethod
+    def backward(ctx, dy_shard):
+        x, w = ctx.saved_tensors
+        sctx = ctx.sctx
+        dy_shard = dy_shard.contiguous()
+        ts, n = dy_shard.shape
+        t, kl = x.shape
+        staged = _stage(sctx, "ag_dy_bwd", dy_shard)
+        # dX = all_gather(dYs) @ W: A rows gathered, B = W read N-major
+        dx = torch.empty(t, kl, dtype=x.dtype, device=x.device)
+        comm_gemm(sctx, a_ptrs=staged.ptrs(), b_ptrs=[w.data_ptr()], M=t, N=kl, K=n, lda=n,
+                  ldb=w.stride(0), a_mn=False, b_mn=True, dtype=x.dtype, gather=GATHER_A_ROWS,
+                  seg_len=ts, out_ptr=dx.data_ptr(), ldo=kl)
+        # dW = all_gather(dYs)^T @ X: A gathered along the contraction (M-major), B = X N-major
+        dw = torch.empty_like(w)
+        comm_gemm(sctx, a_ptrs=staged.ptrs(), b_ptrs=[x.data_ptr()], M=n, N=kl, K=t, lda=n,
+                  ldb=x.stride(0), a_mn=True, b_mn=True, dtype=x.dtype, gather=GATHER_A_K,
+                  seg_len=ts, out_ptr=dw.data_ptr(), ldo=kl)
+        # the bias is added on the owner's rows only: its gradient is partial
+        # (tagged replicated_param -> summed over the group by the engine)
+        db = dy_shard.float().sum(0).to(dy_shard.dtype) if ctx.has_bias else None
+        return dx, dw, db, None
+
+
+class _ARLinear(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, w, bias, sctx):
+        ctx.save_for_backward(x, w)
+        ctx.has_bias = bias is not None
+        return gemm_ar(sctx, x.contiguous(), w, bias)
+
+    @staticmethod
+    def backward(ctx, dy):
+        x, w = ctx.saved_tensors
+        dx = dy @ w
+        dw = dy.t() @ x
+        db = dy.float().sum(0).to(dy.dtype) if ctx.has_bias else None
+        return dx, dw, db, None
+
+
+def _as_2d(x):
+    return x.reshape(-1, x.shape[-1])
+
+
+def ag_linear(x_shard, w, bias, sctx):
+    """Column-parallel linear under token (sequence) parallelism.  ``x_shard``
+    is ``[..., K]`` with this rank's tokens; returns all tokens ``[..., N_local]``
+    (the leading dimension grows by the group size)."""
+    lead = x_shard.shape[:-1]
+    y = _AGLinear.apply(_as_2d(x_shard), w, bias, sctx)
+    return y.view((lead[0] * sctx.world,) + tuple(lead[1:]) + (w.shape[0],))
+
+
+def rs_linear(x, w, bias, sctx):
+    """Row-parallel linear whose partial sums are reduce-scattered over tokens."""
+    lead = x.shape[:-1]
+    if lead[0] % sctx.world:
+        raise ValueError(f"leading dimension {lead[0]} is not divisible by {sctx.world}")
+    y = _RSLinear.apply(_as_2d(x), w, bias, sctx)
+    return y.view((lead[0] // sctx.world,) + tuple(lead[1:]) + (w.shape[0],))
+
+
+def ar_linear(x, w, bias, sctx):
+    """Row-parallel linear whose partial sums are all-reduced."""
+    lead = x.shape[:-1]
+    y = _ARLinear.apply(_as_2d(x), w, bias, sctx)
+    return y.view(tuple(lead) + (w.shape[0],))

@@ -1,0 +1,165 @@
+"""Symmetric peer memory for the fused compute+collective kernels.
+
+``SymmContext(group)`` owns, for one tensor-parallel (or data-parallel)
+group on one node:
+
+* a flag pad (64 x int32) in symmetric memory - ``ready[8] | done[8] |
+  done2[8] | counters[..]`` - that the kernels use for flow control;
+* named symmetric buffers (``buffer(name, nbytes)``): the same allocation on
+  every rank, reachable from every rank through NVLink with plain loads and
+  stores (and TMA tile loads without any cluster options);
+* the job-wide *epoch* counter: every fused operation takes the next number,
+  identically on all ranks because the program is SPMD.
+
+Allocation goes through ``torch.distributed._symmetric_memory`` (CUDA
+virtual-memory handles exchanged over the process group).  ``LocalSymmContext``
+is a stand-in with ``world`` fake ranks whose buffers all live on one GPU: the
+kernels are exercised rank by rank with the peers' flags pre-set, which is how
+their numerics are tested without several GPUs and without ever running two
+mutually waiting kernels on one device.
+"""
+from __future__ import annotations
+
+import torch
+import torch.distributed as dist
+
+from ..logger import get_logger
+
+logger = get_logger("symm")
+
+FLAG_WORDS = 64
+
+
+def _align(n, a=256):
+    return (n + a - 1) // a * a
+
+
+class SymmBuffer:
+    """A symmetric allocation: local tensor (uint8) + every rank's base address."""
+
+    def __init__(self, local: torch.Tensor, peer_ptrs, handle=None):
+        self.local = local
+        self.peer_ptrs = list(peer_ptrs)
+        self.handle = handle
+        self.nbytes = local.numel() * local.element_size()
+
+    def view(self, dtype, shape, offset_bytes=0):
+        n = 1
+        for s in shape:
+            n *= s
+        esize = torch.empty((), dtype=dtype).element_size()
+        if offset_bytes + n * esize > self.nbytes:
+            raise ValueError("view exceeds the symmetric buffer")
+        flat = self.local.view(torch.uint8)[offset_bytes:offset_bytes + n * esize]
+        return flat.view(dtype).view(shape)
+
+    def ptrs(self, offset_bytes=0):
+        return [p + offset_bytes for p in self.peer_ptrs]
+
+
+class SymmContext:
+    def __init__(self, group=None, device=None, wait_seconds: float = 2.0):
+        import torch.distributed._symmetric_memory as symm_mem
+
+        self._symm = symm_mem
+        self.group = group if group is not None else dist.group.WORLD
+        self.world = dist.get_world_size(self.group)
+        self.rank = dist.get_rank(self.group)
+        if self.world > 8:
+            raise ValueError("fused kernels support groups of at most 8 ranks (one NVSwitch node)")
+        self.device = torch.device(device) if device is not None else torch.device(
+            "cuda", torch.cuda.current_device())
+        self.wait_seconds = wait_seconds
+        self.epoch = 0
+        self._buffers: dict[str, SymmBuffer] = {}
+        flags = self._alloc("__flags__", FLAG_WORDS * 4)
+        self.flags = flags
+        flags.local.zero_()
+        torch.cuda.synchronize(self.device)
+        dist.barrier(group=self.group)
+
+    def _alloc(self, name, nbytes) -> SymmBuffer:
+        nbytes = _align(nbytes)
+        t = self._symm.empty(nbytes, dtype=torch.uint8, device=self.device)
+        hdl = self._symm.rendezvous(t, group=self.group)
+        ptrs = [int(p) for p in hdl.buffer_ptrs]
+        buf = SymmBuffer(t, ptrs, hdl)
+        self._buffers[name] = buf
+        return buf
+
+    def buffer(self, name: str, nbytes: int) -> SymmBuffer:
+        """Get (or grow) the symmetric buffer ``name``.  Collective: every rank
+        of the group must call it with the same arguments in the same order."""
+        buf = self._buffers.get(name)
+        if buf is None or buf.nbytes < nbytes:
+            buf = self._alloc(name, nbytes)
+        return buf
+
+    def next_epoch(self) -> int:
+        self.epoch += 1
+        return self.epoch
+
+    @property
+    def flags_ptr(self):
+        return self.flags.peer_ptrs[self.rank]
+
+    @property
+    def peer_flag_ptrs(self):
+        return self.flags.peer_ptrs
+
+
+class LocalSymmContext:
+    """``world`` fake ranks on one GPU (see the module docstring).  ``as_rank(r)``
+    selects which rank the next kernels impersonate."""
+
+    def __init__(self, world: int, device=None, wait_seconds: float = 0.05):
+        self.world, self.rank = world, 0
+        self.group = None
+        self.device = torch.device(device) if device is not None else torch.device(
+            "cuda", torch.cuda.current_device())
+        self.wait_seconds = wait_seconds
+        self.epoch = 0
+        self._buffers: dict[str, list[torch.Tensor]] = {}
+        self._flag_pads = [torch.zeros(FLAG_WORDS, dtype=torch.int32, device=self.device)
+                           for _ in range(world)]
+
+    def as_rank(self, rank: int):
+        self.rank = rank
+        return self
+
+    def buffer(self, name, nbytes) -> SymmBuffer:
+        nbytes = _align(nbytes)
+        bufs = self._buffers.get(name)
+        if bufs is None or bufs[0].numel() < nbytes:
+            bufs = [torch.zeros(nbytes, dtype=torch.uint8, device=self.device)
+                    for _ in range(self.world)]
+            self._buffers[name] = bufs
+        return SymmBuffer(bufs[self.rank], [b.data_ptr() for b in bufs])
+
+    def rank_view(self, name, rank, dtype, shape):
+        return SymmBuffer(self._buffers[name][rank], []).view(dtype, shape)
+
+    def next_epoch(self) -> int:
+        self.epoch += 1
+        return self.epoch
+
+    def preset_flags(self, epoch, ready=True, done=False, done2=False):
+        """Pretend that every other rank has reached the given stages."""
+        pad = self._flag_pads[self.rank]
+        for r in range(self.world):
+            if r == self.rank:
+                continue
+            if ready:
+                pad[r] = epoch
+            if done:
+                pad[8 + r] = epoch
+            if done2:
+                pad[16 + r] = epoch
+
+    @property
+    def flags_ptr(self):
+        return self._flag_pads[self.rank].data_ptr()
+
+    @property
+    def peer_flag_ptrs(self):
+        return [p.data_ptr() for p in self._flag_pads]

@@ -1,0 +1,123 @@
+"""Fused GEMM+collective kernels, exercised on ONE GPU: the ranks of a group
+are impersonated one after the other with the peers' flags pre-set (never two
+mutually waiting kernels on a device).  Reference = fp32 matmuls on the
+gathered operands."""
+import pytest
+import torch
+
+from slapo_b200.ops import native
+from slapo_b200.parallel import fused_tp as ft
+from slapo_b200.parallel.symm import LocalSymmContext
+
+pytestmark = pytest.mark.gpu
+
+
+def _close(a, b, k, tol=2e-2):
+    scale = max(1.0, k ** 0.5)
+    torch.testing.assert_close(a.float() / scale, b.float() / scale, rtol=tol, atol=tol)
+
+
+@pytest.mark.parametrize("world", [2, 4])
+def test_all_gather_gemm(world):
+    torch.manual_seed(0)
+    ts, k, n = 256, 192, 320
+    ctx = LocalSymmContext(world)
+    shards = [torch.randn(ts, k, device="cuda", dtype=torch.bfloat16) for _ in range(world)]
+    w = [torch.randn(n, k, device="cuda", dtype=torch.bfloat16) for _ in range(world)]
+    bias = torch.randn(n, device="cuda", dtype=torch.bfloat16)
+    for r in range(world):
+        ft._stage(ctx.as_rank(r), "ag_in", shards[r])
+    full = torch.cat(shards, 0).float()
+    for r in range(world):
+        ctx.as_rank(r)
+        ctx.preset_flags(ctx.epoch + 1)
+        y = ft.ag_gemm(ctx, shards[r], w[r], bias, staged=ctx.buffer("ag_in", ts * k * 2))
+        assert native.ops().device_status() == 0
+        _close(y, full @ w[r].float().t() + bias.float(), k)
+
+
+@pytest.mark.parametrize("world", [2, 4])
+@pytest.mark.parametrize("mode", ["rs", "ar"])
+def test_gemm_reduce_scatter_and_all_reduce(world, mode):
+    torch.manual_seed(1)
+    t, kl, n = 128 * world * 2, 128, 256
+    ctx = LocalSymmContext(world)
+    x = [torch.randn(t, kl, device="cuda", dtype=torch.bfloat16) for _ in range(world)]
+    w = [torch.randn(n, kl, device="cuda", dtype=torch.bfloat16) for _ in range(world)]
+    bias = torch.randn(n, device="cuda", dtype=torch.bfloat16)
+    partials = [x[r].float() @ w[r].float().t() for r in range(world)]
+    # the reduction sums 16-bit partials, like the kernel
+    total = sum(p.to(torch.bfloat16).float() for p in partials) + bias.float()
+    outs = [None] * world
+    for sweep in range(2):  # sweep 0 fills every receive slot, sweep 1 reduces real data
+        for r in range(world):
+            ctx.as_rank(r)
+            ctx.preset_flags(ctx.epoch + 1, ready=True, done=True, done2=True)
+            if mode == "rs":
+                outs[r] = ft.gemm_rs(ctx, x[r], w[r], bias)
+            else:
+                outs[r] = ft.gemm_ar(ctx, x[r], w[r], bias)
+            assert native.ops().device_status() == 0
+    rows = t // world
+    for r in range(world):
+        if mode == "rs":
+            _close(outs[r], total[r * rows:(r + 1) * rows], kl * world)
+        else:
+            # a fake rank only receives its own reduced rows in its output buffer
+            _close(outs[r][r * rows:(r + 1) * rows], total[r * rows:(r + 1) * rows], kl * world)
+
+
+def test_gathered_contraction_weight_gradients():
+    """dW = dY^T all_gather(X) (B gathered along K) and dW = all_gather(dY)^T X
+    (A gathered along K)."""
+    torch.manual_seed(2)
+    world, ts, k, n = 2, 128, 192, 128
+    t = ts * world
+    ctx = LocalSymmContext(world)
+    xs = [torch.randn(ts, k, device="cuda", dtype=torch.bfloat16) for _ in range(world)]
+    dy = torch.randn(t, n, device="cuda", dtype=torch.bfloat16)
+    for r in range(world):
+        ft._stage(ctx.as_rank(r), "xs", xs[r])
+    ctx.as_rank(0)
+    ctx.preset_flags(ctx.epoch + 1)
+    staged = ctx.buffer("xs", ts * k * 2)
+    dw = torch.empty(n, k, device="cuda", dtype=torch.bfloat16)
+    ft.comm_gemm(ctx, a_ptrs=[dy.data_ptr()], b_ptrs=staged.ptrs(), M=n, N=k, K=t, lda=n, ldb=k,
+                 a_mn=True, b_mn=True, dtype=dy.dtype, gather=ft.GATHER_B_K, seg_len=ts,
+                 out_ptr=dw.data_ptr(), ldo=k)
+    assert native.ops().device_status() == 0
+    _close(dw, dy.float().t() @ torch.cat(xs, 0).float(), t)
+    # A gathered along the contraction
+    dys = [torch.randn(ts, n, device="cuda", dtype=torch.bfloat16) for _ in range(world)]
+    x = torch.randn(t, k, device="cuda", dtype=torch.bfloat16)
+    for r in range(world):
+        ft._stage(ctx.as_rank(r), "dys", dys[r])
+    ctx.as_rank(1)
+    ctx.preset_flags(ctx.epoch + 1)
+    staged = ctx.buffer("dys", ts * n * 2)
+    dw2 = torch.empty(n, k, device="cuda", dtype=torch.bfloat16)
+    ft.comm_gemm(ctx, a_ptrs=staged.ptrs(), b_ptrs=[x.data_ptr()], M=n, N=k, K=t, lda=n, ldb=k,
+                 a_mn=True, b_mn=True, dtype=x.dtype, gather=ft.GATHER_A_K, seg_len=ts,
+                 out_ptr=dw2.data_ptr(), ldo=k)
+    assert native.ops().device_status() == 0
+    _close(dw2, torch.cat(dys, 0).float().t() @ x.float(), t)
+
+
+def test_missing_peer_times_out_cleanly():
+    """A peer that never shows up: the bounded wait runs out, the kernel sets
+    the status word and returns; the context stays usable."""
+    world, ts, k, n = 2, 128, 64, 64
+    ctx = LocalSymmContext(world, wait_seconds=0.02)
+    xs = torch.randn(ts, k, device="cuda", dtype=torch.bfloat16)
+    w = torch.randn(n, k, device="cuda", dtype=torch.bfloat16)
+    ft._stage(ctx.as_rank(0), "ag_in", xs)
+    ft._stage(ctx.as_rank(1), "ag_in", xs)
+    ctx.as_rank(0)  # flags of rank 1 are NOT set
+    ft.ag_gemm(ctx, xs, w, None, staged=ctx.buffer("ag_in", ts * k * 2))
+    torch.cuda.synchronize()
+    assert native.ops().device_status() == 4
+    # the device is fine afterwards
+    ctx.preset_flags(ctx.epoch + 1)
+    y = ft.ag_gemm(ctx, xs, w, None, staged=ctx.buffer("ag_in", ts * k * 2))
+    assert native.ops().device_status() == 0
+    _close(y, torch.cat([xs, xs], 0).float() @ w.float().t(), k)
