@@ -20,8 +20,20 @@ def init_native_engine(sch, model, config=None, mesh=None, loss_fn=None, dp_grou
         engine = PipelineEngine(model, config=config, mesh=mesh, loss_fn=loss_fn,
                                 tp_group=sch.group, **kwargs)
         return engine, engine
+    fused = kwargs.get("fused_tp", True)
+    if fused and sch.world_size > 1:
+        import torch
+
+        if torch.cuda.is_available():
+            from ..parallel.lowering import lower_fused_tp
+            from ..parallel.symm import SymmContext
+
+            ctx = SymmContext(sch.group)
+            lower_fused_tp(sch, ctx)
+            model = sch.mod
     engine = TrainEngine(model, config=config, mesh=mesh, tp_group=sch.group,
                          dp_group=dp_group, loss_fn=loss_fn)
+    engine.symm_ctx = locals().get("ctx")
     return engine, engine
 
 

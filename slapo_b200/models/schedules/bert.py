@@ -12,7 +12,10 @@
 ``disable_flash_attn`` keep the model's own attention
 ``fuse``               fuse bias+GeLU and bias+dropout+residual+LayerNorm
                        (default True)
-``sequence_parallel``  shard LN/dropout regions along the sequence
+``sequence_parallel``  shard the LN/dropout regions over the tokens
+``sequence_parallel_axis``  which activation axis is split there: 0 = batch
+                       (whole sequences per rank; the layout the fused
+                       all-gather/reduce-scatter GEMMs take), 1 = sequence
 ``ckpt_ratio``         fraction of layers to checkpoint (0 = none)
 ``checkpoint_method``  "uniform" (spread) or "head" (first layers)
 ``bcast_input``        broadcast rank-0 inputs inside the TP group
@@ -99,7 +102,7 @@ def fuse_blocks(sch, config, prefix):
     return count
 
 
-def shard_layers(sch, config, prefix, sequence_parallel):
+def shard_layers(sch, config, prefix, sequence_parallel, sp_axis=0):
     if sch.world_size == 1:
         return 0
     if config.num_attention_heads % sch.world_size != 0:
@@ -108,15 +111,16 @@ def shard_layers(sch, config, prefix, sequence_parallel):
     for path in _layer_paths(sch, prefix):
         attn = sch[f"{path}.attention.self"]
         if isinstance(attn.mod, SelfAttentionAdapter):
-            shard_column(attn["self_attn.qkv"], sequence_parallel=sequence_parallel)
+            shard_column(attn["self_attn.qkv"], sequence_parallel=sequence_parallel, sp_axis=sp_axis)
             if not sequence_parallel and config.attention_probs_dropout_prob > 0:
                 attn["self_attn.attn_op"].fork_rng()
         else:
             for name in ("query", "key", "value"):
-                shard_column(attn[name], sequence_parallel=sequence_parallel)
-        shard_row(sch[f"{path}.attention.output.dense"], sequence_parallel)
-        shard_column(sch[f"{path}.intermediate.dense"], sequence_parallel=sequence_parallel)
-        shard_row(sch[f"{path}.output.dense"], sequence_parallel)
+                shard_column(attn[name], sequence_parallel=sequence_parallel, sp_axis=sp_axis)
+        shard_row(sch[f"{path}.attention.output.dense"], sequence_parallel, sp_axis)
+        shard_column(sch[f"{path}.intermediate.dense"], sequence_parallel=sequence_parallel,
+                     sp_axis=sp_axis)
+        shard_row(sch[f"{path}.output.dense"], sequence_parallel, sp_axis)
         if sequence_parallel:
             annotate_replicated(
                 sch, [f"{path}.attention.output.LayerNorm", f"{path}.output.LayerNorm"],
@@ -125,8 +129,8 @@ def shard_layers(sch, config, prefix, sequence_parallel):
         # the embedding block computes the full sequence on every rank; keep
         # this rank's part, and put the sequence together again after the
         # last layer (the consumers are replicas, so the gradient is sliced)
-        sch[_j(prefix, "embeddings")].sync("fwd_post", "scatter", axis=1)
-        sch[_j(prefix, "encoder")].sync("fwd_post", "all_gather", axis=1,
+        sch[_j(prefix, "embeddings")].sync("fwd_post", "scatter", axis=sp_axis)
+        sch[_j(prefix, "encoder")].sync("fwd_post", "all_gather", axis=sp_axis,
                                       tensor_parallel_output_grad=False)
     return len(_layer_paths(sch, prefix))
 
@@ -154,7 +158,7 @@ def pipeline_cut(sch, prefix, cuts):
 @register_schedule("bert")
 def schedule_bert(model, model_config=None, prefix="bert", fp16=False, bf16=False, group=None,
                   attn_op_name="auto", disable_flash_attn=False, fuse=True,
-                  sequence_parallel=False, ckpt_ratio=0.0, checkpoint_method="uniform",
+                  sequence_parallel=False, sequence_parallel_axis=0, ckpt_ratio=0.0, checkpoint_method="uniform",
                   bcast_input=False, pipeline_cuts=None, shard_vocab=True, delay_init=True,
                   **_unused):
     config = model_config if model_config is not None else getattr(model, "config", None)
@@ -167,7 +171,7 @@ def schedule_bert(model, model_config=None, prefix="bert", fp16=False, bf16=Fals
     pre = prefix
     n_attn = 0 if disable_flash_attn else replace_attention(sch, config, pre, attn_op_name)
     n_fused = fuse_blocks(sch, config, pre) if fuse else 0
-    n_shard = shard_layers(sch, config, pre, sequence_parallel)
+    n_shard = shard_layers(sch, config, pre, sequence_parallel, sequence_parallel_axis)
     if shard_vocab and config.vocab_size % max(sch.world_size, 1) == 0:
         shard_lm_head(sch, config, pre)
     if bcast_input:

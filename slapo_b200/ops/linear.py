@@ -29,7 +29,15 @@ class LinearWithSeparateBias(nn.Linear):
 
 
 class LinearWithSyncFunc(nn.Linear):
-    """``F.linear(x, W) -> sync_fn -> + bias``."""
+    """``F.linear(x, W) -> sync_fn -> + bias``.
+
+    After :func:`slapo_b200.parallel.lowering.lower_fused_tp` the module carries
+    a *fused plan*: ``fused_pre = ("ag", ctx)`` (its input is all-gathered
+    inside the GEMM), ``fused_post = ("rs" | "ar", ctx)`` (its partial output is
+    reduce-scattered / all-reduced by the GEMM's epilogue) or ``fused_bwd =
+    ("ar", ctx)`` (its input gradient is all-reduced by the dgrad GEMM); CUDA
+    16-bit inputs then run the single-kernel paths, everything else the
+    unfused one above."""
 
     traceable = False
 
@@ -37,16 +45,51 @@ class LinearWithSyncFunc(nn.Linear):
                  sync_fn=None):
         super().__init__(in_features, out_features, bias, device, dtype)
         self.sync_fn = sync_fn
+        self.fused_pre = None
+        self.fused_post = None
+        self.fused_bwd = None
+
+    def matmul_sync(self, x, epilogue_bias=None):
+        """matmul and the collectives around it, without the module's own bias
+        handling; ``epilogue_bias`` is added inside the GEMM when that is legal
+        (i.e. no reduction follows)."""
+        if self.fused_pre or self.fused_post or self.fused_bwd:
+            from ..parallel import fused_tp
+
+            if fused_tp.supported(x):
+                if self.fused_pre is not None:
+                    return fused_tp.ag_linear(x, self.weight, epilogue_bias, self.fused_pre[1])
+                if self.fused_post is not None:
+                    kind, ctx = self.fused_post
+                    fn = fused_tp.rs_linear if kind == "rs" else fused_tp.ar_linear
+                    out = fn(x, self.weight, None, ctx)
+                    return out if epilogue_bias is None else out + epilogue_bias
+                return fused_tp.col_linear_ar_bwd(x, self.weight, epilogue_bias, self.fused_bwd[1])
+            return self._unfused_fallback(x, epilogue_bias)
+        out = F.linear(x, self.weight, None)
+        if self.sync_fn is not None:
+            out = self.sync_fn(out)
+        return out if epilogue_bias is None else out + epilogue_bias
+
+    def _unfused_fallback(self, x, epilogue_bias):
+        """The plan's collectives through torch.distributed (CPU tensors, fp32)."""
+        from ..parallel import sync_ops as so
+
+        if self.fused_pre is not None:
+            x = so.all_gather_forward_output(x, 0, self.fused_pre[1].group)
+        elif self.fused_bwd is not None:
+            x = so.reduce_backward_grad(x, self.fused_bwd[1].group)
+        out = F.linear(x, self.weight, None)
+        if self.fused_post is not None:
+            kind, ctx = self.fused_post
+            out = (so.reduce_scatter_forward_output(out, 0, ctx.group) if kind == "rs"
+                   else so.reduce_forward_output(out, ctx.group))
+        return out if epilogue_bias is None else out + epilogue_bias
 
     def forward(self, x, skip_bias: bool = False):
         """``skip_bias=True`` leaves the bias to the caller, which fuses it
         into the kernel that follows (dropout / residual / LayerNorm)."""
-        out = F.linear(x, self.weight, None)
-        if self.sync_fn is not None:
-            out = self.sync_fn(out)
-        if self.bias is not None and not skip_bias:
-            out = out + self.bias
-        return out
+        return self.matmul_sync(x, None if (skip_bias or self.bias is None) else self.bias)
 
     @classmethod
     def from_linear(cls, linear: nn.Linear, **kwargs):
@@ -74,7 +117,12 @@ class LinearWithSyncFunc(nn.Linear):
         return text
 
     def extra_repr(self):
-        return f"{super().extra_repr()}, sync_fn={self._sync_repr()}"
+        text = f"{super().extra_repr()}, sync_fn={self._sync_repr()}"
+        for name in ("fused_pre", "fused_post", "fused_bwd"):
+            plan = getattr(self, name, None)
+            if plan is not None:
+                text += f", {name}={plan[0]}"
+        return text
 
 
 _ACTS = ("gelu", "gelu_new", "gelu_tanh", "gelu_pytorch_tanh", "relu")
@@ -91,10 +139,7 @@ class LinearWithAct(LinearWithSyncFunc):
         self.act_fn = act_fn
 
     def forward(self, x):
-        out = F.linear(x, self.weight, None)
-        if self.sync_fn is not None:
-            out = self.sync_fn(out)
-        return NF.bias_act(out, self.bias, self.act_fn)
+        return NF.bias_act(self.matmul_sync(x), self.bias, self.act_fn)
 
     def extra_repr(self):
         return f"{super().extra_repr()}, act_fn={self.act_fn}"
@@ -109,10 +154,7 @@ class LinearWithDropout(LinearWithSyncFunc):
         self.p = p
 
     def forward(self, x):
-        out = F.linear(x, self.weight, None)
-        if self.sync_fn is not None:
-            out = self.sync_fn(out)
-        return NF.bias_dropout(out, self.bias, self.p, self.training)
+        return NF.bias_dropout(self.matmul_sync(x), self.bias, self.p, self.training)
 
     def extra_repr(self):
         return f"{super().extra_repr()}, p={self.p}"

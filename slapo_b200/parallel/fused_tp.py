@@ -61,7 +61,15 @@ def comm_gemm(ctx, *, a_ptrs, b_ptrs, M, N, K, lda, ldb, a_mn, b_mn, dtype, gath
 
 
 def _stage(ctx, name, t: torch.Tensor):
-    """Copy a local tensor into the symmetric buffer ``name`` (peers read it)."""
+    """Copy a local tensor into the symmetric buffer ``name`` (peers read it).
+
+    Two physical buffers alternate per name: a peer may still be reading the
+    previous contents while this rank is already one operation ahead, but it
+    cannot be two behind, because every fused operation waits for all peers to
+    have entered it (and hence to have finished the one before)."""
+    toggles = ctx.__dict__.setdefault("_stage_toggle", {})
+    toggles[name] = toggles.get(name, 0) ^ 1
+    name = f"{name}#{toggles[name]}"
     buf = ctx.buffer(name, t.numel() * t.element_size())
     buf.view(t.dtype, tuple(t.shape)).copy_(t)
     return buf
@@ -181,6 +189,40 @@ class _ARLinear(torch.autograd.Function):
         dw = dy.t() @ x
         db = dy.float().sum(0).to(dy.dtype) if ctx.has_bias else None
         return dx, dw, db, None
+
+
+class _ColLinearARBwd(torch.autograd.Function):
+    """Column-parallel linear with replicated input: the forward is local, the
+    input gradient ``dY W`` is a partial sum that the dgrad GEMM all-reduces."""
+
+    @staticmethod
+    def forward(ctx, x, w, bias, sctx):
+        ctx.sctx = sctx
+        ctx.save_for_backward(x, w)
+        ctx.has_bias = bias is not None
+        return torch.nn.functional.linear(x, w, bias)
+
+    @staticmethod
+    def backward(ctx, dy):
+        x, w = ctx.saved_tensors
+        dy = dy.contiguous()
+        t = dy.shape[0]
+        if t % (128 * ctx.sctx.world) == 0:
+            dx = gemm_ar(ctx.sctx, dy, w, None, b_mn=True, name="ar_bwd")
+        else:  # row blocks do not split evenly over the group
+            import torch.distributed as dist
+
+            dx = dy @ w
+            dist.all_reduce(dx, group=ctx.sctx.group)
+        dw = dy.t() @ x
+        db = dy.float().sum(0).to(dy.dtype) if ctx.has_bias else None
+        return dx, dw, db, None
+
+
+def col_linear_ar_bwd(x, w, bias, sctx):
+    lead = x.shape[:-1]
+    y = _ColLinearARBwd.apply(_as_2d(x), w, bias, sctx)
+    return y.view(tuple(lead) + (w.shape[0],))
 
 
 def _as_2d(x):

@@ -50,7 +50,9 @@ class ScheduleMetadata:
 class Schedule:
     def __init__(self, mod: nn.Module, name: str = "", path: str = "",
                  parent: Optional["Schedule"] = None, group=None):
-        if dist.is_available() and dist.is_initialized():
+        if group is False:  # explicit "no tensor parallelism" inside a distributed job
+            self.world_size, self.rank, group = 1, 0, None
+        elif dist.is_available() and dist.is_initialized():
             self.world_size = dist.get_world_size(group)
             self.rank = dist.get_rank(group)
         else:

@@ -20,7 +20,7 @@ def _make_batch(vocab, batch=8, seq=128, seed=0):
     return ids, labels
 
 
-def _tp_worker(rank, world, sequence_parallel, via_verify):
+def _tp_worker(rank, world, sequence_parallel, via_verify, sp_axis=0):
     cfg = BertConfig(vocab_size=30522, hidden_size=768, num_hidden_layers=2,
                      num_attention_heads=12, intermediate_size=3072,
                      hidden_dropout_prob=0.0, attention_probs_dropout_prob=0.0)
@@ -48,7 +48,7 @@ def _tp_worker(rank, world, sequence_parallel, via_verify):
     model = copy.deepcopy(ref)
     sch = slapo.model_schedule.apply_schedule(
         model, "bert", model_config=cfg, prefix="", sequence_parallel=sequence_parallel,
-        attn_op_name="reference")
+        sequence_parallel_axis=sp_axis, attn_op_name="reference")
     tp_model, _ = slapo.build(sch, init_weights=False)
     out_ref = ref(ids)["last_hidden_state"]
     out_ref.pow(2).mean().backward()
@@ -85,7 +85,11 @@ def test_bert_tp2_recipe_matches_unsharded():
 
 
 def test_bert_tp2_sequence_parallel_matches_unsharded():
-    run_distributed(_tp_worker, 2, True, False)
+    run_distributed(_tp_worker, 2, True, False, 0)
+
+
+def test_bert_tp2_sequence_parallel_axis1_matches_unsharded():
+    run_distributed(_tp_worker, 2, True, False, 1)
 
 
 def _mlm_worker(rank, world):

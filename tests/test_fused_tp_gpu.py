@@ -12,6 +12,12 @@ from slapo_b200.parallel.symm import LocalSymmContext
 pytestmark = pytest.mark.gpu
 
 
+def _put(ctx, rank, name, t):
+    """Fill fake rank ``rank``'s symmetric buffer ``name`` with ``t``."""
+    buf = ctx.as_rank(rank).buffer(name, t.numel() * t.element_size())
+    buf.view(t.dtype, tuple(t.shape)).copy_(t)
+
+
 def _close(a, b, k, tol=2e-2):
     scale = max(1.0, k ** 0.5)
     torch.testing.assert_close(a.float() / scale, b.float() / scale, rtol=tol, atol=tol)
@@ -26,7 +32,7 @@ def test_all_gather_gemm(world):
     w = [torch.randn(n, k, device="cuda", dtype=torch.bfloat16) for _ in range(world)]
     bias = torch.randn(n, device="cuda", dtype=torch.bfloat16)
     for r in range(world):
-        ft._stage(ctx.as_rank(r), "ag_in", shards[r])
+        _put(ctx, r, "ag_in", shards[r])
     full = torch.cat(shards, 0).float()
     for r in range(world):
         ctx.as_rank(r)
@@ -77,7 +83,7 @@ def test_gathered_contraction_weight_gradients():
     xs = [torch.randn(ts, k, device="cuda", dtype=torch.bfloat16) for _ in range(world)]
     dy = torch.randn(t, n, device="cuda", dtype=torch.bfloat16)
     for r in range(world):
-        ft._stage(ctx.as_rank(r), "xs", xs[r])
+        _put(ctx, r, "xs", xs[r])
     ctx.as_rank(0)
     ctx.preset_flags(ctx.epoch + 1)
     staged = ctx.buffer("xs", ts * k * 2)
@@ -91,7 +97,7 @@ def test_gathered_contraction_weight_gradients():
     dys = [torch.randn(ts, n, device="cuda", dtype=torch.bfloat16) for _ in range(world)]
     x = torch.randn(t, k, device="cuda", dtype=torch.bfloat16)
     for r in range(world):
-        ft._stage(ctx.as_rank(r), "dys", dys[r])
+        _put(ctx, r, "dys", dys[r])
     ctx.as_rank(1)
     ctx.preset_flags(ctx.epoch + 1)
     staged = ctx.buffer("dys", ts * n * 2)
@@ -110,8 +116,8 @@ def test_missing_peer_times_out_cleanly():
     ctx = LocalSymmContext(world, wait_seconds=0.02)
     xs = torch.randn(ts, k, device="cuda", dtype=torch.bfloat16)
     w = torch.randn(n, k, device="cuda", dtype=torch.bfloat16)
-    ft._stage(ctx.as_rank(0), "ag_in", xs)
-    ft._stage(ctx.as_rank(1), "ag_in", xs)
+    _put(ctx, 0, "ag_in", xs)
+    _put(ctx, 1, "ag_in", xs)
     ctx.as_rank(0)  # flags of rank 1 are NOT set
     ft.ag_gemm(ctx, xs, w, None, staged=ctx.buffer("ag_in", ts * k * 2))
     torch.cuda.synchronize()
