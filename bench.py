@@ -56,6 +56,9 @@ def parse_args():
     ap.add_argument("--parallelism", default="tp", choices=["tp", "dp"])
     ap.add_argument("--no-sequence-parallel", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--profile", action="store_true",
+                    help="print a per-kernel time table of one step (torch.profiler, rank 0); "
+                         "analysis aid only, the reported numbers are taken without it")
     return ap.parse_args()
 
 
@@ -230,6 +233,15 @@ def run_native(args):
     clocks = sampler.finish()
     value = global_batch * args.steps / (ms / 1e3)
 
+    if args.profile:
+        from torch.profiler import ProfilerActivity, profile
+
+        with profile(activities=[ProfilerActivity.CPU, ProfilerActivity.CUDA]) as prof:
+            step(0)
+            torch.cuda.synchronize()
+        if rank == 0:
+            print(prof.key_averages().table(sort_by="cuda_time_total", row_limit=40,
+                                            max_name_column_width=70), file=sys.stderr)
     e2e = None
     if not args.no_e2e:
         host = [make_batch(vocab, local_batch, args.seq, 77 + dp_rank * 100 + i, "cpu", pin=True)

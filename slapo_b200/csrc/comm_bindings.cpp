@@ -45,6 +45,20 @@ void comm_gemm(std::vector<int64_t> a_ptrs, std::vector<int64_t> b_ptrs, int64_t
               "): check divisibility by the group size / 128-row blocks and 16-byte alignment");
 }
 
+void peer_gather(std::vector<int64_t> src_ptrs, int64_t dst_ptr, int64_t seg_bytes, int64_t world,
+                 int64_t rank, int64_t epoch, int64_t flags_ptr, std::vector<int64_t> peer_flags,
+                 double wait_seconds) {
+  auto src = to_ptrs<void*>(src_ptrs);
+  auto pf = to_ptrs<int*>(peer_flags);
+  const int dev = at::cuda::current_device();
+  int rc = slapo::launch_peer_gather(
+      src.data(), reinterpret_cast<void*>(dst_ptr), seg_bytes, static_cast<int>(world),
+      static_cast<int>(rank), static_cast<int>(epoch), reinterpret_cast<int*>(flags_ptr),
+      peer_flags.empty() ? nullptr : pf.data(), slapo_status_ptr(dev), wait_seconds,
+      at::cuda::getCurrentCUDAStream().stream());
+  TORCH_CHECK(rc == 0, "peer_gather: launch refused (code ", rc, ")");
+}
+
 }  // namespace
 
 void register_comm_ops(torch::Library& m) {
@@ -52,4 +66,6 @@ void register_comm_ops(torch::Library& m) {
         "bool b_mn, bool bf16, int gather, int seg_len, int mode, int world, int rank, int epoch, "
         "int out_ptr, int ldo, int bias_ptr, int act, int flags_ptr, int[] peer_flags, "
         "int[] peer_recv, int[] peer_out, float wait_seconds) -> ()", &comm_gemm);
+  m.def("peer_gather(int[] src_ptrs, int dst_ptr, int seg_bytes, int world, int rank, int epoch, "
+        "int flags_ptr, int[] peer_flags, float wait_seconds) -> ()", &peer_gather);
 }

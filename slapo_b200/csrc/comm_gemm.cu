@@ -13,13 +13,14 @@
 //                        sequence parallelism, dgrad of a row-parallel one) or
 //                        the contraction dimension of A or B (weight
 //                        gradients, where the gathered tensor is contracted).
-//   GEMM -> reduce-scatter   the epilogue pushes each 16-bit partial tile with
-//                        peer stores into the slot [owner][source] of the
-//                        owner rank's receive buffer; when a source has
-//                        finished a row block it releases a flag on the owner;
-//                        after its own tiles every CTA joins the reduction of
-//                        this rank's rows (fp32 sum over the p slots, optional
-//                        bias) - still the same launch.
+//   GEMM -> reduce-scatter   the epilogue writes each 16-bit partial tile into
+//                        this rank's symmetric partial buffer, visiting the
+//                        row blocks of the other owners first; when a source
+//                        has finished an owner's row block it releases a flag
+//                        on that owner; after its own tiles every CTA joins
+//                        the reduction of this rank's rows, pulling the p
+//                        partials over NVLink with wide coalesced loads (fp32
+//                        sum, optional bias) - still the same launch.
 //   GEMM -> all-reduce   reduce-scatter as above, then the reduced rows are
 //                        pushed to every peer's output buffer and a second
 //                        flag round closes the operation.
@@ -67,7 +68,7 @@ struct CommGemmParams {
   // symmetric state
   int* flags;                    // local pad: ready[8] | done[8] | done2[8] | counters[8]
   int* peer_flags[kMaxRanks];    // the same pad on every rank
-  void* peer_recv[kMaxRanks];    // receive buffers [world][M / world, N] 16-bit
+  void* peer_recv[kMaxRanks];    // every rank's partial-product buffer [M, N] 16-bit
   void* peer_out[kMaxRanks];     // all-reduce output buffers [M, N]
   int* status;
   long long wait_cycles;         // budget of a cross-GPU wait
@@ -306,11 +307,11 @@ comm_gemm_kernel(const __grid_constant__ SegMaps maps_a, const __grid_constant__
       int row_off = 0;
       if (scatter) {
         owner = m0 / rows_per_rank;
-        // slot [owner][source = this rank] of the owner's receive buffer
-        dst_base = static_cast<uint8_t*>(p.peer_recv[owner]) +
-                   static_cast<int64_t>(p.rank) * rows_per_rank * p.N * 2;
+        // the partial tile stays in this rank's own symmetric buffer [M, N];
+        // the owner of the rows pulls it with wide coalesced loads
+        dst_base = static_cast<uint8_t*>(p.peer_recv[p.rank]);
         dst_ld = p.N;
-        row_off = owner * rows_per_rank;
+        row_off = 0;
         if (!(seen_ready & (1u << owner))) {
           // the owner must have left its previous consumers of the buffer
           bool w = true;
@@ -365,9 +366,9 @@ comm_gemm_kernel(const __grid_constant__ SegMaps maps_a, const __grid_constant__
       __syncwarp();
       if (lane == 0) tc::mbar_arrive(&tmem_empty[acc]);
       if (scatter) {
-        // publish: make this warp's peer stores visible, count it; the warp
-        // that completes the owner's row block releases the owner's flag
-        __threadfence_system();
+        // publish: make this warp's stores visible, count it; the warp that
+        // completes the owner's row block releases the owner's flag
+        __threadfence();
         __syncwarp();
         if (lane == 0) {
           const int prev = atomicAdd(counters + owner, 1);
@@ -396,18 +397,38 @@ comm_gemm_kernel(const __grid_constant__ SegMaps maps_a, const __grid_constant__
     if (s_ok) {
       const int64_t vec_per_row = p.N / 8;
       const int64_t n_vec = static_cast<int64_t>(rows_per_rank) * vec_per_row;
-      const int64_t slot = static_cast<int64_t>(rows_per_rank) * p.N;  // elements per source slot
-      const uint8_t* recv = static_cast<const uint8_t*>(p.peer_recv[p.rank]);
+      // this rank's rows inside every source's partial buffer [M, N]
+      const int64_t my_off = static_cast<int64_t>(p.rank) * rows_per_rank * p.N;
       for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < n_vec;
            i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
         const int64_t e = i * 8;
         float acc8[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-        for (int r = 0; r < p.world; ++r) {
-          float v[8];
-          if (p.bf16) Vec8<__nv_bfloat16>::load(reinterpret_cast<const __nv_bfloat16*>(recv) + r * slot + e, v);
-          else Vec8<__half>::load(reinterpret_cast<const __half*>(recv) + r * slot + e, v);
+        uint4 raw[kMaxRanks];
 #pragma unroll
-          for (int k = 0; k < 8; ++k) acc8[k] += v[k];
+        for (int r = 0; r < kMaxRanks; ++r) {
+          if (r < p.world) {
+            // start with the next rank so that the peers' links share the load
+            const int src = (p.rank + 1 + r) % p.world;
+            raw[r] = *reinterpret_cast<const uint4*>(
+                static_cast<const uint8_t*>(p.peer_recv[src]) + (my_off + e) * 2);
+          }
+        }
+#pragma unroll
+        for (int r = 0; r < kMaxRanks; ++r) {
+          if (r < p.world) {
+            float v[8];
+            if (p.bf16) {
+              const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw[r]);
+#pragma unroll
+              for (int k = 0; k < 4; ++k) { float2 f = __bfloat1622float2(h[k]); v[2 * k] = f.x; v[2 * k + 1] = f.y; }
+            } else {
+              const __half2* h = reinterpret_cast<const __half2*>(&raw[r]);
+#pragma unroll
+              for (int k = 0; k < 4; ++k) { float2 f = __half22float2(h[k]); v[2 * k] = f.x; v[2 * k + 1] = f.y; }
+            }
+#pragma unroll
+            for (int k = 0; k < 8; ++k) acc8[k] += v[k];
+          }
         }
         const int col = static_cast<int>(e % p.N);
         if (p.bias != nullptr) {
@@ -461,6 +482,64 @@ comm_gemm_kernel(const __grid_constant__ SegMaps maps_a, const __grid_constant__
     tc::fence_after_sync();
     tc::tmem_dealloc(tmem_base, kTmemCols);
   }
+}
+
+// ------------------------------------------------------------------------ //
+// All-gather by peer loads: dst[r * seg : (r + 1) * seg] = segment of rank r,
+// read from rank r's symmetric buffer with 16-byte coalesced loads.  Same
+// flag protocol as above (announce, then wait for a peer before reading it).
+struct PeerGatherParams {
+  const void* src[kMaxRanks];
+  void* dst;
+  int64_t seg_bytes;
+  int world, rank, epoch;
+  int* flags;
+  int* peer_flags[kMaxRanks];
+  int* status;
+  long long wait_cycles;
+};
+
+__global__ void __launch_bounds__(256) peer_gather_kernel(const PeerGatherParams p) {
+  __shared__ int s_abort;
+  __shared__ int s_ok;
+  if (threadIdx.x == 0) {
+    s_abort = 0;
+    if (blockIdx.x == 0)
+      for (int r = 0; r < p.world; ++r) st_release_sys(p.peer_flags[r] + p.rank, p.epoch);
+  }
+  __syncthreads();
+  const int64_t n_vec = p.seg_bytes / 16;
+  for (int i = 0; i < p.world; ++i) {
+    const int r = (p.rank + i) % p.world;  // local segment first
+    if (threadIdx.x == 0)
+      s_ok = (r == p.rank) || wait_flag(p.flags + r, p.epoch, p.wait_cycles, &s_abort);
+    __syncthreads();
+    if (!s_ok) break;
+    const uint4* src = static_cast<const uint4*>(p.src[r]);
+    uint4* dst = reinterpret_cast<uint4*>(static_cast<uint8_t*>(p.dst) + r * p.seg_bytes);
+    for (int64_t v = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; v < n_vec;
+         v += static_cast<int64_t>(gridDim.x) * blockDim.x)
+      dst[v] = src[v];
+    __syncthreads();
+  }
+  if (threadIdx.x == 0 && s_abort != 0 && p.status != nullptr) atomicExch(p.status, 5);
+}
+
+int launch_peer_gather(void* const* src_ptrs, void* dst, int64_t seg_bytes, int world, int rank,
+                       int epoch, int* flags, int* const* peer_flags, int* status,
+                       double wait_seconds, cudaStream_t stream) {
+  if (seg_bytes % 16 || world < 1 || world > kMaxRanks) return 1;
+  PeerGatherParams p{};
+  for (int r = 0; r < world; ++r) {
+    p.src[r] = src_ptrs[r];
+    p.peer_flags[r] = peer_flags != nullptr ? peer_flags[r] : flags;
+  }
+  p.dst = dst; p.seg_bytes = seg_bytes; p.world = world; p.rank = rank; p.epoch = epoch;
+  p.flags = flags; p.status = status;
+  p.wait_cycles = static_cast<long long>(wait_seconds * 1.9e9);
+  count_launch();
+  peer_gather_kernel<<<sm_count() * 2, 256, 0, stream>>>(p);
+  return cudaGetLastError() == cudaSuccess ? 0 : 4;
 }
 
 // ------------------------------------------------------------------------ //

@@ -55,6 +55,11 @@ int launch_comm_gemm(void* const* a_ptrs, void* const* b_ptrs, int M, int N, int
                      void* const* peer_out, int* status, double wait_seconds,
                      cudaStream_t stream);
 
+// dst = concatenation of every rank's segment, pulled over NVLink (comm_gemm.cu)
+int launch_peer_gather(void* const* src_ptrs, void* dst, int64_t seg_bytes, int world, int rank,
+                       int epoch, int* flags, int* const* peer_flags, int* status,
+                       double wait_seconds, cudaStream_t stream);
+
 }  // namespace slapo
 
 #include "common_host.h"

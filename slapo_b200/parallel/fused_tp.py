@@ -75,6 +75,21 @@ def _stage(ctx, name, t: torch.Tensor):
     return buf
 
 
+def peer_gather(ctx, shard, name):
+    """All-gather ``shard`` (rows) over the group with this framework's own
+    pull kernel: stage into symmetric memory, every rank copies the peers'
+    segments over NVLink.  Used where the gathered tensor feeds a plain local
+    GEMM (weight gradients, whose contraction runs over the gathered tokens)."""
+    staged = _stage(ctx, name, shard)
+    full = torch.empty((shard.shape[0] * ctx.world,) + tuple(shard.shape[1:]), dtype=shard.dtype,
+                       device=shard.device)
+    epoch = ctx.next_epoch()
+    native.ops().peer_gather([int(p) for p in staged.ptrs()], full.data_ptr(),
+                             shard.numel() * shard.element_size(), ctx.world, ctx.rank, epoch,
+                             ctx.flags_ptr, list(ctx.peer_flag_ptrs), float(ctx.wait_seconds))
+    return full
+
+
 # ---------------------------------------------------------------------- #
 def ag_gemm(ctx, x_shard, w, bias=None, act=-1, name="ag_in", staged=None):
     """``all_gather(x_shard) @ w.T`` with the gather inside the GEMM."""
@@ -131,14 +146,10 @@ class _AGLinear(torch.autograd.Function):
         dy = dy.contiguous()
         # dXs = reduce_scatter(dY @ W):  B = W read N-major ([N_local, K] = [contraction, out])
         dx = gemm_rs(sctx, dy, w, None, b_mn=True, name="rs_recv_bwd")
-        # dW = dY^T @ all_gather(Xs): A = dY M-major, B = X gathered along the contraction
-        ts, k = x_shard.shape
-        n = w.shape[0]
-        staged = _stage(sctx, "ag_in_bwd", x_shard.contiguous())
-        dw = torch.empty_like(w)
-        comm_gemm(sctx, a_ptrs=[dy.data_ptr()], b_ptrs=staged.ptrs(), M=n, N=k, K=ts * sctx.world,
-                  lda=dy.stride(0), ldb=k, a_mn=True, b_mn=True, dtype=dy.dtype,
-                  gather=GATHER_B_K, seg_len=ts, out_ptr=dw.data_ptr(), ldo=k)
+        # dW = dY^T @ all_gather(Xs): few output tiles and a very long
+        # contraction - gather the tokens with the pull kernel and let the
+        # library's split-K GEMM do the rest
+        dw = dy.t() @ peer_gather(sctx, x_shard.contiguous(), "ag_in_bwd")
         db = dy.float().sum(0).to(dy.dtype) if ctx.has_bias else None
         return dx, dw, db, None
 
@@ -159,16 +170,13 @@ class _RSLinear(torch.autograd.Function):
         ts, n = dy_shard.shape
         t, kl = x.shape
         staged = _stage(sctx, "ag_dy_bwd", dy_shard)
-        # dX = all_gather(dYs) @ W: A rows gathered, B = W read N-major
+        # dX = all_gather(dYs) @ W: A rows gathered inside the GEMM, B = W read N-major
         dx = torch.empty(t, kl, dtype=x.dtype, device=x.device)
         comm_gemm(sctx, a_ptrs=staged.ptrs(), b_ptrs=[w.data_ptr()], M=t, N=kl, K=n, lda=n,
                   ldb=w.stride(0), a_mn=False, b_mn=True, dtype=x.dtype, gather=GATHER_A_ROWS,
                   seg_len=ts, out_ptr=dx.data_ptr(), ldo=kl)
-        # dW = all_gather(dYs)^T @ X: A gathered along the contraction (M-major), B = X N-major
-        dw = torch.empty_like(w)
-        comm_gemm(sctx, a_ptrs=staged.ptrs(), b_ptrs=[x.data_ptr()], M=n, N=kl, K=t, lda=n,
-                  ldb=x.stride(0), a_mn=True, b_mn=True, dtype=x.dtype, gather=GATHER_A_K,
-                  seg_len=ts, out_ptr=dw.data_ptr(), ldo=kl)
+        # dW = all_gather(dYs)^T @ X: long contraction, few tiles (see _AGLinear)
+        dw = peer_gather(sctx, dy_shard, "ag_dy_bwd2").t() @ x
         # the bias is added on the owner's rows only: its gradient is partial
         # (tagged replicated_param -> summed over the group by the engine)
         db = dy_shard.float().sum(0).to(dy_shard.dtype) if ctx.has_bias else None
