@@ -17,6 +17,7 @@ def init_native_engine(sch, model, config=None, mesh=None, loss_fn=None, dp_grou
     from ..runtime.pipeline_engine import PipelineEngine, PipelineModel
 
     if isinstance(model, PipelineModel):
+        kwargs.pop("fused_tp", None)
         engine = PipelineEngine(model, config=config, mesh=mesh, loss_fn=loss_fn,
                                 tp_group=sch.group, **kwargs)
         return engine, engine

@@ -161,16 +161,43 @@ def _trace_level(root: nn.Module, *, leaf_modules, flatten, recursive, concrete_
     judge = HierTracer(leaf_modules)
     forced = [] if flatten else _direct_child_names(root)
     tracer = HierTracer(leaf_modules, forced)
+    graph = None
+    cargs = _fill_concrete_args(root, concrete_args, call_node)
     try:
-        cargs = _fill_concrete_args(root, concrete_args, call_node)
         graph = tracer.trace(root, concrete_args=cargs or None)
-    except Exception as err:  # untraceable level: keep the eager module
+    except Exception as first_err:
+        # Optional inputs (default None) that steer Python control flow cannot
+        # stay symbolic.  Retry once with every such input frozen at None; the
+        # caller names the ones it needs live through concrete_args.
+        sig = inspect.signature(root.forward)
+        optional = {n: None for n, p in sig.parameters.items()
+                    if p.default is None and n not in cargs}
+        if optional and call_node is None:
+            try:
+                cargs = dict(cargs, **optional)
+                graph = HierTracer(leaf_modules, forced).trace(root, concrete_args=cargs)
+                logger.info("traced %s with optional inputs %s frozen at None",
+                            type(root).__name__, sorted(optional))
+            except Exception:
+                graph = None
+        if graph is None:
+            err = first_err
+    if graph is None:  # untraceable level: keep the eager module
+        err = locals().get("err", "unknown error")
         logger.debug(traceback.format_exc())
         logger.warning("cannot trace %s (%s); left as an eager module",
                        type(root).__name__, err)
         return root
 
     _strip_specialisation_guards(graph, cargs)
+    for node in graph.nodes:
+        # a child module literally called "self" (Hugging Face attention blocks)
+        # would shadow the module reference in the generated forward
+        if node.name == "self" and node.op != "placeholder":
+            if hasattr(node, "_rename"):
+                node._rename("self_mod")
+            else:  # pragma: no cover - older fx
+                node.name = "self_mod"
     if flatten:
         gm = fx.GraphModule(root, graph, class_name=type(root).__name__)
     else:

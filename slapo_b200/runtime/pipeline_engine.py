@@ -1,3 +1,317 @@
-class PipelineModel: pass
-class PipelineEngine: pass
-class PipelineStage: pass
+"""Pipeline-parallel runtime: stage wrappers and the 1F1B engine.
+
+``build(sch, target="native", mesh=..., loss_fn=...)`` on a schedule with
+``cut_pipeline_stage`` marks returns a :class:`PipelineEngine`.  Each rank
+along the mesh's ``pp`` axis owns one stage module.  ``train_batch`` splits the
+global batch into micro-batches and runs the one-forward-one-backward schedule:
+``P - 1 - stage`` warm-up forwards, then alternating forward / backward, then
+the remaining backwards, so that at most ``P - stage`` micro-batches are alive
+per stage.
+
+Stage boundaries are described statically (``live_in`` of
+:func:`slapo_b200.parallel.pipeline_partition.analyze_pipeline_module`): the
+ordered value names that cross each boundary.  Shapes and dtypes are exchanged
+ONCE, with the first micro-batch; afterwards only tensors move, as batched
+``isend`` / ``irecv`` pairs over the process group (NCCL on GPUs: the transfers
+run on the communicator's stream and overlap the neighbouring compute; gloo on
+CPU ranks).  The reference delegates all of this to DeepSpeed's
+``PipelineModule`` and re-decodes a metadata tensor on the host for every
+micro-batch (slapo/framework_dialect/deepspeed/pipeline.py:226-354).
+
+Parameters shared by two stages (tied embeddings) get their gradients summed
+over the owning stages before the optimizer step.
+"""
+from __future__ import annotations
+
+import torch
+import torch.distributed as dist
+from torch import nn
+
+from ..logger import get_logger
+from .engine import EngineConfig, TrainEngine
+
+logger = get_logger("pipeline_engine")
+
+
+class PipelineStage(nn.Module):
+    """One stage: maps value names to the stage module's arguments and back."""
+
+    def __init__(self, module, index, n_stages, input_names, output_names):
+        super().__init__()
+        self.module = module
+        self.index, self.n_stages = index, n_stages
+        self.input_names = list(input_names)
+        self.output_names = list(output_names)
+
+    def forward(self, env: dict):
+        out = self.module(*[env[n] for n in self.input_names])
+        produced = {}
+        for name, idx in self.output_names:
+            produced[name] = out if idx is None else out[idx]
+        return produced
+
+
+class PipelineModel(nn.Module):
+    """All stages plus the boundary contract; runs them in sequence when called
+    directly (single process, e.g. for verification)."""
+
+    def __init__(self, stages, live_in, input_names, output_spec):
+        super().__init__()
+        self.stages = nn.ModuleList(stages)
+        self.live_in = [list(x) for x in live_in]
+        self.input_names = list(input_names)
+        self.output_spec = output_spec
+
+    def materialize_output(self, env):
+        def pick(x):
+            if isinstance(x, str):
+                return env[x]
+            if isinstance(x, dict):
+                return {k: pick(v) for k, v in x.items()}
+            if isinstance(x, (tuple, list)):
+                return type(x)(pick(v) for v in x)
+            return x
+
+        return pick(self.output_spec)
+
+    def bind_inputs(self, args, kwargs):
+        env = dict(zip(self.input_names, args))
+        env.update(kwargs)
+        for name in self.input_names:
+            env.setdefault(name, None)
+        return env
+
+    def forward(self, *args, **kwargs):
+        env = self.bind_inputs(args, kwargs)
+        for stage in self.stages:
+            env.update(stage(env))
+        return self.materialize_output(env)
+
+
+def _split_micro(t, m):
+    if torch.is_tensor(t) and t.dim() > 0:
+        return list(t.chunk(m, dim=0))
+    return [t] * m
+
+
+class PipelineEngine:
+    def __init__(self, model: PipelineModel, config=None, mesh=None, loss_fn=None, tp_group=None,
+                 num_micro_batches=None, **_unused):
+        if mesh is None:
+            raise ValueError("the pipeline engine needs mesh=DeviceMesh(pp=..., dp=..., tp=...)")
+        self.model = model
+        self.mesh = mesh
+        self.cfg = EngineConfig.from_dict(config)
+        self.loss_fn = loss_fn
+        self.stage_id = mesh.pp_rank
+        self.n_stages = mesh.pp_size
+        if self.n_stages != len(model.stages):
+            raise ValueError(f"{len(model.stages)} stages were cut but the mesh has pp={self.n_stages}")
+        self.stage = model.stages[self.stage_id]
+        self.num_micro_batches = num_micro_batches or self.cfg.extra.get("num_micro_batches") \
+            or self.n_stages
+        self.prev_rank, self.next_rank = mesh.prev_stage_rank(), mesh.next_stage_rank()
+        self.device = next(self.stage.parameters()).device
+        self.inner = TrainEngine(self.stage, config=self.cfg, mesh=mesh, tp_group=tp_group,
+                                 dp_group=mesh.dp_group)
+        self.inner.cfg.grad_accum_steps = 1
+        self._meta_fwd = None   # [(name, shape, dtype, requires_grad)] of live_in[stage]
+        self._tied = self._find_tied()
+        self.last_loss = None
+
+    # ---- tied parameters across stages --------------------------------- #
+    def _find_tied(self):
+        owners = {}
+        for s, stage in enumerate(self.model.stages):
+            for p in stage.parameters():
+                owners.setdefault(id(p), (p, set()))[1].add(s)
+        groups = []
+        for p, stages in owners.values():
+            if len(stages) > 1:
+                groups.append((p, sorted(stages)))
+        if groups:
+            logger.info("tied parameters across stages: %s", [g[1] for g in groups], ranks=0)
+        return groups
+
+    def _sync_tied_grads(self):
+        c = self.mesh.get_coord()
+        for p, stages in self._tied:
+            if self.stage_id not in stages or p.grad is None:
+                continue
+            ranks = [self.mesh.get_rank(pp=s, dp=c["dp"], tp=c["tp"]) for s in stages]
+            # pairwise exchange keeps it group-free: sum = mine + theirs
+            others = [r for r in ranks if r != self.mesh.rank]
+            recv = [torch.empty_like(p.grad) for _ in others]
+            ops = []
+            for r, buf in zip(others, recv):
+                ops.append(dist.P2POp(dist.isend, p.grad.contiguous(), r))
+                ops.append(dist.P2POp(dist.irecv, buf, r))
+            for w in dist.batch_isend_irecv(ops):
+                w.wait()
+            for buf in recv:
+                p.grad.add_(buf)
+
+    # ---- p2p helpers ---------------------------------------------------- #
+    # Every exchange is ONE batched isend/irecv group, and a stage always
+    # pairs "send to a neighbour" with the matching "receive from that
+    # neighbour" in the same group (send_forward_recv_backward etc.), so the
+    # two sides of a link never wait for each other in opposite order.
+    def _exchange(self, sends, recvs):
+        ops = [dist.P2POp(dist.isend, t.contiguous(), peer) for t, peer in sends]
+        ops += [dist.P2POp(dist.irecv, t, peer) for t, peer in recvs]
+        if ops:
+            for w in dist.batch_isend_irecv(ops):
+                w.wait()
+
+    def _handshake_send(self, tensors, names):
+        meta = [(n, tuple(t.shape), str(t.dtype).replace("torch.", ""), bool(t.requires_grad))
+                if torch.is_tensor(t) else (n, None, None, t) for n, t in zip(names, tensors)]
+        dist.send_object_list([meta], dst=self.next_rank, device=self.device)
+
+    def _handshake_recv(self):
+        box = [None]
+        dist.recv_object_list(box, src=self.prev_rank, device=self.device)
+        return box[0]
+
+    def _fwd_recv_buffers(self):
+        """Empty tensors for the values entering this stage (None on stage 0)."""
+        if self.stage_id == 0:
+            return None
+        if self._meta_fwd is None:
+            self._meta_fwd = self._handshake_recv()
+        bufs = []
+        for name, shape, dtype, rg in self._meta_fwd:
+            if shape is None:
+                bufs.append((name, None, rg))
+            else:
+                bufs.append((name, torch.empty(shape, dtype=getattr(torch, dtype),
+                                               device=self.device), rg))
+        return bufs
+
+    @staticmethod
+    def _tensor_list(bufs):
+        return [t for _, t, _ in bufs if t is not None] if bufs else []
+
+    # ---- compute ---------------------------------------------------------- #
+    def _compute_forward(self, mb_inputs, labels, bufs):
+        env, received = {}, []
+        if self.stage_id == 0:
+            env.update(mb_inputs)
+        else:
+            for name, t, rg in bufs:
+                if t is None:
+                    env[name] = rg  # a python constant that travelled in the handshake
+                    continue
+                if rg and t.is_floating_point():
+                    t.requires_grad_(True)
+                    received.append(t)
+                env[name] = t
+        env.update(self.stage(env))
+        rec = {"received": received, "loss": None, "sent": [], "payload": []}
+        if self.stage_id == self.n_stages - 1:
+            out = self.model.materialize_output(env)
+            loss = self.loss_fn(out, labels) if self.loss_fn is not None else (
+                out["loss"] if isinstance(out, dict) else out)
+            if loss.dim() > 0:
+                loss = loss.float().mean()
+            rec["loss"] = loss / self.num_micro_batches
+            return rec
+        names = self.model.live_in[self.stage_id + 1]
+        tensors = [env[n] for n in names]
+        if not getattr(self, "_meta_sent", False):
+            self._handshake_send(tensors, names)
+            self._meta_sent = True
+        rec["payload"] = [t for t in tensors if torch.is_tensor(t)]
+        rec["sent"] = [t for t in rec["payload"] if t.requires_grad]
+        return rec
+
+    def _compute_backward(self, rec, grads):
+        if rec["loss"] is not None:
+            rec["loss"].backward()
+        elif rec["sent"]:
+            torch.autograd.backward(rec["sent"], grads)
+        return [t.grad if t.grad is not None else torch.zeros_like(t) for t in rec["received"]]
+
+    # ---- the schedule ---------------------------------------------------- #
+    def train_batch(self, *args, labels=None, **kwargs):
+        m = self.num_micro_batches
+        env = self.model.bind_inputs(args, kwargs)
+        micro_inputs = [{} for _ in range(m)]
+        for name, val in env.items():
+            for i, piece in enumerate(_split_micro(val, m)):
+                micro_inputs[i][name] = piece
+        micro_labels = _split_micro(labels, m) if labels is not None else [None] * m
+        first, last = self.stage_id == 0, self.stage_id == self.n_stages - 1
+        warmup = min(self.n_stages - self.stage_id - 1, m)
+        steady = m - warmup
+        prev, nxt = self.prev_rank, self.next_rank
+        pending, losses = [], []
+        fwd_i = 0
+
+        def recv_forward():
+            bufs = self._fwd_recv_buffers()
+            if not first:
+                self._exchange([], [(t, prev) for t in self._tensor_list(bufs)])
+            return bufs
+
+        def send_forward(rec):
+            if not last:
+                self._exchange([(t.detach(), nxt) for t in rec["payload"]], [])
+
+        def grad_buffers(rec):
+            return [torch.empty_like(t) for t in rec["sent"]]
+
+        for _ in range(warmup):
+            bufs = recv_forward()
+            rec = self._compute_forward(micro_inputs[fwd_i], micro_labels[fwd_i], bufs)
+            fwd_i += 1
+            send_forward(rec)
+            pending.append(rec)
+        bufs = recv_forward() if steady > 0 else None
+        for it in range(steady):
+            rec = self._compute_forward(micro_inputs[fwd_i], micro_labels[fwd_i], bufs)
+            fwd_i += 1
+            pending.append(rec)
+            # send this forward result, receive the gradient of the oldest one
+            done = pending.pop(0)
+            grads = grad_buffers(done)
+            if not last:
+                self._exchange([(t.detach(), nxt) for t in rec["payload"]],
+                               [(g, nxt) for g in grads])
+            if done["loss"] is not None:
+                losses.append(done["loss"].detach())
+            in_grads = self._compute_backward(done, grads)
+            # send the input gradients, receive the next forward input
+            more = it + 1 < steady
+            bufs = self._fwd_recv_buffers() if (more and not first) else None
+            if not first:
+                self._exchange([(g, prev) for g in in_grads],
+                               [(t, prev) for t in self._tensor_list(bufs)])
+        while pending:
+            done = pending.pop(0)
+            grads = grad_buffers(done)
+            if not last:
+                self._exchange([], [(g, nxt) for g in grads])
+            if done["loss"] is not None:
+                losses.append(done["loss"].detach())
+            in_grads = self._compute_backward(done, grads)
+            if not first:
+                self._exchange([(g, prev) for g in in_grads], [])
+        self._sync_tied_grads()
+        self.inner.micro_step = 0
+        self.inner.step()
+        # the loss lives on the last stage; share it along the pipeline
+        loss = torch.zeros((), device=self.device)
+        if losses:
+            loss = torch.stack(losses).sum().float()
+        if self.mesh.pp_group is not None:
+            src = self.mesh.get_rank(pp=self.n_stages - 1, dp=self.mesh.dp_rank, tp=self.mesh.tp_rank)
+            dist.broadcast(loss, src=src, group=self.mesh.pp_group)
+        self.last_loss = loss
+        return loss
+
+    def __call__(self, *args, **kwargs):
+        return self.model(*args, **kwargs)
+
+    def step(self):
+        return self.inner.step()
