@@ -24,7 +24,8 @@ void comm_gemm(std::vector<int64_t> a_ptrs, std::vector<int64_t> b_ptrs, int64_t
                int64_t gather, int64_t seg_len, int64_t mode, int64_t world, int64_t rank,
                int64_t epoch, int64_t out_ptr, int64_t ldo, int64_t bias_ptr, int64_t act,
                int64_t flags_ptr, std::vector<int64_t> peer_flags, std::vector<int64_t> peer_recv,
-               std::vector<int64_t> peer_out, double wait_seconds) {
+               std::vector<int64_t> peer_out, double wait_seconds, int64_t stage_ptr,
+               int64_t chunk_flags_ptr) {
   TORCH_CHECK(!a_ptrs.empty() && !b_ptrs.empty(), "comm_gemm: operand pointers missing");
   auto a = to_ptrs<void*>(a_ptrs);
   auto b = to_ptrs<void*>(b_ptrs);
@@ -40,7 +41,8 @@ void comm_gemm(std::vector<int64_t> a_ptrs, std::vector<int64_t> b_ptrs, int64_t
       static_cast<int>(ldo), reinterpret_cast<const void*>(bias_ptr), static_cast<int>(act),
       reinterpret_cast<int*>(flags_ptr), peer_flags.empty() ? nullptr : pf.data(),
       peer_recv.empty() ? nullptr : pr.data(), peer_out.empty() ? nullptr : po.data(),
-      slapo_status_ptr(dev), wait_seconds, at::cuda::getCurrentCUDAStream().stream());
+      slapo_status_ptr(dev), wait_seconds, reinterpret_cast<void*>(stage_ptr),
+      reinterpret_cast<int*>(chunk_flags_ptr), at::cuda::getCurrentCUDAStream().stream());
   TORCH_CHECK(rc == 0, "comm_gemm: launch refused (code ", rc,
               "): check divisibility by the group size / 128-row blocks and 16-byte alignment");
 }
@@ -65,7 +67,8 @@ void register_comm_ops(torch::Library& m) {
   m.def("comm_gemm(int[] a_ptrs, int[] b_ptrs, int M, int N, int K, int lda, int ldb, bool a_mn, "
         "bool b_mn, bool bf16, int gather, int seg_len, int mode, int world, int rank, int epoch, "
         "int out_ptr, int ldo, int bias_ptr, int act, int flags_ptr, int[] peer_flags, "
-        "int[] peer_recv, int[] peer_out, float wait_seconds) -> ()", &comm_gemm);
+        "int[] peer_recv, int[] peer_out, float wait_seconds, int stage_ptr, "
+        "int chunk_flags_ptr) -> ()", &comm_gemm);
   m.def("peer_gather(int[] src_ptrs, int dst_ptr, int seg_bytes, int world, int rank, int epoch, "
         "int flags_ptr, int[] peer_flags, float wait_seconds) -> ()", &peer_gather);
 }

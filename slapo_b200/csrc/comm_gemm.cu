@@ -72,6 +72,11 @@ struct CommGemmParams {
   void* peer_out[kMaxRanks];     // all-reduce output buffers [M, N]
   int* status;
   long long wait_cycles;         // budget of a cross-GPU wait
+  // gather mode 4 (rows of A staged through local memory)
+  void* stage_dst;               // local [M, K] buffer the copier warps fill
+  int* chunk_flags;              // local, one word per 128-row block: epoch when staged
+  const void* seg_src[kMaxRanks];  // every rank's shard [seg_len, K]
+  int row_bytes;                 // K * 2
 };
 
 __device__ __forceinline__ void st_release_sys(int* addr, int v) {
@@ -102,6 +107,16 @@ __device__ __forceinline__ bool wait_flag(const int* addr, int epoch, long long 
   return true;
 }
 
+// all 128 copier threads agree on a predicate computed by one of them
+__device__ __forceinline__ int __syncthreads_or_named(int v) {
+  __shared__ int s_copier_vote;
+  if (threadIdx.x == 192) s_copier_vote = v;
+  asm volatile("bar.sync 2, 128;" ::: "memory");
+  const int r = s_copier_vote;
+  asm volatile("bar.sync 2, 128;" ::: "memory");
+  return r;
+}
+
 template <int BN, int STAGES>
 struct CommSmem {
   static constexpr int kABytes = CBM * CBK * 2;
@@ -127,19 +142,22 @@ __device__ __forceinline__ float cload(const void* p, int64_t i, int bf16) {
 // after this one (its data has the longest way to go) and ending with the
 // local block; inside an owner, row blocks then column tiles.
 __device__ __forceinline__ void tile_coords(int t, int tiles_n, int blocks_per_owner, int world,
-                                            int rank, bool rotate, int& m_blk, int& n_blk) {
+                                            int rank, bool rotate, int& m_blk, int& n_blk,
+                                            int first = 1) {
   n_blk = t % tiles_n;
   int mb = t / tiles_n;
   if (rotate) {
+    // first = 1: start with the next rank's rows, own rows last (scatter);
+    // first = 0: own rows first, remote rows while they are being staged (gather)
     const int o_idx = mb / blocks_per_owner;
-    const int owner = (rank + 1 + o_idx) % world;
+    const int owner = (rank + first + o_idx) % world;
     mb = owner * blocks_per_owner + mb % blocks_per_owner;
   }
   m_blk = mb;
 }
 
 template <int BN, int STAGES, bool A_MN, bool B_MN>
-__global__ void __launch_bounds__(192, 1)
+__global__ void __launch_bounds__(320, 1)
 comm_gemm_kernel(const __grid_constant__ SegMaps maps_a, const __grid_constant__ SegMaps maps_b,
                  const CommGemmParams p) {
   using S = CommSmem<BN, STAGES>;
@@ -162,7 +180,9 @@ comm_gemm_kernel(const __grid_constant__ SegMaps maps_a, const __grid_constant__
   const int num_kb = (p.K + CBK - 1) / CBK;
   const bool scatter = p.mode != kModeLocal;
   const int rows_per_rank = p.M / p.world;               // used when rows are owned (gather 1 / scatter)
-  const bool rotate = p.world > 1 && (scatter || p.gather == 1) && rows_per_rank % CBM == 0;
+  const bool staged = p.gather == 4;
+  const int first = staged ? 0 : 1;
+  const bool rotate = p.world > 1 && (scatter || p.gather == 1 || staged) && rows_per_rank % CBM == 0;
   const int blocks_per_owner = rotate ? rows_per_rank / CBM : tiles_m;
   constexpr uint32_t kTmemCols = 2 * BN <= 128 ? 128 : (2 * BN <= 256 ? 256 : 512);
 
@@ -213,13 +233,25 @@ comm_gemm_kernel(const __grid_constant__ SegMaps maps_a, const __grid_constant__
       };
       for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
         int m_blk, n_blk;
-        tile_coords(t, tiles_n, blocks_per_owner, p.world, p.rank, rotate, m_blk, n_blk);
+        tile_coords(t, tiles_n, blocks_per_owner, p.world, p.rank, rotate, m_blk, n_blk, first);
         const int m0 = m_blk * CBM, n0 = n_blk * BN;
         int a_seg = 0, a_row = m0;
         if (p.gather == 1) {
           a_seg = m0 / p.seg_len;
           a_row = m0 - a_seg * p.seg_len;
           if (!need_ready(a_seg)) { ok = false; break; }
+        } else if (staged) {
+          if (m0 / p.seg_len == p.rank) {
+            a_seg = 0;                      // own shard, read in place
+            a_row = m0 - p.rank * p.seg_len;
+          } else {
+            a_seg = 1;                      // staged copy in local memory
+            if (!wait_flag(p.chunk_flags + m_blk, p.epoch, p.wait_cycles, abort_flag)) {
+              ok = false;
+              break;
+            }
+            asm volatile("fence.proxy.async;" ::: "memory");
+          }
         }
         for (int kb = 0; kb < num_kb; ++kb) {
           int k_a = kb * CBK, k_b = kb * CBK, seg_a = a_seg, seg_b = 0;
@@ -288,6 +320,50 @@ comm_gemm_kernel(const __grid_constant__ SegMaps maps_a, const __grid_constant__
         if (ok) tc::umma_commit(&tmem_full[acc]);
       }
     }
+  } else if (warp >= 6) {
+    // ------------------------------ copier warps --------------------------------
+    // Remote shards cross NVLink exactly once: 128-row blocks are pulled into
+    // the local staging buffer (16-byte coalesced loads, 8 in flight per
+    // thread) and published block by block; the producer warps of all CTAs
+    // read staged blocks with local TMA loads.
+    if (staged && p.world > 1) {
+      const int ct = threadIdx.x - 192;
+      const int64_t blk_vec = static_cast<int64_t>(CBM) * p.row_bytes / 16;
+      int j = 0;
+      bool ok = true;
+      for (int o_idx = 1; o_idx < p.world && ok; ++o_idx) {
+        const int owner = (p.rank + o_idx) % p.world;
+        bool owner_ready = false;
+        for (int b = 0; b < blocks_per_owner; ++b, ++j) {
+          if (j % static_cast<int>(gridDim.x) != static_cast<int>(blockIdx.x)) continue;
+          if (!owner_ready) {
+            int w = 1;
+            if (ct == 0) w = wait_flag(ready + owner, p.epoch, p.wait_cycles, abort_flag) ? 1 : 0;
+            w = __syncthreads_or_named(w);
+            if (!w) { ok = false; break; }
+            owner_ready = true;
+          }
+          const uint4* src = reinterpret_cast<const uint4*>(
+              static_cast<const uint8_t*>(p.seg_src[owner]) +
+              static_cast<int64_t>(b) * CBM * p.row_bytes);
+          const int m_blk = owner * blocks_per_owner + b;
+          uint4* dst = reinterpret_cast<uint4*>(static_cast<uint8_t*>(p.stage_dst) +
+                                                static_cast<int64_t>(m_blk) * CBM * p.row_bytes);
+          for (int64_t v = ct; v < blk_vec; v += 128 * 8) {
+            uint4 tmp[8];
+#pragma unroll
+            for (int u = 0; u < 8; ++u)
+              if (v + u * 128 < blk_vec) tmp[u] = src[v + u * 128];
+#pragma unroll
+            for (int u = 0; u < 8; ++u)
+              if (v + u * 128 < blk_vec) dst[v + u * 128] = tmp[u];
+          }
+          __threadfence();
+          asm volatile("bar.sync 2, 128;" ::: "memory");
+          if (ct == 0) st_release_sys(p.chunk_flags + m_blk, p.epoch);
+        }
+      }
+    }
   } else {
     // ------------------------------ epilogue ----------------------------------
     const int quarter = warp & 3;
@@ -297,7 +373,7 @@ comm_gemm_kernel(const __grid_constant__ SegMaps maps_a, const __grid_constant__
     const int tiles_per_owner = blocks_per_owner * tiles_n;
     for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, ++iter) {
       int m_blk, n_blk;
-      tile_coords(t, tiles_n, blocks_per_owner, p.world, p.rank, rotate, m_blk, n_blk);
+      tile_coords(t, tiles_n, blocks_per_owner, p.world, p.rank, rotate, m_blk, n_blk, first);
       const int m0 = m_blk * CBM, n0 = n_blk * BN;
       const int acc = iter & 1;
       const uint32_t acc_phase = (iter >> 1) & 1;
@@ -559,7 +635,7 @@ static int launch_comm_variant(const SegMaps& ma, const SegMaps& mb, const CommG
   int grid = tiles < sm_count() ? tiles : sm_count();
   if (p.mode != kModeLocal) grid = sm_count();  // all CTAs take part in the reduction
   count_launch();
-  kernel<<<grid, 192, S::kTotal, stream>>>(ma, mb, p);
+  kernel<<<grid, p.gather == 4 ? 320 : 192, S::kTotal, stream>>>(ma, mb, p);
   return cudaGetLastError() == cudaSuccess ? 0 : 4;
 }
 
@@ -569,9 +645,12 @@ int launch_comm_gemm(void* const* a_ptrs, void* const* b_ptrs, int M, int N, int
                      int ldb, bool a_mn, bool b_mn, bool bf16, int gather, int seg_len, int mode,
                      int world, int rank, int epoch, void* out, int ldo, const void* bias, int act,
                      int* flags, int* const* peer_flags, void* const* peer_recv,
-                     void* const* peer_out, int* status, double wait_seconds,
-                     cudaStream_t stream) {
+                     void* const* peer_out, int* status, double wait_seconds, void* stage_dst,
+                     int* chunk_flags, cudaStream_t stream) {
   if (M <= 0 || N <= 0 || K <= 0) return 0;
+  if (gather == 4 && (a_mn || stage_dst == nullptr || chunk_flags == nullptr || lda != K ||
+                      seg_len % CBM != 0 || seg_len * world != M))
+    return 1;
   if (N % 8 || K % 8 || lda % 8 || ldb % 8 || ldo % 8) return 1;
   if (world < 1 || world > kMaxRanks) return 1;
   if (a_mn && M % 8) return 1;
@@ -582,7 +661,13 @@ int launch_comm_gemm(void* const* a_ptrs, void* const* b_ptrs, int M, int N, int
   SegMaps ma, mb;
   const int a_segs = (gather == 1 || gather == 2) ? world : 1;
   const int b_segs = gather == 3 ? world : 1;
-  for (int s = 0; s < a_segs; ++s) {
+  if (gather == 4) {
+    // map 0: this rank's shard in place; map 1: the local staging buffer [M, K]
+    if (!make_tmap_2d(&ma.map[0], a_ptrs[rank], K, seg_len, lda, 64, CBM, 2, bf16) ||
+        !make_tmap_2d(&ma.map[1], stage_dst, K, M, lda, 64, CBM, 2, bf16))
+      return 2;
+  }
+  for (int s = 0; s < a_segs && gather != 4; ++s) {
     // extents of one segment
     const uint64_t rows = gather == 1 ? seg_len : M;
     const uint64_t kk = gather == 2 ? seg_len : K;
@@ -602,7 +687,9 @@ int launch_comm_gemm(void* const* a_ptrs, void* const* b_ptrs, int M, int N, int
   p.bias = bias; p.act = act; p.bf16 = bf16 ? 1 : 0; p.flags = flags; p.status = status;
   p.idesc = tc::instr_desc_f16(CBM, BN, bf16 ? 1 : 0, a_mn, b_mn);
   p.wait_cycles = static_cast<long long>(wait_seconds * 1.9e9);
+  p.stage_dst = stage_dst; p.chunk_flags = chunk_flags; p.row_bytes = K * 2;
   for (int r = 0; r < world; ++r) {
+    p.seg_src[r] = gather == 4 ? a_ptrs[r] : nullptr;
     p.peer_flags[r] = peer_flags != nullptr ? peer_flags[r] : flags;
     p.peer_recv[r] = peer_recv != nullptr ? peer_recv[r] : nullptr;
     p.peer_out[r] = peer_out != nullptr ? peer_out[r] : nullptr;

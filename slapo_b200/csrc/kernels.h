@@ -46,14 +46,16 @@ void launch_sq_norm(const void* x, const uint8_t* mask, float* out2, int64_t n, 
                     cudaStream_t stream);
 
 // Fused GEMM + collective over peer memory (comm_gemm.cu).
-//   gather: 0 none, 1 rows of A, 2 contraction dim of A, 3 contraction dim of B
+//   gather: 0 none, 1 rows of A, 2 contraction dim of A, 3 contraction dim of B,
+//           4 rows of A staged once through the local buffer stage_dst (chunk_flags: one
+//           int per 128-row block, zero-initialised, kept across calls)
 //   mode:   0 local output, 1 reduce-scatter, 2 all-reduce
 int launch_comm_gemm(void* const* a_ptrs, void* const* b_ptrs, int M, int N, int K, int lda,
                      int ldb, bool a_mn, bool b_mn, bool bf16, int gather, int seg_len, int mode,
                      int world, int rank, int epoch, void* out, int ldo, const void* bias, int act,
                      int* flags, int* const* peer_flags, void* const* peer_recv,
-                     void* const* peer_out, int* status, double wait_seconds,
-                     cudaStream_t stream);
+                     void* const* peer_out, int* status, double wait_seconds, void* stage_dst,
+                     int* chunk_flags, cudaStream_t stream);
 
 // dst = concatenation of every rank's segment, pulled over NVLink (comm_gemm.cu)
 int launch_peer_gather(void* const* src_ptrs, void* dst, int64_t seg_bytes, int world, int rank,

@@ -30,7 +30,7 @@ import torch
 
 from ..ops import native
 
-GATHER_NONE, GATHER_A_ROWS, GATHER_A_K, GATHER_B_K = 0, 1, 2, 3
+GATHER_NONE, GATHER_A_ROWS, GATHER_A_K, GATHER_B_K, GATHER_A_ROWS_STAGED = 0, 1, 2, 3, 4
 MODE_LOCAL, MODE_RS, MODE_AR = 0, 1, 2
 
 
@@ -48,7 +48,7 @@ def _check_status():
 
 def comm_gemm(ctx, *, a_ptrs, b_ptrs, M, N, K, lda, ldb, a_mn, b_mn, dtype, gather=GATHER_NONE,
               seg_len=0, mode=MODE_LOCAL, out_ptr=0, ldo=0, bias=None, act=-1, recv=None,
-              ar_out=None):
+              ar_out=None, stage=None, chunk_flags=None):
     """Thin wrapper of ``torch.ops.slapo_b200.comm_gemm``; takes the next epoch."""
     epoch = ctx.next_epoch()
     native.ops().comm_gemm(
@@ -56,8 +56,26 @@ def comm_gemm(ctx, *, a_ptrs, b_ptrs, M, N, K, lda, ldb, a_mn, b_mn, dtype, gath
         dtype == torch.bfloat16, gather, seg_len, mode, ctx.world, ctx.rank, epoch, int(out_ptr),
         ldo, bias.data_ptr() if bias is not None else 0, act, ctx.flags_ptr,
         list(ctx.peer_flag_ptrs), list(recv.ptrs()) if recv is not None else [],
-        list(ar_out.ptrs()) if ar_out is not None else [], float(ctx.wait_seconds))
+        list(ar_out.ptrs()) if ar_out is not None else [], float(ctx.wait_seconds),
+        stage.data_ptr() if stage is not None else 0,
+        chunk_flags.data_ptr() if chunk_flags is not None else 0)
     return epoch
+
+
+def _staging(ctx, t, k, dtype, device):
+    """Local staging buffer [t, k] and per-block flags for the staged gather."""
+    st = ctx.__dict__.setdefault("_stage_local", {})
+    key = (dtype, str(device))
+    buf = st.get(key)
+    if buf is None or buf.numel() < t * k:
+        buf = torch.empty(t * k, dtype=dtype, device=device)
+        st[key] = buf
+    flags = st.get("flags")
+    need = (t + 127) // 128
+    if flags is None or flags.numel() < need:
+        flags = torch.zeros(max(need, 4096), dtype=torch.int32, device=device)
+        st["flags"] = flags
+    return buf[:t * k].view(t, k), flags
 
 
 def _stage(ctx, name, t: torch.Tensor):
@@ -91,15 +109,24 @@ def peer_gather(ctx, shard, name):
 
 
 # ---------------------------------------------------------------------- #
-def ag_gemm(ctx, x_shard, w, bias=None, act=-1, name="ag_in", staged=None):
-    """``all_gather(x_shard) @ w.T`` with the gather inside the GEMM."""
+def ag_gemm(ctx, x_shard, w, bias=None, act=-1, name="ag_in", staged=None, b_mn=False):
+    """``all_gather(x_shard) @ w.T`` with the gather inside the GEMM
+    (``b_mn``: ``w`` is ``[K, N]`` and the product is ``all_gather(x) @ w``)."""
     ts, k = x_shard.shape
-    n = w.shape[0]
+    n = w.shape[1] if b_mn else w.shape[0]
     t = ts * ctx.world
     buf = staged if staged is not None else _stage(ctx, name, x_shard)
     y = torch.empty(t, n, dtype=x_shard.dtype, device=x_shard.device)
+    if ts % 128 == 0 and ctx.world > 1:
+        # remote rows are pulled once into a local staging buffer by copier warps
+        stage, flags = _staging(ctx, t, k, x_shard.dtype, x_shard.device)
+        comm_gemm(ctx, a_ptrs=buf.ptrs(), b_ptrs=[w.data_ptr()], M=t, N=n, K=k, lda=k,
+                  ldb=w.stride(0), a_mn=False, b_mn=b_mn, dtype=x_shard.dtype,
+                  gather=GATHER_A_ROWS_STAGED, seg_len=ts, out_ptr=y.data_ptr(), ldo=n, bias=bias,
+                  act=act, stage=stage, chunk_flags=flags)
+        return y
     comm_gemm(ctx, a_ptrs=buf.ptrs(), b_ptrs=[w.data_ptr()], M=t, N=n, K=k, lda=k,
-              ldb=w.stride(0), a_mn=False, b_mn=False, dtype=x_shard.dtype,
+              ldb=w.stride(0), a_mn=False, b_mn=b_mn, dtype=x_shard.dtype,
               gather=GATHER_A_ROWS, seg_len=ts, out_ptr=y.data_ptr(), ldo=n, bias=bias, act=act)
     return y
 
@@ -169,12 +196,8 @@ class _RSLinear(torch.autograd.Function):
         dy_shard = dy_shard.contiguous()
         ts, n = dy_shard.shape
         t, kl = x.shape
-        staged = _stage(sctx, "ag_dy_bwd", dy_shard)
         # dX = all_gather(dYs) @ W: A rows gathered inside the GEMM, B = W read N-major
-        dx = torch.empty(t, kl, dtype=x.dtype, device=x.device)
-        comm_gemm(sctx, a_ptrs=staged.ptrs(), b_ptrs=[w.data_ptr()], M=t, N=kl, K=n, lda=n,
-                  ldb=w.stride(0), a_mn=False, b_mn=True, dtype=x.dtype, gather=GATHER_A_ROWS,
-                  seg_len=ts, out_ptr=dx.data_ptr(), ldo=kl)
+        dx = ag_gemm(sctx, dy_shard, w, None, name="ag_dy_bwd", b_mn=True)
         # dW = all_gather(dYs)^T @ X: long contraction, few tiles (see _AGLinear)
         dw = peer_gather(sctx, dy_shard, "ag_dy_bwd2").t() @ x
         # the bias is added on the owner's rows only: its gradient is partial
