@@ -1,2 +1,2 @@
 """Per-model scheduling recipes (registered on import)."""
-from . import bert  # noqa: F401
+from . import bert, decoder  # noqa: F401

@@ -82,15 +82,17 @@ class VocabParallelEmbeddingHooks:
         return reduce_forward_output(output, self.group)
 
 
-def shard_word_embedding(sch, vocab_size, sequence_parallel=False):
-    """Vocabulary-parallel word embedding (the tied LM head follows)."""
+def shard_word_embedding(sch, vocab_size, sequence_parallel=False, sp_axis=1):
+    """Vocabulary-parallel word embedding (the tied LM head follows).  Under
+    sequence parallelism the partial lookups are reduce-scattered along
+    ``sp_axis`` instead of all-reduced."""
     if sch.world_size == 1:
         return
     if vocab_size % sch.world_size != 0:
         raise ValueError(f"vocab size {vocab_size} must be padded to a multiple of "
                          f"{sch.world_size} before sharding")
     sch.shard("weight", axis=0)
-    hooks = VocabParallelEmbeddingHooks(sch, sequence_parallel)
+    hooks = VocabParallelEmbeddingHooks(sch, sequence_parallel, sp_axis)
     sch.sync("fwd_pre", hooks.pre)
     sch.sync("fwd_post", hooks.post)
 

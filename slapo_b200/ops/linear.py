@@ -125,6 +125,29 @@ class LinearWithSyncFunc(nn.Linear):
         return text
 
 
+class Conv1DWithSyncFunc(nn.Module):
+    """GPT-2 ``Conv1D`` (weight ``[in, out]``) as ``x @ W -> sync_fn -> + bias``."""
+
+    traceable = False
+
+    def __init__(self, nf, nx, device=None, dtype=None, sync_fn=None):
+        super().__init__()
+        self.nf, self.nx = nf, nx
+        self.weight = nn.Parameter(torch.empty(nx, nf, device=device, dtype=dtype))
+        self.bias = nn.Parameter(torch.zeros(nf, device=device, dtype=dtype))
+        self.sync_fn = sync_fn
+
+    def forward(self, x):
+        size_out = x.size()[:-1] + (self.weight.shape[-1],)
+        out = torch.mm(x.view(-1, x.size(-1)), self.weight).view(size_out)
+        if self.sync_fn is not None:
+            out = self.sync_fn(out)
+        return out + self.bias
+
+    def extra_repr(self):
+        return f"nx={self.nx}, nf={self.nf}, sync_fn={self.sync_fn}"
+
+
 _ACTS = ("gelu", "gelu_new", "gelu_tanh", "gelu_pytorch_tanh", "relu")
 
 

@@ -342,6 +342,46 @@ class ShardEmbedding(ShardMethod):
         return ("partial", None) if axis == 0 else ("partition", -1)
 
 
+def _conv1d_cls():
+    try:
+        from ..models.gpt import Conv1D
+
+        return Conv1D
+    except Exception:  # pragma: no cover
+        return None
+
+
+@register_shard_method(_conv1d_cls())
+class ShardConv1D(ShardMethod):
+    """GPT-2 ``Conv1D``: the weight is ``[in, out]``, so axis 1 splits the
+    output features (partitioned output) and axis 0 the input features
+    (partial sums)."""
+
+    @staticmethod
+    def postproc(sch, param_name, sharded_size, axis):
+        if param_name == "bias" or axis == 1:
+            sch.mod.nf = sharded_size
+        else:
+            sch.mod.nx = sharded_size
+
+    @staticmethod
+    def infer_output_type(sch, param_name, sharded_size, axis):
+        if param_name == "bias" or axis == 1:
+            return "partition", -1
+        return "partial", None
+
+    @staticmethod
+    def sync(sch, mode, sync_op_or_fn, **kwargs):
+        from ..ops.linear import Conv1DWithSyncFunc
+
+        def make(mod, fn):
+            new = Conv1DWithSyncFunc(mod.nf, mod.nx, device="meta", sync_fn=fn)
+            new.weight, new.bias = mod.weight, mod.bias
+            return new
+
+        return _sync_with_deferred_bias(sch, mode, sync_op_or_fn, make, **kwargs)
+
+
 @register_shard_method(nn.LayerNorm)
 class ShardLayerNorm(ShardMethod):
     @staticmethod
