@@ -1,2 +1,2 @@
 """Per-model scheduling recipes (registered on import)."""
-from . import bert, decoder  # noqa: F401
+from . import albert, bert, decoder, t5, wideresnet  # noqa: F401

@@ -1,0 +1,63 @@
+"""Scheduling recipe for ALBERT: the single shared layer group is scheduled
+once and every depth benefits.  q / k / v and ``ffn`` column-parallel,
+``attention.dense`` and ``ffn_output`` row-parallel, the factorised word
+embedding vocabulary-parallel, bias + activation of ``ffn`` fused.
+
+Parity: slapo/model_schedule/albert.py:21-353 of the reference.
+"""
+from __future__ import annotations
+
+from ... import create_schedule
+from ...model_schedule.registry import register_schedule
+from ...ops.linear import LinearWithAct
+from .common import (broadcast_input, cast_dtype, logger, shard_column, shard_row,
+                     shard_word_embedding)
+
+
+def _layers(sch, prefix):
+    out = []
+    enc = sch[f"{prefix}.encoder"]
+    for g in [k for k in enc.child if k.startswith("albert_layer_groups.")]:
+        grp = enc[g]
+        for l in [k for k in grp.child if k.startswith("albert_layers.")]:
+            out.append(f"{prefix}.encoder.{g}.{l}")
+    return out
+
+
+@register_schedule("albert")
+def schedule_albert(model, model_config=None, prefix="albert", fp16=False, bf16=False,
+                    group=None, fuse=True, ckpt_ratio=0.0, bcast_input=False, **_unused):
+    config = model_config if model_config is not None else getattr(model, "config", None)
+    if config is None:
+        raise ValueError("model_config is required")
+    cast_dtype(model, fp16, bf16)
+    sch = create_schedule(model, group=group)
+    layers = _layers(sch, prefix)
+    for path in layers:
+        if fuse:
+            ffn = sch[f"{path}.ffn"]
+            ffn.replace(LinearWithAct.from_linear(ffn.mod, act_fn=config.hidden_act))
+            # the activation module after it becomes the identity
+            sch[f"{path}.activation"].replace(__import__("torch").nn.Identity())
+        if sch.world_size > 1:
+            for name in ("query", "key", "value"):
+                shard_column(sch[f"{path}.attention.{name}"])
+            shard_row(sch[f"{path}.attention.dense"])
+            shard_column(sch[f"{path}.ffn"])
+            shard_row(sch[f"{path}.ffn_output"])
+    if sch.world_size > 1 and config.vocab_size % sch.world_size == 0:
+        shard_word_embedding(sch[f"{prefix}.embeddings.word_embeddings"], config.vocab_size)
+        if "predictions" in sch:
+            head = sch["predictions"]
+            head["decoder"].shard("weight", axis=0)
+            head["decoder"].shard("bias", axis=0)
+            head.shard("bias", axis=0)
+            head["decoder"].sync("bwd_post", "all_reduce")
+    if bcast_input:
+        broadcast_input(sch)
+    if ckpt_ratio > 0:
+        for path in layers:
+            sch[path].checkpoint()
+    logger.info("albert schedule: %d shared layers scheduled (tp=%d)", len(layers),
+                sch.world_size, ranks=0)
+    return sch

@@ -97,12 +97,15 @@ class Schedule:
     # path handling
     @staticmethod
     def tokenize_module_path(module_path: str) -> list[str]:
-        """``"a.b.0.c"`` -> ``["a", "b.0", "c"]`` (an index joins its list)."""
+        """``"a.b.0.c"`` -> ``["a", "b.0", "c"]`` (an index joins its list; a
+        leading index, as in ``sch["layer1"]["0"]``, names a child of an
+        ``nn.Sequential`` and stays a token of its own)."""
         tokens: list[str] = []
         for piece in module_path.split("."):
             if piece.isdigit():
                 if not tokens:
-                    raise KeyError(f"invalid module path '{module_path}'")
+                    tokens.append(piece)
+                    continue
                 tokens[-1] = f"{tokens[-1]}.{piece}"
             else:
                 tokens.append(piece)
