@@ -99,7 +99,7 @@ def bench_gelu(small, iters):
 
 
 def bench_attn(small, iters):
-    shapes = [(4, 512, 16, 64, False)] if small else [
+    shapes = [(64, 512, 16, 64, False)] if small else [
         (32, 512, 16, 64, False), (4, 1024, 20, 128, True), (8, 2048, 16, 64, True)]
     for (bsz, s, h, d, causal) in shapes:
         qkv = torch.randn(bsz, s, h, 3, d, device="cuda", dtype=torch.bfloat16, requires_grad=True)
@@ -118,7 +118,7 @@ def bench_attn(small, iters):
 
 
 def bench_gemm(small, iters):
-    shapes = [(2048, 2048, 1024)] if small else [
+    shapes = [(8192, 8192, 2048)] if small else [
         (16384, 4096, 1024), (16384, 1024, 4096), (16384, 3072, 1024), (8192, 8192, 8192)]
     for (m, n, k) in shapes:
         a = torch.randn(m, k, device="cuda", dtype=torch.bfloat16)

@@ -26,6 +26,47 @@ from torch import nn
 from .base import Primitive, register_primitive
 
 
+_FUNCTION_MODULES = {
+    torch.nn.functional.relu: nn.ReLU,
+    torch.relu: nn.ReLU,
+    torch.nn.functional.gelu: nn.GELU,
+    torch.tanh: nn.Tanh,
+    torch.nn.functional.silu: nn.SiLU,
+    torch.sigmoid: nn.Sigmoid,
+}
+
+
+def _group_as_sequential(sch, chain, gm, name):
+    """An ``nn.Sequential`` subclass named ``name``.  A straight chain of module
+    calls and single-input activations keeps its members as elements ``0..n-1``;
+    anything else is grouped as one extracted graph module.  The first element
+    receives every external input of the chain."""
+
+    def forward(self, *args):
+        mods = list(self)
+        out = mods[0](*args)
+        for mod in mods[1:]:
+            out = mod(out)
+        return out
+
+    seq_cls = type(name, (nn.Sequential,), {"forward": forward})
+    members = []
+    prev = None
+    for path, node in chain:
+        owner = sch.mod if not path else sch.get_module(path)
+        straight = prev is None or (len(node.all_input_nodes) == 1
+                                    and node.all_input_nodes[0] is prev)
+        if node.op == "call_module" and straight:
+            members.append(owner.get_submodule(node.target))
+        elif (node.op == "call_function" and straight and node.target in _FUNCTION_MODULES
+              and len(node.args) == 1 and not node.kwargs):
+            members.append(_FUNCTION_MODULES[node.target]())
+        else:
+            return seq_cls(gm)
+        prev = node
+    return seq_cls(*members)
+
+
 @register_primitive()
 class FusePrimitive(Primitive):
     @staticmethod
@@ -50,8 +91,7 @@ class FusePrimitive(Primitive):
             if compiler == "TorchScript":
                 new_mod = torch.jit.script(gm)
             elif compiler is None:
-                seq_cls = type(name, (nn.Sequential,), {})
-                new_mod = seq_cls(gm)
+                new_mod = _group_as_sequential(sch, chain, gm, name)
             else:
                 raise ValueError(f"unknown compiler {compiler}")
         return sch.replace(new_mod, subgraph, name=name)
