@@ -418,6 +418,67 @@ class TrainEngine:
             self.flat_param[lo:hi].copy_(self.master[pos:pos + hi - lo])
         self._gather_params()
 
+    def _param_names(self):
+        names = {}
+        for name, p in self.model.named_parameters():
+            names.setdefault(id(p), name)
+        return [names[id(p)] for p in self.params]
+
+    def _gather_flat_state(self, own: torch.Tensor) -> torch.Tensor:
+        """This rank's packed optimizer slices -> the whole flat fp32 vector
+        (all-gathered bucket by bucket under ZeRO)."""
+        flat = torch.zeros(self.total, dtype=torch.float32, device=self.device)
+        sharded = self.cfg.zero and self.dp_size > 1
+        for bucket, (lo, hi), pos in zip(self.buckets, self.shard_ranges, self.shard_offsets):
+            piece = own[pos:pos + hi - lo]
+            if sharded:
+                dist.all_gather_into_tensor(flat[bucket.start:bucket.end], piece.contiguous(),
+                                            group=self.dp_group)
+            else:
+                flat[lo:hi].copy_(piece)
+        return flat
+
+    def full_optimizer_state(self, to_cpu=True):
+        """Optimizer state keyed by parameter name, each tensor in the local
+        (tensor-parallel shard) shape of its parameter - the layout-free form
+        that checkpoints store, so that a run with another DP size, bucket size
+        or ZeRO setting can resume from it.  Collective over the DP group."""
+        out = {"step": self.step_count, "state": {}}
+        names = self._param_names()
+        for key in ("master", "exp_avg", "exp_avg_sq"):
+            flat = self._gather_flat_state(getattr(self, key))
+            for name, p, (off, n, _) in zip(names, self.params, self.param_slices):
+                t = flat[off:off + n].view(p.shape)
+                out["state"].setdefault(name, {})[key] = t.cpu() if to_cpu else t.clone()
+            del flat
+        return out
+
+    def load_full_optimizer_state(self, full):
+        """Inverse of :meth:`full_optimizer_state`; parameters missing from
+        ``full`` keep a fresh state (master = current weights, moments = 0)."""
+        self.step_count = int(full.get("step", 0))
+        names = self._param_names()
+        for key in ("master", "exp_avg", "exp_avg_sq"):
+            flat = torch.zeros(self.total, dtype=torch.float32, device=self.device)
+            if key == "master":
+                flat.copy_(self.flat_param)
+            for name, p, (off, n, _) in zip(names, self.params, self.param_slices):
+                entry = full["state"].get(name)
+                if entry is None or key not in entry:
+                    continue
+                src = entry[key]
+                if tuple(src.shape) != tuple(p.shape):
+                    raise ValueError(f"optimizer state of {name}: shape {tuple(src.shape)} does "
+                                     f"not match the parameter's {tuple(p.shape)}")
+                flat[off:off + n].copy_(src.reshape(-1))
+            own = getattr(self, key)
+            for (lo, hi), pos in zip(self.shard_ranges, self.shard_offsets):
+                own[pos:pos + hi - lo].copy_(flat[lo:hi])
+            del flat
+        for (lo, hi), pos in zip(self.shard_ranges, self.shard_offsets):
+            self.flat_param[lo:hi].copy_(self.master[pos:pos + hi - lo])
+        self._gather_params()
+
     def refresh_master_from_params(self):
         """After loading model weights into ``p.data``: re-seed the fp32 master."""
         for (lo, hi), pos in zip(self.shard_ranges, self.shard_offsets):
