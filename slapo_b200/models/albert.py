@@ -48,7 +48,7 @@ class AlbertEmbeddings(nn.Module):
                              persistent=False)
 
     def forward(self, input_ids, token_type_ids=None):
-        pos = self.position_ids[:, :input_ids.size(1)]
+        pos = self.position_ids.narrow(1, 0, input_ids.size(1))
         emb = self.word_embeddings(input_ids) + self.position_embeddings(pos)
         emb = emb + (self.token_type_embeddings.weight[0] if token_type_ids is None
                      else self.token_type_embeddings(token_type_ids))

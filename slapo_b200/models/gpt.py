@@ -261,7 +261,7 @@ class GPTTransformer(_GPTBase):
 
     def forward(self, input_ids, attention_mask=None, position_ids=None):
         if position_ids is None:
-            position_ids = self.position_ids[:, :input_ids.size(1)]
+            position_ids = self.position_ids.narrow(1, 0, input_ids.size(1))
         ext_mask = None
         if attention_mask is not None:
             ext_mask = (1.0 - attention_mask[:, None, None, :].to(self.ln_f.weight.dtype)) * -10000.0

@@ -113,7 +113,7 @@ class OPTDecoder(_GPTBase):
                              persistent=False)
 
     def forward(self, input_ids, attention_mask=None):
-        positions = self.position_ids[:, :input_ids.size(1)]
+        positions = self.position_ids.narrow(1, 0, input_ids.size(1))
         ext_mask = None
         if attention_mask is not None:
             ext_mask = (1.0 - attention_mask[:, None, None, :].to(

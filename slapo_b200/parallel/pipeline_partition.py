@@ -242,9 +242,18 @@ def build_pipeline_model(sch, target, **kwargs):
     stage_cls = get_dialect_cls("pipeline_stage", target)
     engine_cls = get_dialect_cls("pipeline_engine", target)
     stages = []
+    top_attrs = {}
+    for node in sch.mod.graph.nodes:
+        if node.op == "get_attr":
+            value = sch.mod
+            for tok in node.target.split("."):
+                value = getattr(value, tok)
+            top_attrs[node.name] = value
     for i, name in enumerate(stage_names):
+        consts = {n: top_attrs[n] for n in stage_inputs[i] if n in top_attrs}
+        extra = {"constants": consts} if consts else {}
         stages.append(stage_cls(getattr(sch.mod, name), i, len(stage_names), stage_inputs[i],
-                                stage_output_names(sch.mod)[i]))
+                                stage_output_names(sch.mod)[i], **extra))
     input_names = [n.name for n in sch.mod.graph.nodes if n.op == "placeholder"]
     return engine_cls(stages, live_in=live_in, input_names=input_names,
                       output_spec=final_output_spec(sch.mod))

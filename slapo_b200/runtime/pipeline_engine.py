@@ -36,15 +36,30 @@ logger = get_logger("pipeline_engine")
 class PipelineStage(nn.Module):
     """One stage: maps value names to the stage module's arguments and back."""
 
-    def __init__(self, module, index, n_stages, input_names, output_names):
+    def __init__(self, module, index, n_stages, input_names, output_names, constants=None):
         super().__init__()
         self.module = module
         self.index, self.n_stages = index, n_stages
         self.input_names = list(input_names)
         self.output_names = list(output_names)
+        # buffers / parameters that the split left at the top level (for example a
+        # position-id table read by the first stage): owned by the stage that reads them
+        self.const_names = {}
+        for name, value in (constants or {}).items():
+            attr = f"const_{name}"
+            if isinstance(value, nn.Parameter):
+                self.register_parameter(attr, value)
+            else:
+                self.register_buffer(attr, value, persistent=False)
+            self.const_names[name] = attr
+
+    def _value(self, env, name):
+        if name in self.const_names and name not in env:
+            return getattr(self, self.const_names[name])
+        return env[name]
 
     def forward(self, env: dict):
-        out = self.module(*[env[n] for n in self.input_names])
+        out = self.module(*[self._value(env, n) for n in self.input_names])
         produced = {}
         for name, idx in self.output_names:
             produced[name] = out if idx is None else out[idx]

@@ -78,3 +78,47 @@ def _pp_worker(rank, world):
 
 def test_pipeline_1f1b_loss_matches_reference():
     run_distributed(_pp_worker, 2)
+
+
+def _zoo_pipeline(name, n_stages):
+    """Scheduled + partitioned model of the zoo, run stage after stage in one
+    process, against the unpartitioned model."""
+    from slapo_b200.models.zoo import get_model_spec
+    from slapo_b200.framework_dialect import get_dialect_cls  # noqa: F401
+    from slapo_b200.parallel.pipeline_partition import build_pipeline_model
+
+    spec = get_model_spec(name)
+    cfg = spec.config
+    for key, val in (("num_hidden_layers", 4), ("num_layers", 4), ("num_decoder_layers", 4),
+                     ("hidden_size", 32), ("d_model", 32), ("intermediate_size", 64),
+                     ("ffn_dim", 64), ("d_ff", 64), ("num_attention_heads", 2), ("num_heads", 2),
+                     ("d_kv", 16), ("vocab_size", 128), ("dropout", 0.0), ("dropout_rate", 0.0),
+                     ("resid_dropout", 0.0), ("embed_dropout", 0.0), ("attention_dropout", 0.0)):
+        if hasattr(cfg, key) and not isinstance(getattr(type(cfg), key, None), property):
+            setattr(cfg, key, val)
+    torch.manual_seed(3)
+    model = spec.build().init_weights().eval()
+    inputs, labels = spec.make_batch(2, 16, 8, seed=1)
+    want = model(*inputs)["logits"]
+    if spec.kind == "seq2seq":
+        cuts = [generate_pipeline_cuts(4, n_stages // 2), generate_pipeline_cuts(4, n_stages // 2)]
+    else:
+        cuts = generate_pipeline_cuts(4, n_stages)
+    sch = slapo.model_schedule.apply_schedule(copy.deepcopy(model), spec.schedule_key,
+                                              model_config=cfg, group=False,
+                                              attn_op_name="reference", pipeline_cuts=cuts)
+    pipe_sch = slapo.pipeline.generate_pipeline_partition(sch)
+    pipe = build_pipeline_model(pipe_sch, "native")
+    model_ = getattr(pipe, "model", pipe)
+    assert len(model_.stages) == n_stages
+    torch.testing.assert_close(model_.eval()(*inputs)["logits"], want, rtol=1e-4, atol=1e-4)
+
+
+def test_decoder_families_partition_into_equivalent_stages():
+    for name in ("gpt2-medium", "gpt-neo-125m", "opt-350m"):
+        _zoo_pipeline(name, 2)
+
+
+def test_t5_encoder_boundary_is_a_stage_boundary():
+    # one cut inside the encoder, one inside the decoder, plus the encoder end: 4 stages
+    _zoo_pipeline("t5-base", 4)
