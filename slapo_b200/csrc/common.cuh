@@ -57,11 +57,14 @@ __device__ __forceinline__ uint4 philox4x32(uint64_t seed, uint64_t offset, uint
   return c;
 }
 
-// Cheaper variant for attention-probability dropout: 7 rounds and 16-bit
-// draws, so one call serves 8 consecutive keys of one query row.  Bit k of
-// the result is set when key k is kept (draw >= p * 65536).
-__device__ __forceinline__ uint32_t philox_keep8_u16(uint64_t seed, uint64_t offset,
-                                                     uint64_t index, uint32_t thr16) {
+// Attention-probability dropout: one 7-round Philox call decides 16
+// consecutive keys of one query row.  Each of the 16 result bytes yields a
+// 7-bit draw; a key is kept when draw >= thr7, so the dropout probability is
+// quantised to thr7 / 128.  ``add4`` = (128 - thr7) * 0x01010101: adding it to
+// the draws (byte lanes cannot carry into each other: 127 + 128 = 255) leaves
+// bit 7 of byte j of word w set exactly when key 4 w + j is kept.
+__device__ __forceinline__ uint4 philox_keep16(uint64_t seed, uint64_t offset, uint64_t index,
+                                               uint32_t add4) {
   uint4 c = make_uint4(static_cast<uint32_t>(offset), static_cast<uint32_t>(offset >> 32),
                        static_cast<uint32_t>(index), static_cast<uint32_t>(index >> 32));
   uint2 k = make_uint2(static_cast<uint32_t>(seed), static_cast<uint32_t>(seed >> 32));
@@ -73,27 +76,48 @@ __device__ __forceinline__ uint32_t philox_keep8_u16(uint64_t seed, uint64_t off
     k.x += 0x9E3779B9u;
     k.y += 0xBB67AE85u;
   }
-  uint32_t bits = 0;
-  bits |= ((c.x & 0xffffu) >= thr16) << 0;
-  bits |= ((c.x >> 16) >= thr16) << 1;
-  bits |= ((c.y & 0xffffu) >= thr16) << 2;
-  bits |= ((c.y >> 16) >= thr16) << 3;
-  bits |= ((c.z & 0xffffu) >= thr16) << 4;
-  bits |= ((c.z >> 16) >= thr16) << 5;
-  bits |= ((c.w & 0xffffu) >= thr16) << 6;
-  bits |= ((c.w >> 16) >= thr16) << 7;
-  return bits;
+  c.x = (c.x & 0x7f7f7f7fu) + add4;
+  c.y = (c.y & 0x7f7f7f7fu) + add4;
+  c.z = (c.z & 0x7f7f7f7fu) + add4;
+  c.w = (c.w & 0x7f7f7f7fu) + add4;
+  return c;
+}
+__host__ __device__ __forceinline__ uint32_t dropout_thr7(float p) {
+  int t = static_cast<int>(p * 128.f + 0.5f);
+  return static_cast<uint32_t>(t < 0 ? 0 : (t > 127 ? 127 : t));
+}
+// byte permute with sign replication: selector nibble 8 + j spreads bit 7 of byte j
+// over the whole destination byte
+__device__ __forceinline__ uint32_t prmt_sign(uint32_t a, uint32_t selector) {
+  uint32_t d;
+  asm("prmt.b32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(0u), "r"(selector));
+  return d;
+}
+// keep word -> AND-mask for the 16-bit pair (2 k, 2 k + 1), k = 0 or 1
+__device__ __forceinline__ uint32_t keep_mask_pair(uint32_t keep_word, int k) {
+  return prmt_sign(keep_word, k == 0 ? 0x9988u : 0xBBAAu);
+}
+// keep word -> all-ones / zero 32-bit mask for element j (0..3)
+__device__ __forceinline__ uint32_t keep_mask_full(uint32_t keep_word, int j) {
+  return prmt_sign(keep_word, 0x8888u + 0x1111u * static_cast<uint32_t>(j));
 }
 
-// keep-mask bits for 8 consecutive elements starting at element index e0
-// (e0 a multiple of 8): element e uses word (e % 4) of philox(index = e / 4).
+// keep decisions for 8 consecutive elements starting at element index e0 (a
+// multiple of 8): element e is byte (e % 16) of philox_keep16(index = e / 16),
+// so the two threads that share a group of 16 elements evaluate the same call
+// and each uses one half of its 16 draws.  The probability is quantised to
+// thr7 / 128 like in the attention kernels; dropout_scale() is the matching
+// 1 / (1 - p).
 __device__ __forceinline__ void dropout_keep8(uint64_t seed, uint64_t offset, uint64_t e0,
                                               float p, bool keep[8]) {
-  uint4 r0 = philox4x32(seed, offset, e0 >> 2);
-  uint4 r1 = philox4x32(seed, offset, (e0 >> 2) + 1);
-  const uint32_t thr = static_cast<uint32_t>(fminf(p, 1.f) * 4294967295.0f);
-  keep[0] = r0.x >= thr; keep[1] = r0.y >= thr; keep[2] = r0.z >= thr; keep[3] = r0.w >= thr;
-  keep[4] = r1.x >= thr; keep[5] = r1.y >= thr; keep[6] = r1.z >= thr; keep[7] = r1.w >= thr;
+  const uint32_t add4 = (128u - dropout_thr7(p)) * 0x01010101u;
+  const uint4 c = philox_keep16(seed, offset, e0 >> 4, add4);
+  const uint32_t lo = (e0 & 8) ? c.z : c.x, hi = (e0 & 8) ? c.w : c.y;
+  keep[0] = lo & 0x80u; keep[1] = lo & 0x8000u; keep[2] = lo & 0x800000u; keep[3] = lo & 0x80000000u;
+  keep[4] = hi & 0x80u; keep[5] = hi & 0x8000u; keep[6] = hi & 0x800000u; keep[7] = hi & 0x80000000u;
+}
+__host__ __device__ __forceinline__ float dropout_scale(float p) {
+  return 128.f / (128.f - static_cast<float>(dropout_thr7(p)));
 }
 
 // ---------------------------------------------------------------------------
@@ -164,9 +188,27 @@ __device__ __forceinline__ float warp_max(float v) {
   return v;
 }
 
+// erf by Abramowitz & Stegun 7.1.26 (|error| < 1.5e-7): one reciprocal, one exp2 and a
+// degree-5 polynomial - about a third of the instructions of erff(), which matters because
+// bias + GeLU on bf16 data has a budget of ~20 instructions per element before it becomes
+// compute-bound on this GPU.  ``e`` returns exp(-x^2) for callers that need the Gaussian too.
+__device__ __forceinline__ float erf_as(float x, float& e) {
+  const float ax = fabsf(x);
+  const float t = __frcp_rn(fmaf(0.3275911f, ax, 1.f));
+  float poly = fmaf(1.061405429f, t, -1.453152027f);
+  poly = fmaf(poly, t, 1.421413741f);
+  poly = fmaf(poly, t, -0.284496736f);
+  poly = fmaf(poly, t, 0.254829592f);
+  e = exp2f(-1.4426950408889634f * ax * ax);
+  return copysignf(fmaf(-poly * t, e, 1.f), x);
+}
+
 // activation codes shared with the Python side: 0 = GeLU (erf), 1 = GeLU (tanh), 2 = ReLU
 __device__ __forceinline__ float act_fwd(float x, int act) {
-  if (act == 0) return 0.5f * x * (1.f + erff(x * 0.70710678118654752f));
+  if (act == 0) {
+    float e;
+    return 0.5f * x * (1.f + erf_as(x * 0.70710678118654752f, e));
+  }
   if (act == 1) {
     float u = 0.7978845608028654f * (x + 0.044715f * x * x * x);
     return 0.5f * x * (1.f + tanhf(u));
@@ -176,9 +218,9 @@ __device__ __forceinline__ float act_fwd(float x, int act) {
 
 __device__ __forceinline__ float act_grad(float x, int act) {
   if (act == 0) {
-    float cdf = 0.5f * (1.f + erff(x * 0.70710678118654752f));
-    float pdf = 0.3989422804014327f * __expf(-0.5f * x * x);
-    return cdf + x * pdf;
+    float e;  // exp(-x^2 / 2): shared by the cdf's erf and the pdf
+    const float cdf = 0.5f * (1.f + erf_as(x * 0.70710678118654752f, e));
+    return fmaf(x * 0.3989422804014327f, e, cdf);
   }
   if (act == 1) {
     float x2 = x * x;

@@ -110,7 +110,7 @@ __global__ void __launch_bounds__(256) bias_dropout_add_fwd_kernel(
     T* __restrict__ y, int64_t n_vec, int cols, float p, PhiloxArgs rng) {
   uint64_t seed, offset;
   philox_unpack(rng, seed, offset);
-  const float scale = 1.f / (1.f - p);
+  const float scale = dropout_scale(p);
   const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
   for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < n_vec;
        i += stride) {
@@ -141,7 +141,7 @@ __global__ void __launch_bounds__(256) bias_dropout_add_bwd_kernel(
     int cols, int rows_per_chunk, float p, PhiloxArgs rng) {
   uint64_t seed, offset;
   philox_unpack(rng, seed, offset);
-  const float scale = 1.f / (1.f - p);
+  const float scale = dropout_scale(p);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int col = blockIdx.x * 256 + lane * 8;
   const bool col_ok = col + 8 <= cols;

@@ -66,7 +66,8 @@ struct FlashFwdParams {
   const float* rel;    // [H, Sq + Sk - 1] additive bias by (key - query) + Sq - 1, or nullptr
   float scale_log2;    // softmax scale * log2(e)
   int causal;
-  float p_drop;
+  float p_drop;        // effective probability thr7 / 128
+  uint32_t thr7;
   PhiloxArgs rng;
   int out_bf16;
   uint32_t idesc_qk, idesc_pv;
@@ -100,7 +101,10 @@ __device__ __forceinline__ void score_chunk(const uint32_t (&raw)[32], float (&v
   }
 }
 
-template <int D>
+// kPlain: no key bias, no relative bias, not causal, Sk a multiple of 128 and a positive
+// scale - the row maximum is then taken on the raw scores and every probability is one
+// fused multiply-add plus one exp2.
+template <int D, bool kPlain>
 __global__ void __launch_bounds__(192, D == 64 ? 2 : 1)
 flash_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                  const __grid_constant__ CUtensorMap tm_v, const FlashFwdParams p) {
@@ -241,10 +245,10 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
     const int sm_tid = (warp - 2) * 32 + lane;
     uint64_t seed = 0, offset = 0;
     if (p.p_drop > 0.f) philox_unpack(p.rng, seed, offset);
-    const uint32_t thr16 = static_cast<uint32_t>(p.p_drop * 65536.f);
-    const int sk8 = (p.Sk + 7) >> 3;
+    const uint32_t add4 = (128u - p.thr7) * 0x01010101u;
+    const int sk16 = (p.Sk + 15) >> 4;
     const uint64_t drop_row_base =
-        (static_cast<uint64_t>(batch * p.H + head) * p.Sq + min(row, p.Sq - 1)) * sk8;
+        (static_cast<uint64_t>(batch * p.H + head) * p.Sq + min(row, p.Sq - 1)) * sk16;
     const float* rel_row = nullptr;
     if (p.rel != nullptr)
       rel_row = p.rel + static_cast<int64_t>(head) * (p.Sq + p.Sk - 1) + (p.Sq - 1) - min(row, p.Sq - 1);
@@ -287,17 +291,24 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
       if (p.causal) key_limit = min(key_limit, row + diag + 1);
       const float* kb = p.kbias != nullptr ? kb_tile : nullptr;
       // pass 1: row maximum
-      float m_tile = -INFINITY;
+      float mm[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};  // 4 chains for ILP
 #pragma unroll 1
       for (int c = 0; c < kBlockN / 32; ++c) {
         uint32_t raw[32];
-        float v[32];
         tc::tmem_ld_x32(tmem_s + c * 32 + lane_sel, raw);
         tc::tmem_ld_wait();
-        score_chunk<true>(raw, v, row, k0 + c * 32, p, kb, rel_row, key_limit, c * 32);
+        if constexpr (kPlain) {
 #pragma unroll
-        for (int t = 0; t < 32; ++t) m_tile = fmaxf(m_tile, v[t]);
+          for (int t = 0; t < 32; ++t) mm[t & 3] = fmaxf(mm[t & 3], __uint_as_float(raw[t]));
+        } else {
+          float v[32];
+          score_chunk<true>(raw, v, row, k0 + c * 32, p, kb, rel_row, key_limit, c * 32);
+#pragma unroll
+          for (int t = 0; t < 32; ++t) mm[t & 3] = fmaxf(mm[t & 3], v[t]);
+        }
       }
+      float m_tile = fmaxf(fmaxf(mm[0], mm[1]), fmaxf(mm[2], mm[3]));
+      if constexpr (kPlain) m_tile *= p.scale_log2;
       const float m_new = fmaxf(m_run, m_tile);
       const float m_use = m_new == -INFINITY ? 0.f : m_new;
       const float alpha = m_run == -INFINITY ? 0.f : exp2f(m_run - m_use);
@@ -308,7 +319,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
         break;
       }
       // pass 2: probabilities, row sum, dropout, P -> shared memory
-      float l_tile = 0.f;
+      float ll[4] = {0.f, 0.f, 0.f, 0.f};
       uint8_t* p_row = s_p + row_in_tile * 128;
 #pragma unroll 1
       for (int c = 0; c < kBlockN / 32; ++c) {
@@ -316,39 +327,51 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
         float v[32];
         tc::tmem_ld_x32(tmem_s + c * 32 + lane_sel, raw);
         tc::tmem_ld_wait();
-        score_chunk<false>(raw, v, row, k0 + c * 32, p, kb, rel_row, key_limit, c * 32);
+        if constexpr (kPlain) {
 #pragma unroll
-        for (int t = 0; t < 32; ++t) {
-          v[t] = exp2f(v[t] - m_use);
-          l_tile += v[t];
+          for (int t = 0; t < 32; ++t) {
+            v[t] = exp2f(fmaf(__uint_as_float(raw[t]), p.scale_log2, -m_use));
+            ll[t & 3] += v[t];
+          }
+        } else {
+          score_chunk<false>(raw, v, row, k0 + c * 32, p, kb, rel_row, key_limit, c * 32);
+#pragma unroll
+          for (int t = 0; t < 32; ++t) {
+            v[t] = exp2f(v[t] - m_use);
+            ll[t & 3] += v[t];
+          }
         }
+        uint32_t pk[16];
+#pragma unroll
+        for (int i = 0; i < 16; ++i) pk[i] = pack_pair(v[2 * i], v[2 * i + 1], p.out_bf16);
         if (p.p_drop > 0.f) {
+          // dropped probabilities are cleared in the packed 16-bit pairs
 #pragma unroll
-          for (int g = 0; g < 4; ++g) {
-            const uint32_t bits = philox_keep8_u16(
-                seed, offset, drop_row_base + ((k0 + c * 32 + g * 8) >> 3), thr16);
+          for (int h = 0; h < 2; ++h) {
+            const uint4 kw = philox_keep16(seed, offset,
+                                           drop_row_base + ((k0 + c * 32 + h * 16) >> 4), add4);
+            const uint32_t w[4] = {kw.x, kw.y, kw.z, kw.w};
 #pragma unroll
-            for (int t = 0; t < 8; ++t)
-              if (!((bits >> t) & 1u)) v[g * 8 + t] = 0.f;
+            for (int i = 0; i < 4; ++i) {
+              pk[h * 8 + i * 2 + 0] &= keep_mask_pair(w[i], 0);
+              pk[h * 8 + i * 2 + 1] &= keep_mask_pair(w[i], 1);
+            }
           }
         }
         // keys [c*32, c*32+32) of this row: block (c >> 1), 16-byte chunks (c & 1) * 4 + g
 #pragma unroll
         for (int g = 0; g < 4; ++g) {
           const int chunk = (c & 1) * 4 + g;
-          uint4 pk = make_uint4(pack_pair(v[g * 8 + 0], v[g * 8 + 1], p.out_bf16),
-                                pack_pair(v[g * 8 + 2], v[g * 8 + 3], p.out_bf16),
-                                pack_pair(v[g * 8 + 4], v[g * 8 + 5], p.out_bf16),
-                                pack_pair(v[g * 8 + 6], v[g * 8 + 7], p.out_bf16));
           *reinterpret_cast<uint4*>(p_row + (c >> 1) * kBlkBytes +
-                                    ((chunk ^ (row_in_tile & 7)) << 4)) = pk;
+                                    ((chunk ^ (row_in_tile & 7)) << 4)) =
+              make_uint4(pk[g * 4], pk[g * 4 + 1], pk[g * 4 + 2], pk[g * 4 + 3]);
         }
       }
       tc::fence_before_sync();   // S reads are complete
       tc::fence_proxy_async();   // P stores visible to the tensor core
       __syncwarp();
       if (lane == 0) tc::mbar_arrive(p_full);
-      l_run = l_run * alpha + l_tile;
+      l_run = l_run * alpha + ((ll[0] + ll[1]) + (ll[2] + ll[3]));
       if (j > 0) ok = fold(j - 1);
       alpha_fold = alpha;
       m_run = m_new;
@@ -386,16 +409,17 @@ __global__ void flash_dropout_mask_kernel(uint8_t* mask, int B, int H, int Sq, i
                                           PhiloxArgs rng) {
   uint64_t seed, offset;
   philox_unpack(rng, seed, offset);
-  const uint32_t thr16 = static_cast<uint32_t>(p_drop * 65536.f);
-  const int sk8 = (Sk + 7) >> 3;
-  const int64_t total = static_cast<int64_t>(B) * H * Sq * sk8;
+  const uint32_t add4 = (128u - dropout_thr7(p_drop)) * 0x01010101u;
+  const int sk16 = (Sk + 15) >> 4;
+  const int64_t total = static_cast<int64_t>(B) * H * Sq * sk16;
   for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < total;
        i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
-    const uint32_t bits = philox_keep8_u16(seed, offset, static_cast<uint64_t>(i), thr16);
-    const int64_t rowi = i / sk8;
-    const int k8 = static_cast<int>(i % sk8) * 8;
-    for (int t = 0; t < 8; ++t)
-      if (k8 + t < Sk) mask[rowi * Sk + k8 + t] = (bits >> t) & 1u;
+    const uint4 kw = philox_keep16(seed, offset, static_cast<uint64_t>(i), add4);
+    const uint32_t w[4] = {kw.x, kw.y, kw.z, kw.w};
+    const int64_t rowi = i / sk16;
+    const int k16 = static_cast<int>(i % sk16) * 16;
+    for (int t = 0; t < 16; ++t)
+      if (k16 + t < Sk) mask[rowi * Sk + k16 + t] = (w[t >> 2] >> (8 * (t & 3) + 7)) & 1u;
   }
 }
 
@@ -405,11 +429,11 @@ void launch_flash_dropout_mask(uint8_t* mask, int B, int H, int Sq, int Sk, floa
   flash_dropout_mask_kernel<<<sm_count() * 4, 256, 0, stream>>>(mask, B, H, Sq, Sk, p_drop, rng);
 }
 
-template <int D>
+template <int D, bool kPlain>
 static int launch_fwd_d(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv,
                         const FlashFwdParams& p, cudaStream_t stream) {
   constexpr int kSmem = 4 * 128 * D * 2 + 2 * 128 * 128 + 16 * 8 + 128 * 4 + 1024;
-  auto kernel = flash_fwd_kernel<D>;
+  auto kernel = flash_fwd_kernel<D, kPlain>;
   static bool configured = false;
   if (!configured) {
     if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem) !=
@@ -436,11 +460,19 @@ int launch_flash_fwd(const void* q, const void* k, const void* v, void* o, float
     return 2;
   FlashFwdParams p;
   p.B = B; p.H = H; p.Sq = Sq; p.Sk = Sk; p.O = o; p.lse = lse; p.kbias = kbias; p.rel = rel;
-  p.scale_log2 = scale * kLog2e; p.causal = causal; p.p_drop = p_drop; p.rng = rng;
+  p.scale_log2 = scale * kLog2e; p.causal = causal; p.rng = rng;
+  // the dropout probability is quantised to a multiple of 1/128 (see philox_keep16)
+  p.thr7 = dropout_thr7(p_drop);
+  p.p_drop = p.thr7 / 128.f;
   p.out_bf16 = bf16 ? 1 : 0; p.status = status;
   p.idesc_qk = tc::instr_desc_f16(128, 128, bf16 ? 1 : 0, false, false);
   p.idesc_pv = tc::instr_desc_f16(128, D, bf16 ? 1 : 0, false, true);
-  return D == 64 ? launch_fwd_d<64>(tq, tk, tv, p, stream) : launch_fwd_d<128>(tq, tk, tv, p, stream);
+  const bool plain = kbias == nullptr && rel == nullptr && !causal && Sk % kBlockN == 0 && scale > 0.f;
+  if (D == 64)
+    return plain ? launch_fwd_d<64, true>(tq, tk, tv, p, stream)
+                 : launch_fwd_d<64, false>(tq, tk, tv, p, stream);
+  return plain ? launch_fwd_d<128, true>(tq, tk, tv, p, stream)
+               : launch_fwd_d<128, false>(tq, tk, tv, p, stream);
 }
 
 }  // namespace slapo

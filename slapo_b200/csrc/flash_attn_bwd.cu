@@ -33,7 +33,8 @@ struct FlashBwdParams {
   float* drel;          // same shape fp32 accumulator or nullptr
   float scale, scale_log2;
   int causal;
-  float p_drop;
+  float p_drop;         // effective probability thr7 / 128
+  uint32_t thr7;
   PhiloxArgs rng;
   int bf16;
   uint32_t idesc_s, idesc_dvk, idesc_dq;
@@ -82,8 +83,12 @@ __global__ void flash_bwd_delta_kernel(const T* __restrict__ dout, const T* __re
   }
 }
 
-template <int D>
-__global__ void __launch_bounds__(192, 1)
+// 10 warps: TMA, MMA and 8 softmax warps.  Softmax warps w and w + 4 share a quarter of the
+// TMEM lanes (query rows) and split the 128 key columns (and later the D output columns)
+// in halves, so every scheduler of the SM has two of them to interleave.
+// kPlain: no key bias / relative bias, not causal, Sq and Sk multiples of 128.
+template <int D, bool kPlain>
+__global__ void __launch_bounds__(320, 1)
 flash_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                  const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_do,
                  const FlashBwdParams p) {
@@ -134,9 +139,9 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
       tc::mbar_init(&qdo_empty[s], 1);
     }
     tc::mbar_init(sdp_full, 1);
-    tc::mbar_init(pds_full, 4);
+    tc::mbar_init(pds_full, 8);
     tc::mbar_init(dq_full, 1);
-    tc::mbar_init(dq_empty, 4);
+    tc::mbar_init(dq_empty, 8);
     tc::mbar_init(acc_full, 1);
     *abort_flag = 0;
     tc::fence_barrier_init();
@@ -145,7 +150,7 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
     tc::tmem_alloc(tmem_slot, kTmemCols);
     tc::tmem_relinquish();
   }
-  if (warp >= 2) {
+  if (warp >= 2 && warp < 6) {
     const int t = (warp - 2) * 32 + lane;
     const int key = n0 + t;
     kb_tile[t] = (p.kbias != nullptr && key < p.Sk)
@@ -245,21 +250,26 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
     }
   } else {
     const int quarter = warp & 3;
+    const int half = (warp - 2) >> 2;   // which 64 of the 128 key columns / which output half
     const int r_in = quarter * 32 + lane;
     const uint32_t lane_sel = static_cast<uint32_t>(quarter * 32) << 16;
     uint64_t seed = 0, offset = 0;
     if (p.p_drop > 0.f) philox_unpack(p.rng, seed, offset);
-    const uint32_t thr16 = static_cast<uint32_t>(p.p_drop * 65536.f);
-    const float inv_keep = 1.f / (1.f - p.p_drop);
-    const int sk8 = (p.Sk + 7) >> 3;
+    const uint32_t add4 = (128u - p.thr7) * 0x01010101u;
+    const float keep_prob = 1.f - p.p_drop;
+    const float inv_keep = 1.f / keep_prob;
+    // dS is formed without the factors scale and 1 / keep_prob; they are applied once to
+    // dQ and dK (and 1 / keep_prob to dV) when those leave TMEM
+    const float out_scale = p.scale * inv_keep;
+    const int sk16 = (p.Sk + 15) >> 4;
     bool ok = true;
     for (int it = 0; it < n_iter && ok; ++it) {
       const int row = (i_begin + it) * 128 + r_in;
       const bool row_ok = row < p.Sq;
       const int64_t stat_idx = (static_cast<int64_t>(batch) * p.H + head) * p.Sq + min(row, p.Sq - 1);
       const float lse2 = row_ok ? p.lse[stat_idx] * kLog2eB : -INFINITY;
-      const float delta = row_ok ? p.delta[stat_idx] : 0.f;
-      const uint64_t drop_row_base = static_cast<uint64_t>(stat_idx) * sk8;
+      const float delta = row_ok ? p.delta[stat_idx] * keep_prob : 0.f;
+      const uint64_t drop_row_base = static_cast<uint64_t>(stat_idx) * sk16;
       const float* rel_row = nullptr;
       float* drel_row = nullptr;
       if (p.rel != nullptr) {
@@ -275,44 +285,53 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
       uint8_t* p_row = s_p + r_in * 128;
       uint8_t* ds_row = s_ds + r_in * 128;
 #pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
+      for (int c = 2 * half; c < 2 * half + 2; ++c) {
         uint32_t s_raw[32], dp_raw[32];
         tc::tmem_ld_x32(tmem_base + kColS + c * 32 + lane_sel, s_raw);
         tc::tmem_ld_x32(tmem_base + kColDP + c * 32 + lane_sel, dp_raw);
         tc::tmem_ld_wait();
         float pv[32], dsv[32];
+        if constexpr (kPlain) {
 #pragma unroll
-        for (int t = 0; t < 32; ++t) {
-          const int key = n0 + c * 32 + t;
-          float s2 = __uint_as_float(s_raw[t]) * p.scale_log2 + kb_tile[c * 32 + t];
-          if (rel_row != nullptr) s2 += rel_row[key] * kLog2eB;
-          const float pr = key < key_limit ? exp2f(s2 - lse2) : 0.f;
-          pv[t] = pr;
-          dsv[t] = __uint_as_float(dp_raw[t]);
+          for (int t = 0; t < 32; ++t)
+            pv[t] = exp2f(fmaf(__uint_as_float(s_raw[t]), p.scale_log2, -lse2));
+        } else {
+#pragma unroll
+          for (int t = 0; t < 32; ++t) {
+            const int key = n0 + c * 32 + t;
+            float s2 = __uint_as_float(s_raw[t]) * p.scale_log2 + kb_tile[c * 32 + t];
+            if (rel_row != nullptr) s2 += rel_row[key] * kLog2eB;
+            pv[t] = key < key_limit ? exp2f(s2 - lse2) : 0.f;
+          }
         }
         if (p.p_drop > 0.f) {
 #pragma unroll
-          for (int g = 0; g < 4; ++g) {
-            const uint32_t bits = philox_keep8_u16(
-                seed, offset, drop_row_base + ((n0 + c * 32 + g * 8) >> 3), thr16);
+          for (int h = 0; h < 2; ++h) {
+            const uint4 kw = philox_keep16(seed, offset,
+                                           drop_row_base + ((n0 + c * 32 + h * 16) >> 4), add4);
+            const uint32_t w[4] = {kw.x, kw.y, kw.z, kw.w};
 #pragma unroll
-            for (int t = 0; t < 8; ++t) {
-              const bool keep = (bits >> t) & 1u;
-              const float pr = pv[g * 8 + t];
-              // grad wrt the un-dropped probability, then softmax backward
-              dsv[g * 8 + t] = pr * ((keep ? dsv[g * 8 + t] * inv_keep : 0.f) - delta);
-              pv[g * 8 + t] = keep ? pr * inv_keep : 0.f;
+            for (int i = 0; i < 4; ++i) {
+#pragma unroll
+              for (int j = 0; j < 4; ++j) {
+                const int e = h * 16 + i * 4 + j;
+                const float pr = pv[e];
+                // kept probability (zero where dropped); dS / keep_prob = P (mask dP - delta')
+                const float pm = __uint_as_float(__float_as_uint(pr) & keep_mask_full(w[i], j));
+                dsv[e] = fmaf(pm, __uint_as_float(dp_raw[e]), -pr * delta);
+                pv[e] = pm;
+              }
             }
           }
         } else {
 #pragma unroll
-          for (int t = 0; t < 32; ++t) dsv[t] = pv[t] * (dsv[t] - delta);
+          for (int t = 0; t < 32; ++t) dsv[t] = pv[t] * (__uint_as_float(dp_raw[t]) - delta);
         }
         if (drel_row != nullptr) {
 #pragma unroll
           for (int t = 0; t < 32; ++t) {
             const int key = n0 + c * 32 + t;
-            if (key < key_limit && dsv[t] != 0.f) atomicAdd(drel_row + key, dsv[t]);
+            if (key < key_limit && dsv[t] != 0.f) atomicAdd(drel_row + key, dsv[t] * inv_keep);
           }
         }
 #pragma unroll
@@ -324,11 +343,10 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
                                 pack_pair_b(pv[g * 8 + 4], pv[g * 8 + 5], p.bf16),
                                 pack_pair_b(pv[g * 8 + 6], pv[g * 8 + 7], p.bf16));
           *reinterpret_cast<uint4*>(p_row + off) = pk;
-          uint4 dk = make_uint4(
-              pack_pair_b(dsv[g * 8 + 0] * p.scale, dsv[g * 8 + 1] * p.scale, p.bf16),
-              pack_pair_b(dsv[g * 8 + 2] * p.scale, dsv[g * 8 + 3] * p.scale, p.bf16),
-              pack_pair_b(dsv[g * 8 + 4] * p.scale, dsv[g * 8 + 5] * p.scale, p.bf16),
-              pack_pair_b(dsv[g * 8 + 6] * p.scale, dsv[g * 8 + 7] * p.scale, p.bf16));
+          uint4 dk = make_uint4(pack_pair_b(dsv[g * 8 + 0], dsv[g * 8 + 1], p.bf16),
+                                pack_pair_b(dsv[g * 8 + 2], dsv[g * 8 + 3], p.bf16),
+                                pack_pair_b(dsv[g * 8 + 4], dsv[g * 8 + 5], p.bf16),
+                                pack_pair_b(dsv[g * 8 + 6], dsv[g * 8 + 7], p.bf16));
           *reinterpret_cast<uint4*>(ds_row + off) = dk;
         }
       }
@@ -342,15 +360,18 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
       float* dq_dst = p.dq_accum +
                       ((static_cast<int64_t>(batch) * p.Sq + min(row, p.Sq - 1)) * p.H + head) * D;
 #pragma unroll
-      for (int c = 0; c < D / 32; ++c) {
+      for (int cc = 0; cc < D / 64; ++cc) {
+        const int c = half * (D / 64) + cc;   // this warp's share of the D columns
         uint32_t r[32];
         tc::tmem_ld_x32(tmem_base + kColDQ + c * 32 + lane_sel, r);
         tc::tmem_ld_wait();
         if (row_ok) {
 #pragma unroll
           for (int g = 0; g < 8; ++g)
-            red_add_v4(dq_dst + c * 32 + g * 4, __uint_as_float(r[g * 4]), __uint_as_float(r[g * 4 + 1]),
-                       __uint_as_float(r[g * 4 + 2]), __uint_as_float(r[g * 4 + 3]));
+            red_add_v4(dq_dst + c * 32 + g * 4, __uint_as_float(r[g * 4]) * out_scale,
+                       __uint_as_float(r[g * 4 + 1]) * out_scale,
+                       __uint_as_float(r[g * 4 + 2]) * out_scale,
+                       __uint_as_float(r[g * 4 + 3]) * out_scale);
         }
       }
       tc::fence_before_sync();
@@ -369,10 +390,12 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
                         ((static_cast<int64_t>(batch) * p.Sk + key_c) * p.H + head) * p.dkv_row_stride * 2;
       uint8_t* dv_dst = static_cast<uint8_t*>(p.dV) +
                         ((static_cast<int64_t>(batch) * p.Sk + key_c) * p.H + head) * p.dkv_row_stride * 2;
-#pragma unroll
-      for (int which = 0; which < 2; ++which) {
+      {
+        // the first four softmax warps write dV, the other four dK
+        const int which = half;
         uint8_t* dst = which == 0 ? dv_dst : dk_dst;
         const uint32_t col = which == 0 ? kColDV : kColDK;
+        const float f = which == 0 ? inv_keep : out_scale;
 #pragma unroll
         for (int c = 0; c < D / 32; ++c) {
           uint32_t r[32];
@@ -387,10 +410,10 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
 #pragma unroll
             for (int g = 0; g < 4; ++g) {
               uint4 pk = make_uint4(
-                  pack_pair_b(__uint_as_float(r[g * 8 + 0]), __uint_as_float(r[g * 8 + 1]), p.bf16),
-                  pack_pair_b(__uint_as_float(r[g * 8 + 2]), __uint_as_float(r[g * 8 + 3]), p.bf16),
-                  pack_pair_b(__uint_as_float(r[g * 8 + 4]), __uint_as_float(r[g * 8 + 5]), p.bf16),
-                  pack_pair_b(__uint_as_float(r[g * 8 + 6]), __uint_as_float(r[g * 8 + 7]), p.bf16));
+                  pack_pair_b(__uint_as_float(r[g * 8 + 0]) * f, __uint_as_float(r[g * 8 + 1]) * f, p.bf16),
+                  pack_pair_b(__uint_as_float(r[g * 8 + 2]) * f, __uint_as_float(r[g * 8 + 3]) * f, p.bf16),
+                  pack_pair_b(__uint_as_float(r[g * 8 + 4]) * f, __uint_as_float(r[g * 8 + 5]) * f, p.bf16),
+                  pack_pair_b(__uint_as_float(r[g * 8 + 6]) * f, __uint_as_float(r[g * 8 + 7]) * f, p.bf16));
               *reinterpret_cast<uint4*>(dst + (c * 32 + g * 8) * 2) = pk;
             }
           }
@@ -408,12 +431,12 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
   }
 }
 
-template <int D>
+template <int D, bool kPlain>
 static int launch_bwd_d(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv,
                         const CUtensorMap& tdo, const FlashBwdParams& p, cudaStream_t stream) {
   constexpr int kStages = D == 64 ? 2 : 1;
   constexpr int kSmem = (2 + 2 * kStages) * 128 * D * 2 + 4 * 128 * 128 + 12 * 8 + 128 * 4 + 1024;
-  auto kernel = flash_bwd_kernel<D>;
+  auto kernel = flash_bwd_kernel<D, kPlain>;
   static bool configured = false;
   if (!configured) {
     if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem) !=
@@ -423,7 +446,7 @@ static int launch_bwd_d(const CUtensorMap& tq, const CUtensorMap& tk, const CUte
   }
   dim3 grid((p.Sk + 127) / 128, p.H, p.B);
   count_launch();
-  kernel<<<grid, 192, kSmem, stream>>>(tq, tk, tv, tdo, p);
+  kernel<<<grid, 320, kSmem, stream>>>(tq, tk, tv, tdo, p);
   return cudaGetLastError() == cudaSuccess ? 0 : 4;
 }
 
@@ -458,14 +481,20 @@ int launch_flash_bwd(const void* q, const void* k, const void* v, const void* o,
   FlashBwdParams p;
   p.B = B; p.H = H; p.Sq = Sq; p.Sk = Sk; p.lse = lse; p.delta = delta; p.dq_accum = dq_accum;
   p.dK = dk; p.dV = dv; p.dkv_row_stride = dkv_row_stride; p.kbias = kbias; p.rel = rel; p.drel = drel; p.scale = scale;
-  p.scale_log2 = scale * kLog2eB; p.causal = causal; p.p_drop = p_drop; p.rng = rng;
+  p.scale_log2 = scale * kLog2eB; p.causal = causal; p.rng = rng;
+  p.thr7 = dropout_thr7(p_drop);   // same quantisation as the forward kernel
+  p.p_drop = p.thr7 / 128.f;
   p.bf16 = bf16 ? 1 : 0; p.status = status;
   const int f = bf16 ? 1 : 0;
   p.idesc_s = tc::instr_desc_f16(128, 128, f, false, false);   // S, dP
   p.idesc_dvk = tc::instr_desc_f16(128, D, f, true, true);     // dV, dK
   p.idesc_dq = tc::instr_desc_f16(128, D, f, false, true);     // dQ
-  return D == 64 ? launch_bwd_d<64>(tq, tk, tv, tdo, p, stream)
-                 : launch_bwd_d<128>(tq, tk, tv, tdo, p, stream);
+  const bool plain = kbias == nullptr && rel == nullptr && !causal && Sk % 128 == 0 && Sq % 128 == 0;
+  if (D == 64)
+    return plain ? launch_bwd_d<64, true>(tq, tk, tv, tdo, p, stream)
+                 : launch_bwd_d<64, false>(tq, tk, tv, tdo, p, stream);
+  return plain ? launch_bwd_d<128, true>(tq, tk, tv, tdo, p, stream)
+               : launch_bwd_d<128, false>(tq, tk, tv, tdo, p, stream);
 }
 
 }  // namespace slapo

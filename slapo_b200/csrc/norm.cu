@@ -49,7 +49,7 @@ __global__ void __launch_bounds__(32 * WPR * RG, (VPL == 1 && WPR * RG == 16) ? 
   const int group = warp / WPR, wir = warp % WPR;
   uint64_t seed = 0, offset = 0;
   if (p > 0.f) philox_unpack(rng, seed, offset);
-  const float scale = 1.f / (1.f - p);
+  const float scale = dropout_scale(p);
   const float inv_cols = 1.f / static_cast<float>(cols);
 
   float gw[VPL][8], gb[VPL][8];
@@ -150,7 +150,7 @@ __global__ void __launch_bounds__(32 * WPR * RG, (VPL == 1 && WPR * RG == 16) ? 
   const int group = warp / WPR, wir = warp % WPR;
   uint64_t seed = 0, offset = 0;
   if (p > 0.f) philox_unpack(rng, seed, offset);
-  const float scale = 1.f / (1.f - p);
+  const float scale = dropout_scale(p);
   const float inv_cols = 1.f / static_cast<float>(cols);
 
   float gw[VPL][8], dgam[VPL][8], dbet[VPL][8], dbia[VPL][8];

@@ -112,6 +112,13 @@ def packed_supported(qkv) -> bool:
             and qkv.shape[-1] in _HEAD_DIMS and native.available())
 
 
+def effective_dropout_p(p: float) -> float:
+    """See :func:`slapo_b200.ops.functional.effective_dropout_p`."""
+    from .functional import effective_dropout_p as impl
+
+    return impl(p)
+
+
 def dropout_keep_mask(b, h, sq, sk, p):
     """The keep mask the next flash-attention call with dropout ``p`` would
     draw, WITHOUT advancing the generator (testing aid)."""

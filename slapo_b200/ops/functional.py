@@ -86,6 +86,14 @@ def bias_gelu(x, bias, approximate: str = "none"):
 
 # ---------------------------------------------------------------------- #
 # dropout family
+def effective_dropout_p(p: float) -> float:
+    """Dropout probability the CUDA kernels actually apply.  They draw 7-bit
+    random numbers (16 decisions per Philox call), so ``p`` is rounded to a
+    multiple of 1/128 (0.1 -> 13/128 = 0.1016); kept values are rescaled by
+    ``1 / (1 - effective p)``, which keeps the expectation exact."""
+    return min(max(int(p * 128.0 + 0.5), 0), 127) / 128.0
+
+
 def _philox_reserve(numel):
     """Reserve Philox offsets on the current CUDA generator (so masks follow
     torch's RNG state: manual_seed, fork_rng, checkpoint replay).  Returns the

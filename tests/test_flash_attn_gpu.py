@@ -5,7 +5,7 @@ import torch
 
 from slapo_b200.ops import functional as NF
 from slapo_b200.ops import native
-from slapo_b200.ops.flash_attn import dropout_keep_mask
+from slapo_b200.ops.flash_attn import dropout_keep_mask, effective_dropout_p
 
 pytestmark = pytest.mark.gpu
 
@@ -82,6 +82,29 @@ def test_flash_attention_t5_relative_bias(bidirectional):
     assert err < 3e-2, f"relative-position table grad: {err}"
 
 
+@pytest.mark.parametrize("shape,causal", [((2, 200, 3, 64), False), ((2, 384, 2, 64), True),
+                                          ((1, 256, 2, 128), False), ((1, 300, 2, 128), True)])
+def test_flash_attention_dropout_masked_paths(shape, causal):
+    """Dropout on the general path (causal, ragged sequence lengths, head dim 128)."""
+    b, s, h, d = shape
+    p = 0.2
+    q, k, v = _mk(b, s, h, d, torch.bfloat16)
+    torch.cuda.manual_seed(7)
+    mask = dropout_keep_mask(b, h, s, s, p)
+    _compare(q, k, v,
+             lambda q, k, v: NF.flash_attention(q, k, v, causal=causal, dropout_p=p, training=True),
+             lambda q, k, v: NF.attention_reference(q, k, v, causal=causal,
+                                                    dropout_p=effective_dropout_p(p),
+                                                    dropout_mask=mask.float()))
+
+
+def test_effective_dropout_probability():
+    assert effective_dropout_p(0.0) == 0.0 and effective_dropout_p(0.5) == 0.5
+    assert abs(effective_dropout_p(0.1) - 13 / 128) < 1e-9
+    mask = dropout_keep_mask(2, 4, 512, 512, 0.1)
+    assert abs(mask.float().mean().item() - (1 - 13 / 128)) < 2e-3
+
+
 @pytest.mark.parametrize("p", [0.1, 0.3])
 def test_flash_attention_dropout_replay(p):
     b, s, h, d = 2, 256, 2, 64
@@ -92,4 +115,5 @@ def test_flash_attention_dropout_replay(p):
     assert abs(keep - (1 - p)) < 0.01, keep
     _compare(q, k, v,
              lambda q, k, v: NF.flash_attention(q, k, v, dropout_p=p, training=True),
-             lambda q, k, v: NF.attention_reference(q, k, v, dropout_p=p, dropout_mask=mask.float()))
+             lambda q, k, v: NF.attention_reference(q, k, v, dropout_p=effective_dropout_p(p),
+                                                    dropout_mask=mask.float()))

@@ -103,7 +103,7 @@ def test_bias_dropout_add(dtype, p):
     g = torch.randn_like(y)
     y.backward(g)
     xr, br, rr = (t.detach().float().requires_grad_(True) for t in (x, b, r))
-    yr = (xr + br) * mask / (1 - p) + rr
+    yr = (xr + br) * mask / (1 - NF.effective_dropout_p(p)) + rr
     yr.backward(g.float())
     rtol, atol = _tol(dtype)
     torch.testing.assert_close(y.float(), yr, rtol=rtol, atol=atol)
@@ -129,7 +129,7 @@ def test_dropout_add_layer_norm(dtype, p, cols):
     gy, gz = torch.randn_like(y), torch.randn_like(z)
     torch.autograd.backward([y, z], [gy, gz])
     xr, br, rr, wr, lbr = (t.detach().float().requires_grad_(True) for t in (x, b, r, w, lb))
-    zr = (xr + br) * mask / (1 - p) + rr
+    zr = (xr + br) * mask / (1 - NF.effective_dropout_p(p)) + rr
     yr = F.layer_norm(zr, (cols,), wr, lbr, 1e-5)
     torch.autograd.backward([yr, zr], [gy.float(), gz.float()])
     rtol, atol = _tol(dtype)
