@@ -17,24 +17,57 @@ void count_launch(int n) { g_launches.fetch_add(n, std::memory_order_relaxed); }
 int64_t launch_count() { return g_launches.load(std::memory_order_relaxed); }
 
 // ------------------------------------------------------------------------ //
+// Four independent 16-byte loads per thread are issued before any of them is used: with
+// 2048 resident threads per SM a single load each leaves too few bytes in flight to cover the
+// HBM latency at full bandwidth.
 template <typename T>
 __global__ void __launch_bounds__(256) bias_act_fwd_kernel(
     const T* __restrict__ x, const T* __restrict__ bias, T* __restrict__ y, int64_t n_vec,
     int cols, int act) {
+  constexpr int kUnroll = 4;
   const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
-  for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < n_vec;
-       i += stride) {
-    const int64_t e = i * kVec;
-    float v[8], b[8];
-    Vec8<T>::load(x + e, v);
+  const int vpr = cols / kVec;  // vectors per row
+  int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  // column (in vectors) of the first vector and its advance per step, kept in 32 bits
+  int cv = static_cast<int>(i % vpr);
+  const int step = static_cast<int>(stride % vpr);
+  for (; i + (kUnroll - 1) * stride < n_vec; i += kUnroll * stride) {
+    float v[kUnroll][8];
+    int cvs[kUnroll];
+#pragma unroll
+    for (int u = 0; u < kUnroll; ++u) {
+      Vec8<T>::load(x + (i + u * stride) * kVec, v[u]);
+      cvs[u] = cv;
+      cv += step;
+      if (cv >= vpr) cv -= vpr;
+    }
+#pragma unroll
+    for (int u = 0; u < kUnroll; ++u) {
+      if (bias != nullptr) {
+        float b[8];
+        Vec8<T>::load(bias + cvs[u] * kVec, b);
+#pragma unroll
+        for (int k = 0; k < 8; ++k) v[u][k] += b[k];
+      }
+#pragma unroll
+      for (int k = 0; k < 8; ++k) v[u][k] = act_fwd(v[u][k], act);
+      Vec8<T>::store(y + (i + u * stride) * kVec, v[u]);
+    }
+  }
+  for (; i < n_vec; i += stride) {
+    float v[8];
+    Vec8<T>::load(x + i * kVec, v);
     if (bias != nullptr) {
-      Vec8<T>::load(bias + (e % cols), b);
+      float b[8];
+      Vec8<T>::load(bias + cv * kVec, b);
 #pragma unroll
       for (int k = 0; k < 8; ++k) v[k] += b[k];
     }
+    cv += step;
+    if (cv >= vpr) cv -= vpr;
 #pragma unroll
     for (int k = 0; k < 8; ++k) v[k] = act_fwd(v[k], act);
-    Vec8<T>::store(y + e, v);
+    Vec8<T>::store(y + i * kVec, v);
   }
 }
 
@@ -76,6 +109,7 @@ __global__ void __launch_bounds__(256) bias_act_bwd_kernel(
     if (bias != nullptr) Vec8<T>::load(bias + col, b);
     const int r0 = blockIdx.y * rows_per_chunk;
     const int r1 = min(rows, r0 + rows_per_chunk);
+#pragma unroll 4
     for (int r = r0 + warp; r < r1; r += 8) {
       const int64_t e = static_cast<int64_t>(r) * cols + col;
       float g[8], v[8];

@@ -168,6 +168,7 @@ __global__ void __launch_bounds__(32 * WPR * RG, (VPL == 1 && WPR * RG == 16) ? 
     const float mean = row_ok ? mean_in[row] : 0.f;
     const float rstd = row_ok ? rstd_in[row] : 0.f;
     float g[VPL][8], xh[VPL][8];
+    uint4 gz_raw[VPL][sizeof(T) == 2 ? 1 : 2];  // fetched with the other operands, used after the reductions
     float s1 = 0.f, s2 = 0.f;
 #pragma unroll
     for (int i = 0; i < VPL; ++i) {
@@ -176,6 +177,11 @@ __global__ void __launch_bounds__(32 * WPR * RG, (VPL == 1 && WPR * RG == 16) ? 
         const int64_t e = static_cast<int64_t>(row) * cols + col;
         Vec8<T>::load(gy + e, g[i]);
         Vec8<T>::load(zin + e, xh[i]);
+        if (gz != nullptr) {
+#pragma unroll
+          for (int q = 0; q < (sizeof(T) == 2 ? 1 : 2); ++q)
+            gz_raw[i][q] = reinterpret_cast<const uint4*>(gz + e)[q];
+        }
 #pragma unroll
         for (int k = 0; k < 8; ++k) {
           xh[i][k] = (xh[i][k] - mean) * rstd;
@@ -204,7 +210,7 @@ __global__ void __launch_bounds__(32 * WPR * RG, (VPL == 1 && WPR * RG == 16) ? 
           for (int k = 0; k < 8; ++k) d[k] = rstd * (g[i][k] - m1 - xh[i][k] * m2);
           if (gz != nullptr) {
             float t[8];
-            Vec8<T>::load(gz + e, t);
+            Vec8<T>::load(reinterpret_cast<const T*>(gz_raw[i]), t);
 #pragma unroll
             for (int k = 0; k < 8; ++k) d[k] += t[k];
           }
