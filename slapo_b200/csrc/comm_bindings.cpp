@@ -61,9 +61,66 @@ void peer_gather(std::vector<int64_t> src_ptrs, int64_t dst_ptr, int64_t seg_byt
   TORCH_CHECK(rc == 0, "peer_gather: launch refused (code ", rc, ")");
 }
 
+int dtype16(const at::Tensor& t) {
+  TORCH_CHECK(t.scalar_type() == at::kBFloat16 || t.scalar_type() == at::kHalf,
+              "fused data-parallel kernels need bf16 or fp16 parameters");
+  return t.scalar_type() == at::kBFloat16 ? 0 : 1;
+}
+
+// out <- mean over ranks of grads[lo : lo + out.numel()] pulled from every rank's flat gradient
+void dp_grad_rs(std::vector<int64_t> grad_ptrs, std::vector<int64_t> flag_ptrs, int64_t world,
+                int64_t rank, int64_t bucket, int64_t epoch, int64_t lo, at::Tensor out,
+                const c10::optional<at::Tensor>& dup_mask,
+                const c10::optional<at::Tensor>& norm_acc, double wait_seconds, int64_t phase) {
+  c10::cuda::CUDAGuard guard(out.device());
+  auto g = to_ptrs<void*>(grad_ptrs);
+  auto f = to_ptrs<int*>(flag_ptrs);
+  const int dev = at::cuda::current_device();
+  int rc = slapo::launch_dp_grad_rs(
+      g.data(), f.data(), static_cast<int>(world), static_cast<int>(rank),
+      static_cast<int>(bucket), static_cast<int>(epoch), lo, out.numel(), out.data_ptr(),
+      dup_mask.has_value() && dup_mask->defined() ? dup_mask->data_ptr<uint8_t>() : nullptr,
+      norm_acc.has_value() && norm_acc->defined() ? norm_acc->data_ptr<float>() : nullptr,
+      slapo_status_ptr(dev), wait_seconds, dtype16(out), static_cast<int>(phase),
+      at::cuda::getCurrentCUDAStream().stream());
+  TORCH_CHECK(rc == 0, "dp_grad_rs: launch refused (code ", rc, ")");
+}
+
+// AdamW on this rank's slice, new parameters written to every rank's flat parameter buffer
+void dp_adamw_ag(std::vector<int64_t> param_ptrs, std::vector<int64_t> flag_ptrs, int64_t world,
+                 int64_t rank, int64_t n_buckets, int64_t epoch, bool last, int64_t lo,
+                 at::Tensor grad, at::Tensor master, at::Tensor exp_avg, at::Tensor exp_avg_sq,
+                 at::Tensor decay_mask, at::Tensor grad_scale, double lr, double beta1,
+                 double beta2, double eps, double weight_decay, double bc1, double bc2,
+                 at::Tensor cta_counter, double wait_seconds) {
+  c10::cuda::CUDAGuard guard(grad.device());
+  auto p = to_ptrs<void*>(param_ptrs);
+  auto f = to_ptrs<int*>(flag_ptrs);
+  const int dev = at::cuda::current_device();
+  int rc = slapo::launch_dp_adamw_ag(
+      p.data(), f.data(), static_cast<int>(world), static_cast<int>(rank),
+      static_cast<int>(n_buckets), static_cast<int>(epoch), last ? 1 : 0, lo, grad.numel(),
+      grad.data_ptr(), master.data_ptr<float>(), exp_avg.data_ptr<float>(),
+      exp_avg_sq.data_ptr<float>(), decay_mask.data_ptr<uint8_t>(), grad_scale.data_ptr<float>(),
+      static_cast<float>(lr), static_cast<float>(beta1), static_cast<float>(beta2),
+      static_cast<float>(eps), static_cast<float>(weight_decay), static_cast<float>(bc1),
+      static_cast<float>(bc2), reinterpret_cast<unsigned int*>(cta_counter.data_ptr<int>()),
+      slapo_status_ptr(dev), wait_seconds, dtype16(grad), at::cuda::getCurrentCUDAStream().stream());
+  TORCH_CHECK(rc == 0, "dp_adamw_ag: launch refused (code ", rc, ")");
+}
+
 }  // namespace
 
 void register_comm_ops(torch::Library& m) {
+  m.def("dp_grad_rs(int[] grad_ptrs, int[] flag_ptrs, int world, int rank, int bucket, int epoch, "
+        "int lo, Tensor(a!) out, Tensor? dup_mask, Tensor(b!)? norm_acc, float wait_seconds, "
+        "int phase) -> ()",
+        &dp_grad_rs);
+  m.def("dp_adamw_ag(int[] param_ptrs, int[] flag_ptrs, int world, int rank, int n_buckets, "
+        "int epoch, bool last, int lo, Tensor grad, Tensor(a!) master, Tensor(b!) exp_avg, "
+        "Tensor(c!) exp_avg_sq, Tensor decay_mask, Tensor grad_scale, float lr, float beta1, "
+        "float beta2, float eps, float weight_decay, float bc1, float bc2, Tensor(d!) cta_counter, "
+        "float wait_seconds) -> ()", &dp_adamw_ag);
   m.def("comm_gemm(int[] a_ptrs, int[] b_ptrs, int M, int N, int K, int lda, int ldb, bool a_mn, "
         "bool b_mn, bool bf16, int gather, int seg_len, int mode, int world, int rank, int epoch, "
         "int out_ptr, int ldo, int bias_ptr, int act, int flags_ptr, int[] peer_flags, "

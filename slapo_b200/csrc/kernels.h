@@ -62,6 +62,20 @@ int launch_peer_gather(void* const* src_ptrs, void* dst, int64_t seg_bytes, int 
                        int epoch, int* flags, int* const* peer_flags, int* status,
                        double wait_seconds, cudaStream_t stream);
 
+// Data-parallel gradient reduce-scatter (pull) and AdamW + parameter all-gather (push) over
+// peer memory (dp_comm.cu).  lo / n are element offsets / counts (multiples of 8) of this
+// rank's slice inside the flat buffers; 16-bit dtypes only.
+int launch_dp_grad_rs(void* const* grad_ptrs, int* const* flag_ptrs, int world, int rank,
+                      int bucket, int epoch, int64_t lo, int64_t n, void* out,
+                      const uint8_t* dup_mask, float* norm_acc, int* status, double wait_seconds,
+                      int dtype, int phase, cudaStream_t stream);
+int launch_dp_adamw_ag(void* const* param_ptrs, int* const* flag_ptrs, int world, int rank,
+                       int n_buckets, int epoch, int last, int64_t lo, int64_t n, const void* grad,
+                       float* master, float* exp_avg, float* exp_avg_sq, const uint8_t* decay_mask,
+                       const float* grad_scale, float lr, float beta1, float beta2, float eps,
+                       float weight_decay, float bc1, float bc2, unsigned int* cta_counter,
+                       int* status, double wait_seconds, int dtype, cudaStream_t stream);
+
 }  // namespace slapo
 
 #include "common_host.h"

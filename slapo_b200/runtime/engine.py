@@ -101,7 +101,7 @@ class TrainEngine:
     ``engine.train_batch(*inputs, **kw)`` does all three and returns the loss."""
 
     def __init__(self, model: nn.Module, config=None, mesh=None, tp_group=None, dp_group=None,
-                 loss_fn=None):
+                 loss_fn=None, dp_symm=None):
         self.model = model
         self.cfg = EngineConfig.from_dict(config)
         self.mesh = mesh
@@ -115,6 +115,9 @@ class TrainEngine:
         else:
             self.dp_size, self.dp_rank = 1, 0
         self.loss_fn = loss_fn
+        self.dp_symm = dp_symm      # symmetric-memory context of the DP group (made on demand)
+        self._params_pushed = False
+        self.fdp = None
         self.step_count = 0
         self.micro_step = 0
         self.last_grad_norm = None
@@ -161,8 +164,19 @@ class TrainEngine:
         bucket.end = offset
         self.buckets.append(bucket)
         self.total = offset
-        self.flat_param = torch.zeros(self.total, dtype=self.param_dtype, device=self.device)
-        self.flat_grad = torch.zeros(self.total, dtype=self.param_dtype, device=self.device)
+        if self._want_fused_dp():
+            from ..parallel.fused_dp import FusedDP
+            from ..parallel.symm import SymmContext
+
+            ctx = self.dp_symm if self.dp_symm is not None else SymmContext(
+                self.dp_group, device=self.device)
+            self.fdp = FusedDP(ctx, self.total, self.param_dtype, len(self.buckets))
+            self.flat_param, self.flat_grad = self.fdp.flat_param, self.fdp.flat_grad
+            logger.info("data parallelism over peer memory: %d buckets, %.0f MiB of gradients",
+                        len(self.buckets), self.total * 2 / 2**20, ranks=0)
+        else:
+            self.flat_param = torch.zeros(self.total, dtype=self.param_dtype, device=self.device)
+            self.flat_grad = torch.zeros(self.total, dtype=self.param_dtype, device=self.device)
         self.sp_sync_params = []
         for p, (off, n, _) in zip(self.params, self.param_slices):
             view = self.flat_param[off:off + n].view(p.shape)
@@ -172,6 +186,17 @@ class TrainEngine:
             if getattr(p, "replicated_param", False) and self.tp_size > 1:
                 self.sp_sync_params.append(p)
         self.n_params_local = sum(n for _, n, _ in self.param_slices)
+
+    def _want_fused_dp(self):
+        """ZeRO-1 over NVLink peer memory instead of NCCL: CUDA, 16-bit parameters, a
+        data-parallel group of 2..8 ranks on this node, not switched off by ``fused_dp=False``."""
+        if not (self.cfg.zero and 1 < self.dp_size <= 8 and self.device.type == "cuda"):
+            return False
+        if not self.cfg.extra.get("fused_dp", True) or not native.available():
+            return False
+        if self.param_dtype not in (torch.bfloat16, torch.float16):
+            return False
+        return hasattr(torch.ops.slapo_b200, "dp_grad_rs")
 
     def _shard_range(self, bucket):
         if not (self.cfg.zero and self.dp_size > 1):
@@ -244,7 +269,13 @@ class TrainEngine:
 
             ctx = contextlib.nullcontext()
         with ctx:
-            if self.cfg.zero:
+            if self.fdp is not None:
+                pos = self.shard_offsets[b_idx]
+                lo, hi = self.shard_ranges[b_idx]
+                mask = self.tp_dup_mask_u8[pos:pos + hi - lo] if self.tp_dup_mask is not None else None
+                self.fdp.grad_rs(b_idx, self.step_count + 1, lo, self.grad_shard[pos:pos + hi - lo],
+                                 mask)
+            elif self.cfg.zero:
                 pos = self.shard_offsets[b_idx]
                 lo, hi = self.shard_ranges[b_idx]
                 out = self.grad_shard[pos:pos + hi - lo]
@@ -336,10 +367,13 @@ class TrainEngine:
             lr = lr * self.cfg.lr_schedule(self.step_count)
         clip_coef = None
         if self.cfg.clip_grad and self.cfg.clip_grad > 0:
-            norm = self._grad_norm(grad)
+            # the fused reduce-scatter kernels already accumulated the squared norm
+            norm = self._finish_norm(self.fdp.take_norm_parts()) if self.fdp is not None \
+                else self._grad_norm(grad)
             self.last_grad_norm = norm
             clip_coef = torch.clamp(self.cfg.clip_grad / (norm + 1e-6), max=1.0)
         self._adamw(grad, lr, clip_coef)
+        self._params_pushed = self.fdp is not None
         self._gather_params()
         self.flat_grad.zero_()
         return True
@@ -349,6 +383,18 @@ class TrainEngine:
         t = self.step_count
         bc1, bc2 = 1 - b1**t, 1 - b2**t
         contiguous_owner = not (self.cfg.zero and self.dp_size > 1)
+        if self.fdp is not None:
+            coef = (clip_coef if clip_coef is not None
+                    else torch.ones((), device=self.device)).float().reshape(1)
+            last_idx = len(self.shard_ranges) - 1
+            for idx, ((lo, hi), pos) in enumerate(zip(self.shard_ranges, self.shard_offsets)):
+                n = hi - lo
+                self.fdp.adamw_ag(
+                    self.step_count, idx == last_idx, lo, grad[pos:pos + n],
+                    self.master[pos:pos + n], self.exp_avg[pos:pos + n],
+                    self.exp_avg_sq[pos:pos + n], self.decay_mask[pos:pos + n], coef, lr,
+                    (b1, b2), self.cfg.eps, self.cfg.weight_decay, bc1, bc2)
+            return
         if self.device.type == "cuda" and native.available() and hasattr(
                 torch.ops.slapo_b200, "fused_adamw"):
             coef = clip_coef if clip_coef is not None else torch.ones((), device=self.device)
@@ -379,6 +425,9 @@ class TrainEngine:
 
     def _gather_params(self):
         if not (self.cfg.zero and self.dp_size > 1):
+            return
+        if self.fdp is not None and self._params_pushed:
+            self._params_pushed = False   # the fused AdamW kernel stored them on every rank
             return
         for bucket, (lo, hi) in zip(self.buckets, self.shard_ranges):
             full = self.flat_param[bucket.start:bucket.end]
