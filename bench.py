@@ -191,7 +191,7 @@ def build_native(args, world, rank):
     with slapo.init_empty_weights():
         model = BertForMaskedLM(cfg)
     sch = slapo.model_schedule.apply_schedule(
-        model, "bert", model_config=cfg, bf16=True, group=mesh.tp_group if mesh else None,
+        model, "bert", model_config=cfg, bf16=True, group=mesh.schedule_group if mesh else None,
         ckpt_ratio=args.ckpt_ratio, sequence_parallel=sp)
     vocab_parallel = tp > 1
     tp_group = mesh.tp_group if mesh else None

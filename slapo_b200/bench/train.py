@@ -140,11 +140,14 @@ def build_engine(args, world, device):
         model = spec.build()
         if hasattr(model, "init_weights"):
             model.init_weights()
-    kwargs = dict(model_config=cfg, group=mesh.tp_group if mesh else None,
+    kwargs = dict(model_config=cfg, group=mesh.schedule_group if mesh else None,
                   ckpt_ratio=args.ckpt_ratio, fuse=not args.no_fuse, attn_op_name=args.attn_op,
                   bf16=args.dtype == "bf16", fp16=args.dtype == "fp16")
     if spec.schedule_key in ("bert", "roberta", "gpt2", "gpt_neo", "opt"):
         kwargs["sequence_parallel"] = sp
+        # token shards along the batch axis: gathered rows are a plain concatenation, which
+        # is what the fused all-gather -> GEMM kernel consumes
+        kwargs["sequence_parallel_axis"] = 0
     if pp > 1:
         if spec.kind == "seq2seq":
             half = pp // 2
@@ -203,6 +206,9 @@ def run(args):
     seq_dec = args.seq_len_dec or spec.default_seq_dec
     batches = [spec.make_batch(per_call, seq, seq_dec, seed=args.seed + 17 * dp_rank + i,
                                device=device) for i in range(calls)]
+    if spec.kind == "image":   # images follow the parameter dtype
+        pdtype = next(inner.model.parameters()).dtype
+        batches = [(tuple(t.to(pdtype) for t in inputs), labels) for inputs, labels in batches]
 
     def step():
         loss = None

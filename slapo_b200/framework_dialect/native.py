@@ -16,12 +16,8 @@ def init_native_engine(sch, model, config=None, mesh=None, loss_fn=None, dp_grou
     from ..runtime.engine import TrainEngine
     from ..runtime.pipeline_engine import PipelineEngine, PipelineModel
 
-    if isinstance(model, PipelineModel):
-        kwargs.pop("fused_tp", None)
-        engine = PipelineEngine(model, config=config, mesh=mesh, loss_fn=loss_fn,
-                                tp_group=sch.group, **kwargs)
-        return engine, engine
-    fused = kwargs.get("fused_tp", True)
+    fused = kwargs.pop("fused_tp", True)
+    ctx = None
     if fused and sch.world_size > 1:
         import torch
 
@@ -29,12 +25,20 @@ def init_native_engine(sch, model, config=None, mesh=None, loss_fn=None, dp_grou
             from ..parallel.lowering import lower_fused_tp
             from ..parallel.symm import SymmContext
 
+            # structural only (plans on the Linear modules); inside a pipeline the stage
+            # modules are the very objects the schedule tree points at
             ctx = SymmContext(sch.group)
             lower_fused_tp(sch, ctx)
-            model = sch.mod
+    if isinstance(model, PipelineModel):
+        engine = PipelineEngine(model, config=config, mesh=mesh, loss_fn=loss_fn,
+                                tp_group=sch.group, **kwargs)
+        engine.symm_ctx = ctx
+        return engine, engine
+    if ctx is not None:
+        model = sch.mod
     engine = TrainEngine(model, config=config, mesh=mesh, tp_group=sch.group,
                          dp_group=dp_group, loss_fn=loss_fn)
-    engine.symm_ctx = locals().get("ctx")
+    engine.symm_ctx = ctx
     return engine, engine
 
 

@@ -86,6 +86,13 @@ class DeviceMesh:
                 if self.rank in ranks:
                     self.groups[axis] = group
 
+    @property
+    def schedule_group(self):
+        """What to pass as ``group=`` to ``create_schedule`` / ``apply_schedule``: the
+        tensor-parallel group, or ``False`` - "no tensor parallelism" - when ``tp == 1``
+        (``None`` would mean the whole job, i.e. sharding over data / pipeline peers)."""
+        return self.groups["tp"] if self.dims["tp"] > 1 else False
+
     tp_group = property(lambda self: self.groups["tp"])
     dp_group = property(lambda self: self.groups["dp"])
     pp_group = property(lambda self: self.groups["pp"])

@@ -44,6 +44,22 @@ def test_train_entry_dp2_sequence_parallel_tp():
     assert rec["dp"] == 2 and rec["sequence_parallel"] is True
 
 
+def test_train_entry_without_tensor_parallelism_never_shards_over_other_axes():
+    """tp == 1 with several ranks (pure pipeline, pure data parallel): the schedule must not
+    treat the whole job as a tensor-parallel group."""
+    import bench_single_node as B
+    rec, text = B.launch("gpt-neo-125m", 2, ["--pp", "2", "--micro-batches", "2"] + TINY,
+                         port=29564)
+    assert rec is not None, text[-3000:]
+    assert (rec["tp"], rec["pp"], rec["dp"]) == (1, 2, 1)
+    assert rec["param_per_gpu_m"] > 0
+    rec2, text = B.launch("gpt-neo-125m", 2, TINY, port=29565)       # dp = 2
+    assert rec2 is not None, text[-3000:]
+    assert (rec2["tp"], rec2["pp"], rec2["dp"]) == (1, 1, 2)
+    # unsharded: each rank holds the full model (a pipeline stage holds about half of it)
+    assert rec2["param_per_gpu_m"] > rec["param_per_gpu_m"]
+
+
 def test_benchmark_config_and_flops():
     import bench_single_node as B
     runs = B.parse_config(os.path.join(ROOT, "benchmark", "configs", "single_node_b200.cfg"))
