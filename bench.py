@@ -56,6 +56,8 @@ def parse_args():
     ap.add_argument("--parallelism", default="tp", choices=["tp", "dp"])
     ap.add_argument("--no-sequence-parallel", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--no-fused-dp", action="store_true",
+                    help="data parallelism through NCCL instead of the peer-memory kernels")
     ap.add_argument("--profile", action="store_true",
                     help="print a per-kernel time table of one step (torch.profiler, rank 0); "
                          "analysis aid only, the reported numbers are taken without it")
@@ -200,7 +202,8 @@ def build_native(args, world, rank):
         return mlm_loss(out["logits"], labels, tp_group, vocab_parallel)
 
     engine, _ = slapo.build(sch, target="native", mesh=mesh, loss_fn=loss_fn,
-                            config={"lr": 1e-4, "weight_decay": 0.01, "clip_grad": 1.0})
+                            config={"lr": 1e-4, "weight_decay": 0.01, "clip_grad": 1.0,
+                                    "fused_dp": not args.no_fused_dp})
     parallelism = f"tp{tp}" + ("+sp" if sp else "") if tp > 1 else (f"dp{dp}" if dp > 1 else "single")
     return engine, vocab, parallelism, dp
 

@@ -129,16 +129,52 @@ def bench_gemm(small, iters):
         report("gemm_cublas", t2, flops=2 * m * n * k, shape=[m, n, k])
 
 
+def bench_comm(small, iters):
+    """Fused GEMM + collective kernels as ONE emulated rank of a 2-rank group whose "peer"
+    buffers live on this GPU too, with the peer's flags pre-set: the kernel runs its full
+    code path (copier warps, staging, pull-based reduction) and its tensor-core / memory
+    behaviour can be profiled on a single GPU; NVLink time is not part of these numbers."""
+    from slapo_b200.parallel import fused_tp as ft
+    from slapo_b200.parallel.symm import LocalSymmContext
+
+    world = 2
+    ts, k, n = (4096, 1024, 4096) if small else (8192, 1024, 4096)
+    ctx = LocalSymmContext(world, wait_seconds=0.05)
+    shards = [torch.randn(ts, k, device="cuda", dtype=torch.bfloat16) for _ in range(world)]
+    for r in range(world):
+        buf = ctx.as_rank(r).buffer("ag_in", ts * k * 2)
+        buf.view(torch.bfloat16, (ts, k)).copy_(shards[r])
+    w = torch.randn(n, k, device="cuda", dtype=torch.bfloat16)
+    ctx.as_rank(0)
+
+    def ag():
+        ctx.preset_flags(ctx.epoch + 1)
+        return ft.ag_gemm(ctx, shards[0], w, None, staged=ctx.buffer("ag_in", ts * k * 2))
+
+    report("ag_gemm_emulated", timeit(ag, iters), flops=2 * ts * world * n * k,
+           shape=[ts * world, n, k], world=world)
+    x = torch.randn(ts * world, n, device="cuda", dtype=torch.bfloat16)
+    w2 = torch.randn(k, n, device="cuda", dtype=torch.bfloat16)
+
+    def rs():
+        ctx.preset_flags(ctx.epoch + 1, ready=True, done=True, done2=True)
+        return ft.gemm_rs(ctx, x, w2, None)
+
+    report("gemm_rs_emulated", timeit(rs, iters), flops=2 * ts * world * n * k,
+           shape=[ts * world, k, n], world=world)
+
+
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--op", default="all", choices=["all", "ln", "gelu", "attn", "gemm"])
+    ap.add_argument("--op", default="all", choices=["all", "ln", "gelu", "attn", "gemm", "comm"])
     ap.add_argument("--small", action="store_true", help="small inputs for profiler captures")
     ap.add_argument("--iters", type=int, default=20)
     args = ap.parse_args()
     assert native.available(), native.load_error()
     todo = ["ln", "gelu", "attn", "gemm"] if args.op == "all" else [args.op]
     for op in todo:
-        {"ln": bench_ln, "gelu": bench_gelu, "attn": bench_attn, "gemm": bench_gemm}[op](
+        {"ln": bench_ln, "gelu": bench_gelu, "attn": bench_attn, "gemm": bench_gemm,
+         "comm": bench_comm}[op](
             args.small, args.iters)
     print(json.dumps({"device_status": int(native.ops().device_status())}))
 

@@ -56,6 +56,11 @@ def parse_args(argv=None):
     ap.add_argument("--save", default=None, help="write a sharded checkpoint here at the end")
     ap.add_argument("--resume", default=None, help="resume from this sharded checkpoint")
     ap.add_argument("--log-file", default=None, help="also append the JSON record to this file")
+    ap.add_argument("--hang-dump", type=float, default=0.0,
+                    help="dump every thread's Python stack to stderr after this many seconds "
+                         "(and every such interval again): shows where a stuck rank waits")
+    ap.add_argument("--no-fused-dp", action="store_true",
+                    help="data parallelism through NCCL instead of the peer-memory kernels")
     return ap.parse_args(argv)
 
 
@@ -173,6 +178,7 @@ def build_engine(args, world, device):
     loss_fn = spec.loss_fn(tp_group, vocab_parallel)
     build_kwargs = dict(target="native", mesh=mesh, loss_fn=loss_fn,
                         config={"lr": args.lr, "weight_decay": 0.01, "clip_grad": 1.0,
+                                "fused_dp": not args.no_fused_dp,
                                 "grad_accum_steps": args.micro_batches if pp == 1 else 1})
     if pp > 1:
         build_kwargs["num_micro_batches"] = args.micro_batches
@@ -257,6 +263,10 @@ def run(args):
 
 def main(argv=None):
     args = parse_args(argv)
+    if args.hang_dump > 0:
+        import faulthandler
+
+        faulthandler.dump_traceback_later(args.hang_dump, repeat=True, file=sys.stderr)
     t0 = time.time()
     try:
         run(args)

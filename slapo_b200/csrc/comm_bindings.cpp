@@ -109,9 +109,33 @@ void dp_adamw_ag(std::vector<int64_t> param_ptrs, std::vector<int64_t> flag_ptrs
   TORCH_CHECK(rc == 0, "dp_adamw_ag: launch refused (code ", rc, ")");
 }
 
+void peer_all_to_all(at::Tensor src, std::vector<int64_t> dst_ptrs, std::vector<int64_t> flag_ptrs,
+                     int64_t world, int64_t rank, int64_t epoch, int64_t outer, int64_t rows,
+                     int64_t row_bytes, int64_t src_block_stride, int64_t src_outer_stride,
+                     int64_t src_row_stride, int64_t dst_block_offset, int64_t dst_outer_stride,
+                     int64_t dst_row_stride, at::Tensor cta_counter, double wait_seconds) {
+  c10::cuda::CUDAGuard guard(src.device());
+  auto d = to_ptrs<void*>(dst_ptrs);
+  auto f = to_ptrs<int*>(flag_ptrs);
+  const int dev = at::cuda::current_device();
+  int rc = slapo::launch_peer_all_to_all(
+      src.data_ptr(), d.data(), f.data(), static_cast<int>(world), static_cast<int>(rank),
+      static_cast<int>(epoch), static_cast<int>(outer), static_cast<int>(rows),
+      static_cast<int>(row_bytes), src_block_stride, src_outer_stride, src_row_stride,
+      dst_block_offset, dst_outer_stride, dst_row_stride,
+      reinterpret_cast<unsigned int*>(cta_counter.data_ptr<int>()), slapo_status_ptr(dev),
+      wait_seconds, at::cuda::getCurrentCUDAStream().stream());
+  TORCH_CHECK(rc == 0, "peer_all_to_all: launch refused (code ", rc,
+              "): rows and strides must be multiples of 16 bytes");
+}
+
 }  // namespace
 
 void register_comm_ops(torch::Library& m) {
+  m.def("peer_all_to_all(Tensor src, int[] dst_ptrs, int[] flag_ptrs, int world, int rank, "
+        "int epoch, int outer, int rows, int row_bytes, int src_block_stride, "
+        "int src_outer_stride, int src_row_stride, int dst_block_offset, int dst_outer_stride, "
+        "int dst_row_stride, Tensor(a!) cta_counter, float wait_seconds) -> ()", &peer_all_to_all);
   m.def("dp_grad_rs(int[] grad_ptrs, int[] flag_ptrs, int world, int rank, int bucket, int epoch, "
         "int lo, Tensor(a!) out, Tensor? dup_mask, Tensor(b!)? norm_acc, float wait_seconds, "
         "int phase) -> ()",

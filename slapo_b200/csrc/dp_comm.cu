@@ -215,6 +215,64 @@ __global__ void __launch_bounds__(256) dp_adamw_ag_kernel(
 }
 
 // ------------------------------------------------------------------------ //
+// All-to-all of activation blocks by peer stores (the RS <-> SR reshard).
+// Rank r's block for rank j is a strided 3-D box [outer, rows, row_vecs * 8]; it lands in
+// rank j's receive buffer at the position that concatenation along the other axis asks for,
+// so neither side needs a packing or an un-packing copy.  The CTA that finishes last
+// publishes "sent" to every peer and waits (bounded) for theirs: when the kernel ends, this
+// rank's receive buffer is complete.
+struct A2AParams {
+  const void* src;
+  void* dst[kDpMaxRanks];       // every rank's receive buffer
+  int* flags[kDpMaxRanks];      // every rank's flag pad (slots 0..7: sent by rank i)
+  int world, rank, epoch;
+  int outer, rows, row_vecs;    // box extent (row_vecs in 16-byte vectors)
+  // element offsets (in 16-byte vectors) of block j inside src, and of this rank's block
+  // inside a destination buffer
+  int64_t src_block_stride, src_outer_stride, src_row_stride;
+  int64_t dst_block_offset, dst_outer_stride, dst_row_stride;
+  unsigned int* cta_counter;
+  int* status;
+  long long wait_cycles;
+};
+
+__global__ void __launch_bounds__(256) peer_all_to_all_kernel(A2AParams p) {
+  const int64_t per_block = static_cast<int64_t>(p.outer) * p.rows * p.row_vecs;
+  const int64_t total = per_block * p.world;
+  const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
+  const uint4* src = static_cast<const uint4*>(p.src);
+  for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < total;
+       i += stride) {
+    int j = static_cast<int>(i / per_block);         // destination slot, rotated below
+    int64_t rem = i - j * per_block;
+    const int v = static_cast<int>(rem % p.row_vecs);
+    rem /= p.row_vecs;
+    const int r = static_cast<int>(rem % p.rows);
+    const int o = static_cast<int>(rem / p.rows);
+    j += p.rank;                                     // start with the own block, then rank + 1 ...
+    if (j >= p.world) j -= p.world;
+    const uint4 val = src[j * p.src_block_stride + o * p.src_outer_stride + r * p.src_row_stride + v];
+    static_cast<uint4*>(p.dst[j])[p.dst_block_offset + o * p.dst_outer_stride +
+                                  r * p.dst_row_stride + v] = val;
+  }
+  __shared__ int s_last;
+  __threadfence_system();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const unsigned int done = atomicAdd(p.cta_counter, 1u);
+    s_last = (done == gridDim.x - 1) ? 1 : 0;
+  }
+  __syncthreads();
+  if (!s_last) return;
+  if (threadIdx.x == 0) *p.cta_counter = 0u;
+  if (threadIdx.x < p.world && threadIdx.x != p.rank) {
+    __threadfence_system();
+    dp_st_release(p.flags[threadIdx.x] + p.rank, p.epoch);
+    if (!dp_wait(p.flags[p.rank] + threadIdx.x, p.epoch, p.wait_cycles)) atomicExch(p.status, 7);
+  }
+}
+
+// ------------------------------------------------------------------------ //
 static long long dp_wait_cycles(double seconds) {
   int dev = 0, khz = 0;
   cudaGetDevice(&dev);
@@ -285,6 +343,36 @@ int launch_dp_adamw_ag(void* const* param_ptrs, int* const* flag_ptrs, int world
         p, f, world, rank, n_buckets, epoch, last, lo, n_vec, static_cast<const __half*>(grad),
         master, exp_avg, exp_avg_sq, decay_mask, grad_scale, lr, beta1, beta2, eps, weight_decay,
         bc1, bc2, cta_counter, status, cycles);
+  return cudaGetLastError() == cudaSuccess ? 0 : 4;
+}
+
+int launch_peer_all_to_all(const void* src, void* const* dst_ptrs, int* const* flag_ptrs,
+                           int world, int rank, int epoch, int outer, int rows, int row_bytes,
+                           int64_t src_block_stride, int64_t src_outer_stride,
+                           int64_t src_row_stride, int64_t dst_block_offset,
+                           int64_t dst_outer_stride, int64_t dst_row_stride,
+                           unsigned int* cta_counter, int* status, double wait_seconds,
+                           cudaStream_t stream) {
+  if (world < 1 || world > kDpMaxRanks || row_bytes % 16 != 0) return 1;
+  const int64_t strides[6] = {src_block_stride, src_outer_stride, src_row_stride,
+                              dst_block_offset, dst_outer_stride, dst_row_stride};
+  for (int64_t v : strides)
+    if (v % 16 != 0) return 2;   // byte strides must keep 16-byte alignment
+  A2AParams p;
+  p.src = src;
+  for (int r = 0; r < kDpMaxRanks; ++r) {
+    p.dst[r] = r < world ? dst_ptrs[r] : nullptr;
+    p.flags[r] = r < world ? flag_ptrs[r] : nullptr;
+  }
+  p.world = world; p.rank = rank; p.epoch = epoch;
+  p.outer = outer; p.rows = rows; p.row_vecs = row_bytes / 16;
+  p.src_block_stride = src_block_stride / 16; p.src_outer_stride = src_outer_stride / 16;
+  p.src_row_stride = src_row_stride / 16; p.dst_block_offset = dst_block_offset / 16;
+  p.dst_outer_stride = dst_outer_stride / 16; p.dst_row_stride = dst_row_stride / 16;
+  p.cta_counter = cta_counter; p.status = status; p.wait_cycles = dp_wait_cycles(wait_seconds);
+  const int64_t total = static_cast<int64_t>(outer) * rows * p.row_vecs * world;
+  count_launch();
+  peer_all_to_all_kernel<<<dp_grid(total), 256, 0, stream>>>(p);
   return cudaGetLastError() == cudaSuccess ? 0 : 4;
 }
 

@@ -126,15 +126,25 @@ __global__ void __launch_bounds__(256) bias_act_bwd_kernel(
   if (partial != nullptr) slab_reduce_store(acc, partial, cols, col, col_ok);
 }
 
+// 32 x 32 threads per 32 columns: threadIdx.y strides over the chunks (see ln_bwd_finalize).
 template <typename T>
-__global__ void colsum_finalize_kernel(const float* __restrict__ partial, T* __restrict__ out,
-                                       int chunks, int cols) {
-  const int c = blockIdx.x * blockDim.x + threadIdx.x;
-  if (c >= cols) return;
+__global__ void __launch_bounds__(1024) colsum_finalize_kernel(
+    const float* __restrict__ partial, T* __restrict__ out, int chunks, int cols) {
+  __shared__ float red[32][33];
+  const int c = blockIdx.x * 32 + threadIdx.x;
   float s = 0.f;
-  for (int i = 0; i < chunks; ++i) s += partial[static_cast<int64_t>(i) * cols + c];
-  if constexpr (sizeof(T) == 4) out[c] = s;
-  else out[c] = static_cast<T>(s);
+  if (c < cols) {
+    for (int i = threadIdx.y; i < chunks; i += 32) s += partial[static_cast<int64_t>(i) * cols + c];
+  }
+  red[threadIdx.y][threadIdx.x] = s;
+  __syncthreads();
+  if (threadIdx.y == 0 && c < cols) {
+    float t = 0.f;
+#pragma unroll
+    for (int y = 0; y < 32; ++y) t += red[y][threadIdx.x];
+    if constexpr (sizeof(T) == 4) out[c] = t;
+    else out[c] = static_cast<T>(t);
+  }
 }
 
 // ------------------------------------------------------------------------ //
@@ -272,7 +282,7 @@ void launch_bias_act_fwd(const void* x, const void* bias, void* y, int64_t rows,
 void launch_colsum_finalize(const float* partial, void* out, int chunks, int cols, int dtype,
                             cudaStream_t stream) {
   count_launch();
-  DISPATCH_DTYPE(dtype, (colsum_finalize_kernel<T><<<(cols + 255) / 256, 256, 0, stream>>>(
+  DISPATCH_DTYPE(dtype, (colsum_finalize_kernel<T><<<(cols + 31) / 32, dim3(32, 32), 0, stream>>>(
       partial, static_cast<T*>(out), chunks, cols)));
 }
 

@@ -56,25 +56,29 @@ __device__ __forceinline__ void red_add_v4(float* addr, float a, float b, float 
                : "memory");
 }
 
-// delta[b, h, i] = sum_d dO[b, i, h, d] * O[b, i, h, d]   (both contiguous [B, Sq, H, D])
+// delta[b, h, i] = sum_d dO[b, i, h, d] * O[b, i, h, d]   (both contiguous [B, Sq, H, D]).
+// D / 8 lanes share a row (16-byte loads, every lane busy), so a warp covers 256 / D rows.
 template <typename T>
 __global__ void flash_bwd_delta_kernel(const T* __restrict__ dout, const T* __restrict__ out,
                                        float* __restrict__ delta, int B, int H, int Sq, int D) {
+  const int lanes_per_row = D >> 3;              // 8 (D = 64) or 16 (D = 128)
+  const int rows_per_warp = 32 / lanes_per_row;
   const int warps_per_block = blockDim.x >> 5;
-  const int64_t row = static_cast<int64_t>(blockIdx.x) * warps_per_block + (threadIdx.x >> 5);
   const int lane = threadIdx.x & 31;
+  const int64_t warp_id = static_cast<int64_t>(blockIdx.x) * warps_per_block + (threadIdx.x >> 5);
+  const int64_t row = warp_id * rows_per_warp + lane / lanes_per_row;
   const int64_t rows = static_cast<int64_t>(B) * Sq * H;
-  if (row >= rows) return;
   float s = 0.f;
-  for (int d = lane * 8; d < D; d += 256) {
+  if (row < rows) {
+    const int d = (lane % lanes_per_row) * 8;
     float a[8], b[8];
     Vec8<T>::load(dout + row * D + d, a);
     Vec8<T>::load(out + row * D + d, b);
 #pragma unroll
     for (int k = 0; k < 8; ++k) s += a[k] * b[k];
   }
-  s = warp_sum(s);
-  if (lane == 0) {
+  for (int o = lanes_per_row >> 1; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+  if (row < rows && lane % lanes_per_row == 0) {
     const int h = static_cast<int>(row % H);
     const int64_t bi = row / H;
     const int i = static_cast<int>(bi % Sq);
@@ -461,7 +465,8 @@ int launch_flash_bwd(const void* q, const void* k, const void* v, const void* o,
   {
     const int64_t rows = static_cast<int64_t>(B) * Sq * H;
     const int wpb = 8;
-    const unsigned blocks = static_cast<unsigned>((rows + wpb - 1) / wpb);
+    const int64_t rows_per_block = static_cast<int64_t>(wpb) * (256 / D);
+    const unsigned blocks = static_cast<unsigned>((rows + rows_per_block - 1) / rows_per_block);
     count_launch();
     if (bf16)
       flash_bwd_delta_kernel<__nv_bfloat16><<<blocks, wpb * 32, 0, stream>>>(

@@ -76,6 +76,16 @@ int launch_dp_adamw_ag(void* const* param_ptrs, int* const* flag_ptrs, int world
                        float weight_decay, float bc1, float bc2, unsigned int* cta_counter,
                        int* status, double wait_seconds, int dtype, cudaStream_t stream);
 
+// All-to-all of strided activation blocks by peer stores; strides and offsets in BYTES
+// (multiples of 16).  Block j of src goes to dst_ptrs[j] + dst_block_offset.
+int launch_peer_all_to_all(const void* src, void* const* dst_ptrs, int* const* flag_ptrs,
+                           int world, int rank, int epoch, int outer, int rows, int row_bytes,
+                           int64_t src_block_stride, int64_t src_outer_stride,
+                           int64_t src_row_stride, int64_t dst_block_offset,
+                           int64_t dst_outer_stride, int64_t dst_row_stride,
+                           unsigned int* cta_counter, int* status, double wait_seconds,
+                           cudaStream_t stream);
+
 }  // namespace slapo
 
 #include "common_host.h"

@@ -268,18 +268,32 @@ __global__ void __launch_bounds__(32 * WPR * RG, (VPL == 1 && WPR * RG == 16) ? 
   }
 }
 
+// Column sums of the per-CTA partials.  A 32 x 32 thread block owns 32 columns: threadIdx.y
+// strides over the partial rows (coalesced 128-byte reads), shared memory combines the 32
+// row groups - ~n_part / 32 dependent loads per thread instead of n_part.
 template <typename T>
-__global__ void ln_bwd_finalize_kernel(const float* __restrict__ partial, T* __restrict__ dgamma,
-                                       T* __restrict__ dbeta, T* __restrict__ dbias, int n_part,
-                                       int cols) {
-  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+__global__ void __launch_bounds__(1024) ln_bwd_finalize_kernel(
+    const float* __restrict__ partial, T* __restrict__ dgamma, T* __restrict__ dbeta,
+    T* __restrict__ dbias, int n_part, int cols) {
+  __shared__ float red[32][33];
+  const int c = blockIdx.x * 32 + threadIdx.x;
   const int which = blockIdx.y;  // 0 gamma, 1 beta, 2 bias
   T* dst = which == 0 ? dgamma : (which == 1 ? dbeta : dbias);
-  if (c >= cols || dst == nullptr) return;
+  if (dst == nullptr) return;
   float s = 0.f;
-  for (int i = 0; i < n_part; ++i) s += partial[(static_cast<int64_t>(i) * 3 + which) * cols + c];
-  if constexpr (sizeof(T) == 4) dst[c] = s;
-  else dst[c] = static_cast<T>(s);
+  if (c < cols) {
+    for (int i = threadIdx.y; i < n_part; i += 32)
+      s += partial[(static_cast<int64_t>(i) * 3 + which) * cols + c];
+  }
+  red[threadIdx.y][threadIdx.x] = s;
+  __syncthreads();
+  if (threadIdx.y == 0 && c < cols) {
+    float t = 0.f;
+#pragma unroll
+    for (int y = 0; y < 32; ++y) t += red[y][threadIdx.x];
+    if constexpr (sizeof(T) == 4) dst[c] = t;
+    else dst[c] = static_cast<T>(t);
+  }
 }
 
 // ------------------------------------------------------------------------ //
@@ -358,8 +372,8 @@ void launch_ln_bwd(const void* gy, const void* gz, const void* zin, const void* 
           static_cast<const T*>(gy), static_cast<const T*>(gz), static_cast<const T*>(zin),
           static_cast<const T*>(gamma), mean, rstd, static_cast<T*>(dx), static_cast<T*>(dres),
           partial, rows, cols, p, rng, rms, want_dbias))));
-  dim3 fgrid((cols + 255) / 256, 3);
-  DISPATCH_DTYPE(dtype, (ln_bwd_finalize_kernel<T><<<fgrid, 256, 0, stream>>>(
+  dim3 fgrid((cols + 31) / 32, 3);
+  DISPATCH_DTYPE(dtype, (ln_bwd_finalize_kernel<T><<<fgrid, dim3(32, 32), 0, stream>>>(
       partial, static_cast<T*>(dgamma), static_cast<T*>(dbeta), static_cast<T*>(dbias), grid,
       cols)));
 }

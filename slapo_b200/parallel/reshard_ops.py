@@ -45,6 +45,18 @@ RESHARD_COST = {
 
 _AXIS = {"RS": -1, "SR": -2}
 
+# process group (or None for the default group) -> FusedAllToAll
+_FUSED_A2A = {}
+
+
+def enable_fused_all_to_all(group, ctx):
+    """Route the ``RS <-> SR`` all-to-all of ``group`` through the peer-store kernel over the
+    symmetric-memory context ``ctx`` (collective: every rank of the group calls it)."""
+    from .fused_a2a import FusedAllToAll
+
+    _FUSED_A2A[group] = FusedAllToAll(ctx)
+    return _FUSED_A2A[group]
+
 
 def _all_to_all_dims(inp, split_dim, cat_dim, group):
     """Split ``inp`` along split_dim into p pieces, send piece j to rank j,
@@ -54,6 +66,11 @@ def _all_to_all_dims(inp, split_dim, cat_dim, group):
         return inp
     ndim = inp.dim()
     split_dim, cat_dim = split_dim % ndim, cat_dim % ndim
+    fused = _FUSED_A2A.get(group)
+    if fused is not None:
+        inp_c = inp.contiguous()
+        if fused.supports(inp_c, split_dim, cat_dim, world):
+            return fused(inp_c, split_dim, cat_dim)
     pieces = [c.contiguous() for c in inp.chunk(world, dim=split_dim)]
     backend = dist.get_backend(group)
     if backend == "gloo":

@@ -132,6 +132,7 @@ class PipelineEngine:
         self.inner.cfg.grad_accum_steps = 1
         self._meta_fwd = None   # [(name, shape, dtype, requires_grad)] of live_in[stage]
         self._tied = self._find_tied()
+        self._sync_tied_params()
         self.last_loss = None
 
     # ---- tied parameters across stages --------------------------------- #
@@ -147,6 +148,22 @@ class PipelineEngine:
         if groups:
             logger.info("tied parameters across stages: %s", [g[1] for g in groups], ranks=0)
         return groups
+
+    def _sync_tied_params(self):
+        """Stages initialise their parameters independently; a parameter shared by several
+        stages (tied embedding / LM head) takes the value of the first stage that owns it."""
+        c = self.mesh.get_coord()
+        for p, stages in self._tied:
+            if self.stage_id not in stages or p.is_meta:
+                continue
+            src_stage = stages[0]
+            if self.stage_id == src_stage:
+                for s in stages[1:]:
+                    dist.send(p.data.contiguous(), dst=self.mesh.get_rank(pp=s, dp=c["dp"], tp=c["tp"]))
+            else:
+                buf = torch.empty_like(p.data)
+                dist.recv(buf, src=self.mesh.get_rank(pp=src_stage, dp=c["dp"], tp=c["tp"]))
+                p.data.copy_(buf)
 
     def _sync_tied_grads(self):
         c = self.mesh.get_coord()

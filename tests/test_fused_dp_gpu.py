@@ -150,3 +150,73 @@ def test_fused_dp_engine_two_gpus():
     if torch.cuda.device_count() < 2:
         pytest.skip("needs 2 GPUs")
     run_distributed(_dp_worker, 2, backend="nccl")
+
+
+@pytest.mark.parametrize("world", [2, 4])
+@pytest.mark.parametrize("direction", ["RS->SR", "SR->RS"])
+def test_fused_all_to_all_emulated_ranks(world, direction):
+    """The reshard all-to-all as peer stores: every emulated rank pushes its blocks, then each
+    rank's receive buffer must hold the resharded tensor."""
+    from slapo_b200.ops import native
+    from slapo_b200.parallel.fused_a2a import FusedAllToAll
+    from slapo_b200.parallel.symm import LocalSymmContext
+
+    torch.manual_seed(3)
+    b, s, h = 3, 8 * world, 16 * world
+    full = torch.randn(b, s, h, device="cuda").bfloat16()
+    ctx = LocalSymmContext(world)
+    a2as = [FusedAllToAll(ctx.as_rank(r), wait_seconds=0.05) for r in range(world)]
+    if direction == "RS->SR":
+        ins = [full.chunk(world, 2)[r].contiguous() for r in range(world)]
+        want = [full.chunk(world, 1)[r] for r in range(world)]
+        split_dim, cat_dim = -2, -1
+    else:
+        ins = [full.chunk(world, 1)[r].contiguous() for r in range(world)]
+        want = [full.chunk(world, 2)[r] for r in range(world)]
+        split_dim, cat_dim = -1, -2
+    views = []
+    for r in range(world):
+        ctx.as_rank(r)
+        ctx.epoch = 0                                   # SPMD: every rank counts the same epochs
+        a2as[r].flag_buf.view(torch.int32, (8,)).fill_(1)   # the peers "sent" epoch 1 already
+        assert a2as[r].supports(ins[r], split_dim, cat_dim, world)
+        views.append(a2as[r].push(ins[r], split_dim, cat_dim))
+    torch.cuda.synchronize()
+    assert native.ops().device_status() == 0
+    for r in range(world):
+        assert torch.equal(views[r], want[r]), f"rank {r}"
+
+
+def _a2a_worker(rank, world):
+    import torch.distributed as dist
+
+    from slapo_b200.ops import native
+    from slapo_b200.parallel import reshard_ops
+    from slapo_b200.parallel.symm import SymmContext
+
+    dev = torch.device("cuda", rank)
+    torch.manual_seed(5)
+    full = torch.randn(2, 64, 256, device=dev).bfloat16()
+    local = full.chunk(world, 2)[rank].contiguous().requires_grad_(True)
+    ref = reshard_ops.reshard("RS->SR", local, None)            # NCCL all-to-all
+    ref.backward(torch.ones_like(ref) * (rank + 1))
+    g_ref = local.grad.clone()
+    local.grad = None
+    reshard_ops.enable_fused_all_to_all(None, SymmContext(None, device=dev))
+    before = native.launch_count()
+    out = reshard_ops.reshard("RS->SR", local, None)
+    assert native.launch_count() == before + 1
+    assert torch.equal(out, ref) and torch.equal(out, full.chunk(world, 1)[rank])
+    out.backward(torch.ones_like(out) * (rank + 1))              # the backward is SR->RS, fused too
+    assert torch.equal(local.grad, g_ref)
+    assert native.ops().device_status() == 0
+    dist.barrier()
+
+
+@pytest.mark.multigpu
+def test_fused_all_to_all_two_gpus():
+    from dist_utils import run_distributed
+
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    run_distributed(_a2a_worker, 2, backend="nccl")
