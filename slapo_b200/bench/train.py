@@ -184,6 +184,10 @@ def build_engine(args, world, device):
         build_kwargs["num_micro_batches"] = args.micro_batches
     if not on_gpu:
         build_kwargs["init_weights"] = False
+    elif hasattr(model, "_init_weights"):
+        # the model's own initialiser also after pipeline partitioning (the split graph
+        # module has lost the method, and PyTorch's per-layer defaults are another scheme)
+        build_kwargs["init_weights"] = model._init_weights
     engine, _ = slapo.build(sch, **build_kwargs)
     return engine, spec, mesh, dp
 

@@ -273,12 +273,11 @@ __global__ void __launch_bounds__(256) peer_all_to_all_kernel(A2AParams p) {
 }
 
 // ------------------------------------------------------------------------ //
+// clock64() ticks at the SM clock; its maximum (1.965 GHz on B200) turns seconds into a
+// cycle budget.  A constant on purpose: querying the clock-rate attribute costs about a
+// millisecond per call, which is more than the kernels these budgets guard.
 static long long dp_wait_cycles(double seconds) {
-  int dev = 0, khz = 0;
-  cudaGetDevice(&dev);
-  cudaDeviceGetAttribute(&khz, cudaDevAttrClockRate, dev);
-  if (khz <= 0) khz = 1900000;
-  return static_cast<long long>(seconds * 1e3 * khz);
+  return static_cast<long long>(seconds * 1.965e9);
 }
 
 static int dp_grid(int64_t n_vec) {

@@ -154,7 +154,7 @@ def generate_pipeline_partition(sch):
     split = split_module(root, root, lambda n: stage_of[n], keep_original_order=True)
     from ..schedule import create_schedule
 
-    new_sch = create_schedule(split, group=sch.group)
+    new_sch = create_schedule(split, group=sch.group_arg)
     new_sch.metadata.primitives = sch.metadata.primitives
     new_sch.metadata.param_tags = sch.metadata.param_tags
     for name, sub in new_sch.child.items():

@@ -199,7 +199,7 @@ def _module_replace(sch, new_mod: nn.Module):
         return
     transfer_hooks(sch.mod, new_mod)
     new_mod.train(sch.mod.training)  # a fresh module defaults to training mode
-    new_sch = create_schedule(new_mod, sch.name, sch.path, sch.parent, sch.group)
+    new_sch = create_schedule(new_mod, sch.name, sch.path, sch.parent, sch.group_arg)
     sch.mod = new_mod
     sch.child = new_sch.child
     for child in sch.child.values():
@@ -213,7 +213,7 @@ def _resync_children(sch):
     schedules for new ones, keep the untouched ones (they carry metadata)."""
     from ..schedule import create_schedule
 
-    fresh = create_schedule(sch.mod, sch.name, sch.path, sch.parent, sch.group)
+    fresh = create_schedule(sch.mod, sch.name, sch.path, sch.parent, sch.group_arg)
     merged = {}
     for key, child in fresh.child.items():
         old = sch.child.get(key)

@@ -50,6 +50,9 @@ class ScheduleMetadata:
 class Schedule:
     def __init__(self, mod: nn.Module, name: str = "", path: str = "",
                  parent: Optional["Schedule"] = None, group=None):
+        # what to hand to create_schedule() to get a schedule over the same ranks again
+        # (``group`` itself becomes None for the "no tensor parallelism" sentinel)
+        self.group_arg = group
         if group is False:  # explicit "no tensor parallelism" inside a distributed job
             self.world_size, self.rank, group = 1, 0, None
         elif dist.is_available() and dist.is_initialized():

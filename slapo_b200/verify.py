@@ -129,7 +129,7 @@ class Verify(ContextDecorator):
         ref_out, ref_grads = self._run(orig_model, inputs)
 
         # 2. scheduled copy with the matching slices of the same weights
-        new_sch = create_schedule(copy.deepcopy(sch.mod), group=sch.group)
+        new_sch = create_schedule(copy.deepcopy(sch.mod), group=sch.group_arg)
         new_sch.metadata = copy.copy(sch.metadata)
         rank = sch.rank
 

@@ -122,3 +122,27 @@ def test_decoder_families_partition_into_equivalent_stages():
 def test_t5_encoder_boundary_is_a_stage_boundary():
     # one cut inside the encoder, one inside the decoder, plus the encoder end: 4 stages
     _zoo_pipeline("t5-base", 4)
+
+
+def _sentinel_worker(rank, world):
+    """group=False ("no tensor parallelism") must survive module replacement and
+    pipeline partitioning inside a distributed job."""
+    from slapo_b200.pipeline import generate_pipeline_partition
+
+    cfg = _tiny_cfg()
+    model = BertForMaskedLM(cfg)
+    sch = slapo.create_schedule(model, group=False)
+    assert sch.world_size == 1 and sch["bert.encoder.layer.0"].world_size == 1
+    sch["bert.encoder.layer.0.output.dense"].replace(nn.Linear(64, 32))
+    assert sch["bert.encoder.layer.0.output.dense"].world_size == 1
+    sch.trace_until("bert.encoder")
+    sch["bert.encoder.layer.1"].cut_pipeline_stage()
+    pipe = generate_pipeline_partition(sch)
+    assert pipe.world_size == 1
+    assert all(s.world_size == 1 for _, s in pipe.named_schedules())
+    # a default schedule in the same job does span the ranks
+    assert slapo.create_schedule(nn.Linear(4, 4)).world_size == world
+
+
+def test_no_tp_sentinel_survives_replace_and_partition():
+    run_distributed(_sentinel_worker, 2)
