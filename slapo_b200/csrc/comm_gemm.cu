@@ -156,6 +156,89 @@ __device__ __forceinline__ void tile_coords(int t, int tiles_n, int blocks_per_o
   m_blk = mb;
 }
 
+// Reduction phase of GEMM -> reduce-scatter / all-reduce: this rank sums its rows of every
+// rank's partial-product buffer (16-byte coalesced peer loads), adds bias / activation and
+// writes the result (to every rank's output for all-reduce).  W = group size known at compile
+// time (0 = generic), U = row vectors per thread per iteration: W * U loads are in flight per
+// thread before the first is used, which is what hides the NVLink round trip.
+template <int W, int U>
+__device__ __forceinline__ void reduce_rows(const CommGemmParams& p, int rows_per_rank) {
+  constexpr int kW = W > 0 ? W : kMaxRanks;
+  const int world = W > 0 ? W : p.world;
+  const int64_t vec_per_row = p.N / 8;
+  const int64_t n_vec = static_cast<int64_t>(rows_per_rank) * vec_per_row;
+  // this rank's rows inside every source's partial buffer [M, N]
+  const int64_t my_off = static_cast<int64_t>(p.rank) * rows_per_rank * p.N;
+  const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
+  for (int64_t i0 = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i0 < n_vec;
+       i0 += stride * U) {
+    uint4 raw[U][kW];
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const int64_t e = (i0 + u * stride) * 8;
+#pragma unroll
+      for (int r = 0; r < kW; ++r) {
+        if (r < world && i0 + u * stride < n_vec) {
+          // start with the next rank so that the peers' links share the load
+          int src = p.rank + 1 + r;
+          if (src >= world) src -= world;
+          raw[u][r] = *reinterpret_cast<const uint4*>(
+              static_cast<const uint8_t*>(p.peer_recv[src]) + (my_off + e) * 2);
+        }
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const int64_t i = i0 + u * stride;
+      if (i >= n_vec) break;
+      const int64_t e = i * 8;
+      float acc8[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+      for (int r = 0; r < kW; ++r) {
+        if (r < world) {
+          float v[8];
+          if (p.bf16) {
+            const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw[u][r]);
+#pragma unroll
+            for (int k = 0; k < 4; ++k) { float2 f = __bfloat1622float2(h[k]); v[2 * k] = f.x; v[2 * k + 1] = f.y; }
+          } else {
+            const __half2* h = reinterpret_cast<const __half2*>(&raw[u][r]);
+#pragma unroll
+            for (int k = 0; k < 4; ++k) { float2 f = __half22float2(h[k]); v[2 * k] = f.x; v[2 * k + 1] = f.y; }
+          }
+#pragma unroll
+          for (int k = 0; k < 8; ++k) acc8[k] += v[k];
+        }
+      }
+      const int col = static_cast<int>(e % p.N);
+      if (p.bias != nullptr) {
+#pragma unroll
+        for (int k = 0; k < 8; ++k) acc8[k] += cload(p.bias, col + k, p.bf16);
+      }
+      if (p.act >= 0) {
+#pragma unroll
+        for (int k = 0; k < 8; ++k) acc8[k] = act_fwd(acc8[k], p.act);
+      }
+      const int64_t lrow = e / p.N;
+      if (p.mode == kModeReduceScatter) {
+        void* o = static_cast<uint8_t*>(p.out) + (lrow * p.ldo + col) * 2;
+        if (p.bf16) Vec8<__nv_bfloat16>::store(static_cast<__nv_bfloat16*>(o), acc8);
+        else Vec8<__half>::store(static_cast<__half*>(o), acc8);
+      } else {
+        // all-reduce: the reduced rows go to every rank's output buffer
+        const int64_t grow = static_cast<int64_t>(p.rank) * rows_per_rank + lrow;
+        for (int r = 0; r < world; ++r) {
+          int peer = p.rank + r;
+          if (peer >= world) peer -= world;
+          void* o = static_cast<uint8_t*>(p.peer_out[peer]) + (grow * p.ldo + col) * 2;
+          if (p.bf16) Vec8<__nv_bfloat16>::store(static_cast<__nv_bfloat16*>(o), acc8);
+          else Vec8<__half>::store(static_cast<__half*>(o), acc8);
+        }
+      }
+    }
+  }
+}
+
 template <int BN, int STAGES, bool A_MN, bool B_MN>
 __global__ void __launch_bounds__(320, 1)
 comm_gemm_kernel(const __grid_constant__ SegMaps maps_a, const __grid_constant__ SegMaps maps_b,
@@ -471,65 +554,11 @@ comm_gemm_kernel(const __grid_constant__ SegMaps maps_a, const __grid_constant__
     }
     __syncthreads();
     if (s_ok) {
-      const int64_t vec_per_row = p.N / 8;
-      const int64_t n_vec = static_cast<int64_t>(rows_per_rank) * vec_per_row;
-      // this rank's rows inside every source's partial buffer [M, N]
-      const int64_t my_off = static_cast<int64_t>(p.rank) * rows_per_rank * p.N;
-      for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < n_vec;
-           i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
-        const int64_t e = i * 8;
-        float acc8[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-        uint4 raw[kMaxRanks];
-#pragma unroll
-        for (int r = 0; r < kMaxRanks; ++r) {
-          if (r < p.world) {
-            // start with the next rank so that the peers' links share the load
-            const int src = (p.rank + 1 + r) % p.world;
-            raw[r] = *reinterpret_cast<const uint4*>(
-                static_cast<const uint8_t*>(p.peer_recv[src]) + (my_off + e) * 2);
-          }
-        }
-#pragma unroll
-        for (int r = 0; r < kMaxRanks; ++r) {
-          if (r < p.world) {
-            float v[8];
-            if (p.bf16) {
-              const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw[r]);
-#pragma unroll
-              for (int k = 0; k < 4; ++k) { float2 f = __bfloat1622float2(h[k]); v[2 * k] = f.x; v[2 * k + 1] = f.y; }
-            } else {
-              const __half2* h = reinterpret_cast<const __half2*>(&raw[r]);
-#pragma unroll
-              for (int k = 0; k < 4; ++k) { float2 f = __half22float2(h[k]); v[2 * k] = f.x; v[2 * k + 1] = f.y; }
-            }
-#pragma unroll
-            for (int k = 0; k < 8; ++k) acc8[k] += v[k];
-          }
-        }
-        const int col = static_cast<int>(e % p.N);
-        if (p.bias != nullptr) {
-#pragma unroll
-          for (int k = 0; k < 8; ++k) acc8[k] += cload(p.bias, col + k, p.bf16);
-        }
-        if (p.act >= 0) {
-#pragma unroll
-          for (int k = 0; k < 8; ++k) acc8[k] = act_fwd(acc8[k], p.act);
-        }
-        const int64_t lrow = e / p.N;
-        if (p.mode == kModeReduceScatter) {
-          void* o = static_cast<uint8_t*>(p.out) + (lrow * p.ldo + col) * 2;
-          if (p.bf16) Vec8<__nv_bfloat16>::store(static_cast<__nv_bfloat16*>(o), acc8);
-          else Vec8<__half>::store(static_cast<__half*>(o), acc8);
-        } else {
-          // all-reduce: the reduced rows go to every rank's output buffer
-          const int64_t grow = static_cast<int64_t>(p.rank) * rows_per_rank + lrow;
-          for (int r = 0; r < p.world; ++r) {
-            const int peer = (p.rank + r) % p.world;
-            void* o = static_cast<uint8_t*>(p.peer_out[peer]) + (grow * p.ldo + col) * 2;
-            if (p.bf16) Vec8<__nv_bfloat16>::store(static_cast<__nv_bfloat16*>(o), acc8);
-            else Vec8<__half>::store(static_cast<__half*>(o), acc8);
-          }
-        }
+      switch (p.world) {
+        case 2: reduce_rows<2, 4>(p, rows_per_rank); break;
+        case 4: reduce_rows<4, 2>(p, rows_per_rank); break;
+        case 8: reduce_rows<8, 1>(p, rows_per_rank); break;
+        default: reduce_rows<0, 1>(p, rows_per_rank); break;
       }
       if (p.mode == kModeAllReduce) {
         // close the all-gather half: count CTAs, the last one releases done2
