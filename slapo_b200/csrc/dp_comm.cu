@@ -273,6 +273,63 @@ __global__ void __launch_bounds__(256) peer_all_to_all_kernel(A2AParams p) {
 }
 
 // ------------------------------------------------------------------------ //
+// ------------------------------------------------------------------------ //
+// Vocabulary-parallel embedding forward without an all-reduce: exactly one rank owns the
+// row of each token id, so that rank stores the row straight into EVERY rank's output
+// (peer stores); ranks that do not own an id write nothing.  One warp per token.  The
+// last CTA to finish exchanges "sent" flags with the peers (bounded wait): when the kernel
+// ends this rank's output holds every row.
+struct VocabEmbedParams {
+  const int64_t* ids;
+  const void* weight;           // [vocab_local, hidden] 16-bit
+  void* out[kDpMaxRanks];       // every rank's [tokens, hidden] output buffer
+  int* flags[kDpMaxRanks];
+  int world, rank, epoch;
+  int64_t tokens;
+  int hidden_vecs;              // hidden * 2 / 16
+  int64_t vocab_lo, vocab_local;
+  unsigned int* cta_counter;
+  int* status;
+  long long wait_cycles;
+};
+
+__global__ void __launch_bounds__(256) vocab_embed_fwd_kernel(VocabEmbedParams p) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int64_t warps = static_cast<int64_t>(gridDim.x) * (blockDim.x >> 5);
+  for (int64_t t = static_cast<int64_t>(blockIdx.x) * (blockDim.x >> 5) + warp; t < p.tokens;
+       t += warps) {
+    const int64_t id = p.ids[t] - p.vocab_lo;
+    if (id < 0 || id >= p.vocab_local) continue;   // another rank owns this row
+    const uint4* src = static_cast<const uint4*>(p.weight) + id * p.hidden_vecs;
+    for (int v = lane; v < p.hidden_vecs; v += 32) {
+      const uint4 val = src[v];
+#pragma unroll
+      for (int r = 0; r < kDpMaxRanks; ++r) {
+        if (r < p.world) {
+          int dst = p.rank + r;
+          if (dst >= p.world) dst -= p.world;
+          static_cast<uint4*>(p.out[dst])[t * p.hidden_vecs + v] = val;
+        }
+      }
+    }
+  }
+  __shared__ int s_last;
+  __threadfence_system();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const unsigned int done = atomicAdd(p.cta_counter, 1u);
+    s_last = (done == gridDim.x - 1) ? 1 : 0;
+  }
+  __syncthreads();
+  if (!s_last) return;
+  if (threadIdx.x == 0) *p.cta_counter = 0u;
+  if (threadIdx.x < p.world && threadIdx.x != p.rank) {
+    __threadfence_system();
+    dp_st_release(p.flags[threadIdx.x] + p.rank, p.epoch);
+    if (!dp_wait(p.flags[p.rank] + threadIdx.x, p.epoch, p.wait_cycles)) atomicExch(p.status, 8);
+  }
+}
+
 // clock64() ticks at the SM clock; its maximum (1.965 GHz on B200) turns seconds into a
 // cycle budget.  A constant on purpose: querying the clock-rate attribute costs about a
 // millisecond per call, which is more than the kernels these budgets guard.
@@ -372,6 +429,30 @@ int launch_peer_all_to_all(const void* src, void* const* dst_ptrs, int* const* f
   const int64_t total = static_cast<int64_t>(outer) * rows * p.row_vecs * world;
   count_launch();
   peer_all_to_all_kernel<<<dp_grid(total), 256, 0, stream>>>(p);
+  return cudaGetLastError() == cudaSuccess ? 0 : 4;
+}
+
+int launch_vocab_embed_fwd(const int64_t* ids, const void* weight, void* const* out_ptrs,
+                           int* const* flag_ptrs, int world, int rank, int epoch, int64_t tokens,
+                           int hidden, int64_t vocab_lo, int64_t vocab_local,
+                           unsigned int* cta_counter, int* status, double wait_seconds,
+                           cudaStream_t stream) {
+  if (world < 1 || world > kDpMaxRanks || hidden % 8 != 0) return 1;
+  VocabEmbedParams p;
+  p.ids = ids; p.weight = weight;
+  for (int r = 0; r < kDpMaxRanks; ++r) {
+    p.out[r] = r < world ? out_ptrs[r] : nullptr;
+    p.flags[r] = r < world ? flag_ptrs[r] : nullptr;
+  }
+  p.world = world; p.rank = rank; p.epoch = epoch; p.tokens = tokens;
+  p.hidden_vecs = hidden / 8; p.vocab_lo = vocab_lo; p.vocab_local = vocab_local;
+  p.cta_counter = cta_counter; p.status = status; p.wait_cycles = dp_wait_cycles(wait_seconds);
+  int64_t blocks = (tokens + 7) / 8;
+  const int64_t cap = static_cast<int64_t>(sm_count()) * 8;
+  if (blocks > cap) blocks = cap;
+  if (blocks < 1) blocks = 1;
+  count_launch();
+  vocab_embed_fwd_kernel<<<static_cast<int>(blocks), 256, 0, stream>>>(p);
   return cudaGetLastError() == cudaSuccess ? 0 : 4;
 }
 

@@ -86,6 +86,13 @@ int launch_peer_all_to_all(const void* src, void* const* dst_ptrs, int* const* f
                            unsigned int* cta_counter, int* status, double wait_seconds,
                            cudaStream_t stream);
 
+// Vocabulary-parallel embedding forward by peer stores (16-bit weights, hidden % 8 == 0).
+int launch_vocab_embed_fwd(const int64_t* ids, const void* weight, void* const* out_ptrs,
+                           int* const* flag_ptrs, int world, int rank, int epoch, int64_t tokens,
+                           int hidden, int64_t vocab_lo, int64_t vocab_local,
+                           unsigned int* cta_counter, int* status, double wait_seconds,
+                           cudaStream_t stream);
+
 }  // namespace slapo
 
 #include "common_host.h"

@@ -95,6 +95,8 @@ def shard_word_embedding(sch, vocab_size, sequence_parallel=False, sp_axis=1):
     hooks = VocabParallelEmbeddingHooks(sch, sequence_parallel, sp_axis)
     sch.sync("fwd_pre", hooks.pre)
     sch.sync("fwd_post", hooks.post)
+    # lets the lowering pass recognise the pair and swap in the peer-store kernel
+    sch.mod._vocab_parallel_hooks = hooks
 
 
 def checkpoint_layers(sch, layer_paths, ckpt_ratio, method="uniform", order_args_fn=None):

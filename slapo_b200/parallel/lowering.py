@@ -40,11 +40,37 @@ def _pop_sync_hook(mod, op, **match):
     return None
 
 
+def _lower_vocab_embedding(sub, ctx) -> bool:
+    """``shard_word_embedding`` (masked lookup + all-reduce hooks) -> the peer-store kernel.
+    Only the all-reduce form on 16-bit weights; the sequence-parallel form keeps its hooks."""
+    import torch
+
+    from ..ops.embedding import FusedVocabParallelEmbedding
+
+    mod = sub.mod
+    hooks = getattr(mod, "_vocab_parallel_hooks", None)
+    if hooks is None or hooks.sequence_parallel or mod.weight.is_meta:
+        return False
+    if mod.weight.dtype not in (torch.bfloat16, torch.float16) or mod.embedding_dim % 8:
+        return False
+    for table in (mod._forward_pre_hooks, mod._forward_hooks):
+        for key, fn in list(table.items()):
+            if getattr(fn, "__self__", None) is hooks:
+                del table[key]
+    sub.replace(FusedVocabParallelEmbedding.from_sharded(mod, sub.rank, ctx))
+    return True
+
+
 def lower_fused_tp(sch, ctx) -> int:
     """Attach fused plans below schedule ``sch``; returns how many Linears changed."""
     changed = 0
     for _, sub in list(sch.named_schedules()):
         mod = sub.mod
+        if isinstance(mod, nn.Embedding):
+            if _lower_vocab_embedding(sub, ctx):
+                logger.info("lowered %s to the peer-store vocabulary-parallel embedding",
+                            sub.path, ranks=0)
+            continue
         if not isinstance(mod, nn.Linear):
             continue
         pre_ag = _pop_sync_hook(mod, "all_gather", axis=(0, 0),

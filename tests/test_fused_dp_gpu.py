@@ -220,3 +220,45 @@ def test_fused_all_to_all_two_gpus():
     if torch.cuda.device_count() < 2:
         pytest.skip("needs 2 GPUs")
     run_distributed(_a2a_worker, 2, backend="nccl")
+
+
+@pytest.mark.parametrize("world", [2, 4])
+def test_vocab_parallel_embedding_emulated_ranks(world):
+    """Every emulated rank stores the rows it owns into all ranks' outputs; afterwards each
+    output equals the plain embedding lookup, and the backward gives each rank the gradient of
+    its vocabulary slice."""
+    from slapo_b200.ops import native
+    from slapo_b200.ops.embedding import FusedVocabParallelEmbedding
+    from slapo_b200.parallel.symm import LocalSymmContext
+
+    torch.manual_seed(4)
+    vocab, hidden = 64 * world, 256
+    table = torch.randn(vocab, hidden, device="cuda").bfloat16()
+    ids = torch.randint(0, vocab, (3, 50), device="cuda")
+    ids[0, :4] = torch.tensor([0, vocab - 1, vocab // world, vocab // world - 1])   # shard edges
+    want = table[ids]
+    ctx = LocalSymmContext(world)
+    mods = []
+    for r in range(world):
+        w = torch.nn.Parameter(table.chunk(world)[r].clone())
+        mods.append(FusedVocabParallelEmbedding(w, r * (vocab // world), ctx.as_rank(r)))
+    outs = []
+    for r in range(world):
+        ctx.as_rank(r)
+        ctx.epoch = 0
+        mods[r].flag_buf.view(torch.int32, (8,)).fill_(1)
+        outs.append(mods[r](ids))           # a clone taken right after this rank's stores
+    torch.cuda.synchronize()
+    assert native.ops().device_status() == 0
+    # the symmetric output of every rank is complete once all ranks have run
+    for r in range(world):
+        full = ctx.rank_view("vocab_embed_out_0", r, torch.bfloat16, (ids.numel(), hidden))
+        assert torch.equal(full.view(3, 50, hidden), want), f"rank {r}"
+    # backward: only the owned rows receive gradient
+    g = torch.randn(3, 50, hidden, device="cuda").bfloat16()
+    ref = torch.zeros(vocab, hidden, device="cuda")
+    ref.index_add_(0, ids.reshape(-1), g.reshape(-1, hidden).float())
+    for r in range(world):
+        outs[r].backward(g)
+        torch.testing.assert_close(mods[r].weight.grad.float(), ref.chunk(world)[r],
+                                   rtol=2e-2, atol=2e-2)
