@@ -56,6 +56,9 @@ def parse_args():
     ap.add_argument("--parallelism", default="tp", choices=["tp", "dp"])
     ap.add_argument("--no-sequence-parallel", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--no-cuda-graph", action="store_true",
+                    help="single-GPU runs replay the whole step from one CUDA graph; this flag "
+                         "launches the kernels one by one instead")
     ap.add_argument("--no-fused-dp", action="store_true",
                     help="data parallelism through NCCL instead of the peer-memory kernels")
     ap.add_argument("--profile", action="store_true",
@@ -223,8 +226,21 @@ def run_native(args):
     ids, labels = make_batch(vocab, local_batch, args.seq, 1234 + dp_rank, device)
     global_batch = local_batch * dp
 
+    graphed = None
+    if world == 1 and not args.no_cuda_graph and not args.profile:
+        try:
+            graphed = engine.capture_step(ids, labels=labels, warmup=max(args.warmup, 3))
+        except Exception as err:  # fall back to launching kernel by kernel
+            print(f"# CUDA graph capture failed, running eagerly: {type(err).__name__}: {err}",
+                  file=sys.stderr)
+            graphed = None
+            torch.cuda.synchronize()
+
     def step(_i):
-        engine.train_batch(ids, labels=labels)
+        if graphed is not None:
+            graphed(ids, labels=labels)
+        else:
+            engine.train_batch(ids, labels=labels)
 
     for i in range(args.warmup):
         step(i)
@@ -233,6 +249,8 @@ def run_native(args):
     launches0 = native.launch_count()
     ms = timed_loop(step, args.steps, device, world)
     launches = native.launch_count() - launches0
+    if graphed is not None:   # kernels inside the replayed graph are not counted by the host
+        launches = graphed.kernels_per_step * args.steps
     clocks = sampler.finish()
     value = global_batch * args.steps / (ms / 1e3)
 
@@ -255,7 +273,8 @@ def run_native(args):
             hi, hl = host[i % 2]
             di = hi.to(device, non_blocking=True)
             dl = hl.to(device, non_blocking=True)
-            loss = engine.train_batch(di, labels=dl)
+            loss = graphed(di, labels=dl) if graphed is not None else \
+                engine.train_batch(di, labels=dl)
             return float(loss.item())  # device -> host read of the result
 
         e2e_step(0)
@@ -275,6 +294,7 @@ def run_native(args):
                        "l2_policy": "per-step working set (weights+activations, >10 GB) "
                                     "exceeds the 126 MB L2, nothing survives between steps"},
             "clocks": clocks, "e2e": e2e, "gpu_launches": int(launches),
+            "cuda_graph": graphed is not None,
             "max_mem_mb": torch.cuda.max_memory_allocated() / 2**20,
         }), flush=True)
     if world > 1:

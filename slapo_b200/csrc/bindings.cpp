@@ -235,7 +235,7 @@ std::tuple<Tensor, Tensor, Tensor, Tensor, Tensor> dropout_add_ln_bwd(
 void fused_adamw(Tensor param, const Tensor& grad, Tensor master, Tensor exp_avg,
                  Tensor exp_avg_sq, const Tensor& decay_mask, const Tensor& grad_scale, double lr,
                  double beta1, double beta2, double eps, double weight_decay, double bc1,
-                 double bc2) {
+                 double bc2, const optional<Tensor>& hyper) {
   check_cuda_contig(param, "param");
   check_cuda_contig(grad, "grad");
   check_cuda_contig(master, "master");
@@ -251,7 +251,9 @@ void fused_adamw(Tensor param, const Tensor& grad, Tensor master, Tensor exp_avg
                             static_cast<float>(lr), static_cast<float>(beta1),
                             static_cast<float>(beta2), static_cast<float>(eps),
                             static_cast<float>(weight_decay), static_cast<float>(bc1),
-                            static_cast<float>(bc2), dtype_code(param), cur_stream());
+                            static_cast<float>(bc2), dtype_code(param), cur_stream(),
+                            hyper.has_value() && hyper->defined() ? hyper->data_ptr<float>()
+                                                                  : nullptr);
 }
 
 }  // namespace
@@ -279,7 +281,7 @@ TORCH_LIBRARY(slapo_b200, m) {
         &dropout_add_ln_fwd);
   m.def("dropout_add_ln_bwd(Tensor gy, Tensor? gz, Tensor z, Tensor gamma, Tensor mean, Tensor rstd, float p, Tensor? rng, bool want_dbias) -> (Tensor, Tensor, Tensor, Tensor, Tensor)",
         &dropout_add_ln_bwd);
-  m.def("fused_adamw(Tensor(a!) param, Tensor grad, Tensor(b!) master, Tensor(c!) exp_avg, Tensor(d!) exp_avg_sq, Tensor decay_mask, Tensor grad_scale, float lr, float beta1, float beta2, float eps, float weight_decay, float bc1, float bc2) -> ()",
+  m.def("fused_adamw(Tensor(a!) param, Tensor grad, Tensor(b!) master, Tensor(c!) exp_avg, Tensor(d!) exp_avg_sq, Tensor decay_mask, Tensor grad_scale, float lr, float beta1, float beta2, float eps, float weight_decay, float bc1, float bc2, Tensor? hyper=None) -> ()",
         &fused_adamw);
   register_gemm_ops(m);
   register_attn_ops(m);

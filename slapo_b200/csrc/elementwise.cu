@@ -216,7 +216,11 @@ __global__ void __launch_bounds__(256) fused_adamw_kernel(
     T* __restrict__ param, const T* __restrict__ grad, float* __restrict__ master,
     float* __restrict__ exp_avg, float* __restrict__ exp_avg_sq,
     const uint8_t* __restrict__ decay_mask, const float* __restrict__ grad_scale, int64_t n_vec,
-    float lr, float beta1, float beta2, float eps, float weight_decay, float bc1, float bc2) {
+    float lr, float beta1, float beta2, float eps, float weight_decay, float bc1, float bc2,
+    const float* __restrict__ hyper) {
+  // hyper = {lr, bias correction 1, bias correction 2} in device memory: the values that change
+  // from step to step, so that a captured CUDA graph of the step stays valid
+  if (hyper != nullptr) { lr = hyper[0]; bc1 = hyper[1]; bc2 = hyper[2]; }
   const float gs = grad_scale != nullptr ? *grad_scale : 1.f;
   const float inv_bc1 = 1.f / bc1, inv_sqrt_bc2 = rsqrtf(bc2);
   const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
@@ -330,13 +334,13 @@ void launch_fused_adamw(void* param, const void* grad, float* master, float* exp
                         float* exp_avg_sq, const uint8_t* decay_mask, const float* grad_scale,
                         int64_t n, float lr, float beta1, float beta2, float eps,
                         float weight_decay, float bc1, float bc2, int dtype,
-                        cudaStream_t stream) {
+                        cudaStream_t stream, const float* hyper) {
   const int64_t n_vec = n / kVec;
   if (n_vec == 0) return;
   count_launch();
   DISPATCH_DTYPE(dtype, (fused_adamw_kernel<T><<<flat_grid(n_vec), 256, 0, stream>>>(
       static_cast<T*>(param), static_cast<const T*>(grad), master, exp_avg, exp_avg_sq, decay_mask,
-      grad_scale, n_vec, lr, beta1, beta2, eps, weight_decay, bc1, bc2)));
+      grad_scale, n_vec, lr, beta1, beta2, eps, weight_decay, bc1, bc2, hyper)));
 }
 
 }  // namespace slapo

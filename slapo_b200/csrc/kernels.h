@@ -26,7 +26,8 @@ void launch_colsum_finalize(const float* partial, void* out, int chunks, int col
 void launch_fused_adamw(void* param, const void* grad, float* master, float* exp_avg,
                         float* exp_avg_sq, const uint8_t* decay_mask, const float* grad_scale,
                         int64_t n, float lr, float beta1, float beta2, float eps,
-                        float weight_decay, float bc1, float bc2, int dtype, cudaStream_t stream);
+                        float weight_decay, float bc1, float bc2, int dtype, cudaStream_t stream,
+                        const float* hyper = nullptr);
 
 // C[M,N] = act(A B^T + bias); a_mn / b_mn select M/N-major operands (see gemm.cu).
 // Returns 0 on success, >0 when the launch was refused on the host.

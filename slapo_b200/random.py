@@ -32,15 +32,28 @@ def _use_cuda() -> bool:
     return torch.cuda.is_available()
 
 
+def _capturing() -> bool:
+    return _use_cuda() and torch.cuda.is_current_stream_capturing()
+
+
 def _get_state():
-    return torch.cuda.get_rng_state() if _use_cuda() else torch.get_rng_state()
+    """State of the device generator (CPU generator without CUDA).  While a CUDA graph is
+    being captured the ordinary state cannot be read; the graph-safe handle (which carries the
+    offset inside the graph) is returned instead and ``_set_state`` accepts it back."""
+    if not _use_cuda():
+        return torch.get_rng_state()
+    if _capturing():
+        return torch.cuda.default_generators[torch.cuda.current_device()].graphsafe_get_state()
+    return torch.cuda.get_rng_state()
 
 
 def _set_state(state):
-    if _use_cuda():
-        torch.cuda.set_rng_state(state)
-    else:
+    if not _use_cuda():
         torch.set_rng_state(state)
+    elif isinstance(state, torch.Generator):
+        torch.cuda.default_generators[torch.cuda.current_device()].graphsafe_set_state(state)
+    else:
+        torch.cuda.set_rng_state(state)
 
 
 def _manual_seed(seed):
