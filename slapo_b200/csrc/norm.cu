@@ -10,8 +10,6 @@
 #include "common.cuh"
 #include "kernels.h"
 
-#include <stdlib.h>
-
 namespace slapo {
 
 // Threads of a CTA are organised as RG row groups of WPR warps; each group
@@ -304,11 +302,9 @@ struct LnShape { int vpl; int wpr; int rg; };
 static LnShape pick_shape(int cols) {
   const int vecs = cols / 8;
   if (vecs <= 32) return {1, 1, 4};
-  if (vecs > 64 && vecs <= 128) {
-    static const char* knob = getenv("SLAPO_B200_LN_SHAPE");
-    if (knob != nullptr && knob[0] == 'a') return {4, 1, 8};   // one warp per row
-    if (knob != nullptr && knob[0] == 'b') return {2, 2, 8};   // two warps per row
-  }
+  // for 1024 columns one warp per row (4 vectors per lane) and two warps per row were
+  // measured slower (fwd 341 / 199 us, bwd 457 / 309 us on 65536 rows) than four warps per row
+  // with four row groups per CTA (129 / 264 us): registers, not barriers, limit the latter
   if (vecs <= 128) return {1, 4, 4};
   if (vecs <= 256) return {2, 4, 4};
   if (vecs <= 512) return {1, 16, 1};
@@ -329,13 +325,7 @@ int ln_bwd_grid(int rows, int cols) {
 }
 
 #define LN_SHAPE_SWITCH(s, ...)                                                     \
-  if (s.wpr == 1 && s.vpl == 4) {                                                   \
-    constexpr int WPR = 1, RG = 8, VPL = 4;                                         \
-    __VA_ARGS__;                                                                    \
-  } else if (s.wpr == 2) {                                                          \
-    constexpr int WPR = 2, RG = 8, VPL = 2;                                         \
-    __VA_ARGS__;                                                                    \
-  } else if (s.wpr == 1) {                                                          \
+  if (s.wpr == 1) {                                                          \
     constexpr int WPR = 1, RG = 4, VPL = 1;                                         \
     __VA_ARGS__;                                                                    \
   } else if (s.wpr == 4) {                                                          \

@@ -308,31 +308,8 @@ class TrainEngine:
     def backward(self, loss):
         if self.cfg.grad_accum_steps > 1:
             loss = loss / self.cfg.grad_accum_steps
-        direct = self._direct_grads()
-        if direct:
-            # With ``p.grad`` unset autograd hands over the gradient tensor it computed
-            # instead of adding it into the (zeroed) flat view - one fused multi-tensor copy
-            # afterwards replaces one read-modify-write kernel per parameter.
-            for p in self.params:
-                p.grad = None
         loss.backward()
-        if direct:
-            srcs, dsts = [], []
-            for p, (off, n, _) in zip(self.params, self.param_slices):
-                view = self.flat_grad[off:off + n].view(p.shape)
-                if p.grad is not None:
-                    srcs.append(p.grad)
-                    dsts.append(view)
-                p.grad = view
-            if srcs:
-                torch._foreach_copy_(dsts, srcs)
         self.micro_step += 1
-
-    def _direct_grads(self):
-        """No gradient accumulation and no per-bucket hooks waiting for ``p.grad`` views:
-        single data-parallel rank, one micro-batch per step, CUDA."""
-        return (self.dp_size == 1 and self.cfg.grad_accum_steps == 1
-                and self.device.type == "cuda" and not self.sp_sync_params)
 
     def _own_grad(self):
         """This rank's reduced gradient slice as one flat view list."""
