@@ -90,7 +90,9 @@ def build(verbose: bool = False, force: bool = False) -> str:
                 print(cmd)
                 print(out)
         ptxas = os.path.join(OBJ_DIR, "ptxas.log")
-        with open(ptxas, "a") as fh:
+        # append, but start over once the log has grown past a few MB
+        mode = "a" if os.path.exists(ptxas) and os.path.getsize(ptxas) < 4 * 2**20 else "w"
+        with open(ptxas, mode) as fh:
             for cmd, out in log:
                 fh.write(cmd + "\n" + out + "\n")
     if jobs or force or _newer(objs, OUT):

@@ -7,9 +7,11 @@ collective" pairs that ``shard`` + ``sync`` describe:
 op                 forward                     backward
 =================  ==========================  =====================================
 ``ag_linear``      Y = all_gather(Xs) W^T      dXs = reduce_scatter(dY W)   (fused)
-                   (gather inside the GEMM)    dW  = dY^T all_gather(Xs)    (fused)
+                   (gather inside the GEMM)    dW  = dY^T X, X = the tokens the forward
+                                               kernel already gathered into local memory
 ``rs_linear``      Ys = reduce_scatter(X W^T)  dX  = all_gather(dYs) W      (fused)
-                   (+ bias after reduction)    dW  = all_gather(dYs)^T X    (fused)
+                   (+ bias after reduction)    dW  = dY^T X, dY = what the dgrad kernel
+                                               gathered (library split-K GEMM, no 2nd gather)
 ``ar_linear``      Y = all_reduce(X W^T)       dX  = dY W,  dW = dY^T X     (local)
 =================  ==========================  =====================================
 
@@ -109,9 +111,15 @@ def peer_gather(ctx, shard, name):
 
 
 # ---------------------------------------------------------------------- #
-def ag_gemm(ctx, x_shard, w, bias=None, act=-1, name="ag_in", staged=None, b_mn=False):
+def ag_gemm(ctx, x_shard, w, bias=None, act=-1, name="ag_in", staged=None, b_mn=False,
+            keep_gathered=False):
     """``all_gather(x_shard) @ w.T`` with the gather inside the GEMM
-    (``b_mn``: ``w`` is ``[K, N]`` and the product is ``all_gather(x) @ w``)."""
+    (``b_mn``: ``w`` is ``[K, N]`` and the product is ``all_gather(x) @ w``).
+
+    ``keep_gathered``: also return the gathered operand ``[T, K]``.  The kernel pulls the
+    remote rows into a local buffer anyway; with this flag the buffer is private to the call
+    (and gets this rank's own rows copied in), so that the weight-gradient GEMM of the same
+    layer can contract over it instead of gathering the tokens over NVLink a second time."""
     ts, k = x_shard.shape
     n = w.shape[1] if b_mn else w.shape[0]
     t = ts * ctx.world
@@ -120,14 +128,21 @@ def ag_gemm(ctx, x_shard, w, bias=None, act=-1, name="ag_in", staged=None, b_mn=
     if ts % 128 == 0 and ctx.world > 1:
         # remote rows are pulled once into a local staging buffer by copier warps
         stage, flags = _staging(ctx, t, k, x_shard.dtype, x_shard.device)
+        if keep_gathered:
+            stage = torch.empty(t, k, dtype=x_shard.dtype, device=x_shard.device)
         comm_gemm(ctx, a_ptrs=buf.ptrs(), b_ptrs=[w.data_ptr()], M=t, N=n, K=k, lda=k,
                   ldb=w.stride(0), a_mn=False, b_mn=b_mn, dtype=x_shard.dtype,
                   gather=GATHER_A_ROWS_STAGED, seg_len=ts, out_ptr=y.data_ptr(), ldo=n, bias=bias,
                   act=act, stage=stage, chunk_flags=flags)
+        if keep_gathered:
+            stage[ctx.rank * ts:(ctx.rank + 1) * ts].copy_(x_shard)   # own rows are read in place
+            return y, stage
         return y
     comm_gemm(ctx, a_ptrs=buf.ptrs(), b_ptrs=[w.data_ptr()], M=t, N=n, K=k, lda=k,
               ldb=w.stride(0), a_mn=False, b_mn=b_mn, dtype=x_shard.dtype,
               gather=GATHER_A_ROWS, seg_len=ts, out_ptr=y.data_ptr(), ldo=n, bias=bias, act=act)
+    if keep_gathered:
+        return y, None
     return y
 
 
@@ -162,13 +177,18 @@ class _AGLinear(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x_shard, w, bias, sctx):
         ctx.sctx = sctx
-        ctx.save_for_backward(x_shard, w)
+        x_shard = x_shard.contiguous()
+        y, full_x = ag_gemm(sctx, x_shard, w, bias, keep_gathered=True)
+        # the gathered tokens are kept for the weight gradient when the kernel staged them
+        # (HBM is plentiful; the second NVLink gather in backward is not)
+        ctx.gathered = full_x is not None
+        ctx.save_for_backward(full_x if ctx.gathered else x_shard, w)
         ctx.has_bias = bias is not None
-        return ag_gemm(sctx, x_shard.contiguous(), w, bias)
+        return y
 
     @staticmethod
     def backward(ctx, dy):
-        x_shard, w = ctx.saved_tensors
+        x_saved, w = ctx.saved_tensors
         sctx = ctx.sctx
         dy = dy.contiguous()
         # dXs = reduce_scatter(dY @ W):  B = W read N-major ([N_local, K] = [contraction, out])
@@ -176,7 +196,8 @@ class _AGLinear(torch.autograd.Function):
         # dW = dY^T @ all_gather(Xs): few output tiles and a very long
         # contraction - gather the tokens with the pull kernel and let the
         # library's split-K GEMM do the rest
-        dw = dy.t() @ peer_gather(sctx, x_shard.contiguous(), "ag_in_bwd")
+        full_x = x_saved if ctx.gathered else peer_gather(sctx, x_saved.contiguous(), "ag_in_bwd")
+        dw = dy.t() @ full_x
         db = dy.float().sum(0).to(dy.dtype) if ctx.has_bias else None
         return dx, dw, db, None
 
@@ -197,9 +218,13 @@ class _RSLinear(torch.autograd.Function):
         ts, n = dy_shard.shape
         t, kl = x.shape
         # dX = all_gather(dYs) @ W: A rows gathered inside the GEMM, B = W read N-major
-        dx = ag_gemm(sctx, dy_shard, w, None, name="ag_dy_bwd", b_mn=True)
-        # dW = all_gather(dYs)^T @ X: long contraction, few tiles (see _AGLinear)
-        dw = peer_gather(sctx, dy_shard, "ag_dy_bwd2").t() @ x
+        dx, full_dy = ag_gemm(sctx, dy_shard, w, None, name="ag_dy_bwd", b_mn=True,
+                              keep_gathered=True)
+        # dW = all_gather(dYs)^T @ X: long contraction, few tiles (see _AGLinear); the dgrad
+        # kernel above has already gathered dY into local memory
+        if full_dy is None:
+            full_dy = peer_gather(sctx, dy_shard, "ag_dy_bwd2")
+        dw = full_dy.t() @ x
         # the bias is added on the owner's rows only: its gradient is partial
         # (tagged replicated_param -> summed over the group by the engine)
         db = dy_shard.float().sum(0).to(dy_shard.dtype) if ctx.has_bias else None
