@@ -114,11 +114,19 @@ std::tuple<Tensor, Tensor, Tensor, Tensor> flash_attn_bwd(
       q.scalar_type() == at::kBFloat16, slapo_status_ptr(q.get_device()),
       at::cuda::getCurrentCUDAStream().stream());
   TORCH_CHECK(rc == 0, "flash_attn_bwd: launch refused (code ", rc, ")");
+  const bool bf16 = q.scalar_type() == at::kBFloat16;
+  const int64_t rows = static_cast<int64_t>(B) * Sq * H;
+  auto stream = at::cuda::getCurrentCUDAStream().stream();
   if (packed_qkv) {
-    dqkv.select(3, 0).copy_(dq_accum);
+    // dq is slice 0 of the packed gradient: rows of D values, 3 D apart
+    slapo::launch_flash_dq_convert(dq_accum.data_ptr<float>(), dqkv.data_ptr(), rows, D, 3 * D,
+                                   bf16, stream);
     return {dqkv, dk, dv, drel};
   }
-  return {dq_accum.to(q.scalar_type()), dk, dv, drel};
+  Tensor dq = at::empty({B, Sq, H, D}, q.options());
+  slapo::launch_flash_dq_convert(dq_accum.data_ptr<float>(), dq.data_ptr(), rows, D, D, bf16,
+                                 stream);
+  return {dq, dk, dv, drel};
 }
 
 Tensor flash_attn_dropout_mask(int64_t B, int64_t H, int64_t Sq, int64_t Sk, double p_drop,

@@ -435,6 +435,41 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
   }
 }
 
+// dq (16-bit, rows spaced out_row_stride elements apart) <- dq_accum (fp32, contiguous rows of D):
+// the conversion that closes the backward pass; 8 values per thread, 16-byte stores.
+template <typename T>
+__global__ void __launch_bounds__(256) flash_dq_convert_kernel(const float* __restrict__ acc,
+                                                               T* __restrict__ out, int64_t rows,
+                                                               int D, int64_t out_row_stride) {
+  const int vecs_per_row = D >> 3;
+  const int64_t n_vec = rows * vecs_per_row;
+  const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
+  for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < n_vec;
+       i += stride) {
+    const int64_t row = i / vecs_per_row;
+    const int d = static_cast<int>(i - row * vecs_per_row) * 8;
+    float v[8];
+    Vec8<float>::load(acc + row * D + d, v);
+    Vec8<T>::store(out + row * out_row_stride + d, v);
+  }
+}
+
+void launch_flash_dq_convert(const float* acc, void* out, int64_t rows, int D,
+                             int64_t out_row_stride, bool bf16, cudaStream_t stream) {
+  const int64_t n_vec = rows * (D >> 3);
+  if (n_vec == 0) return;
+  int64_t blocks = (n_vec + 255) / 256;
+  const int64_t cap = static_cast<int64_t>(sm_count()) * 16;
+  if (blocks > cap) blocks = cap;
+  count_launch();
+  if (bf16)
+    flash_dq_convert_kernel<__nv_bfloat16><<<static_cast<int>(blocks), 256, 0, stream>>>(
+        acc, static_cast<__nv_bfloat16*>(out), rows, D, out_row_stride);
+  else
+    flash_dq_convert_kernel<__half><<<static_cast<int>(blocks), 256, 0, stream>>>(
+        acc, static_cast<__half*>(out), rows, D, out_row_stride);
+}
+
 template <int D, bool kPlain>
 static int launch_bwd_d(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv,
                         const CUtensorMap& tdo, const FlashBwdParams& p, cudaStream_t stream) {
