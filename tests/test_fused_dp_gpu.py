@@ -20,7 +20,7 @@ def _adamw_ref(w, g, m, v, decay, lr, b1, b2, eps, wd, step, coef):
     return w - lr * upd, m, v
 
 
-@pytest.mark.parametrize("world", [2, 4])
+@pytest.mark.parametrize("world", [2, 4, 8])
 def test_fused_dp_emulated_ranks(world):
     from slapo_b200.ops import native
     from slapo_b200.parallel.fused_dp import FusedDP

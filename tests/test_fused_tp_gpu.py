@@ -23,10 +23,10 @@ def _close(a, b, k, tol=2e-2):
     torch.testing.assert_close(a.float() / scale, b.float() / scale, rtol=tol, atol=tol)
 
 
-@pytest.mark.parametrize("world", [2, 4])
-def test_all_gather_gemm(world):
+@pytest.mark.parametrize("world,n", [(2, 320), (4, 320), (8, 384), (8, 512)])
+def test_all_gather_gemm(world, n):
     torch.manual_seed(0)
-    ts, k, n = 256, 192, 320
+    ts, k = 256, 192
     ctx = LocalSymmContext(world)
     shards = [torch.randn(ts, k, device="cuda", dtype=torch.bfloat16) for _ in range(world)]
     w = [torch.randn(n, k, device="cuda", dtype=torch.bfloat16) for _ in range(world)]
@@ -42,7 +42,7 @@ def test_all_gather_gemm(world):
         _close(y, full @ w[r].float().t() + bias.float(), k)
 
 
-@pytest.mark.parametrize("world", [2, 4])
+@pytest.mark.parametrize("world", [2, 4, 8])
 @pytest.mark.parametrize("mode", ["rs", "ar"])
 def test_gemm_reduce_scatter_and_all_reduce(world, mode):
     torch.manual_seed(1)
