@@ -41,6 +41,9 @@
 namespace slapo {
 
 constexpr int kMaxRanks = 8;
+// the chunk_flags argument points at 2 * kChunkCountOffset words: ready flags of the staged row
+// blocks first, slice counters of the same blocks behind them
+constexpr int kChunkCountOffset = 8192;
 constexpr int CBM = 128;
 constexpr int CBK = 64;
 
@@ -411,39 +414,55 @@ comm_gemm_kernel(const __grid_constant__ SegMaps maps_a, const __grid_constant__
     // read staged blocks with local TMA loads.
     if (staged && p.world > 1) {
       const int ct = threadIdx.x - 192;
-      const int64_t blk_vec = static_cast<int64_t>(CBM) * p.row_bytes / 16;
-      int j = 0;
+      // A 128-row block is copied as kSlices slices of 32 rows by (usually) different CTAs,
+      // units in (block, slice) order, so that the first blocks are complete after a few
+      // NVLink round trips instead of all blocks becoming visible at the same late moment.
+      constexpr int kSlices = 4;
+      int* chunk_count = p.chunk_flags + kChunkCountOffset;
+      const int64_t slice_vec = static_cast<int64_t>(CBM / kSlices) * p.row_bytes / 16;
+      int u = 0;
       bool ok = true;
       for (int o_idx = 1; o_idx < p.world && ok; ++o_idx) {
         const int owner = (p.rank + o_idx) % p.world;
         bool owner_ready = false;
-        for (int b = 0; b < blocks_per_owner; ++b, ++j) {
-          if (j % static_cast<int>(gridDim.x) != static_cast<int>(blockIdx.x)) continue;
-          if (!owner_ready) {
-            int w = 1;
-            if (ct == 0) w = wait_flag(ready + owner, p.epoch, p.wait_cycles, abort_flag) ? 1 : 0;
-            w = __syncthreads_or_named(w);
-            if (!w) { ok = false; break; }
-            owner_ready = true;
-          }
-          const uint4* src = reinterpret_cast<const uint4*>(
-              static_cast<const uint8_t*>(p.seg_src[owner]) +
-              static_cast<int64_t>(b) * CBM * p.row_bytes);
-          const int m_blk = owner * blocks_per_owner + b;
-          uint4* dst = reinterpret_cast<uint4*>(static_cast<uint8_t*>(p.stage_dst) +
-                                                static_cast<int64_t>(m_blk) * CBM * p.row_bytes);
-          for (int64_t v = ct; v < blk_vec; v += 128 * 8) {
-            uint4 tmp[8];
+        for (int b = 0; b < blocks_per_owner && ok; ++b) {
+          for (int sl = 0; sl < kSlices; ++sl, ++u) {
+            if (u % static_cast<int>(gridDim.x) != static_cast<int>(blockIdx.x)) continue;
+            if (!owner_ready) {
+              int w = 1;
+              if (ct == 0) w = wait_flag(ready + owner, p.epoch, p.wait_cycles, abort_flag) ? 1 : 0;
+              w = __syncthreads_or_named(w);
+              if (!w) { ok = false; break; }
+              owner_ready = true;
+            }
+            const int64_t off = (static_cast<int64_t>(b) * CBM + sl * (CBM / kSlices)) * p.row_bytes;
+            const uint4* src = reinterpret_cast<const uint4*>(
+                static_cast<const uint8_t*>(p.seg_src[owner]) + off);
+            const int m_blk = owner * blocks_per_owner + b;
+            uint4* dst = reinterpret_cast<uint4*>(
+                static_cast<uint8_t*>(p.stage_dst) +
+                (static_cast<int64_t>(m_blk) * CBM + sl * (CBM / kSlices)) * p.row_bytes);
+            for (int64_t v = ct; v < slice_vec; v += 128 * 8) {
+              uint4 tmp[8];
 #pragma unroll
-            for (int u = 0; u < 8; ++u)
-              if (v + u * 128 < blk_vec) tmp[u] = src[v + u * 128];
+              for (int q = 0; q < 8; ++q)
+                if (v + q * 128 < slice_vec) tmp[q] = src[v + q * 128];
 #pragma unroll
-            for (int u = 0; u < 8; ++u)
-              if (v + u * 128 < blk_vec) dst[v + u * 128] = tmp[u];
+              for (int q = 0; q < 8; ++q)
+                if (v + q * 128 < slice_vec) dst[v + q * 128] = tmp[q];
+            }
+            __threadfence();
+            asm volatile("bar.sync 2, 128;" ::: "memory");
+            if (ct == 0) {
+              // the copier that completes the block publishes it
+              const int prev = atomicAdd(chunk_count + m_blk, 1);
+              if (prev + 1 == kSlices) {
+                atomicExch(chunk_count + m_blk, 0);
+                __threadfence();
+                st_release_sys(p.chunk_flags + m_blk, p.epoch);
+              }
+            }
           }
-          __threadfence();
-          asm volatile("bar.sync 2, 128;" ::: "memory");
-          if (ct == 0) st_release_sys(p.chunk_flags + m_blk, p.epoch);
         }
       }
     }
@@ -677,6 +696,7 @@ int launch_comm_gemm(void* const* a_ptrs, void* const* b_ptrs, int M, int N, int
                      void* const* peer_out, int* status, double wait_seconds, void* stage_dst,
                      int* chunk_flags, cudaStream_t stream) {
   if (M <= 0 || N <= 0 || K <= 0) return 0;
+  if (gather == 4 && (M + CBM - 1) / CBM > kChunkCountOffset) return 6;
   if (gather == 4 && (a_mn || stage_dst == nullptr || chunk_flags == nullptr || lda != K ||
                       seg_len % CBM != 0 || seg_len * world != M))
     return 1;

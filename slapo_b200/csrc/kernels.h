@@ -48,8 +48,9 @@ void launch_sq_norm(const void* x, const uint8_t* mask, float* out2, int64_t n, 
 
 // Fused GEMM + collective over peer memory (comm_gemm.cu).
 //   gather: 0 none, 1 rows of A, 2 contraction dim of A, 3 contraction dim of B,
-//           4 rows of A staged once through the local buffer stage_dst (chunk_flags: one
-//           int per 128-row block, zero-initialised, kept across calls)
+//           4 rows of A staged once through the local buffer stage_dst (chunk_flags: 2 * 8192
+//             ints, zero-initialised, kept across calls - the epoch at which each 128-row
+//             block was staged, then the slice counters of the same blocks)
 //   mode:   0 local output, 1 reduce-scatter, 2 all-reduce
 int launch_comm_gemm(void* const* a_ptrs, void* const* b_ptrs, int M, int N, int K, int lda,
                      int ldb, bool a_mn, bool b_mn, bool bf16, int gather, int seg_len, int mode,

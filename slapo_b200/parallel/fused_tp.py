@@ -33,6 +33,7 @@ import torch
 from ..ops import native
 
 GATHER_NONE, GATHER_A_ROWS, GATHER_A_K, GATHER_B_K, GATHER_A_ROWS_STAGED = 0, 1, 2, 3, 4
+_CHUNK_WORDS = 8192   # kChunkCountOffset of csrc/comm_gemm.cu
 MODE_LOCAL, MODE_RS, MODE_AR = 0, 1, 2
 
 
@@ -74,8 +75,11 @@ def _staging(ctx, t, k, dtype, device):
         st[key] = buf
     flags = st.get("flags")
     need = (t + 127) // 128
-    if flags is None or flags.numel() < need:
-        flags = torch.zeros(max(need, 4096), dtype=torch.int32, device=device)
+    if need > _CHUNK_WORDS:
+        raise ValueError(f"{t} gathered rows exceed the {_CHUNK_WORDS * 128} the staged gather handles")
+    if flags is None:
+        # [0, 8192): epoch at which a 128-row block was staged; [8192, 16384): slice counters
+        flags = torch.zeros(2 * _CHUNK_WORDS, dtype=torch.int32, device=device)
         st["flags"] = flags
     return buf[:t * k].view(t, k), flags
 
