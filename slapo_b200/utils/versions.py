@@ -13,7 +13,9 @@ _OPS = {
 def compare_versions(lib_or_version, op: str, requirement: str) -> bool:
     if op not in _OPS:
         raise ValueError(f"operation must be one of {list(_OPS)}, got {op}")
-    if isinstance(lib_or_version, str):
+    # a string is a library name (its __version__ is compared) unless it already looks
+    # like a version number
+    if isinstance(lib_or_version, str) and not lib_or_version[:1].isdigit():
         lib_or_version = importlib.import_module(lib_or_version).__version__
     return _OPS[op](_v.parse(str(lib_or_version)), _v.parse(requirement))
 
