@@ -233,11 +233,29 @@ def _trace_level(root: nn.Module, *, leaf_modules, flatten, recursive, concrete_
 
 
 def _trace_dynamo(root, concrete_args):
-    example = (concrete_args or {}).get("example_inputs")
-    if example is None:
-        raise ValueError('the "dynamo" tracer needs concrete_args={"example_inputs": (...)}')
-    exported = torch.export.export(root, tuple(example), strict=False)
-    return exported.module()
+    """``torch.export`` capture.  ``concrete_args`` holds the example inputs: either under the
+    key ``"example_inputs"`` (a tuple of positional arguments) or, as in the reference
+    (slapo/tracer.py:642-659), one entry per forward argument."""
+    concrete_args = dict(concrete_args or {})
+    if not concrete_args:
+        raise ValueError('the "dynamo" tracer needs example inputs in concrete_args')
+    if "example_inputs" in concrete_args:
+        args, kwargs = tuple(concrete_args["example_inputs"]), {}
+    else:
+        args, kwargs = (), concrete_args
+    try:
+        device = next(root.parameters()).device
+    except StopIteration:
+        device = None
+    move = lambda v: v.to(device) if isinstance(v, torch.Tensor) and device is not None else v
+    exported = torch.export.export(root, tuple(move(a) for a in args),
+                                   {k: move(v) for k, v in kwargs.items()}, strict=False)
+    captured = exported.module()
+    # The exported module refuses train() / eval(); an ordinary GraphModule over the same
+    # graph and attributes behaves like every other traced module of the schedule.
+    gm = fx.GraphModule(captured, captured.graph)
+    gm.train(root.training)
+    return gm
 
 
 def trace(model: nn.Module, tracer: str = "pytorch", recursive: bool = True,

@@ -300,3 +300,23 @@ def test_fuse_native_bias_gelu_and_dropout_add_ln():
         sch2 = slapo.create_schedule(Layer())
         sch2.trace(flatten=True)
         sch2.fuse(sch2.find(lambda x: F.relu(call_module("dense", x))), compiler="native")
+
+
+def test_dynamo_and_huggingface_tracer_names():
+    model = SelfAttn()
+    x = torch.randn(2, 4, 16)
+    want = model(x)
+    sch = slapo.create_schedule(SelfAttn())
+    sch.mod.load_state_dict(model.state_dict())
+    assert sch.trace(tracer="huggingface")
+    torch.testing.assert_close(sch.mod(x), want)
+    sch2 = slapo.create_schedule(SelfAttn())
+    sch2.mod.load_state_dict(model.state_dict())
+    assert sch2.trace(tracer="dynamo", concrete_args={"example_inputs": (x,)})
+    assert isinstance(sch2.mod, fx.GraphModule)
+    torch.testing.assert_close(sch2.mod(x), want)
+    sch3 = slapo.create_schedule(SelfAttn())
+    sch3.mod.load_state_dict(model.state_dict())
+    assert sch3.trace(tracer="dynamo", concrete_args={"x": x})       # the reference's spelling
+    torch.testing.assert_close(sch3.mod(x), want)
+    assert not slapo.create_schedule(SelfAttn()).trace(tracer="no-such-tracer")
