@@ -59,6 +59,8 @@ def main():
     ap.add_argument("--hidden", type=int, default=1024)
     ap.add_argument("--ffn", type=int, default=4096)
     ap.add_argument("--iters", type=int, default=10)
+    ap.add_argument("--ops", default="ag,rs,dp", help="comma list of ag, rs, dp")
+    ap.add_argument("--no-baseline", action="store_true", help="skip the NCCL + cuBLAS lines")
     args = ap.parse_args()
     local = int(os.environ.get("LOCAL_RANK", "0"))
     torch.cuda.set_device(local)
@@ -75,7 +77,8 @@ def main():
     t = ts * world                        # tokens seen by a TP region
     h, f = args.hidden, args.ffn
     torch.manual_seed(rank)
-    for label, n_full, k in (("qkv", 3 * h, h), ("fc1", f, h)):
+    ops = set(args.ops.split(","))
+    for label, n_full, k in (("qkv", 3 * h, h), ("fc1", f, h)) if "ag" in ops else ():
         n = n_full // world
         x = torch.randn(ts, k, device=dev, dtype=dt)
         w = torch.randn(n, k, device=dev, dtype=dt)
@@ -88,10 +91,11 @@ def main():
             dist.all_gather_into_tensor(full, x)
             return F.linear(full, w)
 
-        us_b = _time(base, args.iters)
-        _report(rank, f"nccl_all_gather+cublas[{label}]", us_b, 2.0 * t * n * k, link,
-                shape=[t, n, k], world=world)
-    for label, n, k_full in (("attn_out", h, h), ("fc2", h, f)):
+        if not args.no_baseline:
+            us_b = _time(base, args.iters)
+            _report(rank, f"nccl_all_gather+cublas[{label}]", us_b, 2.0 * t * n * k, link,
+                    shape=[t, n, k], world=world)
+    for label, n, k_full in (("attn_out", h, h), ("fc2", h, f)) if "rs" in ops else ():
         k = k_full // world
         x = torch.randn(t, k, device=dev, dtype=dt)
         w = torch.randn(n, k, device=dev, dtype=dt)
@@ -104,30 +108,32 @@ def main():
             dist.reduce_scatter_tensor(out, F.linear(x, w))
             return out
 
-        us_b = _time(base_rs, args.iters)
-        _report(rank, f"cublas+nccl_reduce_scatter[{label}]", us_b, 2.0 * t * n * k, link,
-                shape=[t, n, k], world=world)
+        if not args.no_baseline:
+            us_b = _time(base_rs, args.iters)
+            _report(rank, f"cublas+nccl_reduce_scatter[{label}]", us_b, 2.0 * t * n * k, link,
+                    shape=[t, n, k], world=world)
         us = _time(lambda: ft.gemm_ar(ctx, x, w), args.iters)
         _report(rank, f"gemm_ar[{label}]", us, 2.0 * t * n * k, 2 * link, shape=[t, n, k],
                 world=world)
     # fused data parallel: one 64 MiB bucket
-    from slapo_b200.parallel.fused_dp import FusedDP
+    if "dp" in ops:
+        from slapo_b200.parallel.fused_dp import FusedDP
 
-    elems = 32 * 2**20
-    fdp = FusedDP(ctx, elems, dt, 1)
-    shard = elems // world
-    out = torch.empty(shard, device=dev, dtype=dt)
-    state = {"epoch": 0}
+        elems = 32 * 2**20
+        fdp = FusedDP(ctx, elems, dt, 1)
+        shard = elems // world
+        out = torch.empty(shard, device=dev, dtype=dt)
+        state = {"epoch": 0}
 
-    def rs():
-        state["epoch"] += 1
-        fdp.grad_rs(0, state["epoch"], rank * shard, out, None)
+        def rs():
+            state["epoch"] += 1
+            fdp.grad_rs(0, state["epoch"], rank * shard, out, None)
 
-    us = _time(rs, args.iters)
-    _report(rank, "dp_grad_rs[64MiB]", us, 0.0, (world - 1) * shard * 2, world=world)
-    grad = torch.randn(elems, device=dev, dtype=dt)
-    us = _time(lambda: dist.reduce_scatter_tensor(out, grad, op=dist.ReduceOp.AVG), args.iters)
-    _report(rank, "nccl_reduce_scatter[64MiB]", us, 0.0, (world - 1) * shard * 2, world=world)
+        us = _time(rs, args.iters)
+        _report(rank, "dp_grad_rs[64MiB]", us, 0.0, (world - 1) * shard * 2, world=world)
+        grad = torch.randn(elems, device=dev, dtype=dt)
+        us = _time(lambda: dist.reduce_scatter_tensor(out, grad, op=dist.ReduceOp.AVG), args.iters)
+        _report(rank, "nccl_reduce_scatter[64MiB]", us, 0.0, (world - 1) * shard * 2, world=world)
     if rank == 0:
         print(json.dumps({"device_status": int(native.ops().device_status())}))
     dist.barrier()

@@ -156,8 +156,11 @@ def bench_comm(small, iters):
     x = torch.randn(ts * world, n, device="cuda", dtype=torch.bfloat16)
     w2 = torch.randn(k, n, device="cuda", dtype=torch.bfloat16)
 
+    ctx.buffer("rs_recv", ft.RECV_HEADER_BYTES + ts * world * k * 2)
+
     def rs():
         ctx.preset_flags(ctx.epoch + 1, ready=True, done=True, done2=True)
+        ctx.preset_block_flags("rs_recv", ctx.epoch + 1, ts // 128)
         return ft.gemm_rs(ctx, x, w2, None)
 
     report("gemm_rs_emulated", timeit(rs, iters), flops=2 * ts * world * n * k,

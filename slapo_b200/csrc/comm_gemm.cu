@@ -14,26 +14,32 @@
 //                        the contraction dimension of A or B (weight
 //                        gradients, where the gathered tensor is contracted).
 //   GEMM -> reduce-scatter   the epilogue writes each 16-bit partial tile into
-//                        this rank's symmetric partial buffer, visiting the
-//                        row blocks of the other owners first; when a source
-//                        has finished an owner's row block it releases a flag
-//                        on that owner; after its own tiles every CTA joins
-//                        the reduction of this rank's rows, pulling the p
-//                        partials over NVLink with wide coalesced loads (fp32
-//                        sum, optional bias) - still the same launch.
-//   GEMM -> all-reduce   reduce-scatter as above, then the reduced rows are
-//                        pushed to every peer's output buffer and a second
-//                        flag round closes the operation.
+//                        this rank's symmetric partial buffer.  Tiles are
+//                        visited row block by row block: block b of every
+//                        owner's rows in turn, then block b + 1.  When a
+//                        source has finished block b of an owner it releases
+//                        the flag (source, b) in that owner's buffer header;
+//                        the owner's reducer warps (warps 6-9 of every CTA)
+//                        then pull the block from all ranks over NVLink with
+//                        wide coalesced loads (fp32 sum, optional bias) and
+//                        write the result - while the tensor core works on the
+//                        later blocks.  Only the last block is not hidden.
+//   GEMM -> all-reduce   reduce-scatter as above, the reduced rows go to
+//                        every peer's output buffer and a second flag round
+//                        closes the operation.
 //
 // Flow control is an int32 flag pad in symmetric memory and one job-wide
 // monotone epoch number per fused operation (identical on all ranks):
 //   ready[src] >= epoch   rank src has entered this operation, i.e. everything
 //                         it launched before (producers of its buffers,
 //                         consumers of what we are about to overwrite) is done
-//   done[src]  >= epoch   rank src has delivered its contribution to my rows
+//   blk[src][b] >= epoch  rank src has written block b of my rows (partial-buffer header)
 //   done2[src] >= epoch   rank src has delivered its reduced rows (all-reduce)
 // Every wait is bounded; on time-out the kernel records an error code in the
 // device status word, stops issuing work and leaves (TMEM freed).
+#include <cstdio>
+#include <cstdlib>
+
 #include "common.cuh"
 #include "kernels.h"
 #include "tc05.cuh"
@@ -44,6 +50,10 @@ constexpr int kMaxRanks = 8;
 // the chunk_flags argument points at 2 * kChunkCountOffset words: ready flags of the staged row
 // blocks first, slice counters of the same blocks behind them
 constexpr int kChunkCountOffset = 8192;
+// header of a partial-product (receive) buffer: kChunkCountOffset block flags + as many counters
+constexpr int kRecvHeaderBytes = 2 * kChunkCountOffset * 4;
+constexpr int kDefaultAgSlices = 4;
+constexpr int kDefaultAgInflight = 8;
 constexpr int CBM = 128;
 constexpr int CBK = 64;
 
@@ -80,6 +90,13 @@ struct CommGemmParams {
   int* chunk_flags;              // local, one word per 128-row block: epoch when staged
   const void* seg_src[kMaxRanks];  // every rank's shard [seg_len, K]
   int row_bytes;                 // K * 2
+  int ag_slices;                 // staged gather: slices per 128-row block (1, 2 or 4)
+  int ag_inflight;               // staged gather: 16-byte loads in flight per thread (8 or 16)
+  // reduce-scatter / all-reduce: per (source rank, 128-row block of the owner's rows) flags in
+  // the header of every rank's partial-product buffer, and the local arrival counters
+  int* blk_flags;
+  int* peer_blk_flags[kMaxRanks];
+  int* blk_counters;
 };
 
 __device__ __forceinline__ void st_release_sys(int* addr, int v) {
@@ -141,20 +158,27 @@ __device__ __forceinline__ float cload(const void* p, int64_t i, int bf16) {
   return __half2float(static_cast<const __half*>(p)[i]);
 }
 
-// Tile order: row blocks are visited owner by owner starting with the rank
-// after this one (its data has the longest way to go) and ending with the
-// local block; inside an owner, row blocks then column tiles.
+// Tile order.  Gather: row blocks are visited owner by owner, own rows first (first = 0), remote
+// rows while they are being staged.  Scatter (interleave): the b-th row block of every owner in
+// turn, starting with the rank after this one, then block b + 1 - so that block b of an owner is
+// complete on ALL ranks after (b + 1) / blocks_per_owner of the main loop and its reduction
+// overlaps the rest of the GEMM.
 __device__ __forceinline__ void tile_coords(int t, int tiles_n, int blocks_per_owner, int world,
                                             int rank, bool rotate, int& m_blk, int& n_blk,
-                                            int first = 1) {
+                                            int first = 1, bool interleave = false) {
   n_blk = t % tiles_n;
   int mb = t / tiles_n;
   if (rotate) {
-    // first = 1: start with the next rank's rows, own rows last (scatter);
-    // first = 0: own rows first, remote rows while they are being staged (gather)
-    const int o_idx = mb / blocks_per_owner;
+    int o_idx, b;
+    if (interleave) {
+      o_idx = mb % world;
+      b = mb / world;
+    } else {
+      o_idx = mb / blocks_per_owner;
+      b = mb % blocks_per_owner;
+    }
     const int owner = (rank + first + o_idx) % world;
-    mb = owner * blocks_per_owner + mb % blocks_per_owner;
+    mb = owner * blocks_per_owner + b;
   }
   m_blk = mb;
 }
@@ -165,41 +189,47 @@ __device__ __forceinline__ void tile_coords(int t, int tiles_n, int blocks_per_o
 // time (0 = generic), U = row vectors per thread per iteration: W * U loads are in flight per
 // thread before the first is used, which is what hides the NVLink round trip.
 template <int W, int U>
-__device__ __forceinline__ void reduce_rows(const CommGemmParams& p, int rows_per_rank) {
+__device__ __forceinline__ void reduce_span(const CommGemmParams& p, int rows_per_rank, int row0,
+                                            int nrows, int tid, int nthr) {
+  // rows [row0, row0 + nrows) of this rank's [rows_per_rank, N] rows; 32-bit indices inside the span
   constexpr int kW = W > 0 ? W : kMaxRanks;
   const int world = W > 0 ? W : p.world;
-  const int64_t vec_per_row = p.N / 8;
-  const int64_t n_vec = static_cast<int64_t>(rows_per_rank) * vec_per_row;
+  const unsigned vpr = static_cast<unsigned>(p.N) / 8u;     // 8-element vectors per row
+  const unsigned n_loc = static_cast<unsigned>(nrows) * vpr;
   // this rank's rows inside every source's partial buffer [M, N]
-  const int64_t my_off = static_cast<int64_t>(p.rank) * rows_per_rank * p.N;
-  const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
-  for (int64_t i0 = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i0 < n_vec;
-       i0 += stride * U) {
+  const int64_t my_off = (static_cast<int64_t>(p.rank) * rows_per_rank + row0) * p.N;
+  const uint8_t* srcs[kW];
+#pragma unroll
+  for (int r = 0; r < kW; ++r) {
+    // start with the next rank so that the peers' links share the load
+    int src = p.rank + 1 + r;
+    if (src >= world) src -= world;
+    srcs[r] = r < world ? static_cast<const uint8_t*>(p.peer_recv[src]) + my_off * 2 : nullptr;
+  }
+  for (unsigned j0 = tid; j0 < n_loc; j0 += static_cast<unsigned>(nthr) * U) {
     uint4 raw[U][kW];
+    if constexpr (W > 0) {
 #pragma unroll
-    for (int u = 0; u < U; ++u) {
-      const int64_t e = (i0 + u * stride) * 8;
+      for (int u = 0; u < U; ++u) {
+        const unsigned j = j0 + u * nthr;
 #pragma unroll
-      for (int r = 0; r < kW; ++r) {
-        if (r < world && i0 + u * stride < n_vec) {
-          // start with the next rank so that the peers' links share the load
-          int src = p.rank + 1 + r;
-          if (src >= world) src -= world;
-          raw[u][r] = *reinterpret_cast<const uint4*>(
-              static_cast<const uint8_t*>(p.peer_recv[src]) + (my_off + e) * 2);
-        }
+        for (int r = 0; r < kW; ++r)
+          if (j < n_loc)
+            raw[u][r] = *reinterpret_cast<const uint4*>(srcs[r] + static_cast<size_t>(j) * 16);
       }
     }
 #pragma unroll
     for (int u = 0; u < U; ++u) {
-      const int64_t i = i0 + u * stride;
-      if (i >= n_vec) break;
-      const int64_t e = i * 8;
+      const unsigned j = j0 + u * nthr;
+      if (j >= n_loc) break;
       float acc8[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
 #pragma unroll
       for (int r = 0; r < kW; ++r) {
         if (r < world) {
           float v[8];
+          // group sizes without an instantiation (3, 5, 6, 7) load source by source
+          if constexpr (W == 0)
+            raw[u][r] = *reinterpret_cast<const uint4*>(srcs[r] + static_cast<size_t>(j) * 16);
           if (p.bf16) {
             const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw[u][r]);
 #pragma unroll
@@ -213,7 +243,8 @@ __device__ __forceinline__ void reduce_rows(const CommGemmParams& p, int rows_pe
           for (int k = 0; k < 8; ++k) acc8[k] += v[k];
         }
       }
-      const int col = static_cast<int>(e % p.N);
+      const unsigned lr = j / vpr;
+      const int col = static_cast<int>(j - lr * vpr) * 8;
       if (p.bias != nullptr) {
 #pragma unroll
         for (int k = 0; k < 8; ++k) acc8[k] += cload(p.bias, col + k, p.bf16);
@@ -222,7 +253,7 @@ __device__ __forceinline__ void reduce_rows(const CommGemmParams& p, int rows_pe
 #pragma unroll
         for (int k = 0; k < 8; ++k) acc8[k] = act_fwd(acc8[k], p.act);
       }
-      const int64_t lrow = e / p.N;
+      const int64_t lrow = row0 + static_cast<int>(lr);
       if (p.mode == kModeReduceScatter) {
         void* o = static_cast<uint8_t*>(p.out) + (lrow * p.ldo + col) * 2;
         if (p.bf16) Vec8<__nv_bfloat16>::store(static_cast<__nv_bfloat16*>(o), acc8);
@@ -239,6 +270,21 @@ __device__ __forceinline__ void reduce_rows(const CommGemmParams& p, int rows_pe
         }
       }
     }
+  }
+}
+
+// 128 threads copy n_vec 16-byte vectors, F loads in flight per thread
+template <int F>
+__device__ __forceinline__ void copy_vecs(const uint4* __restrict__ src, uint4* __restrict__ dst,
+                                          int64_t n_vec, int ct) {
+  for (int64_t v = ct; v < n_vec; v += 128 * F) {
+    uint4 tmp[F];
+#pragma unroll
+    for (int q = 0; q < F; ++q)
+      if (v + q * 128 < n_vec) tmp[q] = src[v + q * 128];
+#pragma unroll
+    for (int q = 0; q < F; ++q)
+      if (v + q * 128 < n_vec) dst[v + q * 128] = tmp[q];
   }
 }
 
@@ -319,7 +365,8 @@ comm_gemm_kernel(const __grid_constant__ SegMaps maps_a, const __grid_constant__
       };
       for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
         int m_blk, n_blk;
-        tile_coords(t, tiles_n, blocks_per_owner, p.world, p.rank, rotate, m_blk, n_blk, first);
+        tile_coords(t, tiles_n, blocks_per_owner, p.world, p.rank, rotate, m_blk, n_blk, first,
+                    scatter);
         const int m0 = m_blk * CBM, n0 = n_blk * BN;
         int a_seg = 0, a_row = m0;
         if (p.gather == 1) {
@@ -414,19 +461,20 @@ comm_gemm_kernel(const __grid_constant__ SegMaps maps_a, const __grid_constant__
     // read staged blocks with local TMA loads.
     if (staged && p.world > 1) {
       const int ct = threadIdx.x - 192;
-      // A 128-row block is copied as kSlices slices of 32 rows by (usually) different CTAs,
-      // units in (block, slice) order, so that the first blocks are complete after a few
-      // NVLink round trips instead of all blocks becoming visible at the same late moment.
-      constexpr int kSlices = 4;
+      // A 128-row block is copied as `slices` slices by (usually) different CTAs, units in
+      // (block, slice) order, so that the first blocks are complete after a few NVLink round
+      // trips instead of all blocks becoming visible at the same late moment.
+      const int slices = p.ag_slices;
+      const int slice_rows = CBM / slices;
       int* chunk_count = p.chunk_flags + kChunkCountOffset;
-      const int64_t slice_vec = static_cast<int64_t>(CBM / kSlices) * p.row_bytes / 16;
+      const int64_t slice_vec = static_cast<int64_t>(slice_rows) * p.row_bytes / 16;
       int u = 0;
       bool ok = true;
       for (int o_idx = 1; o_idx < p.world && ok; ++o_idx) {
         const int owner = (p.rank + o_idx) % p.world;
         bool owner_ready = false;
         for (int b = 0; b < blocks_per_owner && ok; ++b) {
-          for (int sl = 0; sl < kSlices; ++sl, ++u) {
+          for (int sl = 0; sl < slices; ++sl, ++u) {
             if (u % static_cast<int>(gridDim.x) != static_cast<int>(blockIdx.x)) continue;
             if (!owner_ready) {
               int w = 1;
@@ -435,29 +483,24 @@ comm_gemm_kernel(const __grid_constant__ SegMaps maps_a, const __grid_constant__
               if (!w) { ok = false; break; }
               owner_ready = true;
             }
-            const int64_t off = (static_cast<int64_t>(b) * CBM + sl * (CBM / kSlices)) * p.row_bytes;
+            const int64_t off = (static_cast<int64_t>(b) * CBM + sl * slice_rows) * p.row_bytes;
             const uint4* src = reinterpret_cast<const uint4*>(
                 static_cast<const uint8_t*>(p.seg_src[owner]) + off);
             const int m_blk = owner * blocks_per_owner + b;
             uint4* dst = reinterpret_cast<uint4*>(
                 static_cast<uint8_t*>(p.stage_dst) +
-                (static_cast<int64_t>(m_blk) * CBM + sl * (CBM / kSlices)) * p.row_bytes);
-            for (int64_t v = ct; v < slice_vec; v += 128 * 8) {
-              uint4 tmp[8];
-#pragma unroll
-              for (int q = 0; q < 8; ++q)
-                if (v + q * 128 < slice_vec) tmp[q] = src[v + q * 128];
-#pragma unroll
-              for (int q = 0; q < 8; ++q)
-                if (v + q * 128 < slice_vec) dst[v + q * 128] = tmp[q];
-            }
+                (static_cast<int64_t>(m_blk) * CBM + sl * slice_rows) * p.row_bytes);
+            // 8 or 16 16-byte loads per thread are issued before the first store: 128 threads
+            // keep 16 or 32 KB per SM on the wire to cover the NVLink round trip.
+            if (p.ag_inflight == 16) copy_vecs<16>(src, dst, slice_vec, ct);
+            else copy_vecs<8>(src, dst, slice_vec, ct);
             __threadfence();
             asm volatile("bar.sync 2, 128;" ::: "memory");
             if (ct == 0) {
               // the copier that completes the block publishes it
-              const int prev = atomicAdd(chunk_count + m_blk, 1);
-              if (prev + 1 == kSlices) {
-                atomicExch(chunk_count + m_blk, 0);
+              const int prev = slices > 1 ? atomicAdd(chunk_count + m_blk, 1) : 0;
+              if (prev + 1 == slices) {
+                if (slices > 1) atomicExch(chunk_count + m_blk, 0);
                 __threadfence();
                 st_release_sys(p.chunk_flags + m_blk, p.epoch);
               }
@@ -465,6 +508,36 @@ comm_gemm_kernel(const __grid_constant__ SegMaps maps_a, const __grid_constant__
           }
         }
       }
+    } else if (scatter) {
+      // ------------------------------ reducer warps -------------------------------
+      // Reduce-scatter / all-reduce: as soon as the b-th 128-row block of this rank's rows is
+      // complete in every rank's partial-product buffer (flags written by the epilogue warps of
+      // all ranks), a 32-row slice of it is pulled from all ranks over NVLink, summed in fp32,
+      // finished with bias / activation and written out - while the main loop computes the
+      // later blocks.  Only the last block's reduction is not hidden behind the GEMM.
+      const int ct = threadIdx.x - 192;
+      constexpr int kRedSlices = 4;
+      const int units = blocks_per_owner * kRedSlices;
+      for (int u = blockIdx.x; u < units; u += gridDim.x) {
+        const int b = u / kRedSlices, sl = u % kRedSlices;
+        int w = 1;
+        if (ct == 0) {
+          for (int src = 0; src < p.world && w; ++src)
+            w = wait_flag(p.blk_flags + src * blocks_per_owner + b, p.epoch, p.wait_cycles,
+                          abort_flag) ? 1 : 0;
+        }
+        w = __syncthreads_or_named(w);
+        if (!w) break;
+        const int row0 = b * CBM + sl * (CBM / kRedSlices);
+        switch (p.world) {
+          case 2: reduce_span<2, 4>(p, rows_per_rank, row0, CBM / kRedSlices, ct, 128); break;
+          case 4: reduce_span<4, 4>(p, rows_per_rank, row0, CBM / kRedSlices, ct, 128); break;
+          case 8: reduce_span<8, 2>(p, rows_per_rank, row0, CBM / kRedSlices, ct, 128); break;
+          default: reduce_span<0, 1>(p, rows_per_rank, row0, CBM / kRedSlices, ct, 128); break;
+        }
+      }
+      // all-reduce: the reduced rows stored to the peers must be visible before done2
+      if (p.mode == kModeAllReduce) __threadfence_system();
     }
   } else {
     // ------------------------------ epilogue ----------------------------------
@@ -472,10 +545,10 @@ comm_gemm_kernel(const __grid_constant__ SegMaps maps_a, const __grid_constant__
     int iter = 0;
     bool ok = true;
     uint32_t seen_ready = 1u << p.rank;
-    const int tiles_per_owner = blocks_per_owner * tiles_n;
     for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, ++iter) {
       int m_blk, n_blk;
-      tile_coords(t, tiles_n, blocks_per_owner, p.world, p.rank, rotate, m_blk, n_blk, first);
+      tile_coords(t, tiles_n, blocks_per_owner, p.world, p.rank, rotate, m_blk, n_blk, first,
+                    scatter);
       const int m0 = m_blk * CBM, n0 = n_blk * BN;
       const int acc = iter & 1;
       const uint32_t acc_phase = (iter >> 1) & 1;
@@ -544,59 +617,43 @@ comm_gemm_kernel(const __grid_constant__ SegMaps maps_a, const __grid_constant__
       __syncwarp();
       if (lane == 0) tc::mbar_arrive(&tmem_empty[acc]);
       if (scatter) {
-        // publish: make this warp's stores visible, count it; the warp that
-        // completes the owner's row block releases the owner's flag
+        // publish: make this warp's stores visible, count it; the warp that completes the
+        // row block (all column tiles) releases the flag of (this rank, block) at the owner
         __threadfence();
         __syncwarp();
         if (lane == 0) {
-          const int prev = atomicAdd(counters + owner, 1);
-          if (prev + 1 == tiles_per_owner * 4) {
-            atomicExch(counters + owner, 0);
+          const int slot = owner * blocks_per_owner + (m_blk - owner * blocks_per_owner);
+          const int prev = atomicAdd(p.blk_counters + slot, 1);
+          if (prev + 1 == tiles_n * 4) {
+            atomicExch(p.blk_counters + slot, 0);
             __threadfence_system();
-            st_release_sys(p.peer_flags[owner] + 8 + p.rank, p.epoch);
+            st_release_sys(p.peer_blk_flags[owner] + p.rank * blocks_per_owner +
+                               (m_blk - owner * blocks_per_owner),
+                           p.epoch);
           }
         }
       }
     }
   }
 
-  // ------------------------------ reduction phase --------------------------------
+  // ------------------------------ all-reduce closing -----------------------------
   tc::fence_before_sync();
   __syncthreads();
-  if (scatter && *abort_flag == 0) {
-    __shared__ int s_ok;
+  if (p.mode == kModeAllReduce && *abort_flag == 0) {
+    // count CTAs, the last one tells every rank that this rank's reduced rows are in place;
+    // the kernel leaves when every rank has said so
     if (threadIdx.x == 0) {
-      int okk = 1;
-      for (int r = 0; r < p.world && okk; ++r)
-        if (!wait_flag(done + r, p.epoch, p.wait_cycles, abort_flag)) okk = 0;
-      s_ok = okk;
+      __threadfence_system();
+      const int prev = atomicAdd(counters + 8, 1);
+      if (prev + 1 == static_cast<int>(gridDim.x)) {
+        atomicExch(counters + 8, 0);
+        __threadfence_system();
+        for (int r = 0; r < p.world; ++r) st_release_sys(p.peer_flags[r] + 16 + p.rank, p.epoch);
+      }
+      for (int r = 0; r < p.world; ++r)
+        if (!wait_flag(done2 + r, p.epoch, p.wait_cycles, abort_flag)) break;
     }
     __syncthreads();
-    if (s_ok) {
-      switch (p.world) {
-        case 2: reduce_rows<2, 4>(p, rows_per_rank); break;
-        case 4: reduce_rows<4, 2>(p, rows_per_rank); break;
-        case 8: reduce_rows<8, 1>(p, rows_per_rank); break;
-        default: reduce_rows<0, 1>(p, rows_per_rank); break;
-      }
-      if (p.mode == kModeAllReduce) {
-        // close the all-gather half: count CTAs, the last one releases done2
-        __threadfence_system();
-        __syncthreads();
-        if (threadIdx.x == 0) {
-          const int prev = atomicAdd(counters + 8, 1);
-          if (prev + 1 == static_cast<int>(gridDim.x)) {
-            atomicExch(counters + 8, 0);
-            __threadfence_system();
-            for (int r = 0; r < p.world; ++r) st_release_sys(p.peer_flags[r] + 16 + p.rank, p.epoch);
-          }
-          int okk = 1;
-          for (int r = 0; r < p.world && okk; ++r)
-            if (!wait_flag(done2 + r, p.epoch, p.wait_cycles, abort_flag)) okk = 0;
-        }
-        __syncthreads();
-      }
-    }
   }
 
   // ------------------------------ teardown ------------------------------------
@@ -683,8 +740,27 @@ static int launch_comm_variant(const SegMaps& ma, const SegMaps& mb, const CommG
   int grid = tiles < sm_count() ? tiles : sm_count();
   if (p.mode != kModeLocal) grid = sm_count();  // all CTAs take part in the reduction
   count_launch();
-  kernel<<<grid, p.gather == 4 ? 320 : 192, S::kTotal, stream>>>(ma, mb, p);
+  // warps 6-9: copiers of the staged gather / reducers of the scatter modes
+  kernel<<<grid, (p.gather == 4 || p.mode != kModeLocal) ? 320 : 192, S::kTotal, stream>>>(ma, mb, p);
   return cudaGetLastError() == cudaSuccess ? 0 : 4;
+}
+
+// Tuning of the staged gather's copier warps, read once from SLAPO_B200_AG_COPY="slices,inflight"
+// (slices per 128-row block: 1, 2 or 4; 16-byte loads in flight per thread: 8 or 16).
+struct CopyTuning { int slices, inflight; };
+static CopyTuning copy_tuning() {
+  static const CopyTuning t = [] {
+    CopyTuning v{kDefaultAgSlices, kDefaultAgInflight};
+    if (const char* e = std::getenv("SLAPO_B200_AG_COPY")) {
+      int a = 0, b = 0;
+      if (std::sscanf(e, "%d,%d", &a, &b) == 2 && (a == 1 || a == 2 || a == 4) && (b == 8 || b == 16)) {
+        v.slices = a;
+        v.inflight = b;
+      }
+    }
+    return v;
+  }();
+  return t;
 }
 
 // a_ptrs / b_ptrs: one base pointer per segment (rank) when the operand is
@@ -696,7 +772,9 @@ int launch_comm_gemm(void* const* a_ptrs, void* const* b_ptrs, int M, int N, int
                      void* const* peer_out, int* status, double wait_seconds, void* stage_dst,
                      int* chunk_flags, cudaStream_t stream) {
   if (M <= 0 || N <= 0 || K <= 0) return 0;
-  if (gather == 4 && (M + CBM - 1) / CBM > kChunkCountOffset) return 6;
+  if ((gather == 4 || mode != kModeLocal) && (M + CBM - 1) / CBM > kChunkCountOffset) return 6;
+  if (gather == 4 && mode != kModeLocal) return 1;   // warps 6-9 have one job per launch
+  if (mode != kModeLocal && peer_recv == nullptr) return 1;
   if (gather == 4 && (a_mn || stage_dst == nullptr || chunk_flags == nullptr || lda != K ||
                       seg_len % CBM != 0 || seg_len * world != M))
     return 1;
@@ -737,12 +815,20 @@ int launch_comm_gemm(void* const* a_ptrs, void* const* b_ptrs, int M, int N, int
   p.idesc = tc::instr_desc_f16(CBM, BN, bf16 ? 1 : 0, a_mn, b_mn);
   p.wait_cycles = static_cast<long long>(wait_seconds * 1.9e9);
   p.stage_dst = stage_dst; p.chunk_flags = chunk_flags; p.row_bytes = K * 2;
+  const CopyTuning tune = copy_tuning();
+  p.ag_slices = tune.slices; p.ag_inflight = tune.inflight;
   for (int r = 0; r < world; ++r) {
     p.seg_src[r] = gather == 4 ? a_ptrs[r] : nullptr;
     p.peer_flags[r] = peer_flags != nullptr ? peer_flags[r] : flags;
-    p.peer_recv[r] = peer_recv != nullptr ? peer_recv[r] : nullptr;
+    // a partial-product buffer starts with kRecvHeaderBytes of block flags (written by the
+    // peers) and arrival counters (local), zero when the buffer was allocated
+    uint8_t* recv = peer_recv != nullptr ? static_cast<uint8_t*>(peer_recv[r]) : nullptr;
+    p.peer_blk_flags[r] = reinterpret_cast<int*>(recv);
+    p.peer_recv[r] = recv != nullptr ? recv + kRecvHeaderBytes : nullptr;
     p.peer_out[r] = peer_out != nullptr ? peer_out[r] : nullptr;
   }
+  p.blk_flags = p.peer_blk_flags[rank];
+  p.blk_counters = p.blk_flags != nullptr ? p.blk_flags + kChunkCountOffset : nullptr;
 
 #define COMM_CASE(BN_, ST_)                                                                   \
   if (BN == BN_) {                                                                            \

@@ -34,6 +34,11 @@ from ..ops import native
 
 GATHER_NONE, GATHER_A_ROWS, GATHER_A_K, GATHER_B_K, GATHER_A_ROWS_STAGED = 0, 1, 2, 3, 4
 _CHUNK_WORDS = 8192   # kChunkCountOffset of csrc/comm_gemm.cu
+# A partial-product (receive) buffer of the scatter modes starts with a header: one flag per
+# (source rank, 128-row block of the owner's rows), written by the peers, then as many local
+# arrival counters (kRecvHeaderBytes of csrc/comm_gemm.cu).  Symmetric buffers are zero when
+# allocated, flags only ever grow (epoch numbers), counters return to zero.
+RECV_HEADER_BYTES = 2 * _CHUNK_WORDS * 4
 MODE_LOCAL, MODE_RS, MODE_AR = 0, 1, 2
 
 
@@ -155,7 +160,9 @@ def gemm_rs(ctx, x, w, bias=None, b_mn=False, name="rs_recv"):
     ``bias`` is added once, after the reduction.  ``b_mn``: ``w`` is ``[K, N]``."""
     t, k = x.shape
     n = w.shape[1] if b_mn else w.shape[0]
-    recv = ctx.buffer(name, t * n * x.element_size())
+    if t // 128 > _CHUNK_WORDS:
+        raise ValueError(f"{t} rows exceed the {_CHUNK_WORDS * 128} a fused reduce-scatter handles")
+    recv = ctx.buffer(name, RECV_HEADER_BYTES + t * n * x.element_size())
     y = torch.empty(t // ctx.world, n, dtype=x.dtype, device=x.device)
     comm_gemm(ctx, a_ptrs=[x.data_ptr()], b_ptrs=[w.data_ptr()], M=t, N=n, K=k, lda=x.stride(0),
               ldb=w.stride(0), a_mn=False, b_mn=b_mn, dtype=x.dtype, mode=MODE_RS,
@@ -167,7 +174,9 @@ def gemm_ar(ctx, x, w, bias=None, b_mn=False, name="ar"):
     """``all_reduce(x @ w.T)``: reduce-scatter + all-gather halves in one kernel."""
     t, k = x.shape
     n = w.shape[1] if b_mn else w.shape[0]
-    recv = ctx.buffer(name + "_recv", t * n * x.element_size())
+    if t // 128 > _CHUNK_WORDS:
+        raise ValueError(f"{t} rows exceed the {_CHUNK_WORDS * 128} a fused all-reduce handles")
+    recv = ctx.buffer(name + "_recv", RECV_HEADER_BYTES + t * n * x.element_size())
     out = ctx.buffer(name + "_out", t * n * x.element_size())
     comm_gemm(ctx, a_ptrs=[x.data_ptr()], b_ptrs=[w.data_ptr()], M=t, N=n, K=k, lda=x.stride(0),
               ldb=w.stride(0), a_mn=False, b_mn=b_mn, dtype=x.dtype, mode=MODE_AR,

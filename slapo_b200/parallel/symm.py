@@ -81,6 +81,10 @@ class SymmContext:
     def _alloc(self, name, nbytes) -> SymmBuffer:
         nbytes = _align(nbytes)
         t = self._symm.empty(nbytes, dtype=torch.uint8, device=self.device)
+        # Buffers start out zero (flag words inside them count epochs upwards), and the zeros
+        # are in memory on every rank before any peer learns the address.
+        t.zero_()
+        torch.cuda.synchronize(self.device)
         hdl = self._symm.rendezvous(t, group=self.group)
         ptrs = [int(p) for p in hdl.buffer_ptrs]
         buf = SymmBuffer(t, ptrs, hdl)
@@ -155,6 +159,15 @@ class LocalSymmContext:
                 pad[8 + r] = epoch
             if done2:
                 pad[16 + r] = epoch
+
+    def preset_block_flags(self, name, epoch, blocks_per_owner):
+        """Pretend that every other rank has written all row blocks of the current rank's rows
+        into its partial-product buffer: header flags of buffer ``name``, laid out as
+        ``[source rank][block]``."""
+        hdr = self._buffers[name][self.rank][:self.world * blocks_per_owner * 4].view(torch.int32)
+        for r in range(self.world):
+            if r != self.rank:
+                hdr[r * blocks_per_owner:(r + 1) * blocks_per_owner] = epoch
 
     @property
     def flags_ptr(self):

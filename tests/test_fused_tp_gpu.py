@@ -55,10 +55,13 @@ def test_gemm_reduce_scatter_and_all_reduce(world, mode):
     # the reduction sums 16-bit partials, like the kernel
     total = sum(p.to(torch.bfloat16).float() for p in partials) + bias.float()
     outs = [None] * world
+    recv_name = "rs_recv" if mode == "rs" else "ar_recv"
+    ctx.buffer(recv_name, ft.RECV_HEADER_BYTES + t * n * 2)   # exists before the flags are preset
     for sweep in range(2):  # sweep 0 fills every receive slot, sweep 1 reduces real data
         for r in range(world):
             ctx.as_rank(r)
             ctx.preset_flags(ctx.epoch + 1, ready=True, done=True, done2=True)
+            ctx.preset_block_flags(recv_name, ctx.epoch + 1, t // world // 128)
             if mode == "rs":
                 outs[r] = ft.gemm_rs(ctx, x[r], w[r], bias)
             else:
