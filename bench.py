@@ -263,6 +263,15 @@ def run_native(args):
         if rank == 0:
             print(prof.key_averages().table(sort_by="cuda_time_total", row_limit=40,
                                             max_name_column_width=70), file=sys.stderr)
+            # device kernels only: total ms, launches, name
+            rows = [(e.device_time_total / 1e3, e.count, e.key) for e in prof.key_averages()
+                    if getattr(e, "device_type", None) is not None
+                    and "cuda" in str(e.device_type).lower() and e.device_time_total > 0]
+            rows.sort(reverse=True)
+            print("# device kernels of one step (ms, launches, name); sum = "
+                  f"{sum(r[0] for r in rows):.2f} ms", file=sys.stderr)
+            for ms_k, cnt, key in rows[:45]:
+                print(f"#   {ms_k:9.3f} {cnt:5d}  {key[:110]}", file=sys.stderr)
     e2e = None
     if not args.no_e2e:
         host = [make_batch(vocab, local_batch, args.seq, 77 + dp_rank * 100 + i, "cpu", pin=True)

@@ -43,6 +43,30 @@ def _time(fn, iters, warmup=3):
     return float(us.item())
 
 
+def _trace_summary(rank, name, scatter=False):
+    """With SLAPO_B200_COMM_TRACE=1 the fused kernels record per-CTA time stamps; print, for the
+    last launch, each phase's median / maximum over the CTAs in microseconds after the first
+    CTA entered the kernel."""
+    if os.environ.get("SLAPO_B200_COMM_TRACE") != "1" or rank != 0:
+        return
+    tr = torch.ops.slapo_b200.comm_trace()[:148].double()
+    t0 = tr[:, 0].min()
+    names = (["entry", "reduce_first", "reduce_last", "-", "-", "tiles_done", "exit"] if scatter
+             else ["entry", "copy_first", "copy_last", "wait_begin", "wait_end", "tiles_done", "exit"])
+    out = {}
+    for i, nm in enumerate(names):
+        if nm == "-":
+            continue
+        col = tr[:, i]
+        col = col[col >= t0]
+        if col.numel():
+            rel = (col - t0) / 1e3
+            out[nm] = [round(float(rel.median()), 1), round(float(rel.max()), 1)]
+    w = tr[:, 7] / 1e3
+    out["staged_wait_us"] = [round(float(w.median()), 1), round(float(w.max()), 1)]
+    print(json.dumps({"trace": name, "median_max_us": out}), flush=True)
+
+
 def _report(rank, name, us, flops, link_bytes, **extra):
     t_flops = flops / (GEMM_PEAK_TFLOPS * 1e12) * 1e6
     t_link = link_bytes / (LINK_GBS * 1e9) * 1e6
@@ -86,6 +110,7 @@ def main():
         us = _time(lambda: ft.ag_gemm(ctx, x, w), args.iters)
         link = (world - 1) * ts * k * 2
         _report(rank, f"ag_gemm[{label}]", us, 2.0 * t * n * k, link, shape=[t, n, k], world=world)
+        _trace_summary(rank, f"ag_gemm[{label}]")
 
         def base():
             dist.all_gather_into_tensor(full, x)
@@ -103,6 +128,7 @@ def main():
         link = (world - 1) * ts * n * 2
         us = _time(lambda: ft.gemm_rs(ctx, x, w), args.iters)
         _report(rank, f"gemm_rs[{label}]", us, 2.0 * t * n * k, link, shape=[t, n, k], world=world)
+        _trace_summary(rank, f"gemm_rs[{label}]", scatter=True)
 
         def base_rs():
             dist.reduce_scatter_tensor(out, F.linear(x, w))

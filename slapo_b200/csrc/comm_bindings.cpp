@@ -47,6 +47,14 @@ void comm_gemm(std::vector<int64_t> a_ptrs, std::vector<int64_t> b_ptrs, int64_t
               "): check divisibility by the group size / 128-row blocks and 16-byte alignment");
 }
 
+at::Tensor comm_trace() {
+  auto out = at::zeros({256, 8}, at::TensorOptions().dtype(at::kLong).device(at::kCPU));
+  at::cuda::getCurrentCUDAStream().synchronize();
+  TORCH_CHECK(slapo::read_comm_trace(reinterpret_cast<unsigned long long*>(out.data_ptr<int64_t>()),
+                                     256 * 8) == 0, "reading the phase trace failed");
+  return out;
+}
+
 void peer_gather(std::vector<int64_t> src_ptrs, int64_t dst_ptr, int64_t seg_bytes, int64_t world,
                  int64_t rank, int64_t epoch, int64_t flags_ptr, std::vector<int64_t> peer_flags,
                  double wait_seconds) {
@@ -173,6 +181,7 @@ void register_comm_ops(torch::Library& m) {
         "int out_ptr, int ldo, int bias_ptr, int act, int flags_ptr, int[] peer_flags, "
         "int[] peer_recv, int[] peer_out, float wait_seconds, int stage_ptr, "
         "int chunk_flags_ptr) -> ()", &comm_gemm);
+  m.def("comm_trace() -> Tensor", &comm_trace);
   m.def("peer_gather(int[] src_ptrs, int dst_ptr, int seg_bytes, int world, int rank, int epoch, "
         "int flags_ptr, int[] peer_flags, float wait_seconds) -> ()", &peer_gather);
 }

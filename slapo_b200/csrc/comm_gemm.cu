@@ -19,11 +19,12 @@
 //                        owner's rows in turn, then block b + 1.  When a
 //                        source has finished block b of an owner it releases
 //                        the flag (source, b) in that owner's buffer header;
-//                        the owner's reducer warps (warps 6-9 of every CTA)
-//                        then pull the block from all ranks over NVLink with
-//                        wide coalesced loads (fp32 sum, optional bias) and
-//                        write the result - while the tensor core works on the
-//                        later blocks.  Only the last block is not hidden.
+//                        the owner's reducer warps (warps 6-9 of every CTA,
+//                        joined by the epilogue warps once their tiles are
+//                        stored) pull the block from all ranks over NVLink
+//                        with wide coalesced loads (fp32 sum, optional bias)
+//                        and write the result - while the tensor core works
+//                        on the later blocks.
 //   GEMM -> all-reduce   reduce-scatter as above, the reduced rows go to
 //                        every peer's output buffer and a second flag round
 //                        closes the operation.
@@ -52,8 +53,8 @@ constexpr int kMaxRanks = 8;
 constexpr int kChunkCountOffset = 8192;
 // header of a partial-product (receive) buffer: kChunkCountOffset block flags + as many counters
 constexpr int kRecvHeaderBytes = 2 * kChunkCountOffset * 4;
-constexpr int kDefaultAgSlices = 4;
-constexpr int kDefaultAgInflight = 8;
+constexpr int kDefaultAgSlices = 1;
+constexpr int kDefaultAgInflight = 16;
 constexpr int CBM = 128;
 constexpr int CBK = 64;
 
@@ -90,6 +91,7 @@ struct CommGemmParams {
   int* chunk_flags;              // local, one word per 128-row block: epoch when staged
   const void* seg_src[kMaxRanks];  // every rank's shard [seg_len, K]
   int row_bytes;                 // K * 2
+  int trace;                     // record phase time stamps (debug aid)
   int ag_slices;                 // staged gather: slices per 128-row block (1, 2 or 4)
   int ag_inflight;               // staged gather: 16-byte loads in flight per thread (8 or 16)
   // reduce-scatter / all-reduce: per (source rank, 128-row block of the owner's rows) flags in
@@ -106,6 +108,23 @@ __device__ __forceinline__ int ld_acquire_sys(const int* addr) {
   int v;
   asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(addr) : "memory");
   return v;
+}
+
+// Phase trace, a debugging aid (off unless SLAPO_B200_COMM_TRACE=1): every CTA of the last fused
+// kernel records the nanosecond timer at a few points; `read_comm_trace` copies the table out.
+//   0 kernel entry   1 copier / reducer: first unit starts   2 copier / reducer: last unit done
+//   3 producer: first wait for a staged block begins   4 ... ends   5 epilogue: last tile stored
+//   6 kernel exit    7 producer: nanoseconds spent waiting for staged blocks
+constexpr int kTraceSlots = 8;
+constexpr int kTraceCtas = 256;
+__device__ unsigned long long g_comm_trace[kTraceCtas * kTraceSlots];
+__device__ __forceinline__ unsigned long long gtimer() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+__device__ __forceinline__ void trace_mark(int on, int slot) {
+  if (on && blockIdx.x < kTraceCtas) g_comm_trace[blockIdx.x * kTraceSlots + slot] = gtimer();
 }
 
 // bounded spin on a flag written by another GPU
@@ -215,7 +234,7 @@ __device__ __forceinline__ void reduce_span(const CommGemmParams& p, int rows_pe
 #pragma unroll
         for (int r = 0; r < kW; ++r)
           if (j < n_loc)
-            raw[u][r] = *reinterpret_cast<const uint4*>(srcs[r] + static_cast<size_t>(j) * 16);
+            raw[u][r] = __ldcg(reinterpret_cast<const uint4*>(srcs[r] + static_cast<size_t>(j) * 16));
       }
     }
 #pragma unroll
@@ -229,7 +248,7 @@ __device__ __forceinline__ void reduce_span(const CommGemmParams& p, int rows_pe
           float v[8];
           // group sizes without an instantiation (3, 5, 6, 7) load source by source
           if constexpr (W == 0)
-            raw[u][r] = *reinterpret_cast<const uint4*>(srcs[r] + static_cast<size_t>(j) * 16);
+            raw[u][r] = __ldcg(reinterpret_cast<const uint4*>(srcs[r] + static_cast<size_t>(j) * 16));
           if (p.bf16) {
             const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw[u][r]);
 #pragma unroll
@@ -273,15 +292,56 @@ __device__ __forceinline__ void reduce_span(const CommGemmParams& p, int rows_pe
   }
 }
 
+// One group of 128 threads (named barrier `bar_id`, `gt` = thread index inside the group) takes
+// reduction units of this CTA until none is left.  A unit is a 32-row slice of a 128-row block of
+// this rank's rows; the CTA's units are u = blockIdx.x + k * gridDim.x in block order and `next_k`
+// is the CTA-wide counter that hands out k, so that the reducer warps (from the start) and the
+// epilogue warps (once their tiles are done) share the work.  A unit is reduced when the block's
+// flags from every source rank have arrived.
+__device__ __forceinline__ void reduce_units(const CommGemmParams& p, int rows_per_rank,
+                                             int blocks_per_owner, int gt, int bar_id, int* next_k,
+                                             volatile int* vote, volatile int* abort_flag) {
+  constexpr int kRedSlices = 4;
+  const int units = blocks_per_owner * kRedSlices;
+  for (;;) {
+    if (gt == 0) {
+      const int u = static_cast<int>(blockIdx.x) + atomicAdd(next_k, 1) * static_cast<int>(gridDim.x);
+      int w = -1;                      // -1: no unit left, 0: a wait ran out, 1: go
+      if (*abort_flag != 0) {
+        w = 0;
+      } else if (u < units) {
+        w = 1;
+        const int b = u / kRedSlices;
+        for (int src = 0; src < p.world && w == 1; ++src)
+          w = wait_flag(p.blk_flags + src * blocks_per_owner + b, p.epoch, p.wait_cycles,
+                        abort_flag) ? 1 : 0;
+      }
+      vote[0] = u;
+      vote[1] = w;
+    }
+    asm volatile("bar.sync %0, 128;" ::"r"(bar_id) : "memory");
+    const int u = vote[0], w = vote[1];
+    asm volatile("bar.sync %0, 128;" ::"r"(bar_id) : "memory");
+    if (w != 1) break;
+    const int row0 = (u / kRedSlices) * CBM + (u % kRedSlices) * (CBM / kRedSlices);
+    switch (p.world) {
+      case 2: reduce_span<2, 8>(p, rows_per_rank, row0, CBM / kRedSlices, gt, 128); break;
+      case 4: reduce_span<4, 4>(p, rows_per_rank, row0, CBM / kRedSlices, gt, 128); break;
+      case 8: reduce_span<8, 2>(p, rows_per_rank, row0, CBM / kRedSlices, gt, 128); break;
+      default: reduce_span<0, 1>(p, rows_per_rank, row0, CBM / kRedSlices, gt, 128); break;
+    }
+  }
+}
+
 // 128 threads copy n_vec 16-byte vectors, F loads in flight per thread
 template <int F>
-__device__ __forceinline__ void copy_vecs(const uint4* __restrict__ src, uint4* __restrict__ dst,
+__device__ __forceinline__ void copy_vecs(const uint4* src, uint4* dst,
                                           int64_t n_vec, int ct) {
   for (int64_t v = ct; v < n_vec; v += 128 * F) {
     uint4 tmp[F];
 #pragma unroll
     for (int q = 0; q < F; ++q)
-      if (v + q * 128 < n_vec) tmp[q] = src[v + q * 128];
+      if (v + q * 128 < n_vec) tmp[q] = __ldcg(src + v + q * 128);
 #pragma unroll
     for (int q = 0; q < F; ++q)
       if (v + q * 128 < n_vec) dst[v + q * 128] = tmp[q];
@@ -304,6 +364,8 @@ comm_gemm_kernel(const __grid_constant__ SegMaps maps_a, const __grid_constant__
   uint64_t* tmem_empty = tmem_full + 2;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tmem_empty + 2);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  __shared__ int s_red_next;          // next reduction unit of this CTA (scatter modes)
+  __shared__ int s_red_vote[2][2];    // per reducing group: unit, go / stop
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int tiles_m = (p.M + CBM - 1) / CBM;
@@ -333,7 +395,10 @@ comm_gemm_kernel(const __grid_constant__ SegMaps maps_a, const __grid_constant__
       tc::mbar_init(&tmem_empty[a], 4);
     }
     *abort_flag = 0;
+    s_red_next = 0;
     tc::fence_barrier_init();
+    trace_mark(p.trace, 0);
+    if (p.trace && blockIdx.x < kTraceCtas) g_comm_trace[blockIdx.x * kTraceSlots + 7] = 0;
     // announce: this rank has entered operation `epoch`
     if (blockIdx.x == 0 && p.world > 1) {
       for (int r = 0; r < p.world; ++r) st_release_sys(p.peer_flags[r] + p.rank, p.epoch);
@@ -355,6 +420,7 @@ comm_gemm_kernel(const __grid_constant__ SegMaps maps_a, const __grid_constant__
       uint32_t phase = 0;
       bool ok = true;
       uint32_t seen_ready = 1u << p.rank;  // peers whose ready flag has been observed
+      bool traced_first = false;
       auto need_ready = [&](int r) -> bool {
         if (seen_ready & (1u << r)) return true;
         if (!wait_flag(ready + r, p.epoch, p.wait_cycles, abort_flag)) return false;
@@ -379,9 +445,20 @@ comm_gemm_kernel(const __grid_constant__ SegMaps maps_a, const __grid_constant__
             a_row = m0 - p.rank * p.seg_len;
           } else {
             a_seg = 1;                      // staged copy in local memory
+            unsigned long long t_wait = 0;
+            if (p.trace) {
+              t_wait = gtimer();
+              if (!traced_first) g_comm_trace[(blockIdx.x % kTraceCtas) * kTraceSlots + 3] = t_wait;
+            }
             if (!wait_flag(p.chunk_flags + m_blk, p.epoch, p.wait_cycles, abort_flag)) {
               ok = false;
               break;
+            }
+            if (p.trace) {
+              const unsigned long long t_end = gtimer();
+              if (!traced_first) g_comm_trace[(blockIdx.x % kTraceCtas) * kTraceSlots + 4] = t_end;
+              g_comm_trace[(blockIdx.x % kTraceCtas) * kTraceSlots + 7] += t_end - t_wait;
+              traced_first = true;
             }
             asm volatile("fence.proxy.async;" ::: "memory");
           }
@@ -469,7 +546,7 @@ comm_gemm_kernel(const __grid_constant__ SegMaps maps_a, const __grid_constant__
       int* chunk_count = p.chunk_flags + kChunkCountOffset;
       const int64_t slice_vec = static_cast<int64_t>(slice_rows) * p.row_bytes / 16;
       int u = 0;
-      bool ok = true;
+      bool ok = true, marked = false;
       for (int o_idx = 1; o_idx < p.world && ok; ++o_idx) {
         const int owner = (p.rank + o_idx) % p.world;
         bool owner_ready = false;
@@ -492,6 +569,7 @@ comm_gemm_kernel(const __grid_constant__ SegMaps maps_a, const __grid_constant__
                 (static_cast<int64_t>(m_blk) * CBM + sl * slice_rows) * p.row_bytes);
             // 8 or 16 16-byte loads per thread are issued before the first store: 128 threads
             // keep 16 or 32 KB per SM on the wire to cover the NVLink round trip.
+            if (ct == 0 && !marked) { trace_mark(p.trace, 1); marked = true; }
             if (p.ag_inflight == 16) copy_vecs<16>(src, dst, slice_vec, ct);
             else copy_vecs<8>(src, dst, slice_vec, ct);
             __threadfence();
@@ -508,34 +586,18 @@ comm_gemm_kernel(const __grid_constant__ SegMaps maps_a, const __grid_constant__
           }
         }
       }
+      if (ct == 0) trace_mark(p.trace, 2);
     } else if (scatter) {
       // ------------------------------ reducer warps -------------------------------
-      // Reduce-scatter / all-reduce: as soon as the b-th 128-row block of this rank's rows is
-      // complete in every rank's partial-product buffer (flags written by the epilogue warps of
-      // all ranks), a 32-row slice of it is pulled from all ranks over NVLink, summed in fp32,
+      // Reduce-scatter / all-reduce: as soon as a 128-row block of this rank's rows is complete
+      // in every rank's partial-product buffer (flags written by the epilogue warps of all
+      // ranks), 32-row slices of it are pulled from all ranks over NVLink, summed in fp32,
       // finished with bias / activation and written out - while the main loop computes the
-      // later blocks.  Only the last block's reduction is not hidden behind the GEMM.
-      const int ct = threadIdx.x - 192;
-      constexpr int kRedSlices = 4;
-      const int units = blocks_per_owner * kRedSlices;
-      for (int u = blockIdx.x; u < units; u += gridDim.x) {
-        const int b = u / kRedSlices, sl = u % kRedSlices;
-        int w = 1;
-        if (ct == 0) {
-          for (int src = 0; src < p.world && w; ++src)
-            w = wait_flag(p.blk_flags + src * blocks_per_owner + b, p.epoch, p.wait_cycles,
-                          abort_flag) ? 1 : 0;
-        }
-        w = __syncthreads_or_named(w);
-        if (!w) break;
-        const int row0 = b * CBM + sl * (CBM / kRedSlices);
-        switch (p.world) {
-          case 2: reduce_span<2, 4>(p, rows_per_rank, row0, CBM / kRedSlices, ct, 128); break;
-          case 4: reduce_span<4, 4>(p, rows_per_rank, row0, CBM / kRedSlices, ct, 128); break;
-          case 8: reduce_span<8, 2>(p, rows_per_rank, row0, CBM / kRedSlices, ct, 128); break;
-          default: reduce_span<0, 1>(p, rows_per_rank, row0, CBM / kRedSlices, ct, 128); break;
-        }
-      }
+      // later blocks (see reduce_units).
+      trace_mark(threadIdx.x == 192 ? p.trace : 0, 1);
+      reduce_units(p, rows_per_rank, blocks_per_owner, threadIdx.x - 192, 2, &s_red_next,
+                   s_red_vote[0], abort_flag);
+      trace_mark(threadIdx.x == 192 ? p.trace : 0, 2);
       // all-reduce: the reduced rows stored to the peers must be visible before done2
       if (p.mode == kModeAllReduce) __threadfence_system();
     }
@@ -622,10 +684,9 @@ comm_gemm_kernel(const __grid_constant__ SegMaps maps_a, const __grid_constant__
         __threadfence();
         __syncwarp();
         if (lane == 0) {
-          const int slot = owner * blocks_per_owner + (m_blk - owner * blocks_per_owner);
-          const int prev = atomicAdd(p.blk_counters + slot, 1);
+          const int prev = atomicAdd(p.blk_counters + m_blk, 1);
           if (prev + 1 == tiles_n * 4) {
-            atomicExch(p.blk_counters + slot, 0);
+            atomicExch(p.blk_counters + m_blk, 0);
             __threadfence_system();
             st_release_sys(p.peer_blk_flags[owner] + p.rank * blocks_per_owner +
                                (m_blk - owner * blocks_per_owner),
@@ -633,6 +694,14 @@ comm_gemm_kernel(const __grid_constant__ SegMaps maps_a, const __grid_constant__
           }
         }
       }
+    }
+    trace_mark(threadIdx.x == 64 ? p.trace : 0, 5);
+    if (scatter) {
+      // tiles stored: the four epilogue warps become a second reducing group (all four enter,
+      // whatever their own `ok`: the group's leader looks at the CTA-wide abort flag)
+      reduce_units(p, rows_per_rank, blocks_per_owner, threadIdx.x - 64, 3, &s_red_next,
+                   s_red_vote[1], abort_flag);
+      if (p.mode == kModeAllReduce) __threadfence_system();
     }
   }
 
@@ -658,6 +727,7 @@ comm_gemm_kernel(const __grid_constant__ SegMaps maps_a, const __grid_constant__
 
   // ------------------------------ teardown ------------------------------------
   __syncthreads();
+  trace_mark(threadIdx.x == 0 ? p.trace : 0, 6);
   if (threadIdx.x == 0 && *abort_flag != 0 && p.status != nullptr) atomicExch(p.status, 4);
   if (warp == 1) {
     tc::fence_after_sync();
@@ -763,6 +833,12 @@ static CopyTuning copy_tuning() {
   return t;
 }
 
+// Copies the phase trace of the last fused kernel ([kTraceCtas][kTraceSlots] 64-bit words) to the host.
+int read_comm_trace(unsigned long long* host, int n_words) {
+  const int n = n_words < kTraceCtas * kTraceSlots ? n_words : kTraceCtas * kTraceSlots;
+  return cudaMemcpyFromSymbol(host, g_comm_trace, static_cast<size_t>(n) * 8) == cudaSuccess ? 0 : 1;
+}
+
 // a_ptrs / b_ptrs: one base pointer per segment (rank) when the operand is
 // gathered, else only entry 0 is used.  Shapes follow gemm.cu (a_mn / b_mn).
 int launch_comm_gemm(void* const* a_ptrs, void* const* b_ptrs, int M, int N, int K, int lda,
@@ -817,6 +893,11 @@ int launch_comm_gemm(void* const* a_ptrs, void* const* b_ptrs, int M, int N, int
   p.stage_dst = stage_dst; p.chunk_flags = chunk_flags; p.row_bytes = K * 2;
   const CopyTuning tune = copy_tuning();
   p.ag_slices = tune.slices; p.ag_inflight = tune.inflight;
+  static const bool trace_on = [] {
+    const char* e = std::getenv("SLAPO_B200_COMM_TRACE");
+    return e != nullptr && e[0] == '1';
+  }();
+  p.trace = trace_on ? 1 : 0;
   for (int r = 0; r < world; ++r) {
     p.seg_src[r] = gather == 4 ? a_ptrs[r] : nullptr;
     p.peer_flags[r] = peer_flags != nullptr ? peer_flags[r] : flags;

@@ -59,6 +59,10 @@ int launch_comm_gemm(void* const* a_ptrs, void* const* b_ptrs, int M, int N, int
                      void* const* peer_out, int* status, double wait_seconds, void* stage_dst,
                      int* chunk_flags, cudaStream_t stream);
 
+// Phase trace of the last fused GEMM + collective kernel (recorded when the environment has
+// SLAPO_B200_COMM_TRACE=1): [256 CTAs][8 slots] nanosecond time stamps, see comm_gemm.cu.
+int read_comm_trace(unsigned long long* host, int n_words);
+
 // dst = concatenation of every rank's segment, pulled over NVLink (comm_gemm.cu)
 int launch_peer_gather(void* const* src_ptrs, void* dst, int64_t seg_bytes, int world, int rank,
                        int epoch, int* flags, int* const* peer_flags, int* status,
