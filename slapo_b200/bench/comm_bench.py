@@ -62,6 +62,10 @@ def _trace_summary(rank, name, scatter=False):
         if col.numel():
             rel = (col - t0) / 1e3
             out[nm] = [round(float(rel.median()), 1), round(float(rel.max()), 1)]
+            if nm == "tiles_done":   # spread over the CTAs: deciles and the five slowest CTAs
+                q = torch.quantile(rel, torch.linspace(0, 1, 11, dtype=rel.dtype))
+                out["tiles_done_deciles"] = [round(float(v), 1) for v in q]
+                out["slowest_ctas"] = [int(i) for i in torch.argsort(tr[:, i], descending=True)[:5]]
     w = tr[:, 7] / 1e3
     out["staged_wait_us"] = [round(float(w.median()), 1), round(float(w.max()), 1)]
     print(json.dumps({"trace": name, "median_max_us": out}), flush=True)

@@ -17,9 +17,9 @@
 //                        this rank's symmetric partial buffer.  Tiles are
 //                        visited row block by row block: block b of every
 //                        owner's rows in turn, then block b + 1.  When a
-//                        source has finished block b of an owner it releases
-//                        the flag (source, b) in that owner's buffer header;
-//                        the owner's reducer warps (warps 6-9 of every CTA,
+//                        source has finished a block it raises the block's
+//                        flag in its own buffer header, which the owner
+//                        polls over NVLink; the owner's reducer warps (warps 6-9 of every CTA,
 //                        joined by the epilogue warps once their tiles are
 //                        stored) pull the block from all ranks over NVLink
 //                        with wide coalesced loads (fp32 sum, optional bias)
@@ -34,7 +34,7 @@
 //   ready[src] >= epoch   rank src has entered this operation, i.e. everything
 //                         it launched before (producers of its buffers,
 //                         consumers of what we are about to overwrite) is done
-//   blk[src][b] >= epoch  rank src has written block b of my rows (partial-buffer header)
+//   blk[m] >= epoch       (header of rank src's partial buffer) src has stored row block m
 //   done2[src] >= epoch   rank src has delivered its reduced rows (all-reduce)
 // Every wait is bounded; on time-out the kernel records an error code in the
 // device status word, stops issuing work and leaves (TMEM freed).
@@ -94,8 +94,9 @@ struct CommGemmParams {
   int trace;                     // record phase time stamps (debug aid)
   int ag_slices;                 // staged gather: slices per 128-row block (1, 2 or 4)
   int ag_inflight;               // staged gather: 16-byte loads in flight per thread (8 or 16)
-  // reduce-scatter / all-reduce: per (source rank, 128-row block of the owner's rows) flags in
-  // the header of every rank's partial-product buffer, and the local arrival counters
+  // reduce-scatter / all-reduce: the header of every rank's partial-product buffer holds one
+  // flag per 128-row block of that buffer (epoch when all its tiles were stored; owners poll the
+  // flags of their rows in every rank's header) and the local arrival counters
   int* blk_flags;
   int* peer_blk_flags[kMaxRanks];
   int* blk_counters;
@@ -312,9 +313,13 @@ __device__ __forceinline__ void reduce_units(const CommGemmParams& p, int rows_p
       } else if (u < units) {
         w = 1;
         const int b = u / kRedSlices;
-        for (int src = 0; src < p.world && w == 1; ++src)
-          w = wait_flag(p.blk_flags + src * blocks_per_owner + b, p.epoch, p.wait_cycles,
-                        abort_flag) ? 1 : 0;
+        // flag of block b of this rank's rows in every source's header (a word of the peer's
+        // memory, polled over NVLink); the own one last, it is the last to be computed
+        for (int i = 1; i <= p.world && w == 1; ++i) {
+          const int src = (p.rank + i) % p.world;
+          w = wait_flag(p.peer_blk_flags[src] + p.rank * blocks_per_owner + b, p.epoch,
+                        p.wait_cycles, abort_flag) ? 1 : 0;
+        }
       }
       vote[0] = u;
       vote[1] = w;
@@ -579,7 +584,6 @@ comm_gemm_kernel(const __grid_constant__ SegMaps maps_a, const __grid_constant__
               const int prev = slices > 1 ? atomicAdd(chunk_count + m_blk, 1) : 0;
               if (prev + 1 == slices) {
                 if (slices > 1) atomicExch(chunk_count + m_blk, 0);
-                __threadfence();
                 st_release_sys(p.chunk_flags + m_blk, p.epoch);
               }
             }
@@ -679,18 +683,17 @@ comm_gemm_kernel(const __grid_constant__ SegMaps maps_a, const __grid_constant__
       __syncwarp();
       if (lane == 0) tc::mbar_arrive(&tmem_empty[acc]);
       if (scatter) {
-        // publish: make this warp's stores visible, count it; the warp that completes the
-        // row block (all column tiles) releases the flag of (this rank, block) at the owner
+        // publish: make this warp's stores visible, count it; the warp that completes the row
+        // block (all column tiles) raises the block's flag in THIS rank's buffer header.  The
+        // owner polls that word over NVLink (see reduce_units), so the tensor-core pipeline
+        // never waits for a store to a peer to be acknowledged.
         __threadfence();
         __syncwarp();
         if (lane == 0) {
           const int prev = atomicAdd(p.blk_counters + m_blk, 1);
           if (prev + 1 == tiles_n * 4) {
             atomicExch(p.blk_counters + m_blk, 0);
-            __threadfence_system();
-            st_release_sys(p.peer_blk_flags[owner] + p.rank * blocks_per_owner +
-                               (m_blk - owner * blocks_per_owner),
-                           p.epoch);
+            st_release_sys(p.blk_flags + m_blk, p.epoch);
           }
         }
       }

@@ -161,13 +161,14 @@ class LocalSymmContext:
                 pad[16 + r] = epoch
 
     def preset_block_flags(self, name, epoch, blocks_per_owner):
-        """Pretend that every other rank has written all row blocks of the current rank's rows
-        into its partial-product buffer: header flags of buffer ``name``, laid out as
-        ``[source rank][block]``."""
-        hdr = self._buffers[name][self.rank][:self.world * blocks_per_owner * 4].view(torch.int32)
+        """Pretend that every other rank has stored all row blocks of the current rank's rows in
+        its partial-product buffer: the flags of those blocks in the header of every other
+        rank's buffer ``name`` (one word per 128-row block of the ``[M, N]`` buffer)."""
+        lo = self.rank * blocks_per_owner
         for r in range(self.world):
             if r != self.rank:
-                hdr[r * blocks_per_owner:(r + 1) * blocks_per_owner] = epoch
+                hdr = self._buffers[name][r][:self.world * blocks_per_owner * 4].view(torch.int32)
+                hdr[lo:lo + blocks_per_owner] = epoch
 
     @property
     def flags_ptr(self):
