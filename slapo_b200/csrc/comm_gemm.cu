@@ -24,7 +24,10 @@
 //                        stored) pull the block from all ranks over NVLink
 //                        with wide coalesced loads (fp32 sum, optional bias)
 //                        and write the result - while the tensor core works
-//                        on the later blocks.
+//                        on the later blocks.  Once a CTA's main loop is over
+//                        the pulled vectors are parked in the operand
+//                        pipeline's shared memory (asynchronous copies, 192
+//                        KB per SM on the wire) instead of in registers.
 //   GEMM -> all-reduce   reduce-scatter as above, the reduced rows go to
 //                        every peer's output buffer and a second flag round
 //                        closes the operation.
@@ -147,13 +150,14 @@ __device__ __forceinline__ bool wait_flag(const int* addr, int epoch, long long 
   return true;
 }
 
-// all 128 copier threads agree on a predicate computed by one of them
+// all NT threads of the copier / reducer group agree on a predicate computed by its first thread
+template <int NT = 128>
 __device__ __forceinline__ int __syncthreads_or_named(int v) {
   __shared__ int s_copier_vote;
   if (threadIdx.x == 192) s_copier_vote = v;
-  asm volatile("bar.sync 2, 128;" ::: "memory");
+  asm volatile("bar.sync 2, %0;" ::"n"(NT) : "memory");
   const int r = s_copier_vote;
-  asm volatile("bar.sync 2, 128;" ::: "memory");
+  asm volatile("bar.sync 2, %0;" ::"n"(NT) : "memory");
   return r;
 }
 
@@ -163,6 +167,8 @@ struct CommSmem {
   static constexpr int kBBytes = BN * CBK * 2;
   static constexpr int kBarOffset = STAGES * (kABytes + kBBytes);
   static constexpr int kTotal = kBarOffset + 256 + 1024;
+  // after the main loop the reduction parks pulled vectors in the pipeline's memory (2 x 96 KB)
+  static_assert(kBarOffset >= 192 * 1024, "operand pipeline smaller than the reduction's staging area");
 };
 
 __device__ __forceinline__ uint32_t cpack2(float a, float b, int bf16) {
@@ -293,6 +299,95 @@ __device__ __forceinline__ void reduce_span(const CommGemmParams& p, int rows_pe
   }
 }
 
+// The same reduction with the pulled vectors parked in shared memory instead of registers, for
+// the time after the main loop when the operand pipeline's 192 KB are free: every thread of a
+// 128-thread group owns 768 bytes of the group's 96 KB and fills them with 48 asynchronous
+// 16-byte copies (48 / W vectors from each of the W sources) before it waits - 96 KB per group on
+// the wire instead of the 32 KB that registers hold, which turns the pull from round-trip-bound
+// into bandwidth-bound.  A thread only reads back what it copied itself, so the copies need no
+// barrier.  `region` = shared-memory address of the group's 96 KB.
+template <int W>
+__device__ __forceinline__ void reduce_span_smem(const CommGemmParams& p, int rows_per_rank,
+                                                 int row0, int nrows, int gt, uint32_t region) {
+  constexpr int U = 48 / W;
+  const unsigned vpr = static_cast<unsigned>(p.N) / 8u;
+  const unsigned n_loc = static_cast<unsigned>(nrows) * vpr;
+  const int64_t my_off = (static_cast<int64_t>(p.rank) * rows_per_rank + row0) * p.N;
+  const uint8_t* srcs[W];
+#pragma unroll
+  for (int r = 0; r < W; ++r) {
+    int src = p.rank + 1 + r;
+    if (src >= W) src -= W;
+    srcs[r] = static_cast<const uint8_t*>(p.peer_recv[src]) + my_off * 2;
+  }
+  const uint32_t mine = region + static_cast<uint32_t>(gt) * 16u;   // slot (u, r) at + (u * W + r) * 2048
+  for (unsigned j0 = gt; j0 < n_loc; j0 += 128u * U) {
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const unsigned j = j0 + u * 128u;
+      if (j < n_loc) {
+#pragma unroll
+        for (int r = 0; r < W; ++r)
+          asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(mine + (u * W + r) * 2048u),
+                       "l"(srcs[r] + static_cast<size_t>(j) * 16)
+                       : "memory");
+      }
+    }
+    asm volatile("cp.async.commit_group;" ::: "memory");
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
+#pragma unroll 2
+    for (int u = 0; u < U; ++u) {
+      const unsigned j = j0 + u * 128u;
+      if (j >= n_loc) break;
+      float acc8[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+      for (int r = 0; r < W; ++r) {
+        uint4 raw;
+        asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];"
+                     : "=r"(raw.x), "=r"(raw.y), "=r"(raw.z), "=r"(raw.w)
+                     : "r"(mine + (u * W + r) * 2048u));
+        float v[8];
+        if (p.bf16) {
+          const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+          for (int k = 0; k < 4; ++k) { float2 f = __bfloat1622float2(h[k]); v[2 * k] = f.x; v[2 * k + 1] = f.y; }
+        } else {
+          const __half2* h = reinterpret_cast<const __half2*>(&raw);
+#pragma unroll
+          for (int k = 0; k < 4; ++k) { float2 f = __half22float2(h[k]); v[2 * k] = f.x; v[2 * k + 1] = f.y; }
+        }
+#pragma unroll
+        for (int k = 0; k < 8; ++k) acc8[k] += v[k];
+      }
+      const unsigned lr = j / vpr;
+      const int col = static_cast<int>(j - lr * vpr) * 8;
+      if (p.bias != nullptr) {
+#pragma unroll
+        for (int k = 0; k < 8; ++k) acc8[k] += cload(p.bias, col + k, p.bf16);
+      }
+      if (p.act >= 0) {
+#pragma unroll
+        for (int k = 0; k < 8; ++k) acc8[k] = act_fwd(acc8[k], p.act);
+      }
+      const int64_t lrow = row0 + static_cast<int>(lr);
+      if (p.mode == kModeReduceScatter) {
+        void* o = static_cast<uint8_t*>(p.out) + (lrow * p.ldo + col) * 2;
+        if (p.bf16) Vec8<__nv_bfloat16>::store(static_cast<__nv_bfloat16*>(o), acc8);
+        else Vec8<__half>::store(static_cast<__half*>(o), acc8);
+      } else {
+        const int64_t grow = static_cast<int64_t>(p.rank) * rows_per_rank + lrow;
+        for (int r = 0; r < W; ++r) {
+          int peer = p.rank + r;
+          if (peer >= W) peer -= W;
+          void* o = static_cast<uint8_t*>(p.peer_out[peer]) + (grow * p.ldo + col) * 2;
+          if (p.bf16) Vec8<__nv_bfloat16>::store(static_cast<__nv_bfloat16*>(o), acc8);
+          else Vec8<__half>::store(static_cast<__half*>(o), acc8);
+        }
+      }
+    }
+  }
+}
+
 // One group of 128 threads (named barrier `bar_id`, `gt` = thread index inside the group) takes
 // reduction units of this CTA until none is left.  A unit is a 32-row slice of a 128-row block of
 // this rank's rows; the CTA's units are u = blockIdx.x + k * gridDim.x in block order and `next_k`
@@ -301,34 +396,39 @@ __device__ __forceinline__ void reduce_span(const CommGemmParams& p, int rows_pe
 // flags from every source rank have arrived.
 __device__ __forceinline__ void reduce_units(const CommGemmParams& p, int rows_per_rank,
                                              int blocks_per_owner, int gt, int bar_id, int* next_k,
-                                             volatile int* vote, volatile int* abort_flag) {
+                                             volatile int* vote, volatile int* abort_flag,
+                                             volatile int* pipe_free, uint32_t region) {
   constexpr int kRedSlices = 4;
   const int units = blocks_per_owner * kRedSlices;
   for (;;) {
     if (gt == 0) {
       const int u = static_cast<int>(blockIdx.x) + atomicAdd(next_k, 1) * static_cast<int>(gridDim.x);
-      int w = -1;                      // -1: no unit left, 0: a wait ran out, 1: go
-      if (*abort_flag != 0) {
-        w = 0;
-      } else if (u < units) {
-        w = 1;
-        const int b = u / kRedSlices;
-        // flag of block b of this rank's rows in every source's header (a word of the peer's
-        // memory, polled over NVLink); the own one last, it is the last to be computed
-        for (int i = 1; i <= p.world && w == 1; ++i) {
-          const int src = (p.rank + i) % p.world;
-          w = wait_flag(p.peer_blk_flags[src] + p.rank * blocks_per_owner + b, p.epoch,
-                        p.wait_cycles, abort_flag) ? 1 : 0;
-        }
-      }
       vote[0] = u;
-      vote[1] = w;
+      vote[1] = *abort_flag != 0 ? 0 : (u < units ? 1 : -1);   // 0 stop (error), -1 no unit left
+      vote[2] = *pipe_free;   // the main loop of this CTA is over: its shared memory is free
     }
     asm volatile("bar.sync %0, 128;" ::"r"(bar_id) : "memory");
-    const int u = vote[0], w = vote[1];
+    const int u = vote[0];
+    if (vote[1] == 1 && gt < p.world) {
+      // flag of block b of this rank's rows in every source's header (a word of the peer's
+      // memory, polled over NVLink): one thread per source, so the round trips overlap
+      const int src = (p.rank + 1 + gt) % p.world;
+      if (!wait_flag(p.peer_blk_flags[src] + p.rank * blocks_per_owner + u / kRedSlices, p.epoch,
+                     p.wait_cycles, abort_flag))
+        vote[1] = 0;
+    }
+    asm volatile("bar.sync %0, 128;" ::"r"(bar_id) : "memory");
+    const int w = vote[1];
+    const int in_smem = vote[2];
     asm volatile("bar.sync %0, 128;" ::"r"(bar_id) : "memory");
     if (w != 1) break;
     const int row0 = (u / kRedSlices) * CBM + (u % kRedSlices) * (CBM / kRedSlices);
+    if (in_smem && (p.world == 2 || p.world == 4 || p.world == 8)) {
+      if (p.world == 2) reduce_span_smem<2>(p, rows_per_rank, row0, CBM / kRedSlices, gt, region);
+      else if (p.world == 4) reduce_span_smem<4>(p, rows_per_rank, row0, CBM / kRedSlices, gt, region);
+      else reduce_span_smem<8>(p, rows_per_rank, row0, CBM / kRedSlices, gt, region);
+      continue;
+    }
     switch (p.world) {
       case 2: reduce_span<2, 8>(p, rows_per_rank, row0, CBM / kRedSlices, gt, 128); break;
       case 4: reduce_span<4, 4>(p, rows_per_rank, row0, CBM / kRedSlices, gt, 128); break;
@@ -338,23 +438,24 @@ __device__ __forceinline__ void reduce_units(const CommGemmParams& p, int rows_p
   }
 }
 
-// 128 threads copy n_vec 16-byte vectors, F loads in flight per thread
-template <int F>
-__device__ __forceinline__ void copy_vecs(const uint4* src, uint4* dst,
-                                          int64_t n_vec, int ct) {
-  for (int64_t v = ct; v < n_vec; v += 128 * F) {
+// NT threads copy n_vec 16-byte vectors, F loads in flight per thread
+template <int F, int NT>
+__device__ __forceinline__ void copy_vecs(const uint4* src, uint4* dst, int64_t n_vec, int ct) {
+  for (int64_t v = ct; v < n_vec; v += NT * F) {
     uint4 tmp[F];
 #pragma unroll
     for (int q = 0; q < F; ++q)
-      if (v + q * 128 < n_vec) tmp[q] = __ldcg(src + v + q * 128);
+      if (v + q * NT < n_vec) tmp[q] = __ldcg(src + v + q * NT);
 #pragma unroll
     for (int q = 0; q < F; ++q)
-      if (v + q * 128 < n_vec) dst[v + q * 128] = tmp[q];
+      if (v + q * NT < n_vec) dst[v + q * NT] = tmp[q];
   }
 }
 
-template <int BN, int STAGES, bool A_MN, bool B_MN>
-__global__ void __launch_bounds__(320, 1)
+// CW: warps 6 .. 5 + CW are the copier (staged gather, CW = 8) or reducer (scatter modes, CW = 4)
+// warps; kernels without either are launched with the first six warps only.
+template <int BN, int STAGES, bool A_MN, bool B_MN, int CW>
+__global__ void __launch_bounds__(192 + CW * 32, 1)
 comm_gemm_kernel(const __grid_constant__ SegMaps maps_a, const __grid_constant__ SegMaps maps_b,
                  const CommGemmParams p) {
   using S = CommSmem<BN, STAGES>;
@@ -370,7 +471,8 @@ comm_gemm_kernel(const __grid_constant__ SegMaps maps_a, const __grid_constant__
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tmem_empty + 2);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
   __shared__ int s_red_next;          // next reduction unit of this CTA (scatter modes)
-  __shared__ int s_red_vote[2][2];    // per reducing group: unit, go / stop
+  __shared__ int s_red_vote[2][4];    // per reducing group: unit, go / stop, pipeline memory free
+  __shared__ int s_pipe_free;         // the main loop is over, the operand pipeline's memory is free
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int tiles_m = (p.M + CBM - 1) / CBM;
@@ -401,6 +503,7 @@ comm_gemm_kernel(const __grid_constant__ SegMaps maps_a, const __grid_constant__
     }
     *abort_flag = 0;
     s_red_next = 0;
+    s_pipe_free = 0;
     tc::fence_barrier_init();
     trace_mark(p.trace, 0);
     if (p.trace && blockIdx.x < kTraceCtas) g_comm_trace[blockIdx.x * kTraceSlots + 7] = 0;
@@ -542,6 +645,7 @@ comm_gemm_kernel(const __grid_constant__ SegMaps maps_a, const __grid_constant__
     // thread) and published block by block; the producer warps of all CTAs
     // read staged blocks with local TMA loads.
     if (staged && p.world > 1) {
+      if constexpr (CW == 8) {
       const int ct = threadIdx.x - 192;
       // A 128-row block is copied as `slices` slices by (usually) different CTAs, units in
       // (block, slice) order, so that the first blocks are complete after a few NVLink round
@@ -561,7 +665,7 @@ comm_gemm_kernel(const __grid_constant__ SegMaps maps_a, const __grid_constant__
             if (!owner_ready) {
               int w = 1;
               if (ct == 0) w = wait_flag(ready + owner, p.epoch, p.wait_cycles, abort_flag) ? 1 : 0;
-              w = __syncthreads_or_named(w);
+              w = __syncthreads_or_named<CW * 32>(w);
               if (!w) { ok = false; break; }
               owner_ready = true;
             }
@@ -572,13 +676,13 @@ comm_gemm_kernel(const __grid_constant__ SegMaps maps_a, const __grid_constant__
             uint4* dst = reinterpret_cast<uint4*>(
                 static_cast<uint8_t*>(p.stage_dst) +
                 (static_cast<int64_t>(m_blk) * CBM + sl * slice_rows) * p.row_bytes);
-            // 8 or 16 16-byte loads per thread are issued before the first store: 128 threads
-            // keep 16 or 32 KB per SM on the wire to cover the NVLink round trip.
+            // 8 or 16 16-byte loads per thread are issued before the first store: with 256
+            // threads that keeps 32 or 64 KB per SM on the wire to cover the NVLink round trip.
             if (ct == 0 && !marked) { trace_mark(p.trace, 1); marked = true; }
-            if (p.ag_inflight == 16) copy_vecs<16>(src, dst, slice_vec, ct);
-            else copy_vecs<8>(src, dst, slice_vec, ct);
+            if (p.ag_inflight == 16) copy_vecs<16, CW * 32>(src, dst, slice_vec, ct);
+            else copy_vecs<8, CW * 32>(src, dst, slice_vec, ct);
             __threadfence();
-            asm volatile("bar.sync 2, 128;" ::: "memory");
+            asm volatile("bar.sync 2, %0;" ::"n"(CW * 32) : "memory");
             if (ct == 0) {
               // the copier that completes the block publishes it
               const int prev = slices > 1 ? atomicAdd(chunk_count + m_blk, 1) : 0;
@@ -591,6 +695,7 @@ comm_gemm_kernel(const __grid_constant__ SegMaps maps_a, const __grid_constant__
         }
       }
       if (ct == 0) trace_mark(p.trace, 2);
+      }
     } else if (scatter) {
       // ------------------------------ reducer warps -------------------------------
       // Reduce-scatter / all-reduce: as soon as a 128-row block of this rank's rows is complete
@@ -598,12 +703,14 @@ comm_gemm_kernel(const __grid_constant__ SegMaps maps_a, const __grid_constant__
       // ranks), 32-row slices of it are pulled from all ranks over NVLink, summed in fp32,
       // finished with bias / activation and written out - while the main loop computes the
       // later blocks (see reduce_units).
-      trace_mark(threadIdx.x == 192 ? p.trace : 0, 1);
-      reduce_units(p, rows_per_rank, blocks_per_owner, threadIdx.x - 192, 2, &s_red_next,
-                   s_red_vote[0], abort_flag);
-      trace_mark(threadIdx.x == 192 ? p.trace : 0, 2);
-      // all-reduce: the reduced rows stored to the peers must be visible before done2
-      if (p.mode == kModeAllReduce) __threadfence_system();
+      if constexpr (CW == 4) {
+        trace_mark(threadIdx.x == 192 ? p.trace : 0, 1);
+        reduce_units(p, rows_per_rank, blocks_per_owner, threadIdx.x - 192, 2, &s_red_next,
+                     s_red_vote[0], abort_flag, &s_pipe_free, tc::smem_u32(smem));
+        trace_mark(threadIdx.x == 192 ? p.trace : 0, 2);
+        // all-reduce: the reduced rows stored to the peers must be visible before done2
+        if (p.mode == kModeAllReduce) __threadfence_system();
+      }
     }
   } else {
     // ------------------------------ epilogue ----------------------------------
@@ -702,9 +809,20 @@ comm_gemm_kernel(const __grid_constant__ SegMaps maps_a, const __grid_constant__
     if (scatter) {
       // tiles stored: the four epilogue warps become a second reducing group (all four enter,
       // whatever their own `ok`: the group's leader looks at the CTA-wide abort flag)
-      reduce_units(p, rows_per_rank, blocks_per_owner, threadIdx.x - 64, 3, &s_red_next,
-                   s_red_vote[1], abort_flag);
-      if (p.mode == kModeAllReduce) __threadfence_system();
+      if constexpr (CW == 4) {
+        // Every accumulator of this CTA has been read, so every MMA has completed and every
+        // TMA load has landed: the operand pipeline's shared memory is free for the reduction
+        // (96 KB per group).  Not after an error: loads may still be in flight then.
+        asm volatile("bar.sync 3, 128;" ::: "memory");
+        if (threadIdx.x == 64 && *abort_flag == 0) {
+          asm volatile("fence.proxy.async;" ::: "memory");
+          s_pipe_free = 1;
+        }
+        asm volatile("bar.sync 3, 128;" ::: "memory");
+        reduce_units(p, rows_per_rank, blocks_per_owner, threadIdx.x - 64, 3, &s_red_next,
+                     s_red_vote[1], abort_flag, &s_pipe_free, tc::smem_u32(smem) + 96 * 1024);
+        if (p.mode == kModeAllReduce) __threadfence_system();
+      }
     }
   }
 
@@ -797,11 +915,11 @@ int launch_peer_gather(void* const* src_ptrs, void* dst, int64_t seg_bytes, int 
 }
 
 // ------------------------------------------------------------------------ //
-template <int BN, int STAGES, bool A_MN, bool B_MN>
-static int launch_comm_variant(const SegMaps& ma, const SegMaps& mb, const CommGemmParams& p,
-                               cudaStream_t stream) {
+template <int BN, int STAGES, bool A_MN, bool B_MN, int CW>
+static int launch_comm_kernel(const SegMaps& ma, const SegMaps& mb, const CommGemmParams& p,
+                              int grid, int threads, cudaStream_t stream) {
   using S = CommSmem<BN, STAGES>;
-  auto kernel = comm_gemm_kernel<BN, STAGES, A_MN, B_MN>;
+  auto kernel = comm_gemm_kernel<BN, STAGES, A_MN, B_MN, CW>;
   static bool configured = false;
   if (!configured) {
     if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, S::kTotal) !=
@@ -809,13 +927,25 @@ static int launch_comm_variant(const SegMaps& ma, const SegMaps& mb, const CommG
       return 3;
     configured = true;
   }
+  count_launch();
+  kernel<<<grid, threads, S::kTotal, stream>>>(ma, mb, p);
+  return cudaGetLastError() == cudaSuccess ? 0 : 4;
+}
+
+template <int BN, int STAGES, bool A_MN, bool B_MN>
+static int launch_comm_variant(const SegMaps& ma, const SegMaps& mb, const CommGemmParams& p,
+                               cudaStream_t stream) {
   const int tiles = ((p.M + CBM - 1) / CBM) * ((p.N + BN - 1) / BN);
   int grid = tiles < sm_count() ? tiles : sm_count();
   if (p.mode != kModeLocal) grid = sm_count();  // all CTAs take part in the reduction
-  count_launch();
-  // warps 6-9: copiers of the staged gather / reducers of the scatter modes
-  kernel<<<grid, (p.gather == 4 || p.mode != kModeLocal) ? 320 : 192, S::kTotal, stream>>>(ma, mb, p);
-  return cudaGetLastError() == cudaSuccess ? 0 : 4;
+  if constexpr (!A_MN) {
+    // staged gather: eight copier warps (the launch checks rule out a transposed A here)
+    if (p.gather == 4)
+      return launch_comm_kernel<BN, STAGES, A_MN, B_MN, 8>(ma, mb, p, grid, 192 + 8 * 32, stream);
+  }
+  // scatter modes: four reducer warps; otherwise the six warps of the plain pipeline
+  return launch_comm_kernel<BN, STAGES, A_MN, B_MN, 4>(ma, mb, p, grid,
+                                                       p.mode != kModeLocal ? 320 : 192, stream);
 }
 
 // Tuning of the staged gather's copier warps, read once from SLAPO_B200_AG_COPY="slices,inflight"
