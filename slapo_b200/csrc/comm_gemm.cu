@@ -645,7 +645,6 @@ comm_gemm_kernel(const __grid_constant__ SegMaps maps_a, const __grid_constant__
     // thread) and published block by block; the producer warps of all CTAs
     // read staged blocks with local TMA loads.
     if (staged && p.world > 1) {
-      if constexpr (CW == 8) {
       const int ct = threadIdx.x - 192;
       // A 128-row block is copied as `slices` slices by (usually) different CTAs, units in
       // (block, slice) order, so that the first blocks are complete after a few NVLink round
@@ -695,7 +694,6 @@ comm_gemm_kernel(const __grid_constant__ SegMaps maps_a, const __grid_constant__
         }
       }
       if (ct == 0) trace_mark(p.trace, 2);
-      }
     } else if (scatter) {
       // ------------------------------ reducer warps -------------------------------
       // Reduce-scatter / all-reduce: as soon as a 128-row block of this rank's rows is complete
@@ -939,9 +937,14 @@ static int launch_comm_variant(const SegMaps& ma, const SegMaps& mb, const CommG
   int grid = tiles < sm_count() ? tiles : sm_count();
   if (p.mode != kModeLocal) grid = sm_count();  // all CTAs take part in the reduction
   if constexpr (!A_MN) {
-    // staged gather: eight copier warps (the launch checks rule out a transposed A here)
-    if (p.gather == 4)
+    // Staged gather (the launch checks rule out a transposed A here).  From four ranks on the
+    // kernel is bound by the gather, not by the tensor core: eight copier warps keep 64 KB per
+    // SM in flight.  Between two ranks the transfer hides behind the own-row tiles and the
+    // leaner variant (four copier warps, more registers for the main roles) measured faster.
+    if (p.gather == 4 && p.world >= 4)
       return launch_comm_kernel<BN, STAGES, A_MN, B_MN, 8>(ma, mb, p, grid, 192 + 8 * 32, stream);
+    if (p.gather == 4)
+      return launch_comm_kernel<BN, STAGES, A_MN, B_MN, 4>(ma, mb, p, grid, 320, stream);
   }
   // scatter modes: four reducer warps; otherwise the six warps of the plain pipeline
   return launch_comm_kernel<BN, STAGES, A_MN, B_MN, 4>(ma, mb, p, grid,

@@ -130,7 +130,9 @@ def _wrn(name):
                      sum(cfg["block_size"][1]))
 
 
-_V_BERT, _V_GPT, _V_OPT = _pad_vocab(30522), _pad_vocab(50257), 50272
+# GPT-2 / GPT-Neo: 50257 -> 50304, a multiple of 128, so that a vocabulary shard stays a multiple of
+# 8 elements (16 bytes, what TMA and the vector kernels need) for every group size up to 8
+_V_BERT, _V_GPT, _V_OPT = _pad_vocab(30522), _pad_vocab(50257, 128), 50272
 
 MODEL_BUILDERS = {
     "bert-base": lambda: _bert("bert-base", vocab_size=_V_BERT, hidden_size=768,

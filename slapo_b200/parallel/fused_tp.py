@@ -276,7 +276,8 @@ class _ColLinearARBwd(torch.autograd.Function):
         x, w = ctx.saved_tensors
         dy = dy.contiguous()
         t = dy.shape[0]
-        if t % (128 * ctx.sctx.world) == 0:
+        # the fused kernel wants whole 128-row blocks per rank and 16-byte aligned rows
+        if t % (128 * ctx.sctx.world) == 0 and dy.shape[1] % 8 == 0 and w.shape[1] % 8 == 0:
             dx = gemm_ar(ctx.sctx, dy, w, None, b_mn=True, name="ar_bwd")
         else:  # row blocks do not split evenly over the group
             import torch.distributed as dist

@@ -85,6 +85,11 @@ def lower_fused_tp(sch, ctx) -> int:
                 post = "ar"
         if not (pre_ag or bwd_ar or post):
             continue
+        if (pre_ag or post) and (mod.weight.shape[0] % 8 or mod.weight.shape[1] % 8):
+            # rows of 16-bit operands must be multiples of 16 bytes for TMA: put the hooks back
+            raise ValueError(
+                f"{sub.path}: the fused tensor-parallel kernels need weight shards whose "
+                f"dimensions are multiples of 8, got {tuple(mod.weight.shape)}")
         if not isinstance(mod, LinearWithSyncFunc):
             new = LinearWithSyncFunc.from_linear(mod)
             sub.replace(new)
