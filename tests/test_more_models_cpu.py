@@ -160,3 +160,15 @@ def test_wideresnet_pipeline_cuts():
     out = pipe.mod.eval()(x, y)
     out = out["loss"] if isinstance(out, dict) else out[-1]
     torch.testing.assert_close(out, ref(x, y)["loss"], rtol=1e-4, atol=1e-4)
+
+
+def test_decoder_vocab_shards_stay_16_byte_aligned():
+    """A vocabulary shard of the GPT family is a multiple of 8 rows for every group size up to 8
+    (rows of 16-bit logits / gradients must be multiples of 16 bytes for the fused kernels)."""
+    from slapo_b200.models import zoo
+
+    for name in ("gpt2-medium", "gpt-neo-125m", "gpt-neo-2.7b"):
+        vocab = zoo.get_model_spec(name).config.vocab_size
+        assert vocab >= 50257
+        for tp in (2, 4, 8):
+            assert vocab % tp == 0 and (vocab // tp) % 8 == 0, (name, vocab, tp)
