@@ -937,11 +937,15 @@ static int launch_comm_variant(const SegMaps& ma, const SegMaps& mb, const CommG
   int grid = tiles < sm_count() ? tiles : sm_count();
   if (p.mode != kModeLocal) grid = sm_count();  // all CTAs take part in the reduction
   if constexpr (!A_MN) {
-    // Staged gather (the launch checks rule out a transposed A here).  From four ranks on the
-    // kernel is bound by the gather, not by the tensor core: eight copier warps keep 64 KB per
-    // SM in flight.  Between two ranks the transfer hides behind the own-row tiles and the
-    // leaner variant (four copier warps, more registers for the main roles) measured faster.
-    if (p.gather == 4 && p.world >= 4)
+    // Staged gather (the launch checks rule out a transposed A here).  The variant with eight
+    // copier warps (64 KB per SM in flight) measured slower than four warps at 2 and at 8 GPUs
+    // (qkv / fc1 of BERT-large: 150 / 181 us against 140 / 159 us, 813 / 792 us against
+    // 647 / 729 us); SLAPO_B200_AG_WIDE=1 selects it for experiments.
+    static const bool wide = [] {
+      const char* e = std::getenv("SLAPO_B200_AG_WIDE");
+      return e != nullptr && e[0] == '1';
+    }();
+    if (p.gather == 4 && wide)
       return launch_comm_kernel<BN, STAGES, A_MN, B_MN, 8>(ma, mb, p, grid, 192 + 8 * 32, stream);
     if (p.gather == 4)
       return launch_comm_kernel<BN, STAGES, A_MN, B_MN, 4>(ma, mb, p, grid, 320, stream);
