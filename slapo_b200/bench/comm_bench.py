@@ -89,6 +89,9 @@ def main():
     ap.add_argument("--iters", type=int, default=10)
     ap.add_argument("--ops", default="ag,rs,dp", help="comma list of ag, rs, dp")
     ap.add_argument("--no-baseline", action="store_true", help="skip the NCCL + cuBLAS lines")
+    ap.add_argument("--nvls", type=int, default=-1,
+                    help="1 / 0: reduce through the NVSwitch (multimem) or by peer loads; "
+                         "-1: the context's default for the group size")
     args = ap.parse_args()
     local = int(os.environ.get("LOCAL_RANK", "0"))
     torch.cuda.set_device(local)
@@ -99,7 +102,9 @@ def main():
     from slapo_b200.parallel import fused_tp as ft
     from slapo_b200.parallel.symm import SymmContext
 
-    ctx = SymmContext(None)
+    ctx = SymmContext(None, nvls=None if args.nvls < 0 else bool(args.nvls))
+    if rank == 0:
+        print(json.dumps({"world": world, "nvls": ctx.nvls}), flush=True)
     dev, dt = torch.device("cuda", local), torch.bfloat16
     ts = args.tokens_per_gpu              # token shard of this rank (sequence parallel)
     t = ts * world                        # tokens seen by a TP region

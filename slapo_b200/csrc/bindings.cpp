@@ -111,6 +111,38 @@ std::tuple<Tensor, Tensor> bias_act_bwd(const Tensor& dy, const Tensor& x,
   return {dx, dbias};
 }
 
+// dz = dy * act'(z), dbias = column sums of dz: the backward of an activation whose input z
+// already contains the bias (the GEMM epilogue added it)
+std::tuple<Tensor, Tensor> act_bwd_colsum(const Tensor& dy, const Tensor& z, int64_t act) {
+  check_cuda_contig(dy, "dy");
+  check_cuda_contig(z, "z");
+  c10::cuda::CUDAGuard guard(z.device());
+  const int cols = static_cast<int>(z.size(-1));
+  const int rows = static_cast<int>(z.numel() / cols);
+  TORCH_CHECK(cols % 8 == 0, "last dimension must be a multiple of 8");
+  Tensor dz = at::empty_like(z);
+  Tensor dbias = at::empty({cols}, z.options());
+  Tensor partial = at::empty({slapo::colsum_chunks(rows, cols), cols}, z.options().dtype(at::kFloat));
+  slapo::launch_bias_act_bwd(dy.data_ptr(), z.data_ptr(), nullptr, dz.data_ptr(), dbias.data_ptr(),
+                             partial.data_ptr<float>(), rows, cols, static_cast<int>(act),
+                             dtype_code(z), cur_stream());
+  return {dz, dbias};
+}
+
+// column sums of a 2-D tensor with contiguous rows (row stride free)
+Tensor colsum(const Tensor& x) {
+  TORCH_CHECK(x.is_cuda() && x.dim() == 2 && x.stride(1) == 1, "colsum: 2-D CUDA tensor with contiguous rows");
+  c10::cuda::CUDAGuard guard(x.device());
+  const int rows = static_cast<int>(x.size(0)), cols = static_cast<int>(x.size(1));
+  TORCH_CHECK(cols % 8 == 0 && x.stride(0) % 8 == 0, "colsum: columns and row stride must be multiples of 8");
+  Tensor out = at::empty({cols}, x.options());
+  if (rows == 0) return out.zero_();
+  Tensor partial = at::empty({slapo::colsum_chunks(rows, cols), cols}, x.options().dtype(at::kFloat));
+  slapo::launch_colsum(x.data_ptr(), out.data_ptr(), partial.data_ptr<float>(), rows, cols,
+                       x.stride(0), dtype_code(x), cur_stream());
+  return out;
+}
+
 Tensor bias_dropout_add_fwd(const Tensor& x, const optional<Tensor>& bias,
                             const optional<Tensor>& residual, double p, const Tensor& rng) {
   check_cuda_contig(x, "x");
@@ -269,6 +301,8 @@ TORCH_LIBRARY(slapo_b200, m) {
   m.def("bias_act_fwd(Tensor x, Tensor? bias, int act) -> Tensor", &bias_act_fwd);
   m.def("bias_act_bwd(Tensor dy, Tensor x, Tensor? bias, int act) -> (Tensor, Tensor)",
         &bias_act_bwd);
+  m.def("act_bwd_colsum(Tensor dy, Tensor z, int act) -> (Tensor, Tensor)", &act_bwd_colsum);
+  m.def("colsum(Tensor x) -> Tensor", &colsum);
   m.def("bias_dropout_add_fwd(Tensor x, Tensor? bias, Tensor? residual, float p, Tensor rng) -> Tensor",
         &bias_dropout_add_fwd);
   m.def("bias_dropout_add_bwd(Tensor dy, float p, Tensor rng, bool want_dbias) -> (Tensor, Tensor)",

@@ -25,7 +25,7 @@ void comm_gemm(std::vector<int64_t> a_ptrs, std::vector<int64_t> b_ptrs, int64_t
                int64_t epoch, int64_t out_ptr, int64_t ldo, int64_t bias_ptr, int64_t act,
                int64_t flags_ptr, std::vector<int64_t> peer_flags, std::vector<int64_t> peer_recv,
                std::vector<int64_t> peer_out, double wait_seconds, int64_t stage_ptr,
-               int64_t chunk_flags_ptr) {
+               int64_t chunk_flags_ptr, int64_t recv_mc, int64_t out_mc) {
   TORCH_CHECK(!a_ptrs.empty() && !b_ptrs.empty(), "comm_gemm: operand pointers missing");
   auto a = to_ptrs<void*>(a_ptrs);
   auto b = to_ptrs<void*>(b_ptrs);
@@ -42,7 +42,8 @@ void comm_gemm(std::vector<int64_t> a_ptrs, std::vector<int64_t> b_ptrs, int64_t
       reinterpret_cast<int*>(flags_ptr), peer_flags.empty() ? nullptr : pf.data(),
       peer_recv.empty() ? nullptr : pr.data(), peer_out.empty() ? nullptr : po.data(),
       slapo_status_ptr(dev), wait_seconds, reinterpret_cast<void*>(stage_ptr),
-      reinterpret_cast<int*>(chunk_flags_ptr), at::cuda::getCurrentCUDAStream().stream());
+      reinterpret_cast<int*>(chunk_flags_ptr), reinterpret_cast<void*>(recv_mc),
+      reinterpret_cast<void*>(out_mc), at::cuda::getCurrentCUDAStream().stream());
   TORCH_CHECK(rc == 0, "comm_gemm: launch refused (code ", rc,
               "): check divisibility by the group size / 128-row blocks and 16-byte alignment");
 }
@@ -180,7 +181,7 @@ void register_comm_ops(torch::Library& m) {
         "bool b_mn, bool bf16, int gather, int seg_len, int mode, int world, int rank, int epoch, "
         "int out_ptr, int ldo, int bias_ptr, int act, int flags_ptr, int[] peer_flags, "
         "int[] peer_recv, int[] peer_out, float wait_seconds, int stage_ptr, "
-        "int chunk_flags_ptr) -> ()", &comm_gemm);
+        "int chunk_flags_ptr, int recv_mc, int out_mc) -> ()", &comm_gemm);
   m.def("comm_trace() -> Tensor", &comm_trace);
   m.def("peer_gather(int[] src_ptrs, int dst_ptr, int seg_bytes, int world, int rank, int epoch, "
         "int flags_ptr, int[] peer_flags, float wait_seconds) -> ()", &peer_gather);

@@ -32,6 +32,20 @@
 //                        every peer's output buffer and a second flag round
 //                        closes the operation.
 //
+// Both transfers spread over all peers at once: the gather's copy units are taken block by
+// block across owners (a CTA pulls block b of owner o while its neighbour pulls block b of
+// owner o + 1), and the reduction reads a vector from every source together.  Peer by peer
+// - every GPU reading from exactly one other GPU at a time - measured half the bandwidth
+// of the spread pattern on an 8-GPU NVSwitch node.
+//
+// With an NVLS address of the partial-product buffers (`mc_recv`, the same symmetric buffer
+// bound to an NVSwitch group) the reduction issues ONE `multimem.ld_reduce` per 16 bytes: the
+// switch fetches and adds the eight ranks' vectors (fp32 accumulation) and a tenth of the
+// loads in flight reaches the link rate, so the reducer warps alone keep NVLink busy while
+// the main loop still runs; the all-reduce's second half is one `multimem.st` per vector.
+// The peer-load path stays for groups without such an address (and for tests where a rank
+// may leave: a rank must not die while bound to a switch group).
+//
 // Flow control is an int32 flag pad in symmetric memory and one job-wide
 // monotone epoch number per fused operation (identical on all ranks):
 //   ready[src] >= epoch   rank src has entered this operation, i.e. everything
@@ -103,6 +117,11 @@ struct CommGemmParams {
   int* blk_flags;
   int* peer_blk_flags[kMaxRanks];
   int* blk_counters;
+  // NVLS addresses (null = peer loads / stores): the partial-product buffers of all ranks
+  // behind one address (header first), and the all-reduce output buffers
+  int* mc_blk_flags;
+  void* mc_recv;
+  void* mc_out;
 };
 
 __device__ __forceinline__ void st_release_sys(int* addr, int v) {
@@ -191,12 +210,24 @@ __device__ __forceinline__ float cload(const void* p, int64_t i, int bf16) {
 // overlaps the rest of the GEMM.
 __device__ __forceinline__ void tile_coords(int t, int tiles_n, int blocks_per_owner, int world,
                                             int rank, bool rotate, int& m_blk, int& n_blk,
-                                            int first = 1, bool interleave = false) {
+                                            int first = 1, bool interleave = false,
+                                            bool own_then_spread = false) {
   n_blk = t % tiles_n;
   int mb = t / tiles_n;
   if (rotate) {
     int o_idx, b;
-    if (interleave) {
+    if (own_then_spread) {
+      // staged gather: this rank's blocks, then block b of every other owner in turn - the
+      // order in which the copier warps of all CTAs bring them in
+      if (mb < blocks_per_owner) {
+        o_idx = 0;
+        b = mb;
+      } else {
+        const int idx = mb - blocks_per_owner;
+        b = idx / (world - 1);
+        o_idx = 1 + idx % (world - 1);
+      }
+    } else if (interleave) {
       o_idx = mb % world;
       b = mb / world;
     } else {
@@ -388,6 +419,110 @@ __device__ __forceinline__ void reduce_span_smem(const CommGemmParams& p, int ro
   }
 }
 
+
+// ---- NVLS (multimem) -------------------------------------------------------
+// one load returns the sum over all ranks of the 16-byte vector at this address
+__device__ __forceinline__ uint4 mc_ld_reduce_add(const void* mc_addr, int bf16) {
+  uint4 v;
+  if (bf16)
+    asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.bf16x2 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(mc_addr) : "memory");
+  else
+    asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.f16x2 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(mc_addr) : "memory");
+  return v;
+}
+// the smallest value that any rank holds in this flag word
+__device__ __forceinline__ int mc_ld_min_acquire(const int* mc_addr) {
+  int v;
+  asm volatile("multimem.ld_reduce.acquire.sys.global.min.s32 %0, [%1];" : "=r"(v) : "l"(mc_addr) : "memory");
+  return v;
+}
+// one store lands in every rank's copy of the buffer
+__device__ __forceinline__ void mc_st(void* mc_addr, uint4 v) {
+  asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(mc_addr),
+               "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
+}
+__device__ __forceinline__ bool wait_flag_mc(const int* mc_addr, int epoch, long long budget,
+                                             volatile int* abort_flag) {
+  if (mc_ld_min_acquire(mc_addr) >= epoch) return true;
+  const long long start = clock64();
+  int spins = 0;
+  while (mc_ld_min_acquire(mc_addr) < epoch) {
+    if ((++spins & 0x3f) == 0) {
+      if (*abort_flag != 0) return false;
+      if (clock64() - start > budget) {
+        *abort_flag = 1;
+        return false;
+      }
+    }
+    __nanosleep(64);
+  }
+  return true;
+}
+
+// The reduction through the switch: U loads in flight per thread, each already the fp32-
+// accumulated sum over the group rounded to the 16-bit type; bias / activation follow.
+template <int U>
+__device__ __forceinline__ void reduce_span_mc(const CommGemmParams& p, int rows_per_rank,
+                                               int row0, int nrows, int tid, int nthr) {
+  const unsigned vpr = static_cast<unsigned>(p.N) / 8u;
+  const unsigned n_loc = static_cast<unsigned>(nrows) * vpr;
+  const int64_t my_off = (static_cast<int64_t>(p.rank) * rows_per_rank + row0) * p.N;
+  const uint8_t* src = static_cast<const uint8_t*>(p.mc_recv) + my_off * 2;
+  for (unsigned j0 = tid; j0 < n_loc; j0 += static_cast<unsigned>(nthr) * U) {
+    uint4 raw[U];
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const unsigned j = j0 + u * nthr;
+      if (j < n_loc) raw[u] = mc_ld_reduce_add(src + static_cast<size_t>(j) * 16, p.bf16);
+    }
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const unsigned j = j0 + u * nthr;
+      if (j >= n_loc) break;
+      const unsigned lr = j / vpr;
+      const int col = static_cast<int>(j - lr * vpr) * 8;
+      uint4 outv = raw[u];
+      if (p.bias != nullptr || p.act >= 0) {
+        float v[8];
+        if (p.bf16) {
+          const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw[u]);
+#pragma unroll
+          for (int k = 0; k < 4; ++k) { float2 f = __bfloat1622float2(h[k]); v[2 * k] = f.x; v[2 * k + 1] = f.y; }
+        } else {
+          const __half2* h = reinterpret_cast<const __half2*>(&raw[u]);
+#pragma unroll
+          for (int k = 0; k < 4; ++k) { float2 f = __half22float2(h[k]); v[2 * k] = f.x; v[2 * k + 1] = f.y; }
+        }
+        if (p.bias != nullptr) {
+#pragma unroll
+          for (int k = 0; k < 8; ++k) v[k] += cload(p.bias, col + k, p.bf16);
+        }
+        if (p.act >= 0) {
+#pragma unroll
+          for (int k = 0; k < 8; ++k) v[k] = act_fwd(v[k], p.act);
+        }
+        outv = make_uint4(cpack2(v[0], v[1], p.bf16), cpack2(v[2], v[3], p.bf16),
+                          cpack2(v[4], v[5], p.bf16), cpack2(v[6], v[7], p.bf16));
+      }
+      const int64_t lrow = row0 + static_cast<int>(lr);
+      if (p.mode == kModeReduceScatter) {
+        *reinterpret_cast<uint4*>(static_cast<uint8_t*>(p.out) + (lrow * p.ldo + col) * 2) = outv;
+      } else {
+        const int64_t grow = static_cast<int64_t>(p.rank) * rows_per_rank + lrow;
+        if (p.mc_out != nullptr) {
+          mc_st(static_cast<uint8_t*>(p.mc_out) + (grow * p.ldo + col) * 2, outv);
+        } else {
+          for (int r = 0; r < p.world; ++r)
+            *reinterpret_cast<uint4*>(static_cast<uint8_t*>(p.peer_out[r]) +
+                                      (grow * p.ldo + col) * 2) = outv;
+        }
+      }
+    }
+  }
+}
+
 // One group of 128 threads (named barrier `bar_id`, `gt` = thread index inside the group) takes
 // reduction units of this CTA until none is left.  A unit is a 32-row slice of a 128-row block of
 // this rank's rows; the CTA's units are u = blockIdx.x + k * gridDim.x in block order and `next_k`
@@ -409,7 +544,12 @@ __device__ __forceinline__ void reduce_units(const CommGemmParams& p, int rows_p
     }
     asm volatile("bar.sync %0, 128;" ::"r"(bar_id) : "memory");
     const int u = vote[0];
-    if (vote[1] == 1 && gt < p.world) {
+    if (vote[1] == 1 && p.mc_blk_flags != nullptr) {
+      // one load through the switch returns the minimum of the block's flag over all ranks
+      if (gt == 0 && !wait_flag_mc(p.mc_blk_flags + p.rank * blocks_per_owner + u / kRedSlices,
+                                   p.epoch, p.wait_cycles, abort_flag))
+        vote[1] = 0;
+    } else if (vote[1] == 1 && gt < p.world) {
       // flag of block b of this rank's rows in every source's header (a word of the peer's
       // memory, polled over NVLink): one thread per source, so the round trips overlap
       const int src = (p.rank + 1 + gt) % p.world;
@@ -423,6 +563,10 @@ __device__ __forceinline__ void reduce_units(const CommGemmParams& p, int rows_p
     asm volatile("bar.sync %0, 128;" ::"r"(bar_id) : "memory");
     if (w != 1) break;
     const int row0 = (u / kRedSlices) * CBM + (u % kRedSlices) * (CBM / kRedSlices);
+    if (p.mc_recv != nullptr) {
+      reduce_span_mc<8>(p, rows_per_rank, row0, CBM / kRedSlices, gt, 128);
+      continue;
+    }
     if (in_smem && (p.world == 2 || p.world == 4 || p.world == 8)) {
       if (p.world == 2) reduce_span_smem<2>(p, rows_per_rank, row0, CBM / kRedSlices, gt, region);
       else if (p.world == 4) reduce_span_smem<4>(p, rows_per_rank, row0, CBM / kRedSlices, gt, region);
@@ -479,6 +623,9 @@ comm_gemm_kernel(const __grid_constant__ SegMaps maps_a, const __grid_constant__
   const int tiles_n = (p.N + BN - 1) / BN;
   const int num_tiles = tiles_m * tiles_n;
   const int num_kb = (p.K + CBK - 1) / CBK;
+  // a role that waits (through an mbarrier) behind another role's wait for a peer GPU must
+  // outlast that wait
+  const long long mbar_budget = p.wait_cycles + tc::kWaitCycles;
   const bool scatter = p.mode != kModeLocal;
   const int rows_per_rank = p.M / p.world;               // used when rows are owned (gather 1 / scatter)
   const bool staged = p.gather == 4;
@@ -540,7 +687,7 @@ comm_gemm_kernel(const __grid_constant__ SegMaps maps_a, const __grid_constant__
       for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
         int m_blk, n_blk;
         tile_coords(t, tiles_n, blocks_per_owner, p.world, p.rank, rotate, m_blk, n_blk, first,
-                    scatter);
+                    scatter, staged);
         const int m0 = m_blk * CBM, n0 = n_blk * BN;
         int a_seg = 0, a_row = m0;
         if (p.gather == 1) {
@@ -582,7 +729,7 @@ comm_gemm_kernel(const __grid_constant__ SegMaps maps_a, const __grid_constant__
             k_b -= seg_b * p.seg_len;
             if (!need_ready(seg_b)) { ok = false; break; }
           }
-          if (!tc::mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag)) { ok = false; break; }
+          if (!tc::mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag, mbar_budget)) { ok = false; break; }
           tc::mbar_arrive_expect_tx(&full_bar[stage], S::kABytes + S::kBBytes);
           uint8_t* sa = smem_a + stage * S::kABytes;
           uint8_t* sb = smem_b + stage * S::kBBytes;
@@ -616,11 +763,11 @@ comm_gemm_kernel(const __grid_constant__ SegMaps maps_a, const __grid_constant__
       for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, ++iter) {
         const int acc = iter & 1;
         const uint32_t acc_phase = (iter >> 1) & 1;
-        if (!tc::mbar_wait(&tmem_empty[acc], acc_phase ^ 1, abort_flag)) { ok = false; break; }
+        if (!tc::mbar_wait(&tmem_empty[acc], acc_phase ^ 1, abort_flag, mbar_budget)) { ok = false; break; }
         tc::fence_after_sync();
         const uint32_t d_tmem = tmem_base + acc * BN;
         for (int kb = 0; kb < num_kb; ++kb) {
-          if (!tc::mbar_wait(&full_bar[stage], phase, abort_flag)) { ok = false; break; }
+          if (!tc::mbar_wait(&full_bar[stage], phase, abort_flag, mbar_budget)) { ok = false; break; }
           tc::fence_after_sync();
           const uint32_t a_addr = tc::smem_u32(smem_a + stage * S::kABytes);
           const uint32_t b_addr = tc::smem_u32(smem_b + stage * S::kBBytes);
@@ -655,18 +802,20 @@ comm_gemm_kernel(const __grid_constant__ SegMaps maps_a, const __grid_constant__
       const int64_t slice_vec = static_cast<int64_t>(slice_rows) * p.row_bytes / 16;
       int u = 0;
       bool ok = true, marked = false;
-      for (int o_idx = 1; o_idx < p.world && ok; ++o_idx) {
-        const int owner = (p.rank + o_idx) % p.world;
-        bool owner_ready = false;
-        for (int b = 0; b < blocks_per_owner && ok; ++b) {
+      uint32_t owner_seen = 0;    // owners whose "entered" flag this CTA has observed
+      // units in (block, owner, slice) order: at any moment the CTAs of this GPU pull from
+      // all peers at once, and block b of every owner is complete before block b + 1
+      for (int b = 0; b < blocks_per_owner && ok; ++b) {
+        for (int o_idx = 1; o_idx < p.world && ok; ++o_idx) {
+          const int owner = (p.rank + o_idx) % p.world;
           for (int sl = 0; sl < slices; ++sl, ++u) {
             if (u % static_cast<int>(gridDim.x) != static_cast<int>(blockIdx.x)) continue;
-            if (!owner_ready) {
+            if (!(owner_seen & (1u << owner))) {
               int w = 1;
               if (ct == 0) w = wait_flag(ready + owner, p.epoch, p.wait_cycles, abort_flag) ? 1 : 0;
               w = __syncthreads_or_named<CW * 32>(w);
               if (!w) { ok = false; break; }
-              owner_ready = true;
+              owner_seen |= 1u << owner;
             }
             const int64_t off = (static_cast<int64_t>(b) * CBM + sl * slice_rows) * p.row_bytes;
             const uint4* src = reinterpret_cast<const uint4*>(
@@ -675,8 +824,8 @@ comm_gemm_kernel(const __grid_constant__ SegMaps maps_a, const __grid_constant__
             uint4* dst = reinterpret_cast<uint4*>(
                 static_cast<uint8_t*>(p.stage_dst) +
                 (static_cast<int64_t>(m_blk) * CBM + sl * slice_rows) * p.row_bytes);
-            // 8 or 16 16-byte loads per thread are issued before the first store: with 256
-            // threads that keeps 32 or 64 KB per SM on the wire to cover the NVLink round trip.
+            // 8 or 16 16-byte loads per thread are issued before the first store: with 128
+            // threads that keeps 16 or 32 KB per SM on the wire to cover the NVLink round trip.
             if (ct == 0 && !marked) { trace_mark(p.trace, 1); marked = true; }
             if (p.ag_inflight == 16) copy_vecs<16, CW * 32>(src, dst, slice_vec, ct);
             else copy_vecs<8, CW * 32>(src, dst, slice_vec, ct);
@@ -719,7 +868,7 @@ comm_gemm_kernel(const __grid_constant__ SegMaps maps_a, const __grid_constant__
     for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, ++iter) {
       int m_blk, n_blk;
       tile_coords(t, tiles_n, blocks_per_owner, p.world, p.rank, rotate, m_blk, n_blk, first,
-                    scatter);
+                    scatter, staged);
       const int m0 = m_blk * CBM, n0 = n_blk * BN;
       const int acc = iter & 1;
       const uint32_t acc_phase = (iter >> 1) & 1;
@@ -746,7 +895,7 @@ comm_gemm_kernel(const __grid_constant__ SegMaps maps_a, const __grid_constant__
         dst_base = static_cast<uint8_t*>(p.out);
         dst_ld = p.ldo;
       }
-      if (!tc::mbar_wait_warp(&tmem_full[acc], acc_phase, abort_flag)) { ok = false; break; }
+      if (!tc::mbar_wait_warp(&tmem_full[acc], acc_phase, abort_flag, mbar_budget)) { ok = false; break; }
       tc::fence_after_sync();
       const int row = m0 + quarter * 32 + lane;
       const uint32_t t_row = tmem_base + acc * BN + (static_cast<uint32_t>(quarter * 32) << 16);
@@ -986,7 +1135,7 @@ int launch_comm_gemm(void* const* a_ptrs, void* const* b_ptrs, int M, int N, int
                      int world, int rank, int epoch, void* out, int ldo, const void* bias, int act,
                      int* flags, int* const* peer_flags, void* const* peer_recv,
                      void* const* peer_out, int* status, double wait_seconds, void* stage_dst,
-                     int* chunk_flags, cudaStream_t stream) {
+                     int* chunk_flags, void* recv_mc, void* out_mc, cudaStream_t stream) {
   if (M <= 0 || N <= 0 || K <= 0) return 0;
   if ((gather == 4 || mode != kModeLocal) && (M + CBM - 1) / CBM > kChunkCountOffset) return 6;
   if (gather == 4 && mode != kModeLocal) return 1;   // warps 6-9 have one job per launch
@@ -1047,6 +1196,11 @@ int launch_comm_gemm(void* const* a_ptrs, void* const* b_ptrs, int M, int N, int
     p.peer_blk_flags[r] = reinterpret_cast<int*>(recv);
     p.peer_recv[r] = recv != nullptr ? recv + kRecvHeaderBytes : nullptr;
     p.peer_out[r] = peer_out != nullptr ? peer_out[r] : nullptr;
+  }
+  if (recv_mc != nullptr && mode != kModeLocal && world > 1) {
+    p.mc_blk_flags = reinterpret_cast<int*>(recv_mc);
+    p.mc_recv = static_cast<uint8_t*>(recv_mc) + kRecvHeaderBytes;
+    p.mc_out = mode == kModeAllReduce ? out_mc : nullptr;
   }
   p.blk_flags = p.peer_blk_flags[rank];
   p.blk_counters = p.blk_flags != nullptr ? p.blk_flags + kChunkCountOffset : nullptr;

@@ -127,8 +127,8 @@ __global__ void __launch_bounds__(256) dp_grad_rs_kernel(
       const uint8_t* dmb = reinterpret_cast<const uint8_t*>(&dm);
 #pragma unroll
       for (int k = 0; k < 8; ++k) {
-        if (dmb[k]) sq_dup += acc[k] * acc[k];
-        else sq_shard += acc[k] * acc[k];
+        if (dmb[k] == 1) sq_dup += acc[k] * acc[k];
+        else if (dmb[k] == 0) sq_shard += acc[k] * acc[k];
       }
     } else {
 #pragma unroll

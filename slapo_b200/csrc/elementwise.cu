@@ -126,6 +126,31 @@ __global__ void __launch_bounds__(256) bias_act_bwd_kernel(
   if (partial != nullptr) slab_reduce_store(acc, partial, cols, col, col_ok);
 }
 
+// Column sums of a [rows, cols] matrix (the bias gradient of a plain linear layer): same slab
+// decomposition as above, reading only.
+template <typename T>
+__global__ void __launch_bounds__(256) colsum_kernel(const T* __restrict__ x,
+                                                     float* __restrict__ partial, int rows,
+                                                     int cols, int64_t row_stride,
+                                                     int rows_per_chunk) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int col = blockIdx.x * 256 + lane * 8;
+  const bool col_ok = col + 8 <= cols;
+  float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+  if (col_ok) {
+    const int r0 = blockIdx.y * rows_per_chunk;
+    const int r1 = min(rows, r0 + rows_per_chunk);
+#pragma unroll 4
+    for (int r = r0 + warp; r < r1; r += 8) {
+      float g[8];
+      Vec8<T>::load(x + static_cast<int64_t>(r) * row_stride + col, g);
+#pragma unroll
+      for (int k = 0; k < 8; ++k) acc[k] += g[k];
+    }
+  }
+  slab_reduce_store(acc, partial, cols, col, col_ok);
+}
+
 // 32 x 32 threads per 32 columns: threadIdx.y strides over the chunks (see ln_bwd_finalize).
 template <typename T>
 __global__ void __launch_bounds__(1024) colsum_finalize_kernel(
@@ -303,6 +328,18 @@ void launch_bias_act_bwd(const void* dy, const void* x, const void* bias, void* 
       static_cast<const T*>(dy), static_cast<const T*>(x), static_cast<const T*>(bias),
       static_cast<T*>(dx), part, rows, cols, rows_per_chunk, act)));
   if (dbias != nullptr) launch_colsum_finalize(partial, dbias, chunks, cols, dtype, stream);
+}
+
+void launch_colsum(const void* x, void* out, float* partial, int rows, int cols,
+                   int64_t row_stride, int dtype, cudaStream_t stream) {
+  if (rows == 0 || cols == 0) return;
+  const int chunks = colsum_chunks(rows, cols);
+  const int rows_per_chunk = (rows + chunks - 1) / chunks;
+  dim3 grid((cols + 255) / 256, chunks);
+  count_launch();
+  DISPATCH_DTYPE(dtype, (colsum_kernel<T><<<grid, 256, 0, stream>>>(
+      static_cast<const T*>(x), partial, rows, cols, row_stride, rows_per_chunk)));
+  launch_colsum_finalize(partial, out, chunks, cols, dtype, stream);
 }
 
 void launch_bias_dropout_add_fwd(const void* x, const void* bias, const void* residual, void* y,

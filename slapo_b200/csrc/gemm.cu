@@ -292,8 +292,8 @@ struct TmapKeyHash {
   }
 };
 
-static bool cached_tmap(CUtensorMap* out, const void* base, uint64_t inner, uint64_t outer,
-                        uint64_t stride, uint32_t box_outer, bool bf16) {
+bool cached_tmap_2d(CUtensorMap* out, const void* base, uint64_t inner, uint64_t outer,
+                    uint64_t stride, uint32_t box_outer, bool bf16) {
   static std::unordered_map<TmapKey, CUtensorMap, TmapKeyHash> cache;
   static std::mutex mu;
   TmapKey key{base, inner, outer, stride, box_outer, bf16 ? 1 : 0};
@@ -340,9 +340,9 @@ int launch_gemm(const void* A, const void* B, void* C, const void* bias, int M, 
   bool ok;
   // K-major: [rows, K] -> inner K, outer rows, box 64 x rows_per_tile
   // MN-major: [K, rows] -> inner rows, outer K, box 64 x BK
-  ok = a_mn ? cached_tmap(&ta, A, M, K, lda, BK, bf16) : cached_tmap(&ta, A, K, M, lda, BM, bf16);
+  ok = a_mn ? cached_tmap_2d(&ta, A, M, K, lda, BK, bf16) : cached_tmap_2d(&ta, A, K, M, lda, BM, bf16);
   if (!ok) return 2;
-  ok = b_mn ? cached_tmap(&tb, B, N, K, ldb, BK, bf16) : cached_tmap(&tb, B, K, N, ldb, BN, bf16);
+  ok = b_mn ? cached_tmap_2d(&tb, B, N, K, ldb, BK, bf16) : cached_tmap_2d(&tb, B, K, N, ldb, BN, bf16);
   if (!ok) return 2;
   GemmParams p;
   p.M = M; p.N = N; p.K = K; p.C = C; p.ldc = ldc; p.bias = bias; p.act = act;

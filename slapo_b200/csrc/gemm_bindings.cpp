@@ -28,8 +28,28 @@ int64_t device_status() {
   return v;
 }
 
-Tensor gemm(const Tensor& a, const Tensor& b, const c10::optional<Tensor>& bias, int64_t act,
-            bool a_mn, bool b_mn) {
+// fp32 scratch of the split-K pair GEMM, one per device, zero between launches (the kernel
+// leaves it zeroed); grown on demand.  All GEMMs of a device run on one stream at a time.
+struct SplitScratch { Tensor ws, counters; };
+SplitScratch& split_scratch(int device, int64_t floats, int64_t ints) {
+  static std::vector<SplitScratch> s(64);
+  SplitScratch& e = s[device];
+  if (!e.ws.defined() || e.ws.numel() < floats)
+    e.ws = at::zeros({floats}, at::TensorOptions().dtype(at::kFloat).device(at::kCUDA, device));
+  if (!e.counters.defined() || e.counters.numel() < ints)
+    e.counters = at::zeros({ints}, at::TensorOptions().dtype(at::kInt).device(at::kCUDA, device));
+  return e;
+}
+
+// impl: 0 = pick (CTA-pair kernel when the problem has at least one pair tile, else the
+// single-CTA kernel), 1 = single-CTA kernel, 2 = CTA-pair kernel or fail.
+// split_k: allow several CTA pairs per output tile (weight gradients).
+// the word itself (device tensor), for callers that copy it out asynchronously
+Tensor device_status_tensor() { return status_word(at::cuda::current_device()); }
+
+Tensor gemm_out(const Tensor& a, const Tensor& b, const c10::optional<Tensor>& bias, int64_t act,
+                bool a_mn, bool b_mn, const c10::optional<Tensor>& out,
+                const c10::optional<Tensor>& pre_act, int64_t impl, bool split_k) {
   TORCH_CHECK(a.is_cuda() && b.is_cuda(), "gemm: CUDA tensors required");
   TORCH_CHECK(a.dim() == 2 && b.dim() == 2, "gemm: 2-D operands required");
   TORCH_CHECK(a.scalar_type() == b.scalar_type() &&
@@ -42,21 +62,63 @@ Tensor gemm(const Tensor& a, const Tensor& b, const c10::optional<Tensor>& bias,
   const int N = static_cast<int>(b_mn ? b.size(1) : b.size(0));
   const int Kb = static_cast<int>(b_mn ? b.size(0) : b.size(1));
   TORCH_CHECK(K == Kb, "gemm: contraction sizes differ: ", K, " vs ", Kb);
-  Tensor c = at::empty({M, N}, a.options());
+  Tensor c;
+  if (out.has_value() && out->defined()) {
+    c = *out;
+    TORCH_CHECK(c.dim() == 2 && c.size(0) == M && c.size(1) == N && c.stride(1) == 1 &&
+                    c.scalar_type() == a.scalar_type(),
+                "gemm: `out` must be an [M, N] tensor of the operand dtype with contiguous rows");
+  } else {
+    c = at::empty({M, N}, a.options());
+  }
+  void* c2 = nullptr;
+  if (pre_act.has_value() && pre_act->defined()) {
+    TORCH_CHECK(pre_act->sizes() == c.sizes() && pre_act->strides() == c.strides() &&
+                    pre_act->scalar_type() == c.scalar_type(),
+                "gemm: `pre_act` must match the output's shape, strides and dtype");
+    c2 = pre_act->data_ptr();
+  }
   const void* bias_ptr = nullptr;
   if (bias.has_value() && bias->defined()) {
     TORCH_CHECK(bias->scalar_type() == a.scalar_type() && bias->numel() == N && bias->is_contiguous(),
                 "gemm: bias must be a contiguous [N] tensor of the operand dtype");
     bias_ptr = bias->data_ptr();
   }
-  int rc = slapo::launch_gemm(a.data_ptr(), b.data_ptr(), c.data_ptr(), bias_ptr, M, N, K,
-                              static_cast<int>(a.stride(0)), static_cast<int>(b.stride(0)), N,
-                              a_mn, b_mn, a.scalar_type() == at::kBFloat16, static_cast<int>(act),
-                              status_word(a.get_device()).data_ptr<int>(),
-                              at::cuda::getCurrentCUDAStream().stream());
+  const int dev = a.get_device();
+  const bool bf16 = a.scalar_type() == at::kBFloat16;
+  auto stream = at::cuda::getCurrentCUDAStream().stream();
+  int rc = 5;
+  if (impl != 1) {
+    float* ws = nullptr;
+    int* counters = nullptr;
+    if (split_k && slapo::gemm2_splits(M, N, K, N > 128 ? 256 : 128) > 1) {
+      const int64_t tiles = static_cast<int64_t>((M + 255) / 256) * ((N + 127) / 128);
+      SplitScratch& sc = split_scratch(dev, static_cast<int64_t>(M) * N, tiles * 8);
+      ws = sc.ws.data_ptr<float>();
+      counters = sc.counters.data_ptr<int>();
+    }
+    rc = slapo::launch_gemm2(a.data_ptr(), b.data_ptr(), c.data_ptr(), c2, bias_ptr, M, N, K,
+                             static_cast<int>(a.stride(0)), static_cast<int>(b.stride(0)),
+                             static_cast<int>(c.stride(0)), a_mn, b_mn, bf16,
+                             static_cast<int>(act), ws, counters,
+                             status_word(dev).data_ptr<int>(), stream);
+    TORCH_CHECK(impl != 2 || rc == 0, "gemm: the CTA-pair kernel refused the launch (code ", rc, ")");
+  }
+  if (rc == 5) {
+    TORCH_CHECK(c2 == nullptr, "gemm: `pre_act` needs a problem of at least one 256 x 128 tile");
+    rc = slapo::launch_gemm(a.data_ptr(), b.data_ptr(), c.data_ptr(), bias_ptr, M, N, K,
+                            static_cast<int>(a.stride(0)), static_cast<int>(b.stride(0)),
+                            static_cast<int>(c.stride(0)), a_mn, b_mn, bf16, static_cast<int>(act),
+                            status_word(dev).data_ptr<int>(), stream);
+  }
   TORCH_CHECK(rc == 0, "gemm: launch refused (code ", rc,
               "): sizes must be multiples of 8 and pointers 16-byte aligned");
   return c;
+}
+
+Tensor gemm(const Tensor& a, const Tensor& b, const c10::optional<Tensor>& bias, int64_t act,
+            bool a_mn, bool b_mn) {
+  return gemm_out(a, b, bias, act, a_mn, b_mn, c10::nullopt, c10::nullopt, 0, false);
 }
 
 }  // namespace
@@ -65,5 +127,8 @@ int* slapo_status_ptr(int device) { return status_word(device).data_ptr<int>(); 
 
 void register_gemm_ops(torch::Library& m) {
   m.def("gemm(Tensor a, Tensor b, Tensor? bias, int act, bool a_mn, bool b_mn) -> Tensor", &gemm);
+  m.def("gemm_out(Tensor a, Tensor b, Tensor? bias, int act, bool a_mn, bool b_mn, Tensor? out, "
+        "Tensor? pre_act, int impl, bool split_k) -> Tensor", &gemm_out);
   m.def("device_status() -> int", &device_status);
+  m.def("device_status_tensor() -> Tensor", &device_status_tensor);
 }

@@ -21,6 +21,9 @@ void launch_bias_act_fwd(const void* x, const void* bias, void* y, int64_t rows,
 void launch_bias_act_bwd(const void* dy, const void* x, const void* bias, void* dx, void* dbias,
                          float* partial, int rows, int cols, int act, int dtype,
                          cudaStream_t stream);
+// out[c] = sum over rows of x[r, c] (cols % 8 == 0); partial: colsum_chunks(rows, cols) * cols floats
+void launch_colsum(const void* x, void* out, float* partial, int rows, int cols,
+                   int64_t row_stride, int dtype, cudaStream_t stream);
 void launch_colsum_finalize(const float* partial, void* out, int chunks, int cols, int dtype,
                             cudaStream_t stream);
 void launch_fused_adamw(void* param, const void* grad, float* master, float* exp_avg,
@@ -35,6 +38,15 @@ int launch_gemm(const void* A, const void* B, void* C, const void* bias, int M, 
                 int lda, int ldb, int ldc, bool a_mn, bool b_mn, bool bf16, int act, int* status,
                 cudaStream_t stream);
 
+// The same product on CTA pairs (gemm2.cu): 256 x 256 tiles shared by two SMs, optional second
+// output `C2` (the value before the activation), optional split-K through `workspace`
+// (M * N floats) and `counters` (8 ints per tile), both zero between launches.  Returns 5 when
+// the problem is smaller than one pair tile (use launch_gemm).
+int gemm2_splits(int M, int N, int K, int bn);
+int launch_gemm2(const void* A, const void* B, void* C, void* C2, const void* bias, int M, int N,
+                 int K, int lda, int ldb, int ldc, bool a_mn, bool b_mn, bool bf16, int act,
+                 float* workspace, int* counters, int* status, cudaStream_t stream);
+
 // Cross entropy in two steps (per-row statistics, then gradient); see loss.cu.
 void launch_ce_stats(const void* logits, const int64_t* labels, float* stats, int rows, int cols,
                      int64_t row_stride, int vocab_start, int64_t ignore_index, int dtype,
@@ -42,7 +54,8 @@ void launch_ce_stats(const void* logits, const int64_t* labels, float* stats, in
 void launch_ce_grad(const void* logits, const int64_t* labels, const float* lse,
                     const float* coef, void* grad, int rows, int cols, int64_t row_stride,
                     int vocab_start, int64_t ignore_index, int dtype, cudaStream_t stream);
-// out2[0] += sum x^2 where mask == 0 (or no mask), out2[1] += sum x^2 where mask != 0
+// out2[0] += sum x^2 where mask == 0 (or no mask), out2[1] += sum x^2 where mask == 1
+// (elements with any other mask value are left out)
 void launch_sq_norm(const void* x, const uint8_t* mask, float* out2, int64_t n, int dtype,
                     cudaStream_t stream);
 
@@ -52,12 +65,14 @@ void launch_sq_norm(const void* x, const uint8_t* mask, float* out2, int64_t n, 
 //             ints, zero-initialised, kept across calls - the epoch at which each 128-row
 //             block was staged, then the slice counters of the same blocks)
 //   mode:   0 local output, 1 reduce-scatter, 2 all-reduce
+//   recv_mc / out_mc: NVLS addresses of the partial-product buffers (header first) and of the
+//           all-reduce outputs, or null: the reduction then loads from every peer
 int launch_comm_gemm(void* const* a_ptrs, void* const* b_ptrs, int M, int N, int K, int lda,
                      int ldb, bool a_mn, bool b_mn, bool bf16, int gather, int seg_len, int mode,
                      int world, int rank, int epoch, void* out, int ldo, const void* bias, int act,
                      int* flags, int* const* peer_flags, void* const* peer_recv,
                      void* const* peer_out, int* status, double wait_seconds, void* stage_dst,
-                     int* chunk_flags, cudaStream_t stream);
+                     int* chunk_flags, void* recv_mc, void* out_mc, cudaStream_t stream);
 
 // Phase trace of the last fused GEMM + collective kernel (recorded when the environment has
 // SLAPO_B200_COMM_TRACE=1): [256 CTAs][8 slots] nanosecond time stamps, see comm_gemm.cu.

@@ -103,7 +103,7 @@ __global__ void __launch_bounds__(256) ce_grad_kernel(
 }
 
 // sum of squares of a flat low-precision buffer, split by an optional byte
-// mask: out[0] += sum over mask == 0, out[1] += sum over mask != 0.
+// mask: out[0] += sum over mask == 0, out[1] += sum over mask == 1; other values are skipped.
 template <typename T>
 __global__ void __launch_bounds__(256) sq_norm_kernel(const T* __restrict__ x,
                                                       const uint8_t* __restrict__ mask,
@@ -120,8 +120,8 @@ __global__ void __launch_bounds__(256) sq_norm_kernel(const T* __restrict__ x,
       const uint8_t* mb = reinterpret_cast<const uint8_t*>(&mk);
 #pragma unroll
       for (int k = 0; k < 8; ++k) {
-        if (mb[k]) a1 += v[k] * v[k];
-        else a0 += v[k] * v[k];
+        if (mb[k] == 1) a1 += v[k] * v[k];
+        else if (mb[k] == 0) a0 += v[k] * v[k];
       }
     } else {
 #pragma unroll

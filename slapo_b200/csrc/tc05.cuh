@@ -51,15 +51,18 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
 }
 // Bounded wait.  Returns false when the budget ran out (or another role of
 // the CTA already gave up, signalled through *abort_flag).
+// `budget`: cycles; kernels whose pipeline can legitimately stall on another GPU pass that
+// wait's limit plus kWaitCycles, so that the roles behind the stalled one do not give up first.
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity,
-                                          volatile int* abort_flag) {
+                                          volatile int* abort_flag,
+                                          long long budget = kWaitCycles) {
   if (mbar_try_wait(bar, parity)) return true;
   const long long start = clock64();
   int spins = 0;
   while (!mbar_try_wait(bar, parity)) {
     if ((++spins & 0xff) == 0) {
       if (*abort_flag != 0) return false;
-      if (clock64() - start > kWaitCycles) {
+      if (clock64() - start > budget) {
         *abort_flag = 1;
         return false;
       }
@@ -71,8 +74,9 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity,
 // Same, called by all 32 lanes of a warp: the result is made warp-uniform so
 // that warp-collective instructions after it never run under divergence.
 __device__ __forceinline__ bool mbar_wait_warp(uint64_t* bar, uint32_t parity,
-                                               volatile int* abort_flag) {
-  const bool ok = mbar_wait(bar, parity, abort_flag);
+                                               volatile int* abort_flag,
+                                               long long budget = kWaitCycles) {
+  const bool ok = mbar_wait(bar, parity, abort_flag, budget);
   return __all_sync(0xffffffffu, ok);
 }
 
@@ -147,6 +151,86 @@ __device__ __forceinline__ void umma_f16_ts(uint32_t d_tmem, uint32_t a_tmem, ui
 __device__ __forceinline__ void umma_commit(uint64_t* bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(
                    smem_u32(bar))
+               : "memory");
+}
+
+// ---- CTA pairs (cta_group::2): two CTAs of one cluster share an MMA ---------------
+// The pair's leader (cluster rank 0) issues tcgen05.mma with M = 256: each CTA
+// supplies its own 128 rows of A and its own half of B from its shared memory
+// and receives its 128 rows of D in its tensor memory.  Every CTA loads its own
+// operand tiles (tile loads into the issuing CTA's shared memory only); the
+// completion is signalled on a barrier of the leader.
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// shared::cluster address of `smem_addr` (a shared::cta address) in the CTA of rank `rank`
+__device__ __forceinline__ uint32_t map_to_cta(uint32_t smem_addr, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(smem_addr), "r"(rank));
+  return r;
+}
+// (default semantics - release at CTA scope - on purpose: a cluster-scope release makes the
+// compiler put a full memory barrier in front of every arrival, which serialises the
+// producer to one stage per barrier latency)
+__device__ __forceinline__ void mbar_arrive_expect_tx_cluster(uint32_t bar_cluster_addr,
+                                                              uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cluster.b64 _, [%0], %1;" ::"r"(
+                   bar_cluster_addr),
+               "r"(bytes)
+               : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t bar_cluster_addr) {
+  asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(
+                   bar_cluster_addr)
+               : "memory");
+}
+// tile load into this CTA's shared memory whose completion bytes are counted on a barrier
+// that may live in the pair's other CTA (`bar_cluster_addr` from map_to_cta)
+__device__ __forceinline__ void tma_load_2d_pair(uint32_t smem_dst, const CUtensorMap* tmap,
+                                                 uint32_t bar_cluster_addr, int c0, int c1) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes"
+      " [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(smem_dst), "l"(tmap), "r"(bar_cluster_addr), "r"(c0), "r"(c1)
+      : "memory");
+}
+// whole-warp calls, issued by one warp of EACH CTA of the pair
+__device__ __forceinline__ void tmem_alloc_pair(uint32_t* smem_dst, uint32_t ncols) {
+  asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
+                   smem_u32(smem_dst)),
+               "r"(ncols)
+               : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish_pair() {
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc_pair(uint32_t taddr, uint32_t ncols) {
+  asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols)
+               : "memory");
+}
+// D[tmem of both CTAs] (+)= A * B over the pair; the leader's elected thread issues
+__device__ __forceinline__ void umma_f16_pair(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc,
+                                              uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n"
+      ".reg .pred p;\n"
+      "setp.ne.b32 p, %4, 0;\n"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n"
+      "}\n" ::"r"(d_tmem),
+      "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// arrive on ONE barrier (shared::cluster address, either CTA) once the pair's MMAs issued so
+// far are done; the leader issues one of these per CTA that has to learn of it
+__device__ __forceinline__ void umma_commit_pair(uint32_t bar_cluster_addr) {
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(
+                   bar_cluster_addr)
                : "memory");
 }
 

@@ -66,7 +66,9 @@ def comm_gemm(ctx, *, a_ptrs, b_ptrs, M, N, K, lda, ldb, a_mn, b_mn, dtype, gath
         list(ctx.peer_flag_ptrs), list(recv.ptrs()) if recv is not None else [],
         list(ar_out.ptrs()) if ar_out is not None else [], float(ctx.wait_seconds),
         stage.data_ptr() if stage is not None else 0,
-        chunk_flags.data_ptr() if chunk_flags is not None else 0)
+        chunk_flags.data_ptr() if chunk_flags is not None else 0,
+        int(getattr(recv, "mc_ptr", 0)) if recv is not None else 0,
+        int(getattr(ar_out, "mc_ptr", 0)) if ar_out is not None else 0)
     return epoch
 
 

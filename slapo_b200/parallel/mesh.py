@@ -35,6 +35,9 @@ class DeviceMesh:
             rank = dist.get_rank() if dist.is_available() and dist.is_initialized() else 0
         self.rank = rank
         self.groups = {axis: None for axis in _AXES}
+        # (lower stage, "fwd" | "bwd") -> 2-rank group of this rank's pipeline link in that
+        # direction (only the links this rank is an end of)
+        self.p2p_groups = {}
         if create_groups and dist.is_available() and dist.is_initialized():
             if dist.get_world_size() != self.world_size:
                 raise ValueError(f"mesh {self.dims} needs {self.world_size} ranks, "
@@ -85,6 +88,20 @@ class DeviceMesh:
                 group = dist.new_group(ranks) if len(ranks) > 1 else None
                 if self.rank in ranks:
                     self.groups[axis] = group
+        # Pipeline links: one 2-rank group per adjacent stage pair AND direction, so that every
+        # direction has its own communicator (on GPUs: its own NCCL stream).  Activations going
+        # down the pipeline and gradients coming back never queue behind each other, both ends
+        # of a communicator issue its transfers in micro-batch order, and plain (unbatched)
+        # isend / irecv cannot dead-lock.
+        for stage in range(self.dims["pp"] - 1):
+            for dp in range(self.dims["dp"]):
+                for tp in range(self.dims["tp"]):
+                    pair = [self.get_rank(pp=stage, dp=dp, tp=tp),
+                            self.get_rank(pp=stage + 1, dp=dp, tp=tp)]
+                    for direction in ("fwd", "bwd"):
+                        group = dist.new_group(pair)
+                        if self.rank in pair:
+                            self.p2p_groups[(stage, direction)] = group
 
     @property
     def schedule_group(self):

@@ -37,10 +37,13 @@ def _align(n, a=256):
 class SymmBuffer:
     """A symmetric allocation: local tensor (uint8) + every rank's base address."""
 
-    def __init__(self, local: torch.Tensor, peer_ptrs, handle=None):
+    def __init__(self, local: torch.Tensor, peer_ptrs, handle=None, mc_ptr=0):
         self.local = local
         self.peer_ptrs = list(peer_ptrs)
         self.handle = handle
+        # NVLS address: loads through it return a reduction over every rank's copy, stores
+        # land in every copy (0 = the buffer is not bound to an NVSwitch group)
+        self.mc_ptr = int(mc_ptr)
         self.nbytes = local.numel() * local.element_size()
 
     def view(self, dtype, shape, offset_bytes=0):
@@ -58,7 +61,15 @@ class SymmBuffer:
 
 
 class SymmContext:
-    def __init__(self, group=None, device=None, wait_seconds: float = 2.0):
+    def __init__(self, group=None, device=None, wait_seconds: float = 30.0, nvls=None):
+        """``wait_seconds``: limit of a kernel's wait for a peer (ranks of a training job drift
+        apart by whole seconds around checkpoints and data stalls; tests that make a wait run
+        out pass a short limit).  ``nvls``: let the kernels reduce through the NVSwitch
+        (``multimem``) where the buffers have such an address; default: groups of four ranks
+        or more - at two ranks peer loads are faster - unless ``SLAPO_B200_NVLS`` is 0 / 1.
+        Jobs in which a rank may leave while others run keep it off."""
+        import os
+
         import torch.distributed._symmetric_memory as symm_mem
 
         self._symm = symm_mem
@@ -70,6 +81,10 @@ class SymmContext:
         self.device = torch.device(device) if device is not None else torch.device(
             "cuda", torch.cuda.current_device())
         self.wait_seconds = wait_seconds
+        env = os.environ.get("SLAPO_B200_NVLS")
+        if nvls is None:
+            nvls = self.world >= 4 if env is None else env == "1"
+        self.nvls = bool(nvls)
         self.epoch = 0
         self._buffers: dict[str, SymmBuffer] = {}
         flags = self._alloc("__flags__", FLAG_WORDS * 4)
@@ -87,7 +102,13 @@ class SymmContext:
         torch.cuda.synchronize(self.device)
         hdl = self._symm.rendezvous(t, group=self.group)
         ptrs = [int(p) for p in hdl.buffer_ptrs]
-        buf = SymmBuffer(t, ptrs, hdl)
+        mc = 0
+        if self.nvls:
+            try:
+                mc = int(hdl.multicast_ptr)
+            except Exception:   # no NVSwitch group on this system
+                mc = 0
+        buf = SymmBuffer(t, ptrs, hdl, mc)
         self._buffers[name] = buf
         return buf
 
@@ -119,6 +140,7 @@ class LocalSymmContext:
     def __init__(self, world: int, device=None, wait_seconds: float = 0.05):
         self.world, self.rank = world, 0
         self.group = None
+        self.nvls = False
         self.device = torch.device(device) if device is not None else torch.device(
             "cuda", torch.cuda.current_device())
         self.wait_seconds = wait_seconds

@@ -85,14 +85,24 @@ def _is_tp_sharded(p) -> bool:
 
 
 class _Bucket:
-    __slots__ = ("start", "end", "pending", "n_params", "event", "handle")
+    """A slice of the flat gradient buffer that is reduced as one unit.
+
+    ``fired`` counts gradient-accumulation events of the bucket's parameters during the last
+    backward of a step; ``expected`` is that count as calibrated on the first step (a module
+    called several times under re-entrant checkpointing accumulates into its parameters once
+    per call, so the number of parameters is not the right figure).  The bucket is reduced
+    from the hook when ``fired`` reaches ``expected``; ``late`` records an accumulation that
+    arrived after that launch."""
+    __slots__ = ("start", "end", "n_params", "fired", "expected", "launched", "late", "deferred")
 
     def __init__(self, start):
         self.start, self.end = start, start
-        self.pending = 0
         self.n_params = 0
-        self.event = None
-        self.handle = None
+        self.fired = 0
+        self.expected = None
+        self.launched = False
+        self.late = False
+        self.deferred = False
 
 
 class TrainEngine:
@@ -122,6 +132,10 @@ class TrainEngine:
         self.step_count = 0
         self.micro_step = 0
         self.last_grad_norm = None
+        self.heartbeat = None       # runtime.health.Heartbeat, told about device-side give-ups
+        self._final_backward = True   # the running backward is the last one before step()
+        self._status_host = None      # pinned copy of the kernels' status word, one step behind
+        self._status_event = None
         self._build_flat_storage()
         self._build_optimizer_state()
         self._install_grad_hooks()
@@ -143,20 +157,36 @@ class TrainEngine:
             raise ValueError("all trainable parameters must share one dtype")
         # reverse registration order ~ the order in which backward finishes them
         self.params = list(reversed(params))
+        # Parameters replicated over the tensor-parallel group whose gradients are partial sums
+        # (sequence parallelism) go to the end of the flat buffer as one contiguous region in
+        # buckets of their own, so that their gradient sync is ONE in-place all-reduce.
+        n_rep = 0
+        if self.tp_size > 1:
+            rep = [p for p in self.params if getattr(p, "replicated_param", False)]
+            n_rep = len(rep)
+            if rep:
+                self.params = [p for p in self.params
+                               if not getattr(p, "replicated_param", False)] + rep
+        first_rep = len(self.params) - n_rep
         align = 128 * max(self.dp_size, 1)  # elements; keeps every shard 256-byte aligned
         bucket_elems = max(int(self.cfg.bucket_mb * 2**20 / params[0].element_size()), align)
         self.buckets: list[_Bucket] = []
         self.param_slices = []
         offset = 0
         bucket = _Bucket(0)
-        for p in self.params:
+        self.sp_region = None
+        for i_p, p in enumerate(self.params):
             n = p.numel()
             padded = (n + 7) // 8 * 8
-            if bucket.end - bucket.start > 0 and (bucket.end - bucket.start) + padded > bucket_elems:
+            new_region = n_rep > 0 and i_p == first_rep and bucket.end - bucket.start > 0
+            if new_region or (bucket.end - bucket.start > 0
+                              and (bucket.end - bucket.start) + padded > bucket_elems):
                 offset = (offset + align - 1) // align * align
                 bucket.end = offset
                 self.buckets.append(bucket)
                 bucket = _Bucket(offset)
+            if n_rep > 0 and i_p == first_rep:
+                self.sp_region = [offset, offset]
             self.param_slices.append((offset, n, len(self.buckets)))
             offset += padded
             bucket.end = offset
@@ -165,6 +195,13 @@ class TrainEngine:
         bucket.end = offset
         self.buckets.append(bucket)
         self.total = offset
+        if self.sp_region is not None:
+            self.sp_region[1] = offset   # padding between parameters stays zero on every rank
+            # summed over the tensor-parallel group in step() BEFORE the data-parallel
+            # reduction: these buckets are never reduced from the backward hooks
+            for b in self.buckets:
+                if b.start >= self.sp_region[0]:
+                    b.deferred = True
         if self._want_fused_dp():
             from ..parallel.fused_dp import FusedDP
             from ..parallel.symm import SymmContext
@@ -229,19 +266,38 @@ class TrainEngine:
             if p.dim() > 1 and not getattr(p, "no_weight_decay", False):
                 wd_flat[off:off + n] = True
         self.decay_mask = torch.cat([wd_flat[lo:hi] for lo, hi in self.shard_ranges]).to(torch.uint8)
-        # norm bookkeeping: replicated-over-TP parameters are counted once
-        self.tp_dup_mask = None
-        if self.tp_size > 1:
-            dup = torch.zeros(self.total, dtype=torch.bool, device=self.device)
-            for p, (off, n, _) in zip(self.params, self.param_slices):
-                if not _is_tp_sharded(p):
-                    dup[off:off + n] = True
-            self.tp_dup_mask = torch.cat([dup[lo:hi] for lo, hi in self.shard_ranges])
-            self.tp_dup_mask_u8 = self.tp_dup_mask.to(torch.uint8)
+        self._norm_skip = set()
+        self._build_norm_classes()
         self.comm_stream = torch.cuda.Stream() if self.device.type == "cuda" else None
 
+    def _build_norm_classes(self):
+        """Per-element class of this rank's gradient slices for the global norm: 0 = counted on
+        every tensor-parallel rank (sharded parameters), 1 = replicated over the tensor-parallel
+        group (counted once), 2 = not counted here (a parameter tied across pipeline stages is
+        counted by the first stage that owns it)."""
+        self.tp_dup_mask = None
+        self.tp_dup_mask_u8 = None
+        if self.tp_size <= 1 and not self._norm_skip:
+            return
+        cls = torch.zeros(self.total, dtype=torch.uint8, device=self.device)
+        for p, (off, n, _) in zip(self.params, self.param_slices):
+            if id(p) in self._norm_skip:
+                cls[off:off + n] = 2
+            elif self.tp_size > 1 and not _is_tp_sharded(p):
+                cls[off:off + n] = 1
+        self.tp_dup_mask_u8 = torch.cat([cls[lo:hi] for lo, hi in self.shard_ranges])
+        self.tp_dup_mask = self.tp_dup_mask_u8
+
+    def exclude_from_norm(self, params):
+        """Leave ``params`` out of this rank's share of the gradient norm."""
+        self._norm_skip |= {id(p) for p in params}
+        self._build_norm_classes()
+
     def _install_grad_hooks(self):
-        self._overlap = (self.cfg.overlap_comm and self.dp_size > 1 and self.device.type == "cuda")
+        # on CPU ranks the reduction of a bucket runs synchronously inside the hook; that mode
+        # exists to test the hook logic without GPUs (``overlap_on_cpu`` in the config)
+        self._overlap = (self.cfg.overlap_comm and self.dp_size > 1 and
+                         (self.device.type == "cuda" or bool(self.cfg.extra.get("overlap_on_cpu"))))
         if not self._overlap:
             return
         for p, (_, _, b_idx) in zip(self.params, self.param_slices):
@@ -249,14 +305,31 @@ class TrainEngine:
 
     def _make_hook(self, b_idx):
         def hook(_param):
-            if (self.micro_step + 1) % self.cfg.grad_accum_steps != 0:
+            if not self._final_backward:
                 return
             bucket = self.buckets[b_idx]
-            bucket.pending += 1
-            if bucket.pending == bucket.n_params:
+            bucket.fired += 1
+            if bucket.launched:
+                bucket.late = True      # dealt with in step()
+            elif (bucket.expected is not None and not bucket.deferred
+                  and bucket.fired == bucket.expected):
                 self._launch_bucket_reduce(b_idx)
 
         return hook
+
+    def set_final_backward(self, flag: bool):
+        """Tell the overlap hooks whether the backward about to run is the last one before
+        ``step()``.  ``backward()`` does it from the accumulation counter; a caller that drives
+        autograd itself (the pipeline engine: one backward per micro-batch) sets it by hand."""
+        self._final_backward = bool(flag)
+
+    def defer_params(self, params):
+        """Never reduce the buckets of ``params`` from the hooks: their gradients are still
+        modified after backward (parameters tied across pipeline stages)."""
+        ids = {id(p) for p in params}
+        for p, (_, _, b_idx) in zip(self.params, self.param_slices):
+            if id(p) in ids:
+                self.buckets[b_idx].deferred = True
 
     # ------------------------------------------------------------------ #
     def _launch_bucket_reduce(self, b_idx):
@@ -288,18 +361,32 @@ class TrainEngine:
             else:
                 dist.all_reduce(grad, group=self.dp_group)
                 grad.div_(self.dp_size)
-        bucket.pending = 0
-        bucket.handle = True
+        bucket.launched = True
 
     def _reduce_all_buckets(self):
         for i, bucket in enumerate(self.buckets):
-            if bucket.handle is None:
+            if bucket.launched and bucket.late:
+                # A gradient was accumulated after the bucket had been reduced from its hook
+                # (the autograd graph differs from the calibrated step).  Reduce-scatter
+                # leaves the flat gradient untouched, so it can simply run again; the in-place
+                # all-reduce and the peer-memory kernels (one launch per step epoch) cannot.
+                if self.fdp is None and self.cfg.zero:
+                    bucket.launched = False
+                else:
+                    raise RuntimeError(
+                        "a gradient arrived after its bucket had been reduced during backward "
+                        "(the set of gradient accumulations changed between steps); build the "
+                        "engine with overlap_comm=False for models whose graph varies")
+            if not bucket.launched:
                 self._launch_bucket_reduce(i)
         if self.comm_stream is not None:
             torch.cuda.current_stream().wait_stream(self.comm_stream)
         for bucket in self.buckets:
-            bucket.handle = None
-            bucket.pending = 0
+            if self._overlap and bucket.fired and bucket.expected != bucket.fired:
+                bucket.expected = bucket.fired     # first step, or the graph changed
+            bucket.fired = 0
+            bucket.launched = False
+            bucket.late = False
 
     # ------------------------------------------------------------------ #
     def __call__(self, *args, **kwargs):
@@ -308,6 +395,7 @@ class TrainEngine:
     def backward(self, loss):
         if self.cfg.grad_accum_steps > 1:
             loss = loss / self.cfg.grad_accum_steps
+        self._final_backward = (self.micro_step + 1) % self.cfg.grad_accum_steps == 0
         loss.backward()
         self.micro_step += 1
 
@@ -328,9 +416,9 @@ class TrainEngine:
             return self._finish_norm(parts)
         g = grad.float()
         if self.tp_dup_mask is not None:
-            dup = self.tp_dup_mask
-            sq_shard = (g * (~dup)).pow(2).sum()
-            sq_dup = (g * dup).pow(2).sum()
+            cls = self.tp_dup_mask
+            sq_shard = (g * (cls == 0)).pow(2).sum()
+            sq_dup = (g * (cls == 1)).pow(2).sum()
             parts = torch.stack([sq_shard, sq_dup])
         else:
             parts = torch.stack([g.pow(2).sum(), torch.zeros((), device=g.device)])
@@ -345,20 +433,22 @@ class TrainEngine:
             total = shard_part[0] + parts[1]
         else:
             total = parts[0] + parts[1]
+        if self.mesh is not None and self.mesh.pp_size > 1 and self.mesh.pp_group is not None:
+            # one norm for the whole model: the stages add up their parts
+            total = total.reshape(1).clone()
+            dist.all_reduce(total, group=self.mesh.pp_group)
+            total = total[0]
         return total.sqrt()
 
     def step(self):
         """Synchronise gradients, clip, AdamW-update, re-gather parameters."""
         if self.micro_step % self.cfg.grad_accum_steps != 0:
             return False
-        # sequence-parallel: replicated parameters got partial gradients
+        # sequence-parallel: replicated parameters got partial gradients; they are one
+        # contiguous region of the flat gradient buffer, summed in place
         if self.sp_sync_params:
-            flat = torch.cat([p.grad.reshape(-1) for p in self.sp_sync_params])
-            dist.all_reduce(flat, group=self.tp_group)
-            pos = 0
-            for p in self.sp_sync_params:
-                p.grad.copy_(flat[pos:pos + p.numel()].view_as(p.grad))
-                pos += p.numel()
+            lo, hi = self.sp_region
+            dist.all_reduce(self.flat_grad[lo:hi], group=self.tp_group)
         if self.dp_size > 1:
             self._reduce_all_buckets()
         grad = self._own_grad()
@@ -377,7 +467,48 @@ class TrainEngine:
         self._params_pushed = self.fdp is not None
         self._gather_params()
         self.flat_grad.zero_()
+        self._poll_device_status()
         return True
+
+    # ---- device status (bounded waits of the peer-memory kernels) -------- #
+    def _watches_status(self):
+        return (self.device.type == "cuda" and native.available()
+                and (self.tp_size > 1 or self.dp_size > 1 or self.mesh is not None))
+
+    def _raise_device_status(self, code):
+        native.ops().device_status()     # reads and clears the word
+        msg = (f"device status {code} after step {self.step_count}: a bounded wait on a peer ran "
+               "out inside a fused kernel (a rank is missing, stuck or more than the wait limit "
+               "behind); the outputs of that step are not valid")
+        if self.heartbeat is not None:
+            self.heartbeat.report_failure(msg)
+        raise RuntimeError(msg)
+
+    def _poll_device_status(self):
+        """Once per step, without a device synchronisation: the status word of the step that
+        just ended is copied to pinned memory behind the step's work, and the copy made at the
+        end of the PREVIOUS step - long complete by now - is examined.  A give-up is therefore
+        reported one step late; ``check_device_status()`` closes that gap at the end of a run."""
+        if not self._watches_status() or torch.cuda.is_current_stream_capturing():
+            return
+        if self._status_event is None:
+            self._status_host = torch.zeros(1, dtype=torch.int32).pin_memory()
+            self._status_event = torch.cuda.Event()
+        else:
+            self._status_event.synchronize()
+            code = int(self._status_host[0])
+            if code:
+                self._raise_device_status(code)
+        self._status_host.copy_(native.ops().device_status_tensor()[:1], non_blocking=True)
+        self._status_event.record()
+
+    def check_device_status(self):
+        """Synchronise and raise if any kernel of this device gave up a bounded wait."""
+        if not self._watches_status():
+            return
+        code = int(native.ops().device_status())
+        if code:
+            self._raise_device_status(code)
 
     def _adamw(self, grad, lr, clip_coef):
         b1, b2 = self.cfg.betas

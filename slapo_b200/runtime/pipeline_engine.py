@@ -11,12 +11,22 @@ per stage.
 Stage boundaries are described statically (``live_in`` of
 :func:`slapo_b200.parallel.pipeline_partition.analyze_pipeline_module`): the
 ordered value names that cross each boundary.  Shapes and dtypes are exchanged
-ONCE, with the first micro-batch; afterwards only tensors move, as batched
-``isend`` / ``irecv`` pairs over the process group (NCCL on GPUs: the transfers
-run on the communicator's stream and overlap the neighbouring compute; gloo on
-CPU ranks).  The reference delegates all of this to DeepSpeed's
-``PipelineModule`` and re-decodes a metadata tensor on the host for every
-micro-batch (slapo/framework_dialect/deepspeed/pipeline.py:226-354).
+ONCE, with the first micro-batch; afterwards only tensors move.
+
+Transfers overlap compute.  Every pipeline link has one 2-rank process group per
+direction (``DeviceMesh.p2p_groups``): on GPUs that is one NCCL communicator
+with its own stream for the activations going down and another for the
+gradients coming back.  Receives are posted one micro-batch ahead (the input
+of micro-batch i + 1 and the output gradient of the oldest micro-batch in
+flight are on the wire while micro-batch i computes) and waited for only where
+the tensor is consumed; sends are never waited for until the end of the batch
+(the Work objects keep the tensors alive).  ``Work.wait()`` on NCCL makes the
+compute stream wait, not the host, so the host runs ahead and keeps both
+queues full.  On CPU ranks (gloo) the same code runs with host-blocking waits.
+The reference delegates all of this to DeepSpeed's ``PipelineModule``, which
+exchanges blocking send / recv pairs and re-decodes a metadata tensor on the
+host for every micro-batch
+(slapo/framework_dialect/deepspeed/pipeline.py:205-354).
 
 Parameters shared by two stages (tied embeddings) get their gradients summed
 over the owning stages before the optimizer step.
@@ -131,7 +141,15 @@ class PipelineEngine:
                                  dp_group=mesh.dp_group)
         self.inner.cfg.grad_accum_steps = 1
         self._meta_fwd = None   # [(name, shape, dtype, requires_grad)] of live_in[stage]
+        self._meta_sent = False
+        self._inflight = []     # Work objects of sends not yet waited for
         self._tied = self._find_tied()
+        # gradients of parameters shared with another stage change after backward (the other
+        # stage's part is added): their buckets are reduced in step(), never from a hook
+        self.inner.defer_params([p for p, stages in self._tied if self.stage_id in stages])
+        # ... and they enter the global gradient norm once, on the first stage that owns them
+        self.inner.exclude_from_norm([p for p, stages in self._tied
+                                      if self.stage_id in stages and self.stage_id != stages[0]])
         self._sync_tied_params()
         self.last_loss = None
 
@@ -151,58 +169,81 @@ class PipelineEngine:
 
     def _sync_tied_params(self):
         """Stages initialise their parameters independently; a parameter shared by several
-        stages (tied embedding / LM head) takes the value of the first stage that owns it."""
+        stages (tied embedding / LM head) takes the value of the first stage that owns it.
+        One batched group of sends / receives per rank."""
         c = self.mesh.get_coord()
+        ops, copies = [], []
         for p, stages in self._tied:
             if self.stage_id not in stages or p.is_meta:
                 continue
             src_stage = stages[0]
             if self.stage_id == src_stage:
                 for s in stages[1:]:
-                    dist.send(p.data.contiguous(), dst=self.mesh.get_rank(pp=s, dp=c["dp"], tp=c["tp"]))
+                    ops.append(dist.P2POp(dist.isend, p.data.contiguous(),
+                                          self.mesh.get_rank(pp=s, dp=c["dp"], tp=c["tp"])))
             else:
                 buf = torch.empty_like(p.data)
-                dist.recv(buf, src=self.mesh.get_rank(pp=src_stage, dp=c["dp"], tp=c["tp"]))
-                p.data.copy_(buf)
+                ops.append(dist.P2POp(dist.irecv, buf,
+                                      self.mesh.get_rank(pp=src_stage, dp=c["dp"], tp=c["tp"])))
+                copies.append((p, buf))
+        if ops:
+            for w in dist.batch_isend_irecv(ops):
+                w.wait()
+        for p, buf in copies:
+            p.data.copy_(buf)
 
     def _sync_tied_grads(self):
         c = self.mesh.get_coord()
+        ops, adds = [], []
         for p, stages in self._tied:
             if self.stage_id not in stages or p.grad is None:
                 continue
             ranks = [self.mesh.get_rank(pp=s, dp=c["dp"], tp=c["tp"]) for s in stages]
             # pairwise exchange keeps it group-free: sum = mine + theirs
-            others = [r for r in ranks if r != self.mesh.rank]
-            recv = [torch.empty_like(p.grad) for _ in others]
-            ops = []
-            for r, buf in zip(others, recv):
+            for r in ranks:
+                if r == self.mesh.rank:
+                    continue
+                buf = torch.empty_like(p.grad)
                 ops.append(dist.P2POp(dist.isend, p.grad.contiguous(), r))
                 ops.append(dist.P2POp(dist.irecv, buf, r))
-            for w in dist.batch_isend_irecv(ops):
-                w.wait()
-            for buf in recv:
-                p.grad.add_(buf)
-
-    # ---- p2p helpers ---------------------------------------------------- #
-    # Every exchange is ONE batched isend/irecv group, and a stage always
-    # pairs "send to a neighbour" with the matching "receive from that
-    # neighbour" in the same group (send_forward_recv_backward etc.), so the
-    # two sides of a link never wait for each other in opposite order.
-    def _exchange(self, sends, recvs):
-        ops = [dist.P2POp(dist.isend, t.contiguous(), peer) for t, peer in sends]
-        ops += [dist.P2POp(dist.irecv, t, peer) for t, peer in recvs]
+                adds.append((p, buf))
         if ops:
             for w in dist.batch_isend_irecv(ops):
                 w.wait()
+        for p, buf in adds:
+            p.grad.add_(buf)
+
+    # ---- p2p helpers ---------------------------------------------------- #
+    def _link(self, lower_stage, direction):
+        group = self.mesh.p2p_groups.get((lower_stage, direction))
+        if group is None:
+            raise RuntimeError(f"no pipeline link group for stage {lower_stage} ({direction}); "
+                               "build the DeviceMesh with create_groups=True")
+        return group
+
+    def _isend(self, tensors, peer, group):
+        for t in tensors:
+            self._inflight.append(dist.isend(t.contiguous(), dst=peer, group=group))
+
+    @staticmethod
+    def _irecv(tensors, peer, group):
+        return [dist.irecv(t, src=peer, group=group) for t in tensors]
+
+    @staticmethod
+    def _wait(works):
+        for w in works or ():
+            w.wait()
 
     def _handshake_send(self, tensors, names):
         meta = [(n, tuple(t.shape), str(t.dtype).replace("torch.", ""), bool(t.requires_grad))
                 if torch.is_tensor(t) else (n, None, None, t) for n, t in zip(names, tensors)]
-        dist.send_object_list([meta], dst=self.next_rank, device=self.device)
+        dist.send_object_list([meta], dst=self.next_rank, group=self._link(self.stage_id, "fwd"),
+                              device=self.device)
 
     def _handshake_recv(self):
         box = [None]
-        dist.recv_object_list(box, src=self.prev_rank, device=self.device)
+        dist.recv_object_list(box, src=self.prev_rank, group=self._link(self.stage_id - 1, "fwd"),
+                              device=self.device)
         return box[0]
 
     def _fwd_recv_buffers(self):
@@ -223,6 +264,32 @@ class PipelineEngine:
     @staticmethod
     def _tensor_list(bufs):
         return [t for _, t, _ in bufs if t is not None] if bufs else []
+
+    def _post_recv_forward(self):
+        """Post the receives of the next micro-batch's inputs: (buffers, works)."""
+        if self.stage_id == 0:
+            return None, None
+        bufs = self._fwd_recv_buffers()
+        works = self._irecv(self._tensor_list(bufs), self.prev_rank,
+                            self._link(self.stage_id - 1, "fwd"))
+        return bufs, works
+
+    def _send_forward(self, rec):
+        if self.stage_id < self.n_stages - 1:
+            self._isend([t.detach() for t in rec["payload"]], self.next_rank,
+                        self._link(self.stage_id, "fwd"))
+
+    def _post_recv_backward(self, rec):
+        """Post the receives of the output gradients of a micro-batch in flight."""
+        grads = [torch.empty_like(t) for t in rec["sent"]]
+        works = []
+        if self.stage_id < self.n_stages - 1 and grads:
+            works = self._irecv(grads, self.next_rank, self._link(self.stage_id, "bwd"))
+        return grads, works
+
+    def _send_backward(self, in_grads):
+        if self.stage_id > 0 and in_grads:
+            self._isend(in_grads, self.prev_rank, self._link(self.stage_id - 1, "bwd"))
 
     # ---- compute ---------------------------------------------------------- #
     def _compute_forward(self, mb_inputs, labels, bufs):
@@ -250,7 +317,7 @@ class PipelineEngine:
             return rec
         names = self.model.live_in[self.stage_id + 1]
         tensors = [env[n] for n in names]
-        if not getattr(self, "_meta_sent", False):
+        if not self._meta_sent:
             self._handshake_send(tensors, names)
             self._meta_sent = True
         rec["payload"] = [t for t in tensors if torch.is_tensor(t)]
@@ -273,62 +340,61 @@ class PipelineEngine:
             for i, piece in enumerate(_split_micro(val, m)):
                 micro_inputs[i][name] = piece
         micro_labels = _split_micro(labels, m) if labels is not None else [None] * m
-        first, last = self.stage_id == 0, self.stage_id == self.n_stages - 1
         warmup = min(self.n_stages - self.stage_id - 1, m)
         steady = m - warmup
-        prev, nxt = self.prev_rank, self.next_rank
         pending, losses = [], []
         fwd_i = 0
+        bwd_i = 0
+        self.inner.set_final_backward(False)
 
-        def recv_forward():
-            bufs = self._fwd_recv_buffers()
-            if not first:
-                self._exchange([], [(t, prev) for t in self._tensor_list(bufs)])
-            return bufs
-
-        def send_forward(rec):
-            if not last:
-                self._exchange([(t.detach(), nxt) for t in rec["payload"]], [])
-
-        def grad_buffers(rec):
-            return [torch.empty_like(t) for t in rec["sent"]]
-
-        for _ in range(warmup):
-            bufs = recv_forward()
+        def forward_one(cur):
+            """Prefetch the next input, then run micro-batch ``fwd_i`` on the input ``cur``
+            whose receives were posted one micro-batch ago."""
+            nonlocal fwd_i
+            nxt = self._post_recv_forward() if fwd_i + 1 < m else (None, None)
+            bufs, works = cur
+            self._wait(works)
             rec = self._compute_forward(micro_inputs[fwd_i], micro_labels[fwd_i], bufs)
             fwd_i += 1
-            send_forward(rec)
+            self._send_forward(rec)
             pending.append(rec)
-        bufs = recv_forward() if steady > 0 else None
-        for it in range(steady):
-            rec = self._compute_forward(micro_inputs[fwd_i], micro_labels[fwd_i], bufs)
-            fwd_i += 1
-            pending.append(rec)
-            # send this forward result, receive the gradient of the oldest one
-            done = pending.pop(0)
-            grads = grad_buffers(done)
-            if not last:
-                self._exchange([(t.detach(), nxt) for t in rec["payload"]],
-                               [(g, nxt) for g in grads])
+            return nxt
+
+        def backward_one(done, posted):
+            nonlocal bwd_i
+            grads, works = posted
+            self._wait(works)
             if done["loss"] is not None:
                 losses.append(done["loss"].detach())
-            in_grads = self._compute_backward(done, grads)
-            # send the input gradients, receive the next forward input
-            more = it + 1 < steady
-            bufs = self._fwd_recv_buffers() if (more and not first) else None
-            if not first:
-                self._exchange([(g, prev) for g in in_grads],
-                               [(t, prev) for t in self._tensor_list(bufs)])
+            # the data-parallel hooks may reduce a bucket only during the step's last backward
+            self.inner.set_final_backward(bwd_i == m - 1)
+            bwd_i += 1
+            self._send_backward(self._compute_backward(done, grads))
+
+        cur = self._post_recv_forward()
+        for _ in range(warmup):
+            cur = forward_one(cur)
+        posted = None
+        for _ in range(steady):
+            # the output gradient of the oldest micro-batch travels during this forward
+            if pending and posted is None:
+                posted = self._post_recv_backward(pending[0])
+            cur = forward_one(cur)
+            done = pending.pop(0)
+            if posted is None:     # last stage: nothing in flight before this forward
+                posted = self._post_recv_backward(done)
+            this, posted = posted, None
+            backward_one(done, this)
         while pending:
             done = pending.pop(0)
-            grads = grad_buffers(done)
-            if not last:
-                self._exchange([], [(g, nxt) for g in grads])
-            if done["loss"] is not None:
-                losses.append(done["loss"].detach())
-            in_grads = self._compute_backward(done, grads)
-            if not first:
-                self._exchange([(g, prev) for g in in_grads], [])
+            this = posted if posted is not None else self._post_recv_backward(done)
+            # ... and the next one's during this backward
+            posted = self._post_recv_backward(pending[0]) if pending else None
+            backward_one(done, this)
+        # sends: make the compute stream (NCCL) or the host (gloo) wait before buffers go away
+        self._wait(self._inflight)
+        self._inflight = []
+        self.inner.set_final_backward(True)
         self._sync_tied_grads()
         self.inner.micro_step = 0
         self.inner.step()

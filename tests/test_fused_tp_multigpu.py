@@ -20,7 +20,7 @@ def _close(a, b, k, tol=3e-2):
     torch.testing.assert_close(a.float() / scale, b.float() / scale, rtol=tol, atol=tol)
 
 
-def _worker(rank, world):
+def _worker(rank, world, nvls):
     import torch.distributed as dist
 
     from slapo_b200.ops import native
@@ -28,7 +28,8 @@ def _worker(rank, world):
     from slapo_b200.parallel.symm import SymmContext
 
     dev = torch.device("cuda", rank)
-    ctx = SymmContext(None, dev)
+    # nvls: the reduction goes through the NVSwitch (multimem) instead of loading from every peer
+    ctx = SymmContext(None, dev, nvls=nvls)
     torch.manual_seed(1234)
     ts, k, n = 256, 256, 384
     t = ts * world
@@ -88,7 +89,8 @@ def _worker(rank, world):
     dist.barrier()
 
 
+@pytest.mark.parametrize("nvls", [False, True])
 @pytest.mark.parametrize("world", [2, 4])
-def test_fused_tp_linears_on_peers(world):
+def test_fused_tp_linears_on_peers(world, nvls):
     _need_gpus(world)
-    run_distributed(_worker, world, backend="nccl")
+    run_distributed(_worker, world, nvls, backend="nccl")
