@@ -41,6 +41,23 @@ ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
 MODEL = dict(layers=24, hidden=1024, heads=16, ffn=4096, vocab=30522, seq=512)
+# the second headline model: OPT-2.7B-shaped causal LM, sequence 1024, micro-batches of 4,
+# 8 samples per GPU per step (global batch 64 on 8 GPUs, where the native arm runs the
+# pipeline configuration PP 2 x TP 4 with 16 micro-batches)
+OPT = dict(name="opt-2.7b", layers=32, hidden=2560, heads=32, ffn=10240, vocab=50272, seq=1024,
+           micro_batch=4, batch_per_gpu=8)
+
+# keys of the "config" object, identical for both arms (arm-specific remarks go to "notes")
+CONFIG_KEYS = ("model", "layers", "global_batch", "seq_len", "parallelism", "ckpt_ratio",
+               "optimizer", "micro_batch", "l2_policy")
+L2_POLICY = ("per-step working set (weights+activations, >10 GB) exceeds the 126 MB L2, "
+             "nothing survives between steps")
+
+
+def make_config(model, layers, global_batch, seq_len, parallelism, ckpt_ratio, micro_batch):
+    return {"model": model, "layers": layers, "global_batch": global_batch, "seq_len": seq_len,
+            "parallelism": parallelism, "ckpt_ratio": ckpt_ratio, "optimizer": "AdamW",
+            "micro_batch": micro_batch, "l2_policy": L2_POLICY}
 
 
 def parse_args():
@@ -49,10 +66,21 @@ def parse_args():
     ap.add_argument("--steps", type=int, default=8)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="native", choices=["native", "reference"])
-    ap.add_argument("--batch-per-gpu", type=int, default=32)
-    ap.add_argument("--seq", type=int, default=MODEL["seq"])
-    ap.add_argument("--layers", type=int, default=MODEL["layers"])
-    ap.add_argument("--ckpt-ratio", type=float, default=0.5)
+    ap.add_argument("--model", default="bert-large", choices=["bert-large", "opt-2.7b"],
+                    help="bert-large: the headline run; opt-2.7b: the second headline model "
+                         "(same JSON line, metric 'train samples/sec, OPT-2.7B causal LM')")
+    ap.add_argument("--with-opt", action="store_true",
+                    help="after the BERT-large run also run OPT-2.7B and attach its record to "
+                         "the JSON line under 'opt'")
+    ap.add_argument("--batch-per-gpu", type=int, default=0, help="0 = the model's default")
+    ap.add_argument("--seq", type=int, default=0, help="0 = the model's default")
+    ap.add_argument("--layers", type=int, default=0, help="0 = the model's default")
+    ap.add_argument("--ckpt-ratio", type=float, default=-1.0,
+                    help="-1 = the model's default (bert-large 0.5, opt-2.7b 0)")
+    ap.add_argument("--opt-layout", default="auto", choices=["auto", "tp", "pp2"],
+                    help="opt-2.7b on 8 GPUs: pp2 = PP 2 x TP 4 (default), tp = TP 8")
+    ap.add_argument("--no-tp-check", action="store_true",
+                    help="skip the fused-vs-NCCL numerical check that multi-GPU runs do first")
     ap.add_argument("--parallelism", default="tp", choices=["tp", "dp"])
     ap.add_argument("--no-sequence-parallel", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
@@ -64,7 +92,14 @@ def parse_args():
     ap.add_argument("--profile", action="store_true",
                     help="print a per-kernel time table of one step (torch.profiler, rank 0); "
                          "analysis aid only, the reported numbers are taken without it")
-    return ap.parse_args()
+    args = ap.parse_args()
+    bert = args.model == "bert-large"
+    args.batch_per_gpu = args.batch_per_gpu or (32 if bert else OPT["batch_per_gpu"])
+    args.seq = args.seq or (MODEL["seq"] if bert else OPT["seq"])
+    args.layers = args.layers or (MODEL["layers"] if bert else OPT["layers"])
+    if args.ckpt_ratio < 0:
+        args.ckpt_ratio = 0.5 if bert else 0.0
+    return args
 
 
 # --------------------------------------------------------------------------- #
@@ -211,13 +246,76 @@ def build_native(args, world, rank):
     return engine, vocab, parallelism, dp
 
 
+def tp_numerical_check(world, device):
+    """Before a tensor-parallel run is timed: the same 2-layer BERT-large-shaped model, same
+    weights, same batch, once through the fused GEMM + collective kernels and once through
+    this framework's NCCL ``sync`` ops; returns the relative differences of the loss and of the
+    gradients (max over parameters of max|g_fused - g_nccl| / max|g_nccl|).  This is the
+    evidence that the peer-memory path computes the right thing on real NVLink."""
+    import torch
+
+    import slapo_b200 as slapo
+    from slapo_b200.models import BertConfig, BertForMaskedLM, mlm_loss
+    from slapo_b200.models.schedules.common import pad_vocab
+    from slapo_b200.parallel.mesh import DeviceMesh
+
+    mesh = DeviceMesh(pp=1, dp=1, tp=world)
+    vocab = pad_vocab(MODEL["vocab"], 8 * world)
+    cfg = BertConfig(vocab_size=vocab, hidden_size=MODEL["hidden"], num_hidden_layers=2,
+                     num_attention_heads=MODEL["heads"], intermediate_size=MODEL["ffn"],
+                     max_position_embeddings=512, hidden_dropout_prob=0.0,
+                     attention_probs_dropout_prob=0.0)
+    ids, labels = make_batch(vocab, 4 * world, 512, 4321, device)
+    runs = []
+    for fused in (True, False):
+        slapo.set_random_seed(77, dp_rank=0, tp_rank=mesh.tp_rank, always_enable_tp_seed=True)
+        with slapo.init_empty_weights():
+            model = BertForMaskedLM(cfg)
+        sch = slapo.model_schedule.apply_schedule(
+            model, "bert", model_config=cfg, bf16=True, group=mesh.schedule_group,
+            ckpt_ratio=0.0, sequence_parallel=True)
+        engine, _ = slapo.build(sch, target="native", mesh=mesh, fused_tp=fused,
+                                config={"lr": 0.0, "clip_grad": 0.0})
+        out = engine(ids)
+        loss = mlm_loss(out["logits"], labels, mesh.tp_group, True)
+        loss.backward()
+        torch.cuda.synchronize()
+        runs.append((float(loss), [p.grad.detach().float().clone() for p in engine.params]))
+        del engine, model, sch, out, loss
+    (l_f, g_f), (l_n, g_n) = runs
+    grad_err = 0.0
+    for a, b in zip(g_f, g_n):
+        denom = float(b.abs().max())
+        if denom > 0:
+            grad_err = max(grad_err, float((a - b).abs().max()) / denom)
+    t = torch.tensor([abs(l_f - l_n) / max(abs(l_n), 1e-6), grad_err], device=device)
+    import torch.distributed as dist
+
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    torch.cuda.empty_cache()
+    return {"loss_fused": l_f, "loss_nccl": l_n, "loss_rel_err": float(t[0]),
+            "grad_max_rel_err": float(t[1]), "ok": bool(t[0] < 2e-2 and t[1] < 2e-2),
+            "model": "2-layer bert-large shape, 4 samples x 512 tokens per rank, tp+sp"}
+
+
 def run_native(args):
     import torch
 
     from slapo_b200.ops import native
 
+    if args.model == "opt-2.7b":
+        return run_native_opt(args)
     world, rank, local = dist_setup(args)
     device = torch.device("cuda", local)
+    tp_check = None
+    if world > 1 and args.parallelism == "tp" and not args.no_tp_check \
+            and not args.no_sequence_parallel:
+        tp_check = tp_numerical_check(world, device)
+        if rank == 0 and not tp_check["ok"]:
+            print(f"# WARNING: fused and NCCL tensor-parallel paths disagree: {tp_check}",
+                  file=sys.stderr)
+        if max(tp_check["loss_rel_err"], tp_check["grad_max_rel_err"]) > 0.1:
+            raise RuntimeError(f"fused tensor-parallel kernels give wrong results: {tp_check}")
     engine, vocab, parallelism, dp = build_native(args, world, rank)
     tp = world // dp
     # TP ranks consume the same batch; DP replicas different ones
@@ -242,6 +340,7 @@ def run_native(args):
         else:
             engine.train_batch(ids, labels=labels)
 
+    args.cuda_graph_used = graphed is not None
     for i in range(args.warmup):
         step(i)
     sampler = ClockSampler(local)
@@ -273,6 +372,7 @@ def run_native(args):
             for ms_k, cnt, key in rows[:45]:
                 print(f"#   {ms_k:9.3f} {cnt:5d}  {key[:110]}", file=sys.stderr)
     e2e = None
+    losses = []
     if not args.no_e2e:
         host = [make_batch(vocab, local_batch, args.seq, 77 + dp_rank * 100 + i, "cpu", pin=True)
                 for i in range(2)]
@@ -284,32 +384,144 @@ def run_native(args):
             dl = hl.to(device, non_blocking=True)
             loss = graphed(di, labels=dl) if graphed is not None else \
                 engine.train_batch(di, labels=dl)
-            return float(loss.item())  # device -> host read of the result
+            losses.append(float(loss.item()))  # device -> host read of the result
+            return losses[-1]
 
         e2e_step(0)
         ms_e = timed_loop(e2e_step, args.steps, device, world)
         e2e = {"value": global_batch * args.steps / (ms_e / 1e3), "unit": "samples/s",
                "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": 4,
                "ms_per_step": ms_e / args.steps}
+    getattr(engine, "check_device_status", lambda: None)()
+    opt_record = None
+    if args.with_opt:
+        del engine, graphed
+        torch.cuda.empty_cache()
+        opt_record = run_native_opt(args, setup=(world, rank, local), emit=False)
     if rank == 0:
         print(json.dumps({
             "metric": "train samples/sec, BERT-large MLM", "value": value, "unit": "samples/s",
             "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
             "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak",
             "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "impl": "native",
-            "config": {"model": "bert-large", "layers": args.layers, "global_batch": global_batch,
-                       "seq_len": args.seq, "parallelism": parallelism,
-                       "ckpt_ratio": args.ckpt_ratio, "optimizer": "AdamW",
-                       "l2_policy": "per-step working set (weights+activations, >10 GB) "
-                                    "exceeds the 126 MB L2, nothing survives between steps"},
+            "config": make_config("bert-large", args.layers, global_batch, args.seq,
+                                  parallelism.replace("+sp", ""), args.ckpt_ratio, local_batch),
+            "notes": {"sequence_parallel": "+sp" in parallelism,
+                      "attention": "tcgen05 flash attention (this library)",
+                      "gemm": "tcgen05 GEMM (this library); fused GEMM + collective under TP"},
             "clocks": clocks, "e2e": e2e, "gpu_launches": int(launches),
-            "cuda_graph": graphed is not None,
+            "cuda_graph": args.cuda_graph_used,
+            "loss": {"first": losses[0] if losses else None, "last": losses[-1] if losses else None,
+                     "steps_trained_before_last": args.warmup * 2 + args.steps * 2},
+            "tp_check": tp_check, "opt": opt_record,
             "max_mem_mb": torch.cuda.max_memory_allocated() / 2**20,
         }), flush=True)
     if world > 1:
         import torch.distributed as dist
 
         dist.destroy_process_group()
+
+
+# --------------------------------------------------------------------------- #
+def opt_layout(world, choice):
+    """(tp, pp) of the OPT-2.7B run on ``world`` GPUs: tensor parallel over all of them, except
+    on 8 GPUs where the target configuration is 2 pipeline stages of 4-way tensor parallelism."""
+    if world == 8 and choice in ("auto", "pp2"):
+        return 4, 2
+    return world, 1
+
+
+def run_native_opt(args, setup=None, emit=True):
+    """OPT-2.7B-shaped causal LM through the same public API (zoo spec -> ``apply_schedule`` ->
+    ``build(target="native")`` -> ``engine.train_batch``), micro-batches of 4 x 1024 tokens."""
+    import argparse as _argparse
+
+    import torch
+
+    from slapo_b200.bench.train import build_engine
+    from slapo_b200.ops import native
+
+    world, rank, local = setup if setup is not None else dist_setup(args)
+    device = torch.device("cuda", local)
+    tp, pp = opt_layout(world, args.opt_layout)
+    micro = OPT["micro_batch"]
+    per_gpu = OPT["batch_per_gpu"] if args.model != "opt-2.7b" else args.batch_per_gpu
+    global_batch = per_gpu * world
+    n_micro = max(global_batch // micro, 1)
+    layers = OPT["layers"] if args.model != "opt-2.7b" else args.layers
+    seq = OPT["seq"] if args.model != "opt-2.7b" else args.seq
+    ckpt = 0.0 if args.model != "opt-2.7b" else args.ckpt_ratio
+    targs = _argparse.Namespace(
+        model="opt-2.7b", tp=tp, pp=pp, dp=1, batch_size=micro, micro_batches=n_micro,
+        seq_len=seq, seq_len_dec=0, layers=layers if layers != OPT["layers"] else 0, hidden=0,
+        heads=0, vocab=0, ckpt_ratio=ckpt, sequence_parallel=tp > 1, no_fuse=False,
+        attn_op="auto", dtype="bf16", lr=1e-4, seed=2013, no_fused_dp=False)
+    engine, spec, mesh, dp = build_engine(targs, world, device)
+    per_call = micro * (n_micro if pp > 1 else 1)
+    calls = 1 if pp > 1 else n_micro
+    batches = [spec.make_batch(per_call, seq, 0, seed=2013 + i, device=device) for i in range(calls)]
+
+    def step(_i):
+        loss = None
+        for inputs, labels in batches:
+            loss = engine.train_batch(*inputs, labels=labels)
+        return loss
+
+    for i in range(args.warmup):
+        step(i)
+    sampler = ClockSampler(local)
+    sampler.start()
+    launches0 = native.launch_count()
+    ms = timed_loop(step, args.steps, device, world)
+    launches = native.launch_count() - launches0
+    clocks = sampler.finish()
+    value = global_batch * args.steps / (ms / 1e3)
+    e2e, losses = None, []
+    if not args.no_e2e:
+        host = [[spec.make_batch(per_call, seq, 0, seed=4000 + 10 * j + i, device="cpu", pin=True)
+                 for i in range(calls)] for j in range(2)]
+        h2d = sum(t.numel() * t.element_size() for inputs, labels in host[0]
+                  for t in list(inputs) + [labels])
+
+        def e2e_step(i):
+            loss = None
+            for inputs, labels in host[i % 2]:
+                dev_in = [t.to(device, non_blocking=True) for t in inputs]
+                loss = engine.train_batch(*dev_in, labels=labels.to(device, non_blocking=True))
+            losses.append(float(loss.item()))
+            return losses[-1]
+
+        e2e_step(0)
+        ms_e = timed_loop(e2e_step, args.steps, device, world)
+        e2e = {"value": global_batch * args.steps / (ms_e / 1e3), "unit": "samples/s",
+               "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": 4 * calls,
+               "ms_per_step": ms_e / args.steps}
+    getattr(getattr(engine, "inner", engine), "check_device_status", lambda: None)()
+    # model FLOPs per sample (the reference's formula: 3 x (L (4 h s^2 + 24 s h^2) + 2 s h v))
+    h_, s_, v_ = OPT["hidden"], seq, OPT["vocab"]
+    flops = 3.0 * (layers * (4 * h_ * s_ * s_ + 24 * s_ * h_ * h_) + 2 * s_ * h_ * v_)
+    parallelism = (f"pp{pp}xtp{tp}" if pp > 1 else (f"tp{tp}" if tp > 1 else "single"))
+    record = {
+        "metric": "train samples/sec, OPT-2.7B causal LM", "value": value, "unit": "samples/s",
+        "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "impl": "native",
+        "config": make_config("opt-2.7b", layers, global_batch, seq, parallelism, ckpt, micro),
+        "notes": {"sequence_parallel": tp > 1, "micro_batches": n_micro,
+                  "attention": "tcgen05 flash attention, head dim 80 (this library)"},
+        "clocks": clocks, "e2e": e2e, "gpu_launches": int(launches), "cuda_graph": False,
+        "loss": {"first": losses[0] if losses else None, "last": losses[-1] if losses else None},
+        "model_tflops_per_gpu": flops * value / world / 1e12,
+        "max_mem_mb": torch.cuda.max_memory_allocated() / 2**20,
+    }
+    if emit:
+        if rank == 0:
+            print(json.dumps(record), flush=True)
+        if world > 1:
+            import torch.distributed as dist
+
+            dist.destroy_process_group()
+    return record
 
 
 # --------------------------------------------------------------------------- #
@@ -324,7 +536,12 @@ def run_reference(args):
     except Exception as err:  # pragma: no cover
         print(json.dumps({"impl": "reference", "unavailable": f"harness import failed: {err}"}))
         return
-    run(args, ref_root, MODEL, dist_setup, make_batch, timed_loop, ClockSampler)
+    if args.model == "opt-2.7b":
+        from baseline.reference_arm import run_opt
+
+        run_opt(args, ref_root, OPT, dist_setup, timed_loop, ClockSampler, make_config)
+        return
+    run(args, ref_root, MODEL, dist_setup, make_batch, timed_loop, ClockSampler, make_config)
 
 
 def maybe_self_launch(args):

@@ -27,12 +27,31 @@ def canonical_name(name: str) -> str:
     return _STAGE_PREFIX.sub("", name)
 
 
-def _coords(mesh):
-    if mesh is None:
-        rank = dist.get_rank() if dist.is_available() and dist.is_initialized() else 0
-        return {"pp": 0, "dp": 0, "tp": 0}, {"pp": 1, "dp": 1, "tp": 1}, rank
-    coord = mesh.get_coord()
-    return dict(coord), dict(mesh.dims), mesh.rank
+def _coords(mesh, model=None):
+    """This rank's (pp, dp, tp) coordinates, the mesh dimensions and the global rank.
+
+    Without a mesh a job of several ranks is read as ONE tensor-parallel group over the whole
+    world when the model carries sharded tensors (``create_schedule(model)`` with the default
+    group shards over all ranks), and as plain data parallelism when it does not - so that
+    the ranks never write the same shard file with different contents."""
+    if mesh is not None:
+        coord = mesh.get_coord()
+        return dict(coord), dict(mesh.dims), mesh.rank
+    if not (dist.is_available() and dist.is_initialized()) or dist.get_world_size() == 1:
+        return {"pp": 0, "dp": 0, "tp": 0}, {"pp": 1, "dp": 1, "tp": 1}, 0
+    rank, world = dist.get_rank(), dist.get_world_size()
+    sharded = model is not None and any(
+        tuple(getattr(t, "orig_shape", t.shape)) != tuple(t.shape)
+        for _, t in _unique_named_tensors(model))
+    # every rank must take the same branch: a rank whose own tensors happen to be whole still
+    # belongs to the tensor-parallel group of its peers
+    flag = torch.tensor([1 if sharded else 0])
+    if dist.get_backend() == "nccl":
+        flag = flag.cuda()
+    dist.all_reduce(flag, op=dist.ReduceOp.MAX)
+    if int(flag.item()):
+        return {"pp": 0, "dp": 0, "tp": rank}, {"pp": 1, "dp": 1, "tp": world}, rank
+    return {"pp": 0, "dp": rank, "tp": 0}, {"pp": 1, "dp": world, "tp": 1}, rank
 
 
 def _shard_axis(full_shape, local_shape):
@@ -88,7 +107,7 @@ def _barrier():
 def save_checkpoint(path, model, engine=None, mesh=None, step=None, extra=None):
     """Write this rank's part of a checkpoint into directory ``path``.
     Collective: every rank of the job calls it."""
-    coord, dims, rank = _coords(mesh)
+    coord, dims, rank = _coords(mesh, model)
     os.makedirs(path, exist_ok=True)
     tag = f"pp{coord['pp']}_tp{coord['tp']}"
     table, tensors = {}, {}
@@ -143,8 +162,13 @@ def _load_file(path, name):
     return torch.load(os.path.join(path, name), map_location="cpu", weights_only=False)
 
 
-def _merge_tp(pieces, axis):
-    return pieces[0] if axis is None else torch.cat(pieces, dim=axis)
+def _merge_tp(pieces, axis, name=None, full_shape=None):
+    out = pieces[0] if axis is None else torch.cat(pieces, dim=axis)
+    if full_shape is not None and tuple(out.shape) != tuple(full_shape):
+        raise ValueError(f"{name}: the shards put together have shape {tuple(out.shape)}, the "
+                         f"manifest records {tuple(full_shape)}: the checkpoint's shard files "
+                         "do not belong to one tensor-parallel layout")
+    return out
 
 
 def consolidate_checkpoint(path, with_optimizer=False, out_file=None):
@@ -156,7 +180,8 @@ def consolidate_checkpoint(path, with_optimizer=False, out_file=None):
     for pp in range(dims["pp"]):
         shards = [_load_file(path, f"model_pp{pp}_tp{tp}.pt") for tp in range(dims["tp"])]
         for name in shards[0]:
-            weights[name] = _merge_tp([s[name] for s in shards], table[name]["axis"])
+            weights[name] = _merge_tp([s[name] for s in shards], table[name]["axis"], name,
+                                      table[name]["orig_shape"])
         if with_optimizer and manifest["has_optimizer"]:
             opt = [_load_file(path, f"optim_pp{pp}_tp{tp}.pt") for tp in range(dims["tp"])]
             optim["step"] = opt[0]["step"]
@@ -188,7 +213,7 @@ def load_checkpoint(path, model, engine=None, mesh=None, strict=True, load_rng=T
     model's are consolidated along their recorded axis and re-split.
     Returns ``{"step", "extra"}``."""
     manifest = read_manifest(path)
-    coord, dims, rank = _coords(mesh)
+    coord, dims, rank = _coords(mesh, model)
     saved = manifest["mesh"]
     table = manifest["params"]
     same_layout = saved["tp"] == dims["tp"] and saved["pp"] == dims["pp"]

@@ -35,7 +35,7 @@ void launch_ln_bwd(const void* gy, const void* gz, const void* zin, const void* 
 }  // namespace slapo
 
 namespace slapo {
-// Flash attention on [B, S, H, D] tensors (D contiguous, D in {64, 128});
+// Flash attention on [B, S, H, D] tensors (D contiguous, a multiple of 8 up to 128);
 // *_strides = element strides of (B, S, H).  Return 0 on success.
 int launch_flash_fwd(const void* q, const void* k, const void* v, void* o, float* lse,
                      const float* kbias, const float* rel, int B, int H, int Sq, int Sk, int D,

@@ -60,7 +60,9 @@ constexpr float kLog2e = 1.4426950408889634f;
 
 struct FlashFwdParams {
   int B, H, Sq, Sk;
-  void* O;             // [B, Sq, H, D] contiguous
+  int Dr;              // the tensors' head dimension (<= the kernel's tile width D, % 8 == 0):
+                       // TMA zero-fills columns Dr .. D - 1 of every Q / K / V tile
+  void* O;             // [B, Sq, H, Dr] contiguous
   float* lse;          // [B, H, Sq] natural-log sum-exp of the scaled scores
   const float* kbias;  // [B, Sk] additive key bias or nullptr
   const float* rel;    // [H, Sq + Sk - 1] additive bias by (key - query) + Sq - 1, or nullptr
@@ -380,9 +382,10 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
     if (ok && row < p.Sq) {
       const float inv = l_run > 0.f ? 1.f / (l_run * (1.f - p.p_drop)) : 0.f;
       uint8_t* dst = static_cast<uint8_t*>(p.O) +
-                     ((static_cast<int64_t>(batch) * p.Sq + row) * p.H + head) * D * 2;
+                     ((static_cast<int64_t>(batch) * p.Sq + row) * p.H + head) * p.Dr * 2;
 #pragma unroll
       for (int g = 0; g < D / 8; ++g) {
+        if (g * 8 >= p.Dr) break;     // padded columns (zero) are not part of the output
         uint4 pk = make_uint4(pack_pair(o_acc[g * 8 + 0] * inv, o_acc[g * 8 + 1] * inv, p.out_bf16),
                               pack_pair(o_acc[g * 8 + 2] * inv, o_acc[g * 8 + 3] * inv, p.out_bf16),
                               pack_pair(o_acc[g * 8 + 4] * inv, o_acc[g * 8 + 5] * inv, p.out_bf16),
@@ -452,23 +455,26 @@ int launch_flash_fwd(const void* q, const void* k, const void* v, void* o, float
                      const int64_t* q_strides, const int64_t* k_strides, const int64_t* v_strides,
                      float scale, int causal, float p_drop, PhiloxArgs rng, bool bf16, int* status,
                      cudaStream_t stream) {
-  if (D != 64 && D != 128) return 1;
+  // any head dimension up to 128 that is a multiple of 8 (16-byte rows for TMA): the kernels
+  // work on 64- or 128-wide tiles whose columns beyond D are zero-filled by the tile loads
+  if (D < 8 || D > 128 || D % 8 != 0) return 1;
+  const int Dt = D <= 64 ? 64 : 128;
   CUtensorMap tq, tk, tv;
   if (!make_tmap_bshd(&tq, q, B, Sq, H, D, q_strides[0], q_strides[1], q_strides[2], 128, bf16) ||
       !make_tmap_bshd(&tk, k, B, Sk, H, D, k_strides[0], k_strides[1], k_strides[2], 128, bf16) ||
       !make_tmap_bshd(&tv, v, B, Sk, H, D, v_strides[0], v_strides[1], v_strides[2], 128, bf16))
     return 2;
   FlashFwdParams p;
-  p.B = B; p.H = H; p.Sq = Sq; p.Sk = Sk; p.O = o; p.lse = lse; p.kbias = kbias; p.rel = rel;
+  p.B = B; p.H = H; p.Sq = Sq; p.Sk = Sk; p.Dr = D; p.O = o; p.lse = lse; p.kbias = kbias; p.rel = rel;
   p.scale_log2 = scale * kLog2e; p.causal = causal; p.rng = rng;
   // the dropout probability is quantised to a multiple of 1/128 (see philox_keep16)
   p.thr7 = dropout_thr7(p_drop);
   p.p_drop = p.thr7 / 128.f;
   p.out_bf16 = bf16 ? 1 : 0; p.status = status;
   p.idesc_qk = tc::instr_desc_f16(128, 128, bf16 ? 1 : 0, false, false);
-  p.idesc_pv = tc::instr_desc_f16(128, D, bf16 ? 1 : 0, false, true);
+  p.idesc_pv = tc::instr_desc_f16(128, Dt, bf16 ? 1 : 0, false, true);
   const bool plain = kbias == nullptr && rel == nullptr && !causal && Sk % kBlockN == 0 && scale > 0.f;
-  if (D == 64)
+  if (Dt == 64)
     return plain ? launch_fwd_d<64, true>(tq, tk, tv, p, stream)
                  : launch_fwd_d<64, false>(tq, tk, tv, p, stream);
   return plain ? launch_fwd_d<128, true>(tq, tk, tv, p, stream)

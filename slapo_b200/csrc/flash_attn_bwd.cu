@@ -22,9 +22,10 @@ constexpr float kLog2eB = 1.4426950408889634f;
 
 struct FlashBwdParams {
   int B, H, Sq, Sk;
+  int Dr;               // the tensors' head dimension (<= the tile width D, % 8 == 0)
   const float* lse;     // [B, H, Sq]
   const float* delta;   // [B, H, Sq]
-  float* dq_accum;      // [B, Sq, H, D] fp32, zero-initialised
+  float* dq_accum;      // [B, Sq, H, Dr] fp32, zero-initialised
   void* dK;             // rows (b, key, head) spaced dkv_row_stride elements apart
   void* dV;
   int64_t dkv_row_stride;  // D for contiguous [B, Sk, H, D]; 3 D inside a packed QKV gradient
@@ -56,11 +57,13 @@ __device__ __forceinline__ void red_add_v4(float* addr, float a, float b, float 
                : "memory");
 }
 
-// delta[b, h, i] = sum_d dO[b, i, h, d] * O[b, i, h, d]   (both contiguous [B, Sq, H, D]).
-// D / 8 lanes share a row (16-byte loads, every lane busy), so a warp covers 256 / D rows.
+// delta[b, h, i] = sum_d dO[b, i, h, d] * O[b, i, h, d]   (both contiguous [B, Sq, H, Dr]).
+// D / 8 lanes share a row (16-byte loads), D = Dr rounded up to 64 or 128, so a warp covers
+// 256 / D rows; lanes beyond Dr / 8 contribute zero.
 template <typename T>
 __global__ void flash_bwd_delta_kernel(const T* __restrict__ dout, const T* __restrict__ out,
-                                       float* __restrict__ delta, int B, int H, int Sq, int D) {
+                                       float* __restrict__ delta, int B, int H, int Sq, int D,
+                                       int Dr) {
   const int lanes_per_row = D >> 3;              // 8 (D = 64) or 16 (D = 128)
   const int rows_per_warp = 32 / lanes_per_row;
   const int warps_per_block = blockDim.x >> 5;
@@ -69,11 +72,11 @@ __global__ void flash_bwd_delta_kernel(const T* __restrict__ dout, const T* __re
   const int64_t row = warp_id * rows_per_warp + lane / lanes_per_row;
   const int64_t rows = static_cast<int64_t>(B) * Sq * H;
   float s = 0.f;
-  if (row < rows) {
-    const int d = (lane % lanes_per_row) * 8;
+  const int d = (lane % lanes_per_row) * 8;
+  if (row < rows && d < Dr) {
     float a[8], b[8];
-    Vec8<T>::load(dout + row * D + d, a);
-    Vec8<T>::load(out + row * D + d, b);
+    Vec8<T>::load(dout + row * Dr + d, a);
+    Vec8<T>::load(out + row * Dr + d, b);
 #pragma unroll
     for (int k = 0; k < 8; ++k) s += a[k] * b[k];
   }
@@ -362,7 +365,7 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
       if (!tc::mbar_wait_warp(dq_full, it & 1, abort_flag)) { ok = false; break; }
       tc::fence_after_sync();
       float* dq_dst = p.dq_accum +
-                      ((static_cast<int64_t>(batch) * p.Sq + min(row, p.Sq - 1)) * p.H + head) * D;
+                      ((static_cast<int64_t>(batch) * p.Sq + min(row, p.Sq - 1)) * p.H + head) * p.Dr;
 #pragma unroll
       for (int cc = 0; cc < D / 64; ++cc) {
         const int c = half * (D / 64) + cc;   // this warp's share of the D columns
@@ -372,6 +375,7 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
         if (row_ok) {
 #pragma unroll
           for (int g = 0; g < 8; ++g)
+            if (c * 32 + g * 4 < p.Dr)
             red_add_v4(dq_dst + c * 32 + g * 4, __uint_as_float(r[g * 4]) * out_scale,
                        __uint_as_float(r[g * 4 + 1]) * out_scale,
                        __uint_as_float(r[g * 4 + 2]) * out_scale,
@@ -413,6 +417,7 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
           if (key < p.Sk) {
 #pragma unroll
             for (int g = 0; g < 4; ++g) {
+              if (c * 32 + g * 8 >= p.Dr) break;
               uint4 pk = make_uint4(
                   pack_pair_b(__uint_as_float(r[g * 8 + 0]) * f, __uint_as_float(r[g * 8 + 1]) * f, p.bf16),
                   pack_pair_b(__uint_as_float(r[g * 8 + 2]) * f, __uint_as_float(r[g * 8 + 3]) * f, p.bf16),
@@ -495,21 +500,22 @@ int launch_flash_bwd(const void* q, const void* k, const void* v, const void* o,
                      int B, int H, int Sq, int Sk, int D, const int64_t* q_strides, const int64_t* k_strides,
                      const int64_t* v_strides, float scale, int causal, float p_drop,
                      PhiloxArgs rng, bool bf16, int* status, cudaStream_t stream) {
-  if (D != 64 && D != 128) return 1;
+  if (D < 8 || D > 128 || D % 8 != 0) return 1;
+  const int Dt = D <= 64 ? 64 : 128;     // tile width; columns D .. Dt - 1 are zero-filled by TMA
   // pre-pass: delta (o and dout are contiguous [B, Sq, H, D])
   {
     const int64_t rows = static_cast<int64_t>(B) * Sq * H;
     const int wpb = 8;
-    const int64_t rows_per_block = static_cast<int64_t>(wpb) * (256 / D);
+    const int64_t rows_per_block = static_cast<int64_t>(wpb) * (256 / Dt);
     const unsigned blocks = static_cast<unsigned>((rows + rows_per_block - 1) / rows_per_block);
     count_launch();
     if (bf16)
       flash_bwd_delta_kernel<__nv_bfloat16><<<blocks, wpb * 32, 0, stream>>>(
           static_cast<const __nv_bfloat16*>(dout), static_cast<const __nv_bfloat16*>(o), delta, B, H,
-          Sq, D);
+          Sq, Dt, D);
     else
       flash_bwd_delta_kernel<__half><<<blocks, wpb * 32, 0, stream>>>(
-          static_cast<const __half*>(dout), static_cast<const __half*>(o), delta, B, H, Sq, D);
+          static_cast<const __half*>(dout), static_cast<const __half*>(o), delta, B, H, Sq, Dt, D);
   }
   CUtensorMap tq, tk, tv, tdo;
   const int64_t do_strides[3] = {static_cast<int64_t>(Sq) * H * D, static_cast<int64_t>(H) * D, D};
@@ -519,7 +525,7 @@ int launch_flash_bwd(const void* q, const void* k, const void* v, const void* o,
       !make_tmap_bshd(&tdo, dout, B, Sq, H, D, do_strides[0], do_strides[1], do_strides[2], 128, bf16))
     return 2;
   FlashBwdParams p;
-  p.B = B; p.H = H; p.Sq = Sq; p.Sk = Sk; p.lse = lse; p.delta = delta; p.dq_accum = dq_accum;
+  p.B = B; p.H = H; p.Sq = Sq; p.Sk = Sk; p.Dr = D; p.lse = lse; p.delta = delta; p.dq_accum = dq_accum;
   p.dK = dk; p.dV = dv; p.dkv_row_stride = dkv_row_stride; p.kbias = kbias; p.rel = rel; p.drel = drel; p.scale = scale;
   p.scale_log2 = scale * kLog2eB; p.causal = causal; p.rng = rng;
   p.thr7 = dropout_thr7(p_drop);   // same quantisation as the forward kernel
@@ -527,10 +533,10 @@ int launch_flash_bwd(const void* q, const void* k, const void* v, const void* o,
   p.bf16 = bf16 ? 1 : 0; p.status = status;
   const int f = bf16 ? 1 : 0;
   p.idesc_s = tc::instr_desc_f16(128, 128, f, false, false);   // S, dP
-  p.idesc_dvk = tc::instr_desc_f16(128, D, f, true, true);     // dV, dK
-  p.idesc_dq = tc::instr_desc_f16(128, D, f, false, true);     // dQ
+  p.idesc_dvk = tc::instr_desc_f16(128, Dt, f, true, true);     // dV, dK
+  p.idesc_dq = tc::instr_desc_f16(128, Dt, f, false, true);     // dQ
   const bool plain = kbias == nullptr && rel == nullptr && !causal && Sk % 128 == 0 && Sq % 128 == 0;
-  if (D == 64)
+  if (Dt == 64)
     return plain ? launch_bwd_d<64, true>(tq, tk, tv, tdo, p, stream)
                  : launch_bwd_d<64, false>(tq, tk, tv, tdo, p, stream);
   return plain ? launch_bwd_d<128, true>(tq, tk, tv, tdo, p, stream)

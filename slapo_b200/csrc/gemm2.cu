@@ -18,9 +18,8 @@
 //   tmem_empty[a]  in the leader; the eight epilogue warps of the pair arrive on it
 //
 // Split-K (few output tiles, long contraction - weight gradients): `splits` CTA pairs share
-// a tile, each adds its partial accumulator into an fp32 workspace with vector reductions;
-// the warp that arrives last on a 32-row strip converts the strip, writes the result and
-// leaves workspace and counter zeroed for the next launch.
+// a tile, each stores its partial accumulator into its own fp32 slice of a workspace; a
+// second, memory-bound kernel adds the slices, applies bias / activation and writes C.
 #include "common.cuh"
 #include "kernels.h"
 #include "tc05.cuh"
@@ -38,11 +37,13 @@ struct Gemm2Params {
   uint32_t idesc;
   int splits;         // CTA pairs per output tile (>= 1)
   int kb_per_split;
-  float* workspace;   // [M, N] fp32, zero between launches (splits > 1)
-  int* counters;      // per (tile, CTA of the pair, 32-row strip), zero between launches
+  float* workspace;   // [splits, M, N] fp32 scratch (splits > 1), any contents
   int* status;
+  int wide_store;     // rows of C are 32-byte aligned: the epilogue stores whole sectors
 };
 
+constexpr int kEpiWarps = 8;   // epilogue warps per CTA: two per quarter of the tensor-memory lanes,
+                               // each taking half of the tile's columns
 constexpr int PBM = 128;   // rows of A per CTA (the pair's tile has 256)
 constexpr int PBK = 64;
 
@@ -67,17 +68,35 @@ __device__ __forceinline__ float g2_bias(const void* bias, int col, int out_bf16
   return __half2float(static_cast<const __half*>(bias)[col]);
 }
 
-// bias + activation + pack + store of 32 consecutive columns of one row
+// bias + activation + pack + store of 32 consecutive columns of one row.  (Staging the tile in
+// shared memory for whole-line or TMA stores was measured and lost by a factor of two: the
+// epilogue's shared-memory traffic then competes with the operand fetch of the MMAs that run
+// under it.  Direct stores of whole 32-byte sectors are what is kept.)
+// the 32 bias values of columns [col0, col0 + 32): four 16-byte loads (the same for every
+// row, so they hit L1) instead of one 2-byte load per element; zeros without a bias
+__device__ __forceinline__ void g2_load_bias(const Gemm2Params& p, int col0, uint32_t (&b)[16]) {
+#pragma unroll
+  for (int q = 0; q < 4; ++q) {
+    uint4 t = make_uint4(0u, 0u, 0u, 0u);
+    if (p.bias != nullptr && col0 + q * 8 < p.N)
+      t = __ldg(reinterpret_cast<const uint4*>(static_cast<const uint8_t*>(p.bias) +
+                                               (col0 + q * 8) * 2));
+    b[4 * q] = t.x; b[4 * q + 1] = t.y; b[4 * q + 2] = t.z; b[4 * q + 3] = t.w;
+  }
+}
+
 __device__ __forceinline__ void g2_finish_store(const Gemm2Params& p, const float (&v)[32], int row,
-                                                int col0) {
+                                                int col0, const uint32_t (&bias_raw)[16]) {
   uint32_t packed[16], packed2[16];
 #pragma unroll
   for (int j = 0; j < 16; ++j) {
     float v0 = v[2 * j], v1 = v[2 * j + 1];
     if (p.bias != nullptr) {
-      const int cc = min(col0 + 2 * j, p.N - 2);
-      v0 += g2_bias(p.bias, cc, p.out_bf16);
-      v1 += g2_bias(p.bias, cc + 1, p.out_bf16);
+      float2 b2;
+      if (p.out_bf16) b2 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&bias_raw[j]));
+      else b2 = __half22float2(*reinterpret_cast<const __half2*>(&bias_raw[j]));
+      v0 += b2.x;
+      v1 += b2.y;
     }
     if (p.C2 != nullptr) packed2[j] = g2_pack2(v0, v1, p.out_bf16);
     if (p.act >= 0) {
@@ -88,11 +107,26 @@ __device__ __forceinline__ void g2_finish_store(const Gemm2Params& p, const floa
   }
   const int64_t off = (static_cast<int64_t>(row) * p.ldc + col0) * 2;
   uint8_t* dst = static_cast<uint8_t*>(p.C) + off;
+  if (p.wide_store) {
+    // whole 32-byte sectors per store (rows are 32-byte aligned: checked by the launcher)
 #pragma unroll
-  for (int q = 0; q < 4; ++q)
-    if (col0 + q * 8 < p.N)
-      *reinterpret_cast<uint4*>(dst + q * 16) =
-          make_uint4(packed[4 * q], packed[4 * q + 1], packed[4 * q + 2], packed[4 * q + 3]);
+    for (int q = 0; q < 2; ++q)
+      if (col0 + q * 16 + 8 < p.N)
+        asm volatile("st.global.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"l"(dst + q * 32),
+                     "r"(packed[8 * q]), "r"(packed[8 * q + 1]), "r"(packed[8 * q + 2]),
+                     "r"(packed[8 * q + 3]), "r"(packed[8 * q + 4]), "r"(packed[8 * q + 5]),
+                     "r"(packed[8 * q + 6]), "r"(packed[8 * q + 7])
+                     : "memory");
+      else if (col0 + q * 16 < p.N)
+        *reinterpret_cast<uint4*>(dst + q * 32) = make_uint4(
+            packed[8 * q], packed[8 * q + 1], packed[8 * q + 2], packed[8 * q + 3]);
+  } else {
+#pragma unroll
+    for (int q = 0; q < 4; ++q)
+      if (col0 + q * 8 < p.N)
+        *reinterpret_cast<uint4*>(dst + q * 16) =
+            make_uint4(packed[4 * q], packed[4 * q + 1], packed[4 * q + 2], packed[4 * q + 3]);
+  }
   if (p.C2 != nullptr) {
     uint8_t* dst2 = static_cast<uint8_t*>(p.C2) + off;
 #pragma unroll
@@ -104,7 +138,7 @@ __device__ __forceinline__ void g2_finish_store(const Gemm2Params& p, const floa
 }
 
 template <int BN, int STAGES, bool A_MN, bool B_MN>
-__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(192, 1)
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(64 + 32 * kEpiWarps, 1)
 gemm2_tc05_kernel(const __grid_constant__ CUtensorMap tmap_a,
                   const __grid_constant__ CUtensorMap tmap_b, const Gemm2Params p) {
   using S = Gemm2Smem<BN, STAGES>;
@@ -138,7 +172,7 @@ gemm2_tc05_kernel(const __grid_constant__ CUtensorMap tmap_a,
     }
     for (int a = 0; a < 2; ++a) {
       tc::mbar_init(&tmem_full[a], 1);
-      tc::mbar_init(&tmem_empty[a], 8);  // four epilogue warps in each CTA
+      tc::mbar_init(&tmem_empty[a], 2 * kEpiWarps);  // the epilogue warps of both CTAs
     }
     *abort_flag = 0;
     tc::fence_barrier_init();
@@ -236,6 +270,10 @@ gemm2_tc05_kernel(const __grid_constant__ CUtensorMap tmap_a,
   } else {
     // ------------------------------ epilogue (both CTAs) ----------------------------------
     const int quarter = warp & 3;  // TMEM lane quarter this warp may read
+    // with eight warps, warps w and w + 4 share a quarter and split the columns
+    const int col_part = (warp - 2) >> 2, col_parts = kEpiWarps / 4;
+    constexpr int kChunks = BN / 32;
+    const int c_begin = col_part * (kChunks / col_parts), c_end = c_begin + kChunks / col_parts;
     int iter = 0;
     bool ok = true;
     for (int u = pair; u < units && ok; u += npairs, ++iter) {
@@ -249,8 +287,17 @@ gemm2_tc05_kernel(const __grid_constant__ CUtensorMap tmap_a,
       const int row = m0 + quarter * 32 + lane;
       const uint32_t t_row = tmem_base + acc * BN + (static_cast<uint32_t>(quarter * 32) << 16);
       if (p.splits == 1) {
+        // One tensor-memory load at a time on purpose: reading ahead (two register sets, or
+        // 64 columns per load) measured 20 - 30 % slower on whole GEMMs - the epilogue's
+        // reads compete with the accumulator traffic of the MMAs that run under it.  Only the
+        // bias words are fetched one chunk ahead.
+        uint32_t bias_cur[16], bias_next[16];
+        g2_load_bias(p, n0 + c_begin * 32, bias_next);
 #pragma unroll 1
-        for (int c = 0; c < BN / 32; ++c) {
+        for (int c = c_begin; c < c_end; ++c) {
+#pragma unroll
+          for (int j = 0; j < 16; ++j) bias_cur[j] = bias_next[j];
+          if (c + 1 < c_end) g2_load_bias(p, n0 + (c + 1) * 32, bias_next);
           uint32_t r[32];
           tc::tmem_ld_x32(t_row + c * 32, r);
           tc::tmem_ld_wait();
@@ -259,63 +306,38 @@ gemm2_tc05_kernel(const __grid_constant__ CUtensorMap tmap_a,
             float v[32];
 #pragma unroll
             for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
-            g2_finish_store(p, v, row, col0);
+            g2_finish_store(p, v, row, col0, bias_cur);
           }
         }
         tc::fence_before_sync();
         __syncwarp();
         if (lane == 0) tc::mbar_arrive_cluster(tc::map_to_cta(tc::smem_u32(&tmem_empty[acc]), 0));
       } else {
-        // partial sums of this split go into the fp32 workspace
+        // this split's partial tile goes into ITS slice of the fp32 workspace with plain
+        // stores; splitk_reduce_kernel adds the slices up afterwards with the whole GPU.
+        // (fp32 atomics on rows 4 KB apart measured 0.8 TB/s, and a "last CTA to arrive sums
+        // the slices" epilogue 70 us of serial loads: both slower than not splitting)
+        const int sp = u - tile * p.splits;
+        const int64_t slice = static_cast<int64_t>(p.M) * p.N;
 #pragma unroll 1
-        for (int c = 0; c < BN / 32; ++c) {
+        for (int c = c_begin; c < c_end; ++c) {
           uint32_t r[32];
           tc::tmem_ld_x32(t_row + c * 32, r);
           tc::tmem_ld_wait();
           const int col0 = n0 + c * 32;
           if (row < p.M && col0 < p.N) {
-            float* w = p.workspace + static_cast<int64_t>(row) * p.N + col0;
+            float* w = p.workspace + sp * slice + static_cast<int64_t>(row) * p.N + col0;
 #pragma unroll
             for (int q = 0; q < 8; ++q)
               if (col0 + q * 4 < p.N)
-                asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(w + q * 4),
-                             "f"(__uint_as_float(r[4 * q])), "f"(__uint_as_float(r[4 * q + 1])),
-                             "f"(__uint_as_float(r[4 * q + 2])), "f"(__uint_as_float(r[4 * q + 3]))
-                             : "memory");
+                __stcg(reinterpret_cast<float4*>(w + q * 4),
+                       make_float4(__uint_as_float(r[4 * q]), __uint_as_float(r[4 * q + 1]),
+                                   __uint_as_float(r[4 * q + 2]), __uint_as_float(r[4 * q + 3])));
           }
         }
         tc::fence_before_sync();
         __syncwarp();
         if (lane == 0) tc::mbar_arrive_cluster(tc::map_to_cta(tc::smem_u32(&tmem_empty[acc]), 0));
-        // count this split on the strip; the last one finishes the strip
-        __threadfence();
-        __syncwarp();
-        int* counter = p.counters + (tile * 2 + static_cast<int>(cta)) * 4 + quarter;
-        int last = 0;
-        if (lane == 0) last = atomicAdd(counter, 1) + 1 == p.splits ? 1 : 0;
-        last = __shfl_sync(0xffffffffu, last, 0);
-        if (last) {
-          __threadfence();
-#pragma unroll 1
-          for (int c = 0; c < BN / 32; ++c) {
-            const int col0 = n0 + c * 32;
-            if (row < p.M && col0 < p.N) {
-              float* w = p.workspace + static_cast<int64_t>(row) * p.N + col0;
-              float v[32];
-#pragma unroll
-              for (int q = 0; q < 8; ++q) {
-                float4 t = make_float4(0.f, 0.f, 0.f, 0.f);
-                if (col0 + q * 4 < p.N) {
-                  t = __ldcg(reinterpret_cast<const float4*>(w + q * 4));
-                  __stcg(reinterpret_cast<float4*>(w + q * 4), make_float4(0.f, 0.f, 0.f, 0.f));
-                }
-                v[4 * q] = t.x; v[4 * q + 1] = t.y; v[4 * q + 2] = t.z; v[4 * q + 3] = t.w;
-              }
-              g2_finish_store(p, v, row, col0);
-            }
-          }
-          if (lane == 0) *counter = 0;
-        }
       }
     }
   }
@@ -329,6 +351,43 @@ gemm2_tc05_kernel(const __grid_constant__ CUtensorMap tmap_a,
   if (warp == 1) {
     tc::fence_after_sync();
     tc::tmem_dealloc_pair(tmem_base, kTmemCols);
+  }
+}
+
+// C = act(sum of the split-K slices + bias): one thread per 8 columns, 16-byte stores
+__global__ void __launch_bounds__(256) splitk_reduce_kernel(const Gemm2Params p) {
+  const int vpr = p.N / 8;
+  const int64_t n_vec = static_cast<int64_t>(p.M) * vpr;
+  const int64_t slice = static_cast<int64_t>(p.M) * p.N;
+  for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < n_vec;
+       i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    const int row = static_cast<int>(i / vpr);
+    const int col = static_cast<int>(i - static_cast<int64_t>(row) * vpr) * 8;
+    const float* w = p.workspace + static_cast<int64_t>(row) * p.N + col;
+    float v[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    for (int s2 = 0; s2 < p.splits; ++s2) {
+      const float4 t0 = __ldcs(reinterpret_cast<const float4*>(w + s2 * slice));
+      const float4 t1 = __ldcs(reinterpret_cast<const float4*>(w + s2 * slice + 4));
+      v[0] += t0.x; v[1] += t0.y; v[2] += t0.z; v[3] += t0.w;
+      v[4] += t1.x; v[5] += t1.y; v[6] += t1.z; v[7] += t1.w;
+    }
+    uint32_t packed[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      float v0 = v[2 * j], v1 = v[2 * j + 1];
+      if (p.bias != nullptr) {
+        v0 += g2_bias(p.bias, col + 2 * j, p.out_bf16);
+        v1 += g2_bias(p.bias, col + 2 * j + 1, p.out_bf16);
+      }
+      if (p.act >= 0) {
+        v0 = act_fwd(v0, p.act);
+        v1 = act_fwd(v1, p.act);
+      }
+      packed[j] = g2_pack2(v0, v1, p.out_bf16);
+    }
+    *reinterpret_cast<uint4*>(static_cast<uint8_t*>(p.C) +
+                              (static_cast<int64_t>(row) * p.ldc + col) * 2) =
+        make_uint4(packed[0], packed[1], packed[2], packed[3]);
   }
 }
 
@@ -352,7 +411,14 @@ static int launch_pair_variant(const CUtensorMap& ta, const CUtensorMap& tb, con
   const int pairs = sm_count() / 2;
   const int grid = 2 * (units < pairs ? units : pairs);
   count_launch();
-  kernel<<<grid, 192, S::kTotal, stream>>>(ta, tb, p);
+  kernel<<<grid, 64 + 32 * kEpiWarps, S::kTotal, stream>>>(ta, tb, p);
+  if (p.splits > 1) {
+    const int64_t n_vec = static_cast<int64_t>(p.M) * (p.N / 8);
+    const int64_t blocks = (n_vec + 255) / 256;
+    const int cap = sm_count() * 8;
+    count_launch();
+    splitk_reduce_kernel<<<static_cast<int>(blocks < cap ? blocks : cap), 256, 0, stream>>>(p);
+  }
   return cudaGetLastError() == cudaSuccess ? 0 : 4;
 }
 
@@ -364,19 +430,20 @@ int gemm2_splits(int M, int N, int K, int bn) {
   const int num_kb = (K + PBK - 1) / PBK;
   if (tiles * 2 > pairs || num_kb < 16) return 1;
   int s = pairs / tiles;
+  if (s > 16) s = 16;
   if (s > num_kb / 8) s = num_kb / 8;
   if (s < 1) s = 1;
   const int per = (num_kb + s - 1) / s;
   return (num_kb + per - 1) / per;     // no empty split
 }
 
-// C = act(A B^T + bias) on CTA pairs.  `workspace` / `counters`: zeroed scratch for split-K
-// (M * N floats, 8 ints per 256 x BN tile), may be null when gemm2_splits() == 1.
+// C = act(A B^T + bias) on CTA pairs.  `workspace`: scratch for split-K, gemm2_splits() * M * N
+// floats of any contents, or null (no split).
 // Returns 0 on success; >0 = refused on the host (shape / alignment / driver), 5 = too small
 // for a pair tile (use launch_gemm).
 int launch_gemm2(const void* A, const void* B, void* C, void* C2, const void* bias, int M, int N,
                  int K, int lda, int ldb, int ldc, bool a_mn, bool b_mn, bool bf16, int act,
-                 float* workspace, int* counters, int* status, cudaStream_t stream) {
+                 float* workspace, int* status, cudaStream_t stream) {
   if (M <= 0 || N <= 0 || K <= 0) return 0;
   if (N % 8 || K % 8 || lda % 8 || ldb % 8 || ldc % 8) return 1;
   if ((reinterpret_cast<uintptr_t>(A) | reinterpret_cast<uintptr_t>(B) |
@@ -395,11 +462,13 @@ int launch_gemm2(const void* A, const void* B, void* C, void* C2, const void* bi
   Gemm2Params p;
   p.M = M; p.N = N; p.K = K; p.C = C; p.C2 = C2; p.ldc = ldc; p.bias = bias; p.act = act;
   p.out_bf16 = bf16 ? 1 : 0; p.status = status;
+  p.wide_store = (ldc % 16 == 0 && (reinterpret_cast<uintptr_t>(C) & 31) == 0) ? 1 : 0;
   p.idesc = tc::instr_desc_f16(2 * PBM, BN, bf16 ? 1 : 0, a_mn, b_mn);
-  p.splits = (workspace != nullptr && counters != nullptr) ? gemm2_splits(M, N, K, BN) : 1;
+  p.splits = workspace != nullptr ? gemm2_splits(M, N, K, BN) : 1;
+
   const int num_kb = (K + PBK - 1) / PBK;
   p.kb_per_split = (num_kb + p.splits - 1) / p.splits;
-  p.workspace = workspace; p.counters = counters;
+  p.workspace = workspace;
 
 #define GEMM2_CASE(BN_, ST_)                                                                   \
   if (BN == BN_) {                                                                             \

@@ -28,17 +28,13 @@ int64_t device_status() {
   return v;
 }
 
-// fp32 scratch of the split-K pair GEMM, one per device, zero between launches (the kernel
-// leaves it zeroed); grown on demand.  All GEMMs of a device run on one stream at a time.
-struct SplitScratch { Tensor ws, counters; };
-SplitScratch& split_scratch(int device, int64_t floats, int64_t ints) {
-  static std::vector<SplitScratch> s(64);
-  SplitScratch& e = s[device];
-  if (!e.ws.defined() || e.ws.numel() < floats)
-    e.ws = at::zeros({floats}, at::TensorOptions().dtype(at::kFloat).device(at::kCUDA, device));
-  if (!e.counters.defined() || e.counters.numel() < ints)
-    e.counters = at::zeros({ints}, at::TensorOptions().dtype(at::kInt).device(at::kCUDA, device));
-  return e;
+// fp32 scratch of the split-K pair GEMM (one slice per split; contents do not matter), one per
+// device, grown on demand.  All GEMMs of a device run on one stream at a time.
+Tensor& split_scratch(int device, int64_t floats) {
+  static std::vector<Tensor> s(64);
+  if (!s[device].defined() || s[device].numel() < floats)
+    s[device] = at::empty({floats}, at::TensorOptions().dtype(at::kFloat).device(at::kCUDA, device));
+  return s[device];
 }
 
 // impl: 0 = pick (CTA-pair kernel when the problem has at least one pair tile, else the
@@ -90,17 +86,12 @@ Tensor gemm_out(const Tensor& a, const Tensor& b, const c10::optional<Tensor>& b
   int rc = 5;
   if (impl != 1) {
     float* ws = nullptr;
-    int* counters = nullptr;
-    if (split_k && slapo::gemm2_splits(M, N, K, N > 128 ? 256 : 128) > 1) {
-      const int64_t tiles = static_cast<int64_t>((M + 255) / 256) * ((N + 127) / 128);
-      SplitScratch& sc = split_scratch(dev, static_cast<int64_t>(M) * N, tiles * 8);
-      ws = sc.ws.data_ptr<float>();
-      counters = sc.counters.data_ptr<int>();
-    }
+    const int splits = split_k ? slapo::gemm2_splits(M, N, K, N > 128 ? 256 : 128) : 1;
+    if (splits > 1) ws = split_scratch(dev, static_cast<int64_t>(splits) * M * N).data_ptr<float>();
     rc = slapo::launch_gemm2(a.data_ptr(), b.data_ptr(), c.data_ptr(), c2, bias_ptr, M, N, K,
                              static_cast<int>(a.stride(0)), static_cast<int>(b.stride(0)),
                              static_cast<int>(c.stride(0)), a_mn, b_mn, bf16,
-                             static_cast<int>(act), ws, counters,
+                             static_cast<int>(act), ws,
                              status_word(dev).data_ptr<int>(), stream);
     TORCH_CHECK(impl != 2 || rc == 0, "gemm: the CTA-pair kernel refused the launch (code ", rc, ")");
   }
@@ -129,6 +120,10 @@ void register_gemm_ops(torch::Library& m) {
   m.def("gemm(Tensor a, Tensor b, Tensor? bias, int act, bool a_mn, bool b_mn) -> Tensor", &gemm);
   m.def("gemm_out(Tensor a, Tensor b, Tensor? bias, int act, bool a_mn, bool b_mn, Tensor? out, "
         "Tensor? pre_act, int impl, bool split_k) -> Tensor", &gemm_out);
+  m.def("gemm2_splits(int M, int N, int K) -> int", [](int64_t M, int64_t N, int64_t K) -> int64_t {
+    return slapo::gemm2_splits(static_cast<int>(M), static_cast<int>(N), static_cast<int>(K),
+                               N > 128 ? 256 : 128);
+  });
   m.def("device_status() -> int", &device_status);
   m.def("device_status_tensor() -> Tensor", &device_status_tensor);
 }

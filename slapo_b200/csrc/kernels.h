@@ -40,12 +40,12 @@ int launch_gemm(const void* A, const void* B, void* C, const void* bias, int M, 
 
 // The same product on CTA pairs (gemm2.cu): 256 x 256 tiles shared by two SMs, optional second
 // output `C2` (the value before the activation), optional split-K through `workspace`
-// (M * N floats) and `counters` (8 ints per tile), both zero between launches.  Returns 5 when
+// (gemm2_splits() * M * N floats of scratch).  Returns 5 when
 // the problem is smaller than one pair tile (use launch_gemm).
 int gemm2_splits(int M, int N, int K, int bn);
 int launch_gemm2(const void* A, const void* B, void* C, void* C2, const void* bias, int M, int N,
                  int K, int lda, int ldb, int ldc, bool a_mn, bool b_mn, bool bf16, int act,
-                 float* workspace, int* counters, int* status, cudaStream_t stream);
+                 float* workspace, int* status, cudaStream_t stream);
 
 // Cross entropy in two steps (per-row statistics, then gradient); see loss.cu.
 void launch_ce_stats(const void* logits, const int64_t* labels, float* stats, int rows, int cols,

@@ -76,10 +76,18 @@ extern "C" int slapo_bias_act_bwd_noalloc(const void* dy, const void* x, const v
       return fail(SLAPO_NOALLOC_E_CUDA, err, err_len,
                   "looking up the scratch array failed with CUDA error %ld", static_cast<long>(rc));
   }
+  // only an error that THIS launch raised is reported: an error that was already pending on the
+  // thread (someone else's failed call) is neither consumed nor blamed on this one
+  const cudaError_t before = cudaPeekAtLastError();
   slapo::launch_bias_act_bwd(dy, x, bias, dx, dbias, scratch, rows, cols, act, dtype, stream);
-  const cudaError_t rc = cudaPeekAtLastError();
-  if (rc != cudaSuccess)
+  const cudaError_t after = cudaPeekAtLastError();
+  if (after != cudaSuccess && after != before)
     return fail(SLAPO_NOALLOC_E_CUDA, err, err_len, "kernel launch failed with CUDA error %ld",
-                static_cast<long>(rc));
+                static_cast<long>(after));
   return SLAPO_NOALLOC_OK;
+}
+
+extern "C" long slapo_bias_act_bwd_noalloc_scratch_floats(int rows, int cols) {
+  if (rows <= 0 || cols <= 0) return 0;
+  return static_cast<long>(slapo::colsum_chunks(rows, cols)) * cols;
 }

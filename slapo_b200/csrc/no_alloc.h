@@ -17,6 +17,14 @@
 // = 1.25 MiB) must fit; anything larger is refused with
 // SLAPO_NOALLOC_E_TOO_LARGE and nothing is launched.
 //
+// How much scratch a shape needs depends on the GPU: the column sums are split into
+// about 8 chunks of rows per SM (never more than rows / 8), so the need is
+// min(ceil(8 * SMs / ceil(cols / 256)), ceil(rows / 8)) * cols floats.  On a 148-SM B200
+// that is at most 1184 * 256 + cols floats, which fits for every cols up to the
+// maximum; a part with 160 SMs or more would refuse some tall shapes that fit here.
+// slapo_bias_act_bwd_noalloc_scratch_floats(rows, cols) returns the figure for the
+// current device, so a caller can check a shape without launching anything.
+//
 // Set-up: the first call on each device looks up the device address of the
 // scratch array (once per device, with that device current) and caches it.
 // That look-up is not a stream operation, so make the first call on a device
@@ -55,6 +63,11 @@ extern "C" {
 int slapo_bias_act_bwd_noalloc(const void* dy, const void* x, const void* bias, void* dx,
                                void* dbias, int rows, int cols, int act, int dtype,
                                cudaStream_t stream, char* err, int err_len);
+
+// Scratch floats that (rows, cols) needs on the current device (148 SMs are assumed when no
+// device can be queried); the call above refuses shapes for which this exceeds
+// SLAPO_NOALLOC_SCRATCH_FLOATS.
+long slapo_bias_act_bwd_noalloc_scratch_floats(int rows, int cols);
 
 #ifdef __cplusplus
 }

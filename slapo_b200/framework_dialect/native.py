@@ -18,6 +18,15 @@ def init_native_engine(sch, model, config=None, mesh=None, loss_fn=None, dp_grou
 
     fused = kwargs.pop("fused_tp", True)
     ctx = None
+    import torch as _torch
+
+    if _torch.cuda.is_available():
+        # every remaining plain nn.Linear runs its three GEMMs on this library's kernels
+        from ..ops.linear import adopt_native_linears
+
+        adopt_native_linears(sch.mod)
+        if isinstance(model, _torch.nn.Module):
+            adopt_native_linears(model)
     if fused and sch.world_size > 1:
         import torch
 

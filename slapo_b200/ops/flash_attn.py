@@ -15,13 +15,16 @@ import torch
 
 from . import native
 
-_HEAD_DIMS = (64, 128)
+def head_dim_supported(d: int) -> bool:
+    """Head dimensions the kernels take: multiples of 8 up to 128 (OPT-2.7B's 80 included);
+    tiles are 64 or 128 wide and TMA zero-fills the columns beyond ``d``."""
+    return 8 <= d <= 128 and d % 8 == 0
 
 
 def native_supported(q, k, v) -> bool:
     if not (q.is_cuda and q.dtype in (torch.bfloat16, torch.float16)):
         return False
-    if q.dim() != 4 or q.shape[-1] not in _HEAD_DIMS:
+    if q.dim() != 4 or not head_dim_supported(q.shape[-1]):
         return False
     for t in (q, k, v):
         if t.stride(-1) != 1 or any(s % 8 for s in t.stride()[:3]) or t.data_ptr() % 16:
@@ -109,7 +112,7 @@ def flash_attention_qkvpacked(qkv, key_bias=None, causal=False, scale=None, p=0.
 def packed_supported(qkv) -> bool:
     return (torch.is_tensor(qkv) and qkv.is_cuda and qkv.dim() == 5 and qkv.shape[3] == 3
             and qkv.is_contiguous() and qkv.dtype in (torch.bfloat16, torch.float16)
-            and qkv.shape[-1] in _HEAD_DIMS and native.available())
+            and head_dim_supported(qkv.shape[-1]) and native.available())
 
 
 def effective_dropout_p(p: float) -> float:

@@ -85,6 +85,87 @@ def bias_gelu(x, bias, approximate: str = "none"):
 
 
 # ---------------------------------------------------------------------- #
+# linear layers on the tcgen05 GEMM
+def gemm_supported(x, weight) -> bool:
+    """CUDA 16-bit operands whose dimensions TMA can address (multiples of 8 elements)."""
+    if not (torch.is_tensor(x) and x.is_cuda and x.dtype in (torch.bfloat16, torch.float16)):
+        return False
+    if weight.dtype != x.dtype or weight.dim() != 2 or weight.stride(1) != 1:
+        return False
+    if os.environ.get("SLAPO_B200_LIBRARY_GEMM", "0") == "1":   # A/B switch for measurements
+        return False
+    return (x.shape[-1] % 8 == 0 and weight.shape[0] % 8 == 0 and weight.stride(0) % 8 == 0
+            and x.numel() > 0 and _native_ok(x))
+
+
+def _rows(t):
+    """``t`` as a 2-D matrix with contiguous rows whose stride TMA accepts."""
+    t2 = t.reshape(-1, t.shape[-1])
+    if t2.stride(1) != 1 or t2.stride(0) % 8 or t2.data_ptr() % 16:
+        t2 = t2.contiguous()
+    return t2
+
+
+def gemm(a, b, bias=None, act=-1, a_mn=False, b_mn=False, out=None, pre_act=None, split_k=False):
+    """``act(A B^T + bias)`` on this library's tcgen05 kernels (CTA pairs where the problem
+    has a pair tile).  ``a_mn`` / ``b_mn``: the operand is stored ``[K, M]`` / ``[K, N]``."""
+    return native.ops().gemm_out(a, b, bias, act, a_mn, b_mn, out, pre_act, 0, split_k)
+
+
+_RELU = 2
+
+
+class _LinearFn(torch.autograd.Function):
+    """``y = x W^T + b`` (optionally ``relu`` of it): three GEMMs of this library, none of them
+    transposing an operand in memory.  The bias rides in the forward GEMM's epilogue and so
+    does ReLU, whose derivative the backward reads off the output (``y > 0``).  GeLU is NOT
+    fused: the four epilogue warps of a tcgen05 GEMM have a fraction of the SM's FP32 issue
+    rate, and an erf per element made the GEMM 2.5 x slower than running
+    :func:`bias_act` over the output afterwards."""
+
+    @staticmethod
+    def forward(ctx, x, weight, bias, act):
+        x2 = _rows(x)
+        y = gemm(x2, weight, bias, act)
+        ctx.act, ctx.has_bias = act, bias is not None
+        ctx.save_for_backward(x2, weight, y if act >= 0 else None)
+        ctx.x_shape = x.shape
+        return y.view(tuple(x.shape[:-1]) + (weight.shape[0],))
+
+    @staticmethod
+    def backward(ctx, dy):
+        x2, weight, y = ctx.saved_tensors
+        dy2 = _rows(dy)
+        dbias = None
+        if ctx.act >= 0:
+            # relu'(z) = (y > 0): the saved output stands in for the pre-activation
+            dy2, dbias = native.ops().act_bwd_colsum(dy2.contiguous(), y, ctx.act)
+        elif ctx.has_bias and ctx.needs_input_grad[2]:
+            dbias = native.ops().colsum(dy2)
+        dx = dw = None
+        if ctx.needs_input_grad[0]:
+            # dX = dZ W:  B = W [N, K] read N-major (its rows are the contraction)
+            dx = gemm(dy2, weight, b_mn=True).view(ctx.x_shape)
+        if ctx.needs_input_grad[1]:
+            # dW = dZ^T X:  A = dZ [T, N] read M-major, B = X [T, K] read N-major; few tiles and a
+            # long contraction, hence split-K
+            dw = gemm(dy2, x2, a_mn=True, b_mn=True, split_k=True)
+        return dx, dw, (dbias if ctx.has_bias else None), None
+
+
+def linear(x, weight, bias=None, act=None):
+    """``act(x @ weight.T + bias)``; ``act`` in None / "gelu" / "gelu_new" / "relu".  CUDA
+    16-bit tensors run this library's GEMM (bias and activation in its epilogue), anything
+    else PyTorch."""
+    if gemm_supported(x, weight):
+        if act is None or act == "relu":
+            return _LinearFn.apply(x, weight, bias, -1 if act is None else _RELU)
+        return bias_act(_LinearFn.apply(x, weight, None, -1), bias, act)
+    out = F.linear(x, weight, bias)
+    return out if act is None else _act_ref(out, act)
+
+
+# ---------------------------------------------------------------------- #
 # dropout family
 def effective_dropout_p(p: float) -> float:
     """Dropout probability the CUDA kernels actually apply.  They draw 7-bit
@@ -260,6 +341,35 @@ def attention_reference(q, k, v, key_padding_bias=None, causal=False, scale=None
     return out.transpose(1, 2).to(q.dtype)
 
 
+_FALLBACK_SEEN = set()
+
+
+def _warn_attention_fallback(q, k):
+    """One WARNING per (dtype, head dim, layout problem): a CUDA attention call that the
+    tcgen05 kernels do not take runs the fp32 reference with a materialised [B, H, Sq, Sk]
+    score matrix - correct, but many times slower and memory-hungry."""
+    why = []
+    if q.dtype not in (torch.bfloat16, torch.float16):
+        why.append(f"dtype {q.dtype} (kernels: bf16 / fp16)")
+    d = q.shape[-1]
+    if not (8 <= d <= 128 and d % 8 == 0):
+        why.append(f"head dim {d} (kernels: multiples of 8 up to 128)")
+    if q.dim() != 4:
+        why.append(f"{q.dim()}-D input (kernels: [B, S, H, D])")
+    if not why:
+        why.append("strides or alignment (D contiguous, other strides multiples of 8 "
+                   "elements, 16-byte aligned data)")
+    key = (q.dtype, d, tuple(why))
+    if key in _FALLBACK_SEEN:
+        return
+    _FALLBACK_SEEN.add(key)
+    import logging
+
+    logging.getLogger("slapo_b200.ops").warning(
+        "flash_attention falls back to the PyTorch reference for q %s / k %s: %s",
+        tuple(q.shape), tuple(k.shape), "; ".join(why))
+
+
 def flash_attention(q, k, v, key_padding_bias=None, causal=False, scale=None, dropout_p=0.0,
                     training=True, rel_bias_table=None, rel_bidirectional=True,
                     rel_max_distance=128):
@@ -272,5 +382,7 @@ def flash_attention(q, k, v, key_padding_bias=None, causal=False, scale=None, dr
         return flash_attention_native(q, k, v, key_padding_bias, causal, scale,
                                       dropout_p if training else 0.0, rel_bias_table,
                                       rel_bidirectional, rel_max_distance)
+    if torch.is_tensor(q) and q.is_cuda:
+        _warn_attention_fallback(q, k)
     return attention_reference(q, k, v, key_padding_bias, causal, scale, dropout_p, training,
                                rel_bias_table, rel_bidirectional, rel_max_distance)

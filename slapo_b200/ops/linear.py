@@ -22,9 +22,33 @@ from torch import nn
 from . import functional as NF
 
 
+class Linear(nn.Linear):
+    """``nn.Linear`` whose products run on this library's tcgen05 GEMM (forward, input
+    gradient and weight gradient) when the tensors are CUDA 16-bit; same parameters, same
+    state dict, same behaviour elsewhere."""
+
+    def forward(self, x):
+        return NF.linear(x, self.weight, self.bias)
+
+
+def adopt_native_linears(model: nn.Module) -> int:
+    """Give every plain ``nn.Linear`` below ``model`` the forward of :class:`Linear`.
+
+    The module objects stay what they are - parameters, hooks, schedule-tree references and
+    ``isinstance(m, nn.Linear)`` all survive - only their class changes.  The native dialect
+    calls this when it builds an engine on CUDA, so that no contraction of the step is left to
+    a library GEMM.  Returns the number of modules changed."""
+    n = 0
+    for mod in model.modules():
+        if type(mod) is nn.Linear:
+            mod.__class__ = Linear
+            n += 1
+    return n
+
+
 class LinearWithSeparateBias(nn.Linear):
     def forward(self, x):
-        out = F.linear(x, self.weight, None)
+        out = NF.linear(x, self.weight, None)
         return out + self.bias if self.bias is not None else out
 
 
@@ -66,9 +90,9 @@ class LinearWithSyncFunc(nn.Linear):
                     return out if epilogue_bias is None else out + epilogue_bias
                 return fused_tp.col_linear_ar_bwd(x, self.weight, epilogue_bias, self.fused_bwd[1])
             return self._unfused_fallback(x, epilogue_bias)
-        out = F.linear(x, self.weight, None)
-        if self.sync_fn is not None:
-            out = self.sync_fn(out)
+        if self.sync_fn is None:
+            return NF.linear(x, self.weight, epilogue_bias)     # bias in the GEMM epilogue
+        out = self.sync_fn(NF.linear(x, self.weight, None))
         return out if epilogue_bias is None else out + epilogue_bias
 
     def _unfused_fallback(self, x, epilogue_bias):
@@ -162,6 +186,10 @@ class LinearWithAct(LinearWithSyncFunc):
         self.act_fn = act_fn
 
     def forward(self, x):
+        if (self.sync_fn is None and not (self.fused_pre or self.fused_post or self.fused_bwd)
+                and NF.gemm_supported(x, self.weight)):
+            # local product: bias and activation ride in the GEMM's epilogue
+            return NF.linear(x, self.weight, self.bias, self.act_fn)
         return NF.bias_act(self.matmul_sync(x), self.bias, self.act_fn)
 
     def extra_repr(self):

@@ -30,6 +30,7 @@ from __future__ import annotations
 
 import torch
 
+from ..ops import functional as NF
 from ..ops import native
 
 GATHER_NONE, GATHER_A_ROWS, GATHER_A_K, GATHER_B_K, GATHER_A_ROWS_STAGED = 0, 1, 2, 3, 4
@@ -52,6 +53,29 @@ def _check_status():
     if code:
         raise RuntimeError(f"fused kernel reported error code {code}: a bounded wait on a peer "
                            "ran out (a rank is missing or stuck)")
+
+
+def _wgrad(dy, x):
+    """``dW = dY^T X`` on this library's split-K GEMM (both operands read as stored: ``dY``
+    M-major, ``X`` N-major); tensors the kernel cannot address go to PyTorch."""
+    if (dy.shape[1] % 8 == 0 and x.shape[1] % 8 == 0 and dy.stride(1) == 1 and x.stride(1) == 1
+            and dy.stride(0) % 8 == 0 and x.stride(0) % 8 == 0):
+        return NF.gemm(dy, x, a_mn=True, b_mn=True, split_k=True)
+    return dy.t() @ x
+
+
+def _dgrad(dy, w):
+    """``dX = dY W`` with ``W`` ``[N, K]`` read N-major."""
+    if dy.shape[1] % 8 == 0 and w.shape[1] % 8 == 0 and w.stride(1) == 1 and w.stride(0) % 8 == 0:
+        return NF.gemm(dy, w, b_mn=True)
+    return dy @ w
+
+
+def _dbias(dy):
+    """Column sums of ``dY`` (one streaming kernel, fp32 accumulation)."""
+    if dy.shape[1] % 8 == 0 and dy.stride(1) == 1 and dy.stride(0) % 8 == 0:
+        return native.ops().colsum(dy)
+    return dy.float().sum(0).to(dy.dtype)
 
 
 def comm_gemm(ctx, *, a_ptrs, b_ptrs, M, N, K, lda, ldb, a_mn, b_mn, dtype, gather=GATHER_NONE,
@@ -212,8 +236,8 @@ class _AGLinear(torch.autograd.Function):
         # contraction - gather the tokens with the pull kernel and let the
         # library's split-K GEMM do the rest
         full_x = x_saved if ctx.gathered else peer_gather(sctx, x_saved.contiguous(), "ag_in_bwd")
-        dw = dy.t() @ full_x
-        db = dy.float().sum(0).to(dy.dtype) if ctx.has_bias else None
+        dw = _wgrad(dy, full_x)
+        db = _dbias(dy) if ctx.has_bias else None
         return dx, dw, db, None
 
 
@@ -239,10 +263,10 @@ class _RSLinear(torch.autograd.Function):
         # kernel above has already gathered dY into local memory
         if full_dy is None:
             full_dy = peer_gather(sctx, dy_shard, "ag_dy_bwd2")
-        dw = full_dy.t() @ x
+        dw = _wgrad(full_dy, x)
         # the bias is added on the owner's rows only: its gradient is partial
         # (tagged replicated_param -> summed over the group by the engine)
-        db = dy_shard.float().sum(0).to(dy_shard.dtype) if ctx.has_bias else None
+        db = _dbias(dy_shard) if ctx.has_bias else None
         return dx, dw, db, None
 
 
@@ -256,9 +280,10 @@ class _ARLinear(torch.autograd.Function):
     @staticmethod
     def backward(ctx, dy):
         x, w = ctx.saved_tensors
-        dx = dy @ w
-        dw = dy.t() @ x
-        db = dy.float().sum(0).to(dy.dtype) if ctx.has_bias else None
+        dy = dy.contiguous()
+        dx = _dgrad(dy, w)
+        dw = _wgrad(dy, x)
+        db = _dbias(dy) if ctx.has_bias else None
         return dx, dw, db, None
 
 
@@ -271,6 +296,8 @@ class _ColLinearARBwd(torch.autograd.Function):
         ctx.sctx = sctx
         ctx.save_for_backward(x, w)
         ctx.has_bias = bias is not None
+        if NF.gemm_supported(x, w):
+            return NF.gemm(NF._rows(x), w, bias)
         return torch.nn.functional.linear(x, w, bias)
 
     @staticmethod
@@ -284,10 +311,10 @@ class _ColLinearARBwd(torch.autograd.Function):
         else:  # row blocks do not split evenly over the group
             import torch.distributed as dist
 
-            dx = dy @ w
+            dx = _dgrad(dy, w)
             dist.all_reduce(dx, group=ctx.sctx.group)
-        dw = dy.t() @ x
-        db = dy.float().sum(0).to(dy.dtype) if ctx.has_bias else None
+        dw = _wgrad(dy, x)
+        db = _dbias(dy) if ctx.has_bias else None
         return dx, dw, db, None
 
 

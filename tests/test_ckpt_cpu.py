@@ -164,3 +164,34 @@ def test_strict_mismatch_raises():
         with pytest.raises(KeyError):
             ckpt.load_checkpoint(tmp, nn.Linear(3, 3))
         ckpt.load_checkpoint(tmp, nn.Linear(3, 3), strict=False)
+
+
+def _tp_no_mesh_worker(rank, world, tmp):
+    # sharded over the WORLD group, saved and loaded without a mesh: every rank must write its
+    # own shard file and the manifest must say tp = world
+    model = _tp_model(rank)
+    ckpt.save_checkpoint(tmp, model)
+    model2 = _tp_model(rank)
+    with torch.no_grad():
+        for p in model2.parameters():
+            p.zero_()
+    ckpt.load_checkpoint(tmp, model2)
+    for (n, a), (_, b) in zip(model.named_parameters(), model2.named_parameters()):
+        torch.testing.assert_close(a, b, msg=lambda s: f"{n}: {s}")
+
+
+def test_sharded_model_without_a_mesh_is_saved_as_one_tp_group():
+    with tempfile.TemporaryDirectory() as tmp:
+        run_distributed(_tp_no_mesh_worker, 2, tmp)
+        man = ckpt.read_manifest(tmp)
+        assert man["mesh"] == {"pp": 1, "dp": 1, "tp": 2}
+        assert os.path.exists(os.path.join(tmp, "model_pp0_tp1.pt"))
+        full = ckpt.consolidate_checkpoint(tmp)
+        assert tuple(full["fc1.weight"].shape) == (64, 16)
+        assert tuple(full["fc2.weight"].shape) == (16, 64)
+        # shard files that do not add up to the recorded shape are refused
+        shard = torch.load(os.path.join(tmp, "model_pp0_tp1.pt"), weights_only=False)
+        shard["fc1.weight"] = shard["fc1.weight"][:8]
+        torch.save(shard, os.path.join(tmp, "model_pp0_tp1.pt"))
+        with pytest.raises(ValueError, match="do not belong to one tensor-parallel layout"):
+            ckpt.consolidate_checkpoint(tmp)

@@ -117,3 +117,56 @@ def test_flash_attention_dropout_replay(p):
              lambda q, k, v: NF.flash_attention(q, k, v, dropout_p=p, training=True),
              lambda q, k, v: NF.attention_reference(q, k, v, dropout_p=effective_dropout_p(p),
                                                     dropout_mask=mask.float()))
+
+
+@pytest.mark.parametrize("causal", [False, True])
+@pytest.mark.parametrize("shape,fused", [((2, 256, 4, 80), False), ((2, 200, 3, 80), False),
+                                         ((1, 1024, 2, 80), True), ((2, 384, 2, 96), True),
+                                         ((2, 130, 2, 40), False), ((1, 256, 2, 120), False)])
+def test_flash_attention_padded_head_dims(shape, fused, causal):
+    """Head dimensions between the tile widths (OPT-2.7B: 80): the tile loads zero-fill the
+    columns beyond D, outputs and gradients have exactly D columns; ragged sequence lengths,
+    separate and packed q/k/v layouts."""
+    b, s, h, d = shape
+    q, k, v = _mk(b, s, h, d, torch.bfloat16, fused_layout=fused)
+    from slapo_b200.ops.flash_attn import native_supported
+    assert native_supported(q, k, v)
+    _compare(q, k, v,
+             lambda q, k, v: NF.flash_attention(q, k, v, causal=causal),
+             lambda q, k, v: NF.attention_reference(q, k, v, causal=causal))
+
+
+def test_flash_attention_head_dim_80_packed_with_dropout():
+    from slapo_b200.ops.flash_attn import flash_attention_qkvpacked, packed_supported
+
+    b, s, h, d, p = 2, 256, 4, 80, 0.1
+    qkv = torch.randn(b, s, h, 3, d, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    assert packed_supported(qkv)
+    torch.cuda.manual_seed(11)
+    mask = dropout_keep_mask(b, h, s, s, p)
+    out = flash_attention_qkvpacked(qkv, causal=True, p=p)
+    g = torch.randn_like(out)
+    out.backward(g)
+    ref_in = qkv.detach().float().requires_grad_(True)
+    ref = NF.attention_reference(ref_in[..., 0, :], ref_in[..., 1, :], ref_in[..., 2, :],
+                                 causal=True, dropout_p=effective_dropout_p(p),
+                                 dropout_mask=mask.float())
+    ref.backward(g.float())
+    for name, a, b_ in (("out", out, ref), ("dqkv", qkv.grad, ref_in.grad)):
+        scale = b_.abs().max().clamp(min=1e-3)
+        err = ((a.float() - b_).abs().max() / scale).item()
+        assert err < 3e-2, f"{name}: relative max error {err:.4f}"
+    assert native.ops().device_status() == 0
+
+
+def test_attention_fallback_is_announced(caplog):
+    """Shapes the kernels do not take (head dim not a multiple of 8) run the PyTorch
+    reference - and say so once, instead of silently materialising the score matrix."""
+    import logging
+
+    q = torch.randn(1, 64, 2, 36, device="cuda", dtype=torch.bfloat16)
+    with caplog.at_level(logging.WARNING):
+        NF.flash_attention(q, q, q)
+        NF.flash_attention(q, q, q)
+    hits = [r for r in caplog.records if "falls back" in r.getMessage()]
+    assert len(hits) == 1 and "36" in hits[0].getMessage()

@@ -60,6 +60,9 @@ def test_noalloc_matches_torch_op(dtype, rows, cols, act):
         ref.backward(dy.float())
         tol = dict(rtol=2e-2, atol=2e-2) if dtype == torch.bfloat16 else dict(rtol=2e-4, atol=2e-4)
         torch.testing.assert_close(dx.float(), xf.grad, **tol)
+        # the bias gradient is the column sum of dx (fp32 oracle; sums of `rows` terms)
+        scale = max(1.0, rows ** 0.5)
+        torch.testing.assert_close(db.float() / scale, xf.grad.sum(0) / scale, **tol)
 
 
 def test_noalloc_without_bias_grad():
