@@ -51,7 +51,8 @@ def run(args, ref_root, model_dims, dist_setup, make_batch, timed_loop, clock_sa
         print(json.dumps({"impl": "reference", "unavailable": f"reference import failed: {err}"}))
         return
     if not os.path.abspath(slapo.__file__).startswith(os.path.abspath(ref_root)):
-        print(json.dumps({"impl": "reference", "unavailable": "a different slapo package shadows baseline/_ref"}))
+        print(json.dumps({"impl": "reference",
+                          "unavailable": "a different slapo package shadows baseline/_ref"}))
         return
 
     world, rank, local = dist_setup(args)
@@ -184,7 +185,8 @@ def run_opt(args, ref_root, dims, dist_setup, timed_loop, clock_sampler_cls, mak
         print(json.dumps({"impl": "reference", "unavailable": f"reference import failed: {err}"}))
         return
     if not os.path.abspath(slapo.__file__).startswith(os.path.abspath(ref_root)):
-        print(json.dumps({"impl": "reference", "unavailable": "a different slapo package shadows baseline/_ref"}))
+        print(json.dumps({"impl": "reference",
+                          "unavailable": "a different slapo package shadows baseline/_ref"}))
         return
     world, rank, local = dist_setup(args)
     device = torch.device("cuda", local)

@@ -66,13 +66,17 @@ def build(verbose: bool = False, force: bool = False) -> str:
     cu_srcs = sorted(f for f in os.listdir(HERE) if f.endswith(".cu"))
     cpp_srcs = sorted(f for f in os.listdir(HERE) if f.endswith(".cpp"))
     nvcc = os.path.join(_cuda_home(), "bin", "nvcc")
+    # SLAPO_B200_DEBUG=1 at build time: index / alignment checks inside the fused kernels that
+    # report through the device status word (code 7) instead of touching a bad peer address
+    debug = ["-DSLAPO_B200_DEBUG"] if os.environ.get("SLAPO_B200_DEBUG", "0") == "1" else []
     cxx = os.environ.get("CXX", "g++")
     log, jobs, objs = [], [], []
     for src in cu_srcs:
         obj = os.path.join(OBJ_DIR, src + ".o")
         objs.append(obj)
         if force or _newer([os.path.join(HERE, src)] + headers, obj):
-            jobs.append([nvcc] + NVCC_FLAGS + ["-I", HERE, "-c", os.path.join(HERE, src), "-o", obj])
+            jobs.append([nvcc] + NVCC_FLAGS + debug + ["-I", HERE, "-c", os.path.join(HERE, src),
+                                                       "-o", obj])
     cxx_flags = [f.replace("ABI=1", f"ABI={abi}") for f in CXX_FLAGS]
     for src in cpp_srcs:
         obj = os.path.join(OBJ_DIR, src + ".o")

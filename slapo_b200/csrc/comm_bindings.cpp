@@ -140,7 +140,8 @@ void peer_all_to_all(at::Tensor src, std::vector<int64_t> dst_ptrs, std::vector<
 
 void vocab_embed_fwd(at::Tensor ids, at::Tensor weight, std::vector<int64_t> out_ptrs,
                      std::vector<int64_t> flag_ptrs, int64_t world, int64_t rank, int64_t epoch,
-                     int64_t vocab_lo, at::Tensor cta_counter, double wait_seconds) {
+                     int64_t vocab_lo, at::Tensor cta_counter, double wait_seconds,
+                     int64_t scatter, int64_t seq) {
   TORCH_CHECK(ids.is_cuda() && ids.scalar_type() == at::kLong && ids.is_contiguous(),
               "vocab_embed_fwd: ids must be a contiguous CUDA int64 tensor");
   TORCH_CHECK(weight.dim() == 2 && weight.is_contiguous() && weight.element_size() == 2,
@@ -152,7 +153,7 @@ void vocab_embed_fwd(at::Tensor ids, at::Tensor weight, std::vector<int64_t> out
   int rc = slapo::launch_vocab_embed_fwd(
       ids.data_ptr<int64_t>(), weight.data_ptr(), o.data(), f.data(), static_cast<int>(world),
       static_cast<int>(rank), static_cast<int>(epoch), ids.numel(),
-      static_cast<int>(weight.size(1)), vocab_lo, weight.size(0),
+      static_cast<int>(weight.size(1)), vocab_lo, weight.size(0), static_cast<int>(scatter), seq,
       reinterpret_cast<unsigned int*>(cta_counter.data_ptr<int>()), slapo_status_ptr(dev),
       wait_seconds, at::cuda::getCurrentCUDAStream().stream());
   TORCH_CHECK(rc == 0, "vocab_embed_fwd: launch refused (code ", rc, ")");
@@ -162,7 +163,8 @@ void vocab_embed_fwd(at::Tensor ids, at::Tensor weight, std::vector<int64_t> out
 
 void register_comm_ops(torch::Library& m) {
   m.def("vocab_embed_fwd(Tensor ids, Tensor weight, int[] out_ptrs, int[] flag_ptrs, int world, "
-        "int rank, int epoch, int vocab_lo, Tensor(a!) cta_counter, float wait_seconds) -> ()",
+        "int rank, int epoch, int vocab_lo, Tensor(a!) cta_counter, float wait_seconds, "
+        "int scatter=0, int seq=0) -> ()",
         &vocab_embed_fwd);
   m.def("peer_all_to_all(Tensor src, int[] dst_ptrs, int[] flag_ptrs, int world, int rank, "
         "int epoch, int outer, int rows, int row_bytes, int src_block_stride, "

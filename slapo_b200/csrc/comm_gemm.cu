@@ -150,6 +150,19 @@ __device__ __forceinline__ void trace_mark(int on, int slot) {
   if (on && blockIdx.x < kTraceCtas) g_comm_trace[blockIdx.x * kTraceSlots + slot] = gtimer();
 }
 
+// Debug build (`SLAPO_B200_DEBUG=1 python -m slapo_b200.csrc.build -f`): every index that
+// becomes a peer address or a flag slot is checked first; a violation records status 7 and
+// the access is skipped instead of faulting another GPU's memory.
+#ifdef SLAPO_B200_DEBUG
+#define SLAPO_DBG_CHECK(cond, status_ptr)                                       \
+  if (!(cond)) {                                                                \
+    if ((status_ptr) != nullptr) atomicExch((status_ptr), 7);                   \
+    continue;                                                                   \
+  }
+#else
+#define SLAPO_DBG_CHECK(cond, status_ptr)
+#endif
+
 // bounded spin on a flag written by another GPU
 __device__ __forceinline__ bool wait_flag(const int* addr, int epoch, long long budget,
                                           volatile int* abort_flag) {
@@ -563,6 +576,9 @@ __device__ __forceinline__ void reduce_units(const CommGemmParams& p, int rows_p
     asm volatile("bar.sync %0, 128;" ::"r"(bar_id) : "memory");
     if (w != 1) break;
     const int row0 = (u / kRedSlices) * CBM + (u % kRedSlices) * (CBM / kRedSlices);
+    SLAPO_DBG_CHECK(row0 + CBM / kRedSlices <= rows_per_rank &&
+                        p.rank * blocks_per_owner + u / kRedSlices < kChunkCountOffset,
+                    p.status)
     if (p.mc_recv != nullptr) {
       reduce_span_mc<8>(p, rows_per_rank, row0, CBM / kRedSlices, gt, 128);
       continue;
@@ -821,6 +837,11 @@ comm_gemm_kernel(const __grid_constant__ SegMaps maps_a, const __grid_constant__
             const uint4* src = reinterpret_cast<const uint4*>(
                 static_cast<const uint8_t*>(p.seg_src[owner]) + off);
             const int m_blk = owner * blocks_per_owner + b;
+            SLAPO_DBG_CHECK(off + static_cast<int64_t>(slice_rows) * p.row_bytes <=
+                                    static_cast<int64_t>(p.seg_len) * p.row_bytes &&
+                                m_blk < kChunkCountOffset && (off & 15) == 0 &&
+                                (static_cast<int64_t>(m_blk) * CBM + sl * slice_rows + slice_rows) <= p.M,
+                            p.status)
             uint4* dst = reinterpret_cast<uint4*>(
                 static_cast<uint8_t*>(p.stage_dst) +
                 (static_cast<int64_t>(m_blk) * CBM + sl * slice_rows) * p.row_bytes);

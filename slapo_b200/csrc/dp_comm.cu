@@ -279,6 +279,11 @@ __global__ void __launch_bounds__(256) peer_all_to_all_kernel(A2AParams p) {
 // (peer stores); ranks that do not own an id write nothing.  One warp per token.  The
 // last CTA to finish exchanges "sent" flags with the peers (bounded wait): when the kernel
 // ends this rank's output holds every row.
+// Sequence-parallel form (`scatter` != 0): a rank keeps only ITS tokens, so the owner of a
+// row stores it into the one rank that keeps the token - the reduce-scatter of the masked
+// lookups, without the lookups of zeros and without the reduction.  scatter 1: tokens are
+// split in `world` contiguous chunks (batch-major activations split along the batch);
+// scatter 2: every sequence of `seq` tokens is split in `world` chunks.
 struct VocabEmbedParams {
   const int64_t* ids;
   const void* weight;           // [vocab_local, hidden] 16-bit
@@ -288,6 +293,8 @@ struct VocabEmbedParams {
   int64_t tokens;
   int hidden_vecs;              // hidden * 2 / 16
   int64_t vocab_lo, vocab_local;
+  int scatter;                  // 0 every rank gets every row, 1 / 2 see above
+  int64_t seq;                  // scatter 2: tokens per sequence
   unsigned int* cta_counter;
   int* status;
   long long wait_cycles;
@@ -301,6 +308,22 @@ __global__ void __launch_bounds__(256) vocab_embed_fwd_kernel(VocabEmbedParams p
     const int64_t id = p.ids[t] - p.vocab_lo;
     if (id < 0 || id >= p.vocab_local) continue;   // another rank owns this row
     const uint4* src = static_cast<const uint4*>(p.weight) + id * p.hidden_vecs;
+    if (p.scatter != 0) {
+      int dst;
+      int64_t row;
+      if (p.scatter == 1) {
+        const int64_t per = p.tokens / p.world;
+        dst = static_cast<int>(t / per);
+        row = t - dst * per;
+      } else {
+        const int64_t per = p.seq / p.world, s_pos = t % p.seq;
+        dst = static_cast<int>(s_pos / per);
+        row = (t / p.seq) * per + (s_pos - dst * per);
+      }
+      uint4* out = static_cast<uint4*>(p.out[dst]) + row * p.hidden_vecs;
+      for (int v = lane; v < p.hidden_vecs; v += 32) out[v] = src[v];
+      continue;
+    }
     for (int v = lane; v < p.hidden_vecs; v += 32) {
       const uint4 val = src[v];
 #pragma unroll
@@ -434,10 +457,13 @@ int launch_peer_all_to_all(const void* src, void* const* dst_ptrs, int* const* f
 
 int launch_vocab_embed_fwd(const int64_t* ids, const void* weight, void* const* out_ptrs,
                            int* const* flag_ptrs, int world, int rank, int epoch, int64_t tokens,
-                           int hidden, int64_t vocab_lo, int64_t vocab_local,
-                           unsigned int* cta_counter, int* status, double wait_seconds,
-                           cudaStream_t stream) {
+                           int hidden, int64_t vocab_lo, int64_t vocab_local, int scatter,
+                           int64_t seq, unsigned int* cta_counter, int* status,
+                           double wait_seconds, cudaStream_t stream) {
   if (world < 1 || world > kDpMaxRanks || hidden % 8 != 0) return 1;
+  if (scatter == 1 && tokens % world != 0) return 1;
+  if (scatter == 2 && (seq <= 0 || seq % world != 0 || tokens % seq != 0)) return 1;
+  if (scatter < 0 || scatter > 2) return 1;
   VocabEmbedParams p;
   p.ids = ids; p.weight = weight;
   for (int r = 0; r < kDpMaxRanks; ++r) {
@@ -446,6 +472,7 @@ int launch_vocab_embed_fwd(const int64_t* ids, const void* weight, void* const* 
   }
   p.world = world; p.rank = rank; p.epoch = epoch; p.tokens = tokens;
   p.hidden_vecs = hidden / 8; p.vocab_lo = vocab_lo; p.vocab_local = vocab_local;
+  p.scatter = scatter; p.seq = seq;
   p.cta_counter = cta_counter; p.status = status; p.wait_cycles = dp_wait_cycles(wait_seconds);
   int64_t blocks = (tokens + 7) / 8;
   const int64_t cap = static_cast<int64_t>(sm_count()) * 8;

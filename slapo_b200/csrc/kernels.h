@@ -108,11 +108,14 @@ int launch_peer_all_to_all(const void* src, void* const* dst_ptrs, int* const* f
                            cudaStream_t stream);
 
 // Vocabulary-parallel embedding forward by peer stores (16-bit weights, hidden % 8 == 0).
+// scatter: 0 = every rank receives every token's row; 1 = rank r keeps the r-th contiguous
+// chunk of the tokens; 2 = rank r keeps the r-th chunk of every sequence of `seq` tokens
+// (the sequence-parallel forms: out_ptrs then address [tokens / world, hidden] buffers).
 int launch_vocab_embed_fwd(const int64_t* ids, const void* weight, void* const* out_ptrs,
                            int* const* flag_ptrs, int world, int rank, int epoch, int64_t tokens,
-                           int hidden, int64_t vocab_lo, int64_t vocab_local,
-                           unsigned int* cta_counter, int* status, double wait_seconds,
-                           cudaStream_t stream);
+                           int hidden, int64_t vocab_lo, int64_t vocab_local, int scatter,
+                           int64_t seq, unsigned int* cta_counter, int* status,
+                           double wait_seconds, cudaStream_t stream);
 
 }  // namespace slapo
 

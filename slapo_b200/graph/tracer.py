@@ -13,10 +13,16 @@ and a warning is logged, so scheduling of the rest of the model goes on.
 Three capture engines are selectable by name:
 
 * ``"pytorch"`` - ``torch.fx`` symbolic tracing (default);
-* ``"huggingface"`` - accepted for source compatibility and served by the same
-  engine (``transformers.utils.fx`` no longer exists); ``concrete_args`` are
-  the forward arguments to freeze, lower levels freeze every optional
-  argument their call site leaves out;
+* ``"huggingface"`` - meta-tensor propagation in the manner of the tracer that
+  ``transformers.utils.fx`` used to ship (it no longer exists): the top level
+  is traced on a meta-device copy of the model with dummy meta inputs derived
+  from the forward signature and ``config`` (batch 2, ``config["seq_len"]`` or
+  16 tokens; integer ids for ``*_ids`` / ``labels`` / ``*mask`` arguments,
+  ``[2, seq, hidden_size]`` floats otherwise), every proxy carries the meta
+  tensor of its value, so ``x.size()``, ``x.shape[i]`` and Python control flow
+  on them resolve to constants; shapes and dtypes stay on the nodes
+  (``node.meta["shape"]`` / ``["dtype"]``).  Lower levels of a hierarchical trace
+  use the plain engine;
 * ``"dynamo"`` - ``torch.export`` capture (always flat).
 
 Parity: slapo/tracer.py:150-272 (hierarchical tracing), :24-25,:511-520
@@ -80,6 +86,76 @@ class HierTracer(fx.Tracer):
         if isinstance(m, fx.GraphModule):
             return False
         return super().is_leaf_module(m, module_qualified_name)
+
+
+_META_TRACER_CLS = []
+
+
+def MetaHierTracer(leaf_modules=None, forced_leaf_names=None):   # noqa: N802 - a class factory
+    """The leaf rules of :class:`HierTracer` on ``torch.fx``'s meta-tensor tracer (the class
+    is composed on first use, so the experimental module is imported only then)."""
+    if not _META_TRACER_CLS:
+        from torch.fx.experimental.meta_tracer import MetaTracer
+
+        _META_TRACER_CLS.append(type("MetaHierTracer", (HierTracer, MetaTracer), {
+            "name": "huggingface", "create_proxy": _meta_create_proxy,
+            "call_module": _meta_call_module, "_in_meta_eval": False}))
+    return _META_TRACER_CLS[0](leaf_modules, forced_leaf_names)
+
+
+def _meta_call_module(self, m, forward, args, kwargs):
+    # While the output shape of a leaf module is being computed on meta tensors, the modules
+    # INSIDE that leaf just run: they must not be recorded as nodes of the graph.
+    if self._in_meta_eval:
+        return forward(*args, **kwargs)
+    from torch.fx.experimental.meta_tracer import MetaTracer
+
+    return MetaTracer.call_module(self, m, forward, args, kwargs)
+
+
+def _meta_create_proxy(self, kind, target, args, kwargs, name=None, type_expr=None,
+                       proxy_factory_fn=None):
+    from torch.fx.experimental.meta_tracer import MetaTracer
+
+    self._in_meta_eval = kind == "call_module"
+    try:
+        rv = MetaTracer.create_proxy(self, kind, target, args, kwargs, name, type_expr,
+                                     proxy_factory_fn)
+    finally:
+        self._in_meta_eval = False
+    meta = getattr(rv, "_tensor_meta", None)
+    if isinstance(meta, torch.Tensor):
+        rv.node.meta["shape"] = tuple(meta.shape)
+        rv.node.meta["dtype"] = meta.dtype
+    return rv
+
+
+_INT_ARG_HINTS = ("ids", "labels", "mask", "positions")
+
+
+def dummy_meta_inputs(root: nn.Module, concrete_args=None, config=None):
+    """Meta tensors for the forward arguments that stay symbolic: what the ``"huggingface"``
+    engine propagates.  ``config`` (dict or object) may give ``seq_len``, ``hidden_size``,
+    ``batch_size`` and ``input_shapes = {name: (shape, dtype)}`` for anything unusual."""
+    get = (lambda k, d=None: config.get(k, d)) if isinstance(config, dict) else \
+        (lambda k, d=None: getattr(config, k, d))
+    batch, seq = get("batch_size", 2) or 2, get("seq_len", 16) or 16
+    hidden = get("hidden_size", None) or get("d_model", None) or get("n_embd", None) or 16
+    explicit = get("input_shapes", None) or {}
+    metas = {}
+    for name, par in inspect.signature(root.forward).parameters.items():
+        if par.kind in (par.VAR_POSITIONAL, par.VAR_KEYWORD) or name in (concrete_args or {}):
+            continue
+        if name in explicit:
+            shape, dtype = explicit[name]
+            metas[name] = torch.empty(tuple(shape), dtype=dtype, device="meta")
+        elif par.default is not inspect.Parameter.empty:
+            continue            # optional and not named: frozen at its default by the caller
+        elif any(h in name for h in _INT_ARG_HINTS):
+            metas[name] = torch.empty((batch, seq), dtype=torch.long, device="meta")
+        else:
+            metas[name] = torch.empty((batch, seq, hidden), dtype=torch.float32, device="meta")
+    return metas
 
 
 def _direct_child_names(root: nn.Module):
@@ -154,8 +230,28 @@ def _get_submodule_or_none(root, target):
     return cur
 
 
+def _trace_with_meta(root, leaf_modules, forced, cargs, config):
+    """Top level of the ``"huggingface"`` engine: trace a meta-device copy (so that leaf
+    modules can run on the meta inputs) and return its graph, whose targets are names and
+    therefore fit the real module tree just as well."""
+    import copy
+
+    metas = dummy_meta_inputs(root, cargs, config)
+    frozen = dict(cargs)
+    for name, par in inspect.signature(root.forward).parameters.items():
+        if name not in metas and name not in frozen and par.default is not inspect.Parameter.empty:
+            frozen[name] = par.default
+    try:
+        shadow = copy.deepcopy(root).to("meta")
+    except Exception:       # modules that cannot be copied are traced in place
+        shadow = root
+    tracer = MetaHierTracer(leaf_modules, forced)
+    graph = tracer.trace(shadow, meta_args=metas, concrete_args=frozen or None)
+    return graph, frozen
+
+
 def _trace_level(root: nn.Module, *, leaf_modules, flatten, recursive, concrete_args,
-                 call_node=None):
+                 call_node=None, engine="pytorch", config=None):
     if isinstance(root, fx.GraphModule):
         return root
     judge = HierTracer(leaf_modules)
@@ -163,8 +259,16 @@ def _trace_level(root: nn.Module, *, leaf_modules, flatten, recursive, concrete_
     tracer = HierTracer(leaf_modules, forced)
     graph = None
     cargs = _fill_concrete_args(root, concrete_args, call_node)
+    if engine == "huggingface" and call_node is None:
+        try:
+            graph, cargs = _trace_with_meta(root, leaf_modules, forced, cargs, config)
+        except Exception as meta_err:
+            logger.info("meta-tensor trace of %s failed (%s); trying the plain engine",
+                        type(root).__name__, meta_err)
+            graph = None
     try:
-        graph = tracer.trace(root, concrete_args=cargs or None)
+        if graph is None:
+            graph = tracer.trace(root, concrete_args=cargs or None)
     except Exception as first_err:
         # Optional inputs (default None) that steer Python control flow cannot
         # stay symbolic.  Retry once with every such input frozen at None; the
@@ -273,7 +377,7 @@ def trace(model: nn.Module, tracer: str = "pytorch", recursive: bool = True,
         raise ValueError(f"unknown tracer {tracer}")
     return _trace_level(
         model, leaf_modules=list(leaf_modules or []), flatten=flatten, recursive=recursive,
-        concrete_args=concrete_args)
+        concrete_args=concrete_args, engine=tracer, config=config)
 
 
 trace_module = trace

@@ -158,7 +158,8 @@ def pipeline_cut(sch, prefix, cuts):
 @register_schedule("bert")
 def schedule_bert(model, model_config=None, prefix="bert", fp16=False, bf16=False, group=None,
                   attn_op_name="auto", disable_flash_attn=False, fuse=True,
-                  sequence_parallel=False, sequence_parallel_axis=0, ckpt_ratio=0.0, checkpoint_method="uniform",
+                  sequence_parallel=False, sequence_parallel_axis=0, ckpt_ratio=0.0,
+                  checkpoint_method="uniform",
                   bcast_input=False, pipeline_cuts=None, shard_vocab=True, delay_init=True,
                   **_unused):
     config = model_config if model_config is not None else getattr(model, "config", None)

@@ -3,7 +3,6 @@ from __future__ import annotations
 
 import torch
 import torch.distributed as dist
-from torch import nn
 
 from ...logger import get_logger
 from ...parallel.sync_ops import reduce_forward_output, reduce_scatter_forward_output

@@ -23,7 +23,6 @@ do not divide the group size raise instead of silently mis-sharding.
 """
 from __future__ import annotations
 
-import torch
 from torch import nn
 
 from ... import create_schedule

@@ -1,7 +1,10 @@
 """Scheduling recipe for T5 (encoder-decoder, relative-position bias, plain or
 gated feed-forward).
 
-Tensor parallelism: q / k / v column-parallel (whole heads per rank), ``o``
+Projection fusion (``fuse_qkv``, default on): self-attention q / k / v become one
+``qkv`` GEMM, cross-attention k / v one ``kv`` GEMM (:class:`T5FusedAttention`).
+
+Tensor parallelism: the (fused) projections column-parallel (whole heads per rank), ``o``
 row-parallel, the relative-position table split along its head axis, ``wi``
 (or the gate pair ``wi_0`` / ``wi_1``, split identically) column-parallel,
 ``wo`` row-parallel, the shared embedding vocabulary-parallel with the tied
@@ -28,8 +31,26 @@ def _blocks(sch, stack):
     return [f"{stack}.block.{i}" for i in range(n)]
 
 
+def fuse_projections(sch):
+    """Replace every attention module by its fused-projection form; returns how many."""
+    from ..t5 import T5Attention, T5FusedAttention
+
+    count = 0
+    for stack in ("encoder", "decoder"):
+        for blk in _blocks(sch, stack):
+            paths = [(f"{blk}.layer.0.SelfAttention", False)]
+            if stack == "decoder":
+                paths.append((f"{blk}.layer.1.EncDecAttention", True))
+            for path, cross in paths:
+                if isinstance(sch[path].mod, T5Attention):
+                    sch[path].replace(T5FusedAttention(sch[path].mod, cross))
+                    count += 1
+    return count
+
+
 def _shard_attention(sch, path):
-    for name in ("q", "k", "v"):
+    names = [n for n in ("qkv", "kv", "q", "k", "v") if n in sch[path].child]
+    for name in names:
         sch[f"{path}.{name}"].shard("weight", axis=0)
         sch[f"{path}.{name}"].sync("bwd_post", "all_reduce")
     sch[f"{path}.o"].shard("weight", axis=1)
@@ -70,12 +91,14 @@ def shard_t5(sch, config):
 
 @register_schedule("t5")
 def schedule_t5(model, model_config=None, fp16=False, bf16=False, group=None, ckpt_ratio=0.0,
-                checkpoint_method="uniform", bcast_input=False, pipeline_cuts=None, **_unused):
+                checkpoint_method="uniform", bcast_input=False, pipeline_cuts=None,
+                fuse_qkv=True, **_unused):
     config = model_config if model_config is not None else getattr(model, "config", None)
     if config is None:
         raise ValueError("model_config is required")
     cast_dtype(model, fp16, bf16)
     sch = create_schedule(model, group=group)
+    n_fused = fuse_projections(sch) if fuse_qkv else 0
     n_shard = shard_t5(sch, config)
     if bcast_input:
         broadcast_input(sch)
@@ -90,5 +113,6 @@ def schedule_t5(model, model_config=None, fp16=False, bf16=False, group=None, ck
         sch["encoder"].cut_pipeline_stage()
         for idx in dec_cuts:
             sch[f"decoder.block.{idx}"].cut_pipeline_stage()
-    logger.info("t5 schedule: %d blocks sharded, %d checkpointed", n_shard, n_ckpt, ranks=0)
+    logger.info("t5 schedule: %d attention modules with fused projections, %d blocks sharded, "
+                "%d checkpointed", n_fused, n_shard, n_ckpt, ranks=0)
     return sch

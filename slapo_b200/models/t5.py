@@ -140,6 +140,70 @@ class T5Attention(nn.Module):
         return self.o(ctx.reshape(ctx.shape[:-2] + (-1,)))
 
 
+class T5FusedAttention(nn.Module):
+    """:class:`T5Attention` with its projections fused: self-attention computes q, k and v
+    with ONE GEMM (``qkv``), cross-attention k and v of the encoder output with one (``kv``)
+    next to ``q``.  Weight rows are ordered ``[head][q | k | v][d_kv]`` (``[head][k | v][d_kv]``),
+    so slicing axis 0 by the tensor-parallel size hands each rank whole heads, and the
+    projection output is read in place as strided ``[B, S, H, D]`` views - the packed
+    flash-attention path takes them without a copy.
+
+    Parity: the horizontal ``replace`` of q/k/v by ``FusedQKV`` and of cross-attention k/v by
+    ``FusedKV`` + ``ShardableQ`` (slapo/model_schedule/t5.py:95-143, 168-200 of the reference)."""
+
+    traceable = False
+
+    def __init__(self, attn: "T5Attention", cross: bool):
+        super().__init__()
+        self.n_heads, self.d_kv, self.cross = attn.n_heads, attn.d_kv, cross
+        self.causal, self.dropout = attn.causal, attn.dropout
+        self.num_buckets, self.max_distance = attn.num_buckets, attn.max_distance
+        self.attn_op_name = attn.attn_op_name
+        d_model = attn.q.weight.shape[1]
+        inner = self.n_heads * self.d_kv
+        meta = attn.q.weight.is_meta
+        kw = dict(bias=False, device=attn.q.weight.device, dtype=attn.q.weight.dtype)
+
+        def pack(*mats):
+            parts = [m.reshape(self.n_heads, self.d_kv, d_model) for m in mats]
+            return torch.cat(parts, dim=1).reshape(-1, d_model)
+
+        if cross:
+            self.q = attn.q
+            self.kv = nn.Linear(d_model, 2 * inner, **kw)
+            if not meta:
+                self.kv.weight = nn.Parameter(pack(attn.k.weight.data, attn.v.weight.data))
+        else:
+            self.qkv = nn.Linear(d_model, 3 * inner, **kw)
+            if not meta:
+                self.qkv.weight = nn.Parameter(pack(attn.q.weight.data, attn.k.weight.data,
+                                                    attn.v.weight.data))
+        self.o = attn.o
+        if hasattr(attn, "relative_attention_bias"):
+            self.relative_attention_bias = attn.relative_attention_bias
+
+    def forward(self, hidden_states, key_value_states=None, key_bias=None, rel_table=None):
+        d = self.d_kv
+        if self.cross:
+            q = self.q(hidden_states)
+            q = q.view(q.shape[:-1] + (-1, d))
+            kv = self.kv(key_value_states)
+            kv = kv.view(kv.shape[:-1] + (-1, 2, d))        # -1 absorbs a split of the heads
+            k, v = kv[..., 0, :], kv[..., 1, :]
+        else:
+            qkv = self.qkv(hidden_states)
+            qkv = qkv.view(qkv.shape[:-1] + (-1, 3, d))
+            q, k, v = qkv[..., 0, :], qkv[..., 1, :], qkv[..., 2, :]
+        kwargs = dict(key_padding_bias=key_bias, causal=self.causal, scale=1.0,
+                      dropout_p=self.dropout, training=self.training, rel_bias_table=rel_table,
+                      rel_bidirectional=not self.causal, rel_max_distance=self.max_distance)
+        if self.attn_op_name == "reference":
+            ctx = NF.attention_reference(q, k, v, **kwargs)
+        else:
+            ctx = NF.flash_attention(q, k, v, **kwargs)
+        return self.o(ctx.reshape(ctx.shape[:-2] + (-1,)))
+
+
 class T5LayerSelfAttention(nn.Module):
     def __init__(self, config, has_relative_attention_bias, causal):
         super().__init__()

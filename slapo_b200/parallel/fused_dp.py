@@ -43,6 +43,11 @@ class FusedDP:
         self.flags.zero_()
         self.flat_grad.zero_()
         device = self.flat_grad.device
+        # epoch of the last reduce-scatter per bucket / of the last AdamW: the flag protocol
+        # counts epochs upwards, a repeated or older epoch would find its flags already set
+        # and read peers that are not ready (checked on the host, see _check_epoch)
+        self._rs_epoch = [0] * n_buckets
+        self._ag_epoch = 0
         self.norm_acc = torch.zeros(2, dtype=torch.float32, device=device)
         self.cta_counter = torch.zeros(1, dtype=torch.int32, device=device)
         from .symm import SymmContext
@@ -52,7 +57,18 @@ class FusedDP:
             dist.barrier(group=ctx.group)
 
     # ------------------------------------------------------------------ #
+    @staticmethod
+    def _check_epoch(what, last, epoch):
+        if epoch <= last:
+            raise RuntimeError(
+                f"{what}: epoch {epoch} after epoch {last}; every launch of a flag-synchronised "
+                "kernel needs a larger epoch than the one before (a bucket reduced twice in "
+                "one step, or a step counter that went backwards)")
+
     def grad_rs(self, bucket, epoch, lo, out, dup_mask=None, accumulate_norm=True, split=True):
+        self._check_epoch(f"gradient reduce-scatter of bucket {bucket}", self._rs_epoch[bucket],
+                          epoch)
+        self._rs_epoch[bucket] = epoch
         ops = native.ops()
         args = (self.grad_buf.ptrs(), self.flag_buf.ptrs(), self.world, self.rank, bucket, epoch,
                 lo, out, dup_mask, self.norm_acc if accumulate_norm else None, self.wait_seconds)
@@ -64,6 +80,9 @@ class FusedDP:
 
     def adamw_ag(self, epoch, last, lo, grad, master, exp_avg, exp_avg_sq, decay_mask, grad_scale,
                  lr, betas, eps, weight_decay, bc1, bc2):
+        if epoch < self._ag_epoch:     # one launch per bucket shares the step's epoch
+            self._check_epoch("AdamW + parameter all-gather", self._ag_epoch, epoch)
+        self._ag_epoch = epoch
         native.ops().dp_adamw_ag(
             self.param_buf.ptrs(), self.flag_buf.ptrs(), self.world, self.rank, self.n_buckets,
             epoch, bool(last), lo, grad, master, exp_avg, exp_avg_sq, decay_mask, grad_scale,

@@ -55,6 +55,50 @@ def _check_status():
                            "ran out (a rank is missing or stuck)")
 
 
+_DEBUG = __import__("os").environ.get("SLAPO_B200_DEBUG", "0") == "1"
+
+
+def _debug_check(ctx, epoch, a_ptrs, b_ptrs, M, N, K, lda, ldb, dtype, gather, seg_len, mode,
+                 recv, ar_out, stage, chunk_flags):
+    """Host-side checks of one fused launch (``SLAPO_B200_DEBUG=1``): everything a kernel
+    would otherwise turn into a wrong peer address - alignment of every operand pointer, the
+    sizes of the symmetric buffers against the problem, the flag slots against the pad, the
+    epoch against the previous one."""
+    esize = 2
+    last = ctx.__dict__.get("_debug_last_epoch", 0)
+    if epoch <= last:
+        raise RuntimeError(f"fused op epoch {epoch} does not follow {last}")
+    ctx.__dict__["_debug_last_epoch"] = epoch
+    for name, ptrs in (("A", a_ptrs), ("B", b_ptrs)):
+        for r, p in enumerate(ptrs):
+            if int(p) % 16:
+                raise ValueError(f"operand {name} of rank {r}: address {int(p):#x} is not 16-byte aligned")
+    if lda % 8 or ldb % 8 or N % 8 or K % 8:
+        raise ValueError("leading dimensions / sizes must be multiples of 8: "
+                         f"lda={lda} ldb={ldb} N={N} K={K}")
+    blocks = (M + 127) // 128
+    if (gather == GATHER_A_ROWS_STAGED or mode != MODE_LOCAL) and blocks > _CHUNK_WORDS:
+        raise ValueError(f"{blocks} row blocks exceed the {_CHUNK_WORDS} flag slots")
+    if gather in (GATHER_A_ROWS, GATHER_A_ROWS_STAGED) and seg_len * ctx.world != M:
+        raise ValueError(f"gathered rows: {ctx.world} segments of {seg_len} != M={M}")
+    if gather in (GATHER_A_K, GATHER_B_K) and seg_len * ctx.world != K:
+        raise ValueError(f"gathered contraction: {ctx.world} segments of {seg_len} != K={K}")
+    if mode != MODE_LOCAL:
+        need = RECV_HEADER_BYTES + M * N * esize
+        if recv is None or recv.nbytes < need:
+            raise ValueError(f"partial-product buffer holds {getattr(recv, 'nbytes', 0)} bytes, "
+                             f"the op needs {need}")
+        if len(recv.peer_ptrs) != ctx.world:
+            raise ValueError("partial-product buffer was not rendezvoused over the whole group")
+    if mode == MODE_AR and (ar_out is None or ar_out.nbytes < M * N * esize):
+        raise ValueError("all-reduce output buffer is too small")
+    if gather == GATHER_A_ROWS_STAGED:
+        if stage is None or stage.numel() < M * K:
+            raise ValueError("staging buffer of the gathered operand is too small")
+        if chunk_flags is None or chunk_flags.numel() < 2 * _CHUNK_WORDS:
+            raise ValueError("chunk flag pad is too small")
+
+
 def _wgrad(dy, x):
     """``dW = dY^T X`` on this library's split-K GEMM (both operands read as stored: ``dY``
     M-major, ``X`` N-major); tensors the kernel cannot address go to PyTorch."""
@@ -83,6 +127,9 @@ def comm_gemm(ctx, *, a_ptrs, b_ptrs, M, N, K, lda, ldb, a_mn, b_mn, dtype, gath
               ar_out=None, stage=None, chunk_flags=None):
     """Thin wrapper of ``torch.ops.slapo_b200.comm_gemm``; takes the next epoch."""
     epoch = ctx.next_epoch()
+    if _DEBUG:
+        _debug_check(ctx, epoch, a_ptrs, b_ptrs, M, N, K, lda, ldb, dtype, gather, seg_len, mode,
+                     recv, ar_out, stage, chunk_flags)
     native.ops().comm_gemm(
         [int(p) for p in a_ptrs], [int(p) for p in b_ptrs], M, N, K, lda, ldb, a_mn, b_mn,
         dtype == torch.bfloat16, gather, seg_len, mode, ctx.world, ctx.rank, epoch, int(out_ptr),

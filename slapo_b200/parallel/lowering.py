@@ -41,15 +41,18 @@ def _pop_sync_hook(mod, op, **match):
 
 
 def _lower_vocab_embedding(sub, ctx) -> bool:
-    """``shard_word_embedding`` (masked lookup + all-reduce hooks) -> the peer-store kernel.
-    Only the all-reduce form on 16-bit weights; the sequence-parallel form keeps its hooks."""
+    """``shard_word_embedding`` (masked lookup + all-reduce / reduce-scatter hooks) -> the
+    peer-store kernel, in its all-gather form or - under sequence parallelism - its scatter
+    form.  16-bit weights only."""
     import torch
 
     from ..ops.embedding import FusedVocabParallelEmbedding
 
     mod = sub.mod
     hooks = getattr(mod, "_vocab_parallel_hooks", None)
-    if hooks is None or hooks.sequence_parallel or mod.weight.is_meta:
+    if hooks is None or mod.weight.is_meta:
+        return False
+    if hooks.sequence_parallel and hooks.sp_axis not in (0, 1):
         return False
     if mod.weight.dtype not in (torch.bfloat16, torch.float16) or mod.embedding_dim % 8:
         return False
@@ -57,7 +60,8 @@ def _lower_vocab_embedding(sub, ctx) -> bool:
         for key, fn in list(table.items()):
             if getattr(fn, "__self__", None) is hooks:
                 del table[key]
-    sub.replace(FusedVocabParallelEmbedding.from_sharded(mod, sub.rank, ctx))
+    sub.replace(FusedVocabParallelEmbedding.from_sharded(
+        mod, sub.rank, ctx, hooks.sp_axis if hooks.sequence_parallel else None))
     return True
 
 

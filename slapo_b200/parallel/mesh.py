@@ -134,7 +134,8 @@ class DeviceMesh:
         return self.get_rank(pp=c["pp"] + 1, dp=c["dp"], tp=c["tp"])
 
     def __repr__(self):
-        return f"DeviceMesh(pp={self.dims['pp']}, dp={self.dims['dp']}, tp={self.dims['tp']}, rank={self.rank})"
+        d = self.dims
+        return f"DeviceMesh(pp={d['pp']}, dp={d['dp']}, tp={d['tp']}, rank={self.rank})"
 
 
 def generate_pipeline_cuts(num_layers: int, num_pp: int, is_encoder_decoder: bool = False):

@@ -29,8 +29,7 @@ from __future__ import annotations
 
 import operator
 
-import torch
-from torch import fx, nn
+from torch import fx
 from torch.fx.passes.split_module import split_module
 
 from ..logger import get_logger

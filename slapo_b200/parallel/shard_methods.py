@@ -19,7 +19,6 @@ from __future__ import annotations
 
 from functools import partial
 
-import torch
 from torch import nn
 
 from ..logger import get_logger

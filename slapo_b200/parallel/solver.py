@@ -148,7 +148,8 @@ class ShardingSolver:
         """Time of a collective moving ``factor * (n-1)/n * nbytes`` per rank."""
         if nbytes == 0 or factor == 0:
             return 0.0
-        return self.hw.collective_latency_s + factor * nbytes * (self.n - 1) / self.n / self.hw.link_bytes_per_s
+        moved = factor * nbytes * (self.n - 1) / self.n
+        return self.hw.collective_latency_s + moved / self.hw.link_bytes_per_s
 
     def reshard_cost(self, src, dst, nbytes):
         """Forward + backward time of converting a value's layout."""

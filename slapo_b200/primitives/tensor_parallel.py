@@ -6,7 +6,6 @@ from __future__ import annotations
 
 import functools
 
-from torch import nn
 
 from ..parallel.shard_methods import (apply_shard_method, apply_sync_method,
                                       new_or_get_tied_param)

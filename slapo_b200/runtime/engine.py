@@ -28,7 +28,6 @@ which is how the multi-rank logic is tested without GPUs.
 """
 from __future__ import annotations
 
-import math
 from dataclasses import dataclass, field
 
 import torch
@@ -37,6 +36,7 @@ from torch import nn
 
 from ..logger import get_logger
 from ..ops import native
+from ..utils import nvtx
 
 logger = get_logger("engine")
 
@@ -53,6 +53,9 @@ class EngineConfig:
     overlap_comm: bool = True
     grad_accum_steps: int = 1
     lr_schedule: object = None     # callable(step) -> lr multiplier
+    # profile: NVTX ranges around the phases of every step and around the modules that the
+    # schedule primitives created, plus device-timed phase durations (``phase_times()``);
+    # costs one event pair per phase and no synchronisation
     profile: bool = False
     extra: dict = field(default_factory=dict)
 
@@ -117,7 +120,8 @@ class TrainEngine:
         self.mesh = mesh
         self.tp_group = tp_group if tp_group is not None else (mesh.tp_group if mesh else None)
         self.dp_group = dp_group if dp_group is not None else (mesh.dp_group if mesh else None)
-        self.tp_size = mesh.tp_size if mesh else (dist.get_world_size(tp_group) if tp_group is not None else 1)
+        self.tp_size = mesh.tp_size if mesh else (
+            dist.get_world_size(tp_group) if tp_group is not None else 1)
         if mesh is not None:
             self.dp_size, self.dp_rank = mesh.dp_size, mesh.dp_rank
         elif dp_group is not None:
@@ -139,6 +143,12 @@ class TrainEngine:
         self._build_flat_storage()
         self._build_optimizer_state()
         self._install_grad_hooks()
+        self._phase_events = []       # (name, start event, end event) of the last step
+        if self.cfg.profile:
+            nvtx.enable(True)
+            n = nvtx.annotate_modules(self.model)
+            logger.info("profile: NVTX ranges on %d scheduled modules and on the step phases", n,
+                        ranks=0)
 
     # ------------------------------------------------------------------ #
     def _build_flat_storage(self):
@@ -342,7 +352,7 @@ class TrainEngine:
             import contextlib
 
             ctx = contextlib.nullcontext()
-        with ctx:
+        with ctx, nvtx.range(f"slapo_b200.dp_reduce.bucket{b_idx}"):
             if self.fdp is not None:
                 pos = self.shard_offsets[b_idx]
                 lo, hi = self.shard_ranges[b_idx]
@@ -570,20 +580,55 @@ class TrainEngine:
                 dist.all_gather_into_tensor(full, self.flat_param[lo:hi].clone(), group=self.dp_group)
 
     # ------------------------------------------------------------------ #
+    def _phase(self, name):
+        """Context manager of one step phase: an NVTX range and, with ``profile``, a pair of
+        CUDA events whose distance ``phase_times()`` reports (never synchronises here)."""
+        import contextlib
+
+        @contextlib.contextmanager
+        def ctx():
+            timed = self.cfg.profile and self.device.type == "cuda" \
+                and not torch.cuda.is_current_stream_capturing()
+            if timed:
+                start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                start.record()
+            with nvtx.range(f"slapo_b200.{name}"):
+                yield
+            if timed:
+                end.record()
+                self._phase_events.append((name, start, end))
+
+        return ctx()
+
+    def phase_times(self):
+        """``{"forward": ms, "backward": ms, "optimizer": ms}`` of the last profiled step
+        (device time between the phase's events; synchronises on the last one).  Empty unless
+        the engine was built with ``profile=True`` on a CUDA device."""
+        out = {}
+        for name, start, end in self._phase_events:
+            end.synchronize()
+            out[name] = out.get(name, 0.0) + start.elapsed_time(end)
+        return out
+
     def train_batch(self, *args, labels=None, **kwargs):
-        out = self.model(*args, **kwargs)
-        if self.loss_fn is not None:
-            loss = self.loss_fn(out, labels)
-        elif torch.is_tensor(out):
-            loss = out
-        elif isinstance(out, dict):
-            loss = out["loss"]
-        else:
-            loss = out[0]
-        if loss.dim() > 0:
-            loss = loss.float().mean()
-        self.backward(loss)
-        self.step()
+        if self.micro_step % self.cfg.grad_accum_steps == 0:
+            self._phase_events = []
+        with self._phase("forward"):
+            out = self.model(*args, **kwargs)
+            if self.loss_fn is not None:
+                loss = self.loss_fn(out, labels)
+            elif torch.is_tensor(out):
+                loss = out
+            elif isinstance(out, dict):
+                loss = out["loss"]
+            else:
+                loss = out[0]
+            if loss.dim() > 0:
+                loss = loss.float().mean()
+        with self._phase("backward"):
+            self.backward(loss)
+        with self._phase("optimizer"):
+            self.step()
         return loss.detach()
 
     # ---- checkpoint support ------------------------------------------ #

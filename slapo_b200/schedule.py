@@ -27,7 +27,7 @@ from .graph.tracer import trace as trace_module
 from .logger import get_logger
 from .pattern import Pattern
 from .primitives.base import PRIMITIVES
-from .utils.common import is_module_list, transfer_hooks
+from .utils.common import is_module_list
 
 logger = get_logger("schedule")
 

@@ -78,7 +78,8 @@ def transformer_train_flops_per_sample(layers, hidden, seq, vocab, ffn=None):
     return 3 * (layers * per_layer + 2 * seq * hidden * vocab)
 
 
-def t5_train_flops_per_sample(enc_layers, dec_layers, d_model, d_attn, d_ff, enc_seq, dec_seq, vocab, gated=False):
+def t5_train_flops_per_sample(enc_layers, dec_layers, d_model, d_attn, d_ff, enc_seq, dec_seq,
+                              vocab, gated=False):
     """fwd+bwd FLOPs of one encoder-decoder sample."""
     def attn(sq, sk):
         proj = 2 * d_model * d_attn * (2 * sq + 2 * sk)

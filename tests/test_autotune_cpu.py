@@ -2,8 +2,6 @@
 with early stop, the JSON database, log parsers, dialect registry and the CLI
 driving a (fake) training script."""
 import json
-import os
-import sys
 import textwrap
 
 import pytest

@@ -7,7 +7,6 @@ import tempfile
 
 import pytest
 import torch
-import torch.distributed as dist
 from torch import nn
 
 import slapo_b200 as slapo

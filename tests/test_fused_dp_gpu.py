@@ -262,3 +262,36 @@ def test_vocab_parallel_embedding_emulated_ranks(world):
         outs[r].backward(g)
         torch.testing.assert_close(mods[r].weight.grad.float(), ref.chunk(world)[r],
                                    rtol=2e-2, atol=2e-2)
+
+
+@pytest.mark.parametrize("sp_axis", [0, 1])
+@pytest.mark.parametrize("world", [2, 4])
+def test_vocab_parallel_embedding_scatter_form_emulated_ranks(world, sp_axis):
+    """Sequence-parallel form: the owner of a row stores it into the ONE rank that keeps the
+    token; once all ranks have run, every rank's buffer holds exactly its chunk of the batch
+    (axis 0) or of every sequence (axis 1)."""
+    from slapo_b200.ops import native
+    from slapo_b200.ops.embedding import FusedVocabParallelEmbedding
+    from slapo_b200.parallel.symm import LocalSymmContext
+
+    torch.manual_seed(5)
+    vocab, hidden, b, s = 64 * world, 128, 8, 48
+    table = torch.randn(vocab, hidden, device="cuda").bfloat16()
+    ids = torch.randint(0, vocab, (b, s), device="cuda")
+    want = table[ids].chunk(world, dim=sp_axis)
+    ctx = LocalSymmContext(world)
+    mods = [FusedVocabParallelEmbedding(torch.nn.Parameter(table.chunk(world)[r].clone()),
+                                        r * (vocab // world), ctx.as_rank(r), sp_axis=sp_axis)
+            for r in range(world)]
+    with torch.no_grad():
+        for r in range(world):
+            ctx.as_rank(r)
+            ctx.epoch = 0
+            mods[r].flag_buf.view(torch.int32, (8,)).fill_(1)
+            out = mods[r](ids)
+            assert out.shape == want[r].shape
+    torch.cuda.synchronize()
+    assert native.ops().device_status() == 0
+    for r in range(world):
+        got = ctx.rank_view("vocab_embed_out_0", r, torch.bfloat16, tuple(want[r].shape))
+        assert torch.equal(got, want[r]), f"rank {r}"

@@ -1,6 +1,5 @@
 """Fused TP linears on real peers: 2+ GPUs, NCCL bootstrap, symmetric memory.
 Compared with the gathered fp32 reference, forward and backward."""
-import os
 
 import pytest
 import torch
@@ -94,3 +93,41 @@ def _worker(rank, world, nvls):
 def test_fused_tp_linears_on_peers(world, nvls):
     _need_gpus(world)
     run_distributed(_worker, world, nvls, backend="nccl")
+
+
+def _embed_worker(rank, world, sp_axis):
+    import torch.distributed as dist
+
+    from slapo_b200.ops import native
+    from slapo_b200.ops.embedding import FusedVocabParallelEmbedding
+    from slapo_b200.parallel.symm import SymmContext
+
+    dev = torch.device("cuda", rank)
+    ctx = SymmContext(None, dev, nvls=False)
+    torch.manual_seed(21)
+    vocab, hidden, b, s = 64 * world, 128, 4 * world, 16 * world
+    table = torch.randn(vocab, hidden, device=dev).bfloat16()
+    ids = torch.randint(0, vocab, (b, s), device=dev)
+    g_full = torch.randn(b, s, hidden, device=dev).bfloat16()
+    mod = FusedVocabParallelEmbedding(torch.nn.Parameter(table.chunk(world)[rank].clone()),
+                                      rank * (vocab // world), ctx, sp_axis=sp_axis)
+    for _ in range(2):   # twice: the output buffers alternate
+        mod.weight.grad = None
+        out = mod(ids)
+        want = table[ids] if sp_axis is None else table[ids].chunk(world, dim=sp_axis)[rank]
+        g = g_full if sp_axis is None else g_full.chunk(world, dim=sp_axis)[rank].contiguous()
+        out.backward(g)
+        torch.cuda.synchronize()
+        assert native.ops().device_status() == 0
+        assert torch.equal(out, want)
+        ref = torch.zeros(vocab, hidden, device=dev)
+        ref.index_add_(0, ids.reshape(-1), g_full.reshape(-1, hidden).float())
+        torch.testing.assert_close(mod.weight.grad.float(), ref.chunk(world)[rank], rtol=2e-2,
+                                   atol=2e-2)
+    dist.barrier()
+
+
+@pytest.mark.parametrize("sp_axis", [None, 0, 1])
+def test_vocab_parallel_embedding_on_peers(sp_axis):
+    _need_gpus(2)
+    run_distributed(_embed_worker, 2, sp_axis, backend="nccl")

@@ -320,3 +320,83 @@ def test_dynamo_and_huggingface_tracer_names():
     assert sch3.trace(tracer="dynamo", concrete_args={"x": x})       # the reference's spelling
     torch.testing.assert_close(sch3.mod(x), want)
     assert not slapo.create_schedule(SelfAttn()).trace(tracer="no-such-tracer")
+
+
+def test_checkpoint_of_a_matched_subgraph():
+    """``sch.checkpoint(subgraph)``: the matched chain (dense -> bias add -> relu) becomes its
+    own module under activation checkpointing; outputs and gradients are those of the plain
+    model and the chain's activations are recomputed in backward."""
+    from slapo_b200.primitives.checkpoint import CheckPointWrapper
+
+    torch.manual_seed(0)
+    model = Layer()
+    x = torch.randn(2, 4, 16, requires_grad=True)
+    want = model(x)
+    want.sum().backward()
+    want_grad = x.grad.clone()
+    want_wgrad = model.dense.weight.grad.clone()
+    x.grad = None
+    model.zero_grad()
+
+    sch = slapo.create_schedule(model)
+    sch.trace(flatten=True)
+    sub = sch.find(lambda x: F.relu(call_module("dense", x)))
+    assert len(sub) == 1 and len(sub[0]) == 2
+    sch.checkpoint(sub)
+    wrappers = [m for m in sch.mod.modules() if isinstance(m, CheckPointWrapper)]
+    assert len(wrappers) == 1
+    calls = {"n": 0}
+    wrappers[0].mod.register_forward_hook(lambda *_: calls.__setitem__("n", calls["n"] + 1))
+    built, _ = slapo.build(sch, init_weights=False)
+    got = built(x)
+    torch.testing.assert_close(got, want)
+    assert calls["n"] == 1
+    got.sum().backward()
+    assert calls["n"] == 2            # recomputed once in backward
+    torch.testing.assert_close(x.grad, want_grad)
+    torch.testing.assert_close(model.dense.weight.grad, want_wgrad)
+    with pytest.raises(ValueError, match="exactly one"):
+        sch.checkpoint([sub[0], sub[0]])
+
+
+class ShapeDependent(nn.Module):
+    """Python control flow on tensor shapes: untraceable for plain fx, fine once the proxies
+    carry meta tensors."""
+
+    def __init__(self):
+        super().__init__()
+        self.emb = nn.Embedding(50, 16)
+        self.proj = nn.Linear(16, 16)
+        self.attn = SelfAttn()
+
+    def forward(self, input_ids, attention_mask=None):
+        x = self.emb(input_ids)
+        bsz, seq = input_ids.size()
+        if seq > 4:                         # needs a concrete size
+            x = self.proj(x)
+        if attention_mask is not None:
+            x = x * attention_mask.unsqueeze(-1)
+        x = x.view(bsz, seq, -1)
+        return self.attn(x)
+
+
+def test_huggingface_tracer_propagates_meta_tensors():
+    torch.manual_seed(0)
+    model = ShapeDependent()
+    ids = torch.randint(0, 50, (2, 16))
+    want = model(ids)
+    # the plain engine gives up on the shape-dependent branch and keeps the module eager
+    plain = slapo.create_schedule(ShapeDependent())
+    plain.mod.load_state_dict(model.state_dict())
+    plain.trace(tracer="pytorch")
+    assert not isinstance(plain.mod, fx.GraphModule)
+    # the meta engine resolves it; hierarchy and numerics are preserved
+    sch = slapo.create_schedule(ShapeDependent())
+    sch.mod.load_state_dict(model.state_dict())
+    assert sch.trace(tracer="huggingface", config={"seq_len": 16, "hidden_size": 16})
+    assert isinstance(sch.mod, fx.GraphModule)
+    torch.testing.assert_close(sch.mod(ids), want)
+    assert "attn" in sch.child and isinstance(sch["attn"].mod, fx.GraphModule)
+    shapes = {n.name: n.meta.get("shape") for n in sch.mod.graph.nodes}
+    assert shapes["emb"] == (2, 16, 16) and shapes["input_ids"] == (2, 16)
+    assert [n for n in sch.mod.graph.nodes if n.op == "call_module" and n.target == "proj"]

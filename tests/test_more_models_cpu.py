@@ -51,7 +51,8 @@ def _t5_tp_worker(rank, world, gated):
     loss.backward()
     ffn = lambda m: m.decoder.block[1].layer[2].DenseReluDense.wo.weight.grad  # noqa: E731
     torch.testing.assert_close(ffn(model), ffn(ref).chunk(world, dim=1)[rank], rtol=1e-3, atol=1e-5)
-    tab = lambda m: m.encoder.block[0].layer[0].SelfAttention.relative_attention_bias.weight.grad  # noqa: E731
+    tab = lambda m: (m.encoder.block[0].layer[0].SelfAttention  # noqa: E731
+                     .relative_attention_bias.weight.grad)
     torch.testing.assert_close(tab(model), tab(ref).chunk(world, dim=1)[rank], rtol=1e-3, atol=1e-5)
 
 
@@ -172,3 +173,25 @@ def test_decoder_vocab_shards_stay_16_byte_aligned():
         assert vocab >= 50257
         for tp in (2, 4, 8):
             assert vocab % tp == 0 and (vocab // tp) % 8 == 0, (name, vocab, tp)
+
+
+def test_t5_fused_projections_structure():
+    """Self-attention gets one ``qkv`` projection, cross-attention ``q`` + one ``kv``; the
+    fused weights are the head-interleaved stack of the separate ones."""
+    from slapo_b200.models.t5 import T5FusedAttention
+
+    cfg, ref = _t5(False)
+    sch = slapo.model_schedule.apply_schedule(copy.deepcopy(ref), "t5", model_config=cfg)
+    model, _ = slapo.build(sch, init_weights=False)
+    sa = model.decoder.block[0].layer[0].SelfAttention
+    ca = model.decoder.block[0].layer[1].EncDecAttention
+    assert isinstance(sa, T5FusedAttention) and isinstance(ca, T5FusedAttention)
+    assert not hasattr(sa, "q") and sa.qkv.weight.shape[0] == 3 * cfg.num_heads * cfg.d_kv
+    assert hasattr(ca, "q") and ca.kv.weight.shape[0] == 2 * cfg.num_heads * cfg.d_kv
+    old = ref.decoder.block[0].layer[0].SelfAttention
+    w = sa.qkv.weight.view(cfg.num_heads, 3, cfg.d_kv, -1)
+    torch.testing.assert_close(w[:, 1].reshape(-1, w.shape[-1]), old.k.weight)
+    # and the unfused recipe is still available
+    sch2 = slapo.model_schedule.apply_schedule(copy.deepcopy(ref), "t5", model_config=cfg,
+                                               fuse_qkv=False)
+    assert hasattr(sch2.mod.decoder.block[0].layer[0].SelfAttention, "k")

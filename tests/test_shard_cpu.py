@@ -5,7 +5,6 @@ import copy
 
 import pytest
 import torch
-import torch.distributed as dist
 from torch import nn
 
 import slapo_b200 as slapo

@@ -101,3 +101,31 @@ def test_init_empty_weights():
     with slapo.init_empty_weights(include_buffers=True):
         bn = nn.BatchNorm1d(4)
         assert bn.running_mean.is_meta
+
+
+def test_profile_switch_annotates_modules_and_is_harmless_on_cpu():
+    """``EngineConfig(profile=True)``: NVTX ranges are requested and the scheduled modules get
+    range hooks; without CUDA everything stays a no-op and training is unchanged."""
+    import copy
+
+    import torch
+    from torch import nn
+
+    from slapo_b200.ops.linear import LinearWithSyncFunc
+    from slapo_b200.runtime.engine import TrainEngine
+    from slapo_b200.utils import nvtx
+
+    torch.manual_seed(0)
+    model = nn.Sequential(LinearWithSyncFunc(8, 8), nn.ReLU(), nn.Linear(8, 1))
+    plain = TrainEngine(copy.deepcopy(model), config={"lr": 1e-2})
+    prof = TrainEngine(model, config={"lr": 1e-2, "profile": True})
+    assert getattr(model[0], "_slapo_nvtx", False) and not getattr(model[2], "_slapo_nvtx", False)
+    assert nvtx.annotate_modules(model) == 0          # idempotent
+    x = torch.randn(4, 8)
+    a = plain.train_batch(x)
+    b = prof.train_batch(x)
+    torch.testing.assert_close(a, b)
+    assert prof.phase_times() == {}                   # device timing needs CUDA
+    with nvtx.range("anything"):
+        pass
+    nvtx.enable(False)
