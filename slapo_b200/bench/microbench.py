@@ -15,7 +15,6 @@ import json
 import os
 
 import torch
-import torch.nn.functional as F
 
 from ..ops import functional as NF
 from ..ops import native
@@ -123,9 +122,13 @@ def bench_gemm(small, iters):
     for (m, n, k) in shapes:
         a = torch.randn(m, k, device="cuda", dtype=torch.bfloat16)
         b = torch.randn(n, k, device="cuda", dtype=torch.bfloat16)
-        t1 = timeit(lambda: native.ops().gemm(a, b, None, -1, False, False), iters)
-        t2 = timeit(lambda: F.linear(a, b), iters)
-        report("gemm_tc05", t1, flops=2 * m * n * k, shape=[m, n, k])
+        out = torch.empty(m, n, device="cuda", dtype=torch.bfloat16)
+        ops = native.ops()
+        t0 = timeit(lambda: ops.gemm_out(a, b, None, -1, False, False, out, None, 2, False), iters)
+        t1 = timeit(lambda: ops.gemm_out(a, b, None, -1, False, False, out, None, 1, False), iters)
+        t2 = timeit(lambda: torch.matmul(a, b.t(), out=out), iters)
+        report("gemm2_tc05 (CTA pairs)", t0, flops=2 * m * n * k, shape=[m, n, k])
+        report("gemm_tc05 (single CTA)", t1, flops=2 * m * n * k, shape=[m, n, k])
         report("gemm_cublas", t2, flops=2 * m * n * k, shape=[m, n, k])
 
 
@@ -167,9 +170,109 @@ def bench_comm(small, iters):
            shape=[ts * world, k, n], world=world)
 
 
+def bench_peer(small, iters):
+    """The other peer-memory kernels as ONE emulated rank of a 4-rank group on this GPU (peer
+    buffers are local memory, the peers' flags are preset): data-parallel gradient
+    reduce-scatter, AdamW + parameter all-gather, the reshard all-to-all, the vocabulary-
+    parallel embedding (both forms), the plain peer gather and the GEMM -> all-reduce.  Every
+    kernel runs its full code path; no byte crosses NVLink, so the figures describe the memory
+    side only (the real-NVLink times come from `comm_bench` on several GPUs)."""
+    from slapo_b200.ops.embedding import FusedVocabParallelEmbedding
+    from slapo_b200.parallel import fused_tp as ft
+    from slapo_b200.parallel.fused_a2a import FusedAllToAll
+    from slapo_b200.parallel.fused_dp import FusedDP
+    from slapo_b200.parallel.symm import LocalSymmContext
+
+    world, dev, dt = 4, torch.device("cuda"), torch.bfloat16
+    ctx = LocalSymmContext(world, wait_seconds=0.05)
+    # ---- data parallel: one bucket of 64 MiB (16 MiB for captures)
+    elems = (8 if small else 32) * 2**20
+    shard = elems // world
+    fdps = [FusedDP(ctx.as_rank(r), elems, dt, 1, wait_seconds=0.05) for r in range(world)]
+    for f in fdps:
+        f.flat_grad.normal_()
+        f.flat_param.normal_()
+    out = torch.empty(shard, device=dev, dtype=dt)
+    state = {"epoch": 0}
+
+    def rs():
+        state["epoch"] += 1
+        for f in fdps:
+            f.flags.fill_(state["epoch"])
+        fdps[0].grad_rs(0, state["epoch"], 0, out, None)
+
+    report("dp_grad_rs_emulated", timeit(rs, iters), nbytes=(world + 1) * shard * 2,
+           elems=elems, world=world)
+    master = torch.randn(shard, device=dev)
+    m, v = torch.zeros(shard, device=dev), torch.zeros(shard, device=dev)
+    decay = torch.ones(shard, dtype=torch.uint8, device=dev)
+    coef = torch.ones(1, device=dev)
+
+    def ag():
+        state["epoch"] += 1
+        for f in fdps:
+            f.flags.fill_(state["epoch"])
+        fdps[0].adamw_ag(state["epoch"], True, 0, out, master, m, v, decay, coef, 1e-4, (0.9, 0.999),
+                         1e-8, 0.01, 0.1, 0.001)
+
+    report("dp_adamw_ag_emulated", timeit(ag, iters),
+           nbytes=shard * (2 + 3 * 8 + 1) + world * shard * 2, elems=elems, world=world)
+    # ---- reshard all-to-all: [B, S, H / world] -> [B, S / world, H]
+    b, s_len, h = (8, 512, 1024) if small else (32, 512, 1024)
+    inp = torch.randn(b, s_len, h // world, device=dev, dtype=dt)
+    a2a = FusedAllToAll(ctx.as_rank(0), wait_seconds=0.05)
+
+    def a2a_fn():
+        a2a.flag_buf.view(torch.int32, (8,)).fill_(ctx.epoch + 1)
+        return a2a.push(inp, -2, -1)
+
+    report("peer_all_to_all_emulated", timeit(a2a_fn, iters), nbytes=2 * inp.numel() * 2,
+           shape=list(inp.shape), world=world)
+    # ---- vocabulary-parallel embedding, all-gather and scatter forms
+    vocab, hidden = 30528, 1024
+    ids = torch.randint(0, vocab // world, (b, s_len), device=dev)   # every row owned by rank 0
+    for sp_axis, label in ((None, "all_gather"), (0, "scatter")):
+        emb = FusedVocabParallelEmbedding(
+            torch.nn.Parameter(torch.randn(vocab // world, hidden, device=dev, dtype=dt)), 0,
+            ctx.as_rank(0), sp_axis=sp_axis)
+
+        def embed():
+            emb.flag_buf.view(torch.int32, (8,)).fill_(ctx.epoch + 1)
+            with torch.no_grad():
+                return emb(ids)
+
+        stores = world if sp_axis is None else 1
+        report(f"vocab_embed_fwd_emulated[{label}]", timeit(embed, iters),
+               nbytes=ids.numel() * hidden * 2 * (1 + stores), tokens=ids.numel(), world=world)
+    # ---- plain peer gather of a [ts, k] shard
+    ts, k = (2048, 1024) if small else (8192, 1024)
+    shard_t = torch.randn(ts, k, device=dev, dtype=dt)
+
+    def gather():
+        ctx.preset_flags(ctx.epoch + 1)
+        return ft.peer_gather(ctx, shard_t, "gather_bench")
+
+    report("peer_gather_emulated", timeit(gather, iters), nbytes=2 * world * ts * k * 2,
+           shape=[world * ts, k], world=world)
+    # ---- GEMM -> all-reduce
+    n = 1024
+    x = torch.randn(ts * world, k, device=dev, dtype=dt)
+    w = torch.randn(n, k, device=dev, dtype=dt)
+    ctx.buffer("ar_recv", ft.RECV_HEADER_BYTES + ts * world * n * 2)
+
+    def ar():
+        ctx.preset_flags(ctx.epoch + 1, ready=True, done=True, done2=True)
+        ctx.preset_block_flags("ar_recv", ctx.epoch + 1, ts // 128)
+        return ft.gemm_ar(ctx, x, w, None)
+
+    report("gemm_ar_emulated", timeit(ar, iters), flops=2 * ts * world * n * k,
+           shape=[ts * world, n, k], world=world)
+
+
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--op", default="all", choices=["all", "ln", "gelu", "attn", "gemm", "comm"])
+    ap.add_argument("--op", default="all",
+                    choices=["all", "ln", "gelu", "attn", "gemm", "comm", "peer"])
     ap.add_argument("--small", action="store_true", help="small inputs for profiler captures")
     ap.add_argument("--iters", type=int, default=20)
     args = ap.parse_args()
@@ -177,7 +280,7 @@ def main():
     todo = ["ln", "gelu", "attn", "gemm"] if args.op == "all" else [args.op]
     for op in todo:
         {"ln": bench_ln, "gelu": bench_gelu, "attn": bench_attn, "gemm": bench_gemm,
-         "comm": bench_comm}[op](
+         "comm": bench_comm, "peer": bench_peer}[op](
             args.small, args.iters)
     print(json.dumps({"device_status": int(native.ops().device_status())}))
 

@@ -25,13 +25,15 @@ void comm_gemm(std::vector<int64_t> a_ptrs, std::vector<int64_t> b_ptrs, int64_t
                int64_t epoch, int64_t out_ptr, int64_t ldo, int64_t bias_ptr, int64_t act,
                int64_t flags_ptr, std::vector<int64_t> peer_flags, std::vector<int64_t> peer_recv,
                std::vector<int64_t> peer_out, double wait_seconds, int64_t stage_ptr,
-               int64_t chunk_flags_ptr, int64_t recv_mc, int64_t out_mc) {
+               int64_t chunk_flags_ptr, int64_t recv_mc, int64_t out_mc,
+               std::vector<int64_t> stage_peers, int64_t stage_mc) {
   TORCH_CHECK(!a_ptrs.empty() && !b_ptrs.empty(), "comm_gemm: operand pointers missing");
   auto a = to_ptrs<void*>(a_ptrs);
   auto b = to_ptrs<void*>(b_ptrs);
   auto pf = to_ptrs<int*>(peer_flags);
   auto pr = to_ptrs<void*>(peer_recv);
   auto po = to_ptrs<void*>(peer_out);
+  auto sp = to_ptrs<void*>(stage_peers);
   const int dev = at::cuda::current_device();
   int rc = slapo::launch_comm_gemm(
       a.data(), b.data(), static_cast<int>(M), static_cast<int>(N), static_cast<int>(K),
@@ -43,7 +45,8 @@ void comm_gemm(std::vector<int64_t> a_ptrs, std::vector<int64_t> b_ptrs, int64_t
       peer_recv.empty() ? nullptr : pr.data(), peer_out.empty() ? nullptr : po.data(),
       slapo_status_ptr(dev), wait_seconds, reinterpret_cast<void*>(stage_ptr),
       reinterpret_cast<int*>(chunk_flags_ptr), reinterpret_cast<void*>(recv_mc),
-      reinterpret_cast<void*>(out_mc), at::cuda::getCurrentCUDAStream().stream());
+      reinterpret_cast<void*>(out_mc), stage_peers.empty() ? nullptr : sp.data(),
+      reinterpret_cast<void*>(stage_mc), at::cuda::getCurrentCUDAStream().stream());
   TORCH_CHECK(rc == 0, "comm_gemm: launch refused (code ", rc,
               "): check divisibility by the group size / 128-row blocks and 16-byte alignment");
 }
@@ -183,7 +186,8 @@ void register_comm_ops(torch::Library& m) {
         "bool b_mn, bool bf16, int gather, int seg_len, int mode, int world, int rank, int epoch, "
         "int out_ptr, int ldo, int bias_ptr, int act, int flags_ptr, int[] peer_flags, "
         "int[] peer_recv, int[] peer_out, float wait_seconds, int stage_ptr, "
-        "int chunk_flags_ptr, int recv_mc, int out_mc) -> ()", &comm_gemm);
+        "int chunk_flags_ptr, int recv_mc, int out_mc, int[] stage_peers, int stage_mc) -> ()",
+        &comm_gemm);
   m.def("comm_trace() -> Tensor", &comm_trace);
   m.def("peer_gather(int[] src_ptrs, int dst_ptr, int seg_bytes, int world, int rank, int epoch, "
         "int flags_ptr, int[] peer_flags, float wait_seconds) -> ()", &peer_gather);

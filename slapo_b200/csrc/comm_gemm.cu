@@ -122,6 +122,12 @@ struct CommGemmParams {
   int* mc_blk_flags;
   void* mc_recv;
   void* mc_out;
+  // gather mode 5 (rows of A pushed by their owners): every rank's staging slot [M, K] and the
+  // block flags in the slot's header; `mc_stage` is the slots of all ranks behind one
+  // multicast address (null: one store per rank)
+  void* peer_stage[kMaxRanks];
+  int* peer_chunk_flags[kMaxRanks];
+  void* mc_stage;
 };
 
 __device__ __forceinline__ void st_release_sys(int* addr, int v) {
@@ -612,6 +618,37 @@ __device__ __forceinline__ void copy_vecs(const uint4* src, uint4* dst, int64_t 
   }
 }
 
+// One warp pushes n_vec 16-byte vectors of this rank's shard into the staging slots of all
+// ranks at byte offset dst_off: through the switch (one multicast store) or rank by rank.
+// F local loads are in flight per lane; the stores need no answer.
+template <int F>
+__device__ __forceinline__ void push_vecs(const CommGemmParams& p, const uint4* src,
+                                          int64_t dst_off, int n_vec, int lane) {
+  for (int v = lane; v < n_vec; v += 32 * F) {
+    uint4 tmp[F];
+#pragma unroll
+    for (int q = 0; q < F; ++q)
+      if (v + q * 32 < n_vec) tmp[q] = __ldcg(src + v + q * 32);
+    if (p.mc_stage != nullptr) {
+#pragma unroll
+      for (int q = 0; q < F; ++q)
+        if (v + q * 32 < n_vec)
+          mc_st(static_cast<uint8_t*>(p.mc_stage) + dst_off + static_cast<int64_t>(v + q * 32) * 16,
+                tmp[q]);
+    } else {
+      for (int rr = 0; rr < p.world; ++rr) {
+        int r = p.rank + 1 + rr;             // the other ranks first, this rank's own slot last
+        if (r >= p.world) r -= p.world;
+        uint8_t* dst = static_cast<uint8_t*>(p.peer_stage[r]) + dst_off;
+#pragma unroll
+        for (int q = 0; q < F; ++q)
+          if (v + q * 32 < n_vec)
+            *reinterpret_cast<uint4*>(dst + static_cast<int64_t>(v + q * 32) * 16) = tmp[q];
+      }
+    }
+  }
+}
+
 // CW: warps 6 .. 5 + CW are the copier (staged gather, CW = 8) or reducer (scatter modes, CW = 4)
 // warps; kernels without either are launched with the first six warps only.
 template <int BN, int STAGES, bool A_MN, bool B_MN, int CW>
@@ -644,7 +681,8 @@ comm_gemm_kernel(const __grid_constant__ SegMaps maps_a, const __grid_constant__
   const long long mbar_budget = p.wait_cycles + tc::kWaitCycles;
   const bool scatter = p.mode != kModeLocal;
   const int rows_per_rank = p.M / p.world;               // used when rows are owned (gather 1 / scatter)
-  const bool staged = p.gather == 4;
+  const bool pushed = p.gather == 5;
+  const bool staged = p.gather == 4 || pushed;
   const int first = staged ? 0 : 1;
   const bool rotate = p.world > 1 && (scatter || p.gather == 1 || staged) && rows_per_rank % CBM == 0;
   const int blocks_per_owner = rotate ? rows_per_rank / CBM : tiles_m;
@@ -807,7 +845,55 @@ comm_gemm_kernel(const __grid_constant__ SegMaps maps_a, const __grid_constant__
     // the local staging buffer (16-byte coalesced loads, 8 in flight per
     // thread) and published block by block; the producer warps of all CTAs
     // read staged blocks with local TMA loads.
-    if (staged && p.world > 1) {
+    if (pushed && p.world > 1) {
+      // Pushed gather: every copier warp of every rank is an independent sender.  It takes
+      // slices of this rank's OWN shard (local loads), stores them into the staging slots of
+      // all ranks - one multicast store through the switch, or one store per rank - and
+      // counts the slice in; whoever completes a 128-row block publishes its flag on every
+      // rank.  Stores need no answer, so nothing waits for an NVLink round trip except the
+      // fence in front of the count, and that wait is per warp: the other warps keep sending.
+      // Slices are handed out in row order across the SMs, so blocks complete in order and
+      // the main loops of all ranks start on block 0 of every owner while the rest is in flight.
+      const int cw = warp - 6;
+      const int slices = p.ag_slices;
+      const int slice_rows = CBM / slices;
+      int* chunk_count = p.chunk_flags + kChunkCountOffset;
+      const int slice_vec = slice_rows * (p.row_bytes / 16);
+      // Nobody's slot may be written before its owner has entered this operation: its earlier
+      // kernels, which read the slot's previous contents, are complete by then.
+      int entered = 1;
+      if (lane < p.world && lane != p.rank)
+        entered = wait_flag(ready + lane, p.epoch, p.wait_cycles, abort_flag) ? 1 : 0;
+      const bool ok = __all_sync(0xffffffffu, entered) != 0;
+      const int n_copiers = static_cast<int>(gridDim.x) * CW;
+      const int units = blocks_per_owner * slices;
+      if (cw == 0 && lane == 0) trace_mark(p.trace, 1);
+      for (int u = cw * static_cast<int>(gridDim.x) + static_cast<int>(blockIdx.x);
+           u < units && ok; u += n_copiers) {
+        const int b = u / slices, sl = u - b * slices;
+        const int64_t off = (static_cast<int64_t>(b) * CBM + sl * slice_rows) * p.row_bytes;
+        const int m_blk = p.rank * blocks_per_owner + b;
+        SLAPO_DBG_CHECK(off + static_cast<int64_t>(slice_rows) * p.row_bytes <=
+                                static_cast<int64_t>(p.seg_len) * p.row_bytes &&
+                            m_blk < kChunkCountOffset && (off & 15) == 0,
+                        p.status)
+        const uint4* src = reinterpret_cast<const uint4*>(
+            static_cast<const uint8_t*>(p.seg_src[p.rank]) + off);
+        const int64_t dst_off = static_cast<int64_t>(p.rank) * p.seg_len * p.row_bytes + off;
+        if (p.ag_inflight == 16) push_vecs<16>(p, src, dst_off, slice_vec, lane);
+        else push_vecs<8>(p, src, dst_off, slice_vec, lane);
+        __threadfence_system();
+        __syncwarp();
+        if (lane == 0) {
+          const int prev = slices > 1 ? atomicAdd(chunk_count + m_blk, 1) : 0;
+          if (prev + 1 == slices) {
+            if (slices > 1) atomicExch(chunk_count + m_blk, 0);
+            for (int r = 0; r < p.world; ++r) st_release_sys(p.peer_chunk_flags[r] + m_blk, p.epoch);
+          }
+        }
+      }
+      if (cw == CW - 1 && lane == 0) trace_mark(p.trace, 2);
+    } else if (staged && p.world > 1) {
       const int ct = threadIdx.x - 192;
       // A 128-row block is copied as `slices` slices by (usually) different CTAs, units in
       // (block, slice) order, so that the first blocks are complete after a few NVLink round
@@ -918,6 +1004,7 @@ comm_gemm_kernel(const __grid_constant__ SegMaps maps_a, const __grid_constant__
       }
       if (!tc::mbar_wait_warp(&tmem_full[acc], acc_phase, abort_flag, mbar_budget)) { ok = false; break; }
       tc::fence_after_sync();
+      const bool wide_store = dst_ld % 16 == 0 && (reinterpret_cast<uintptr_t>(dst_base) & 31) == 0;
       const int row = m0 + quarter * 32 + lane;
       const uint32_t t_row = tmem_base + acc * BN + (static_cast<uint32_t>(quarter * 32) << 16);
 #pragma unroll 1
@@ -946,11 +1033,23 @@ comm_gemm_kernel(const __grid_constant__ SegMaps maps_a, const __grid_constant__
             packed[j] = cpack2(v0, v1, p.bf16);
           }
           uint8_t* dst = dst_base + (static_cast<int64_t>(row - row_off) * dst_ld + col0) * 2;
+          if (wide_store && col0 + 32 <= p.N) {
+            // whole 32-byte sectors per store: a 16-byte store makes L2 merge two partial writes
 #pragma unroll
-          for (int v = 0; v < 4; ++v) {
-            if (col0 + v * 8 < p.N)
-              *reinterpret_cast<uint4*>(dst + v * 16) =
-                  make_uint4(packed[4 * v], packed[4 * v + 1], packed[4 * v + 2], packed[4 * v + 3]);
+            for (int v = 0; v < 2; ++v)
+              asm volatile("st.global.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"l"(
+                               dst + v * 32),
+                           "r"(packed[8 * v]), "r"(packed[8 * v + 1]), "r"(packed[8 * v + 2]),
+                           "r"(packed[8 * v + 3]), "r"(packed[8 * v + 4]), "r"(packed[8 * v + 5]),
+                           "r"(packed[8 * v + 6]), "r"(packed[8 * v + 7])
+                           : "memory");
+          } else {
+#pragma unroll
+            for (int v = 0; v < 4; ++v) {
+              if (col0 + v * 8 < p.N)
+                *reinterpret_cast<uint4*>(dst + v * 16) = make_uint4(
+                    packed[4 * v], packed[4 * v + 1], packed[4 * v + 2], packed[4 * v + 3]);
+            }
           }
         }
       }
@@ -1117,7 +1216,7 @@ static int launch_comm_variant(const SegMaps& ma, const SegMaps& mb, const CommG
     }();
     if (p.gather == 4 && wide)
       return launch_comm_kernel<BN, STAGES, A_MN, B_MN, 8>(ma, mb, p, grid, 192 + 8 * 32, stream);
-    if (p.gather == 4)
+    if (p.gather == 4 || p.gather == 5)
       return launch_comm_kernel<BN, STAGES, A_MN, B_MN, 4>(ma, mb, p, grid, 320, stream);
   }
   // scatter modes: four reducer warps; otherwise the six warps of the plain pipeline
@@ -1143,6 +1242,25 @@ static CopyTuning copy_tuning() {
   return t;
 }
 
+// The pushed gather's tuning, SLAPO_B200_AG_PUSH="slices,inflight": slices per 128-row block
+// (1 .. 32, a power of two - one slice is one warp's unit of work) and 16-byte loads in flight
+// per lane (8 or 16).
+static CopyTuning push_tuning() {
+  static const CopyTuning t = [] {
+    CopyTuning v{16, 16};
+    if (const char* e = std::getenv("SLAPO_B200_AG_PUSH")) {
+      int a = 0, b = 0;
+      if (std::sscanf(e, "%d,%d", &a, &b) == 2 && a >= 1 && a <= 32 && (a & (a - 1)) == 0 &&
+          (b == 8 || b == 16)) {
+        v.slices = a;
+        v.inflight = b;
+      }
+    }
+    return v;
+  }();
+  return t;
+}
+
 // Copies the phase trace of the last fused kernel ([kTraceCtas][kTraceSlots] 64-bit words) to the host.
 int read_comm_trace(unsigned long long* host, int n_words) {
   const int n = n_words < kTraceCtas * kTraceSlots ? n_words : kTraceCtas * kTraceSlots;
@@ -1156,10 +1274,22 @@ int launch_comm_gemm(void* const* a_ptrs, void* const* b_ptrs, int M, int N, int
                      int world, int rank, int epoch, void* out, int ldo, const void* bias, int act,
                      int* flags, int* const* peer_flags, void* const* peer_recv,
                      void* const* peer_out, int* status, double wait_seconds, void* stage_dst,
-                     int* chunk_flags, void* recv_mc, void* out_mc, cudaStream_t stream) {
+                     int* chunk_flags, void* recv_mc, void* out_mc, void* const* stage_peers,
+                     void* stage_mc, cudaStream_t stream) {
   if (M <= 0 || N <= 0 || K <= 0) return 0;
-  if ((gather == 4 || mode != kModeLocal) && (M + CBM - 1) / CBM > kChunkCountOffset) return 6;
-  if (gather == 4 && mode != kModeLocal) return 1;   // warps 6-9 have one job per launch
+  if ((gather == 4 || gather == 5 || mode != kModeLocal) && (M + CBM - 1) / CBM > kChunkCountOffset)
+    return 6;
+  if ((gather == 4 || gather == 5) && mode != kModeLocal) return 1;   // warps 6-9 have one job per launch
+  if (gather == 5) {
+    // pushed gather: every rank's staging slot = kRecvHeaderBytes of block flags and slice
+    // counters (zero when allocated, flags only grow), then the gathered operand [M, K]
+    if (a_mn || stage_peers == nullptr || lda != K || seg_len % CBM != 0 || seg_len * world != M)
+      return 1;
+    for (int r = 0; r < world; ++r)
+      if (stage_peers[r] == nullptr || (reinterpret_cast<uintptr_t>(stage_peers[r]) & 15)) return 1;
+    stage_dst = static_cast<uint8_t*>(stage_peers[rank]) + kRecvHeaderBytes;
+    chunk_flags = reinterpret_cast<int*>(stage_peers[rank]);
+  }
   if (mode != kModeLocal && peer_recv == nullptr) return 1;
   if (gather == 4 && (a_mn || stage_dst == nullptr || chunk_flags == nullptr || lda != K ||
                       seg_len % CBM != 0 || seg_len * world != M))
@@ -1174,13 +1304,13 @@ int launch_comm_gemm(void* const* a_ptrs, void* const* b_ptrs, int M, int N, int
   SegMaps ma, mb;
   const int a_segs = (gather == 1 || gather == 2) ? world : 1;
   const int b_segs = gather == 3 ? world : 1;
-  if (gather == 4) {
+  if (gather == 4 || gather == 5) {
     // map 0: this rank's shard in place; map 1: the local staging buffer [M, K]
     if (!make_tmap_2d(&ma.map[0], a_ptrs[rank], K, seg_len, lda, 64, CBM, 2, bf16) ||
         !make_tmap_2d(&ma.map[1], stage_dst, K, M, lda, 64, CBM, 2, bf16))
       return 2;
   }
-  for (int s = 0; s < a_segs && gather != 4; ++s) {
+  for (int s = 0; s < a_segs && gather != 4 && gather != 5; ++s) {
     // extents of one segment
     const uint64_t rows = gather == 1 ? seg_len : M;
     const uint64_t kk = gather == 2 ? seg_len : K;
@@ -1201,15 +1331,21 @@ int launch_comm_gemm(void* const* a_ptrs, void* const* b_ptrs, int M, int N, int
   p.idesc = tc::instr_desc_f16(CBM, BN, bf16 ? 1 : 0, a_mn, b_mn);
   p.wait_cycles = static_cast<long long>(wait_seconds * 1.9e9);
   p.stage_dst = stage_dst; p.chunk_flags = chunk_flags; p.row_bytes = K * 2;
-  const CopyTuning tune = copy_tuning();
+  const CopyTuning tune = gather == 5 ? push_tuning() : copy_tuning();
   p.ag_slices = tune.slices; p.ag_inflight = tune.inflight;
+  // a slice is whole rows of 16-byte vectors
+  if (gather == 5 && (K * 2) % 16 != 0) return 1;
   static const bool trace_on = [] {
     const char* e = std::getenv("SLAPO_B200_COMM_TRACE");
     return e != nullptr && e[0] == '1';
   }();
   p.trace = trace_on ? 1 : 0;
   for (int r = 0; r < world; ++r) {
-    p.seg_src[r] = gather == 4 ? a_ptrs[r] : nullptr;
+    p.seg_src[r] = gather == 4 || (gather == 5 && r == rank) ? a_ptrs[r] : nullptr;
+    if (gather == 5) {
+      p.peer_chunk_flags[r] = reinterpret_cast<int*>(stage_peers[r]);
+      p.peer_stage[r] = static_cast<uint8_t*>(stage_peers[r]) + kRecvHeaderBytes;
+    }
     p.peer_flags[r] = peer_flags != nullptr ? peer_flags[r] : flags;
     // a partial-product buffer starts with kRecvHeaderBytes of block flags (written by the
     // peers) and arrival counters (local), zero when the buffer was allocated
@@ -1223,6 +1359,8 @@ int launch_comm_gemm(void* const* a_ptrs, void* const* b_ptrs, int M, int N, int
     p.mc_recv = static_cast<uint8_t*>(recv_mc) + kRecvHeaderBytes;
     p.mc_out = mode == kModeAllReduce ? out_mc : nullptr;
   }
+  if (gather == 5 && stage_mc != nullptr && world > 1)
+    p.mc_stage = static_cast<uint8_t*>(stage_mc) + kRecvHeaderBytes;
   p.blk_flags = p.peer_blk_flags[rank];
   p.blk_counters = p.blk_flags != nullptr ? p.blk_flags + kChunkCountOffset : nullptr;
 

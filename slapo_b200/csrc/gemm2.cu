@@ -46,11 +46,20 @@ constexpr int kEpiWarps = 8;   // epilogue warps per CTA: two per quarter of the
                                // each taking half of the tile's columns
 constexpr int PBM = 128;   // rows of A per CTA (the pair's tile has 256)
 constexpr int PBK = 64;
+#ifndef SLAPO_GEMM2_KSUB
+#define SLAPO_GEMM2_KSUB 2
+#endif
+constexpr int kKSub = SLAPO_GEMM2_KSUB;   // k-blocks of 64 per pipeline stage
 
-template <int BN, int STAGES>
+// A pipeline stage holds KSUB k-blocks of 64 (each its own 128-byte-swizzled sub-tile): with
+// KSUB = 2 the producer / MMA hand-off (barrier wait, two commits) happens once per 128 of K
+// instead of once per 64.
+template <int BN, int STAGES, int KSUB>
 struct Gemm2Smem {
-  static constexpr int kABytes = PBM * PBK * 2;
-  static constexpr int kBBytes = (BN / 2) * PBK * 2;
+  static constexpr int kASub = PBM * PBK * 2;
+  static constexpr int kBSub = (BN / 2) * PBK * 2;
+  static constexpr int kABytes = KSUB * kASub;
+  static constexpr int kBBytes = KSUB * kBSub;
   static constexpr int kBarOffset = STAGES * (kABytes + kBBytes);
   static constexpr int kTotal = kBarOffset + 256 + 1024;
 };
@@ -137,11 +146,11 @@ __device__ __forceinline__ void g2_finish_store(const Gemm2Params& p, const floa
   }
 }
 
-template <int BN, int STAGES, bool A_MN, bool B_MN>
+template <int BN, int STAGES, int KSUB, bool A_MN, bool B_MN>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(64 + 32 * kEpiWarps, 1)
 gemm2_tc05_kernel(const __grid_constant__ CUtensorMap tmap_a,
                   const __grid_constant__ CUtensorMap tmap_b, const Gemm2Params p) {
-  using S = Gemm2Smem<BN, STAGES>;
+  using S = Gemm2Smem<BN, STAGES, KSUB>;
   constexpr int HBN = BN / 2;   // rows of B per CTA
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>(
@@ -201,25 +210,30 @@ gemm2_tc05_kernel(const __grid_constant__ CUtensorMap tmap_a,
         const int n0 = (tile % tiles_n) * BN + static_cast<int>(cta) * HBN;
         const int kb0 = sp * p.kb_per_split;
         const int kb1 = min(num_kb, kb0 + p.kb_per_split);
-        for (int kb = kb0; kb < kb1; ++kb) {
+        for (int kb = kb0; kb < kb1; kb += KSUB) {
           if (!tc::mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag)) { ok = false; break; }
           const uint32_t bar = tc::map_to_cta(tc::smem_u32(&full_bar[stage]), 0);
           tc::mbar_arrive_expect_tx_cluster(bar, S::kABytes + S::kBBytes);
-          const uint32_t sa = tc::smem_u32(smem_a + stage * S::kABytes);
-          const uint32_t sb = tc::smem_u32(smem_b + stage * S::kBBytes);
-          if constexpr (!A_MN) {
-            tc::tma_load_2d_pair(sa, &tmap_a, bar, kb * PBK, m0);
-          } else {
 #pragma unroll
-            for (int j = 0; j < PBM / 64; ++j)
-              tc::tma_load_2d_pair(sa + j * (PBK * 128), &tmap_a, bar, m0 + j * 64, kb * PBK);
-          }
-          if constexpr (!B_MN) {
-            tc::tma_load_2d_pair(sb, &tmap_b, bar, kb * PBK, n0);
-          } else {
+          for (int s = 0; s < KSUB; ++s) {
+            // a k-block beyond K (last stage of an odd count) is zero-filled by the tile load
+            const int kc = (kb + s) * PBK;
+            const uint32_t sa = tc::smem_u32(smem_a + stage * S::kABytes + s * S::kASub);
+            const uint32_t sb = tc::smem_u32(smem_b + stage * S::kBBytes + s * S::kBSub);
+            if constexpr (!A_MN) {
+              tc::tma_load_2d_pair(sa, &tmap_a, bar, kc, m0);
+            } else {
 #pragma unroll
-            for (int j = 0; j < HBN / 64; ++j)
-              tc::tma_load_2d_pair(sb + j * (PBK * 128), &tmap_b, bar, n0 + j * 64, kb * PBK);
+              for (int j = 0; j < PBM / 64; ++j)
+                tc::tma_load_2d_pair(sa + j * (PBK * 128), &tmap_a, bar, m0 + j * 64, kc);
+            }
+            if constexpr (!B_MN) {
+              tc::tma_load_2d_pair(sb, &tmap_b, bar, kc, n0);
+            } else {
+#pragma unroll
+              for (int j = 0; j < HBN / 64; ++j)
+                tc::tma_load_2d_pair(sb + j * (PBK * 128), &tmap_b, bar, n0 + j * 64, kc);
+            }
           }
           if (++stage == STAGES) { stage = 0; phase ^= 1; }
         }
@@ -241,18 +255,22 @@ gemm2_tc05_kernel(const __grid_constant__ CUtensorMap tmap_a,
         if (!tc::mbar_wait(&tmem_empty[acc], acc_phase ^ 1, abort_flag)) { ok = false; break; }
         tc::fence_after_sync();
         const uint32_t d_tmem = tmem_base + acc * BN;
-        for (int kb = kb0; kb < kb1; ++kb) {
+        for (int kb = kb0; kb < kb1; kb += KSUB) {
           if (!tc::mbar_wait(&full_bar[stage], phase, abort_flag)) { ok = false; break; }
           tc::fence_after_sync();
-          const uint32_t a_addr = tc::smem_u32(smem_a + stage * S::kABytes);
-          const uint32_t b_addr = tc::smem_u32(smem_b + stage * S::kBBytes);
 #pragma unroll
-          for (int k = 0; k < PBK / 16; ++k) {
-            const uint64_t a_desc = A_MN ? tc::smem_desc(a_addr + k * 2048, PBK * 128, 1024)
-                                         : tc::smem_desc(a_addr + k * 32, 16, 1024);
-            const uint64_t b_desc = B_MN ? tc::smem_desc(b_addr + k * 2048, PBK * 128, 1024)
-                                         : tc::smem_desc(b_addr + k * 32, 16, 1024);
-            tc::umma_f16_pair(d_tmem, a_desc, b_desc, p.idesc, (kb > kb0 || k != 0) ? 1u : 0u);
+          for (int s = 0; s < KSUB; ++s) {
+            const uint32_t a_addr = tc::smem_u32(smem_a + stage * S::kABytes + s * S::kASub);
+            const uint32_t b_addr = tc::smem_u32(smem_b + stage * S::kBBytes + s * S::kBSub);
+#pragma unroll
+            for (int k = 0; k < PBK / 16; ++k) {
+              const uint64_t a_desc = A_MN ? tc::smem_desc(a_addr + k * 2048, PBK * 128, 1024)
+                                           : tc::smem_desc(a_addr + k * 32, 16, 1024);
+              const uint64_t b_desc = B_MN ? tc::smem_desc(b_addr + k * 2048, PBK * 128, 1024)
+                                           : tc::smem_desc(b_addr + k * 32, 16, 1024);
+              tc::umma_f16_pair(d_tmem, a_desc, b_desc, p.idesc,
+                                (kb > kb0 || s != 0 || k != 0) ? 1u : 0u);
+            }
           }
           // the stage is reusable in both CTAs once these MMAs retire
           const uint32_t eb = tc::smem_u32(&empty_bar[stage]);
@@ -395,11 +413,11 @@ __global__ void __launch_bounds__(256) splitk_reduce_kernel(const Gemm2Params p)
 bool cached_tmap_2d(CUtensorMap* out, const void* base, uint64_t inner, uint64_t outer,
                     uint64_t stride, uint32_t box_outer, bool bf16);
 
-template <int BN, int STAGES, bool A_MN, bool B_MN>
+template <int BN, int STAGES, int KSUB, bool A_MN, bool B_MN>
 static int launch_pair_variant(const CUtensorMap& ta, const CUtensorMap& tb, const Gemm2Params& p,
                                cudaStream_t stream) {
-  using S = Gemm2Smem<BN, STAGES>;
-  auto kernel = gemm2_tc05_kernel<BN, STAGES, A_MN, B_MN>;
+  using S = Gemm2Smem<BN, STAGES, KSUB>;
+  auto kernel = gemm2_tc05_kernel<BN, STAGES, KSUB, A_MN, B_MN>;
   static bool configured = false;
   if (!configured) {
     if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, S::kTotal) !=
@@ -468,17 +486,20 @@ int launch_gemm2(const void* A, const void* B, void* C, void* C2, const void* bi
 
   const int num_kb = (K + PBK - 1) / PBK;
   p.kb_per_split = (num_kb + p.splits - 1) / p.splits;
+  p.kb_per_split = (p.kb_per_split + kKSub - 1) / kKSub * kKSub;   // whole pipeline stages
+  p.splits = (num_kb + p.kb_per_split - 1) / p.kb_per_split;
   p.workspace = workspace;
 
-#define GEMM2_CASE(BN_, ST_)                                                                   \
-  if (BN == BN_) {                                                                             \
-    if (!a_mn && !b_mn) return launch_pair_variant<BN_, ST_, false, false>(ta, tb, p, stream);  \
-    if (!a_mn && b_mn) return launch_pair_variant<BN_, ST_, false, true>(ta, tb, p, stream);    \
-    if (a_mn && !b_mn) return launch_pair_variant<BN_, ST_, true, false>(ta, tb, p, stream);    \
-    return launch_pair_variant<BN_, ST_, true, true>(ta, tb, p, stream);                        \
+#define GEMM2_CASE(BN_, ST_)                                                                  \
+  if (BN == BN_) {                                                                            \
+    if (!a_mn && !b_mn)                                                                       \
+      return launch_pair_variant<BN_, ST_, kKSub, false, false>(ta, tb, p, stream);            \
+    if (!a_mn && b_mn) return launch_pair_variant<BN_, ST_, kKSub, false, true>(ta, tb, p, stream); \
+    if (a_mn && !b_mn) return launch_pair_variant<BN_, ST_, kKSub, true, false>(ta, tb, p, stream); \
+    return launch_pair_variant<BN_, ST_, kKSub, true, true>(ta, tb, p, stream);                \
   }
-  GEMM2_CASE(256, 6)
-  GEMM2_CASE(128, 8)
+  GEMM2_CASE(256, 6 / kKSub)
+  GEMM2_CASE(128, 8 / kKSub)
 #undef GEMM2_CASE
   return 1;
 }

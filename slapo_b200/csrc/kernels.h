@@ -72,7 +72,8 @@ int launch_comm_gemm(void* const* a_ptrs, void* const* b_ptrs, int M, int N, int
                      int world, int rank, int epoch, void* out, int ldo, const void* bias, int act,
                      int* flags, int* const* peer_flags, void* const* peer_recv,
                      void* const* peer_out, int* status, double wait_seconds, void* stage_dst,
-                     int* chunk_flags, void* recv_mc, void* out_mc, cudaStream_t stream);
+                     int* chunk_flags, void* recv_mc, void* out_mc, void* const* stage_peers,
+                     void* stage_mc, cudaStream_t stream);
 
 // Phase trace of the last fused GEMM + collective kernel (recorded when the environment has
 // SLAPO_B200_COMM_TRACE=1): [256 CTAs][8 slots] nanosecond time stamps, see comm_gemm.cu.

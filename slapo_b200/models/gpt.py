@@ -26,9 +26,9 @@ class Conv1D(nn.Module):
             nn.init.normal_(self.weight, std=0.02)
 
     def forward(self, x):
-        size_out = x.size()[:-1] + (self.weight.shape[-1],)
-        x = torch.addmm(self.bias, x.view(-1, x.size(-1)), self.weight)
-        return x.view(size_out)
+        from ..ops import functional as NF
+
+        return NF.linear_t(x, self.weight, self.bias)
 
 
 @dataclass

@@ -153,6 +153,44 @@ class _LinearFn(torch.autograd.Function):
         return dx, dw, (dbias if ctx.has_bias else None), None
 
 
+class _LinearTFn(torch.autograd.Function):
+    """``y = x W + b`` with ``W`` stored ``[in, out]`` (GPT-2's ``Conv1D``): the same three
+    GEMMs with the operand roles read the other way round, again without a transpose in memory."""
+
+    @staticmethod
+    def forward(ctx, x, weight, bias):
+        x2 = _rows(x)
+        y = gemm(x2, weight, bias, b_mn=True)            # B = W [K, N] read N-major
+        ctx.has_bias = bias is not None
+        ctx.save_for_backward(x2, weight)
+        ctx.x_shape = x.shape
+        return y.view(tuple(x.shape[:-1]) + (weight.shape[1],))
+
+    @staticmethod
+    def backward(ctx, dy):
+        x2, weight = ctx.saved_tensors
+        dy2 = _rows(dy)
+        dbias = native.ops().colsum(dy2) if ctx.has_bias and ctx.needs_input_grad[2] else None
+        dx = dw = None
+        if ctx.needs_input_grad[0]:
+            dx = gemm(dy2, weight).view(ctx.x_shape)      # dX = dY W^T: B = W [in, out] K-major
+        if ctx.needs_input_grad[1]:
+            dw = gemm(x2, dy2, a_mn=True, b_mn=True, split_k=True)    # dW = X^T dY
+        return dx, dw, dbias
+
+
+def linear_t(x, weight, bias=None):
+    """``x @ weight + bias`` for a weight stored ``[in_features, out_features]``."""
+    if (torch.is_tensor(x) and x.is_cuda and x.dtype in (torch.bfloat16, torch.float16)
+            and weight.dtype == x.dtype and weight.dim() == 2 and weight.stride(1) == 1
+            and weight.shape[0] % 8 == 0 and weight.shape[1] % 8 == 0 and weight.stride(0) % 8 == 0
+            and x.numel() > 0 and os.environ.get("SLAPO_B200_LIBRARY_GEMM", "0") != "1"
+            and _native_ok(x)):
+        return _LinearTFn.apply(x, weight, bias)
+    out = torch.matmul(x, weight)
+    return out if bias is None else out + bias
+
+
 def linear(x, weight, bias=None, act=None):
     """``act(x @ weight.T + bias)``; ``act`` in None / "gelu" / "gelu_new" / "relu".  CUDA
     16-bit tensors run this library's GEMM (bias and activation in its epilogue), anything

@@ -162,11 +162,9 @@ class Conv1DWithSyncFunc(nn.Module):
         self.sync_fn = sync_fn
 
     def forward(self, x):
-        size_out = x.size()[:-1] + (self.weight.shape[-1],)
-        out = torch.mm(x.view(-1, x.size(-1)), self.weight).view(size_out)
-        if self.sync_fn is not None:
-            out = self.sync_fn(out)
-        return out + self.bias
+        if self.sync_fn is None:
+            return NF.linear_t(x, self.weight, self.bias)
+        return self.sync_fn(NF.linear_t(x, self.weight, None)) + self.bias
 
     def extra_repr(self):
         return f"nx={self.nx}, nf={self.nf}, sync_fn={self.sync_fn}"

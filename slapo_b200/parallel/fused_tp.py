@@ -34,6 +34,7 @@ from ..ops import functional as NF
 from ..ops import native
 
 GATHER_NONE, GATHER_A_ROWS, GATHER_A_K, GATHER_B_K, GATHER_A_ROWS_STAGED = 0, 1, 2, 3, 4
+GATHER_A_ROWS_PUSHED = 5
 _CHUNK_WORDS = 8192   # kChunkCountOffset of csrc/comm_gemm.cu
 # A partial-product (receive) buffer of the scatter modes starts with a header: one flag per
 # (source rank, 128-row block of the owner's rows), written by the peers, then as many local
@@ -124,7 +125,7 @@ def _dbias(dy):
 
 def comm_gemm(ctx, *, a_ptrs, b_ptrs, M, N, K, lda, ldb, a_mn, b_mn, dtype, gather=GATHER_NONE,
               seg_len=0, mode=MODE_LOCAL, out_ptr=0, ldo=0, bias=None, act=-1, recv=None,
-              ar_out=None, stage=None, chunk_flags=None):
+              ar_out=None, stage=None, chunk_flags=None, slot=None):
     """Thin wrapper of ``torch.ops.slapo_b200.comm_gemm``; takes the next epoch."""
     epoch = ctx.next_epoch()
     if _DEBUG:
@@ -139,8 +140,127 @@ def comm_gemm(ctx, *, a_ptrs, b_ptrs, M, N, K, lda, ldb, a_mn, b_mn, dtype, gath
         stage.data_ptr() if stage is not None else 0,
         chunk_flags.data_ptr() if chunk_flags is not None else 0,
         int(getattr(recv, "mc_ptr", 0)) if recv is not None else 0,
-        int(getattr(ar_out, "mc_ptr", 0)) if ar_out is not None else 0)
+        int(getattr(ar_out, "mc_ptr", 0)) if ar_out is not None else 0,
+        list(slot.ptrs()) if slot is not None else [],
+        int(getattr(slot, "mc_ptr", 0)) if slot is not None else 0)
     return epoch
+
+
+class StagePool:
+    """Staging slots of the pushed all-gather.
+
+    A slot is a symmetric buffer: a header of block flags and slice counters, then the
+    gathered operand ``[T, K]``.  In the pushed gather every rank stores its own rows into the
+    slot of ALL ranks at the same offset (one multicast store through the NVSwitch), so all
+    ranks must use the same slot for the same operation.  They do, because slots are handed
+    out by a deterministic rule (a LIFO free list per size) and every rank issues the same
+    operations in the same order; releases happen at fixed points of the program (the end of
+    the autograd node's backward, or right after the launch when nothing is kept), never from
+    a finaliser.  A slot whose operand is kept for the backward pass stays out of the free
+    list until then - the gathered tokens are read by the weight-gradient GEMM straight from
+    the slot, with no copy.  ``release_all`` (called by the engine at the start of a step)
+    returns slots whose backward never ran.
+
+    When the pool's byte limit (``SLAPO_B200_AG_POOL_GB``, default 32) is reached, ``acquire``
+    returns ``None`` and the caller uses the size's single transient slot and copies what it
+    has to keep."""
+
+    _pools = None
+
+    def __init__(self, ctx):
+        import os
+        import weakref
+
+        self.ctx = ctx
+        self.limit = int(float(os.environ.get("SLAPO_B200_AG_POOL_GB", "32")) * 2**30)
+        self.used = 0
+        self.free: dict[int, list[int]] = {}
+        self.made: dict[int, int] = {}
+        self.out: set = set()
+        if StagePool._pools is None:
+            StagePool._pools = weakref.WeakSet()
+        StagePool._pools.add(self)
+
+    def _buf(self, nbytes, idx):
+        return self.ctx.buffer(f"ag_slot_{nbytes}_{idx}", RECV_HEADER_BYTES + nbytes)
+
+    def acquire(self, nbytes):
+        """(token, buffer) of a free slot for an operand of ``nbytes``, or ``None``."""
+        free = self.free.setdefault(nbytes, [])
+        if free:
+            idx = free.pop()
+        elif self.used + nbytes <= self.limit:
+            idx = self.made.get(nbytes, 0)
+            self.made[nbytes] = idx + 1
+            self.used += nbytes
+        else:
+            return None
+        token = (nbytes, idx)
+        self.out.add(token)
+        return token, self._buf(nbytes, idx)
+
+    def transient(self, nbytes):
+        return self._buf(nbytes, "t")
+
+    def release(self, token):
+        if token is not None and token in self.out:
+            self.out.discard(token)
+            self.free[token[0]].append(token[1])
+
+    def release_all(self):
+        for token in sorted(self.out, reverse=True):
+            self.free[token[0]].append(token[1])
+        self.out.clear()
+
+
+def stage_pool(ctx) -> StagePool:
+    pool = ctx.__dict__.get("_stage_pool")
+    if pool is None:
+        pool = ctx.__dict__["_stage_pool"] = StagePool(ctx)
+    return pool
+
+
+def step_boundary():
+    """Start of a training step: every staging slot still held for a backward pass that never
+    ran goes back to its pool (all ranks call this at the same point of the program)."""
+    for pool in list(StagePool._pools or ()):
+        pool.release_all()
+
+
+def push_enabled(ctx) -> bool:
+    """Pushed (owner stores through the switch) or pulled (consumer loads) all-gather.
+    ``SLAPO_B200_AG_MODE=push|pull``; default: push where the context reduces through the
+    NVSwitch (groups of four ranks or more), pull otherwise."""
+    mode = __import__("os").environ.get("SLAPO_B200_AG_MODE")
+    if mode in ("push", "pull"):
+        return mode == "push"
+    return bool(getattr(ctx, "nvls", False))
+
+
+def ag_gemm_pushed(ctx, x_shard, w, bias=None, act=-1, b_mn=False, keep=False):
+    """``all_gather(x_shard) @ w.T`` with the gather pushed by the owners (see
+    ``comm_gemm.cu``, gather mode 5).  Returns ``(y, gathered, token)``: with ``keep`` the
+    gathered operand ``[T, K]`` stays valid until ``stage_pool(ctx).release(token)``; without
+    it ``gathered`` is ``None``."""
+    ts, k = x_shard.shape
+    n = w.shape[1] if b_mn else w.shape[0]
+    t = ts * ctx.world
+    nbytes = t * k * x_shard.element_size()
+    pool = stage_pool(ctx)
+    got = pool.acquire(nbytes)
+    token, slot = got if got is not None else (None, pool.transient(nbytes))
+    y = torch.empty(t, n, dtype=x_shard.dtype, device=x_shard.device)
+    a_ptrs = [x_shard.data_ptr() if r == ctx.rank else 0 for r in range(ctx.world)]
+    comm_gemm(ctx, a_ptrs=a_ptrs, b_ptrs=[w.data_ptr()], M=t, N=n, K=k, lda=k, ldb=w.stride(0),
+              a_mn=False, b_mn=b_mn, dtype=x_shard.dtype, gather=GATHER_A_ROWS_PUSHED, seg_len=ts,
+              out_ptr=y.data_ptr(), ldo=n, bias=bias, act=act, slot=slot)
+    if not keep:
+        pool.release(token)
+        return y, None, None
+    full = slot.view(x_shard.dtype, (t, k), RECV_HEADER_BYTES)
+    if token is None:            # pool exhausted: the transient slot is reused by the next gather
+        full = full.clone()
+    return y, full, token
 
 
 def _staging(ctx, t, k, dtype, device):
@@ -264,7 +384,18 @@ class _AGLinear(torch.autograd.Function):
     def forward(ctx, x_shard, w, bias, sctx):
         ctx.sctx = sctx
         x_shard = x_shard.contiguous()
-        y, full_x = ag_gemm(sctx, x_shard, w, bias, keep_gathered=True)
+        ctx.token = None
+        if push_enabled(sctx) and x_shard.shape[0] % 128 == 0 and sctx.world > 1:
+            # no backward will run (evaluation, the first pass of a checkpointed layer): keep nothing
+            keep = any(ctx.needs_input_grad[:3])
+            y, full_x, ctx.token = ag_gemm_pushed(sctx, x_shard, w, bias, keep=keep)
+            if not keep:
+                ctx.gathered = False
+                ctx.save_for_backward(x_shard, w)
+                ctx.has_bias = bias is not None
+                return y
+        else:
+            y, full_x = ag_gemm(sctx, x_shard, w, bias, keep_gathered=True)
         # the gathered tokens are kept for the weight gradient when the kernel staged them
         # (HBM is plentiful; the second NVLink gather in backward is not)
         ctx.gathered = full_x is not None
@@ -284,6 +415,9 @@ class _AGLinear(torch.autograd.Function):
         # library's split-K GEMM do the rest
         full_x = x_saved if ctx.gathered else peer_gather(sctx, x_saved.contiguous(), "ag_in_bwd")
         dw = _wgrad(dy, full_x)
+        if ctx.token is not None:       # the staging slot that held the gathered tokens
+            stage_pool(sctx).release(ctx.token)
+            ctx.token = None
         db = _dbias(dy) if ctx.has_bias else None
         return dx, dw, db, None
 
@@ -304,13 +438,18 @@ class _RSLinear(torch.autograd.Function):
         ts, n = dy_shard.shape
         t, kl = x.shape
         # dX = all_gather(dYs) @ W: A rows gathered inside the GEMM, B = W read N-major
-        dx, full_dy = ag_gemm(sctx, dy_shard, w, None, name="ag_dy_bwd", b_mn=True,
-                              keep_gathered=True)
+        token = None
+        if push_enabled(sctx) and ts % 128 == 0 and sctx.world > 1:
+            dx, full_dy, token = ag_gemm_pushed(sctx, dy_shard, w, None, b_mn=True, keep=True)
+        else:
+            dx, full_dy = ag_gemm(sctx, dy_shard, w, None, name="ag_dy_bwd", b_mn=True,
+                                  keep_gathered=True)
         # dW = all_gather(dYs)^T @ X: long contraction, few tiles (see _AGLinear); the dgrad
         # kernel above has already gathered dY into local memory
         if full_dy is None:
             full_dy = peer_gather(sctx, dy_shard, "ag_dy_bwd2")
         dw = _wgrad(full_dy, x)
+        stage_pool(sctx).release(token)
         # the bias is added on the owner's rows only: its gradient is partial
         # (tagged replicated_param -> summed over the group by the engine)
         db = _dbias(dy_shard) if ctx.has_bias else None

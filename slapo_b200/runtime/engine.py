@@ -108,6 +108,15 @@ class _Bucket:
         self.deferred = False
 
 
+def _release_staging_slots():
+    """Staging slots of the pushed all-gather that a backward pass never released (an
+    exception, a forward whose loss was dropped) go back to their pools; nothing of the
+    previous batch is alive at this point."""
+    from ..parallel import fused_tp
+
+    fused_tp.step_boundary()
+
+
 class TrainEngine:
     """See the module docstring.  ``engine(*inputs)`` runs the forward,
     ``engine.backward(loss)`` the backward, ``engine.step()`` the optimizer;
@@ -613,6 +622,7 @@ class TrainEngine:
     def train_batch(self, *args, labels=None, **kwargs):
         if self.micro_step % self.cfg.grad_accum_steps == 0:
             self._phase_events = []
+        _release_staging_slots()
         with self._phase("forward"):
             out = self.model(*args, **kwargs)
             if self.loss_fn is not None:

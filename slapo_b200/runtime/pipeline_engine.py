@@ -334,6 +334,9 @@ class PipelineEngine:
     # ---- the schedule ---------------------------------------------------- #
     def train_batch(self, *args, labels=None, **kwargs):
         m = self.num_micro_batches
+        from .engine import _release_staging_slots
+
+        _release_staging_slots()
         env = self.model.bind_inputs(args, kwargs)
         micro_inputs = [{} for _ in range(m)]
         for name, val in env.items():

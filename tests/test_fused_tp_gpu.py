@@ -42,6 +42,69 @@ def test_all_gather_gemm(world, n):
         _close(y, full @ w[r].float().t() + bias.float(), k)
 
 
+@pytest.mark.parametrize("world,n,ts", [(2, 320, 256), (4, 192, 384), (8, 384, 128)])
+@pytest.mark.parametrize("keep", [False, True])
+def test_all_gather_gemm_pushed(world, n, ts, keep):
+    """Pushed gather: the emulated rank stores its own rows into every rank's staging slot
+    (rank by rank here, the emulation has no multicast address) and multiplies the gathered
+    operand; the other owners' rows and block flags are put into its slot beforehand."""
+    torch.manual_seed(1)
+    k = 192
+    t = ts * world
+    ctx = LocalSymmContext(world)
+    shards = [torch.randn(ts, k, device="cuda", dtype=torch.bfloat16) for _ in range(world)]
+    w = [torch.randn(n, k, device="cuda", dtype=torch.bfloat16) for _ in range(world)]
+    bias = torch.randn(n, device="cuda", dtype=torch.bfloat16)
+    full = torch.cat(shards, 0)
+    nbytes = t * k * 2
+    name = f"ag_slot_{nbytes}_0"
+    for r in range(world):
+        ctx.as_rank(r).buffer(name, ft.RECV_HEADER_BYTES + nbytes)
+    hdr = ft.RECV_HEADER_BYTES
+
+    def data(q):
+        return ctx._buffers[name][q][hdr:hdr + nbytes].view(torch.bfloat16).view(t, k)
+
+    for r in range(world):
+        ctx.as_rank(r)
+        for q in range(world):
+            data(q).copy_(full)
+            data(q)[r * ts:(r + 1) * ts].zero_()          # what rank r has to deliver
+        flags = ctx._buffers[name][r][:t // 128 * 4].view(torch.int32)
+        flags.fill_(ctx.epoch + 1)                         # the other owners' blocks "arrived"
+        flags[r * (ts // 128):(r + 1) * (ts // 128)] = 0
+        ctx.preset_flags(ctx.epoch + 1)
+        y, gathered, token = ft.ag_gemm_pushed(ctx, shards[r], w[r], bias, keep=keep)
+        assert native.ops().device_status() == 0
+        _close(y, full.float() @ w[r].float().t() + bias.float(), k)
+        for q in range(world):
+            assert torch.equal(data(q), full), f"rank {r}'s rows in rank {q}'s slot"
+            fl = ctx._buffers[name][q][:t // 128 * 4].view(torch.int32)
+            assert bool((fl[r * (ts // 128):(r + 1) * (ts // 128)] == ctx.epoch).all())
+        if keep:
+            assert token == (nbytes, 0) and torch.equal(gathered, full)
+            ft.stage_pool(ctx).release(token)
+        else:
+            assert gathered is None and token is None
+
+
+def test_stage_pool_is_deterministic_and_bounded(monkeypatch):
+    """Slots come from a LIFO free list per size; beyond the byte limit `acquire` refuses and
+    the caller falls back to the transient slot; `release_all` returns what was never released."""
+    monkeypatch.setenv("SLAPO_B200_AG_POOL_GB", str(3 * 2**20 / 2**30))
+    ctx = LocalSymmContext(2)
+    pool = ft.StagePool(ctx)
+    a, b, c = (pool.acquire(2**20) for _ in range(3))
+    assert [x[0] for x in (a, b, c)] == [(2**20, 0), (2**20, 1), (2**20, 2)]
+    assert pool.acquire(2**20) is None
+    pool.release(b[0])
+    pool.release(b[0])                                      # a second release is ignored
+    assert pool.acquire(2**20)[0] == (2**20, 1)
+    pool.release_all()
+    assert sorted(pool.free[2**20]) == [0, 1, 2]
+    assert pool.acquire(2**20)[0] == (2**20, 0)
+
+
 @pytest.mark.parametrize("world", [2, 4, 8])
 @pytest.mark.parametrize("mode", ["rs", "ar"])
 def test_gemm_reduce_scatter_and_all_reduce(world, mode):
@@ -130,3 +193,7 @@ def test_missing_peer_times_out_cleanly():
     y = ft.ag_gemm(ctx, xs, w, None, staged=ctx.buffer("ag_in", ts * k * 2))
     assert native.ops().device_status() == 0
     _close(y, torch.cat([xs, xs], 0).float() @ w.float().t(), k)
+    # the pushed form waits for every rank to enter before it writes anybody's slot
+    ft.ag_gemm_pushed(ctx, xs, w)
+    torch.cuda.synchronize()
+    assert native.ops().device_status() == 4

@@ -19,8 +19,13 @@ def _close(a, b, k, tol=3e-2):
     torch.testing.assert_close(a.float() / scale, b.float() / scale, rtol=tol, atol=tol)
 
 
-def _worker(rank, world, nvls):
+def _worker(rank, world, nvls, ag_mode=None):
+    import os
+
     import torch.distributed as dist
+
+    if ag_mode is not None:      # "push" / "pull": the all-gather form (default: push with nvls)
+        os.environ["SLAPO_B200_AG_MODE"] = ag_mode
 
     from slapo_b200.ops import native
     from slapo_b200.parallel import fused_tp as ft
@@ -85,14 +90,20 @@ def _worker(rank, world, nvls):
     torch.cuda.synchronize()
     assert native.ops().device_status() == 0
     _close(z3, ref.detach(), n * world)
+    _close(y3, (x_full.float() @ w_col.float().t())[:, rank * n:(rank + 1) * n], k)
+    if ft.push_enabled(ctx):     # every staging slot went back to the pool
+        assert not ft.stage_pool(ctx).out
     dist.barrier()
 
 
-@pytest.mark.parametrize("nvls", [False, True])
+@pytest.mark.parametrize("nvls,ag_mode", [(False, None), (True, None), (False, "push"), (True, "pull")])
 @pytest.mark.parametrize("world", [2, 4])
-def test_fused_tp_linears_on_peers(world, nvls):
+def test_fused_tp_linears_on_peers(world, nvls, ag_mode):
+    """nvls: reductions through the NVSwitch; the all-gather is pushed through the switch with
+    nvls, pulled by peer loads without, unless ``ag_mode`` says otherwise (pushed rank by rank
+    without nvls)."""
     _need_gpus(world)
-    run_distributed(_worker, world, nvls, backend="nccl")
+    run_distributed(_worker, world, nvls, ag_mode, backend="nccl")
 
 
 def _embed_worker(rank, world, sp_axis):

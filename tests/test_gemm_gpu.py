@@ -147,3 +147,26 @@ def test_colsum_matches_fp32():
     torch.testing.assert_close(_ops().colsum(x).float(), x.float().sum(0), rtol=2e-2, atol=0.5)
     view = x[:, :512]            # row stride larger than the width
     torch.testing.assert_close(_ops().colsum(view).float(), view.float().sum(0), rtol=2e-2, atol=0.5)
+
+
+def test_linear_with_in_out_weight_layout():
+    """GPT-2's Conv1D layout (weight [in, out]): forward and both gradients on the native GEMM."""
+    from slapo_b200.ops import functional as NF
+
+    torch.manual_seed(5)
+    x = torch.randn(3, 128, 256, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    w = (torch.randn(256, 768, device="cuda", dtype=torch.bfloat16) * 0.05).requires_grad_(True)
+    b = torch.randn(768, device="cuda", dtype=torch.bfloat16).requires_grad_(True)
+    g = torch.randn(3, 128, 768, device="cuda", dtype=torch.bfloat16)
+    before = native.launch_count()
+    y = NF.linear_t(x, w, b)
+    y.backward(g)
+    assert native.launch_count() - before >= 4
+    xf, wf, bf = (t.detach().float().requires_grad_(True) for t in (x, w, b))
+    ref = xf @ wf + bf
+    ref.backward(g.float())
+    torch.testing.assert_close(y.float(), ref, rtol=3e-2, atol=3e-2)
+    torch.testing.assert_close(x.grad.float(), xf.grad, rtol=3e-2, atol=5e-2)
+    torch.testing.assert_close(w.grad.float() / 8, wf.grad / 8, rtol=3e-2, atol=5e-2)
+    torch.testing.assert_close(b.grad.float() / 8, bf.grad / 8, rtol=3e-2, atol=5e-2)
+    assert _ops().device_status() == 0
