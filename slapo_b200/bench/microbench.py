@@ -58,7 +58,7 @@ def report(name, us, nbytes=None, flops=None, **extra):
 
 
 def bench_ln(small, iters):
-    rows, cols = (4096, 1024) if small else (65536, 1024)
+    rows, cols = (32768, 1024) if small else (65536, 1024)   # several tensors of 64 MB: beyond L2
     dt = torch.bfloat16
     x = torch.randn(rows, cols, device="cuda", dtype=dt, requires_grad=True)
     r = torch.randn_like(x)
@@ -155,6 +155,21 @@ def bench_comm(small, iters):
         return ft.ag_gemm(ctx, shards[0], w, None, staged=ctx.buffer("ag_in", ts * k * 2))
 
     report("ag_gemm_emulated", timeit(ag, iters), flops=2 * ts * world * n * k,
+           shape=[ts * world, n, k], world=world)
+    # pushed form: this rank stores its rows into both slots; the peer's rows and block flags
+    # are put into this rank's slot beforehand (once: flags only have to be >= the epoch)
+    nbytes = ts * world * k * 2
+    slot = ctx.buffer(f"ag_slot_{nbytes}_0", ft.RECV_HEADER_BYTES + nbytes)
+    ctx.as_rank(1).buffer(f"ag_slot_{nbytes}_0", ft.RECV_HEADER_BYTES + nbytes)
+    ctx.as_rank(0)
+    slot.view(torch.bfloat16, (ts * world, k), ft.RECV_HEADER_BYTES).copy_(torch.cat(shards, 0))
+    slot.view(torch.int32, (ts * world // 128,))[ts // 128:] = 1 << 30
+
+    def ag_push():
+        ctx.preset_flags(ctx.epoch + 1)
+        return ft.ag_gemm_pushed(ctx, shards[0], w)[0]
+
+    report("ag_gemm_push_emulated", timeit(ag_push, iters), flops=2 * ts * world * n * k,
            shape=[ts * world, n, k], world=world)
     x = torch.randn(ts * world, n, device="cuda", dtype=torch.bfloat16)
     w2 = torch.randn(k, n, device="cuda", dtype=torch.bfloat16)

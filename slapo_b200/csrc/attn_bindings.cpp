@@ -81,7 +81,15 @@ std::tuple<Tensor, Tensor, Tensor, Tensor> flash_attn_bwd(
   TORCH_CHECK(dout.is_contiguous() && o.is_contiguous(), "dout and out must be contiguous");
   c10::cuda::CUDAGuard guard(q.device());
   const int B = q.size(0), Sq = q.size(1), H = q.size(2), D = q.size(3), Sk = k.size(1);
-  Tensor dq_accum = at::zeros({B, Sq, H, D}, q.options().dtype(at::kFloat));
+  // dQ: one fp32 partial per 128-key tile, written with plain stores and summed by the
+  // conversion kernel (no zero fill, no atomics); beyond 16 key tiles, or 4 GB of partials,
+  // a single zero-filled accumulator that the key tiles reduce into
+  const int64_t n_kt = (Sk + 127) / 128;
+  const int64_t dq_elems = static_cast<int64_t>(B) * Sq * H * D;
+  const bool sliced = n_kt <= 16 && n_kt * dq_elems * 4 <= (int64_t(4) << 30);
+  const int n_slices = sliced ? static_cast<int>(n_kt) : 1;
+  Tensor dq_accum = sliced ? at::empty({n_kt, B, Sq, H, D}, q.options().dtype(at::kFloat))
+                           : at::zeros({B, Sq, H, D}, q.options().dtype(at::kFloat));
   // packed_qkv: q, k, v are the slices [..., 0/1/2, :] of one [B, S, H, 3, D]
   // projection output; the gradients are written into one tensor of that
   // layout so that autograd needs no concatenation
@@ -107,8 +115,8 @@ std::tuple<Tensor, Tensor, Tensor, Tensor> flash_attn_bwd(
   const int64_t vs[3] = {v.stride(0), v.stride(1), v.stride(2)};
   int rc = slapo::launch_flash_bwd(
       q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), dout.data_ptr(),
-      lse.data_ptr<float>(), delta.data_ptr<float>(), dq_accum.data_ptr<float>(), dk.data_ptr(),
-      dv.data_ptr(), dkv_stride, opt_f32(kbias, "key bias"), opt_f32(rel, "relative bias"),
+      lse.data_ptr<float>(), delta.data_ptr<float>(), dq_accum.data_ptr<float>(),
+      sliced ? dq_elems : 0, dk.data_ptr(), dv.data_ptr(), dkv_stride, opt_f32(kbias, "key bias"), opt_f32(rel, "relative bias"),
       has_rel ? drel.data_ptr<float>() : nullptr, B, H, Sq, Sk, D, qs, ks, vs,
       static_cast<float>(scale), causal ? 1 : 0, static_cast<float>(p_drop), unpack_rng(rng),
       q.scalar_type() == at::kBFloat16, slapo_status_ptr(q.get_device()),
@@ -120,12 +128,12 @@ std::tuple<Tensor, Tensor, Tensor, Tensor> flash_attn_bwd(
   if (packed_qkv) {
     // dq is slice 0 of the packed gradient: rows of D values, 3 D apart
     slapo::launch_flash_dq_convert(dq_accum.data_ptr<float>(), dqkv.data_ptr(), rows, D, 3 * D,
-                                   bf16, stream);
+                                   bf16, n_slices, dq_elems, Sq, Sk, H, causal ? 1 : 0, stream);
     return {dqkv, dk, dv, drel};
   }
   Tensor dq = at::empty({B, Sq, H, D}, q.options());
   slapo::launch_flash_dq_convert(dq_accum.data_ptr<float>(), dq.data_ptr(), rows, D, D, bf16,
-                                 stream);
+                                 n_slices, dq_elems, Sq, Sk, H, causal ? 1 : 0, stream);
   return {dq, dk, dv, drel};
 }
 

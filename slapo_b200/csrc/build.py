@@ -100,11 +100,14 @@ def build(verbose: bool = False, force: bool = False) -> str:
             for cmd, out in log:
                 fh.write(cmd + "\n" + out + "\n")
     if jobs or force or _newer(objs, OUT):
-        link = [cxx, "-shared", "-o", OUT] + objs + [
+        # link beside the target and rename: a reader never sees a half-written library
+        tmp = OUT + ".tmp"
+        link = [cxx, "-shared", "-o", tmp] + objs + [
             "-L", torch_lib, "-L", os.path.join(_cuda_home(), "lib64"),
             "-ltorch", "-ltorch_cpu", "-ltorch_cuda", "-lc10", "-lc10_cuda", "-lcudart",
             f"-Wl,-rpath,{torch_lib}"]
         _run(link, log)
+        os.replace(tmp, OUT)
     return OUT
 
 

@@ -43,13 +43,14 @@ int launch_flash_fwd(const void* q, const void* k, const void* v, void* o, float
                      float scale, int causal, float p_drop, PhiloxArgs rng, bool bf16, int* status,
                      cudaStream_t stream);
 int launch_flash_bwd(const void* q, const void* k, const void* v, const void* o, const void* dout,
-                     const float* lse, float* delta, float* dq_accum, void* dk, void* dv,
-                     int64_t dkv_row_stride, const float* kbias, const float* rel, float* drel,
+                     const float* lse, float* delta, float* dq_accum, int64_t dq_slice_stride,
+                     void* dk, void* dv, int64_t dkv_row_stride, const float* kbias, const float* rel, float* drel,
                      int B, int H, int Sq, int Sk, int D, const int64_t* q_strides, const int64_t* k_strides,
                      const int64_t* v_strides, float scale, int causal, float p_drop,
                      PhiloxArgs rng, bool bf16, int* status, cudaStream_t stream);
 void launch_flash_dq_convert(const float* acc, void* out, int64_t rows, int D,
-                             int64_t out_row_stride, bool bf16, cudaStream_t stream);
+                             int64_t out_row_stride, bool bf16, int n_slices, int64_t slice_stride,
+                             int Sq, int Sk, int H, int causal, cudaStream_t stream);
 void launch_flash_dropout_mask(uint8_t* mask, int B, int H, int Sq, int Sk, float p_drop,
                                PhiloxArgs rng, cudaStream_t stream);
 }  // namespace slapo

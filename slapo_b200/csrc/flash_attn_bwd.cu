@@ -8,7 +8,9 @@
 //                 tiles into swizzled shared memory
 //   tensor core   dV += P^T dO          dK += dS^T Q               (TMEM accumulators
 //                 dQ_tile = dS K                                    over all query tiles)
-//   128 threads   dQ_tile -> fp32 global accumulator (vector red.add)
+//   128 threads   dQ_tile -> fp32 partial of this key tile (plain 16-byte stores; the
+//                 conversion kernel sums the partials), or, for very long key sequences,
+//                 a shared fp32 accumulator (vector red.add)
 // The same shared-memory bytes serve as K-major and M/N-major operands: only
 // the descriptors differ, nothing is transposed.  delta = rowsum(dO * O) comes
 // from a small pre-pass; the fp32 dQ accumulator is converted by the caller.
@@ -25,7 +27,9 @@ struct FlashBwdParams {
   int Dr;               // the tensors' head dimension (<= the tile width D, % 8 == 0)
   const float* lse;     // [B, H, Sq]
   const float* delta;   // [B, H, Sq]
-  float* dq_accum;      // [B, Sq, H, Dr] fp32, zero-initialised
+  float* dq_accum;      // [B, Sq, H, Dr] fp32, zero-initialised (dq_slice_stride == 0), or one
+                        // such partial per 128-key tile, written with plain stores
+  int64_t dq_slice_stride;
   void* dK;             // rows (b, key, head) spaced dkv_row_stride elements apart
   void* dV;
   int64_t dkv_row_stride;  // D for contiguous [B, Sk, H, D]; 3 D inside a packed QKV gradient
@@ -364,7 +368,11 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
       // dQ tile of this query block
       if (!tc::mbar_wait_warp(dq_full, it & 1, abort_flag)) { ok = false; break; }
       tc::fence_after_sync();
-      float* dq_dst = p.dq_accum +
+      // Reductions into one accumulator run at the rate of the L2 atomic units, which for
+      // four or eight key tiles per query row costs more than the whole rest of the kernel:
+      // each key tile stores into its own partial instead.
+      const bool dq_sliced = p.dq_slice_stride != 0;
+      float* dq_dst = p.dq_accum + static_cast<int64_t>(blockIdx.x) * p.dq_slice_stride +
                       ((static_cast<int64_t>(batch) * p.Sq + min(row, p.Sq - 1)) * p.H + head) * p.Dr;
 #pragma unroll
       for (int cc = 0; cc < D / 64; ++cc) {
@@ -374,12 +382,15 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
         tc::tmem_ld_wait();
         if (row_ok) {
 #pragma unroll
-          for (int g = 0; g < 8; ++g)
-            if (c * 32 + g * 4 < p.Dr)
-            red_add_v4(dq_dst + c * 32 + g * 4, __uint_as_float(r[g * 4]) * out_scale,
-                       __uint_as_float(r[g * 4 + 1]) * out_scale,
-                       __uint_as_float(r[g * 4 + 2]) * out_scale,
-                       __uint_as_float(r[g * 4 + 3]) * out_scale);
+          for (int g = 0; g < 8; ++g) {
+            if (c * 32 + g * 4 >= p.Dr) break;
+            const float4 val = make_float4(__uint_as_float(r[g * 4]) * out_scale,
+                                           __uint_as_float(r[g * 4 + 1]) * out_scale,
+                                           __uint_as_float(r[g * 4 + 2]) * out_scale,
+                                           __uint_as_float(r[g * 4 + 3]) * out_scale);
+            if (dq_sliced) *reinterpret_cast<float4*>(dq_dst + c * 32 + g * 4) = val;
+            else red_add_v4(dq_dst + c * 32 + g * 4, val.x, val.y, val.z, val.w);
+          }
         }
       }
       tc::fence_before_sync();
@@ -440,27 +451,44 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
   }
 }
 
-// dq (16-bit, rows spaced out_row_stride elements apart) <- dq_accum (fp32, contiguous rows of D):
-// the conversion that closes the backward pass; 8 values per thread, 16-byte stores.
+// dq (16-bit, rows spaced out_row_stride elements apart) <- sum of the fp32 partials (contiguous
+// rows of D, one partial per 128-key tile, slice_stride elements apart; a single accumulator
+// when n_slices == 1): the conversion that closes the backward pass; 8 values per thread,
+// 16-byte stores.  Under a causal mask key tile kt holds rows of query tiles >= first_q(kt)
+// only (the others were never written and are skipped).
 template <typename T>
-__global__ void __launch_bounds__(256) flash_dq_convert_kernel(const float* __restrict__ acc,
-                                                               T* __restrict__ out, int64_t rows,
-                                                               int D, int64_t out_row_stride) {
+__global__ void __launch_bounds__(256) flash_dq_convert_kernel(
+    const float* __restrict__ acc, T* __restrict__ out, int64_t rows, int D, int64_t out_row_stride,
+    int n_slices, int64_t slice_stride, int Sq, int Sk, int H, int causal) {
   const int vecs_per_row = D >> 3;
   const int64_t n_vec = rows * vecs_per_row;
   const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
+  const int diag = Sk - Sq;
+  const int q_tiles = (Sq + 127) / 128;
   for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < n_vec;
        i += stride) {
     const int64_t row = i / vecs_per_row;
     const int d = static_cast<int>(i - row * vecs_per_row) * 8;
-    float v[8];
-    Vec8<float>::load(acc + row * D + d, v);
+    const int q_tile = static_cast<int>((row / H) % Sq) >> 7;
+    float v[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    for (int kt = 0; kt < n_slices; ++kt) {
+      if (causal && n_slices > 1) {
+        int first_q = (kt * 128 - diag) / 128;
+        first_q = first_q < 0 ? 0 : (first_q > q_tiles ? q_tiles : first_q);
+        if (q_tile < first_q) break;      // later key tiles start even later
+      }
+      float part[8];
+      Vec8<float>::load(acc + kt * slice_stride + row * D + d, part);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) v[j] += part[j];
+    }
     Vec8<T>::store(out + row * out_row_stride + d, v);
   }
 }
 
 void launch_flash_dq_convert(const float* acc, void* out, int64_t rows, int D,
-                             int64_t out_row_stride, bool bf16, cudaStream_t stream) {
+                             int64_t out_row_stride, bool bf16, int n_slices, int64_t slice_stride,
+                             int Sq, int Sk, int H, int causal, cudaStream_t stream) {
   const int64_t n_vec = rows * (D >> 3);
   if (n_vec == 0) return;
   int64_t blocks = (n_vec + 255) / 256;
@@ -469,10 +497,12 @@ void launch_flash_dq_convert(const float* acc, void* out, int64_t rows, int D,
   count_launch();
   if (bf16)
     flash_dq_convert_kernel<__nv_bfloat16><<<static_cast<int>(blocks), 256, 0, stream>>>(
-        acc, static_cast<__nv_bfloat16*>(out), rows, D, out_row_stride);
+        acc, static_cast<__nv_bfloat16*>(out), rows, D, out_row_stride, n_slices, slice_stride, Sq,
+        Sk, H, causal);
   else
     flash_dq_convert_kernel<__half><<<static_cast<int>(blocks), 256, 0, stream>>>(
-        acc, static_cast<__half*>(out), rows, D, out_row_stride);
+        acc, static_cast<__half*>(out), rows, D, out_row_stride, n_slices, slice_stride, Sq, Sk, H,
+        causal);
 }
 
 template <int D, bool kPlain>
@@ -495,8 +525,8 @@ static int launch_bwd_d(const CUtensorMap& tq, const CUtensorMap& tk, const CUte
 }
 
 int launch_flash_bwd(const void* q, const void* k, const void* v, const void* o, const void* dout,
-                     const float* lse, float* delta, float* dq_accum, void* dk, void* dv,
-                     int64_t dkv_row_stride, const float* kbias, const float* rel, float* drel,
+                     const float* lse, float* delta, float* dq_accum, int64_t dq_slice_stride,
+                     void* dk, void* dv, int64_t dkv_row_stride, const float* kbias, const float* rel, float* drel,
                      int B, int H, int Sq, int Sk, int D, const int64_t* q_strides, const int64_t* k_strides,
                      const int64_t* v_strides, float scale, int causal, float p_drop,
                      PhiloxArgs rng, bool bf16, int* status, cudaStream_t stream) {
@@ -526,6 +556,7 @@ int launch_flash_bwd(const void* q, const void* k, const void* v, const void* o,
     return 2;
   FlashBwdParams p;
   p.B = B; p.H = H; p.Sq = Sq; p.Sk = Sk; p.Dr = D; p.lse = lse; p.delta = delta; p.dq_accum = dq_accum;
+  p.dq_slice_stride = dq_slice_stride;
   p.dK = dk; p.dV = dv; p.dkv_row_stride = dkv_row_stride; p.kbias = kbias; p.rel = rel; p.drel = drel; p.scale = scale;
   p.scale_log2 = scale * kLog2eB; p.causal = causal; p.rng = rng;
   p.thr7 = dropout_thr7(p_drop);   // same quantisation as the forward kernel
