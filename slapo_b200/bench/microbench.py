@@ -163,7 +163,7 @@ def bench_comm(small, iters):
     ctx.as_rank(1).buffer(f"ag_slot_{nbytes}_0", ft.RECV_HEADER_BYTES + nbytes)
     ctx.as_rank(0)
     slot.view(torch.bfloat16, (ts * world, k), ft.RECV_HEADER_BYTES).copy_(torch.cat(shards, 0))
-    slot.view(torch.int32, (ts * world // 128,))[ts // 128:] = 1 << 30
+    slot.view(torch.int32, (ts * world // 128 * 16,))[ts // 128 * 16:] = 1 << 30   # 16 flags per block
 
     def ag_push():
         ctx.preset_flags(ctx.epoch + 1)

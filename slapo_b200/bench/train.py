@@ -61,7 +61,55 @@ def parse_args(argv=None):
                          "(and every such interval again): shows where a stuck rank waits")
     ap.add_argument("--no-fused-dp", action="store_true",
                     help="data parallelism through NCCL instead of the peer-memory kernels")
+    ap.add_argument("--profile-table", default=None,
+                    help="after the timed steps run two more under torch.profiler and write, per "
+                         "rank, PATH.rank<r>.txt: the top device kernels and how much of the "
+                         "send / receive kernels' time ran concurrently with other kernels")
     return ap.parse_args(argv)
+
+
+def profile_overlap(step_fn, path, rank, steps=2):
+    """Kernel table of ``steps`` steps and the overlap of point-to-point transfers with compute.
+
+    The overlap is computed from the device-side intervals of the profiler's kernel events:
+    the time covered by NCCL send / receive kernels, and the part of it during which at least
+    one other kernel was running on the same device.  (Times taken under a profiler are not
+    benchmark numbers; the table shows structure.)"""
+    import torch
+    from torch.autograd import DeviceType
+    from torch.profiler import ProfilerActivity, profile
+
+    with profile(activities=[ProfilerActivity.CPU, ProfilerActivity.CUDA]) as prof:
+        for _ in range(steps):
+            step_fn()
+        torch.cuda.synchronize()
+    kernels = [e for e in prof.events() if e.device_type == DeviceType.CUDA and e.time_range is not None]
+    p2p = [(e.time_range.start, e.time_range.end) for e in kernels
+           if "SendRecv" in e.name or "sendrecv" in e.name.lower()]
+    other = sorted((e.time_range.start, e.time_range.end) for e in kernels
+                   if "nccl" not in e.name.lower() and "Memcpy" not in e.name and "Memset" not in e.name)
+    merged = []
+    for a, b in other:                       # union of the compute intervals
+        if merged and a <= merged[-1][1]:
+            merged[-1][1] = max(merged[-1][1], b)
+        else:
+            merged.append([a, b])
+    total = sum(b - a for a, b in p2p)
+    covered = 0.0
+    for a, b in p2p:
+        for c, d in merged:
+            if d <= a:
+                continue
+            if c >= b:
+                break
+            covered += min(b, d) - max(a, c)
+    table = prof.key_averages().table(sort_by="cuda_time_total", row_limit=14, max_name_column_width=60)
+    with open(f"{path}.rank{rank}.txt", "w", encoding="utf-8") as fh:
+        fh.write(f"rank {rank}: {len(p2p)} send/receive kernels in {steps} steps, {total / 1e3:.2f} ms in "
+                 f"total, {covered / 1e3:.2f} ms of it ({100.0 * covered / max(total, 1e-9):.0f} %) while "
+                 "another kernel of this rank was running\n\n")
+        fh.write(table)
+    return {"p2p_kernels": len(p2p), "p2p_ms": total / 1e3, "p2p_overlapped_ms": covered / 1e3}
 
 
 def _even_cuts(n_layers, n_stages):
@@ -254,6 +302,8 @@ def run(args):
     }
     if args.save:
         ckpt.save_checkpoint(args.save, inner.model, inner, mesh=mesh)
+    if args.profile_table and device.type == "cuda":
+        record["p2p_overlap"] = profile_overlap(step, args.profile_table, rank)
     if rank == 0:
         line = json.dumps(record)
         print(line, flush=True)

@@ -70,6 +70,8 @@ constexpr int kMaxRanks = 8;
 constexpr int kChunkCountOffset = 8192;
 // header of a partial-product (receive) buffer: kChunkCountOffset block flags + as many counters
 constexpr int kRecvHeaderBytes = 2 * kChunkCountOffset * 4;
+// pushed gather: flag words per 128-row block in the slot header (one per slice, up to 16)
+constexpr int kSliceFlagStride = 16;
 constexpr int kDefaultAgSlices = 1;
 constexpr int kDefaultAgInflight = 16;
 constexpr int CBM = 128;
@@ -185,6 +187,35 @@ __device__ __forceinline__ bool wait_flag(const int* addr, int epoch, long long 
     }
     __nanosleep(64);
   }
+  return true;
+}
+
+// bounded wait for the first `n` flag words of a 16-word group (the slices of one 128-row block
+// of the pushed gather), polled with 16-byte loads; ends with the acquiring fence
+__device__ __forceinline__ bool wait_flags16(const int* addr, int n, int epoch, long long budget,
+                                             volatile int* abort_flag) {
+  const long long start = clock64();
+  int spins = 0;
+  for (;;) {
+    bool all = true;
+    for (int i = 0; i < n; i += 4) {
+      int4 v;
+      asm volatile("ld.volatile.global.v4.s32 {%0, %1, %2, %3}, [%4];"
+                   : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(addr + i) : "memory");
+      all = all && v.x >= epoch && (i + 1 >= n || v.y >= epoch) && (i + 2 >= n || v.z >= epoch) &&
+            (i + 3 >= n || v.w >= epoch);
+    }
+    if (all) break;
+    if ((++spins & 0x3f) == 0) {
+      if (*abort_flag != 0) return false;
+      if (clock64() - start > budget) {
+        *abort_flag = 1;
+        return false;
+      }
+    }
+    __nanosleep(64);
+  }
+  __threadfence_system();
   return true;
 }
 
@@ -759,7 +790,11 @@ comm_gemm_kernel(const __grid_constant__ SegMaps maps_a, const __grid_constant__
               t_wait = gtimer();
               if (!traced_first) g_comm_trace[(blockIdx.x % kTraceCtas) * kTraceSlots + 3] = t_wait;
             }
-            if (!wait_flag(p.chunk_flags + m_blk, p.epoch, p.wait_cycles, abort_flag)) {
+            const bool arrived =
+                pushed ? wait_flags16(p.chunk_flags + m_blk * kSliceFlagStride, p.ag_slices, p.epoch,
+                                      p.wait_cycles, abort_flag)
+                       : wait_flag(p.chunk_flags + m_blk, p.epoch, p.wait_cycles, abort_flag);
+            if (!arrived) {
               ok = false;
               break;
             }
@@ -846,53 +881,98 @@ comm_gemm_kernel(const __grid_constant__ SegMaps maps_a, const __grid_constant__
     // thread) and published block by block; the producer warps of all CTAs
     // read staged blocks with local TMA loads.
     if (pushed && p.world > 1) {
-      // Pushed gather: every copier warp of every rank is an independent sender.  It takes
-      // slices of this rank's OWN shard (local loads), stores them into the staging slots of
-      // all ranks - one multicast store through the switch, or one store per rank - and
-      // counts the slice in; whoever completes a 128-row block publishes its flag on every
-      // rank.  Stores need no answer, so nothing waits for an NVLink round trip except the
-      // fence in front of the count, and that wait is per warp: the other warps keep sending.
-      // Slices are handed out in row order across the SMs, so blocks complete in order and
-      // the main loops of all ranks start on block 0 of every owner while the rest is in flight.
+      // Pushed gather.  Copier warps 0 .. CW - 2 are senders: each takes 128 / slices-row
+      // slices of this rank's OWN shard in row order (local loads) and stores them into the
+      // staging slots of all ranks - one multicast store through the switch, or one store
+      // per rank.  Stores need no answer, so a sender never waits for an NVLink round trip:
+      // it hands the slice to the publisher through shared memory and goes on; the link's
+      // back pressure paces the senders, and because slices go out in row order they also
+      // arrive in row order.  The last copier warp is the publisher: whenever senders have
+      // handed over new slices it runs ONE system-scope fence - which, being cumulative,
+      // covers the senders' stores that it observed through shared memory - and then raises
+      // the flag of every covered slice on every rank.  (A fence per slice in the sending
+      // warp measured 50 us of stall per round at 8 GPUs.)  The main loops of all ranks wait
+      // for the `slices` flags of a 128-row block.
       const int cw = warp - 6;
+      constexpr int kSenders = CW - 1;
+      __shared__ int s_issued[CW];       // slices handed over by each sender; [CW - 1]: senders done
       const int slices = p.ag_slices;
       const int slice_rows = CBM / slices;
-      int* chunk_count = p.chunk_flags + kChunkCountOffset;
       const int slice_vec = slice_rows * (p.row_bytes / 16);
-      // Nobody's slot may be written before its owner has entered this operation: its earlier
-      // kernels, which read the slot's previous contents, are complete by then.
-      int entered = 1;
-      if (lane < p.world && lane != p.rank)
-        entered = wait_flag(ready + lane, p.epoch, p.wait_cycles, abort_flag) ? 1 : 0;
-      const bool ok = __all_sync(0xffffffffu, entered) != 0;
-      const int n_copiers = static_cast<int>(gridDim.x) * CW;
       const int units = blocks_per_owner * slices;
-      if (cw == 0 && lane == 0) trace_mark(p.trace, 1);
-      for (int u = cw * static_cast<int>(gridDim.x) + static_cast<int>(blockIdx.x);
-           u < units && ok; u += n_copiers) {
-        const int b = u / slices, sl = u - b * slices;
-        const int64_t off = (static_cast<int64_t>(b) * CBM + sl * slice_rows) * p.row_bytes;
-        const int m_blk = p.rank * blocks_per_owner + b;
-        SLAPO_DBG_CHECK(off + static_cast<int64_t>(slice_rows) * p.row_bytes <=
-                                static_cast<int64_t>(p.seg_len) * p.row_bytes &&
-                            m_blk < kChunkCountOffset && (off & 15) == 0,
-                        p.status)
-        const uint4* src = reinterpret_cast<const uint4*>(
-            static_cast<const uint8_t*>(p.seg_src[p.rank]) + off);
-        const int64_t dst_off = static_cast<int64_t>(p.rank) * p.seg_len * p.row_bytes + off;
-        if (p.ag_inflight == 16) push_vecs<16>(p, src, dst_off, slice_vec, lane);
-        else push_vecs<8>(p, src, dst_off, slice_vec, lane);
-        __threadfence_system();
-        __syncwarp();
-        if (lane == 0) {
-          const int prev = slices > 1 ? atomicAdd(chunk_count + m_blk, 1) : 0;
-          if (prev + 1 == slices) {
-            if (slices > 1) atomicExch(chunk_count + m_blk, 0);
-            for (int r = 0; r < p.world; ++r) st_release_sys(p.peer_chunk_flags[r] + m_blk, p.epoch);
+      const int stride = static_cast<int>(gridDim.x) * kSenders;
+      if (cw == 0 && lane < CW) s_issued[lane] = 0;
+      asm volatile("bar.sync 2, %0;" ::"n"(CW * 32) : "memory");
+      if (cw < kSenders) {
+        // Nobody's slot may be written before its owner has entered this operation: its
+        // earlier kernels, which read the slot's previous contents, are complete by then.
+        int entered = 1;
+        if (lane < p.world && lane != p.rank)
+          entered = wait_flag(ready + lane, p.epoch, p.wait_cycles, abort_flag) ? 1 : 0;
+        const bool ok = __all_sync(0xffffffffu, entered) != 0;
+        if (cw == 0 && lane == 0) trace_mark(p.trace, 1);
+        int k = 0;
+        for (int u = cw * static_cast<int>(gridDim.x) + static_cast<int>(blockIdx.x);
+             u < units && ok; u += stride, ++k) {
+          const int b = u / slices, sl = u - b * slices;
+          const int64_t off = (static_cast<int64_t>(b) * CBM + sl * slice_rows) * p.row_bytes;
+          SLAPO_DBG_CHECK(off + static_cast<int64_t>(slice_rows) * p.row_bytes <=
+                                  static_cast<int64_t>(p.seg_len) * p.row_bytes && (off & 15) == 0,
+                          p.status)
+          const uint4* src = reinterpret_cast<const uint4*>(
+              static_cast<const uint8_t*>(p.seg_src[p.rank]) + off);
+          const int64_t dst_off = static_cast<int64_t>(p.rank) * p.seg_len * p.row_bytes + off;
+          if (p.ag_inflight == 16) push_vecs<16>(p, src, dst_off, slice_vec, lane);
+          else push_vecs<8>(p, src, dst_off, slice_vec, lane);
+          __syncwarp();
+          if (lane == 0) {
+            __threadfence_block();      // release at CTA scope: the hand-over below follows the stores
+            *reinterpret_cast<volatile int*>(&s_issued[cw]) = k + 1;
           }
         }
+        __syncwarp();
+        if (lane == 0) {
+          __threadfence_block();
+          atomicAdd(&s_issued[CW - 1], 1);
+        }
+      } else if (lane == 0) {
+        int published[kSenders];
+#pragma unroll
+        for (int w = 0; w < kSenders; ++w) published[w] = 0;
+        const long long start = clock64();
+        for (;;) {
+          const int done = *reinterpret_cast<volatile int*>(&s_issued[CW - 1]);
+          int snap[kSenders];
+          bool any = false;
+#pragma unroll
+          for (int w = 0; w < kSenders; ++w) {
+            snap[w] = *reinterpret_cast<volatile int*>(&s_issued[w]);
+            any = any || snap[w] > published[w];
+          }
+          if (!any) {
+            if (done == kSenders || *abort_flag != 0) break;
+            if (clock64() - start > p.wait_cycles + tc::kWaitCycles) break;   // senders set the error
+            __nanosleep(200);
+            continue;
+          }
+          // acquire (the hand-overs read above) + release (the flags below) in one fence;
+          // its cumulativity extends to the senders' stores
+          __threadfence_system();
+#pragma unroll
+          for (int w = 0; w < kSenders; ++w) {
+            for (int k = published[w]; k < snap[w]; ++k) {
+              const int u = (k * kSenders + w) * static_cast<int>(gridDim.x) + static_cast<int>(blockIdx.x);
+              const int b = u / slices, sl = u - b * slices;
+              const int idx = (p.rank * blocks_per_owner + b) * kSliceFlagStride + sl;
+              SLAPO_DBG_CHECK(idx >= 0 && idx < 2 * kChunkCountOffset, p.status)
+              for (int r = 0; r < p.world; ++r)
+                *reinterpret_cast<volatile int*>(p.peer_chunk_flags[r] + idx) = p.epoch;
+            }
+            published[w] = snap[w];
+          }
+        }
+        trace_mark(p.trace, 2);     // every slice of this CTA is published
       }
-      if (cw == CW - 1 && lane == 0) trace_mark(p.trace, 2);
     } else if (staged && p.world > 1) {
       const int ct = threadIdx.x - 192;
       // A 128-row block is copied as `slices` slices by (usually) different CTAs, units in
@@ -1243,14 +1323,14 @@ static CopyTuning copy_tuning() {
 }
 
 // The pushed gather's tuning, SLAPO_B200_AG_PUSH="slices,inflight": slices per 128-row block
-// (1 .. 32, a power of two - one slice is one warp's unit of work) and 16-byte loads in flight
+// (1 .. 16, a power of two - one slice is one warp's unit of work) and 16-byte loads in flight
 // per lane (8 or 16).
 static CopyTuning push_tuning() {
   static const CopyTuning t = [] {
     CopyTuning v{16, 16};
     if (const char* e = std::getenv("SLAPO_B200_AG_PUSH")) {
       int a = 0, b = 0;
-      if (std::sscanf(e, "%d,%d", &a, &b) == 2 && a >= 1 && a <= 32 && (a & (a - 1)) == 0 &&
+      if (std::sscanf(e, "%d,%d", &a, &b) == 2 && a >= 1 && a <= kSliceFlagStride && (a & (a - 1)) == 0 &&
           (b == 8 || b == 16)) {
         v.slices = a;
         v.inflight = b;
@@ -1285,6 +1365,8 @@ int launch_comm_gemm(void* const* a_ptrs, void* const* b_ptrs, int M, int N, int
     // counters (zero when allocated, flags only grow), then the gathered operand [M, K]
     if (a_mn || stage_peers == nullptr || lda != K || seg_len % CBM != 0 || seg_len * world != M)
       return 1;
+    // the header holds kSliceFlagStride flag words per 128-row block
+    if ((M / CBM) * kSliceFlagStride > 2 * kChunkCountOffset) return 6;
     for (int r = 0; r < world; ++r)
       if (stage_peers[r] == nullptr || (reinterpret_cast<uintptr_t>(stage_peers[r]) & 15)) return 1;
     stage_dst = static_cast<uint8_t*>(stage_peers[rank]) + kRecvHeaderBytes;

@@ -107,6 +107,9 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
   constexpr int kBlkBytes = 128 * 128;
   constexpr int kDBlocks = D / 64;
   constexpr int kStages = D == 64 ? 2 : 1;
+  // D = 64: two P / dS buffers, so that the softmax warps write the tiles of query block j + 1
+  // while the tensor core still reads those of block j (dV, dK, dQ); D = 128 has no room
+  constexpr int kPB = D == 64 ? 2 : 1;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>(
       (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
@@ -114,9 +117,10 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
   uint8_t* s_v = s_k + kTileBytes;
   uint8_t* s_q = s_v + kTileBytes;                  // kStages
   uint8_t* s_do = s_q + kStages * kTileBytes;       // kStages
-  uint8_t* s_p = s_do + kStages * kTileBytes;       // 2 blocks
-  uint8_t* s_ds = s_p + 2 * kBlkBytes;              // 2 blocks
-  uint64_t* bars = reinterpret_cast<uint64_t*>(s_ds + 2 * kBlkBytes);
+  uint8_t* s_p = s_do + kStages * kTileBytes;       // kPB buffers of [P: 2 blocks | dS: 2 blocks]
+  uint8_t* s_ds = s_p + 2 * kBlkBytes;
+  constexpr int kPdsBytes = 4 * kBlkBytes;          // distance between the P / dS buffers
+  uint64_t* bars = reinterpret_cast<uint64_t*>(s_p + kPB * kPdsBytes);
   uint64_t* kv_full = bars;            // 1
   uint64_t* qdo_full = bars + 1;       // kStages (<= 2)
   uint64_t* qdo_empty = bars + 3;      // kStages
@@ -229,18 +233,27 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
       for (int it = 0; it < n_iter && ok; ++it) {
         const int st = it % kStages;
         if (!tc::mbar_wait(pds_full, it & 1, abort_flag)) { ok = false; break; }
+        tc::fence_after_sync();
+        if constexpr (kPB == 2) {
+          // S / dP of the next query block first: the softmax warps have taken block `it` out
+          // of tensor memory, and their work on block it + 1 then runs under the three
+          // products of block `it` below (which read the other P / dS buffer)
+          if (it + 1 < n_iter && !issue_s_dp(it + 1)) { ok = false; break; }
+        }
         if (D == 64 && it > 0 && !tc::mbar_wait(dq_empty, (it - 1) & 1, abort_flag)) { ok = false; break; }
         tc::fence_after_sync();
         const uint32_t q_addr = tc::smem_u32(s_q + st * kTileBytes);
         const uint32_t do_addr = tc::smem_u32(s_do + st * kTileBytes);
+        const uint32_t pb_addr = p_addr + (it % kPB) * kPdsBytes;
+        const uint32_t dsb_addr = ds_addr + (it % kPB) * kPdsBytes;
         // dV += P^T dO ; dK += dS^T Q : A = [q rows x keys] read M-major (M = keys, K = q rows),
         // B = [q rows x D] read N-major.  16 query rows per instruction.
 #pragma unroll
         for (int kk = 0; kk < 128 / 16; ++kk) {
           const uint64_t b_do = tc::smem_desc(do_addr + kk * 2048, kBlkBytes, 1024);
           const uint64_t b_q = tc::smem_desc(q_addr + kk * 2048, kBlkBytes, 1024);
-          const uint64_t a_p = tc::smem_desc(p_addr + kk * 2048, kBlkBytes, 1024);
-          const uint64_t a_ds = tc::smem_desc(ds_addr + kk * 2048, kBlkBytes, 1024);
+          const uint64_t a_p = tc::smem_desc(pb_addr + kk * 2048, kBlkBytes, 1024);
+          const uint64_t a_ds = tc::smem_desc(dsb_addr + kk * 2048, kBlkBytes, 1024);
           const uint32_t accum = (it | kk) != 0 ? 1u : 0u;
           tc::umma_f16(tmem_base + kColDV, a_p, b_do, p.idesc_dvk, accum);
           tc::umma_f16(tmem_base + kColDK, a_ds, b_q, p.idesc_dvk, accum);
@@ -249,13 +262,15 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
 #pragma unroll
         for (int kk = 0; kk < 128 / 16; ++kk) {
           const uint64_t a_ds =
-              tc::smem_desc(ds_addr + (kk >> 2) * kBlkBytes + (kk & 3) * 32, 16, 1024);
+              tc::smem_desc(dsb_addr + (kk >> 2) * kBlkBytes + (kk & 3) * 32, 16, 1024);
           const uint64_t b_k = tc::smem_desc(k_addr + kk * 2048, kBlkBytes, 1024);
           tc::umma_f16(tmem_base + kColDQ, a_ds, b_k, p.idesc_dq, kk != 0 ? 1u : 0u);
         }
         tc::umma_commit(dq_full);
         tc::umma_commit(&qdo_empty[st]);
-        if (it + 1 < n_iter && !issue_s_dp(it + 1)) { ok = false; break; }
+        if constexpr (kPB == 1) {
+          if (it + 1 < n_iter && !issue_s_dp(it + 1)) { ok = false; break; }
+        }
       }
       if (ok) tc::umma_commit(acc_full);
     }
@@ -274,6 +289,41 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
     const float out_scale = p.scale * inv_keep;
     const int sk16 = (p.Sk + 15) >> 4;
     bool ok = true;
+    // dQ tile of query block `j`: out of tensor memory into this key tile's fp32 partial.
+    // Reductions into one accumulator run at the rate of the L2 atomic units; each key tile
+    // stores into its own partial instead (the conversion kernel adds them up).
+    auto dq_readout = [&](int j) -> bool {
+      if (!tc::mbar_wait_warp(dq_full, j & 1, abort_flag)) return false;
+      tc::fence_after_sync();
+      const int row = (i_begin + j) * 128 + r_in;
+      const bool row_ok = row < p.Sq;
+      const bool dq_sliced = p.dq_slice_stride != 0;
+      float* dq_dst = p.dq_accum + static_cast<int64_t>(blockIdx.x) * p.dq_slice_stride +
+                      ((static_cast<int64_t>(batch) * p.Sq + min(row, p.Sq - 1)) * p.H + head) * p.Dr;
+#pragma unroll
+      for (int cc = 0; cc < D / 64; ++cc) {
+        const int c = half * (D / 64) + cc;   // this warp's share of the D columns
+        uint32_t r[32];
+        tc::tmem_ld_x32(tmem_base + kColDQ + c * 32 + lane_sel, r);
+        tc::tmem_ld_wait();
+        if (row_ok) {
+#pragma unroll
+          for (int g = 0; g < 8; ++g) {
+            if (c * 32 + g * 4 >= p.Dr) break;
+            const float4 val = make_float4(__uint_as_float(r[g * 4]) * out_scale,
+                                           __uint_as_float(r[g * 4 + 1]) * out_scale,
+                                           __uint_as_float(r[g * 4 + 2]) * out_scale,
+                                           __uint_as_float(r[g * 4 + 3]) * out_scale);
+            if (dq_sliced) *reinterpret_cast<float4*>(dq_dst + c * 32 + g * 4) = val;
+            else red_add_v4(dq_dst + c * 32 + g * 4, val.x, val.y, val.z, val.w);
+          }
+        }
+      }
+      tc::fence_before_sync();
+      __syncwarp();
+      if (lane == 0) tc::mbar_arrive(dq_empty);
+      return true;
+    };
     for (int it = 0; it < n_iter && ok; ++it) {
       const int row = (i_begin + it) * 128 + r_in;
       const bool row_ok = row < p.Sq;
@@ -293,8 +343,8 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
       if (!row_ok || lse2 == -INFINITY) key_limit = 0;
       if (!tc::mbar_wait_warp(sdp_full, it & 1, abort_flag)) { ok = false; break; }
       tc::fence_after_sync();
-      uint8_t* p_row = s_p + r_in * 128;
-      uint8_t* ds_row = s_ds + r_in * 128;
+      uint8_t* p_row = s_p + (it % kPB) * kPdsBytes + r_in * 128;
+      uint8_t* ds_row = s_ds + (it % kPB) * kPdsBytes + r_in * 128;
 #pragma unroll 1
       for (int c = 2 * half; c < 2 * half + 2; ++c) {
         uint32_t s_raw[32], dp_raw[32];
@@ -365,37 +415,17 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
       tc::fence_proxy_async();
       __syncwarp();
       if (lane == 0) tc::mbar_arrive(pds_full);
-      // dQ tile of this query block
-      if (!tc::mbar_wait_warp(dq_full, it & 1, abort_flag)) { ok = false; break; }
-      tc::fence_after_sync();
-      // Reductions into one accumulator run at the rate of the L2 atomic units, which for
-      // four or eight key tiles per query row costs more than the whole rest of the kernel:
-      // each key tile stores into its own partial instead.
-      const bool dq_sliced = p.dq_slice_stride != 0;
-      float* dq_dst = p.dq_accum + static_cast<int64_t>(blockIdx.x) * p.dq_slice_stride +
-                      ((static_cast<int64_t>(batch) * p.Sq + min(row, p.Sq - 1)) * p.H + head) * p.Dr;
-#pragma unroll
-      for (int cc = 0; cc < D / 64; ++cc) {
-        const int c = half * (D / 64) + cc;   // this warp's share of the D columns
-        uint32_t r[32];
-        tc::tmem_ld_x32(tmem_base + kColDQ + c * 32 + lane_sel, r);
-        tc::tmem_ld_wait();
-        if (row_ok) {
-#pragma unroll
-          for (int g = 0; g < 8; ++g) {
-            if (c * 32 + g * 4 >= p.Dr) break;
-            const float4 val = make_float4(__uint_as_float(r[g * 4]) * out_scale,
-                                           __uint_as_float(r[g * 4 + 1]) * out_scale,
-                                           __uint_as_float(r[g * 4 + 2]) * out_scale,
-                                           __uint_as_float(r[g * 4 + 3]) * out_scale);
-            if (dq_sliced) *reinterpret_cast<float4*>(dq_dst + c * 32 + g * 4) = val;
-            else red_add_v4(dq_dst + c * 32 + g * 4, val.x, val.y, val.z, val.w);
-          }
-        }
+      if constexpr (kPB == 2) {
+        // with two P / dS buffers the tensor core is already on S / dP of block it + 1: take
+        // the dQ tile of the PREVIOUS block out now, the one of this block after the next
+        // block's softmax gradient
+        if (it > 0 && !dq_readout(it - 1)) { ok = false; break; }
+      } else {
+        if (!dq_readout(it)) { ok = false; break; }
       }
-      tc::fence_before_sync();
-      __syncwarp();
-      if (lane == 0) tc::mbar_arrive(dq_empty);
+    }
+    if constexpr (kPB == 2) {
+      if (ok && n_iter > 0) ok = dq_readout(n_iter - 1);
     }
     // dK / dV of this key tile: thread = key row
     if (ok && n_iter > 0) ok = tc::mbar_wait_warp(acc_full, 0, abort_flag);
@@ -509,7 +539,9 @@ template <int D, bool kPlain>
 static int launch_bwd_d(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv,
                         const CUtensorMap& tdo, const FlashBwdParams& p, cudaStream_t stream) {
   constexpr int kStages = D == 64 ? 2 : 1;
-  constexpr int kSmem = (2 + 2 * kStages) * 128 * D * 2 + 4 * 128 * 128 + 12 * 8 + 128 * 4 + 1024;
+  constexpr int kPB = D == 64 ? 2 : 1;
+  constexpr int kSmem = (2 + 2 * kStages) * 128 * D * 2 + kPB * 4 * 128 * 128 + 12 * 8 + 128 * 4 + 1024;
+  static_assert(kSmem <= 227 * 1024, "flash backward: shared memory over the per-CTA limit");
   auto kernel = flash_bwd_kernel<D, kPlain>;
   static bool configured = false;
   if (!configured) {

@@ -237,6 +237,13 @@ def push_enabled(ctx) -> bool:
     return bool(getattr(ctx, "nvls", False))
 
 
+def _can_push(ctx, shard_rows) -> bool:
+    """The pushed gather handles whole 128-row blocks and at most 1024 of them in total (its
+    slot header holds 16 flag words per block)."""
+    return (ctx.world > 1 and shard_rows % 128 == 0 and shard_rows * ctx.world // 128 <= 1024
+            and push_enabled(ctx))
+
+
 def ag_gemm_pushed(ctx, x_shard, w, bias=None, act=-1, b_mn=False, keep=False):
     """``all_gather(x_shard) @ w.T`` with the gather pushed by the owners (see
     ``comm_gemm.cu``, gather mode 5).  Returns ``(y, gathered, token)``: with ``keep`` the
@@ -385,7 +392,7 @@ class _AGLinear(torch.autograd.Function):
         ctx.sctx = sctx
         x_shard = x_shard.contiguous()
         ctx.token = None
-        if push_enabled(sctx) and x_shard.shape[0] % 128 == 0 and sctx.world > 1:
+        if _can_push(sctx, x_shard.shape[0]):
             # no backward will run (evaluation, the first pass of a checkpointed layer): keep nothing
             keep = any(ctx.needs_input_grad[:3])
             y, full_x, ctx.token = ag_gemm_pushed(sctx, x_shard, w, bias, keep=keep)
@@ -439,7 +446,7 @@ class _RSLinear(torch.autograd.Function):
         t, kl = x.shape
         # dX = all_gather(dYs) @ W: A rows gathered inside the GEMM, B = W read N-major
         token = None
-        if push_enabled(sctx) and ts % 128 == 0 and sctx.world > 1:
+        if _can_push(sctx, ts):
             dx, full_dy, token = ag_gemm_pushed(sctx, dy_shard, w, None, b_mn=True, keep=True)
         else:
             dx, full_dy = ag_gemm(sctx, dy_shard, w, None, name="ag_dy_bwd", b_mn=True,

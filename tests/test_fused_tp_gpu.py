@@ -70,17 +70,18 @@ def test_all_gather_gemm_pushed(world, n, ts, keep):
         for q in range(world):
             data(q).copy_(full)
             data(q)[r * ts:(r + 1) * ts].zero_()          # what rank r has to deliver
-        flags = ctx._buffers[name][r][:t // 128 * 4].view(torch.int32)
+        # 16 flag words per 128-row block (one per 8-row slice)
+        flags = ctx._buffers[name][r][:t // 128 * 64].view(torch.int32)
         flags.fill_(ctx.epoch + 1)                         # the other owners' blocks "arrived"
-        flags[r * (ts // 128):(r + 1) * (ts // 128)] = 0
+        flags[r * (ts // 128) * 16:(r + 1) * (ts // 128) * 16] = 0
         ctx.preset_flags(ctx.epoch + 1)
         y, gathered, token = ft.ag_gemm_pushed(ctx, shards[r], w[r], bias, keep=keep)
         assert native.ops().device_status() == 0
         _close(y, full.float() @ w[r].float().t() + bias.float(), k)
         for q in range(world):
             assert torch.equal(data(q), full), f"rank {r}'s rows in rank {q}'s slot"
-            fl = ctx._buffers[name][q][:t // 128 * 4].view(torch.int32)
-            assert bool((fl[r * (ts // 128):(r + 1) * (ts // 128)] == ctx.epoch).all())
+            fl = ctx._buffers[name][q][:t // 128 * 64].view(torch.int32)
+            assert bool((fl[r * (ts // 128) * 16:(r + 1) * (ts // 128) * 16] == ctx.epoch).all())
         if keep:
             assert token == (nbytes, 0) and torch.equal(gathered, full)
             ft.stage_pool(ctx).release(token)
