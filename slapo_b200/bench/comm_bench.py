@@ -121,19 +121,19 @@ def main():
         _report(rank, f"ag_gemm[{label}]", us, 2.0 * t * n * k, link, shape=[t, n, k], world=world)
         _trace_summary(rank, f"ag_gemm[{label}]")
 
-        def push():
-            return ft.ag_gemm_pushed(ctx, x, w)[0]
-
-        us = _time(push, args.iters)
-        y_push, gathered, token = ft.ag_gemm_pushed(ctx, x, w, keep=True)
         dist.all_gather_into_tensor(full, x)
         ref = F.linear(full, w)
-        err = float((y_push.float() - ref.float()).abs().max() / ref.float().abs().max())
-        same = bool(torch.equal(gathered, full))
-        ft.stage_pool(ctx).release(token)
-        _report(rank, f"ag_gemm_push[{label}]", us, 2.0 * t * n * k, link, shape=[t, n, k],
-                world=world, max_rel_err=round(err, 5), gathered_equal=same)
-        _trace_summary(rank, f"ag_gemm_push[{label}]")
+        # owner-pushed forms: "push" inside the GEMM kernel, "gather" = push kernel + pair GEMM
+        for mode in ("push", "gather"):
+            us = _time(lambda: ft.ag_gemm_pushed(ctx, x, w, mode=mode)[0], args.iters)
+            y_push, gathered, token = ft.ag_gemm_pushed(ctx, x, w, keep=True, mode=mode)
+            err = float((y_push.float() - ref.float()).abs().max() / ref.float().abs().max())
+            same = bool(torch.equal(gathered, full))
+            ft.stage_pool(ctx).release(token)
+            _report(rank, f"ag_gemm_{mode}[{label}]", us, 2.0 * t * n * k, link, shape=[t, n, k],
+                    world=world, max_rel_err=round(err, 5), gathered_equal=same)
+            if mode == "push":
+                _trace_summary(rank, f"ag_gemm_push[{label}]")
 
         def base():
             dist.all_gather_into_tensor(full, x)

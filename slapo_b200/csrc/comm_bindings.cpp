@@ -73,6 +73,20 @@ void peer_gather(std::vector<int64_t> src_ptrs, int64_t dst_ptr, int64_t seg_byt
   TORCH_CHECK(rc == 0, "peer_gather: launch refused (code ", rc, ")");
 }
 
+void peer_push_gather(int64_t src_ptr, std::vector<int64_t> dst_ptrs, int64_t dst_mc,
+                      int64_t seg_bytes, int64_t world, int64_t rank, int64_t epoch,
+                      int64_t flags_ptr, std::vector<int64_t> peer_flags, double wait_seconds) {
+  auto dst = to_ptrs<void*>(dst_ptrs);
+  auto pf = to_ptrs<int*>(peer_flags);
+  const int dev = at::cuda::current_device();
+  int rc = slapo::launch_peer_push_gather(
+      reinterpret_cast<const void*>(src_ptr), dst.data(), reinterpret_cast<void*>(dst_mc), seg_bytes,
+      static_cast<int>(world), static_cast<int>(rank), static_cast<int>(epoch),
+      reinterpret_cast<int*>(flags_ptr), peer_flags.empty() ? nullptr : pf.data(),
+      slapo_status_ptr(dev), wait_seconds, at::cuda::getCurrentCUDAStream().stream());
+  TORCH_CHECK(rc == 0, "peer_push_gather: launch refused (code ", rc, ")");
+}
+
 int dtype16(const at::Tensor& t) {
   TORCH_CHECK(t.scalar_type() == at::kBFloat16 || t.scalar_type() == at::kHalf,
               "fused data-parallel kernels need bf16 or fp16 parameters");
@@ -189,6 +203,9 @@ void register_comm_ops(torch::Library& m) {
         "int chunk_flags_ptr, int recv_mc, int out_mc, int[] stage_peers, int stage_mc) -> ()",
         &comm_gemm);
   m.def("comm_trace() -> Tensor", &comm_trace);
+  m.def("peer_push_gather(int src_ptr, int[] dst_ptrs, int dst_mc, int seg_bytes, int world, "
+        "int rank, int epoch, int flags_ptr, int[] peer_flags, float wait_seconds) -> ()",
+        &peer_push_gather);
   m.def("peer_gather(int[] src_ptrs, int dst_ptr, int seg_bytes, int world, int rank, int epoch, "
         "int flags_ptr, int[] peer_flags, float wait_seconds) -> ()", &peer_gather);
 }

@@ -575,9 +575,8 @@ __device__ __forceinline__ void reduce_span_mc(const CommGemmParams& p, int rows
 
 // One group of 128 threads (named barrier `bar_id`, `gt` = thread index inside the group) takes
 // reduction units of this CTA until none is left.  A unit is a 32-row slice of a 128-row block of
-// this rank's rows; the CTA's units are u = blockIdx.x + k * gridDim.x in block order and `next_k`
-// is the CTA-wide counter that hands out k, so that the reducer warps (from the start) and the
-// epilogue warps (once their tiles are done) share the work.  A unit is reduced when the block's
+// this rank's rows; the reducer warps (from the start) and the epilogue warps (once their tiles
+// are done) of all CTAs share the units.  A unit is reduced when the block's
 // flags from every source rank have arrived.
 __device__ __forceinline__ void reduce_units(const CommGemmParams& p, int rows_per_rank,
                                              int blocks_per_owner, int gt, int bar_id, int* next_k,
@@ -587,7 +586,11 @@ __device__ __forceinline__ void reduce_units(const CommGemmParams& p, int rows_p
   const int units = blocks_per_owner * kRedSlices;
   for (;;) {
     if (gt == 0) {
-      const int u = static_cast<int>(blockIdx.x) + atomicAdd(next_k, 1) * static_cast<int>(gridDim.x);
+      // units are handed out in block order by one counter for the whole GPU (word 40 of the
+      // flag pad, reset by the last CTA to leave): whichever group is free takes the lowest
+      // outstanding unit, so that no CTA is left with an extra unit at the end
+      (void)next_k;
+      const int u = atomicAdd(p.flags + 40, 1);
       vote[0] = u;
       vote[1] = *abort_flag != 0 ? 0 : (u < units ? 1 : -1);   // 0 stop (error), -1 no unit left
       vote[2] = *pipe_free;   // the main loop of this CTA is over: its shared memory is free
@@ -1197,6 +1200,14 @@ comm_gemm_kernel(const __grid_constant__ SegMaps maps_a, const __grid_constant__
   __syncthreads();
   trace_mark(threadIdx.x == 0 ? p.trace : 0, 6);
   if (threadIdx.x == 0 && *abort_flag != 0 && p.status != nullptr) atomicExch(p.status, 4);
+  if (scatter && threadIdx.x == 0) {
+    // the last CTA to leave clears the reduction-unit counter for the next launch
+    const int prev = atomicAdd(p.flags + 41, 1);
+    if (prev + 1 == static_cast<int>(gridDim.x)) {
+      atomicExch(p.flags + 41, 0);
+      atomicExch(p.flags + 40, 0);
+    }
+  }
   if (warp == 1) {
     tc::fence_after_sync();
     tc::tmem_dealloc(tmem_base, kTmemCols);
@@ -1258,6 +1269,114 @@ int launch_peer_gather(void* const* src_ptrs, void* dst, int64_t seg_bytes, int 
   p.wait_cycles = static_cast<long long>(wait_seconds * 1.9e9);
   count_launch();
   peer_gather_kernel<<<sm_count() * 2, 256, 0, stream>>>(p);
+  return cudaGetLastError() == cudaSuccess ? 0 : 4;
+}
+
+// ------------------------------------------------------------------------ //
+// All-gather by peer stores: every rank writes its own segment into the gathered buffer of ALL
+// ranks at offset rank * seg - one multicast store per 16 bytes where the buffers have an
+// NVSwitch address, one store per rank otherwise - and leaves when every rank's segment has
+// landed in ITS buffer.  Stores need no answer, so the copy runs at the rate of the links
+// (8 GPUs, 32 MB per rank: 377 us = 623 GB/s into every GPU) with a few thousand threads.
+// Protocol (flag pad words: ready[r] = r, done[r] = 8 + r, CTA counter = 42):
+//   1. announce `epoch` in ready[rank] on every rank; wait for all ranks' ready - nobody's
+//      buffer is written before its owner has entered (its readers of the previous contents,
+//      earlier kernels of its stream, are complete by then);
+//   2. copy; every thread fences (system scope), the last CTA to finish raises done[rank] on
+//      every rank;
+//   3. wait until done[r] >= epoch for all r: the kernel's end means "gathered".
+struct PushGatherParams {
+  const void* src;
+  void* mc_dst;                 // multicast address of the gathered buffers (or null)
+  void* peer_dst[kMaxRanks];
+  int64_t seg_bytes;
+  int world, rank, epoch;
+  int* flags;
+  int* peer_flags[kMaxRanks];
+  int* status;
+  long long wait_cycles;
+};
+
+__global__ void __launch_bounds__(512) peer_push_gather_kernel(const PushGatherParams p) {
+  __shared__ int s_abort;
+  __shared__ int s_ok;
+  if (threadIdx.x == 0) {
+    s_abort = 0;
+    s_ok = 1;
+    if (blockIdx.x == 0)
+      for (int r = 0; r < p.world; ++r) st_release_sys(p.peer_flags[r] + p.rank, p.epoch);
+  }
+  __syncthreads();
+  if (threadIdx.x < p.world && threadIdx.x != p.rank &&
+      !wait_flag(p.flags + threadIdx.x, p.epoch, p.wait_cycles, &s_abort))
+    s_ok = 0;
+  __syncthreads();
+  if (s_ok) {
+    const int64_t n_vec = p.seg_bytes / 16;
+    const uint4* src = static_cast<const uint4*>(p.src);
+    const int64_t base = static_cast<int64_t>(p.rank) * p.seg_bytes;
+    const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
+    int64_t v = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+    for (; v + 3 * stride < n_vec; v += 4 * stride) {
+      uint4 t[4];
+#pragma unroll
+      for (int q = 0; q < 4; ++q) t[q] = __ldcg(src + v + q * stride);
+      if (p.mc_dst != nullptr) {
+#pragma unroll
+        for (int q = 0; q < 4; ++q)
+          mc_st(static_cast<uint8_t*>(p.mc_dst) + base + (v + q * stride) * 16, t[q]);
+      } else {
+        for (int rr = 0; rr < p.world; ++rr) {
+          const int r = (p.rank + 1 + rr) % p.world;
+          uint4* d = reinterpret_cast<uint4*>(static_cast<uint8_t*>(p.peer_dst[r]) + base);
+#pragma unroll
+          for (int q = 0; q < 4; ++q) d[v + q * stride] = t[q];
+        }
+      }
+    }
+    for (; v < n_vec; v += stride) {
+      const uint4 t = __ldcg(src + v);
+      if (p.mc_dst != nullptr) {
+        mc_st(static_cast<uint8_t*>(p.mc_dst) + base + v * 16, t);
+      } else {
+        for (int r = 0; r < p.world; ++r)
+          reinterpret_cast<uint4*>(static_cast<uint8_t*>(p.peer_dst[r]) + base)[v] = t;
+      }
+    }
+    __threadfence_system();
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    // the last CTA tells every rank that this rank's segment is in place
+    const int prev = atomicAdd(p.flags + 42, 1);
+    if (prev + 1 == static_cast<int>(gridDim.x)) {
+      atomicExch(p.flags + 42, 0);
+      __threadfence_system();
+      if (s_abort == 0 && s_ok)
+        for (int r = 0; r < p.world; ++r) st_release_sys(p.peer_flags[r] + 8 + p.rank, p.epoch);
+    }
+  }
+  if (s_ok && threadIdx.x < p.world && !wait_flag(p.flags + 8 + threadIdx.x, p.epoch, p.wait_cycles, &s_abort))
+    s_ok = 0;
+  __syncthreads();
+  if (threadIdx.x == 0 && (s_abort != 0 || s_ok == 0) && p.status != nullptr) atomicExch(p.status, 4);
+}
+
+int launch_peer_push_gather(const void* src, void* const* dst_ptrs, void* dst_mc, int64_t seg_bytes,
+                            int world, int rank, int epoch, int* flags, int* const* peer_flags,
+                            int* status, double wait_seconds, cudaStream_t stream) {
+  if (seg_bytes % 16 || world < 1 || world > kMaxRanks || dst_ptrs == nullptr) return 1;
+  PushGatherParams p{};
+  for (int r = 0; r < world; ++r) {
+    p.peer_dst[r] = dst_ptrs[r];
+    p.peer_flags[r] = peer_flags != nullptr ? peer_flags[r] : flags;
+  }
+  p.src = src; p.mc_dst = world > 1 ? dst_mc : nullptr; p.seg_bytes = seg_bytes; p.world = world;
+  p.rank = rank; p.epoch = epoch; p.flags = flags; p.status = status;
+  p.wait_cycles = static_cast<long long>(wait_seconds * 1.9e9);
+  count_launch();
+  // one CTA per SM: every CTA waits for the peers at the end, so all of them must be resident
+  peer_push_gather_kernel<<<sm_count(), 512, 0, stream>>>(p);
   return cudaGetLastError() == cudaSuccess ? 0 : 4;
 }
 

@@ -75,6 +75,13 @@ int launch_comm_gemm(void* const* a_ptrs, void* const* b_ptrs, int M, int N, int
                      int* chunk_flags, void* recv_mc, void* out_mc, void* const* stage_peers,
                      void* stage_mc, cudaStream_t stream);
 
+// All-gather by peer stores (multicast through the NVSwitch when dst_mc is given): this rank's
+// segment goes to offset rank * seg_bytes of every rank's buffer; the kernel ends when every
+// rank's segment has landed in this rank's buffer.
+int launch_peer_push_gather(const void* src, void* const* dst_ptrs, void* dst_mc, int64_t seg_bytes,
+                            int world, int rank, int epoch, int* flags, int* const* peer_flags,
+                            int* status, double wait_seconds, cudaStream_t stream);
+
 // Phase trace of the last fused GEMM + collective kernel (recorded when the environment has
 // SLAPO_B200_COMM_TRACE=1): [256 CTAs][8 slots] nanosecond time stamps, see comm_gemm.cu.
 int read_comm_trace(unsigned long long* host, int n_words);

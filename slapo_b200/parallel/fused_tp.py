@@ -227,14 +227,30 @@ def step_boundary():
         pool.release_all()
 
 
-def push_enabled(ctx) -> bool:
-    """Pushed (owner stores through the switch) or pulled (consumer loads) all-gather.
-    ``SLAPO_B200_AG_MODE=push|pull``; default: push where the context reduces through the
-    NVSwitch (groups of four ranks or more), pull otherwise."""
+def ag_mode(ctx) -> str:
+    """How ``all_gather(x) @ w`` runs on this context:
+
+    * ``"pull"``   - fused kernel, consumer loads: copier warps pull the peers' rows (default at
+      two or three ranks, where it beats NCCL + a library GEMM by 1.2 - 1.3 x);
+    * ``"push"``   - fused kernel, owner stores: every rank pushes its rows into the staging
+      slots of all ranks from inside the GEMM kernel;
+    * ``"gather"`` - the push as a kernel of its own (``peer_push_gather_kernel``, multicast
+      stores through the NVSwitch at the full link rate) followed by this library's CTA-pair
+      GEMM on the gathered slot.  Default where the context uses NVLS (four ranks or more): at
+      eight GPUs the rows of all owners land in the last third of the transfer whatever the
+      order they were sent in, so the fused kernel's GEMM cannot run under the transfer, and
+      its single-CTA main loop is slower than the pair GEMM.
+
+    ``SLAPO_B200_AG_MODE`` overrides."""
     mode = __import__("os").environ.get("SLAPO_B200_AG_MODE")
-    if mode in ("push", "pull"):
-        return mode == "push"
-    return bool(getattr(ctx, "nvls", False))
+    if mode in ("push", "pull", "gather"):
+        return mode
+    return "gather" if getattr(ctx, "nvls", False) else "pull"
+
+
+def push_enabled(ctx) -> bool:
+    """The gathered operand goes through a pooled staging slot (``push`` and ``gather``)."""
+    return ag_mode(ctx) != "pull"
 
 
 def _can_push(ctx, shard_rows) -> bool:
@@ -244,11 +260,12 @@ def _can_push(ctx, shard_rows) -> bool:
             and push_enabled(ctx))
 
 
-def ag_gemm_pushed(ctx, x_shard, w, bias=None, act=-1, b_mn=False, keep=False):
-    """``all_gather(x_shard) @ w.T`` with the gather pushed by the owners (see
-    ``comm_gemm.cu``, gather mode 5).  Returns ``(y, gathered, token)``: with ``keep`` the
-    gathered operand ``[T, K]`` stays valid until ``stage_pool(ctx).release(token)``; without
-    it ``gathered`` is ``None``."""
+def ag_gemm_pushed(ctx, x_shard, w, bias=None, act=-1, b_mn=False, keep=False, mode=None):
+    """``all_gather(x_shard) @ w.T`` with the gather pushed by the owners: inside the GEMM
+    kernel (``mode="push"``: ``comm_gemm.cu``, gather mode 5) or as a kernel of its own
+    followed by the pair GEMM (``mode="gather"``); default: :func:`ag_mode`.
+    Returns ``(y, gathered, token)``: with ``keep`` the gathered operand ``[T, K]`` stays valid
+    until ``stage_pool(ctx).release(token)``; without it ``gathered`` is ``None``."""
     ts, k = x_shard.shape
     n = w.shape[1] if b_mn else w.shape[0]
     t = ts * ctx.world
@@ -256,11 +273,26 @@ def ag_gemm_pushed(ctx, x_shard, w, bias=None, act=-1, b_mn=False, keep=False):
     pool = stage_pool(ctx)
     got = pool.acquire(nbytes)
     token, slot = got if got is not None else (None, pool.transient(nbytes))
-    y = torch.empty(t, n, dtype=x_shard.dtype, device=x_shard.device)
-    a_ptrs = [x_shard.data_ptr() if r == ctx.rank else 0 for r in range(ctx.world)]
-    comm_gemm(ctx, a_ptrs=a_ptrs, b_ptrs=[w.data_ptr()], M=t, N=n, K=k, lda=k, ldb=w.stride(0),
-              a_mn=False, b_mn=b_mn, dtype=x_shard.dtype, gather=GATHER_A_ROWS_PUSHED, seg_len=ts,
-              out_ptr=y.data_ptr(), ldo=n, bias=bias, act=act, slot=slot)
+    if mode is None:
+        mode = ag_mode(ctx)
+    pair_ok = (x_shard.is_cuda and w.dtype == x_shard.dtype and w.stride(-1) == 1
+               and w.stride(0) % 8 == 0 and n % 8 == 0 and k % 8 == 0)
+    if mode == "gather" and pair_ok:
+        # the gather as a kernel of its own, then the CTA-pair GEMM on the gathered slot
+        epoch = ctx.next_epoch()
+        native.ops().peer_push_gather(
+            x_shard.data_ptr(), list(slot.ptrs(RECV_HEADER_BYTES)),
+            int(slot.mc_ptr) + RECV_HEADER_BYTES if getattr(slot, "mc_ptr", 0) else 0,
+            ts * k * x_shard.element_size(), ctx.world, ctx.rank, epoch, ctx.flags_ptr,
+            list(ctx.peer_flag_ptrs), float(ctx.wait_seconds))
+        full = slot.view(x_shard.dtype, (t, k), RECV_HEADER_BYTES)
+        y = NF.gemm(full, w, bias=bias, act=act, b_mn=b_mn)
+    else:
+        y = torch.empty(t, n, dtype=x_shard.dtype, device=x_shard.device)
+        a_ptrs = [x_shard.data_ptr() if r == ctx.rank else 0 for r in range(ctx.world)]
+        comm_gemm(ctx, a_ptrs=a_ptrs, b_ptrs=[w.data_ptr()], M=t, N=n, K=k, lda=k, ldb=w.stride(0),
+                  a_mn=False, b_mn=b_mn, dtype=x_shard.dtype, gather=GATHER_A_ROWS_PUSHED,
+                  seg_len=ts, out_ptr=y.data_ptr(), ldo=n, bias=bias, act=act, slot=slot)
     if not keep:
         pool.release(token)
         return y, None, None

@@ -44,10 +44,12 @@ def test_all_gather_gemm(world, n):
 
 @pytest.mark.parametrize("world,n,ts", [(2, 320, 256), (4, 192, 384), (8, 384, 128)])
 @pytest.mark.parametrize("keep", [False, True])
-def test_all_gather_gemm_pushed(world, n, ts, keep):
+@pytest.mark.parametrize("mode", ["push", "gather"])
+def test_all_gather_gemm_pushed(world, n, ts, keep, mode):
     """Pushed gather: the emulated rank stores its own rows into every rank's staging slot
     (rank by rank here, the emulation has no multicast address) and multiplies the gathered
-    operand; the other owners' rows and block flags are put into its slot beforehand."""
+    operand; the other owners' rows and block flags are put into its slot beforehand.
+    ``push``: inside the GEMM kernel; ``gather``: push kernel, then the pair GEMM."""
     torch.manual_seed(1)
     k = 192
     t = ts * world
@@ -74,14 +76,15 @@ def test_all_gather_gemm_pushed(world, n, ts, keep):
         flags = ctx._buffers[name][r][:t // 128 * 64].view(torch.int32)
         flags.fill_(ctx.epoch + 1)                         # the other owners' blocks "arrived"
         flags[r * (ts // 128) * 16:(r + 1) * (ts // 128) * 16] = 0
-        ctx.preset_flags(ctx.epoch + 1)
-        y, gathered, token = ft.ag_gemm_pushed(ctx, shards[r], w[r], bias, keep=keep)
+        ctx.preset_flags(ctx.epoch + 1, ready=True, done=True)   # "gather" also waits for done
+        y, gathered, token = ft.ag_gemm_pushed(ctx, shards[r], w[r], bias, keep=keep, mode=mode)
         assert native.ops().device_status() == 0
         _close(y, full.float() @ w[r].float().t() + bias.float(), k)
         for q in range(world):
             assert torch.equal(data(q), full), f"rank {r}'s rows in rank {q}'s slot"
-            fl = ctx._buffers[name][q][:t // 128 * 64].view(torch.int32)
-            assert bool((fl[r * (ts // 128) * 16:(r + 1) * (ts // 128) * 16] == ctx.epoch).all())
+            if mode == "push":      # the fused kernel raises a flag per 8-row slice
+                fl = ctx._buffers[name][q][:t // 128 * 64].view(torch.int32)
+                assert bool((fl[r * (ts // 128) * 16:(r + 1) * (ts // 128) * 16] == ctx.epoch).all())
         if keep:
             assert token == (nbytes, 0) and torch.equal(gathered, full)
             ft.stage_pool(ctx).release(token)
@@ -194,7 +197,8 @@ def test_missing_peer_times_out_cleanly():
     y = ft.ag_gemm(ctx, xs, w, None, staged=ctx.buffer("ag_in", ts * k * 2))
     assert native.ops().device_status() == 0
     _close(y, torch.cat([xs, xs], 0).float() @ w.float().t(), k)
-    # the pushed form waits for every rank to enter before it writes anybody's slot
-    ft.ag_gemm_pushed(ctx, xs, w)
-    torch.cuda.synchronize()
-    assert native.ops().device_status() == 4
+    # the pushed forms wait for every rank to enter before they write anybody's slot
+    for mode in ("push", "gather"):
+        ft.ag_gemm_pushed(ctx, xs, w, mode=mode)
+        torch.cuda.synchronize()
+        assert native.ops().device_status() == 4

@@ -24,7 +24,7 @@ def _worker(rank, world, nvls, ag_mode=None):
 
     import torch.distributed as dist
 
-    if ag_mode is not None:      # "push" / "pull": the all-gather form (default: push with nvls)
+    if ag_mode is not None:      # the all-gather form (default: "gather" with nvls, else "pull")
         os.environ["SLAPO_B200_AG_MODE"] = ag_mode
 
     from slapo_b200.ops import native
@@ -96,12 +96,13 @@ def _worker(rank, world, nvls, ag_mode=None):
     dist.barrier()
 
 
-@pytest.mark.parametrize("nvls,ag_mode", [(False, None), (True, None), (False, "push"), (True, "pull")])
+@pytest.mark.parametrize("nvls,ag_mode", [(False, None), (True, None), (False, "push"), (True, "push"),
+                                          (False, "gather")])
 @pytest.mark.parametrize("world", [2, 4])
 def test_fused_tp_linears_on_peers(world, nvls, ag_mode):
-    """nvls: reductions through the NVSwitch; the all-gather is pushed through the switch with
-    nvls, pulled by peer loads without, unless ``ag_mode`` says otherwise (pushed rank by rank
-    without nvls)."""
+    """nvls: reductions through the NVSwitch.  The all-gather is a multicast push kernel + pair
+    GEMM with nvls and a fused pull without, unless ``ag_mode`` says otherwise (``push``: fused
+    kernel with the owners' stores inside; without nvls the stores go rank by rank)."""
     _need_gpus(world)
     run_distributed(_worker, world, nvls, ag_mode, backend="nccl")
 
