@@ -143,6 +143,18 @@ class PipelineEngine:
         self._meta_fwd = None   # [(name, shape, dtype, requires_grad)] of live_in[stage]
         self._meta_sent = False
         self._inflight = []     # Work objects of sends not yet waited for
+        # Receives are posted one micro-batch ahead unless the stage runs the fused
+        # tensor-parallel kernels.  Those are persistent kernels that need every SM (one CTA
+        # each, all of them waiting on each other and on the peers); a receive posted ahead
+        # is an NCCL kernel that sits on some SMs until its sender sends, and the sender may
+        # be waiting - through its own tensor-parallel peers - for exactly the kernel that
+        # cannot become resident.  OPT-2.7B on 2 stages x 4-way tensor parallelism hung that
+        # way; with receives posted where the tensor is needed (and sends still not waited
+        # for) no such cycle exists.
+        self._prefetch_recv = not (mesh.tp_size > 1 and self.device.type == "cuda")
+        override = self.cfg.extra.get("prefetch_recv")
+        if override is not None:
+            self._prefetch_recv = bool(override)
         self._tied = self._find_tied()
         # gradients of parameters shared with another stage change after backward (the other
         # stage's part is added): their buckets are reduced in step(), never from a hook
@@ -354,7 +366,10 @@ class PipelineEngine:
             """Prefetch the next input, then run micro-batch ``fwd_i`` on the input ``cur``
             whose receives were posted one micro-batch ago."""
             nonlocal fwd_i
-            nxt = self._post_recv_forward() if fwd_i + 1 < m else (None, None)
+            if self._prefetch_recv:
+                nxt = self._post_recv_forward() if fwd_i + 1 < m else (None, None)
+            else:
+                cur, nxt = self._post_recv_forward(), (None, None)
             bufs, works = cur
             self._wait(works)
             rec = self._compute_forward(micro_inputs[fwd_i], micro_labels[fwd_i], bufs)
@@ -374,13 +389,13 @@ class PipelineEngine:
             bwd_i += 1
             self._send_backward(self._compute_backward(done, grads))
 
-        cur = self._post_recv_forward()
+        cur = self._post_recv_forward() if self._prefetch_recv else (None, None)
         for _ in range(warmup):
             cur = forward_one(cur)
         posted = None
         for _ in range(steady):
             # the output gradient of the oldest micro-batch travels during this forward
-            if pending and posted is None:
+            if pending and posted is None and self._prefetch_recv:
                 posted = self._post_recv_backward(pending[0])
             cur = forward_one(cur)
             done = pending.pop(0)
@@ -392,7 +407,7 @@ class PipelineEngine:
             done = pending.pop(0)
             this = posted if posted is not None else self._post_recv_backward(done)
             # ... and the next one's during this backward
-            posted = self._post_recv_backward(pending[0]) if pending else None
+            posted = self._post_recv_backward(pending[0]) if pending and self._prefetch_recv else None
             backward_one(done, this)
         # sends: make the compute stream (NCCL) or the host (gloo) wait before buffers go away
         self._wait(self._inflight)

@@ -1,6 +1,7 @@
 """Pipeline partitioning (structure) and the 1F1B engine on CPU/gloo ranks."""
 import copy
 
+import pytest
 import torch
 from torch import nn
 
@@ -49,7 +50,7 @@ def test_partition_structure_and_equivalence():
     assert stages == [0, 2]
 
 
-def _pp_worker(rank, world):
+def _pp_worker(rank, world, prefetch_recv=True):
     cfg = _tiny_cfg()
     torch.manual_seed(5)
     ref = BertForMaskedLM(cfg).init_weights()
@@ -62,8 +63,9 @@ def _pp_worker(rank, world):
         pipeline_cuts=[1])
     engine, _ = slapo.build(
         sch, target="native", init_weights=False, mesh=mesh, num_micro_batches=4,
-        config={"lr": 0.0, "clip_grad": 0.0, "weight_decay": 0.0},
+        config={"lr": 0.0, "clip_grad": 0.0, "weight_decay": 0.0, "prefetch_recv": prefetch_recv},
         loss_fn=lambda out, lab: mlm_loss(out["logits"], lab))
+    assert engine._prefetch_recv == prefetch_recv
     loss = engine.train_batch(ids, labels=labels)
     # reference: mean over micro-batches of the per-micro-batch mean loss
     ref_losses = [mlm_loss(ref(i)["logits"], l) for i, l in zip(ids.chunk(4), labels.chunk(4))]
@@ -76,8 +78,11 @@ def _pp_worker(rank, world):
     assert engine.inner.last_grad_norm is None or engine.inner.last_grad_norm >= 0
 
 
-def test_pipeline_1f1b_loss_matches_reference():
-    run_distributed(_pp_worker, 2)
+@pytest.mark.parametrize("prefetch_recv", [True, False])
+def test_pipeline_1f1b_loss_matches_reference(prefetch_recv):
+    """Receives posted one micro-batch ahead (the default without fused tensor-parallel
+    kernels) or where the tensor is needed (the form used next to those kernels)."""
+    run_distributed(_pp_worker, 2, prefetch_recv)
 
 
 def _zoo_pipeline(name, n_stages):
