@@ -152,6 +152,42 @@ def cmd_sweep(ns, _extra):
             fh.write("\n".join(rows) + "\n")
 
 
+def cmd_env(ns, _extra):
+    """Versions and devices of this machine, one ``key<TAB>value`` line each (the header block of
+    a results file).  Parity: the ``env`` sub-command of the reference's bench_single_node.py."""
+    import platform
+
+    import torch
+
+    rows = [("python", platform.python_version()), ("torch", torch.__version__),
+            ("cuda (torch)", str(torch.version.cuda)), ("platform", platform.platform())]
+    try:
+        import slapo_b200
+        from slapo_b200.ops import native
+
+        rows.append(("slapo_b200", getattr(slapo_b200, "__version__", "in-tree")))
+        rows.append(("native extension",
+                     "loaded" if native.available() else f"missing: {native.load_error()}"))
+    except Exception as err:        # the report must not fail on a broken install
+        rows.append(("slapo_b200", f"import failed: {err}"))
+    if torch.cuda.is_available():
+        for i in range(torch.cuda.device_count()):
+            prop = torch.cuda.get_device_properties(i)
+            rows.append((f"gpu{i}", f"{prop.name}, {prop.total_memory // 2**20} MiB, "
+                                    f"{prop.multi_processor_count} SMs, sm_{prop.major}{prop.minor}"))
+        try:
+            rows.append(("nccl", ".".join(str(v) for v in torch.cuda.nccl.version())))
+        except Exception:
+            pass
+    else:
+        rows.append(("gpu", "none visible"))
+    text = "\n".join(f"{k}\t{v}" for k, v in rows) + "\n"
+    sys.stdout.write(text)
+    if ns.append_to:
+        with open(ns.append_to, "a", encoding="utf-8") as fh:
+            fh.write(text)
+
+
 def main(argv=None):
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawTextHelpFormatter)
     sub = ap.add_subparsers(dest="cmd", required=True)
@@ -164,11 +200,13 @@ def main(argv=None):
     sweep.add_argument("--only", default=None, help="substring filter on the model name")
     sweep.add_argument("--steps", type=int, default=10)
     sweep.add_argument("--warmup", type=int, default=3)
+    env = sub.add_parser("env", help="versions and devices of this machine")
+    env.add_argument("--append-to", default=None, help="also append the report to this file")
     for p in (run, sweep):
         p.add_argument("--port", type=int, default=29540)
         p.add_argument("--timeout", type=float, default=1800)
     ns, extra = ap.parse_known_args(argv)
-    {"run": cmd_run, "sweep": cmd_sweep}[ns.cmd](ns, extra)
+    {"run": cmd_run, "sweep": cmd_sweep, "env": cmd_env}[ns.cmd](ns, extra)
 
 
 if __name__ == "__main__":
