@@ -23,6 +23,13 @@ the tensor is consumed; sends are never waited for until the end of the batch
 (the Work objects keep the tensors alive).  ``Work.wait()`` on NCCL makes the
 compute stream wait, not the host, so the host runs ahead and keeps both
 queues full.  On CPU ranks (gloo) the same code runs with host-blocking waits.
+
+Next to the fused tensor-parallel kernels (tensor parallelism on GPUs) the engine runs the
+PAIRED schedule instead (``p2p_mode``): every exchange with a neighbour is one batched
+send + receive group that the compute stream waits for.  Those kernels are persistent and
+need every SM; an NCCL kernel that sits on a few SMs until its peer arrives can keep one of
+them from becoming resident, and with receives posted ahead the peer may be waiting for
+exactly that kernel (a 2-stage x 4-way run stopped that way).
 The reference delegates all of this to DeepSpeed's ``PipelineModule``, which
 exchanges blocking send / recv pairs and re-decodes a metadata tensor on the
 host for every micro-batch
@@ -151,10 +158,18 @@ class PipelineEngine:
         # cannot become resident.  OPT-2.7B on 2 stages x 4-way tensor parallelism hung that
         # way; with receives posted where the tensor is needed (and sends still not waited
         # for) no such cycle exists.
-        self._prefetch_recv = not (mesh.tp_size > 1 and self.device.type == "cuda")
+        fused_tp = mesh.tp_size > 1 and self.device.type == "cuda"
+        self._prefetch_recv = not fused_tp
         override = self.cfg.extra.get("prefetch_recv")
         if override is not None:
             self._prefetch_recv = bool(override)
+        # "paired": every exchange with a neighbour is ONE batched send + receive group that the
+        # compute stream waits for before the next kernel, so that no NCCL kernel is ever
+        # resident beside a persistent tensor-parallel kernel (the schedule that ran OPT-2.7B
+        # on 2 stages x 4-way tensor parallelism); "overlap": the side-stream schedule above.
+        self._p2p_mode = self.cfg.extra.get("p2p_mode") or ("paired" if fused_tp else "overlap")
+        if self._p2p_mode not in ("paired", "overlap"):
+            raise ValueError(f"p2p_mode must be 'paired' or 'overlap', not {self._p2p_mode!r}")
         self._tied = self._find_tied()
         # gradients of parameters shared with another stage change after backward (the other
         # stage's part is added): their buckets are reduced in step(), never from a hook
@@ -344,6 +359,93 @@ class PipelineEngine:
         return [t.grad if t.grad is not None else torch.zeros_like(t) for t in rec["received"]]
 
     # ---- the schedule ---------------------------------------------------- #
+    def _exchange(self, sends, recvs):
+        """One batched group of sends and receives with neighbours (global ranks, default
+        group); the compute stream (NCCL) or the host (gloo) waits for all of it."""
+        ops = [dist.P2POp(dist.isend, t.contiguous(), peer) for t, peer in sends]
+        ops += [dist.P2POp(dist.irecv, t, peer) for t, peer in recvs]
+        if ops:
+            for w in dist.batch_isend_irecv(ops):
+                w.wait()
+
+    def _finish_batch(self, losses):
+        self.inner.set_final_backward(True)
+        self._sync_tied_grads()
+        self.inner.micro_step = 0
+        self.inner.step()
+        # the loss lives on the last stage; share it along the pipeline
+        loss = torch.zeros((), device=self.device)
+        if losses:
+            loss = torch.stack(losses).sum().float()
+        if self.mesh.pp_group is not None:
+            src = self.mesh.get_rank(pp=self.n_stages - 1, dp=self.mesh.dp_rank, tp=self.mesh.tp_rank)
+            dist.broadcast(loss, src=src, group=self.mesh.pp_group)
+        self.last_loss = loss
+        return loss
+
+    def _train_batch_paired(self, micro_inputs, micro_labels):
+        """1F1B with paired exchanges: a stage always puts "send to a neighbour" and the
+        matching "receive from that neighbour" into one batched group (send forward + receive
+        backward, send backward + receive forward), so the two sides of a link never wait for
+        each other in opposite order, and waits for the group before it computes on."""
+        m = self.num_micro_batches
+        first, last = self.stage_id == 0, self.stage_id == self.n_stages - 1
+        warmup = min(self.n_stages - self.stage_id - 1, m)
+        steady = m - warmup
+        prev, nxt = self.prev_rank, self.next_rank
+        pending, losses = [], []
+        fwd_i = bwd_i = 0
+
+        def recv_forward():
+            bufs = self._fwd_recv_buffers()
+            if not first:
+                self._exchange([], [(t, prev) for t in self._tensor_list(bufs)])
+            return bufs
+
+        def backward(done, grads):
+            nonlocal bwd_i
+            if done["loss"] is not None:
+                losses.append(done["loss"].detach())
+            # the data-parallel hooks may reduce a bucket only during the step's last backward
+            self.inner.set_final_backward(bwd_i == m - 1)
+            bwd_i += 1
+            return self._compute_backward(done, grads)
+
+        for _ in range(warmup):
+            bufs = recv_forward()
+            rec = self._compute_forward(micro_inputs[fwd_i], micro_labels[fwd_i], bufs)
+            fwd_i += 1
+            if not last:
+                self._exchange([(t.detach(), nxt) for t in rec["payload"]], [])
+            pending.append(rec)
+        bufs = recv_forward() if steady > 0 else None
+        for it in range(steady):
+            rec = self._compute_forward(micro_inputs[fwd_i], micro_labels[fwd_i], bufs)
+            fwd_i += 1
+            pending.append(rec)
+            # send this forward result, receive the gradient of the oldest micro-batch
+            done = pending.pop(0)
+            grads = [torch.empty_like(t) for t in done["sent"]]
+            if not last:
+                self._exchange([(t.detach(), nxt) for t in rec["payload"]],
+                               [(g, nxt) for g in grads])
+            in_grads = backward(done, grads)
+            # send the input gradients, receive the next forward input
+            more = it + 1 < steady
+            bufs = self._fwd_recv_buffers() if (more and not first) else None
+            if not first:
+                self._exchange([(g, prev) for g in in_grads],
+                               [(t, prev) for t in self._tensor_list(bufs)])
+        while pending:
+            done = pending.pop(0)
+            grads = [torch.empty_like(t) for t in done["sent"]]
+            if not last:
+                self._exchange([], [(g, nxt) for g in grads])
+            in_grads = backward(done, grads)
+            if not first:
+                self._exchange([(g, prev) for g in in_grads], [])
+        return self._finish_batch(losses)
+
     def train_batch(self, *args, labels=None, **kwargs):
         m = self.num_micro_batches
         from .engine import _release_staging_slots
@@ -355,12 +457,14 @@ class PipelineEngine:
             for i, piece in enumerate(_split_micro(val, m)):
                 micro_inputs[i][name] = piece
         micro_labels = _split_micro(labels, m) if labels is not None else [None] * m
+        self.inner.set_final_backward(False)
+        if self._p2p_mode == "paired":
+            return self._train_batch_paired(micro_inputs, micro_labels)
         warmup = min(self.n_stages - self.stage_id - 1, m)
         steady = m - warmup
         pending, losses = [], []
         fwd_i = 0
         bwd_i = 0
-        self.inner.set_final_backward(False)
 
         def forward_one(cur):
             """Prefetch the next input, then run micro-batch ``fwd_i`` on the input ``cur``
@@ -412,19 +516,7 @@ class PipelineEngine:
         # sends: make the compute stream (NCCL) or the host (gloo) wait before buffers go away
         self._wait(self._inflight)
         self._inflight = []
-        self.inner.set_final_backward(True)
-        self._sync_tied_grads()
-        self.inner.micro_step = 0
-        self.inner.step()
-        # the loss lives on the last stage; share it along the pipeline
-        loss = torch.zeros((), device=self.device)
-        if losses:
-            loss = torch.stack(losses).sum().float()
-        if self.mesh.pp_group is not None:
-            src = self.mesh.get_rank(pp=self.n_stages - 1, dp=self.mesh.dp_rank, tp=self.mesh.tp_rank)
-            dist.broadcast(loss, src=src, group=self.mesh.pp_group)
-        self.last_loss = loss
-        return loss
+        return self._finish_batch(losses)
 
     def __call__(self, *args, **kwargs):
         return self.model(*args, **kwargs)

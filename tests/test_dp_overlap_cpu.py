@@ -56,7 +56,7 @@ def test_overlap_with_module_called_several_times_under_checkpoint(zero):
     run_distributed(_albert_worker, 2, zero)
 
 
-def _pp_dp_worker(rank, world):
+def _pp_dp_worker(rank, world, p2p_mode="overlap"):
     cfg = BertConfig(vocab_size=128, hidden_size=32, num_hidden_layers=4, num_attention_heads=2,
                      intermediate_size=64, hidden_dropout_prob=0.0,
                      attention_probs_dropout_prob=0.0)
@@ -70,9 +70,9 @@ def _pp_dp_worker(rank, world):
     engine, _ = slapo.build(
         sch, target="native", init_weights=False, mesh=mesh, num_micro_batches=m,
         config={"lr": lr, "clip_grad": clip, "weight_decay": 0.0, "bucket_mb": 0.004,
-                "overlap_on_cpu": True},
+                "overlap_on_cpu": True, "p2p_mode": p2p_mode},
         loss_fn=lambda out, lab: mlm_loss(out["logits"], lab))
-    assert engine.inner._overlap and engine._tied
+    assert engine.inner._overlap and engine._tied and engine._p2p_mode == p2p_mode
     # which reference parameter is which stage parameter (identical initial values)
     names = {}
     for p in engine.stage.parameters():
@@ -111,5 +111,6 @@ def _pp_dp_worker(rank, world):
                                        rtol=1e-3, atol=1e-5, msg=lambda s: f"{name}: {s}")
 
 
-def test_pipeline_times_data_parallel_with_tied_embeddings_and_clipping():
-    run_distributed(_pp_dp_worker, 4)
+@pytest.mark.parametrize("p2p_mode", ["overlap", "paired"])
+def test_pipeline_times_data_parallel_with_tied_embeddings_and_clipping(p2p_mode):
+    run_distributed(_pp_dp_worker, 4, p2p_mode)

@@ -50,7 +50,7 @@ def test_partition_structure_and_equivalence():
     assert stages == [0, 2]
 
 
-def _pp_worker(rank, world, prefetch_recv=True):
+def _pp_worker(rank, world, prefetch_recv=True, p2p_mode="overlap"):
     cfg = _tiny_cfg()
     torch.manual_seed(5)
     ref = BertForMaskedLM(cfg).init_weights()
@@ -63,9 +63,10 @@ def _pp_worker(rank, world, prefetch_recv=True):
         pipeline_cuts=[1])
     engine, _ = slapo.build(
         sch, target="native", init_weights=False, mesh=mesh, num_micro_batches=4,
-        config={"lr": 0.0, "clip_grad": 0.0, "weight_decay": 0.0, "prefetch_recv": prefetch_recv},
+        config={"lr": 0.0, "clip_grad": 0.0, "weight_decay": 0.0, "prefetch_recv": prefetch_recv,
+                "p2p_mode": p2p_mode},
         loss_fn=lambda out, lab: mlm_loss(out["logits"], lab))
-    assert engine._prefetch_recv == prefetch_recv
+    assert engine._prefetch_recv == prefetch_recv and engine._p2p_mode == p2p_mode
     loss = engine.train_batch(ids, labels=labels)
     # reference: mean over micro-batches of the per-micro-batch mean loss
     ref_losses = [mlm_loss(ref(i)["logits"], l) for i, l in zip(ids.chunk(4), labels.chunk(4))]
@@ -78,11 +79,13 @@ def _pp_worker(rank, world, prefetch_recv=True):
     assert engine.inner.last_grad_norm is None or engine.inner.last_grad_norm >= 0
 
 
-@pytest.mark.parametrize("prefetch_recv", [True, False])
-def test_pipeline_1f1b_loss_matches_reference(prefetch_recv):
-    """Receives posted one micro-batch ahead (the default without fused tensor-parallel
-    kernels) or where the tensor is needed (the form used next to those kernels)."""
-    run_distributed(_pp_worker, 2, prefetch_recv)
+@pytest.mark.parametrize("prefetch_recv,p2p_mode", [(True, "overlap"), (False, "overlap"),
+                                                    (False, "paired")])
+def test_pipeline_1f1b_loss_matches_reference(prefetch_recv, p2p_mode):
+    """Side-stream transfers with receives posted one micro-batch ahead (the default without
+    fused tensor-parallel kernels) or where the tensor is needed, and the paired schedule (one
+    batched send + receive group per neighbour, waited for; the default next to those kernels)."""
+    run_distributed(_pp_worker, 2, prefetch_recv, p2p_mode)
 
 
 def _zoo_pipeline(name, n_stages):
