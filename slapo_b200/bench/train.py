@@ -79,10 +79,12 @@ def profile_overlap(step_fn, path, rank, steps=2):
     from torch.autograd import DeviceType
     from torch.profiler import ProfilerActivity, profile
 
-    with profile(activities=[ProfilerActivity.CPU, ProfilerActivity.CUDA]) as prof:
+    acts = [ProfilerActivity.CPU] + ([ProfilerActivity.CUDA] if torch.cuda.is_available() else [])
+    with profile(activities=acts) as prof:
         for _ in range(steps):
             step_fn()
-        torch.cuda.synchronize()
+        if torch.cuda.is_available():
+            torch.cuda.synchronize()
     kernels = [e for e in prof.events() if e.device_type == DeviceType.CUDA and e.time_range is not None]
     p2p = [(e.time_range.start, e.time_range.end) for e in kernels
            if "SendRecv" in e.name or "sendrecv" in e.name.lower()]
@@ -103,7 +105,8 @@ def profile_overlap(step_fn, path, rank, steps=2):
             if c >= b:
                 break
             covered += min(b, d) - max(a, c)
-    table = prof.key_averages().table(sort_by="cuda_time_total", row_limit=14, max_name_column_width=60)
+    sort_key = "cuda_time_total" if torch.cuda.is_available() else "cpu_time_total"
+    table = prof.key_averages().table(sort_by=sort_key, row_limit=14, max_name_column_width=60)
     with open(f"{path}.rank{rank}.txt", "w", encoding="utf-8") as fh:
         fh.write(f"rank {rank}: {len(p2p)} send/receive kernels in {steps} steps, {total / 1e3:.2f} ms in "
                  f"total, {covered / 1e3:.2f} ms of it ({100.0 * covered / max(total, 1e-9):.0f} %) while "
