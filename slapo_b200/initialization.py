@@ -64,6 +64,9 @@ def init_on_device(device, include_buffers: bool = False):
 
 @contextlib.contextmanager
 def init_empty_weights(enable: bool = True, include_buffers: bool = False):
+    """Context manager: modules created inside get their parameters (and, on request, buffers)
+    on the meta device - shapes only, no memory - until ``build`` materialises each rank's
+    shards."""
     if not enable:
         yield
         return

@@ -112,6 +112,8 @@ _TRACKER = RNGStatesTracker()
 
 
 def get_cuda_rng_tracker() -> RNGStatesTracker:
+    """The process-wide tracker of named RNG states (``fork_rng`` regions draw from the
+    tensor-parallel state so that dropout differs across the ranks of a group)."""
     return _TRACKER
 
 

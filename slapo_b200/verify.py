@@ -57,6 +57,11 @@ def _slice_like(full, local_shape, rank, world):
 
 
 class Verify(ContextDecorator):
+    """Context manager around a block of scheduling primitives: on exit the scheduled model is
+    run against a copy taken on entry - forward outputs and, with ``check_grads``, parameter and
+    input gradients (sharded parameters are gathered first) - and a mismatch raises.  Works on
+    CPU (gloo ranks) and on GPUs; ``enable=False`` turns it into a no-op."""
+
     def __init__(self, sch, example_inputs, example_outputs=None, loss_fn=None, device=None,
                  eval_mode=True, enable=True, check_grads=True, init_weights=True,
                  rtol=None, atol=None, **_compat):
