@@ -88,6 +88,9 @@ def parse_args():
                          "launches the kernels one by one instead")
     ap.add_argument("--no-fused-dp", action="store_true",
                     help="data parallelism through NCCL instead of the peer-memory kernels")
+    ap.add_argument("--watchdog", type=float, default=1500.0,
+                    help="seconds after which a run that has not finished dumps every thread's "
+                         "stack and exits with an error instead of blocking its caller (0 = off)")
     ap.add_argument("--profile", action="store_true",
                     help="print a per-kernel time table of one step (torch.profiler, rank 0); "
                          "analysis aid only, the reported numbers are taken without it")
@@ -556,10 +559,21 @@ def maybe_self_launch(args):
 def main():
     args = parse_args()
     maybe_self_launch(args)
-    if args.impl == "reference":
-        run_reference(args)
-    else:
-        run_native(args)
+    if args.watchdog > 0:
+        import faulthandler
+
+        # a rank that hangs (a peer that never arrives, a lost transfer) must not hang the caller
+        faulthandler.dump_traceback_later(args.watchdog, exit=True, file=sys.stderr)
+    try:
+        if args.impl == "reference":
+            run_reference(args)
+        else:
+            run_native(args)
+    finally:
+        if args.watchdog > 0:
+            import faulthandler
+
+            faulthandler.cancel_dump_traceback_later()
 
 
 if __name__ == "__main__":
