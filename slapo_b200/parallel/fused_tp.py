@@ -424,10 +424,12 @@ class _AGLinear(torch.autograd.Function):
         ctx.sctx = sctx
         x_shard = x_shard.contiguous()
         ctx.token = None
+        ctx.pooled = False
         if _can_push(sctx, x_shard.shape[0]):
             # no backward will run (evaluation, the first pass of a checkpointed layer): keep nothing
             keep = any(ctx.needs_input_grad[:3])
             y, full_x, ctx.token = ag_gemm_pushed(sctx, x_shard, w, bias, keep=keep)
+            ctx.pooled = ctx.token is not None
             if not keep:
                 ctx.gathered = False
                 ctx.save_for_backward(x_shard, w)
@@ -446,6 +448,11 @@ class _AGLinear(torch.autograd.Function):
     def backward(ctx, dy):
         x_saved, w = ctx.saved_tensors
         sctx = ctx.sctx
+        if ctx.pooled and ctx.token is None:
+            raise RuntimeError(
+                "second backward pass through an all-gather whose gathered tokens lived in a "
+                "pooled staging slot: the slot went back to the pool after the first pass "
+                "(set SLAPO_B200_AG_MODE=pull for graphs that are backpropagated twice)")
         dy = dy.contiguous()
         # dXs = reduce_scatter(dY @ W):  B = W read N-major ([N_local, K] = [contraction, out])
         dx = gemm_rs(sctx, dy, w, None, b_mn=True, name="rs_recv_bwd")
