@@ -88,6 +88,38 @@ def test_pipeline_1f1b_loss_matches_reference(prefetch_recv, p2p_mode):
     run_distributed(_pp_worker, 2, prefetch_recv, p2p_mode)
 
 
+def _pp4_worker(rank, world, p2p_mode, prefetch_recv):
+    """Four stages, six micro-batches: warm-up depths 3 / 2 / 1 / 0, a steady phase and a drain
+    on every stage; gloo waits block the host, so a schedule whose two sides of a link wait for
+    each other in opposite order would hang here."""
+    cfg = _tiny_cfg()
+    cfg.num_hidden_layers = 4
+    torch.manual_seed(11)
+    ref = BertForMaskedLM(cfg).init_weights()
+    ids = torch.randint(0, 256, (12, 16))
+    labels = ids.clone()
+    labels[:, ::3] = -100
+    mesh = DeviceMesh(pp=4, dp=1, tp=1)
+    sch = slapo.model_schedule.apply_schedule(
+        copy.deepcopy(ref), "bert", model_config=cfg, group=False, attn_op_name="reference",
+        pipeline_cuts=[0, 1, 2])
+    engine, _ = slapo.build(
+        sch, target="native", init_weights=False, mesh=mesh, num_micro_batches=6,
+        config={"lr": 0.0, "clip_grad": 0.0, "weight_decay": 0.0, "p2p_mode": p2p_mode,
+                "prefetch_recv": prefetch_recv},
+        loss_fn=lambda out, lab: mlm_loss(out["logits"], lab))
+    for _ in range(2):      # the second batch runs without the shape handshake
+        loss = engine.train_batch(ids, labels=labels)
+    ref_losses = [mlm_loss(ref(i)["logits"], l) for i, l in zip(ids.chunk(6), labels.chunk(6))]
+    torch.testing.assert_close(loss, torch.stack(ref_losses).mean().detach(), rtol=1e-4, atol=1e-5)
+
+
+@pytest.mark.parametrize("p2p_mode,prefetch_recv", [("paired", False), ("overlap", True),
+                                                    ("overlap", False)])
+def test_pipeline_four_stages(p2p_mode, prefetch_recv):
+    run_distributed(_pp4_worker, 4, p2p_mode, prefetch_recv)
+
+
 def _zoo_pipeline(name, n_stages):
     """Scheduled + partitioned model of the zoo, run stage after stage in one
     process, against the unpartitioned model."""
