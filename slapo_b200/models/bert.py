@@ -201,7 +201,7 @@ class BertPreTrainedModel(nn.Module):
         elif isinstance(module, nn.LayerNorm):
             module.bias.data.zero_()
             module.weight.data.fill_(1.0)
-        elif isinstance(module, BertLMPredictionHead):
+        elif isinstance(module, (BertLMPredictionHead, RobertaLMHead)):
             module.bias.data.zero_()
 
     def init_weights(self):
@@ -311,8 +311,52 @@ def roberta_config(**kw):
 
 
 class RobertaModel(BertModel):
-    """RoBERTa = BERT with shifted position ids and a different vocabulary."""
+    """RoBERTa = BERT with position ids that count the non-padding tokens (starting at
+    ``pad_token_id + 1``; padding positions keep ``pad_token_id``) and a different vocabulary."""
+
+    def forward(self, input_ids, attention_mask=None, token_type_ids=None, position_ids=None):
+        if position_ids is None:
+            pad = self.config.pad_token_id
+            keep = (input_ids != pad).to(torch.long)
+            position_ids = torch.cumsum(keep, dim=1) * keep + pad
+        return super().forward(input_ids, attention_mask, token_type_ids, position_ids)
 
 
-class RobertaForMaskedLM(BertForMaskedLM):
-    pass
+class RobertaLMHead(nn.Module):
+    """dense -> GeLU -> LayerNorm -> decoder (tied to the word embedding), Hugging Face names."""
+
+    def __init__(self, config):
+        super().__init__()
+        self.dense = nn.Linear(config.hidden_size, config.hidden_size)
+        self.layer_norm = nn.LayerNorm(config.hidden_size, eps=config.layer_norm_eps)
+        self.decoder = nn.Linear(config.hidden_size, config.vocab_size, bias=True)
+        self.bias = nn.Parameter(torch.zeros(config.vocab_size))
+        self.decoder.bias = self.bias       # one bias under two names, like Hugging Face
+        self.act = _act("gelu")
+
+    def forward(self, features):
+        return self.decoder(self.layer_norm(self.act(self.dense(features))))
+
+
+class RobertaForMaskedLM(BertPreTrainedModel):
+    """RoBERTa with the masked-LM head, parameter names as in Hugging Face
+    (``roberta.*``, ``lm_head.{dense,layer_norm,decoder,bias}``)."""
+
+    def __init__(self, config):
+        super().__init__()
+        self.config = config
+        self.roberta = RobertaModel(config, add_pooling_layer=False)
+        self.lm_head = RobertaLMHead(config)
+        self.tie_weights()
+
+    def tie_weights(self):
+        self.lm_head.decoder.weight = self.roberta.embeddings.word_embeddings.weight
+
+    def forward(self, input_ids, attention_mask=None, token_type_ids=None, position_ids=None,
+                labels=None):
+        hidden = self.roberta(input_ids, attention_mask, token_type_ids, position_ids)[
+            "last_hidden_state"]
+        logits = self.lm_head(hidden)
+        if labels is None:
+            return {"logits": logits}
+        return {"loss": mlm_loss(logits, labels), "logits": logits}

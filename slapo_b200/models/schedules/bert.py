@@ -141,8 +141,10 @@ def shard_lm_head(sch, config, prefix):
     if sch.world_size == 1:
         return
     shard_word_embedding(sch[_j(prefix, "embeddings.word_embeddings")], config.vocab_size)
-    if "cls.predictions" in sch:
-        head = sch["cls.predictions"]
+    # BERT keeps the head under cls.predictions, RoBERTa under lm_head; same members
+    head_path = "cls.predictions" if "cls.predictions" in sch else ("lm_head" if "lm_head" in sch else None)
+    if head_path is not None:
+        head = sch[head_path]
         head["decoder"].shard("weight", axis=0)  # tied: same shard as the embedding
         head["decoder"].shard("bias", axis=0)
         head.shard("bias", axis=0)               # the same Parameter under its second name

@@ -119,3 +119,38 @@ def _mlm_worker(rank, world):
 
 def test_bert_mlm_vocab_parallel_loss():
     run_distributed(_mlm_worker, 2)
+
+
+def _roberta_mlm_worker(rank, world):
+    """RoBERTa keeps its head under ``lm_head`` and its trunk under ``roberta``: the recipe must
+    shard both like BERT's, tied weight included, and padding-aware position ids must survive."""
+    from slapo_b200.models import RobertaForMaskedLM, roberta_config
+
+    cfg = roberta_config(vocab_size=512, hidden_size=64, num_hidden_layers=2, num_attention_heads=4,
+                         intermediate_size=128, hidden_dropout_prob=0.0,
+                         attention_probs_dropout_prob=0.0, max_position_embeddings=64)
+    torch.manual_seed(8)
+    ref = RobertaForMaskedLM(cfg).init_weights()
+    ids, labels = _make_batch(cfg.vocab_size, 4, 32)
+    ids = ids.clamp(min=2)
+    ids[1, 24:] = cfg.pad_token_id
+    model = copy.deepcopy(ref)
+    sch = slapo.model_schedule.apply_schedule(model, "roberta", model_config=cfg,
+                                              attn_op_name="reference")
+    tp_model, _ = slapo.build(sch, init_weights=False)
+    assert tp_model.lm_head.decoder.weight is tp_model.roberta.embeddings.word_embeddings.weight
+    assert tp_model.lm_head.decoder.weight.shape[0] == cfg.vocab_size // world
+    loss_ref = ref(ids, labels=labels)["loss"]
+    logits = tp_model(ids)["logits"]
+    assert logits.shape[-1] == cfg.vocab_size // world
+    loss_tp = mlm_loss(logits, labels, vocab_parallel=True)
+    torch.testing.assert_close(loss_tp, loss_ref, rtol=1e-4, atol=1e-5)
+    loss_ref.backward()
+    loss_tp.backward()
+    g_ref = ref.roberta.embeddings.word_embeddings.weight.grad
+    g_tp = tp_model.roberta.embeddings.word_embeddings.weight.grad
+    torch.testing.assert_close(g_tp, g_ref.chunk(world, dim=0)[rank], rtol=1e-3, atol=1e-5)
+
+
+def test_roberta_mlm_vocab_parallel_loss():
+    run_distributed(_roberta_mlm_worker, 2)

@@ -1,0 +1,108 @@
+"""The model zoo against Hugging Face transformers: a randomly initialised Hugging Face model's
+``state_dict`` loads into the zoo model with no missing and no unexpected key, and both compute
+the same logits (fp32, dropout off).  This pins the parameter names (checkpoints of either side
+load into the other) and the architectures."""
+import pytest
+import torch
+
+tf = pytest.importorskip("transformers")
+
+from slapo_b200 import models as M  # noqa: E402
+
+SMALL = dict(vocab_size=128, hidden_size=32, num_hidden_layers=2, num_attention_heads=2,
+             intermediate_size=64, hidden_dropout_prob=0.0, attention_probs_dropout_prob=0.0)
+
+
+def _compare(hf, zoo, call_hf, call_zoo, atol=2e-5):
+    hf.eval()
+    zoo.eval()
+    res = zoo.load_state_dict(hf.state_dict(), strict=False)
+    assert not res.missing_keys, res.missing_keys
+    assert not res.unexpected_keys, res.unexpected_keys
+    with torch.no_grad():
+        want, got = call_hf(hf), call_zoo(zoo)
+    torch.testing.assert_close(got, want, rtol=1e-4, atol=atol)
+    # and the other way round: the zoo's names are the Hugging Face names
+    assert set(zoo.state_dict()) == set(hf.state_dict())
+
+
+def _ids(batch=2, seq=16, lo=2, hi=120, seed=0):
+    g = torch.Generator().manual_seed(seed)
+    return torch.randint(lo, hi, (batch, seq), generator=g)
+
+
+def test_bert_with_padding_mask():
+    torch.manual_seed(0)
+    hf = tf.BertForMaskedLM(tf.BertConfig(max_position_embeddings=64, **SMALL))
+    zoo = M.BertForMaskedLM(M.BertConfig(max_position_embeddings=64, **SMALL))
+    ids = _ids()
+    mask = torch.ones_like(ids)
+    mask[1, 10:] = 0
+    types = torch.zeros_like(ids)
+    types[:, 8:] = 1
+    _compare(hf, zoo,
+             lambda m: m(input_ids=ids, attention_mask=mask, token_type_ids=types).logits,
+             lambda m: m(ids, attention_mask=mask, token_type_ids=types)["logits"])
+
+
+def test_roberta_position_ids_skip_padding():
+    torch.manual_seed(1)
+    # Hugging Face counts the two reserved positions in max_position_embeddings, the zoo adds them
+    hf = tf.RobertaForMaskedLM(tf.RobertaConfig(max_position_embeddings=66, pad_token_id=1,
+                                                type_vocab_size=1, layer_norm_eps=1e-5, **SMALL))
+    zoo = M.RobertaForMaskedLM(M.roberta_config(max_position_embeddings=64, **SMALL))
+    ids = _ids()
+    ids[1, 12:] = 1                      # padding at the end of the second sequence
+    mask = (ids != 1).long()
+    _compare(hf, zoo, lambda m: m(input_ids=ids, attention_mask=mask).logits,
+             lambda m: m(ids, attention_mask=mask)["logits"])
+
+
+def test_albert():
+    torch.manual_seed(2)
+    kw = dict(SMALL, embedding_size=16, max_position_embeddings=64)
+    hf = tf.AlbertForMaskedLM(tf.AlbertConfig(classifier_dropout_prob=0.0, **kw))
+    zoo = M.AlbertForMaskedLM(M.AlbertConfig(**kw))
+    ids = _ids()
+    _compare(hf, zoo, lambda m: m(input_ids=ids).logits, lambda m: m(ids)["logits"])
+
+
+def test_gpt2_and_gpt_neo():
+    torch.manual_seed(3)
+    ids = _ids()
+    hf = tf.GPT2LMHeadModel(tf.GPT2Config(vocab_size=128, n_positions=64, n_embd=32, n_layer=2,
+                                          n_head=2, resid_pdrop=0.0, embd_pdrop=0.0, attn_pdrop=0.0))
+    kw = dict(vocab_size=128, n_positions=64, hidden_size=32, num_layers=2, num_heads=2,
+              resid_dropout=0.0, embed_dropout=0.0, attention_dropout=0.0)
+    zoo = M.GPT2LMHeadModel(M.GPTConfig(**kw))
+    _compare(hf, zoo, lambda m: m(input_ids=ids).logits, lambda m: m(ids)["logits"])
+    hf = tf.GPTNeoForCausalLM(tf.GPTNeoConfig(
+        vocab_size=128, max_position_embeddings=64, hidden_size=32, num_layers=2, num_heads=2,
+        attention_types=[[["global"], 2]], resid_dropout=0.0, embed_dropout=0.0,
+        attention_dropout=0.0))
+    zoo = M.GPTNeoForCausalLM(M.GPTConfig(model_type="gpt_neo", **kw))
+    _compare(hf, zoo, lambda m: m(input_ids=ids).logits, lambda m: m(ids)["logits"])
+
+
+def test_opt():
+    torch.manual_seed(4)
+    kw = dict(vocab_size=128, hidden_size=32, num_hidden_layers=2, ffn_dim=64, num_attention_heads=2,
+              max_position_embeddings=64, dropout=0.0, attention_dropout=0.0)
+    hf = tf.OPTForCausalLM(tf.OPTConfig(word_embed_proj_dim=32, **kw))
+    zoo = M.OPTForCausalLM(M.OPTConfig(**kw))
+    ids = _ids()
+    _compare(hf, zoo, lambda m: m(input_ids=ids).logits, lambda m: m(ids)["logits"])
+
+
+@pytest.mark.parametrize("gated", [False, True])
+def test_t5(gated):
+    torch.manual_seed(5)
+    kw = dict(vocab_size=128, d_model=32, d_kv=8, d_ff=64, num_layers=2, num_decoder_layers=2,
+              num_heads=4, relative_attention_num_buckets=8, relative_attention_max_distance=16,
+              dropout_rate=0.0, feed_forward_proj="gated-gelu" if gated else "relu",
+              tie_word_embeddings=not gated)
+    hf = tf.T5ForConditionalGeneration(tf.T5Config(**kw))
+    zoo = M.T5ForConditionalGeneration(M.T5Config(**kw))
+    ids, dec = _ids(), _ids(seq=8, seed=9)
+    _compare(hf, zoo, lambda m: m(input_ids=ids, decoder_input_ids=dec).logits,
+             lambda m: m(ids, decoder_input_ids=dec)["logits"], atol=5e-5)
