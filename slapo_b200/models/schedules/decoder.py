@@ -57,6 +57,28 @@ def _j(*parts):
     return ".".join(p for p in parts if p)
 
 
+# the same field under the names of this library's configs and of Hugging Face's
+_ALIASES = {
+    "num_heads": ("num_heads", "num_attention_heads", "n_head"),
+    "num_attention_heads": ("num_attention_heads", "num_heads", "n_head"),
+    "resid_dropout": ("resid_dropout", "resid_pdrop"),
+    "attention_dropout": ("attention_dropout", "attn_pdrop"),
+    "intermediate_size": ("intermediate_size", "n_inner"),
+}
+
+
+def _cfg(config, key):
+    """``config.<key>`` with the aliases above; a missing or ``None`` feed-forward width is
+    four times the hidden size (the Hugging Face convention)."""
+    for name in _ALIASES.get(key, (key,)):
+        val = getattr(config, name, None)
+        if val is not None:
+            return val
+    if key == "intermediate_size":
+        return 4 * config.hidden_size
+    raise AttributeError(f"the model configuration has none of {_ALIASES.get(key, (key,))}")
+
+
 def _layer_paths(sch, lay, prefix):
     base = sch[prefix]
     n = len([k for k in base.child if k.startswith(lay["layers"] + ".")])
@@ -93,7 +115,7 @@ def _extract_qkv(old, kind, hidden):
 def replace_attention(sch, config, lay, prefix, attn_op_name):
     count = 0
     hidden = config.hidden_size
-    heads = getattr(config, lay["heads"])
+    heads = _cfg(config, lay["heads"])
     for path in _layer_paths(sch, lay, prefix):
         sub = sch[_j(path, lay["attn"])]
         old = sub.mod
@@ -102,8 +124,8 @@ def replace_attention(sch, config, lay, prefix, attn_op_name):
         probe = old.c_attn if lay["kind"] == "conv1d_fused" else old.q_proj
         has_bias = probe.bias is not None
         is_meta = probe.weight.is_meta
-        attn = FlashAttention(hidden, heads, attn_pdrop=getattr(config, lay["attn_pdrop"]),
-                              resid_pdrop=getattr(config, lay["pdrop"]) if lay["mlp"] else 0.0,
+        attn = FlashAttention(hidden, heads, attn_pdrop=_cfg(config, lay["attn_pdrop"]),
+                              resid_pdrop=_cfg(config, lay["pdrop"]) if lay["mlp"] else 0.0,
                               attn_op_name=attn_op_name, bias=has_bias, output_proj=True,
                               fused_qkv=True, causal=True, scale=lay["scale"],
                               device="meta" if is_meta else probe.weight.device,
@@ -134,8 +156,8 @@ def replace_mlp(sch, config, lay, prefix):
             continue
         fc_in, fc_out = getattr(old, lay["fc_in"]), getattr(old, lay["fc_out"])
         is_meta = fc_in.weight.is_meta
-        new = FusedMLP(config.hidden_size, getattr(config, lay["inter"]),
-                       getattr(config, lay["act"]), getattr(config, lay["pdrop"]),
+        new = FusedMLP(config.hidden_size, _cfg(config, lay["inter"]),
+                       _cfg(config, lay["act"]), _cfg(config, lay["pdrop"]),
                        device="meta" if is_meta else fc_in.weight.device, dtype=fc_in.weight.dtype)
         if not is_meta:
             transposed = fc_in.weight.shape[0] == config.hidden_size and \
@@ -165,7 +187,7 @@ def replace_layernorm(sch):
 def shard_layers(sch, config, lay, prefix, sequence_parallel, sp_axis):
     if sch.world_size == 1:
         return 0
-    heads = getattr(config, lay["heads"])
+    heads = _cfg(config, lay["heads"])
     if heads % sch.world_size:
         raise ValueError(
             f"{heads} attention heads cannot be split over {sch.world_size} ranks; use a "

@@ -39,17 +39,7 @@ class FlashAttentionOp(nn.Module):
 
     def forward(self, query_layer, key_layer, value_layer, attention_mask=None, p=0.0,
                 rel_bias_table=None):
-        key_bias = None
-        if attention_mask is not None:
-            b, sk = key_layer.shape[0], key_layer.shape[1]
-            if attention_mask.dim() == 4:
-                if attention_mask.shape[1] != 1 or attention_mask.shape[2] != 1:
-                    raise NotImplementedError(
-                        "only key-padding masks [B,1,1,Sk] are supported; use causal=True "
-                        "for the triangular part")
-                key_bias = attention_mask.reshape(attention_mask.shape[0], sk).expand(b, sk)
-            else:
-                key_bias = attention_mask.reshape(-1, sk).expand(b, sk)
+        key_bias = self._key_bias(attention_mask, key_layer.shape[0], key_layer.shape[1])
         table = rel_bias_table if rel_bias_table is not None else self.rel_bias_table
         args = (query_layer, key_layer, value_layer, key_bias, self.apply_causal_mask,
                 self.scale, p, self.training, table, self.rel_bidirectional,
@@ -59,14 +49,24 @@ class FlashAttentionOp(nn.Module):
         return NF.flash_attention(*args)
 
     def _key_bias(self, attention_mask, b, sk):
+        """Additive per-key bias ``[B, Sk]`` from the mask a model passes.
+
+        Accepted: ``[B, Sk]`` / ``[B, 1, 1, Sk]`` key-padding masks, and - for causal attention
+        - the combined ``[B, 1, Sq, Sk]`` causal + padding mask that Hugging Face models build:
+        its last query row is exactly the key-padding part (the triangular part is applied by
+        the kernel).  Boolean masks (``True`` = attend) become ``0 / -10000``."""
         if attention_mask is None:
             return None
         if attention_mask.dim() == 4:
-            if attention_mask.shape[1] != 1 or attention_mask.shape[2] != 1:
+            if attention_mask.shape[1] != 1 or (attention_mask.shape[2] != 1
+                                                and not self.apply_causal_mask):
                 raise NotImplementedError(
-                    "only key-padding masks [B,1,1,Sk] are supported; use causal=True "
-                    "for the triangular part")
-            return attention_mask.reshape(attention_mask.shape[0], sk).expand(b, sk)
+                    "only key-padding masks [B,1,1,Sk] are supported (or [B,1,Sq,Sk] causal + "
+                    "padding masks with causal=True); use causal=True for the triangular part")
+            attention_mask = attention_mask[:, :, -1, :]
+        if attention_mask.dtype == torch.bool:
+            attention_mask = torch.zeros_like(attention_mask, dtype=torch.float32).masked_fill(
+                ~attention_mask, -10000.0)
         return attention_mask.reshape(-1, sk).expand(b, sk)
 
     def forward_packed(self, qkv, attention_mask=None, p=0.0):
