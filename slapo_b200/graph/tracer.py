@@ -155,7 +155,69 @@ def dummy_meta_inputs(root: nn.Module, concrete_args=None, config=None):
             metas[name] = torch.empty((batch, seq), dtype=torch.long, device="meta")
         else:
             metas[name] = torch.empty((batch, seq, hidden), dtype=torch.float32, device="meta")
+    if not metas:
+        # Hugging Face models declare every input optional (``input_ids=None``): keep the
+        # token ids live (and the decoder's for encoder-decoder models), freeze the rest
+        params = inspect.signature(root.forward).parameters
+        frozen = concrete_args or {}
+        for name in ("input_ids", "decoder_input_ids"):
+            if name in params and name not in frozen and (
+                    name == "input_ids" or get("is_encoder_decoder", False)):
+                metas[name] = torch.empty((batch, seq), dtype=torch.long, device="meta")
     return metas
+
+
+class _fixed_signature:
+    """Context manager: while active, ``root``'s class is a subclass whose ``forward`` has the
+    named parameters of the original one but neither ``*args`` nor ``**kwargs``.
+
+    fx makes one placeholder per parameter of ``type(root).forward`` and then calls it with
+    those placeholders; a ``**kwargs`` placeholder is a Proxy that the call tries to unpack
+    ("Proxy object cannot be iterated").  Hugging Face modules carry a catch-all ``**kwargs``
+    on almost every forward; nothing is passed through it in a training graph, so it is
+    dropped for the trace."""
+
+    def __init__(self, root):
+        self.root = root
+        self.orig_cls = None
+
+    def __enter__(self):
+        root = self.root
+        try:
+            sig = inspect.signature(type(root).forward)
+        except (TypeError, ValueError):
+            return self
+        params = list(sig.parameters.values())
+        if not any(p.kind in (p.VAR_POSITIONAL, p.VAR_KEYWORD) for p in params):
+            return self
+        named = [p for p in params[1:] if p.kind in (p.POSITIONAL_ONLY, p.POSITIONAL_OR_KEYWORD,
+                                                     p.KEYWORD_ONLY)]
+        defaults = {}
+        decl, call = [], []
+        for p in named:
+            if p.default is inspect.Parameter.empty:
+                decl.append(p.name)
+            else:
+                defaults[p.name] = p.default
+                decl.append(f"{p.name}=__defaults[{p.name!r}]")
+            # by keyword: decorators that wrap a forward as (*args, **kwargs) and fill in
+            # keyword defaults of their own must not collide with positional values
+            call.append(p.name if p.kind == p.POSITIONAL_ONLY else f"{p.name}={p.name}")
+        src = (f"def forward(self, {', '.join(decl)}):\n"
+               f"    return __orig(self, {', '.join(call)})\n")
+        scope = {"__orig": type(root).forward, "__defaults": defaults}
+        exec(src, scope)   # noqa: S102 - source built from parameter names only
+        self.orig_cls = type(root)
+        sub = type(self.orig_cls.__name__, (self.orig_cls,), {"forward": scope["forward"]})
+        sub.__module__ = self.orig_cls.__module__
+        sub.__qualname__ = self.orig_cls.__qualname__
+        root.__class__ = sub
+        return self
+
+    def __exit__(self, *exc):
+        if self.orig_cls is not None:
+            self.root.__class__ = self.orig_cls
+        return False
 
 
 def _direct_child_names(root: nn.Module):
@@ -221,6 +283,41 @@ def _strip_specialisation_guards(graph: fx.Graph, frozen: dict):
                 graph.erase_node(user)
 
 
+def _adapt_call_site(node: fx.Node, child: fx.GraphModule):
+    """Make the parent's call of a freshly traced child fit the child's graph.
+
+    * Keyword arguments that the traced child no longer takes (its catch-all ``**kwargs`` was
+      dropped for the trace: Hugging Face's ``return_dict`` and friends) are removed.
+    * A Hugging Face ``ModelOutput`` becomes a plain dict in the child's graph.  The parent
+      written against ``ModelOutput`` reads it by position (``outputs[0]``: the k-th entry that
+      is not None) or by attribute (``outputs.last_hidden_state``); both are rewritten to the
+      dict key."""
+    import builtins
+    import operator
+
+    names = {str(n.target).lstrip("*") for n in child.graph.nodes if n.op == "placeholder"}
+    if any(k not in names for k in node.kwargs):
+        node.kwargs = {k: v for k, v in node.kwargs.items() if k in names}
+    out = next((n for n in child.graph.nodes if n.op == "output"), None)
+    ret = out.args[0] if out is not None and out.args else None
+    if not isinstance(ret, dict):
+        return
+    present = [k for k, v in ret.items() if v is not None]
+    for user in list(node.users):
+        if user.op != "call_function" or not user.args or user.args[0] is not node:
+            continue
+        if user.target is operator.getitem and isinstance(user.args[1], int):
+            idx = user.args[1]
+            if -len(present) <= idx < len(present):
+                user.args = (node, present[idx])
+        elif user.target is builtins.getattr and isinstance(user.args[1], str):
+            if user.args[1] in ret:
+                user.target = operator.getitem
+            elif not hasattr(dict, user.args[1]):
+                # a field the child did not produce reads as None on a ModelOutput
+                user.args = (node, user.args[1], None)
+
+
 def _get_submodule_or_none(root, target):
     cur = root
     for tok in target.split("."):
@@ -246,7 +343,8 @@ def _trace_with_meta(root, leaf_modules, forced, cargs, config):
     except Exception:       # modules that cannot be copied are traced in place
         shadow = root
     tracer = MetaHierTracer(leaf_modules, forced)
-    graph = tracer.trace(shadow, meta_args=metas, concrete_args=frozen or None)
+    with _fixed_signature(shadow):
+        graph = tracer.trace(shadow, meta_args=metas, concrete_args=frozen or None)
     return graph, frozen
 
 
@@ -268,7 +366,8 @@ def _trace_level(root: nn.Module, *, leaf_modules, flatten, recursive, concrete_
             graph = None
     try:
         if graph is None:
-            graph = tracer.trace(root, concrete_args=cargs or None)
+            with _fixed_signature(root):
+                graph = tracer.trace(root, concrete_args=cargs or None)
     except Exception as first_err:
         # Optional inputs (default None) that steer Python control flow cannot
         # stay symbolic.  Retry once with every such input frozen at None; the
@@ -279,7 +378,8 @@ def _trace_level(root: nn.Module, *, leaf_modules, flatten, recursive, concrete_
         if optional and call_node is None:
             try:
                 cargs = dict(cargs, **optional)
-                graph = HierTracer(leaf_modules, forced).trace(root, concrete_args=cargs)
+                with _fixed_signature(root):
+                    graph = HierTracer(leaf_modules, forced).trace(root, concrete_args=cargs)
                 logger.info("traced %s with optional inputs %s frozen at None",
                             type(root).__name__, sorted(optional))
             except Exception:
@@ -315,6 +415,8 @@ def _trace_level(root: nn.Module, *, leaf_modules, flatten, recursive, concrete_
                     child = _trace_level(
                         child, leaf_modules=leaf_modules, flatten=False, recursive=True,
                         concrete_args=concrete_args, call_node=node)
+                    if isinstance(child, fx.GraphModule):
+                        _adapt_call_site(node, child)
                 pieces[node.target] = child
             elif node.op == "get_attr":
                 pieces[node.target] = _get_submodule_or_none(root, node.target)

@@ -178,3 +178,33 @@ def test_causal_plus_padding_mask_reduces_to_the_key_padding_row():
     torch.testing.assert_close(op._key_bias(keep, b, s), pad)
     with pytest.raises(NotImplementedError):
         FlashAttentionOp(attn_op_name="reference")._key_bias(full, b, s)
+
+
+@pytest.mark.parametrize("family,min_graph_modules", [("bert", 10), ("roberta", 10), ("albert", 5),
+                                                      ("gpt2", 1), ("gpt_neo", 1), ("t5", 2),
+                                                      ("opt", 0)])
+def test_hierarchical_trace_of_a_hugging_face_model(family, min_graph_modules):
+    """``trace(tracer="huggingface")`` on an unmodified Hugging Face model: catch-all ``**kwargs``
+    are dropped for the trace, ``ModelOutput`` reads (by position or attribute) become dict
+    reads, levels whose Python control flow depends on tensor values stay eager modules - and
+    the traced tree computes what the model computed."""
+    import copy
+
+    import torch.fx as fx
+
+    import slapo_b200 as slapo
+
+    torch.manual_seed(7)
+    hf = _hf_cases()[family]().eval()
+    ids = _ids()
+    extra = {"decoder_input_ids": _ids(seq=8, seed=4)} if family == "t5" else {}
+    with torch.no_grad():
+        want = hf(input_ids=ids, **extra).logits
+    sch = slapo.create_schedule(copy.deepcopy(hf))
+    sch.trace(tracer="huggingface", config=hf.config)
+    n_traced = sum(isinstance(m, fx.GraphModule) for m in sch.mod.modules())
+    assert n_traced >= min_graph_modules, n_traced
+    with torch.no_grad():
+        out = sch.mod(ids, **extra)
+    got = out["logits"] if isinstance(out, dict) else out.logits
+    torch.testing.assert_close(got, want, rtol=1e-5, atol=1e-6)
