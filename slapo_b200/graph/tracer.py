@@ -81,6 +81,10 @@ class HierTracer(fx.Tracer):
     def is_leaf_module(self, m: nn.Module, module_qualified_name: str) -> bool:
         if module_qualified_name in self.forced_leaf_names:
             return True
+        # a forward that reaches past a child (``self.model.decoder(...)``): the grandchild is
+        # the unit of this level
+        if any(module_qualified_name.startswith(name + ".") for name in self.forced_leaf_names):
+            return True
         if self.user_leaf(m, module_qualified_name):
             return True
         if isinstance(m, fx.GraphModule):
@@ -97,8 +101,20 @@ def MetaHierTracer(leaf_modules=None, forced_leaf_names=None):   # noqa: N802 - 
     if not _META_TRACER_CLS:
         from torch.fx.experimental.meta_tracer import MetaTracer
 
+        from torch.fx.experimental.meta_tracer import MetaProxy
+
+        class ShapeProxy(MetaProxy):
+            """``ndim`` reads like ``dim()``: a plain int once the meta tensor is known."""
+
+            @property
+            def ndim(self):
+                return self.dim()
+
+        def proxy(self, node):
+            return ShapeProxy(node, self)
+
         _META_TRACER_CLS.append(type("MetaHierTracer", (HierTracer, MetaTracer), {
-            "name": "huggingface", "create_proxy": _meta_create_proxy,
+            "name": "huggingface", "create_proxy": _meta_create_proxy, "proxy": proxy,
             "call_module": _meta_call_module, "_in_meta_eval": False}))
     return _META_TRACER_CLS[0](leaf_modules, forced_leaf_names)
 
@@ -327,17 +343,41 @@ def _get_submodule_or_none(root, target):
     return cur
 
 
-def _trace_with_meta(root, leaf_modules, forced, cargs, config):
-    """Top level of the ``"huggingface"`` engine: trace a meta-device copy (so that leaf
-    modules can run on the meta inputs) and return its graph, whose targets are names and
-    therefore fit the real module tree just as well."""
+def _metas_from_call(root, call_node):
+    """Meta tensors for the arguments of a child module, taken from the shapes that the
+    parent's meta-tensor trace recorded on the nodes of the call site; ``None`` when an
+    argument is a node without a recorded tensor shape (then the plain engine runs)."""
+    sig = inspect.signature(root.forward)
+    params = [p for p in sig.parameters.values()
+              if p.kind not in (p.VAR_POSITIONAL, p.VAR_KEYWORD)]
+    bound = dict(zip((p.name for p in params), call_node.args))
+    bound.update({k: v for k, v in call_node.kwargs.items() if k in sig.parameters})
+    metas = {}
+    for name, val in bound.items():
+        if isinstance(val, fx.Node):
+            if "shape" not in val.meta:
+                return None
+            metas[name] = torch.empty(val.meta["shape"], dtype=val.meta["dtype"], device="meta")
+    return metas or None
+
+
+def _trace_with_meta(root, leaf_modules, forced, cargs, config, metas=None):
+    """The ``"huggingface"`` engine: trace a meta-device copy (so that leaf modules can run on
+    the meta inputs) and return its graph, whose targets are names and therefore fit the real
+    module tree just as well.  ``metas``: the inputs of a lower level (from the parent's call
+    site); at the top they are made up from the signature."""
     import copy
 
-    metas = dummy_meta_inputs(root, cargs, config)
+    if metas is None:
+        metas = dummy_meta_inputs(root, cargs, config)
     frozen = dict(cargs)
     for name, par in inspect.signature(root.forward).parameters.items():
         if name not in metas and name not in frozen and par.default is not inspect.Parameter.empty:
             frozen[name] = par.default
+    if frozen.get("use_cache", False) is None:
+        # Hugging Face decoders build a key / value cache object when ``use_cache`` is left to
+        # the configuration; a training graph has none
+        frozen["use_cache"] = False
     try:
         shadow = copy.deepcopy(root).to("meta")
     except Exception:       # modules that cannot be copied are traced in place
@@ -345,6 +385,11 @@ def _trace_with_meta(root, leaf_modules, forced, cargs, config):
     tracer = MetaHierTracer(leaf_modules, forced)
     with _fixed_signature(shadow):
         graph = tracer.trace(shadow, meta_args=metas, concrete_args=frozen or None)
+    for node in graph.nodes:
+        # a tensor built inside forward becomes an attribute of the traced root - here the
+        # meta copy, whose tensors have no values: such a level needs the plain engine
+        if node.op == "get_attr" and _get_submodule_or_none(root, node.target) is None:
+            raise RuntimeError(f"tensor constant {node.target} created during the meta trace")
     return graph, frozen
 
 
@@ -357,9 +402,12 @@ def _trace_level(root: nn.Module, *, leaf_modules, flatten, recursive, concrete_
     tracer = HierTracer(leaf_modules, forced)
     graph = None
     cargs = _fill_concrete_args(root, concrete_args, call_node)
-    if engine == "huggingface" and call_node is None:
+    metas = None
+    if engine == "huggingface" and call_node is not None:
+        metas = _metas_from_call(root, call_node)
+    if engine == "huggingface" and (call_node is None or metas is not None):
         try:
-            graph, cargs = _trace_with_meta(root, leaf_modules, forced, cargs, config)
+            graph, cargs = _trace_with_meta(root, leaf_modules, forced, cargs, config, metas)
         except Exception as meta_err:
             logger.info("meta-tensor trace of %s failed (%s); trying the plain engine",
                         type(root).__name__, meta_err)
@@ -414,7 +462,8 @@ def _trace_level(root: nn.Module, *, leaf_modules, flatten, recursive, concrete_
                         and not fx.Tracer.is_leaf_module(judge, child, qual)):
                     child = _trace_level(
                         child, leaf_modules=leaf_modules, flatten=False, recursive=True,
-                        concrete_args=concrete_args, call_node=node)
+                        concrete_args=concrete_args, call_node=node, engine=engine,
+                        config=config)
                     if isinstance(child, fx.GraphModule):
                         _adapt_call_site(node, child)
                 pieces[node.target] = child

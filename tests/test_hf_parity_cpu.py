@@ -181,12 +181,13 @@ def test_causal_plus_padding_mask_reduces_to_the_key_padding_row():
 
 
 @pytest.mark.parametrize("family,min_graph_modules", [("bert", 10), ("roberta", 10), ("albert", 5),
-                                                      ("gpt2", 1), ("gpt_neo", 1), ("t5", 2),
-                                                      ("opt", 0)])
+                                                      ("gpt2", 10), ("gpt_neo", 8), ("t5", 8),
+                                                      ("opt", 5)])
 def test_hierarchical_trace_of_a_hugging_face_model(family, min_graph_modules):
     """``trace(tracer="huggingface")`` on an unmodified Hugging Face model: catch-all ``**kwargs``
     are dropped for the trace, ``ModelOutput`` reads (by position or attribute) become dict
-    reads, levels whose Python control flow depends on tensor values stay eager modules - and
+    reads, lower levels are traced on the shapes that the parent's meta-tensor trace recorded,
+    levels whose Python control flow still depends on tensor values stay eager modules - and
     the traced tree computes what the model computed."""
     import copy
 
@@ -201,7 +202,13 @@ def test_hierarchical_trace_of_a_hugging_face_model(family, min_graph_modules):
     with torch.no_grad():
         want = hf(input_ids=ids, **extra).logits
     sch = slapo.create_schedule(copy.deepcopy(hf))
-    sch.trace(tracer="huggingface", config=hf.config)
+    config = hf.config
+    if family == "t5":
+        # the meta-tensor engine specialises the graph on the example shapes: inputs of
+        # different lengths are described explicitly
+        config = {"input_shapes": {"input_ids": (tuple(ids.shape), torch.long),
+                                   "decoder_input_ids": ((2, 8), torch.long)}}
+    sch.trace(tracer="huggingface", config=config)
     n_traced = sum(isinstance(m, fx.GraphModule) for m in sch.mod.modules())
     assert n_traced >= min_graph_modules, n_traced
     with torch.no_grad():
