@@ -215,3 +215,54 @@ def test_hierarchical_trace_of_a_hugging_face_model(family, min_graph_modules):
         out = sch.mod(ids, **extra)
     got = out["logits"] if isinstance(out, dict) else out.logits
     torch.testing.assert_close(got, want, rtol=1e-5, atol=1e-6)
+
+
+def test_static_graph_primitives_on_a_traced_hugging_face_attention():
+    """trace -> find -> horizontal replace on Hugging Face's own BertSelfAttention: the three
+    projection chains (linear, view, transpose) are found as three matches and replaced by one
+    fused module whose outputs are picked apart by ``getitem`` nodes."""
+    import copy
+
+    from torch import nn
+
+    import slapo_b200 as slapo
+    from slapo_b200.pattern import call_module
+
+    torch.manual_seed(8)
+    hf = _hf_cases()["bert"]().eval()
+    ids = _ids()
+    with torch.no_grad():
+        want = hf(input_ids=ids).logits
+    sch = slapo.create_schedule(copy.deepcopy(hf))
+    sch.trace(tracer="huggingface", config=hf.config)       # meta shapes: batch 2, 16 tokens
+    att = sch["bert.encoder.layer.0.attention.self"]
+
+    def pattern(x):
+        x = call_module("query|key|value", x)
+        x = x.view(2, 16, -1, 16)
+        return x.transpose(1, 2)
+
+    groups = att.find(pattern)
+    assert len(groups) == 3 and all(len(g) == 3 for g in groups)
+
+    class FusedProjections(nn.Module):
+        def __init__(self, q, k, v, heads):
+            super().__init__()
+            self.fused = nn.Linear(q.in_features, 3 * q.out_features)
+            self.fused.weight.data = torch.cat([q.weight, k.weight, v.weight], 0).data
+            self.fused.bias.data = torch.cat([q.bias, k.bias, v.bias], 0).data
+            self.heads = heads
+
+        def forward(self, x):
+            b, s, _ = x.shape
+            return tuple(t.view(b, s, self.heads, -1).transpose(1, 2)
+                         for t in self.fused(x).chunk(3, -1))
+
+    old = att.mod
+    att.replace(FusedProjections(old.query, old.key, old.value, 2), groups)
+    calls = [n for n in att.mod.graph.nodes if n.op == "call_module"]
+    assert len(calls) == 1 and "FusedProjections" in str(calls[0].target)
+    with torch.no_grad():
+        out = sch.mod(ids)
+    got = out["logits"] if isinstance(out, dict) else out.logits
+    torch.testing.assert_close(got, want, rtol=1e-5, atol=1e-6)
