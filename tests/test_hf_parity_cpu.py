@@ -266,3 +266,37 @@ def test_static_graph_primitives_on_a_traced_hugging_face_attention():
         out = sch.mod(ids)
     got = out["logits"] if isinstance(out, dict) else out.logits
     torch.testing.assert_close(got, want, rtol=1e-5, atol=1e-6)
+
+
+def _hf_tp_worker(rank, world, family):
+    import copy
+
+    import torch.distributed as dist
+
+    import slapo_b200 as slapo
+
+    torch.manual_seed(0)
+    hf = _hf_cases()[family]().eval()
+    slapo.set_random_seed(3, tp_rank=rank)
+    ids = _ids(seed=1)
+    with torch.no_grad():
+        want = hf(input_ids=ids).logits
+    sch = slapo.model_schedule.apply_schedule(copy.deepcopy(hf), family, model_config=hf.config,
+                                              attn_op_name="reference")
+    model, _ = slapo.build(sch, init_weights=False)
+    with torch.no_grad():
+        out = model(ids)
+    got = out["logits"] if isinstance(out, dict) else out.logits
+    assert got.shape[-1] == want.shape[-1] // world         # vocabulary-parallel logits
+    parts = [torch.empty_like(got) for _ in range(world)]
+    dist.all_gather(parts, got.contiguous())
+    torch.testing.assert_close(torch.cat(parts, -1), want, rtol=1e-4, atol=2e-5)
+
+
+@pytest.mark.parametrize("family", ["bert", "gpt2", "opt"])
+def test_tensor_parallel_recipe_on_a_hugging_face_model(family):
+    """Two gloo ranks: the recipe shards an unmodified Hugging Face model (attention, MLP,
+    vocabulary-parallel embedding and head) and the gathered logits equal the model's."""
+    from dist_utils import run_distributed
+
+    run_distributed(_hf_tp_worker, 2, family)
