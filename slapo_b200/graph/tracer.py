@@ -147,6 +147,9 @@ def _meta_create_proxy(self, kind, target, args, kwargs, name=None, type_expr=No
 
 
 _INT_ARG_HINTS = ("ids", "labels", "mask", "positions")
+# a level with at most this many parameter elements may be traced on real inputs (see
+# _trace_with_meta): embeddings and the like, never a whole trunk
+_REAL_RETRACE_LIMIT = 200_000_000
 
 
 def dummy_meta_inputs(root: nn.Module, concrete_args=None, config=None):
@@ -385,11 +388,20 @@ def _trace_with_meta(root, leaf_modules, forced, cargs, config, metas=None):
     tracer = MetaHierTracer(leaf_modules, forced)
     with _fixed_signature(shadow):
         graph = tracer.trace(shadow, meta_args=metas, concrete_args=frozen or None)
-    for node in graph.nodes:
-        # a tensor built inside forward becomes an attribute of the traced root - here the
-        # meta copy, whose tensors have no values: such a level needs the plain engine
-        if node.op == "get_attr" and _get_submodule_or_none(root, node.target) is None:
-            raise RuntimeError(f"tensor constant {node.target} created during the meta trace")
+    if any(node.op == "get_attr" and _get_submodule_or_none(root, node.target) is None
+           for node in graph.nodes):
+        # A tensor built inside forward (a slice of a buffer, say) becomes an attribute of the
+        # traced root - here the meta copy, whose tensors have no values.  A small level on a
+        # real device is traced again IN PLACE on real zero-filled inputs of the same shapes:
+        # the constants then carry values and land on the real module.
+        n_elems = sum(p.numel() for p in root.parameters())
+        device = next((p.device for p in root.parameters()), torch.device("cpu"))
+        if shadow is root or device.type == "meta" or n_elems > _REAL_RETRACE_LIMIT:
+            raise RuntimeError("a tensor constant was created during the meta trace")
+        reals = {k: torch.zeros(v.shape, dtype=v.dtype, device=device) for k, v in metas.items()}
+        tracer = MetaHierTracer(leaf_modules, forced)
+        with _fixed_signature(root), torch.no_grad():
+            graph = tracer.trace(root, meta_args=reals, concrete_args=frozen or None)
     return graph, frozen
 
 
