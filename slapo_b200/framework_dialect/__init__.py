@@ -3,3 +3,4 @@ from .registry import (DIALECTS, get_all_dialects, get_dialect_cls,  # noqa: F40
                        register_framework_dialect)
 from . import log_parsers  # noqa: F401,E402
 from . import native  # noqa: F401,E402
+from . import compat  # noqa: F401,E402

@@ -5,8 +5,9 @@ adapter exist: ``pipeline_stage`` (wraps one stage module), ``pipeline_engine``
 (assembles the stages), ``runtime_engine`` (returns ``(model, optimizer)``)
 and ``log_parser`` (extracts throughput / memory from a training log for the
 auto-tuner).  Built-in targets: ``None`` (no runtime: ``(model, None)``) and
-``"native"`` (this framework's own engines).  ``"deepspeed"`` and
-``"megatron"`` log parsers are provided for logs of those tools.
+``"native"`` (this framework's own engines).  ``"deepspeed"`` and ``"megatron"`` resolve to
+the native engines after their arguments have been translated (``compat.py``), and log
+parsers are provided for logs of those tools.
 
 Parity: slapo/framework_dialect/registry.py:5-50 of the reference.
 """
