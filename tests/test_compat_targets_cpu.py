@@ -61,3 +61,38 @@ def test_build_with_the_deepspeed_target_trains():
     ids = torch.randint(0, 128, (4, 16))
     losses = [float(engine.train_batch(ids, labels=ids.clone())) for _ in range(5)]
     assert losses[-1] < losses[0]
+
+
+def _ds_dp_worker(rank, world):
+    class Topo:
+        def get_dim(self, axis):
+            return {"pipe": 1, "data": world, "model": 1}[axis]
+
+    cfg = BertConfig(vocab_size=128, hidden_size=32, num_hidden_layers=2, num_attention_heads=2,
+                     intermediate_size=64, hidden_dropout_prob=0.0,
+                     attention_probs_dropout_prob=0.0)
+    torch.manual_seed(0)
+    model = BertForMaskedLM(cfg).init_weights()
+    sch = slapo.model_schedule.apply_schedule(copy.deepcopy(model), "bert", model_config=cfg,
+                                              attn_op_name="reference", group=False)
+    engine, _ = slapo.build(sch, target="deepspeed", config=_ds_config(8, 4, zero_stage=1),
+                            topology=Topo(), init_weights=False,
+                            loss_fn=lambda out, lab: mlm_loss(out["logits"], lab))
+    assert engine.mesh.dp_size == world and engine.cfg.zero and engine.cfg.grad_accum_steps == 1
+    g = torch.Generator().manual_seed(rank)
+    ids = torch.randint(0, 128, (4, 16), generator=g)
+    losses = [float(engine.train_batch(ids, labels=ids.clone())) for _ in range(4)]
+    assert losses[-1] < losses[0]
+    # the replicas hold identical parameters after the sharded optimizer steps
+    import torch.distributed as dist
+
+    flat = torch.cat([p.detach().flatten() for p in engine.model.parameters()])
+    other = flat.clone()
+    dist.broadcast(other, src=0)
+    torch.testing.assert_close(flat, other)
+
+
+def test_deepspeed_target_with_a_data_parallel_topology():
+    from dist_utils import run_distributed
+
+    run_distributed(_ds_dp_worker, 2)
