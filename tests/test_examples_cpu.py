@@ -57,3 +57,35 @@ def test_data_util_chunks(tmp_path):
     assert bool((labels[kept] == ids[kept]).all()) and int(ids.max()) <= data_util.EOS
     assert len(val) >= 1
     sampler.set_epoch(1)
+
+
+def test_example_helpers():
+    sys.path.insert(0, os.path.join(ROOT, "examples"))
+    import copy
+
+    import torch
+
+    import utils as ex_utils
+
+    import slapo_b200 as slapo
+    from slapo_b200.models import BertConfig, BertForMaskedLM, mlm_loss
+
+    cfg = ex_utils.get_ds_config(16, 4, fp16=False, zero_stage=1)
+    assert cfg["train_micro_batch_size_per_gpu"] == 4 and cfg["zero_optimization"]["stage"] == 1
+    assert ex_utils.generate_pipeline_cuts(24, 4) == [5, 11, 17]
+    bcfg = BertConfig(vocab_size=128, hidden_size=32, num_hidden_layers=2, num_attention_heads=2,
+                      intermediate_size=64, hidden_dropout_prob=0.0,
+                      attention_probs_dropout_prob=0.0)
+    torch.manual_seed(0)
+    model = BertForMaskedLM(bcfg).init_weights()
+    ids = torch.randint(0, 128, (4, 16))
+    batches = [((ids,), ids.clone()) for _ in range(6)]
+    opt = torch.optim.AdamW(model.parameters(), lr=1e-2)
+    losses = ex_utils.train_with_torch(copy.deepcopy(model), batches, opt, steps=3)
+    assert len(losses) == 3
+    sch = slapo.model_schedule.apply_schedule(model, "bert", model_config=bcfg, group=False,
+                                              attn_op_name="reference")
+    engine, _ = slapo.build(sch, target="deepspeed", config=ex_utils.get_ds_config(4, 4, fp16=False),
+                            init_weights=False, loss_fn=lambda o, l: mlm_loss(o["logits"], l))
+    losses = ex_utils.train_with_deepspeed_engine(engine, batches, steps=6)
+    assert len(losses) == 6 and losses[-1] < losses[0]
