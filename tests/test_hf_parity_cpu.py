@@ -279,13 +279,14 @@ def _hf_tp_worker(rank, world, family):
     hf = _hf_cases()[family]().eval()
     slapo.set_random_seed(3, tp_rank=rank)
     ids = _ids(seed=1)
+    extra = {"decoder_input_ids": _ids(seq=8, seed=2)} if family == "t5" else {}
     with torch.no_grad():
-        want = hf(input_ids=ids).logits
+        want = hf(input_ids=ids, **extra).logits
     sch = slapo.model_schedule.apply_schedule(copy.deepcopy(hf), family, model_config=hf.config,
                                               attn_op_name="reference")
     model, _ = slapo.build(sch, init_weights=False)
     with torch.no_grad():
-        out = model(ids)
+        out = model(ids, **extra)
     got = out["logits"] if isinstance(out, dict) else out.logits
     assert got.shape[-1] == want.shape[-1] // world         # vocabulary-parallel logits
     parts = [torch.empty_like(got) for _ in range(world)]
@@ -293,7 +294,7 @@ def _hf_tp_worker(rank, world, family):
     torch.testing.assert_close(torch.cat(parts, -1), want, rtol=1e-4, atol=2e-5)
 
 
-@pytest.mark.parametrize("family", ["bert", "gpt2", "opt"])
+@pytest.mark.parametrize("family", ["bert", "gpt2", "opt", "t5"])
 def test_tensor_parallel_recipe_on_a_hugging_face_model(family):
     """Two gloo ranks: the recipe shards an unmodified Hugging Face model (attention, MLP,
     vocabulary-parallel embedding and head) and the gathered logits equal the model's."""
