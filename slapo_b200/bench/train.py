@@ -61,6 +61,10 @@ def parse_args(argv=None):
                          "(and every such interval again): shows where a stuck rank waits")
     ap.add_argument("--no-fused-dp", action="store_true",
                     help="data parallelism through NCCL instead of the peer-memory kernels")
+    ap.add_argument("--p2p-mode", default=None, choices=["paired", "overlap"],
+                    help="pipeline transfers: one batched send + receive group per neighbour, "
+                         "waited for (default next to the fused tensor-parallel kernels), or "
+                         "side-stream transfers posted ahead (default otherwise)")
     ap.add_argument("--profile-table", default=None,
                     help="after the timed steps run two more under torch.profiler and write, per "
                          "rank, PATH.rank<r>.txt: the top device kernels and how much of the "
@@ -233,6 +237,8 @@ def build_engine(args, world, device):
                                 "grad_accum_steps": args.micro_batches if pp == 1 else 1})
     if pp > 1:
         build_kwargs["num_micro_batches"] = args.micro_batches
+        if getattr(args, "p2p_mode", None):
+            build_kwargs["config"]["p2p_mode"] = args.p2p_mode
     if not on_gpu:
         build_kwargs["init_weights"] = False
     elif hasattr(model, "_init_weights"):

@@ -472,10 +472,17 @@ def _trace_level(root: nn.Module, *, leaf_modules, flatten, recursive, concrete_
                 qual = node.target
                 if (recursive and child is not None and not judge.user_leaf(child, qual)
                         and not fx.Tracer.is_leaf_module(judge, child, qual)):
+                    eager = child
                     child = _trace_level(
                         child, leaf_modules=leaf_modules, flatten=False, recursive=True,
                         concrete_args=concrete_args, call_node=node, engine=engine,
                         config=config)
+                    if child is not eager:
+                        # the traced child stands in for the eager one: its hooks (the
+                        # collectives that ``sync`` registered among them) move along
+                        from ..utils.common import transfer_hooks
+
+                        transfer_hooks(eager, child)
                     if isinstance(child, fx.GraphModule):
                         _adapt_call_site(node, child)
                 pieces[node.target] = child

@@ -102,7 +102,7 @@ def fuse_blocks(sch, config, prefix):
     return count
 
 
-def shard_layers(sch, config, prefix, sequence_parallel, sp_axis=0):
+def shard_layers(sch, config, prefix, sequence_parallel, sp_axis=0, pipeline=False):
     if sch.world_size == 1:
         return 0
     if config.num_attention_heads % sch.world_size != 0:
@@ -130,8 +130,10 @@ def shard_layers(sch, config, prefix, sequence_parallel, sp_axis=0):
         # this rank's part, and put the sequence together again after the
         # last layer (the consumers are replicas, so the gradient is sliced)
         sch[_j(prefix, "embeddings")].sync("fwd_post", "scatter", axis=sp_axis)
-        sch[_j(prefix, "encoder")].sync("fwd_post", "all_gather", axis=sp_axis,
-                                      tensor_parallel_output_grad=False)
+        # With pipeline cuts the encoder dissolves into the stages and a hook on it would be
+        # lost: the gather then sits on the last layer, which stays a module of the last stage.
+        end = _layer_paths(sch, prefix)[-1] if pipeline else _j(prefix, "encoder")
+        sch[end].sync("fwd_post", "all_gather", axis=sp_axis, tensor_parallel_output_grad=False)
     return len(_layer_paths(sch, prefix))
 
 
@@ -174,7 +176,8 @@ def schedule_bert(model, model_config=None, prefix="bert", fp16=False, bf16=Fals
     pre = prefix
     n_attn = 0 if disable_flash_attn else replace_attention(sch, config, pre, attn_op_name)
     n_fused = fuse_blocks(sch, config, pre) if fuse else 0
-    n_shard = shard_layers(sch, config, pre, sequence_parallel, sequence_parallel_axis)
+    n_shard = shard_layers(sch, config, pre, sequence_parallel, sequence_parallel_axis,
+                           pipeline=bool(pipeline_cuts))
     if shard_vocab and config.vocab_size % max(sch.world_size, 1) == 0:
         shard_lm_head(sch, config, pre)
     if bcast_input:

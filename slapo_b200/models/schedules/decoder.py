@@ -218,6 +218,10 @@ def shard_layers(sch, config, lay, prefix, sequence_parallel, sp_axis):
         for pos in lay["pos"]:
             if sp_axis == 1:  # position embeddings are [1, S, H]: only a sequence split applies
                 sch[_j(prefix, pos)].sync("fwd_post", "scatter", axis=sp_axis)
+            else:
+                # under a batch split every rank adds the whole [1, S, H] table to its own
+                # sequences, so the table's gradient is a partial sum like a LayerNorm's
+                sch[_j(prefix, pos)].annotate("weight", "replicated_param", True)
         sch[_j(prefix, lay["ln_f"])].sync("fwd_post", "all_gather", axis=sp_axis,
                                           tensor_parallel_output_grad=False)
         annotate_replicated(sch, [_j(prefix, lay["ln_f"])], [])

@@ -5,7 +5,8 @@ attention.
 ``[B, S, H, D]`` tensors to the tcgen05 flash-attention kernels (CUDA,
 bf16/fp16) or to the PyTorch reference (everything else).  An HF-style
 additive mask ``[B, 1, 1, Sk]`` is honoured on every path (the reference's
-``cuda`` path silently drops it, slapo/op/attention.py:318-323).
+``cuda`` path silently drops it, slapo/op/attention.py:318-323); a bias per
+head or per (query, key) pair runs the PyTorch reference, with a warning.
 
 ``FlashAttention`` is a complete self-attention block: fused or separate
 q/k/v projections, the op, optional output projection + dropout.  The fused
@@ -24,6 +25,22 @@ from . import functional as NF
 _REFERENCE_NAMES = ("reference", "native_xformers", "native_flash_attn", "eager")
 
 
+_GENERAL_BIAS_SEEN = set()
+
+
+def _warn_general_bias(bias):
+    key = tuple(bias.shape[1:3])
+    if key in _GENERAL_BIAS_SEEN:
+        return
+    _GENERAL_BIAS_SEEN.add(key)
+    import logging
+
+    logging.getLogger("slapo_b200.ops").warning(
+        "attention bias of shape %s is not a key-padding mask: this call runs the PyTorch "
+        "reference with a materialised score matrix (kernels take [B, Sk] / [B, 1, 1, Sk] masks, "
+        "causal=True and T5 relative-position tables)", tuple(bias.shape))
+
+
 class FlashAttentionOp(nn.Module):
     traceable = False
 
@@ -39,14 +56,34 @@ class FlashAttentionOp(nn.Module):
 
     def forward(self, query_layer, key_layer, value_layer, attention_mask=None, p=0.0,
                 rel_bias_table=None):
-        key_bias = self._key_bias(attention_mask, key_layer.shape[0], key_layer.shape[1])
         table = rel_bias_table if rel_bias_table is not None else self.rel_bias_table
+        if self._is_general_bias(attention_mask):
+            # a bias per head or per (query, key) pair: no kernel takes one, the PyTorch
+            # reference does (the path the reference library calls "native_xformers" with a
+            # tensor bias, slapo/op/attention.py:339-365)
+            _warn_general_bias(attention_mask)
+            if attention_mask.dtype == torch.bool:
+                attention_mask = torch.zeros_like(
+                    attention_mask, dtype=torch.float32).masked_fill(~attention_mask, -10000.0)
+            return NF.attention_reference(
+                query_layer, key_layer, value_layer, None, self.apply_causal_mask, self.scale, p,
+                self.training, table, self.rel_bidirectional, self.rel_max_distance,
+                attn_bias=attention_mask)
+        key_bias = self._key_bias(attention_mask, key_layer.shape[0], key_layer.shape[1])
         args = (query_layer, key_layer, value_layer, key_bias, self.apply_causal_mask,
                 self.scale, p, self.training, table, self.rel_bidirectional,
                 self.rel_max_distance)
         if self.attn_op_name in _REFERENCE_NAMES:
             return NF.attention_reference(*args)
         return NF.flash_attention(*args)
+
+    def _is_general_bias(self, attention_mask):
+        """True for a 4-D bias that is not a key-padding mask (nor, for causal attention, the
+        causal + padding mask whose last row is one)."""
+        if attention_mask is None or attention_mask.dim() != 4:
+            return False
+        return attention_mask.shape[1] != 1 or (attention_mask.shape[2] != 1
+                                                and not self.apply_causal_mask)
 
     def _key_bias(self, attention_mask, b, sk):
         """Additive per-key bias ``[B, Sk]`` from the mask a model passes.
@@ -74,7 +111,8 @@ class FlashAttentionOp(nn.Module):
         packed kernel path does not apply (the caller then slices q/k/v)."""
         from .flash_attn import flash_attention_qkvpacked, packed_supported
 
-        if self.attn_op_name in _REFERENCE_NAMES or not packed_supported(qkv):
+        if self.attn_op_name in _REFERENCE_NAMES or not packed_supported(qkv) \
+                or self._is_general_bias(attention_mask):
             return None
         key_bias = self._key_bias(attention_mask, qkv.shape[0], qkv.shape[1])
         return flash_attention_qkvpacked(

@@ -349,11 +349,13 @@ def t5_relative_position_bucket(relative_position, bidirectional=True, num_bucke
 
 def attention_reference(q, k, v, key_padding_bias=None, causal=False, scale=None,
                         dropout_p=0.0, training=False, rel_bias_table=None,
-                        rel_bidirectional=True, rel_max_distance=128, dropout_mask=None):
+                        rel_bidirectional=True, rel_max_distance=128, dropout_mask=None,
+                        attn_bias=None):
     """Plain-PyTorch attention on ``[B, S, H, D]`` tensors (the oracle).
 
     ``key_padding_bias`` is an additive ``[B, Sk]`` bias (0 / large negative);
-    ``rel_bias_table`` a ``[num_buckets, H]`` T5 relative-position table."""
+    ``rel_bias_table`` a ``[num_buckets, H]`` T5 relative-position table; ``attn_bias`` any
+    additive bias that broadcasts to ``[B, H, Sq, Sk]`` (only this function takes one)."""
     b, sq, h, d = q.shape
     sk = k.shape[1]
     scale = (1.0 / math.sqrt(d)) if scale is None else scale
@@ -367,6 +369,8 @@ def attention_reference(q, k, v, key_padding_bias=None, causal=False, scale=None
         scores = scores + rel_bias_table.float()[buckets].permute(2, 0, 1)[None]
     if key_padding_bias is not None:
         scores = scores + key_padding_bias.float().view(b, 1, 1, sk)
+    if attn_bias is not None:
+        scores = scores + attn_bias.float()
     if causal:
         keep = torch.ones(sq, sk, dtype=torch.bool, device=q.device).tril(diagonal=sk - sq)
         scores = scores.masked_fill(~keep, float("-inf"))

@@ -37,6 +37,18 @@ def test_train_entry_tp2_pp2_save_and_resume(tmp_path):
     assert rec2["start_step"] == 3
 
 
+def test_train_entry_tp2_pp2_paired_transfers_match_overlapped_ones():
+    """The paired p2p schedule (the default next to the fused tensor-parallel kernels on GPUs)
+    and the side-stream schedule compute the same step."""
+    import bench_single_node as B
+    args = ["--tp", "2", "--pp", "2", "--micro-batches", "4", "--sequence-parallel"] + TINY
+    a, text = B.launch("opt-350m", 4, args + ["--p2p-mode", "paired"], port=29566, timeout=600)
+    assert a is not None, text[-3000:]
+    b, text = B.launch("opt-350m", 4, args + ["--p2p-mode", "overlap"], port=29567, timeout=600)
+    assert b is not None, text[-3000:]
+    assert abs(a["loss"] - b["loss"]) < 1e-5, (a["loss"], b["loss"])
+
+
 def test_train_entry_dp2_sequence_parallel_tp():
     import bench_single_node as B
     rec, text = B.launch("bert-base", 4, ["--tp", "2", "--sequence-parallel"] + TINY, port=29563)

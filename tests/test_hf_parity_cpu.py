@@ -180,6 +180,32 @@ def test_causal_plus_padding_mask_reduces_to_the_key_padding_row():
         FlashAttentionOp(attn_op_name="reference")._key_bias(full, b, s)
 
 
+def test_bias_per_head_and_query_runs_the_reference_attention():
+    """A ``[B, H, Sq, Sk]`` additive bias (ALiBi-like, or a relative bias computed outside)
+    is honoured: the op takes the PyTorch path for it, whichever kernel name it carries."""
+    from slapo_b200.ops.attention import FlashAttentionOp
+
+    torch.manual_seed(3)
+    b, s, h, d = 2, 6, 3, 8
+    q, k, v = (torch.randn(b, s, h, d) for _ in range(3))
+    bias = torch.randn(b, h, s, s)
+    for causal in (False, True):
+        op = FlashAttentionOp(attn_op_name="auto", apply_causal_mask=causal).eval()
+        scores = torch.einsum("bqhd,bkhd->bhqk", q, k) / d ** 0.5 + bias
+        if causal:
+            scores = scores.masked_fill(torch.ones(s, s).triu(1).bool(), float("-inf"))
+        want = torch.einsum("bhqk,bkhd->bqhd", scores.softmax(-1), v)
+        torch.testing.assert_close(op(q, k, v, bias), want, rtol=1e-5, atol=1e-5)
+    # a boolean mask per (query, key) pair, shared by the heads, without causal masking
+    keep = torch.rand(b, 1, s, s) > 0.3
+    keep[..., 0] = True
+    op = FlashAttentionOp(attn_op_name="auto").eval()
+    scores = torch.einsum("bqhd,bkhd->bhqk", q, k) / d ** 0.5
+    want = torch.einsum("bhqk,bkhd->bqhd",
+                        (scores + (~keep).float() * -10000.0).softmax(-1), v)
+    torch.testing.assert_close(op(q, k, v, keep), want, rtol=1e-5, atol=1e-5)
+
+
 @pytest.mark.parametrize("family,min_graph_modules", [("bert", 10), ("roberta", 10), ("albert", 5),
                                                       ("gpt2", 10), ("gpt_neo", 8), ("t5", 8),
                                                       ("opt", 5)])

@@ -120,6 +120,64 @@ def test_pipeline_four_stages(p2p_mode, prefetch_recv):
     run_distributed(_pp4_worker, 4, p2p_mode, prefetch_recv)
 
 
+def _pp_tp_sp_worker(rank, world, family):
+    """2 stages x 2-way tensor parallelism with sequence parallelism.  The gather that ends
+    the sequence-parallel region sits on a module that the pipeline trace re-creates (the
+    decoders' final LayerNorm becomes a graph module: its ``sync`` hook has to move along) or
+    dissolves (BERT's encoder: the gather moves to the last layer); otherwise the last stage
+    computes the loss on a shard of the batch.  Two steps with a real learning rate: the
+    second loss is right only if the gradients of the first were."""
+    from slapo_b200.models import OPTConfig, OPTForCausalLM, causal_lm_loss
+
+    torch.manual_seed(21)
+    if family == "opt":
+        cfg = OPTConfig(vocab_size=512, hidden_size=64, num_hidden_layers=4, ffn_dim=128,
+                        num_attention_heads=4, max_position_embeddings=64, dropout=0.0)
+        ref = OPTForCausalLM(cfg).init_weights()
+        loss_of = causal_lm_loss
+    else:
+        cfg = BertConfig(vocab_size=512, hidden_size=64, num_hidden_layers=4,
+                         num_attention_heads=4, intermediate_size=128, hidden_dropout_prob=0.0,
+                         attention_probs_dropout_prob=0.0)
+        ref = BertForMaskedLM(cfg).init_weights()
+        loss_of = mlm_loss
+    ids = torch.randint(0, 512, (4, 32))
+    labels = ids.clone()
+    mesh = DeviceMesh(pp=2, dp=1, tp=2)
+    slapo.set_random_seed(1, tp_rank=mesh.tp_rank, pp_rank=mesh.pp_rank)
+    sch = slapo.model_schedule.apply_schedule(
+        copy.deepcopy(ref), family, model_config=cfg, group=mesh.schedule_group,
+        attn_op_name="reference", sequence_parallel=True, sequence_parallel_axis=0,
+        pipeline_cuts=[1])
+    seen = []
+
+    def loss_fn(out, lab):
+        seen.append(tuple(out["logits"].shape))
+        return loss_of(out["logits"], lab, mesh.tp_group, True)
+
+    lr = 1e-2
+    engine, _ = slapo.build(sch, target="native", mesh=mesh, init_weights=False,
+                            num_micro_batches=2, loss_fn=loss_fn,
+                            config={"lr": lr, "clip_grad": 0.0, "weight_decay": 0.0})
+    ref_opt = torch.optim.AdamW(ref.parameters(), lr=lr, weight_decay=0.0, eps=1e-8)
+    for step in range(2):
+        loss = engine.train_batch(ids, labels=labels)
+        ref_opt.zero_grad()
+        want = torch.stack([loss_of(ref(i)["logits"], l)
+                            for i, l in zip(ids.chunk(2), labels.chunk(2))]).mean()
+        want.backward()
+        ref_opt.step()
+        torch.testing.assert_close(loss, want.detach(), rtol=2e-4, atol=2e-5,
+                                   msg=lambda m: f"step {step}: {m}")
+    if mesh.pp_rank == 1:       # whole micro-batches reach the head, vocabulary-sharded
+        assert seen and all(shape == (2, 32, 256) for shape in seen), seen
+
+
+@pytest.mark.parametrize("family", ["opt", "bert"])
+def test_pipeline_with_tensor_and_sequence_parallel_stages(family):
+    run_distributed(_pp_tp_sp_worker, 4, family)
+
+
 def _zoo_pipeline(name, n_stages):
     """Scheduled + partitioned model of the zoo, run stage after stage in one
     process, against the unpartitioned model."""
