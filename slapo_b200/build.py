@@ -179,6 +179,12 @@ def build(sch, target=None, init_weights=True, **kwargs):
     from .pipeline import analyze_tie_weights, build_pipeline_model, generate_pipeline_partition
 
     cuts = sch.metadata.primitives.get("cut_pipeline_stage") or []
+    mesh = kwargs.get("mesh")
+    if not cuts and target is not None and getattr(mesh, "pp_size", 1) > 1:
+        raise ValueError(
+            f"the mesh has {mesh.pp_size} pipeline stages but the schedule has no "
+            "cut_pipeline_stage(): every pipeline rank would train the whole model on its own "
+            "(pass pipeline_cuts to the recipe, or build the mesh with pp=1)")
     if cuts:
         sch = generate_pipeline_partition(sch)
         sch.metadata.tie_weights = analyze_tie_weights(sch.mod, is_pipeline_partitioned=True)

@@ -3,6 +3,13 @@ once and every depth benefits.  q / k / v and ``ffn`` column-parallel,
 ``attention.dense`` and ``ffn_output`` row-parallel, the factorised word
 embedding vocabulary-parallel, bias + activation of ``ffn`` fused.
 
+``pipeline_cuts=[k, ...]`` ends a stage after the k-th pass (0-based) through
+the layers: the encoder is traced, which unrolls its loop into one call of
+the shared group per pass, and the cut is put on that call.  Every stage
+holds the shared layer; the pipeline engine ties the copies.  (The reference
+cuts at ``encoder.layer.k``, a path that ALBERT models do not have -
+slapo/model_schedule/albert.py:118-141.)
+
 Parity: slapo/model_schedule/albert.py:21-353 of the reference.
 """
 from __future__ import annotations
@@ -24,9 +31,23 @@ def _layers(sch, prefix):
     return out
 
 
+def pipeline_cut(sch, config, prefix, cuts):
+    """End a stage after pass ``k`` through the layers, for every ``k`` in ``cuts``."""
+    sch.trace_until(f"{prefix}.encoder", tracer="pytorch")
+    per_group = config.num_hidden_layers // config.num_hidden_groups
+    for k in cuts:
+        if not 0 <= k < config.num_hidden_layers - 1:
+            raise ValueError(f"pipeline cut {k}: the model makes {config.num_hidden_layers} "
+                             "passes, a stage can end after pass 0 .. "
+                             f"{config.num_hidden_layers - 2}")
+        group = sch[f"{prefix}.encoder.albert_layer_groups.{k // per_group}"]
+        group.cut_pipeline_stage(call_index=k % per_group)
+
+
 @register_schedule("albert")
 def schedule_albert(model, model_config=None, prefix="albert", fp16=False, bf16=False,
-                    group=None, fuse=True, ckpt_ratio=0.0, bcast_input=False, **_unused):
+                    group=None, fuse=True, ckpt_ratio=0.0, bcast_input=False, pipeline_cuts=None,
+                    **_unused):
     config = model_config if model_config is not None else getattr(model, "config", None)
     if config is None:
         raise ValueError("model_config is required")
@@ -58,6 +79,8 @@ def schedule_albert(model, model_config=None, prefix="albert", fp16=False, bf16=
     if ckpt_ratio > 0:
         for path in layers:
             sch[path].checkpoint()
+    if pipeline_cuts:
+        pipeline_cut(sch, config, prefix, pipeline_cuts)
     logger.info("albert schedule: %d shared layers scheduled (tp=%d)", len(layers),
                 sch.world_size, ranks=0)
     return sch
