@@ -89,7 +89,8 @@ def translate_ds_config(config, dp_size=1):
     fp16 = cfg.get("fp16") or {}
     if isinstance(fp16, dict) and fp16.get("enabled"):
         logger.info("fp16 is enabled in the configuration: the model's own dtype decides here "
-                    "(pass fp16=True / bf16=True to the schedule recipe)")
+                    "(pass fp16=True / bf16=True to the schedule recipe); the engine's loss "
+                    "scaler takes the block's initial_scale_power / loss_scale / window")
     for key, val in cfg.items():
         out.setdefault(key, val)
     return out

@@ -43,6 +43,18 @@ logger = get_logger("engine")
 
 @dataclass
 class EngineConfig:
+    """Settings of the native engines (``build(..., target="native", config={...})``; a
+    DeepSpeed-style dict with ``optimizer.params``, ``gradient_clipping``,
+    ``gradient_accumulation_steps`` and an ``fp16`` block is accepted too).
+
+    ``lr``, ``betas``, ``eps``, ``weight_decay`` - AdamW (biases and norm weights are not
+    decayed); ``clip_grad`` - global gradient-norm limit over the whole model, 0 = off;
+    ``zero`` - shard the optimizer state over the data-parallel group; ``bucket_mb``,
+    ``overlap_comm`` - gradient buckets reduced during backward; ``grad_accum_steps`` -
+    micro-batches per update; ``lr_schedule`` - ``callable(step) -> multiplier``;
+    ``loss_scale``, ``initial_scale_power``, ``loss_scale_window``, ``min_loss_scale`` - fp16
+    loss scaling (see the fields); ``profile`` - NVTX ranges and phase timers.  Keys the class
+    does not know (``fused_dp``, ``p2p_mode``, ``prefetch_recv``, ...) are kept in ``extra``."""
     lr: float = 1e-4
     betas: tuple = (0.9, 0.999)
     eps: float = 1e-8
@@ -57,6 +69,14 @@ class EngineConfig:
     # schedule primitives created, plus device-timed phase durations (``phase_times()``);
     # costs one event pair per phase and no synchronisation
     profile: bool = False
+    # fp16 loss scaling: None = dynamic when the parameters are fp16, off otherwise; 0 = dynamic;
+    # > 0 = that fixed scale.  Dynamic: start at 2**initial_scale_power, halve (not below
+    # min_loss_scale) and skip the update when a gradient overflowed, double after
+    # loss_scale_window clean steps.
+    loss_scale: float = None
+    initial_scale_power: int = 16
+    loss_scale_window: int = 1000
+    min_loss_scale: float = 1.0
     extra: dict = field(default_factory=dict)
 
     @classmethod
@@ -74,6 +94,12 @@ class EngineConfig:
             for k in ("lr", "betas", "eps", "weight_decay"):
                 if k in params:
                     cfg[k] = tuple(params[k]) if k == "betas" else params[k]
+        fp16 = cfg.get("fp16")
+        if isinstance(fp16, dict):      # DeepSpeed's block; "enabled" is the model's dtype here
+            cfg.pop("fp16")
+            for k in ("loss_scale", "initial_scale_power", "loss_scale_window", "min_loss_scale"):
+                if k in fp16:
+                    cfg.setdefault(k, fp16[k])
         if "gradient_clipping" in cfg:
             cfg["clip_grad"] = cfg.pop("gradient_clipping")
         if "gradient_accumulation_steps" in cfg:
@@ -150,6 +176,7 @@ class TrainEngine:
         self._status_host = None      # pinned copy of the kernels' status word, one step behind
         self._status_event = None
         self._build_flat_storage()
+        self._init_loss_scale()
         self._build_optimizer_state()
         self._install_grad_hooks()
         self._phase_events = []       # (name, start event, end event) of the last step
@@ -244,12 +271,52 @@ class TrainEngine:
                 self.sp_sync_params.append(p)
         self.n_params_local = sum(n for _, n, _ in self.param_slices)
 
+    # ---- fp16 loss scaling --------------------------------------------- #
+    def _init_loss_scale(self):
+        """``self.loss_scale`` is the factor the loss is multiplied by before backward (a float;
+        1.0 = off).  It changes only between steps, on the host, after the one synchronising
+        read of the overflow flag that dynamic scaling needs per step."""
+        want = self.cfg.loss_scale
+        if want is None:
+            self.dynamic_scale = self.param_dtype == torch.float16
+            self.loss_scale = 2.0 ** self.cfg.initial_scale_power if self.dynamic_scale else 1.0
+        elif want == 0:
+            self.dynamic_scale = True
+            self.loss_scale = 2.0 ** self.cfg.initial_scale_power
+        else:
+            self.dynamic_scale = False
+            self.loss_scale = float(want)
+        self.scaling = self.dynamic_scale or self.loss_scale != 1.0
+        self._clean_steps = 0
+        self.skipped_steps = 0
+
+    def scale_loss(self, loss):
+        """The loss as it goes into backward (the pipeline engine scales its last stage's loss
+        with this as well)."""
+        return loss * self.loss_scale if self.scaling else loss
+
+    def _update_loss_scale(self, overflow: bool):
+        if not self.dynamic_scale:
+            return
+        if overflow:
+            self.loss_scale = max(self.loss_scale / 2.0, float(self.cfg.min_loss_scale))
+            self._clean_steps = 0
+            return
+        self._clean_steps += 1
+        if self._clean_steps >= self.cfg.loss_scale_window:
+            self.loss_scale *= 2.0
+            self._clean_steps = 0
+
     def _want_fused_dp(self):
         """ZeRO-1 over NVLink peer memory instead of NCCL: CUDA, 16-bit parameters, a
         data-parallel group of 2..8 ranks on this node, not switched off by ``fused_dp=False``."""
         if not (self.cfg.zero and 1 < self.dp_size <= 8 and self.device.type == "cuda"):
             return False
         if not self.cfg.extra.get("fused_dp", True) or not native.available():
+            return False
+        if self.scaling:
+            # a step skipped after an overflow must not advance the optimizer, but the peer
+            # kernels' hand-shake epochs advance with the step count: NCCL path under scaling
             return False
         if self.param_dtype not in (torch.bfloat16, torch.float16):
             return False
@@ -415,6 +482,7 @@ class TrainEngine:
         if self.cfg.grad_accum_steps > 1:
             loss = loss / self.cfg.grad_accum_steps
         self._final_backward = (self.micro_step + 1) % self.cfg.grad_accum_steps == 0
+        loss = self.scale_loss(loss)
         loss.backward()
         self.micro_step += 1
 
@@ -471,17 +539,37 @@ class TrainEngine:
         if self.dp_size > 1:
             self._reduce_all_buckets()
         grad = self._own_grad()
+        clip_coef = None
+        clipping = bool(self.cfg.clip_grad and self.cfg.clip_grad > 0)
+        if clipping or self.scaling:
+            # the fused reduce-scatter kernels already accumulated the squared norm
+            norm = self._finish_norm(self.fdp.take_norm_parts()) if self.fdp is not None \
+                else self._grad_norm(grad)
+            if self.scaling:
+                # the norm is the same on every rank of the job (summed over the tensor-,
+                # data- and pipeline-parallel groups), so every rank takes the same branch
+                overflow = not bool(torch.isfinite(norm))
+                scale_used = self.loss_scale        # the gradients in the buffers carry this one
+                self._update_loss_scale(overflow)
+                if overflow:
+                    self.skipped_steps += 1
+                    self.flat_grad.zero_()
+                    if self.grad_shard is not None:
+                        self.grad_shard.zero_()
+                    logger.info("gradient overflow: step skipped, loss scale now %g",
+                                self.loss_scale, ranks=0)
+                    return False
+                norm = norm / scale_used
+            self.last_grad_norm = norm
+            if clipping:
+                clip_coef = torch.clamp(self.cfg.clip_grad / (norm + 1e-6), max=1.0)
+            if self.scaling:
+                unscale = torch.full((), 1.0 / scale_used, device=norm.device)
+                clip_coef = unscale if clip_coef is None else clip_coef * unscale
         self.step_count += 1
         lr = self.cfg.lr
         if self.cfg.lr_schedule is not None:
             lr = lr * self.cfg.lr_schedule(self.step_count)
-        clip_coef = None
-        if self.cfg.clip_grad and self.cfg.clip_grad > 0:
-            # the fused reduce-scatter kernels already accumulated the squared norm
-            norm = self._finish_norm(self.fdp.take_norm_parts()) if self.fdp is not None \
-                else self._grad_norm(grad)
-            self.last_grad_norm = norm
-            clip_coef = torch.clamp(self.cfg.clip_grad / (norm + 1e-6), max=1.0)
         self._adamw(grad, lr, clip_coef)
         self._params_pushed = self.fdp is not None
         self._gather_params()
@@ -645,10 +733,14 @@ class TrainEngine:
     def optimizer_state(self):
         return {"step": self.step_count, "master": self.master, "exp_avg": self.exp_avg,
                 "exp_avg_sq": self.exp_avg_sq, "shard_ranges": list(self.shard_ranges),
-                "dp_size": self.dp_size, "dp_rank": self.dp_rank, "zero": self.cfg.zero}
+                "dp_size": self.dp_size, "dp_rank": self.dp_rank, "zero": self.cfg.zero,
+                "loss_scale": self.loss_scale, "clean_steps": self._clean_steps}
 
     def load_optimizer_state(self, state):
         self.step_count = int(state["step"])
+        if self.scaling and "loss_scale" in state:
+            self.loss_scale = float(state["loss_scale"])
+            self._clean_steps = int(state.get("clean_steps", 0))
         for key in ("master", "exp_avg", "exp_avg_sq"):
             getattr(self, key).copy_(state[key])
         for (lo, hi), pos in zip(self.shard_ranges, self.shard_offsets):
@@ -738,6 +830,9 @@ class TrainEngine:
             raise RuntimeError("capture_step supports single-process engines only")
         if self.cfg.grad_accum_steps != 1:
             raise RuntimeError("capture_step needs grad_accum_steps == 1")
+        if self.scaling:
+            raise RuntimeError("capture_step does not support fp16 loss scaling (the overflow "
+                               "check decides on the host whether the update runs); use bf16")
         static_in = [t.clone() if torch.is_tensor(t) else t for t in example_inputs]
         static_labels = labels.clone() if torch.is_tensor(labels) else labels
         self._hyper = torch.zeros(3, dtype=torch.float32, device=self.device)

@@ -353,7 +353,8 @@ class PipelineEngine:
 
     def _compute_backward(self, rec, grads):
         if rec["loss"] is not None:
-            rec["loss"].backward()
+            # fp16 loss scaling: the last stage scales, the earlier ones receive scaled gradients
+            self.inner.scale_loss(rec["loss"]).backward()
         elif rec["sent"]:
             torch.autograd.backward(rec["sent"], grads)
         return [t.grad if t.grad is not None else torch.zeros_like(t) for t in rec["received"]]
