@@ -8,7 +8,8 @@ parallel layouts that combine the most machinery:
 
 The first step's loss checks the forward pass; the second and third only match when every
 gradient - sharded, replicated over the tensor-parallel group, tied across stages, reduced over
-the data-parallel group - and the optimizer state are right.  (The reference library has no such
+the data-parallel group -, the global gradient norm that clipping divides by, the weight-decay
+mask and the optimizer state are right.  (The reference library has no such
 test: its models are trained by DeepSpeed / Megatron-LM, outside its test suite.)"""
 import copy
 import dataclasses
@@ -24,6 +25,7 @@ _TRANSFORMER = dict(vocab_size=512, hidden_size=64, intermediate_size=128, ffn_d
                     num_decoder_layers=4, embedding_size=32, d_model=64, d_kv=16, d_ff=128,
                     hidden_dropout_prob=0.0, attention_probs_dropout_prob=0.0, dropout=0.0,
                     dropout_rate=0.0, resid_dropout=0.0, embed_dropout=0.0, attention_dropout=0.0)
+_CLIP, _DECAY = 0.05, 0.1                # a limit far below the gradient norms: always clipping
 _POSITIONS = {"roberta-large": 66}      # RoBERTa's table starts after the padding index
 _SP_FAMILIES = ("bert", "roberta", "gpt2", "gpt_neo", "opt")
 
@@ -66,10 +68,14 @@ def _worker(rank, world, name, pp, tp, dp, ckpt):
     engine, _ = slapo.build(
         sch, target="native", mesh=mesh, init_weights=False,
         loss_fn=spec.loss_fn(mesh.tp_group, tp > 1),
-        config={"lr": 1e-2, "clip_grad": 0.0, "weight_decay": 0.0,
+        config={"lr": 1e-2, "clip_grad": _CLIP, "weight_decay": _DECAY,
                 "grad_accum_steps": 1 if pp > 1 else micro}, **extra)
     ref_loss = spec.loss_fn(None, False)
-    ref_opt = torch.optim.AdamW(ref.parameters(), lr=1e-2, weight_decay=0.0, eps=1e-8)
+    # the engines decay matrices only (no biases, no norm weights); tied tensors count once
+    unique = list({id(p): p for p in ref.parameters()}.values())
+    ref_opt = torch.optim.AdamW(
+        [{"params": [p for p in unique if p.dim() > 1], "weight_decay": _DECAY},
+         {"params": [p for p in unique if p.dim() <= 1], "weight_decay": 0.0}], lr=1e-2, eps=1e-8)
     # every data-parallel rank trains on its own batch; the reference sees all of them
     batches = [spec.make_batch(4, seq=32, seq_dec=16, seed=3 + r) for r in range(dp)]
     inputs, labels = batches[mesh.dp_rank]
@@ -84,6 +90,7 @@ def _worker(rank, world, name, pp, tp, dp, ckpt):
         wants = [ref_loss(ref(*(t.chunk(micro)[m] for t in ins)), lab.chunk(micro)[m])
                  for ins, lab in batches for m in range(micro)]
         torch.stack(wants).mean().backward()
+        torch.nn.utils.clip_grad_norm_(unique, _CLIP)
         ref_opt.step()
         want = torch.stack(wants[mesh.dp_rank * micro:(mesh.dp_rank + 1) * micro]).mean().detach()
         if pp == 1 or mesh.pp_rank == pp - 1:
