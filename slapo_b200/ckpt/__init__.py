@@ -19,6 +19,14 @@ Because optimizer state is stored per parameter, a checkpoint written by a
 ``dp8`` ZeRO run resumes on ``dp2`` unchanged, and :func:`reshard_checkpoint`
 re-splits both weights and optimizer moments for another TP size by
 concatenating along the recorded axis and slicing again.
+
+Tensors are stored under the names of the unpartitioned model, whatever the pipeline
+layout: the partitioner records them on every stage module (``original_tensor_names``),
+and the other names of a tied tensor travel in the manifest (``aliases``), because a
+stage may hold ``lm_head.weight`` without ``wte.weight``.  A checkpoint written by
+2 stages x 2-way tensor parallelism therefore loads - weights and optimizer state - into
+a tensor-parallel-only job or a single process, and the other way round; ``save_checkpoint``
+and ``load_checkpoint`` accept a pipeline engine in place of ``(stage module, stage engine)``.
 """
 from .io import (consolidate_checkpoint, load_checkpoint, read_manifest,  # noqa: F401
                  reshard_checkpoint, save_checkpoint)

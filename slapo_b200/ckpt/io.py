@@ -61,24 +61,53 @@ def _shard_axis(full_shape, local_shape):
     return diff[0] if diff else None
 
 
-def _unique_named_tensors(model):
-    """(canonical name, tensor) for parameters and persistent buffers; a tied
-    parameter appears once, under its first name."""
-    seen = set()
-    for name, p in model.named_parameters():
-        if id(p) in seen:
-            continue
-        seen.add(id(p))
-        yield canonical_name(name), p
+def original_names(model):
+    """``{name inside model: name in the unpartitioned model}`` for the tensors of pipeline
+    stage modules (the partitioner records them as ``original_tensor_names``); empty for a
+    model that was never partitioned."""
+    out = {}
+    for prefix, mod in model.named_modules():
+        table = getattr(mod, "original_tensor_names", None)
+        if isinstance(table, dict):
+            for local, orig in table.items():
+                out[f"{prefix}.{local}" if prefix else local] = orig
+    return out
+
+
+def _namer(model):
+    table = original_names(model)
+    return lambda name: table[name] if name in table else canonical_name(name)
+
+
+def _tensor_groups(model):
+    """``[(names, tensor)]`` for parameters and persistent buffers: ``names`` are all the
+    (canonical) names under which the model holds the tensor - a tied tensor has several -
+    and the first one is the name it is stored under."""
+    namer = _namer(model)
     skip = set()
     for mod_name, mod in model.named_modules():
         for b in getattr(mod, "_non_persistent_buffers_set", ()):
             skip.add(f"{mod_name}.{b}" if mod_name else b)
-    for name, b in model.named_buffers():
-        if name in skip or id(b) in seen:
+    groups, index = [], {}
+    named = list(model.named_parameters(remove_duplicate=False)) + [
+        (n, b) for n, b in model.named_buffers(remove_duplicate=False) if n not in skip]
+    for name, t in named:
+        canon = namer(name)
+        if id(t) in index:
+            names = groups[index[id(t)]][0]
+            if canon not in names:
+                names.append(canon)
             continue
-        seen.add(id(b))
-        yield canonical_name(name), b
+        index[id(t)] = len(groups)
+        groups.append(([canon], t))
+    return groups
+
+
+def _unique_named_tensors(model):
+    """(canonical name, tensor) for parameters and persistent buffers; a tied
+    parameter appears once, under its first name."""
+    for names, t in _tensor_groups(model):
+        yield names[0], t
 
 
 def _rng_state():
@@ -104,24 +133,48 @@ def _barrier():
 
 
 # ---------------------------------------------------------------------- #
+def _unwrap(model, engine):
+    """A pipeline engine stands for its stage: the engine that owns this rank's parameters is
+    ``engine.inner`` and the module to save or fill is that engine's stage module (the other
+    stages of the pipeline model live on other ranks)."""
+    inner = getattr(engine, "inner", None)
+    if inner is not None and hasattr(inner, "full_optimizer_state"):
+        if model is None or model is getattr(engine, "model", None):
+            model = inner.model
+        engine = inner
+    if model is None and engine is not None:
+        model = engine.model
+    return model, engine
+
+
 def save_checkpoint(path, model, engine=None, mesh=None, step=None, extra=None):
     """Write this rank's part of a checkpoint into directory ``path``.
-    Collective: every rank of the job calls it."""
+    Collective: every rank of the job calls it.  ``engine`` may be a pipeline engine (then
+    ``model`` may be its pipeline model, or None)."""
+    model, engine = _unwrap(model, engine)
+    if mesh is None:
+        mesh = getattr(engine, "mesh", None)
     coord, dims, rank = _coords(mesh, model)
     os.makedirs(path, exist_ok=True)
     tag = f"pp{coord['pp']}_tp{coord['tp']}"
     table, tensors = {}, {}
-    for name, t in _unique_named_tensors(model):
+    for names, t in _tensor_groups(model):
+        name = names[0]
         full_shape = tuple(getattr(t, "orig_shape", t.shape))
         table[name] = {"shape": list(t.shape), "orig_shape": list(full_shape),
                        "axis": _shard_axis(full_shape, tuple(t.shape)),
                        "dtype": str(t.dtype).replace("torch.", ""), "stage": coord["pp"]}
+        if len(names) > 1:
+            # other names of a tied tensor: a model in another layout may know it by one of
+            # them only (a pipeline stage holds "lm_head.weight" but not "wte.weight")
+            table[name]["aliases"] = names[1:]
         tensors[name] = t.detach().cpu()
     # optimizer state is gathered over DP by every rank (collective), written by DP rank 0
     optim = None
     if engine is not None:
         optim = engine.full_optimizer_state(to_cpu=True)
-        optim["state"] = {canonical_name(k): v for k, v in optim["state"].items()}
+        namer = _namer(model)
+        optim["state"] = {namer(k): v for k, v in optim["state"].items()}
         if step is None:
             step = optim["step"]
     if coord["dp"] == 0:
@@ -211,8 +264,11 @@ def load_checkpoint(path, model, engine=None, mesh=None, strict=True, load_rng=T
     model.  The checkpoint may have been written with another DP size, ZeRO
     setting or TP size: tensors whose saved shard shape differs from the
     model's are consolidated along their recorded axis and re-split.
-    Returns ``{"step", "extra"}``."""
+    ``engine`` may be a pipeline engine.  Returns ``{"step", "extra"}``."""
     manifest = read_manifest(path)
+    model, engine = _unwrap(model, engine)
+    if mesh is None:
+        mesh = getattr(engine, "mesh", None)
     coord, dims, rank = _coords(mesh, model)
     saved = manifest["mesh"]
     table = manifest["params"]
@@ -227,10 +283,22 @@ def load_checkpoint(path, model, engine=None, mesh=None, strict=True, load_rng=T
         result = consolidate_checkpoint(path, with_optimizer=need_opt)
         weights, optim = result if need_opt else (result, None)
     missing, loaded = [], set()
+    alias_of = {a: primary for primary, e in table.items() for a in e.get("aliases", ())}
+
+    def stored_name(names, pool):
+        """The name under which the checkpoint holds the tensor this model calls ``names``."""
+        for n in names:
+            if n in pool:
+                return n
+            if alias_of.get(n) in pool:
+                return alias_of[n]
+        return None
+
     with torch.no_grad():
-        for name, t in _unique_named_tensors(model):
-            if name not in weights:
-                missing.append(name)
+        for names, t in _tensor_groups(model):
+            name = stored_name(names, weights)
+            if name is None:
+                missing.append(names[0])
                 continue
             hint = table.get(name, {}).get("axis")
             src = _slice_for(weights[name], t.shape, hint, coord["tp"], dims["tp"], name)
@@ -242,14 +310,18 @@ def load_checkpoint(path, model, engine=None, mesh=None, strict=True, load_rng=T
     if engine is not None:
         if optim is not None:
             local = {"step": optim["step"], "state": {}}
-            shapes = {canonical_name(n): p.shape for n, p in model.named_parameters()}
-            by_canon = {canonical_name(n): n for n in engine._param_names()}
-            for name, entry in optim["state"].items():
-                if name not in by_canon:
+            namer = _namer(model)
+            groups = {names[0]: names for names, _ in _tensor_groups(model)}
+            params = dict(model.named_parameters())
+            for local_name in engine._param_names():
+                names = groups.get(namer(local_name), [namer(local_name)])
+                name = stored_name(names, optim["state"])
+                if name is None:
                     continue
+                entry, shape = optim["state"][name], params[local_name].shape
                 hint = table.get(name, {}).get("axis")
-                local["state"][by_canon[name]] = {
-                    key: _slice_for(entry[key], shapes[name], hint, coord["tp"], dims["tp"], name)
+                local["state"][local_name] = {
+                    key: _slice_for(entry[key], shape, hint, coord["tp"], dims["tp"], name)
                     for key in _STATE_KEYS}
             engine.load_full_optimizer_state(local)
         else:

@@ -503,7 +503,22 @@ def _trace_level(root: nn.Module, *, leaf_modules, flatten, recursive, concrete_
             except Exception:  # pragma: no cover
                 pass
     gm.train(root.training)
+    _keep_buffer_persistence(root, gm)
     return gm
+
+
+def _keep_buffer_persistence(root, gm):
+    """``fx.GraphModule`` registers the buffers it copies as persistent; a buffer that the
+    eager module kept out of its ``state_dict`` (``persistent=False``: position ids, causal
+    masks) stays out of the traced module's as well."""
+    eager = dict(root.named_modules())
+    for path, mod in gm.named_modules():
+        src = eager.get(path)
+        if src is None or src is mod:
+            continue
+        for name in getattr(src, "_non_persistent_buffers_set", ()):
+            if name in mod._buffers:
+                mod._non_persistent_buffers_set.add(name)
 
 
 def _trace_dynamo(root, concrete_args):

@@ -150,7 +150,20 @@ def generate_pipeline_partition(sch):
         n_stages -= 1  # the last cut was on the last node: no empty trailing stage
         for n in stage_of:
             stage_of[n] = min(stage_of[n], n_stages - 1)
+    # names under which the unpartitioned model knows its tensors: checkpoints are keyed by
+    # them, so that one written by a pipeline loads into any other layout (split_module
+    # renames "transformer.h.0" to "transformer_h_0" inside a stage)
+    original = {}
+    for name, t in list(root.named_parameters(remove_duplicate=False)) \
+            + list(root.named_buffers(remove_duplicate=False)):
+        original.setdefault(id(t), name)
     split = split_module(root, root, lambda n: stage_of[n], keep_original_order=True)
+    for name, sub in split.named_children():
+        if name.startswith("submod_"):
+            local = list(sub.named_parameters(remove_duplicate=False)) \
+                + list(sub.named_buffers(remove_duplicate=False))
+            sub.original_tensor_names = {n: original[id(t)] for n, t in local
+                                         if id(t) in original}
     from ..schedule import create_schedule
 
     new_sch = create_schedule(split, group=sch.group_arg)

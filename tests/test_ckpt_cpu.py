@@ -194,3 +194,76 @@ def test_sharded_model_without_a_mesh_is_saved_as_one_tp_group():
         torch.save(shard, os.path.join(tmp, "model_pp0_tp1.pt"))
         with pytest.raises(ValueError, match="do not belong to one tensor-parallel layout"):
             ckpt.consolidate_checkpoint(tmp)
+
+
+# ---- checkpoints across pipeline layouts -------------------------------------------------- #
+def _zoo_engine(name, pp, tp, seed):
+    from test_train_equivalence_cpu import _tiny_spec
+
+    torch.manual_seed(seed)
+    spec = _tiny_spec(name)
+    model = spec.build().init_weights()
+    mesh = DeviceMesh(pp=pp, dp=1, tp=tp)
+    slapo.set_random_seed(1, tp_rank=mesh.tp_rank, pp_rank=mesh.pp_rank)
+    kwargs = dict(model_config=spec.config, group=mesh.schedule_group, attn_op_name="reference")
+    if pp > 1:
+        kwargs["pipeline_cuts"] = [[], []] if spec.kind == "seq2seq" else [1]
+    sch = slapo.model_schedule.apply_schedule(model, spec.schedule_key, **kwargs)
+    extra = dict(num_micro_batches=2) if pp > 1 else {}
+    engine, _ = slapo.build(sch, target="native", mesh=mesh, init_weights=False,
+                            loss_fn=spec.loss_fn(mesh.tp_group, tp > 1),
+                            config={"lr": 1e-2, "clip_grad": 1.0, "weight_decay": 0.01}, **extra)
+    return spec, engine
+
+
+def _layout_worker(rank, world, name, tmp, pp, tp, phase):
+    """``save``: train two steps, save, train two more and record their losses.  ``load``: a
+    differently initialised model in another layout loads the checkpoint (weights and
+    optimizer state) and must reproduce those losses."""
+    spec, engine = _zoo_engine(name, pp, tp, seed=21 if phase == "save" else 99)
+    inputs, labels = spec.make_batch(4, seq=32, seq_dec=16, seed=3)
+    if phase == "save":
+        for _ in range(2):
+            engine.train_batch(*inputs, labels=labels)
+        ckpt.save_checkpoint(tmp, None, engine)       # a pipeline engine stands for its stage
+        after = [float(engine.train_batch(*inputs, labels=labels)) for _ in range(2)]
+        if rank == 0:
+            torch.save(after, os.path.join(tmp, "after.pt"))
+        return
+    info = ckpt.load_checkpoint(tmp, None, engine, load_rng=False)
+    assert info["step"] == 2
+    again = [float(engine.train_batch(*inputs, labels=labels)) for _ in range(2)]
+    assert again == pytest.approx(torch.load(os.path.join(tmp, "after.pt")), rel=2e-5)
+
+
+@pytest.mark.parametrize("name,saved,loaded", [
+    ("gpt-neo-125m", (2, 2), [(2, 2), (1, 2), (1, 1)]),   # pipeline -> same, TP only, one rank
+    ("t5-base", (1, 2), [(2, 2)]),      # into stages that know the tied table by other names
+])
+def test_checkpoint_moves_between_pipeline_layouts(name, saved, loaded):
+    with tempfile.TemporaryDirectory() as tmp:
+        run_distributed(_layout_worker, saved[0] * saved[1], name, tmp, *saved, "save")
+        man = ckpt.read_manifest(tmp)
+        assert man["mesh"]["pp"] == saved[0] and man["mesh"]["tp"] == saved[1]
+        # tensors are stored under the unpartitioned model's names, whatever the layout
+        assert not [n for n in man["params"] if "submod_" in n or n.startswith("module.")]
+        if saved[0] == 1:        # an unpartitioned model knows its tied tables by all names
+            assert any(e.get("aliases") for e in man["params"].values())
+        for pp, tp in loaded:
+            run_distributed(_layout_worker, pp * tp, name, tmp, pp, tp, "load")
+
+
+def test_traced_modules_keep_buffers_out_of_the_state_dict():
+    """A buffer registered with ``persistent=False`` stays non-persistent when its module is
+    re-created as a graph module (fx registers copied buffers as persistent)."""
+    from slapo_b200.models.albert import AlbertConfig, AlbertForMaskedLM
+
+    cfg = AlbertConfig(vocab_size=128, embedding_size=16, hidden_size=32, num_hidden_layers=2,
+                       intermediate_size=64, num_attention_heads=4, max_position_embeddings=32)
+    model = AlbertForMaskedLM(cfg)
+    assert "albert.embeddings.position_ids" not in model.state_dict()
+    sch = slapo.create_schedule(model)
+    sch.trace_until("albert.encoder")
+    assert sch["albert.embeddings"].mod is not model.albert.embeddings       # re-created
+    assert "albert.embeddings.position_ids" not in sch.mod.state_dict()
+    assert "position_ids" in dict(sch["albert.embeddings"].mod.named_buffers())
