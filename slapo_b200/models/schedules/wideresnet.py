@@ -75,7 +75,13 @@ def schedule_wideresnet(model, model_config=None, prefix="model", fp16=False, bf
             raise ValueError("pipeline_cuts needs one list per residual group (4)")
         dot = f"{prefix}." if prefix else ""
         leaves = [f"{dot}layer{i + 1}" for i in range(4) if pipeline_cuts[i]]
-        sch.trace_until(leaves, tracer="pytorch")
+        # the stages compute the logits; the loss (and its labels) stays with the engine's
+        # loss function, so a wrapper's optional ``labels`` input is frozen at None
+        import inspect
+
+        frozen = {"labels": None} if "labels" in inspect.signature(model.forward).parameters \
+            else {}
+        sch.trace_until(leaves, tracer="pytorch", concrete_args=frozen)
         for i, cuts in enumerate(pipeline_cuts):
             for cut in cuts:
                 sch[f"{dot}layer{i + 1}"][str(cut)].cut_pipeline_stage()

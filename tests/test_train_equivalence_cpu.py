@@ -151,3 +151,46 @@ def test_cut_after_a_given_call_of_a_shared_module():
     assert [bool(n.meta.get("partition")) for n in calls] == [False, True, False]
     with pytest.raises(IndexError):
         sch["body.shared"].cut_pipeline_stage(call_index=3)
+
+
+_WRN = {"_name_or_path": "wideresnet-tiny", "block_size": (32, [1, 2, 1, 1])}
+
+
+def _wrn_worker(rank, world):
+    """Two pipeline stages of a Wide ResNet (cut inside the second residual group): BatchNorm
+    statistics per micro-batch, the wrapper's ``labels`` input frozen out of the stages."""
+    from slapo_b200.models import get_wideresnet
+    from slapo_b200.parallel.mesh import DeviceMesh
+
+    torch.manual_seed(3)
+    ref = get_wideresnet(_WRN, num_classes=10)
+    ref.train()
+    mesh = DeviceMesh(pp=2, dp=1, tp=1)
+    slapo.set_random_seed(1, pp_rank=mesh.pp_rank)
+    sch = slapo.model_schedule.apply_schedule(copy.deepcopy(ref), "wideresnet", model_config=_WRN,
+                                              group=mesh.schedule_group,
+                                              pipeline_cuts=[[], [0], [], []])
+
+    def loss_fn(out, labels):
+        return torch.nn.functional.cross_entropy(out["output"].float(), labels.reshape(-1))
+
+    engine, _ = slapo.build(sch, target="native", mesh=mesh, init_weights=False, loss_fn=loss_fn,
+                            num_micro_batches=2,
+                            config={"lr": 1e-3, "clip_grad": 0.5, "weight_decay": 0.0})
+    opt = torch.optim.AdamW(ref.parameters(), lr=1e-3, weight_decay=0.0, eps=1e-8)
+    gen = torch.Generator().manual_seed(5)
+    x = torch.randn(4, 3, 64, 64, generator=gen)
+    y = torch.randint(0, 10, (4,), generator=gen)
+    for step in range(3):
+        loss = engine.train_batch(x, labels=y)
+        opt.zero_grad()
+        want = torch.stack([loss_fn(ref(x.chunk(2)[m]), y.chunk(2)[m]) for m in range(2)]).mean()
+        want.backward()
+        torch.nn.utils.clip_grad_norm_(ref.parameters(), 0.5)
+        opt.step()
+        torch.testing.assert_close(loss.detach().float(), want.detach(), rtol=1e-3, atol=1e-4,
+                                   msg=lambda m: f"step {step}: {m}")
+
+
+def test_wideresnet_pipeline_training_matches_adamw():
+    run_distributed(_wrn_worker, 2)
