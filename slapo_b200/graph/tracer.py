@@ -113,9 +113,18 @@ def MetaHierTracer(leaf_modules=None, forced_leaf_names=None):   # noqa: N802 - 
         def proxy(self, node):
             return ShapeProxy(node, self)
 
+        def user_leaf(self, m, qualname):
+            # The operators of this package that a recipe swapped in (attention, fused MLP,
+            # norms) stay whole: this tracer specialises graphs on the example shapes, and the
+            # batch extent inside them differs between the sequence-parallel regions.
+            if type(m).__module__.startswith(__name__.split(".")[0] + ".ops."):
+                return True
+            return HierTracer.user_leaf(self, m, qualname)
+
         _META_TRACER_CLS.append(type("MetaHierTracer", (HierTracer, MetaTracer), {
             "name": "huggingface", "create_proxy": _meta_create_proxy, "proxy": proxy,
-            "call_module": _meta_call_module, "_in_meta_eval": False}))
+            "call_module": _meta_call_module, "_in_meta_eval": False,
+            "user_leaf": user_leaf}))
     return _META_TRACER_CLS[0](leaf_modules, forced_leaf_names)
 
 
@@ -134,16 +143,73 @@ def _meta_create_proxy(self, kind, target, args, kwargs, name=None, type_expr=No
     from torch.fx.experimental.meta_tracer import MetaTracer
 
     self._in_meta_eval = kind == "call_module"
+    restore = None
+    if kind == "call_module":
+        restore = _apply_pre_hook_shapes(self.root, target, args)
     try:
         rv = MetaTracer.create_proxy(self, kind, target, args, kwargs, name, type_expr,
                                      proxy_factory_fn)
     finally:
         self._in_meta_eval = False
+        if restore is not None:
+            restore[0]._tensor_meta = restore[1]
+    if kind == "call_module":
+        _apply_post_hook_shapes(self.root, target, rv)
     meta = getattr(rv, "_tensor_meta", None)
     if isinstance(meta, torch.Tensor):
         rv.node.meta["shape"] = tuple(meta.shape)
         rv.node.meta["dtype"] = meta.dtype
     return rv
+
+
+def _hook_shape_fns(hooks):
+    """``meta_shape`` callables of the hooks that have one (``sync`` collectives and the
+    vocabulary-parallel embedding hooks): leaf modules run without their hooks while shapes
+    are propagated on meta tensors, so the hooks' effect on the token axes - a scatter at the
+    start of a sequence-parallel region, the all-gather in front of a column-parallel layer -
+    is applied to the recorded shapes instead."""
+    out = []
+    for hook in hooks.values():
+        owner = getattr(hook, "__self__", hook)
+        fn = getattr(owner, "meta_shape", None)
+        # the embedding hooks are a pre / post pair on one object: the shape changes in post
+        if fn is not None and getattr(hook, "__name__", "") != "pre":
+            out.append(fn)
+    return out
+
+
+def _leaf_or_none(root, target):
+    try:
+        return root.get_submodule(target)
+    except AttributeError:
+        return None
+
+
+def _apply_pre_hook_shapes(root, target, args):
+    mod = _leaf_or_none(root, target)
+    first = args[0] if args else None
+    meta = getattr(first, "_tensor_meta", None)
+    if mod is None or not isinstance(meta, torch.Tensor):
+        return None
+    shape = tuple(meta.shape)
+    for fn in _hook_shape_fns(mod._forward_pre_hooks):
+        shape = fn(shape)
+    if shape == tuple(meta.shape):
+        return None
+    first._tensor_meta = meta.new_empty(shape)
+    return first, meta
+
+
+def _apply_post_hook_shapes(root, target, rv):
+    mod = _leaf_or_none(root, target)
+    meta = getattr(rv, "_tensor_meta", None)
+    if mod is None or not isinstance(meta, torch.Tensor):
+        return
+    shape = tuple(meta.shape)
+    for fn in _hook_shape_fns(mod._forward_hooks):
+        shape = fn(shape)
+    if shape != tuple(meta.shape):
+        rv._tensor_meta = meta.new_empty(shape)
 
 
 _INT_ARG_HINTS = ("ids", "labels", "mask", "positions")
@@ -155,7 +221,8 @@ _REAL_RETRACE_LIMIT = 200_000_000
 def dummy_meta_inputs(root: nn.Module, concrete_args=None, config=None):
     """Meta tensors for the forward arguments that stay symbolic: what the ``"huggingface"``
     engine propagates.  ``config`` (dict or object) may give ``seq_len``, ``hidden_size``,
-    ``batch_size`` and ``input_shapes = {name: (shape, dtype)}`` for anything unusual."""
+    ``batch_size`` and ``input_shapes = {name: (shape, dtype)}`` (or just the shape) for anything
+    unusual."""
     get = (lambda k, d=None: config.get(k, d)) if isinstance(config, dict) else \
         (lambda k, d=None: getattr(config, k, d))
     batch, seq = get("batch_size", 2) or 2, get("seq_len", 16) or 16
@@ -166,7 +233,11 @@ def dummy_meta_inputs(root: nn.Module, concrete_args=None, config=None):
         if par.kind in (par.VAR_POSITIONAL, par.VAR_KEYWORD) or name in (concrete_args or {}):
             continue
         if name in explicit:
-            shape, dtype = explicit[name]
+            entry = explicit[name]
+            if entry and all(isinstance(v, int) for v in entry):      # a bare shape
+                entry = (entry, torch.long if any(h in name for h in _INT_ARG_HINTS)
+                         else torch.float32)
+            shape, dtype = entry
             metas[name] = torch.empty(tuple(shape), dtype=dtype, device="meta")
         elif par.default is not inspect.Parameter.empty:
             continue            # optional and not named: frozen at its default by the caller
@@ -409,7 +480,7 @@ def _trace_level(root: nn.Module, *, leaf_modules, flatten, recursive, concrete_
                  call_node=None, engine="pytorch", config=None):
     if isinstance(root, fx.GraphModule):
         return root
-    judge = HierTracer(leaf_modules)
+    judge = MetaHierTracer(leaf_modules) if engine == "huggingface" else HierTracer(leaf_modules)
     forced = [] if flatten else _direct_child_names(root)
     tracer = HierTracer(leaf_modules, forced)
     graph = None
@@ -489,6 +560,14 @@ def _trace_level(root: nn.Module, *, leaf_modules, flatten, recursive, concrete_
             elif node.op == "get_attr":
                 pieces[node.target] = _get_submodule_or_none(root, node.target)
         gm = fx.GraphModule(pieces, graph, class_name=type(root).__name__)
+        for target in pieces:
+            # "model.decoder" as a call target: fx made a bare module "model" to hold it;
+            # the schedule tree walks through such containers to the traced grandchild
+            tokens = target.split(".")
+            for depth in range(1, len(tokens)):
+                holder = _get_submodule_or_none(gm, ".".join(tokens[:depth]))
+                if type(holder) is nn.Module:
+                    holder.schedule_container = True
     gm.graph.eliminate_dead_code()
     gm.delete_all_unused_submodules()
     gm.graph.lint()

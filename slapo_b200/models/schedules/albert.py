@@ -18,7 +18,7 @@ from ... import create_schedule
 from ...model_schedule.registry import register_schedule
 from ...ops.linear import LinearWithAct
 from .common import (broadcast_input, cast_dtype, logger, shard_column, shard_row,
-                     shard_word_embedding)
+                     shard_word_embedding, tracer_for)
 
 
 def _layers(sch, prefix):
@@ -31,9 +31,9 @@ def _layers(sch, prefix):
     return out
 
 
-def pipeline_cut(sch, config, prefix, cuts):
+def pipeline_cut(sch, config, prefix, cuts, trace_config=None):
     """End a stage after pass ``k`` through the layers, for every ``k`` in ``cuts``."""
-    sch.trace_until(f"{prefix}.encoder", tracer="pytorch")
+    sch.trace_until(f"{prefix}.encoder", tracer=tracer_for(sch.mod), config=trace_config)
     per_group = config.num_hidden_layers // config.num_hidden_groups
     for k in cuts:
         if not 0 <= k < config.num_hidden_layers - 1:
@@ -47,7 +47,7 @@ def pipeline_cut(sch, config, prefix, cuts):
 @register_schedule("albert")
 def schedule_albert(model, model_config=None, prefix="albert", fp16=False, bf16=False,
                     group=None, fuse=True, ckpt_ratio=0.0, bcast_input=False, pipeline_cuts=None,
-                    **_unused):
+                    trace_config=None, **_unused):
     config = model_config if model_config is not None else getattr(model, "config", None)
     if config is None:
         raise ValueError("model_config is required")
@@ -80,7 +80,7 @@ def schedule_albert(model, model_config=None, prefix="albert", fp16=False, bf16=
         for path in layers:
             sch[path].checkpoint()
     if pipeline_cuts:
-        pipeline_cut(sch, config, prefix, pipeline_cuts)
+        pipeline_cut(sch, config, prefix, pipeline_cuts, trace_config)
     logger.info("albert schedule: %d shared layers scheduled (tp=%d)", len(layers),
                 sch.world_size, ranks=0)
     return sch

@@ -20,6 +20,9 @@
 ``checkpoint_method``  "uniform" (spread) or "head" (first layers)
 ``bcast_input``        broadcast rank-0 inputs inside the TP group
 ``pipeline_cuts``      layer indices after which a pipeline stage ends
+``trace_config``       for an unmodified Hugging Face model under pipeline cuts: the
+                       example shapes its graphs are specialised on
+                       (``{"batch_size": ..., "seq_len": ...}`` or ``input_shapes``)
 ``delay_init``         unused here (the caller decides to build on meta)
 =====================  =====================================================
 
@@ -35,7 +38,7 @@ from ...model_schedule.registry import register_schedule
 from ...ops.attention import FlashAttention
 from ...ops.blocks import FusedIntermediateBlock, FusedOutputBlock
 from .common import (annotate_replicated, broadcast_input, cast_dtype, checkpoint_layers,
-                     logger, shard_column, shard_row, shard_word_embedding)
+                     logger, shard_column, shard_row, shard_word_embedding, tracer_for)
 
 
 class SelfAttentionAdapter(nn.Module):
@@ -153,8 +156,8 @@ def shard_lm_head(sch, config, prefix):
         head["decoder"].sync("bwd_post", "all_reduce")
 
 
-def pipeline_cut(sch, prefix, cuts):
-    sch.trace_until(_j(prefix, "encoder"), tracer="pytorch")
+def pipeline_cut(sch, prefix, cuts, trace_config=None):
+    sch.trace_until(_j(prefix, "encoder"), tracer=tracer_for(sch.mod), config=trace_config)
     for idx in cuts:
         sch[_j(prefix, f"encoder.layer.{idx}")].cut_pipeline_stage()
 
@@ -165,7 +168,7 @@ def schedule_bert(model, model_config=None, prefix="bert", fp16=False, bf16=Fals
                   sequence_parallel=False, sequence_parallel_axis=0, ckpt_ratio=0.0,
                   checkpoint_method="uniform",
                   bcast_input=False, pipeline_cuts=None, shard_vocab=True, delay_init=True,
-                  **_unused):
+                  trace_config=None, **_unused):
     config = model_config if model_config is not None else getattr(model, "config", None)
     if config is None:
         raise ValueError("model_config is required")
@@ -184,7 +187,7 @@ def schedule_bert(model, model_config=None, prefix="bert", fp16=False, bf16=Fals
         broadcast_input(sch)
     n_ckpt = checkpoint_layers(sch, _layer_paths(sch, pre), ckpt_ratio, checkpoint_method)
     if pipeline_cuts:
-        pipeline_cut(sch, pre, pipeline_cuts)
+        pipeline_cut(sch, pre, pipeline_cuts, trace_config)
     logger.info("bert schedule: %d attention replaced, %d blocks fused, %d layers sharded "
                 "(sp=%s), %d checkpointed", n_attn, n_fused, n_shard, sequence_parallel, n_ckpt,
                 ranks=0)

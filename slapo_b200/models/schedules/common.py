@@ -73,6 +73,13 @@ class VocabParallelEmbeddingHooks:
         self._mask = outside
         return ((ids - lo).masked_fill(outside, 0),) + tuple(inputs[1:])
 
+    def meta_shape(self, shape):
+        """Output shape after the post-hook (see ``SyncHook.meta_shape``)."""
+        out = list(shape)
+        if self.sequence_parallel and len(out) > self.sp_axis:
+            out[self.sp_axis] //= self.world
+        return tuple(out)
+
     def post(self, module, inputs, output):
         output = output.masked_fill(self._mask.unsqueeze(-1), 0.0)
         self._mask = None
@@ -141,6 +148,17 @@ def annotate_replicated(sch, layer_norm_paths=(), bias_paths=()):
     for path in bias_paths:
         if getattr(sch[path].mod, "bias", None) is not None:
             sch[path].annotate("bias", "replicated_param", True)
+
+
+def tracer_for(model):
+    """Tracer name for ``trace_until`` in a recipe's pipeline cut: unmodified Hugging Face
+    models need the ``"huggingface"`` tracer (meta-tensor shapes, ``ModelOutput`` reads,
+    catch-all keyword arguments); this package's own models trace with plain ``"pytorch"``."""
+    try:
+        from transformers import PreTrainedModel
+    except Exception:  # transformers is optional
+        return "pytorch"
+    return "huggingface" if isinstance(model, PreTrainedModel) else "pytorch"
 
 
 def pad_vocab(vocab_size, multiple):

@@ -6,7 +6,9 @@ MLP, embeddings and head live in each model).  Options (``sch_config``):
 ``attn_op_name``, ``disable_flash_attn``, ``fuse`` (FusedMLP / fused
 LayerNorm), ``sequence_parallel`` (+ ``sequence_parallel_axis``),
 ``ckpt_ratio``, ``checkpoint_method`` (``uniform`` | ``head``), ``bcast_input``,
-``pipeline_cuts``.
+``pipeline_cuts``, ``trace_config`` (the example shapes - ``batch_size``, ``seq_len`` or
+``input_shapes`` - that the graphs of an unmodified Hugging Face model are specialised on when
+pipeline cuts make the recipe trace it).
 
 Tensor parallelism: fused QKV column-parallel (whole heads per rank),
 attention output and MLP output row-parallel, vocabulary-parallel embedding
@@ -31,7 +33,7 @@ from ...ops.attention import FlashAttention
 from ...ops.mlp import FusedMLP
 from ...ops.norm import FusedLayerNorm
 from .common import (annotate_replicated, broadcast_input, cast_dtype, checkpoint_layers,
-                     logger, shard_column, shard_row, shard_word_embedding)
+                     logger, shard_column, shard_row, shard_word_embedding, tracer_for)
 
 LAYOUTS = {
     "gpt2": dict(prefix="transformer", layers="h", attn="attn", kind="conv1d_fused",
@@ -243,6 +245,7 @@ def schedule_decoder(model, family, model_config=None, prefix=None, fp16=False, 
                      group=None, attn_op_name="auto", disable_flash_attn=False, fuse=True,
                      sequence_parallel=False, sequence_parallel_axis=1, ckpt_ratio=0.0,
                      checkpoint_method="uniform", bcast_input=False, pipeline_cuts=None,
+                     trace_config=None,
                      shard_vocab=True, **_unused):
     lay = LAYOUTS[family]
     config = model_config if model_config is not None else getattr(model, "config", None)
@@ -264,7 +267,7 @@ def schedule_decoder(model, family, model_config=None, prefix=None, fp16=False, 
         broadcast_input(sch)
     n_ckpt = checkpoint_layers(sch, _layer_paths(sch, lay, prefix), ckpt_ratio, checkpoint_method)
     if pipeline_cuts:
-        sch.trace_until(prefix, tracer="pytorch")
+        sch.trace_until(prefix, tracer=tracer_for(sch.mod), config=trace_config)
         for idx in pipeline_cuts:
             sch[_j(prefix, f"{lay['layers']}.{idx}")].cut_pipeline_stage()
     logger.info("%s schedule: %d attention, %d MLP, %d LayerNorm replaced; %d layers sharded "

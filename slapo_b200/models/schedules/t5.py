@@ -23,7 +23,8 @@ from __future__ import annotations
 
 from ... import create_schedule
 from ...model_schedule.registry import register_schedule
-from .common import (broadcast_input, cast_dtype, checkpoint_layers, logger, shard_word_embedding)
+from .common import (broadcast_input, cast_dtype, checkpoint_layers, logger,
+                     shard_word_embedding, tracer_for)
 
 
 def _blocks(sch, stack):
@@ -83,7 +84,14 @@ def shard_t5(sch, config):
             _shard_ffn(sch, f"{ff}.DenseReluDense", config.is_gated_act)
             count += 1
     if config.vocab_size % sch.world_size == 0:
-        shard_word_embedding(sch["shared"], config.vocab_size)
+        # Hugging Face's T5 (recent versions) gives each stack an embedding module of its own
+        # that shares the weight of ``shared``: every module that looks tokens up needs the
+        # vocabulary-parallel hooks, and ``shard`` keeps the one tensor tied among them
+        seen = set()
+        for path in ("shared", "encoder.embed_tokens", "decoder.embed_tokens"):
+            if path in sch and id(sch[path].mod) not in seen:
+                seen.add(id(sch[path].mod))
+                shard_word_embedding(sch[path], config.vocab_size)
         sch["lm_head"].shard("weight", axis=0)
         sch["lm_head"].sync("bwd_post", "all_reduce")
     return count
@@ -91,7 +99,7 @@ def shard_t5(sch, config):
 
 @register_schedule("t5")
 def schedule_t5(model, model_config=None, fp16=False, bf16=False, group=None, ckpt_ratio=0.0,
-                checkpoint_method="uniform", bcast_input=False, pipeline_cuts=None,
+                checkpoint_method="uniform", bcast_input=False, pipeline_cuts=None, trace_config=None,
                 fuse_qkv=True, **_unused):
     config = model_config if model_config is not None else getattr(model, "config", None)
     if config is None:
@@ -107,7 +115,7 @@ def schedule_t5(model, model_config=None, fp16=False, bf16=False, group=None, ck
         n_ckpt += checkpoint_layers(sch, _blocks(sch, stack), ckpt_ratio, checkpoint_method)
     if pipeline_cuts:
         enc_cuts, dec_cuts = pipeline_cuts
-        sch.trace_until(["encoder", "decoder"], tracer="pytorch")
+        sch.trace_until(["encoder", "decoder"], tracer=tracer_for(sch.mod), config=trace_config)
         for idx in enc_cuts:
             sch[f"encoder.block.{idx}"].cut_pipeline_stage()
         sch["encoder"].cut_pipeline_stage()

@@ -43,11 +43,15 @@ def _resolve_output_access(user: fx.Node, struct):
     statically known dict / tuple structure -> the selected element."""
     if user.op == "call_function" and user.target is operator.getitem:
         key = user.args[1]
+        if isinstance(struct, dict) and isinstance(key, int):
+            # a Hugging Face ModelOutput read by position: its fields that are not None, in order
+            return [v for v in struct.values() if v is not None][key]
         return struct[key]
     if user.op == "call_method" and user.target == "get":
         return struct.get(user.args[1], user.args[2] if len(user.args) > 2 else None)
     if user.op == "call_function" and user.target is getattr:
-        return struct[user.args[1]]
+        # a field that a traced Hugging Face module left out of its output dict was None
+        return struct.get(user.args[1]) if isinstance(struct, dict) else struct[user.args[1]]
     raise RuntimeError(
         f"the output structure of an inlined module is used as a whole by '{user.format_node()}'; "
         "index it (out[...]) in the parent instead")

@@ -17,8 +17,11 @@ Parity: slapo/sharding/shard_ops.py:26-649 of the reference.
 """
 from __future__ import annotations
 
+import copy
 from functools import partial
 
+import torch
+import torch.distributed as dist
 from torch import nn
 
 from ..logger import get_logger
@@ -94,9 +97,35 @@ class SyncHook:
 
     def __call__(self, module, inputs, output=None):
         if self.mode == "fwd_post":
-            return self.fn(output)
+            return self._on_first_tensor(output)
         first = self.fn(inputs[0])
         return (first,) + tuple(inputs[1:])
+
+    def meta_shape(self, shape):
+        """The shape this hook turns ``shape`` into (the module's first input for a forward-pre
+        hook, its main output for a forward hook): what a shape-propagating tracer needs to
+        know about a collective that it cannot run on meta tensors."""
+        axis = self.kwargs.get("axis", 0)
+        if self.op not in ("all_gather", "scatter", "reduce_scatter") or len(shape) <= axis:
+            return tuple(shape)
+        world = dist.get_world_size(self.group) if dist.is_initialized() else 1
+        out = list(shape)
+        out[axis] = out[axis] * world if self.op == "all_gather" else out[axis] // world
+        return tuple(out)
+
+    def _on_first_tensor(self, output):
+        """The collective applies to the module's main output: the tensor itself, the first
+        element of a tuple (a Hugging Face layer returns ``(hidden_states, ...)``) or the first
+        tensor entry of a dict-like output (``last_hidden_state`` of a ``ModelOutput``)."""
+        if isinstance(output, (tuple, list)) and output and torch.is_tensor(output[0]):
+            return type(output)([self.fn(output[0]), *output[1:]])
+        if hasattr(output, "keys") and not torch.is_tensor(output):
+            for key in output.keys():
+                if torch.is_tensor(output[key]):
+                    new = copy.copy(output)
+                    new[key] = self.fn(output[key])
+                    return new
+        return self.fn(output)
 
     def __repr__(self):
         extra = ", ".join(f"{k}={v}" for k, v in self.kwargs.items())

@@ -43,6 +43,7 @@ from __future__ import annotations
 import torch
 import torch.distributed as dist
 from torch import nn
+from torch.utils._pytree import tree_flatten, tree_unflatten
 
 from ..logger import get_logger
 from .engine import EngineConfig, TrainEngine
@@ -147,7 +148,7 @@ class PipelineEngine:
         self.inner = TrainEngine(self.stage, config=self.cfg, mesh=mesh, tp_group=tp_group,
                                  dp_group=mesh.dp_group)
         self.inner.cfg.grad_accum_steps = 1
-        self._meta_fwd = None   # [(name, shape, dtype, requires_grad)] of live_in[stage]
+        self._meta_fwd = None   # [(name, tree spec, per-leaf description)] of live_in[stage]
         self._meta_sent = False
         self._inflight = []     # Work objects of sends not yet waited for
         # Receives are posted one micro-batch ahead unless the stage runs the fused
@@ -261,9 +262,21 @@ class PipelineEngine:
         for w in works or ():
             w.wait()
 
-    def _handshake_send(self, tensors, names):
-        meta = [(n, tuple(t.shape), str(t.dtype).replace("torch.", ""), bool(t.requires_grad))
-                if torch.is_tensor(t) else (n, None, None, t) for n, t in zip(names, tensors)]
+    @staticmethod
+    def _flatten_values(values):
+        """Per value crossing the stage boundary: ``(tree spec, leaves)``.  A value may be a
+        tensor, a Python constant or a nest of them (a Hugging Face layer hands on
+        ``(hidden_states, None)``); only the tensor leaves travel with every micro-batch."""
+        return [tree_flatten(v) for v in values]
+
+    def _handshake_send(self, flat, names):
+        """Once per run: the static description of what will be sent - per value its name,
+        tree structure and, per leaf, either (shape, dtype, requires_grad) or the constant."""
+        meta = []
+        for name, (leaves, spec) in zip(names, flat):
+            desc = [(tuple(t.shape), str(t.dtype).replace("torch.", ""), bool(t.requires_grad))
+                    if torch.is_tensor(t) else ("const", t) for t in leaves]
+            meta.append((name, spec, desc))
         dist.send_object_list([meta], dst=self.next_rank, group=self._link(self.stage_id, "fwd"),
                               device=self.device)
 
@@ -280,17 +293,22 @@ class PipelineEngine:
         if self._meta_fwd is None:
             self._meta_fwd = self._handshake_recv()
         bufs = []
-        for name, shape, dtype, rg in self._meta_fwd:
-            if shape is None:
-                bufs.append((name, None, rg))
-            else:
-                bufs.append((name, torch.empty(shape, dtype=getattr(torch, dtype),
-                                               device=self.device), rg))
+        for name, spec, desc in self._meta_fwd:
+            leaves = []
+            for entry in desc:
+                if entry[0] == "const":
+                    leaves.append((entry[1], False, False))
+                else:
+                    shape, dtype, rg = entry
+                    leaves.append((torch.empty(shape, dtype=getattr(torch, dtype),
+                                               device=self.device), True, rg))
+            bufs.append((name, spec, leaves))
         return bufs
 
     @staticmethod
     def _tensor_list(bufs):
-        return [t for _, t, _ in bufs if t is not None] if bufs else []
+        return [v for _, _, leaves in bufs for v, is_tensor, _ in leaves if is_tensor] \
+            if bufs else []
 
     def _post_recv_forward(self):
         """Post the receives of the next micro-batch's inputs: (buffers, works)."""
@@ -324,14 +342,14 @@ class PipelineEngine:
         if self.stage_id == 0:
             env.update(mb_inputs)
         else:
-            for name, t, rg in bufs:
-                if t is None:
-                    env[name] = rg  # a python constant that travelled in the handshake
-                    continue
-                if rg and t.is_floating_point():
-                    t.requires_grad_(True)
-                    received.append(t)
-                env[name] = t
+            for name, spec, leaves in bufs:
+                values = []
+                for v, is_tensor, rg in leaves:
+                    if is_tensor and rg and v.is_floating_point():
+                        v.requires_grad_(True)
+                        received.append(v)
+                    values.append(v)    # constants travelled in the handshake
+                env[name] = tree_unflatten(values, spec)
         env.update(self.stage(env))
         rec = {"received": received, "loss": None, "sent": [], "payload": []}
         if self.stage_id == self.n_stages - 1:
@@ -343,11 +361,11 @@ class PipelineEngine:
             rec["loss"] = loss / self.num_micro_batches
             return rec
         names = self.model.live_in[self.stage_id + 1]
-        tensors = [env[n] for n in names]
+        flat = self._flatten_values([env[n] for n in names])
         if not self._meta_sent:
-            self._handshake_send(tensors, names)
+            self._handshake_send(flat, names)
             self._meta_sent = True
-        rec["payload"] = [t for t in tensors if torch.is_tensor(t)]
+        rec["payload"] = [t for leaves, _ in flat for t in leaves if torch.is_tensor(t)]
         rec["sent"] = [t for t in rec["payload"] if t.requires_grad]
         return rec
 

@@ -8,7 +8,9 @@ static-graph queries ``trace`` / ``trace_until`` / ``find`` / ``find_node`` /
 
 Tree rules (parity: slapo/schedule.py:509-581 of the reference):
 
-* a module from ``torch.nn`` that is not an ``nn.Sequential`` is a leaf;
+* a module from ``torch.nn`` that is not an ``nn.Sequential`` is a leaf (the bare containers
+  of a flattened trace included; those a hierarchical trace leaves above a grandchild call
+  are not);
 * the elements of a ``ModuleList`` become children named ``"<list>.<i>"``
   (one path token); everything else, ``nn.Sequential`` included, is a direct
   child, so ``sch["seq"]["0"]`` and ``sch["seq.0"]`` both work.
@@ -297,6 +299,12 @@ def list_primitives(name_only: bool = True):
 
 
 def _is_leaf(module: nn.Module) -> bool:
+    if getattr(module, "schedule_container", False):
+        # a bare container that the hierarchical trace left between a graph and the grandchild
+        # it calls ("model.decoder" called from the top graph leaves "model" such a module);
+        # the containers of a flattened trace stay leaves: their members are no longer
+        # schedules of their own
+        return False
     mod_path = type(module).__module__
     return (mod_path.startswith("torch.nn") or mod_path.startswith("torch.ao.nn")) \
         and not isinstance(module, nn.Sequential)

@@ -4,6 +4,7 @@ import copy
 import pytest
 import torch
 from torch import nn
+from torch.nn import functional as F
 
 import slapo_b200 as slapo
 from slapo_b200.models import BertConfig, BertForMaskedLM, mlm_loss
@@ -244,3 +245,58 @@ def _sentinel_worker(rank, world):
 
 def test_no_tp_sentinel_survives_replace_and_partition():
     run_distributed(_sentinel_worker, 2)
+
+
+# ---- structured values across a stage boundary ------------------------------------------- #
+class _TupleLayer(nn.Module):
+    """A layer with the Hugging Face calling convention: returns ``(hidden, None)``."""
+
+    def __init__(self, width):
+        super().__init__()
+        self.fc = nn.Linear(width, width)
+
+    def forward(self, x):
+        x = x[0] if isinstance(x, tuple) else x
+        return torch.tanh(self.fc(x)), None
+
+
+class _TupleNet(nn.Module):
+    def __init__(self):
+        super().__init__()
+        self.layers = nn.ModuleList([_TupleLayer(8) for _ in range(4)])
+        self.head = nn.Linear(8, 3)
+
+    def forward(self, x):
+        for layer in self.layers:
+            x = layer(x)
+        return self.head(x[0])
+
+
+def _tuple_boundary_worker(rank, world):
+    torch.manual_seed(4)
+    ref = _TupleNet()
+    mesh = DeviceMesh(pp=2, dp=1, tp=1)
+    sch = slapo.create_schedule(copy.deepcopy(ref), group=mesh.schedule_group)
+    sch.trace_until("", tracer="pytorch")
+    sch["layers.1"].cut_pipeline_stage()
+    engine, _ = slapo.build(sch, target="native", mesh=mesh, init_weights=False,
+                            num_micro_batches=2, loss_fn=lambda out, lab: F.mse_loss(out, lab),
+                            config={"lr": 1e-2, "clip_grad": 0.0, "weight_decay": 0.0})
+    opt = torch.optim.AdamW(ref.parameters(), lr=1e-2, weight_decay=0.0)
+    for step in range(3):
+        # fresh data every step: a tuple pickled once into the handshake would be stale
+        gen = torch.Generator().manual_seed(10 + step)
+        x, y = torch.randn(4, 8, generator=gen), torch.randn(4, 3, generator=gen)
+        loss = engine.train_batch(x, labels=y)
+        opt.zero_grad()
+        want = torch.stack([F.mse_loss(ref(x.chunk(2)[m]), y.chunk(2)[m]) for m in range(2)]).mean()
+        want.backward()
+        opt.step()
+        torch.testing.assert_close(loss.detach(), want.detach(), rtol=1e-5, atol=1e-6)
+
+
+def test_tuple_valued_stage_boundary():
+    """``(hidden_states, None)`` handed from the last layer of a stage to the first layer of
+    the next: the tensor inside travels with every micro-batch and carries gradients back;
+    only the structure and the constants go into the one-time handshake."""
+    run_distributed(_tuple_boundary_worker, 2)
