@@ -4,9 +4,12 @@ Parity: slapo/primitives/checkpoint.py:12-58 of the reference.
 """
 from __future__ import annotations
 
+import functools
 import inspect
 
+import torch
 from torch import nn
+from torch.utils._pytree import tree_flatten
 
 from ..checkpoint import checkpoint as checkpoint_fn
 from .base import Primitive, register_primitive
@@ -17,7 +20,10 @@ class CheckPointWrapper(nn.Module):
 
     Keyword arguments are bound to the wrapped forward's signature and passed
     positionally (checkpointing with RNG replay is positional); a custom
-    ``order_args_fn(*args, **kwargs) -> list`` overrides the binding."""
+    ``order_args_fn(*args, **kwargs) -> list`` overrides the binding.  What lands in
+    a catch-all ``**kwargs`` of the wrapped forward (Hugging Face layers take flags and
+    position tensors that way) is handed on by name outside the checkpointed argument
+    list - allowed as long as none of it requires a gradient."""
 
     traceable = False
 
@@ -31,27 +37,38 @@ class CheckPointWrapper(nn.Module):
             self._sig = None
 
     def _ordered(self, args, kwargs):
+        """``(positional argument list, extra keyword arguments)``."""
         if self.order_args_fn is not None:
-            return list(self.order_args_fn(*args, **kwargs))
+            return list(self.order_args_fn(*args, **kwargs)), {}
         if not kwargs:
-            return list(args)
+            return list(args), {}
         if self._sig is None:
             raise ValueError("cannot order keyword arguments; pass order_args_fn")
         bound = self._sig.bind(*args, **kwargs)
         bound.apply_defaults()
-        ordered = []
+        ordered, extras = [], {}
         for name, par in self._sig.parameters.items():
             if par.kind is par.VAR_POSITIONAL:
                 ordered += list(bound.arguments.get(name, ()))
             elif par.kind is par.VAR_KEYWORD:
-                if bound.arguments.get(name):
-                    raise ValueError("**kwargs cannot be checkpointed positionally")
+                extras = dict(bound.arguments.get(name) or {})
+                if any(torch.is_tensor(t) and t.requires_grad
+                       for t in tree_flatten(extras)[0]):
+                    raise ValueError(
+                        f"keyword arguments {sorted(extras)} fall into **{name} of the "
+                        "checkpointed forward and carry gradients: they cannot be "
+                        "checkpointed positionally; pass order_args_fn")
+            elif par.kind is par.KEYWORD_ONLY:
+                extras[name] = bound.arguments[name]
             else:
                 ordered.append(bound.arguments[name])
-        return ordered
+        return ordered, extras
 
     def forward(self, *args, **kwargs):
-        return checkpoint_fn(self.mod, *self._ordered(args, kwargs))
+        ordered, extras = self._ordered(args, kwargs)
+        if extras:
+            return checkpoint_fn(functools.partial(self.mod, **extras), *ordered)
+        return checkpoint_fn(self.mod, *ordered)
 
 
 @register_primitive()

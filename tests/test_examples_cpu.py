@@ -5,6 +5,12 @@ import re
 import subprocess
 import sys
 
+import pytest
+import torch
+
+sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
+from dist_utils import run_distributed  # noqa: E402
+
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 SCRIPT = os.path.join(ROOT, "examples", "train_text.py")
 SMALL = ["--text", os.path.join(ROOT, "README.md"), "--layers", "2", "--hidden", "64", "--heads", "2",
@@ -89,3 +95,29 @@ def test_example_helpers():
                             init_weights=False, loss_fn=lambda o, l: mlm_loss(o["logits"], l))
     losses = ex_utils.train_with_deepspeed_engine(engine, batches, steps=6)
     assert len(losses) == 6 and losses[-1] < losses[0]
+
+
+def _hf_example_worker(rank, world, argv, out):
+    import deepspeed_hf as example
+
+    losses = example.train(example.parse_args(argv))
+    if rank == 0:
+        torch.save(losses, out)
+
+
+@pytest.mark.parametrize("family,pmp,tmp,world", [("opt", 2, 2, 4), ("gpt2", 1, 2, 4)])
+def test_hugging_face_example_script(family, pmp, tmp, world, tmp_path):
+    """``examples/deepspeed_hf.py``: a ``transformers`` model built on the meta device, the
+    family's recipe (pipeline cuts, sequence parallelism, recomputation), the ``"deepspeed"``
+    target with a DeepSpeed-layout configuration - on gloo ranks, OPT as 2 stages x TP 2 and
+    GPT-2 as TP 2 x DP 2."""
+    pytest.importorskip("transformers")
+    sys.path.insert(0, os.path.join(ROOT, "examples"))
+    out = str(tmp_path / "losses.pt")
+    argv = ["--family", family, "--hidden", "64", "--layers", "4", "--heads", "4", "--vocab", "512",
+            "--seq-len", "32", "--batch-size", "4", "--micro-batch-size", "2", "--pmp", str(pmp),
+            "--tmp", str(tmp), "--sequence-parallel", "--checkpoint", "0.5", "--iter-nums", "3",
+            "--device", "cpu", "--dtype", "fp32"]
+    run_distributed(_hf_example_worker, world, argv, out)
+    losses = torch.load(out)
+    assert len(losses) == 3 and all(5.5 < v < 7.0 for v in losses)     # ln(512) = 6.24

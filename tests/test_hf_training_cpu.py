@@ -1,6 +1,6 @@
 """Unmodified Hugging Face models through the recipes and the native engines: three optimizer
 steps on 2 pipeline stages x 2-way tensor parallelism (sequence-parallel regions where the
-recipe has them) against ``torch.optim.AdamW`` on the same Hugging Face model, untouched.
+recipe has them, half of the layers recomputed) against ``torch.optim.AdamW`` on the same Hugging Face model, untouched.
 
 This is the workflow of the reference's example scripts (a ``transformers`` model, the family's
 recipe with ``pipeline_cuts``, a pipeline runtime: examples/bert/deepspeed_hf.py:60-140 of the
@@ -66,7 +66,8 @@ def _worker(rank, world, family, pp, tp):
     mesh = DeviceMesh(pp=pp, dp=1, tp=tp)
     sp = family in _SP and tp > 1
     slapo.set_random_seed(1, tp_rank=mesh.tp_rank, pp_rank=mesh.pp_rank, always_enable_tp_seed=sp)
-    kwargs = dict(model_config=ref.config, group=mesh.schedule_group, attn_op_name="reference")
+    kwargs = dict(model_config=ref.config, group=mesh.schedule_group, attn_op_name="reference",
+                  ckpt_ratio=0.5)
     if family in _SP:
         kwargs.update(sequence_parallel=sp, sequence_parallel_axis=0)
     if pp > 1:

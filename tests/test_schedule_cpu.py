@@ -148,3 +148,44 @@ def test_tie_weight_analysis():
     assert len(ties) == 1
     (names,) = ties.values()
     assert sorted(n for n, _ in names) == ["emb.weight", "head.weight"]
+
+
+def test_checkpoint_hands_catch_all_keyword_arguments_on_by_name():
+    """A layer whose forward ends in ``**kwargs`` (the Hugging Face convention): named
+    arguments are checkpointed positionally, what falls into ``**kwargs`` is passed by name -
+    unless it carries a gradient."""
+    import pytest as _pytest
+
+    class Layer(nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.fc = nn.Linear(4, 4)
+
+        def forward(self, x, scale=1.0, **kwargs):
+            return self.fc(x) * scale + kwargs.get("shift", 0.0)
+
+    class Net(nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.layer = Layer()
+
+        def forward(self, x, shift):
+            return self.layer(x, scale=2.0, shift=shift, flag=True)
+
+    torch.manual_seed(0)
+    net = Net()
+    x = torch.randn(3, 4, requires_grad=True)
+    shift = torch.randn(3, 4)
+    want = net(x, shift)
+    want.sum().backward()
+    weight = net.layer.fc.weight
+    grad = weight.grad.clone()
+    net.zero_grad()
+    sch = slapo.create_schedule(net)
+    sch["layer"].checkpoint()
+    got = sch.mod(x, shift)
+    torch.testing.assert_close(got, want)
+    got.sum().backward()
+    torch.testing.assert_close(weight.grad, grad)
+    with _pytest.raises(ValueError, match="carry gradients"):
+        sch.mod(x, shift.clone().requires_grad_(True))
