@@ -1,6 +1,7 @@
 """Unmodified Hugging Face models through the recipes and the native engines: three optimizer
 steps on 2 pipeline stages x 2-way tensor parallelism (sequence-parallel regions where the
-recipe has them, half of the layers recomputed) against ``torch.optim.AdamW`` on the same Hugging Face model, untouched.
+recipe has them, half of the layers recomputed) against ``torch.optim.AdamW`` on the same
+Hugging Face model, untouched.
 
 This is the workflow of the reference's example scripts (a ``transformers`` model, the family's
 recipe with ``pipeline_cuts``, a pipeline runtime: examples/bert/deepspeed_hf.py:60-140 of the
