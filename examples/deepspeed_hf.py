@@ -24,9 +24,9 @@ sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
 import utils  # noqa: E402  (adds the repository root to sys.path)
 
 import slapo_b200 as slapo  # noqa: E402
-from slapo_b200.models import causal_lm_loss, mlm_loss  # noqa: E402
+from slapo_b200.models import causal_lm_loss, mlm_loss, seq2seq_loss  # noqa: E402
 
-FAMILIES = ("bert", "roberta", "albert", "gpt2", "gpt_neo", "opt")
+FAMILIES = ("bert", "roberta", "albert", "gpt2", "gpt_neo", "opt", "t5")
 
 
 def parse_args(argv=None):
@@ -37,6 +37,7 @@ def parse_args(argv=None):
     ap.add_argument("--heads", type=int, default=12)
     ap.add_argument("--vocab", type=int, default=50272)
     ap.add_argument("--seq-len", type=int, default=512)
+    ap.add_argument("--dec-seq-len", type=int, default=128, help="decoder length (t5)")
     ap.add_argument("--batch-size", type=int, default=16, help="samples per step and data-parallel replica")
     ap.add_argument("--micro-batch-size", type=int, default=4)
     ap.add_argument("--pmp", type=int, default=1, help="pipeline stages")
@@ -70,6 +71,10 @@ def hf_model(args):
         config = tr.GPTNeoConfig(vocab_size=v, hidden_size=h, num_layers=n, num_heads=a,
                                  attention_types=[[["global"], n]], max_position_embeddings=s)
         cls = tr.GPTNeoForCausalLM
+    elif args.family == "t5":
+        config = tr.T5Config(vocab_size=v, d_model=h, d_kv=h // a, d_ff=4 * h, num_layers=n,
+                             num_decoder_layers=n, num_heads=a)
+        cls = tr.T5ForConditionalGeneration
     else:
         config = tr.OPTConfig(vocab_size=v, hidden_size=h, num_hidden_layers=n, ffn_dim=4 * h,
                               num_attention_heads=a, max_position_embeddings=s,
@@ -108,16 +113,24 @@ def train(args):
     sch_config = dict(model_config=config, group=mesh.schedule_group, ckpt_ratio=args.checkpoint,
                       bf16=args.dtype == "bf16", fp16=args.dtype == "fp16",
                       attn_op_name="auto" if on_gpu else "reference")
-    if args.family != "albert":
+    seq2seq = args.family == "t5"
+    if args.family not in ("albert", "t5"):
         sch_config.update(sequence_parallel=sp, sequence_parallel_axis=0)
     if args.pmp > 1:
+        shapes = {"batch_size": args.micro_batch_size, "seq_len": args.seq_len}
+        if seq2seq:
+            shapes = {"input_shapes": {
+                "input_ids": (args.micro_batch_size, args.seq_len),
+                "decoder_input_ids": (args.micro_batch_size, args.dec_seq_len)}}
         sch_config.update(
-            pipeline_cuts=utils.generate_pipeline_cuts(args.layers, args.pmp),
-            trace_config={"batch_size": args.micro_batch_size, "seq_len": args.seq_len})
+            pipeline_cuts=utils.generate_pipeline_cuts(args.layers, args.pmp,
+                                                       is_encoder_decoder=seq2seq),
+            trace_config=shapes)
     sch = slapo.model_schedule.apply_schedule(model, args.family, **sch_config)
 
-    kind = "causal" if args.family in ("gpt2", "gpt_neo", "opt") else "mlm"
-    loss_of = causal_lm_loss if kind == "causal" else mlm_loss
+    kind = "seq2seq" if seq2seq else (
+        "causal" if args.family in ("gpt2", "gpt_neo", "opt") else "mlm")
+    loss_of = {"causal": causal_lm_loss, "mlm": mlm_loss, "seq2seq": seq2seq_loss}[kind]
 
     def loss_fn(out, labels):
         logits = out["logits"] if isinstance(out, dict) else out.logits
@@ -144,6 +157,10 @@ def train(args):
     def batches():
         while True:
             ids = torch.randint(0, args.vocab, (per_call, args.seq_len), generator=gen)
+            if kind == "seq2seq":
+                dec = torch.randint(0, args.vocab, (per_call, args.dec_seq_len), generator=gen)
+                yield {"input_ids": ids, "decoder_input_ids": dec}, dec.clone()
+                continue
             if kind == "causal":
                 labels = ids.clone()
             else:

@@ -93,8 +93,12 @@ def train_with_engine(engine, dataloader, preproc=None, postproc=None, steps=40,
     losses, seen, t0 = [], 0, None
     for step, batch in enumerate(dataloader):
         inputs, labels = preproc(step, batch) if preproc is not None else batch
-        inputs = [t.to(device) if torch.is_tensor(t) else t for t in inputs]
-        loss = engine.train_batch(*inputs, labels=labels.to(device))
+        if isinstance(inputs, dict):        # named inputs (encoder-decoder models)
+            inputs = {k: t.to(device) if torch.is_tensor(t) else t for k, t in inputs.items()}
+            loss = engine.train_batch(**inputs, labels=labels.to(device))
+        else:
+            inputs = [t.to(device) if torch.is_tensor(t) else t for t in inputs]
+            loss = engine.train_batch(*inputs, labels=labels.to(device))
         loss = postproc(step, loss) if postproc is not None else loss
         losses.append(float(loss))
         if step == 2:

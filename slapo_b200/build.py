@@ -60,6 +60,28 @@ def _call_init(init_fn, mod, path):
         init_fn(mod)
 
 
+_UNTOUCHED_SEEN = set()
+
+
+def _default_init_if_untouched(mod, names, init_fn):
+    """Initialisers that dispatch on composite classes (Hugging Face's T5 fills the projections
+    from ``T5Attention`` / ``T5DenseActDense``, the embedding from the model class) do nothing
+    for the layer itself when modules are initialised one at a time: a weight matrix that is
+    still all zeros after the call gets the layer's own ``reset_parameters`` instead, so that
+    the model trains - with PyTorch's default scheme for that layer, which the log says once."""
+    still_zero = [n for n in names if mod._parameters[n].dim() > 1
+                  and not bool(mod._parameters[n].data.any())]
+    if not still_zero or not hasattr(mod, "reset_parameters"):
+        return
+    mod.reset_parameters()
+    key = type(mod).__name__
+    if key not in _UNTOUCHED_SEEN:
+        _UNTOUCHED_SEEN.add(key)
+        logger.info("%s left the weights of %s modules untouched (it initialises them from a "
+                    "parent class); PyTorch's default initialiser is used for them",
+                    getattr(init_fn, "__qualname__", init_fn), key, ranks=0)
+
+
 def _pick_init_fn(top_mod, init_weights):
     if callable(init_weights):
         return init_weights
@@ -131,6 +153,8 @@ def consolidate_model(sch, target=None, init_weights=True, device=None, **kwargs
         was_meta = any(p.is_meta for _, p in own if p not in done) or bool(own_bufs)
         if was_meta:
             _call_init(init_fn, mod, path)
+            _default_init_if_untouched(mod, [n for n, p in own if p.is_meta and p not in done],
+                                       init_fn)
         # 3. broadcast + re-split
         for n, old in own:
             if old in done:

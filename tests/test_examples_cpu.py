@@ -105,7 +105,8 @@ def _hf_example_worker(rank, world, argv, out):
         torch.save(losses, out)
 
 
-@pytest.mark.parametrize("family,pmp,tmp,world", [("opt", 2, 2, 4), ("gpt2", 1, 2, 4)])
+@pytest.mark.parametrize("family,pmp,tmp,world", [("opt", 2, 2, 4), ("gpt2", 1, 2, 4),
+                                                  ("t5", 2, 1, 2)])
 def test_hugging_face_example_script(family, pmp, tmp, world, tmp_path):
     """``examples/deepspeed_hf.py``: a ``transformers`` model built on the meta device, the
     family's recipe (pipeline cuts, sequence parallelism, recomputation), the ``"deepspeed"``
@@ -115,9 +116,13 @@ def test_hugging_face_example_script(family, pmp, tmp, world, tmp_path):
     sys.path.insert(0, os.path.join(ROOT, "examples"))
     out = str(tmp_path / "losses.pt")
     argv = ["--family", family, "--hidden", "64", "--layers", "4", "--heads", "4", "--vocab", "512",
-            "--seq-len", "32", "--batch-size", "4", "--micro-batch-size", "2", "--pmp", str(pmp),
+            "--seq-len", "32", "--dec-seq-len", "16", "--batch-size", "4",
+            "--micro-batch-size", "2", "--pmp", str(pmp),
             "--tmp", str(tmp), "--sequence-parallel", "--checkpoint", "0.5", "--iter-nums", "3",
             "--device", "cpu", "--dtype", "fp32"]
     run_distributed(_hf_example_worker, world, argv, out)
     losses = torch.load(out)
-    assert len(losses) == 3 and all(5.5 < v < 7.0 for v in losses)     # ln(512) = 6.24
+    # random tokens: ln(512) = 6.24; T5 starts lower (tied head, labels = decoder inputs)
+    assert len(losses) == 3 and all(0.0 < v < 7.0 for v in losses)
+    if family != "t5":
+        assert all(v > 5.5 for v in losses)
