@@ -111,6 +111,14 @@ def checkpoint_layers(sch, layer_paths, ckpt_ratio, method="uniform", order_args
     n = len(layer_paths)
     if ckpt_ratio <= 0 or n == 0:
         return 0
+    config = getattr(sch.get_top_schedule().mod, "config", None)
+    if getattr(config, "use_cache", False):
+        # A recomputed layer runs twice; a key / value cache that the model threads through
+        # its layers (Hugging Face models build one when ``use_cache`` is on) would be
+        # appended to twice.  Hugging Face's own gradient checkpointing switches it off too.
+        config.use_cache = False
+        logger.info("use_cache is switched off: activation checkpointing runs layers twice",
+                    ranks=0)
     n_ckpt = int(n * min(ckpt_ratio, 1.0))
     if method == "head":
         chosen = list(range(n_ckpt))

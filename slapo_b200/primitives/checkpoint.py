@@ -66,6 +66,12 @@ class CheckPointWrapper(nn.Module):
 
     def forward(self, *args, **kwargs):
         ordered, extras = self._ordered(args, kwargs)
+        for value in list(ordered) + list(extras.values()):
+            if hasattr(value, "get_seq_length") and hasattr(value, "update"):
+                raise ValueError(
+                    f"a key / value cache ({type(value).__name__}) is passed into a checkpointed "
+                    "layer: the layer runs twice and would append to it twice; switch the "
+                    "model's use_cache off for training")
         if extras:
             return checkpoint_fn(functools.partial(self.mod, **extras), *ordered)
         return checkpoint_fn(self.mod, *ordered)

@@ -189,3 +189,38 @@ def test_checkpoint_hands_catch_all_keyword_arguments_on_by_name():
     torch.testing.assert_close(weight.grad, grad)
     with _pytest.raises(ValueError, match="carry gradients"):
         sch.mod(x, shift.clone().requires_grad_(True))
+
+
+def test_checkpoint_refuses_a_key_value_cache():
+    """A stateful cache handed into a recomputed layer would be appended to twice."""
+    import pytest as _pytest
+
+    class Cache:
+        def get_seq_length(self):
+            return 0
+
+        def update(self, *a):
+            return a
+
+    class Net(nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.layer = nn.Linear(4, 4)
+
+        def forward(self, x, cache=None):
+            return self.layer(x)
+
+    class Top(nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.net = Net()
+
+        def forward(self, x, cache=None):
+            return self.net(x, cache=cache)
+
+    sch = slapo.create_schedule(Top())
+    sch["net"].checkpoint()
+    x = torch.randn(2, 4, requires_grad=True)
+    assert sch.mod(x).shape == (2, 4)
+    with _pytest.raises(ValueError, match="use_cache"):
+        sch.mod(x, cache=Cache())
