@@ -213,7 +213,21 @@ def shard_layers(sch, config, lay, prefix, sequence_parallel, sp_axis):
                 sch, [_j(path, lay["ln1"]), _j(path, lay["ln2"])],
                 [_j(path, lay["attn"], "self_attn.out_proj"),
                  _j(mlp_base, "fc_out" if lay["mlp"] else lay["fc_out"])])
-    if sequence_parallel:
+    if sequence_parallel and sp_axis == 1 and lay["mlp"] is None \
+            and tracer_for(sch.mod) == "huggingface":
+        raise ValueError(
+            "Hugging Face's OPT layer flattens its tokens to [batch * sequence, hidden] in front "
+            "of fc1, where a gather along the sequence axis has no meaning; use "
+            "sequence_parallel_axis=0 (whole sequences per rank) for this model")
+    if sequence_parallel and _positions_follow_embeddings(sch, sp_axis):
+        # whole-sequence embeddings (the token table all-reduces), split where the first block
+        # takes them over
+        first = sch[_layer_paths(sch, lay, prefix)[0]]
+        first.sync("fwd_pre", "scatter", axis=sp_axis)
+        sch[_j(prefix, lay["ln_f"])].sync("fwd_post", "all_gather", axis=sp_axis,
+                                          tensor_parallel_output_grad=False)
+        annotate_replicated(sch, [_j(prefix, lay["ln_f"])], [])
+    elif sequence_parallel:
         wte_meta = sch[_j(prefix, lay["wte"])].metadata.primitives.get("shard") or {}
         if "weight" not in wte_meta:  # a vocabulary-parallel embedding reduce-scatters itself
             sch[_j(prefix, lay["wte"])].sync("fwd_post", "scatter", axis=sp_axis)
@@ -230,10 +244,20 @@ def shard_layers(sch, config, lay, prefix, sequence_parallel, sp_axis):
     return len(_layer_paths(sch, lay, prefix))
 
 
+def _positions_follow_embeddings(sch, sp_axis):
+    """Hugging Face decoders (recent ``transformers``) number the positions from the length of
+    the embedded tokens.  With the sequence axis split inside the embedding, every rank would
+    count from zero over its own part; for those models the embeddings stay whole and the
+    split happens in front of the first block."""
+    return sp_axis == 1 and tracer_for(sch.mod) == "huggingface"
+
+
 def shard_embedding_and_head(sch, config, lay, prefix, sequence_parallel, sp_axis=1):
     if sch.world_size == 1 or config.vocab_size % sch.world_size:
         return
     wte = sch[_j(prefix, lay["wte"])]
+    if sequence_parallel and _positions_follow_embeddings(sch, sp_axis):
+        sequence_parallel = False
     shard_word_embedding(wte, config.vocab_size, sequence_parallel, sp_axis)
     if lay["head"] in sch:
         head = sch[lay["head"]]

@@ -182,6 +182,10 @@ def _make_sync_callable(sch, mode, op, **kwargs):
                 tensor_parallel_output_grad=kwargs.get("tensor_parallel_output_grad", True))
         if "->" in op:
             return mode, parse_reshard(op, group)
+        if op == "scatter" and mode == "fwd_pre":
+            # keep this rank's part of the first input (the start of a sequence-parallel
+            # region in front of a block); the gradient is gathered again
+            return mode, partial(scatter_forward_output, dim=axis, group=group)
         if mode == "fwd_post":
             if op == "reduce_scatter":
                 validate_sync(sch, mode, op)

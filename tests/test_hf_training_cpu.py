@@ -57,7 +57,7 @@ def _logits(out):
     return out["logits"] if isinstance(out, dict) else out.logits
 
 
-def _worker(rank, world, family, pp, tp):
+def _worker(rank, world, family, pp, tp, sp_axis=0):
     from slapo_b200.models import causal_lm_loss, mlm_loss, seq2seq_loss
     from slapo_b200.parallel.mesh import DeviceMesh
 
@@ -70,7 +70,7 @@ def _worker(rank, world, family, pp, tp):
     kwargs = dict(model_config=ref.config, group=mesh.schedule_group, attn_op_name="reference",
                   ckpt_ratio=0.5)
     if family in _SP:
-        kwargs.update(sequence_parallel=sp, sequence_parallel_axis=0)
+        kwargs.update(sequence_parallel=sp, sequence_parallel_axis=sp_axis)
     if pp > 1:
         # the graphs of a Hugging Face model are specialised on the micro-batch's shapes
         if kind == "seq2seq":
@@ -129,3 +129,16 @@ def test_hugging_face_t5_keeps_its_embedding_tied_under_tensor_parallelism():
     shared weight: without vocabulary-parallel hooks on each, training would quietly split
     the encoder's table from the head's (two steps are enough to see it)."""
     run_distributed(_worker, 2, "t5", 1, 2)
+
+
+@pytest.mark.parametrize("family", ["bert", "gpt2", "gpt_neo"])
+def test_hugging_face_model_with_the_sequence_axis_split(family):
+    """``sequence_parallel_axis=1`` (the reference's layout).  The decoders of recent
+    ``transformers`` number positions from the embedded tokens' length, so their embeddings
+    stay whole and the split happens in front of the first block."""
+    run_distributed(_worker, 4, family, 2, 2, 1)
+
+
+def test_hugging_face_opt_refuses_the_sequence_axis_split():
+    with pytest.raises(Exception, match="sequence_parallel_axis=0"):
+        run_distributed(_worker, 2, "opt", 1, 2, 1)

@@ -107,7 +107,7 @@ def test_pipeline_x_tensor_parallel_training_matches_adamw(name):
     run_distributed(_worker, 4, name, 2, 2, 1, 0.5)
 
 
-@pytest.mark.parametrize("name", ["bert-base", "gpt2-medium", "opt-350m", "t5-base"])
+@pytest.mark.parametrize("name", _MODELS)
 def test_tensor_x_data_parallel_training_matches_adamw(name):
     run_distributed(_worker, 4, name, 1, 2, 2, 0.0)
 
