@@ -51,6 +51,12 @@ from .engine import EngineConfig, TrainEngine
 logger = get_logger("pipeline_engine")
 
 
+def _dense_like(t):
+    """A contiguous receive buffer of ``t``'s shape (``empty_like`` keeps the strides of a
+    permuted tensor - a relative-position bias, say - and p2p receives need dense memory)."""
+    return torch.empty(t.shape, dtype=t.dtype, device=t.device)
+
+
 class PipelineStage(nn.Module):
     """One stage: maps value names to the stage module's arguments and back."""
 
@@ -210,7 +216,7 @@ class PipelineEngine:
                     ops.append(dist.P2POp(dist.isend, p.data.contiguous(),
                                           self.mesh.get_rank(pp=s, dp=c["dp"], tp=c["tp"])))
             else:
-                buf = torch.empty_like(p.data)
+                buf = _dense_like(p.data)
                 ops.append(dist.P2POp(dist.irecv, buf,
                                       self.mesh.get_rank(pp=src_stage, dp=c["dp"], tp=c["tp"])))
                 copies.append((p, buf))
@@ -231,7 +237,7 @@ class PipelineEngine:
             for r in ranks:
                 if r == self.mesh.rank:
                     continue
-                buf = torch.empty_like(p.grad)
+                buf = _dense_like(p.grad)
                 ops.append(dist.P2POp(dist.isend, p.grad.contiguous(), r))
                 ops.append(dist.P2POp(dist.irecv, buf, r))
                 adds.append((p, buf))
@@ -326,7 +332,7 @@ class PipelineEngine:
 
     def _post_recv_backward(self, rec):
         """Post the receives of the output gradients of a micro-batch in flight."""
-        grads = [torch.empty_like(t) for t in rec["sent"]]
+        grads = [_dense_like(t) for t in rec["sent"]]
         works = []
         if self.stage_id < self.n_stages - 1 and grads:
             works = self._irecv(grads, self.next_rank, self._link(self.stage_id, "bwd"))
@@ -444,7 +450,7 @@ class PipelineEngine:
             pending.append(rec)
             # send this forward result, receive the gradient of the oldest micro-batch
             done = pending.pop(0)
-            grads = [torch.empty_like(t) for t in done["sent"]]
+            grads = [_dense_like(t) for t in done["sent"]]
             if not last:
                 self._exchange([(t.detach(), nxt) for t in rec["payload"]],
                                [(g, nxt) for g in grads])
@@ -457,7 +463,7 @@ class PipelineEngine:
                                [(t, prev) for t in self._tensor_list(bufs)])
         while pending:
             done = pending.pop(0)
-            grads = [torch.empty_like(t) for t in done["sent"]]
+            grads = [_dense_like(t) for t in done["sent"]]
             if not last:
                 self._exchange([], [(g, nxt) for g in grads])
             in_grads = backward(done, grads)

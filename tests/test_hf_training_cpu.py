@@ -74,10 +74,11 @@ def _worker(rank, world, family, pp, tp, sp_axis=0):
     if pp > 1:
         # the graphs of a Hugging Face model are specialised on the micro-batch's shapes
         if kind == "seq2seq":
-            kwargs.update(pipeline_cuts=[[], []], trace_config={
+            kwargs.update(pipeline_cuts=[[], []] if pp == 2 else [[0], [0]], trace_config={
                 "input_shapes": {"input_ids": (2, 32), "decoder_input_ids": (2, 16)}})
         else:
-            kwargs.update(pipeline_cuts=[1], trace_config={"batch_size": 2, "seq_len": 32})
+            kwargs.update(pipeline_cuts=[1] if pp == 2 else [0, 1, 2],
+                          trace_config={"batch_size": 2, "seq_len": 32})
     sch = slapo.model_schedule.apply_schedule(copy.deepcopy(ref), family, **kwargs)
     loss_of = {"mlm": mlm_loss, "causal": causal_lm_loss, "seq2seq": seq2seq_loss}[kind]
     extra = dict(num_micro_batches=2) if pp > 1 else {}
@@ -142,3 +143,10 @@ def test_hugging_face_model_with_the_sequence_axis_split(family):
 def test_hugging_face_opt_refuses_the_sequence_axis_split():
     with pytest.raises(Exception, match="sequence_parallel_axis=0"):
         run_distributed(_worker, 2, "opt", 1, 2, 1)
+
+
+@pytest.mark.parametrize("family", ["t5", "gpt2"])
+def test_hugging_face_model_on_four_stages(family):
+    """More stages than micro-batches; for T5 the relative-position biases (permuted views,
+    with gradients) cross the stage boundaries next to the hidden states."""
+    run_distributed(_worker, 4, family, 4, 1)
