@@ -69,9 +69,14 @@ def _default_init_if_untouched(mod, names, init_fn):
     for the layer itself when modules are initialised one at a time: a weight matrix that is
     still all zeros after the call gets the layer's own ``reset_parameters`` instead, so that
     the model trains - with PyTorch's default scheme for that layer, which the log says once."""
+    owner = getattr(init_fn, "__self__", None)
+    if not hasattr(mod, "reset_parameters") or not any(
+            c.__name__ == "PreTrainedModel" for c in type(owner).__mro__):
+        return      # only for Hugging Face's class-dispatching initialisers: anyone else's
+        #             zeros are taken as meant
     still_zero = [n for n in names if mod._parameters[n].dim() > 1
                   and not bool(mod._parameters[n].data.any())]
-    if not still_zero or not hasattr(mod, "reset_parameters"):
+    if not still_zero:
         return
     mod.reset_parameters()
     key = type(mod).__name__
