@@ -176,7 +176,6 @@ class TrainEngine:
         self._status_host = None      # pinned copy of the kernels' status word, one step behind
         self._status_event = None
         self._build_flat_storage()
-        self._init_loss_scale()
         self._build_optimizer_state()
         self._install_grad_hooks()
         self._phase_events = []       # (name, start event, end event) of the last step
@@ -199,6 +198,7 @@ class TrainEngine:
             raise RuntimeError("parameters are still on the meta device; build with init_weights")
         self.device = params[0].device
         self.param_dtype = params[0].dtype
+        self._init_loss_scale()     # before the choice of the data-parallel path below
         if any(p.dtype != self.param_dtype for p in params):
             raise ValueError("all trainable parameters must share one dtype")
         # reverse registration order ~ the order in which backward finishes them

@@ -114,3 +114,31 @@ def test_pipeline_stages_scale_and_skip_together():
     from dist_utils import run_distributed
 
     run_distributed(_pp_worker, 2)
+
+
+def test_fused_data_parallel_path_is_decided_after_the_loss_scale(monkeypatch):
+    """The choice between the peer-memory and the NCCL data-parallel path is made while the
+    flat buffers are built and reads the scaling state: it must exist by then.  (On a CPU
+    the decision returns early; here it is replayed as on a CUDA device with two replicas.)"""
+    from types import SimpleNamespace
+
+    from slapo_b200.runtime import engine as engine_mod
+
+    calls = []
+    real = TrainEngine._want_fused_dp
+
+    def spy(self):
+        calls.append(hasattr(self, "scaling"))
+        return real(self)
+
+    monkeypatch.setattr(TrainEngine, "_want_fused_dp", spy)
+    eng = TrainEngine(_net().half(), {"loss_scale": 0}, loss_fn=_loss)
+    assert calls and all(calls)
+    monkeypatch.setattr(TrainEngine, "_want_fused_dp", real)
+    monkeypatch.setattr(engine_mod.native, "available", lambda: True)
+    eng.device, eng.dp_size = SimpleNamespace(type="cuda"), 2
+    assert eng.scaling and eng._want_fused_dp() is False          # fp16: NCCL path
+    plain = TrainEngine(_net().bfloat16(), None, loss_fn=_loss)
+    plain.device, plain.dp_size = SimpleNamespace(type="cuda"), 2
+    assert not plain.scaling
+    assert plain._want_fused_dp() == hasattr(torch.ops.slapo_b200, "dp_grad_rs")
