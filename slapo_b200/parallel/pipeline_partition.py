@@ -168,6 +168,19 @@ def generate_pipeline_partition(sch):
                 + list(sub.named_buffers(remove_duplicate=False))
             sub.original_tensor_names = {n: original[id(t)] for n, t in local
                                          if id(t) in original}
+    # Hooks of the whole model follow what they act on (slapo/pipeline.py:214-226 of the
+    # reference): input hooks - a broadcast of the batch inside the tensor-parallel group, say
+    # - stay with the top module, and the pipeline engine runs them over the model's inputs
+    # where those enter (an encoder-decoder model has inputs that only a later stage reads);
+    # backward hooks go to the first stage, output hooks to the last one.
+    from ..utils.common import transfer_hooks
+
+    stages = sorted((n for n, _ in split.named_children() if n.startswith("submod_")),
+                    key=lambda n: int(n.split("_")[1]))
+    transfer_hooks(root, split, ["fwd_pre"])
+    if stages:
+        transfer_hooks(root, getattr(split, stages[0]), ["bwd_post"])
+        transfer_hooks(root, getattr(split, stages[-1]), ["fwd_post"])
     from ..schedule import create_schedule
 
     new_sch = create_schedule(split, group=sch.group_arg)
@@ -272,4 +285,5 @@ def build_pipeline_model(sch, target, **kwargs):
                                 stage_output_names(sch.mod)[i], **extra))
     input_names = [n.name for n in sch.mod.graph.nodes if n.op == "placeholder"]
     return engine_cls(stages, live_in=live_in, input_names=input_names,
-                      output_spec=final_output_spec(sch.mod))
+                      output_spec=final_output_spec(sch.mod),
+                      input_hooks=list(sch.mod._forward_pre_hooks.values()))

@@ -94,12 +94,15 @@ class PipelineModel(nn.Module):
     """All stages plus the boundary contract; runs them in sequence when called
     directly (single process, e.g. for verification)."""
 
-    def __init__(self, stages, live_in, input_names, output_spec):
+    def __init__(self, stages, live_in, input_names, output_spec, input_hooks=()):
         super().__init__()
         self.stages = nn.ModuleList(stages)
         self.live_in = [list(x) for x in live_in]
         self.input_names = list(input_names)
         self.output_spec = output_spec
+        # forward-pre hooks of the unpartitioned model (``sync("fwd_pre", fn)`` on the top
+        # schedule): run over the model's inputs, in declaration order, where they enter
+        self.input_hooks = list(input_hooks)
 
     def materialize_output(self, env):
         def pick(x):
@@ -113,11 +116,17 @@ class PipelineModel(nn.Module):
 
         return pick(self.output_spec)
 
-    def bind_inputs(self, args, kwargs):
+    def bind_inputs(self, args, kwargs, run_hooks=True):
         env = dict(zip(self.input_names, args))
         env.update(kwargs)
         for name in self.input_names:
             env.setdefault(name, None)
+        if run_hooks:
+            for hook in self.input_hooks:
+                result = hook(self, tuple(env[n] for n in self.input_names))
+                if result is not None:
+                    result = result if isinstance(result, tuple) else (result,)
+                    env.update(zip(self.input_names, result))
         return env
 
     def forward(self, *args, **kwargs):
@@ -476,7 +485,9 @@ class PipelineEngine:
         from .engine import _release_staging_slots
 
         _release_staging_slots()
-        env = self.model.bind_inputs(args, kwargs)
+        # the model's input hooks (collectives inside the first stage's tensor-parallel group)
+        # run on the ranks where the inputs enter the pipeline
+        env = self.model.bind_inputs(args, kwargs, run_hooks=self.stage_id == 0)
         micro_inputs = [{} for _ in range(m)]
         for name, val in env.items():
             for i, piece in enumerate(_split_micro(val, m)):

@@ -45,7 +45,7 @@ def _tiny_spec(name):
     return spec
 
 
-def _worker(rank, world, name, pp, tp, dp, ckpt):
+def _worker(rank, world, name, pp, tp, dp, ckpt, bcast=False):
     from slapo_b200.parallel.mesh import DeviceMesh
 
     torch.manual_seed(21)
@@ -57,7 +57,7 @@ def _worker(rank, world, name, pp, tp, dp, ckpt):
     slapo.set_random_seed(1, tp_rank=mesh.tp_rank, pp_rank=mesh.pp_rank, dp_rank=mesh.dp_rank,
                           always_enable_tp_seed=True)
     kwargs = dict(model_config=spec.config, group=mesh.schedule_group, attn_op_name="reference",
-                  ckpt_ratio=ckpt)
+                  ckpt_ratio=ckpt, bcast_input=bcast)
     if spec.schedule_key in _SP_FAMILIES:
         kwargs.update(sequence_parallel=True, sequence_parallel_axis=0)
     if pp > 1:
@@ -79,6 +79,10 @@ def _worker(rank, world, name, pp, tp, dp, ckpt):
     # every data-parallel rank trains on its own batch; the reference sees all of them
     batches = [spec.make_batch(4, seq=32, seq_dec=16, seed=3 + r) for r in range(dp)]
     inputs, labels = batches[mesh.dp_rank]
+    if bcast and mesh.tp_rank > 0:
+        # only the first rank of a tensor-parallel group holds the batch; the recipe's
+        # input hook hands it to the others
+        inputs = tuple(torch.zeros_like(t) for t in inputs)
     for step in range(3):
         if pp > 1:
             loss = engine.train_batch(*inputs, labels=labels)
@@ -110,6 +114,14 @@ def test_pipeline_x_tensor_parallel_training_matches_adamw(name):
 @pytest.mark.parametrize("name", _MODELS)
 def test_tensor_x_data_parallel_training_matches_adamw(name):
     run_distributed(_worker, 4, name, 1, 2, 2, 0.0)
+
+
+@pytest.mark.parametrize("name", ["bert-base", "t5-base"])
+def test_broadcast_input_hook_under_pipeline_stages(name):
+    """``bcast_input=True``: the hook on the whole model survives the partition and runs where
+    the inputs enter the pipeline - for T5 also over the decoder ids, which only the second
+    stage reads."""
+    run_distributed(_worker, 4, name, 2, 2, 1, 0.0, True)
 
 
 def test_pipeline_mesh_without_cuts_is_refused():
