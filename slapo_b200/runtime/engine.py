@@ -329,7 +329,16 @@ class TrainEngine:
         lo = bucket.start + self.dp_rank * per
         return lo, lo + per
 
+    def _sync_initial_params(self):
+        """Data-parallel replicas start from the first replica's parameters.  Replicas that were
+        initialised on their own (meta-device build with per-replica seeds) would otherwise
+        differ until the first optimizer step mixes their shards - and for good without ZeRO."""
+        if self.dp_size > 1 and self.dp_group is not None:
+            dist.broadcast(self.flat_param, src=dist.get_global_rank(self.dp_group, 0),
+                           group=self.dp_group)
+
     def _build_optimizer_state(self):
+        self._sync_initial_params()
         # this rank's slice of every bucket, packed back to back
         self.shard_ranges = [self._shard_range(b) for b in self.buckets]
         n_own = sum(hi - lo for lo, hi in self.shard_ranges)

@@ -8,6 +8,9 @@ import copy
 
 import pytest
 import torch
+import torch.distributed as dist
+from torch import nn
+from torch.nn import functional as F
 
 import slapo_b200 as slapo
 from slapo_b200.models import (AlbertConfig, AlbertForMaskedLM, BertConfig, BertForMaskedLM,
@@ -114,3 +117,31 @@ def _pp_dp_worker(rank, world, p2p_mode="overlap"):
 @pytest.mark.parametrize("p2p_mode", ["overlap", "paired"])
 def test_pipeline_times_data_parallel_with_tied_embeddings_and_clipping(p2p_mode):
     run_distributed(_pp_dp_worker, 4, p2p_mode)
+
+
+def _replica_init_worker(rank, world, zero):
+    """Replicas built from different seeds (a meta-device build seeds every data-parallel rank
+    on its own) train as one model: the engine starts them from the first replica's values."""
+    from slapo_b200.parallel.mesh import DeviceMesh
+    from slapo_b200.runtime.engine import TrainEngine
+
+    mesh = DeviceMesh(pp=1, dp=world, tp=1)
+    torch.manual_seed(100 + rank)
+    model = nn.Sequential(nn.Linear(8, 16), nn.GELU(), nn.Linear(16, 4))
+    engine = TrainEngine(model, {"lr": 1e-2, "zero": zero}, mesh=mesh,
+                         loss_fn=lambda out, lab: F.mse_loss(out, lab))
+    flat = torch.cat([p.detach().reshape(-1) for p in model.parameters()])
+    both = [torch.empty_like(flat) for _ in range(world)]
+    dist.all_gather(both, flat)
+    torch.testing.assert_close(both[0], both[1], rtol=0, atol=0)
+    gen = torch.Generator().manual_seed(5 + rank)
+    for _ in range(2):
+        engine.train_batch(torch.randn(4, 8, generator=gen), labels=torch.randn(4, 4, generator=gen))
+    flat = torch.cat([p.detach().reshape(-1) for p in model.parameters()])
+    dist.all_gather(both, flat)
+    torch.testing.assert_close(both[0], both[1], rtol=0, atol=0)
+
+
+@pytest.mark.parametrize("zero", [True, False])
+def test_replicas_start_from_the_first_replicas_parameters(zero):
+    run_distributed(_replica_init_worker, 2, zero)
