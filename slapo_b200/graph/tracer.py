@@ -51,6 +51,11 @@ def is_fx_tracing() -> bool:
         return False
 
 
+_OPS_PACKAGE = __name__.split(".")[0] + ".ops."
+# ``decompose()`` swaps a Linear for this class precisely so that ``+ bias`` shows up in a graph
+_OPS_MEANT_FOR_TRACING = ("LinearWithSeparateBias",)
+
+
 class HierTracer(fx.Tracer):
     """fx tracer with name/class based leaf rules.
 
@@ -61,14 +66,29 @@ class HierTracer(fx.Tracer):
 
     name = "pytorch"
 
-    def __init__(self, leaf_modules=None, forced_leaf_names=None):
+    def __init__(self, leaf_modules=None, forced_leaf_names=None, keep_ops_whole=True):
         super().__init__(param_shapes_constant=True)
         self.leaf_modules = list(leaf_modules or [])
         self.forced_leaf_names = set(forced_leaf_names or [])
+        self.keep_ops_whole = keep_ops_whole
 
     def user_leaf(self, m: nn.Module, qualname: str) -> bool:
         if getattr(m, "traceable", True) is False:
             return True
+        # The operators of this package that a recipe swapped in (attention, fused blocks,
+        # norms) stay whole when a level above them is traced: dissolved into a graph, their
+        # parameters end up on bare containers (which class-dispatching initialisers do not
+        # recognise) and their forward loses the kernel path.  Tracing one of them on its own
+        # (``sch[path].trace()``) still works: the rule is about children, and a flattened
+        # trace - which asks for everything in one graph - does not apply it.
+        if self.keep_ops_whole and type(m).__name__ not in _OPS_MEANT_FOR_TRACING:
+            if type(m).__module__.startswith(_OPS_PACKAGE):
+                return True
+            # Likewise a module that owns parameters itself (a position table, a norm, a head
+            # with its own bias): its forward is a primitive of the model, and its class is
+            # what an initialiser dispatches on.
+            if any(p is not None for p in m._parameters.values()):
+                return True
         cls = type(m).__name__
         for pat in self.leaf_modules:
             if isinstance(pat, type):
@@ -95,7 +115,7 @@ class HierTracer(fx.Tracer):
 _META_TRACER_CLS = []
 
 
-def MetaHierTracer(leaf_modules=None, forced_leaf_names=None):   # noqa: N802 - a class factory
+def MetaHierTracer(leaf_modules=None, forced_leaf_names=None, keep_ops_whole=True):   # noqa: N802
     """The leaf rules of :class:`HierTracer` on ``torch.fx``'s meta-tensor tracer (the class
     is composed on first use, so the experimental module is imported only then)."""
     if not _META_TRACER_CLS:
@@ -113,19 +133,10 @@ def MetaHierTracer(leaf_modules=None, forced_leaf_names=None):   # noqa: N802 - 
         def proxy(self, node):
             return ShapeProxy(node, self)
 
-        def user_leaf(self, m, qualname):
-            # The operators of this package that a recipe swapped in (attention, fused MLP,
-            # norms) stay whole: this tracer specialises graphs on the example shapes, and the
-            # batch extent inside them differs between the sequence-parallel regions.
-            if type(m).__module__.startswith(__name__.split(".")[0] + ".ops."):
-                return True
-            return HierTracer.user_leaf(self, m, qualname)
-
         _META_TRACER_CLS.append(type("MetaHierTracer", (HierTracer, MetaTracer), {
             "name": "huggingface", "create_proxy": _meta_create_proxy, "proxy": proxy,
-            "call_module": _meta_call_module, "_in_meta_eval": False,
-            "user_leaf": user_leaf}))
-    return _META_TRACER_CLS[0](leaf_modules, forced_leaf_names)
+            "call_module": _meta_call_module, "_in_meta_eval": False}))
+    return _META_TRACER_CLS[0](leaf_modules, forced_leaf_names, keep_ops_whole)
 
 
 def _meta_call_module(self, m, forward, args, kwargs):
@@ -456,7 +467,7 @@ def _trace_with_meta(root, leaf_modules, forced, cargs, config, metas=None):
         shadow = copy.deepcopy(root).to("meta")
     except Exception:       # modules that cannot be copied are traced in place
         shadow = root
-    tracer = MetaHierTracer(leaf_modules, forced)
+    tracer = MetaHierTracer(leaf_modules, forced, bool(forced))
     with _fixed_signature(shadow):
         graph = tracer.trace(shadow, meta_args=metas, concrete_args=frozen or None)
     if any(node.op == "get_attr" and _get_submodule_or_none(root, node.target) is None
@@ -470,7 +481,7 @@ def _trace_with_meta(root, leaf_modules, forced, cargs, config, metas=None):
         if shadow is root or device.type == "meta" or n_elems > _REAL_RETRACE_LIMIT:
             raise RuntimeError("a tensor constant was created during the meta trace")
         reals = {k: torch.zeros(v.shape, dtype=v.dtype, device=device) for k, v in metas.items()}
-        tracer = MetaHierTracer(leaf_modules, forced)
+        tracer = MetaHierTracer(leaf_modules, forced, bool(forced))
         with _fixed_signature(root), torch.no_grad():
             graph = tracer.trace(root, meta_args=reals, concrete_args=frozen or None)
     return graph, frozen
@@ -480,9 +491,11 @@ def _trace_level(root: nn.Module, *, leaf_modules, flatten, recursive, concrete_
                  call_node=None, engine="pytorch", config=None):
     if isinstance(root, fx.GraphModule):
         return root
-    judge = MetaHierTracer(leaf_modules) if engine == "huggingface" else HierTracer(leaf_modules)
+    whole = not flatten
+    judge = MetaHierTracer(leaf_modules, None, whole) if engine == "huggingface" \
+        else HierTracer(leaf_modules, None, whole)
     forced = [] if flatten else _direct_child_names(root)
-    tracer = HierTracer(leaf_modules, forced)
+    tracer = HierTracer(leaf_modules, forced, whole)
     graph = None
     cargs = _fill_concrete_args(root, concrete_args, call_node)
     metas = None
@@ -510,7 +523,7 @@ def _trace_level(root: nn.Module, *, leaf_modules, flatten, recursive, concrete_
             try:
                 cargs = dict(cargs, **optional)
                 with _fixed_signature(root):
-                    graph = HierTracer(leaf_modules, forced).trace(root, concrete_args=cargs)
+                    graph = HierTracer(leaf_modules, forced, whole).trace(root, concrete_args=cargs)
                 logger.info("traced %s with optional inputs %s frozen at None",
                             type(root).__name__, sorted(optional))
             except Exception:

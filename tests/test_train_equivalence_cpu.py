@@ -206,3 +206,41 @@ def _wrn_worker(rank, world):
 
 def test_wideresnet_pipeline_training_matches_adamw():
     run_distributed(_wrn_worker, 2)
+
+
+def _meta_pipeline_worker(rank, world, name):
+    """A model built on the meta device, cut into stages, initialised by ``build``: every norm
+    weight is one and every matrix is filled, on every stage.  (Dissolved into graphs by the
+    trace, the package's fused blocks used to leave their norm weights on bare containers that
+    the model's initialiser did not recognise: they stayed zero and the model was dead.)"""
+    from slapo_b200.parallel.mesh import DeviceMesh
+
+    spec = _tiny_spec(name)
+    mesh = DeviceMesh(pp=2, dp=1, tp=world // 2)
+    slapo.set_random_seed(7, pp_rank=mesh.pp_rank, tp_rank=mesh.tp_rank)
+    with slapo.init_empty_weights():
+        model = spec.build()
+    kwargs = dict(model_config=spec.config, group=mesh.schedule_group, attn_op_name="reference",
+                  pipeline_cuts=[[], []] if spec.kind == "seq2seq" else [1])
+    sch = slapo.model_schedule.apply_schedule(model, spec.schedule_key, **kwargs)
+    engine, _ = slapo.build(sch, target="native", mesh=mesh, init_weights=model._init_weights,
+                            device="cpu", num_micro_batches=2,
+                            loss_fn=spec.loss_fn(mesh.tp_group, mesh.tp_size > 1),
+                            config={"lr": 1e-2, "clip_grad": 1.0})
+    stage = engine.inner.model
+    assert not any(p.is_meta for p in stage.parameters())
+    for pname, p in stage.named_parameters():
+        if p.dim() > 1:
+            assert float(p.abs().sum()) > 0, f"{pname} was left at zero"
+        elif pname.endswith("weight") and ("orm" in pname or "ln_" in pname):
+            torch.testing.assert_close(p.data, torch.ones_like(p), msg=f"{pname} is not one")
+    inputs, labels = spec.make_batch(4, seq=32, seq_dec=16, seed=3)
+    first = float(engine.train_batch(*inputs, labels=labels))
+    for _ in range(3):
+        last = float(engine.train_batch(*inputs, labels=labels))
+    assert last < first - 0.05          # it learns the batch
+
+
+@pytest.mark.parametrize("name", ["bert-base", "opt-350m", "t5-base"])
+def test_meta_device_model_under_pipeline_stages_is_initialised(name):
+    run_distributed(_meta_pipeline_worker, 4, name)
