@@ -184,6 +184,16 @@ def consolidate_model(sch, target=None, init_weights=True, device=None, **kwargs
             for src_param, cur in list(tie.items()):
                 if cur is old:
                     tie[src_param] = new_param
+    if my_stage is not None:
+        # A tensor tied across pipeline stages (word embedding and LM head): the stage modules
+        # of other ranks were skipped above and still name the old meta tensor.  They take the
+        # new one, so that "the same object in two stages" keeps marking the tie - the pipeline
+        # engine finds tied tensors that way, copies the first stage's value to the others and
+        # sums their gradients.
+        for _, sub in sch.named_schedules():
+            for n, old in list(sub.mod._parameters.items()):
+                if old is not None and old in done and old is not done[old]:
+                    sub.mod._parameters[n] = done[old]
     # tensors that were never on meta (e.g. index buffers) follow to the device
     for mod in top_mod.modules():
         for n, b in list(mod._buffers.items()):

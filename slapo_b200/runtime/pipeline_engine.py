@@ -234,6 +234,9 @@ class PipelineEngine:
                 w.wait()
         for p, buf in copies:
             p.data.copy_(buf)
+        if copies:
+            # the stage engine took its fp32 master copies before the values arrived
+            self.inner.refresh_master_from_params()
 
     def _sync_tied_grads(self):
         c = self.mesh.get_coord()

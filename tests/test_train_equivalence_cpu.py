@@ -229,6 +229,16 @@ def _meta_pipeline_worker(rank, world, name):
                             config={"lr": 1e-2, "clip_grad": 1.0})
     stage = engine.inner.model
     assert not any(p.is_meta for p in stage.parameters())
+    # the word embedding and the head stay tied across the stages: each rank materialised only
+    # its own copy, yet the engine knows the tie and both copies hold the first stage's values
+    import torch.distributed as dist
+
+    assert engine._tied, "the tie between the stages was lost"
+    mine = [float(p.detach().double().sum()) for p, _ in engine._tied]
+    sums = [None] * world
+    dist.all_gather_object(sums, mine)
+    tp = mesh.tp_size
+    assert sums[mesh.tp_rank] == sums[tp + mesh.tp_rank], sums
     for pname, p in stage.named_parameters():
         if p.dim() > 1:
             assert float(p.abs().sum()) > 0, f"{pname} was left at zero"
