@@ -119,11 +119,18 @@ def consolidate_model(sch, target=None, init_weights=True, device=None, **kwargs
     tie = sch.metadata.tie_weights
     mesh = kwargs.get("mesh")
     my_stage = mesh.pp_rank if (mesh is not None and mesh.pp_size > 1) else None
+    visited = set()
     for path, sub in sch.named_schedules():
         mod = sub.mod
         stage = getattr(sub, "partition_idx", None)
         if my_stage is not None and stage is not None and stage != my_stage:
             continue  # another pipeline stage owns this module: leave it unmaterialised
+        if id(mod) in visited:
+            # one module under several paths (T5's ``shared`` is also ``encoder.embed_tokens``):
+            # a second pass would take the fresh parameter for an unknown one, re-create it and
+            # so cut it loose from the tensors tied to the first
+            continue
+        visited.add(id(mod))
         own = [(n, p) for n, p in mod._parameters.items() if p is not None]
         own_bufs = [(n, b) for n, b in mod._buffers.items() if b is not None and b.is_meta]
         if not own and not own_bufs:

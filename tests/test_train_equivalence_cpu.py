@@ -254,3 +254,30 @@ def _meta_pipeline_worker(rank, world, name):
 @pytest.mark.parametrize("name", ["bert-base", "opt-350m", "t5-base"])
 def test_meta_device_model_under_pipeline_stages_is_initialised(name):
     run_distributed(_meta_pipeline_worker, 4, name)
+
+
+def _tie_worker(rank, world, name):
+    spec = _tiny_spec(name)
+    with slapo.init_empty_weights():
+        model = spec.build()
+
+    def groups(mod):
+        by_id = {}
+        for pname, p in mod.named_parameters(remove_duplicate=False):
+            by_id.setdefault(id(p), []).append(pname)
+        return sorted(sorted(v) for v in by_id.values() if len(v) > 1)
+
+    want = groups(model)
+    assert want, "the family ties its word embedding to the head"
+    sch = slapo.model_schedule.apply_schedule(model, spec.schedule_key, model_config=spec.config,
+                                              attn_op_name="reference")
+    built, _ = slapo.build(sch, init_weights=model._init_weights, device="cpu")
+    assert groups(built) == want
+
+
+@pytest.mark.parametrize("name", ["bert-base", "albert-large", "gpt2-medium", "opt-350m", "t5-base"])
+def test_meta_device_build_keeps_tied_tensors_tied(name):
+    """Two tensor-parallel ranks, model on the meta device: after ``build`` the head still
+    shares the (sharded) word embedding - also for T5, whose embedding module sits under three
+    paths of the model."""
+    run_distributed(_tie_worker, 2, name)
