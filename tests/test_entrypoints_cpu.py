@@ -102,3 +102,12 @@ def test_tune_configs_load(family):
     cfg = load_config(os.path.join(ROOT, "examples", family, "tune_cfg.py"))
     lo, hi, step = cfg.get_bs_range({"gpus": 8, "tp": 8})
     assert 1 <= lo <= hi and step >= 1
+
+
+def test_train_entry_albert_on_two_stages():
+    """The shared layer of ALBERT on both stages of a pipeline, through the training script."""
+    import bench_single_node as B
+    rec, text = B.launch("albert-large", 2, ["--pp", "2", "--micro-batches", "2"] + TINY,
+                         port=29581, timeout=600)
+    assert rec is not None, text[-3000:]
+    assert rec["pp"] == 2 and rec["samples_per_sec"] > 0 and 0 < rec["loss"] < 12
