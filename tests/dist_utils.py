@@ -1,9 +1,11 @@
 """Run a function on N CPU ranks (gloo) in child processes.
 
-``run_distributed(fn, world_size, *args)`` spawns ``world_size`` processes,
+``run_distributed(fn, world_size, *args)`` starts ``world_size`` processes,
 initialises a gloo group over a temporary file store (no sockets to resolve),
 calls ``fn(rank, world_size, *args)`` on each and re-raises the first failure.
-``fn`` must be defined at module level (it is pickled by name).
+``fn`` must be defined at module level (it is pickled by name).  CPU ranks come
+from a fork server with torch preloaded (``SLAPO_B200_TEST_SPAWN=1`` spawns them
+from scratch instead); NCCL ranks are always spawned.
 """
 import multiprocessing
 import os
