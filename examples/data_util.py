@@ -67,3 +67,33 @@ def get_dataloaders(path, seq_len, micro_batch_size, mesh=None, kind="causal", v
     if device is not None:
         t_loader, v_loader = DevicePrefetcher(t_loader, device), DevicePrefetcher(v_loader, device)
     return t_loader, v_loader, sampler
+
+
+class LossTestDataset(Dataset):
+    """``fn(entry)`` applied to every entry of ``dataset`` on access (the wrapper the
+    reference's scripts put around a tokenised dataset, examples/data_util.py:13-24 there)."""
+
+    def __init__(self, dataset, fn):
+        self.dataset, self.fn = dataset, fn
+
+    def __len__(self):
+        return len(self.dataset)
+
+    def __getitem__(self, index):
+        return self.fn(self.dataset[index])
+
+
+def get_dataloader(model_name, dataset_name, micro_batch_size, enable_pipeline=False,
+                   cache_dir=None, mpu=None, max_seq_length=1024):
+    """``(train loader, validation loader)`` under the call the reference's scripts make
+    (examples/data_util.py:27-68 there).  ``dataset_name`` is the path of a local text file
+    (nothing is downloaded: bytes are the tokens); ``model_name`` picks the objective (masked
+    language modelling for the BERT family, next-token prediction otherwise); ``mpu`` is the
+    :class:`DeviceMesh` that tells which rows this data-parallel replica reads.  ``cache_dir``
+    and ``enable_pipeline`` are accepted for compatibility: batches are ``[input_ids, labels]``
+    in both cases (``engine.train_batch(input_ids, labels=labels)``)."""
+    del cache_dir, enable_pipeline
+    kind = "mlm" if any(k in model_name.lower() for k in ("bert", "roberta", "albert")) else "causal"
+    train, val, _ = get_dataloaders(dataset_name, max_seq_length, micro_batch_size, mesh=mpu,
+                                    kind=kind)
+    return train, val

@@ -126,3 +126,22 @@ def test_hugging_face_example_script(family, pmp, tmp, world, tmp_path):
     assert len(losses) == 3 and all(0.0 < v < 7.0 for v in losses)
     if family != "t5":
         assert all(v > 5.5 for v in losses)
+
+
+def test_reference_named_data_helpers():
+    """``get_dataloader`` / ``LossTestDataset`` / ``train_with_deepspeed_engine`` exist under the
+    names the reference's example scripts import, on local data."""
+    sys.path.insert(0, os.path.join(ROOT, "examples"))
+    import data_util
+    import utils
+
+    train, val = data_util.get_dataloader("bert-large-uncased", os.path.join(ROOT, "README.md"), 2,
+                                          max_seq_length=64)
+    ids, labels = next(iter(train))
+    assert ids.shape == labels.shape == (2, 64) and (labels != -100).any()
+    ids, labels = next(iter(data_util.get_dataloader("gpt2", os.path.join(ROOT, "README.md"), 2,
+                                                     max_seq_length=64)[1]))
+    assert torch.equal(ids, labels)
+    doubled = data_util.LossTestDataset([1, 2, 3], lambda e: 2 * e)
+    assert len(doubled) == 3 and doubled[1] == 4
+    assert utils.train_with_deepspeed_engine is utils.train_with_engine
