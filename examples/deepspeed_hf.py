@@ -3,8 +3,9 @@ the example scripts of the reference are (examples/<model>/deepspeed_hf.py there
 set-up, topology and tensor-parallel group, the model built without memory under
 ``init_empty_weights``, the family's recipe with pipeline cuts, ``build(target="deepspeed",
 config=ds_config, topology=...)``, a training loop on synthetic tokens.  The ``"deepspeed"``
-target resolves to this framework's own engines, so nothing but PyTorch (and ``transformers``
-for the model definition) is needed.
+target (and ``--target megatron``, the counterpart of the reference's ``megatron_hf.py``
+scripts) resolves to this framework's own engines, so nothing but PyTorch (and
+``transformers`` for the model definition) is needed.
 
     torchrun --nnodes=1 --nproc-per-node 8 --master-addr 127.0.0.1 examples/deepspeed_hf.py \
         --family opt --hidden 2560 --layers 32 --heads 32 --pmp 2 --tmp 4 \
@@ -48,6 +49,8 @@ def parse_args(argv=None):
     ap.add_argument("--iter-nums", type=int, default=10)
     ap.add_argument("--device", default="cuda" if torch.cuda.is_available() else "cpu")
     ap.add_argument("--seed", type=int, default=2013)
+    ap.add_argument("--target", default="deepspeed", choices=("deepspeed", "megatron", "native"),
+                    help="runtime dialect named in build(); all three run the native engines")
     return ap.parse_args(argv)
 
 
@@ -145,7 +148,8 @@ def train(args):
     if args.pmp == 1:
         ds_config["gradient_accumulation_steps"] = micro_batches
     # weights are created here, shard by shard, on the device (the model was built empty)
-    engine, _ = slapo.build(sch, target="deepspeed", config=ds_config, topology=topology,
+    engine, _ = slapo.build(sch, target=args.target, config=ds_config,
+                            **({"mesh": mesh} if args.target == "native" else {"topology": topology}),
                             loss_fn=loss_fn, init_weights=model._init_weights, device=device,
                             **({"num_micro_batches": micro_batches} if args.pmp > 1 else {}))
 

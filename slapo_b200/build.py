@@ -225,7 +225,7 @@ def build(sch, target=None, init_weights=True, **kwargs):
     from .pipeline import analyze_tie_weights, build_pipeline_model, generate_pipeline_partition
 
     cuts = sch.metadata.primitives.get("cut_pipeline_stage") or []
-    mesh = kwargs.get("mesh")
+    mesh = kwargs.get("mesh") if kwargs.get("mesh") is not None else kwargs.get("topology")
     if not cuts and target is not None and getattr(mesh, "pp_size", 1) > 1:
         raise ValueError(
             f"the mesh has {mesh.pp_size} pipeline stages but the schedule has no "
