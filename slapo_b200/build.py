@@ -117,8 +117,9 @@ def consolidate_model(sch, target=None, init_weights=True, device=None, **kwargs
 
     done = {}  # old param -> new param (keeps tied weights tied)
     tie = sch.metadata.tie_weights
-    mesh = kwargs.get("mesh")
-    my_stage = mesh.pp_rank if (mesh is not None and mesh.pp_size > 1) else None
+    mesh = kwargs.get("mesh") if kwargs.get("mesh") is not None else kwargs.get("topology")
+    # (a topology object of another kind has no pp_rank: every stage is materialised then)
+    my_stage = getattr(mesh, "pp_rank", None) if getattr(mesh, "pp_size", 1) > 1 else None
     visited = set()
     for path, sub in sch.named_schedules():
         mod = sub.mod
